@@ -1,0 +1,391 @@
+/*
+ * dflash_b200 — C ABI of the B200 (sm_100a) DFlash speculative-decoding step.
+ *
+ * Every entry point replaces one call the reference engine (brittlewis12/qwen-llm)
+ * makes from Rust into its Metal backend; the reference item is cited beside each
+ * declaration as `crate-relative path:line`.  Conventions, mirroring
+ * crates/qwen-llm/src/metal_dflash.rs:2698-2732 (DFlashError) and
+ * crates/qwen-llm/src/metal/completion.rs:18 (checked waits):
+ *
+ *   - every function returns a dfl_status (0 == success); nothing throws across
+ *     the boundary; dfl_last_error() gives the text of the calling thread's last
+ *     failure;
+ *   - handles are opaque; weights are immutable and shareable, a session /
+ *     drafter session / scratch is exclusively owned by the caller for the
+ *     duration of a call (one caller thread per session);
+ *   - calls are synchronous: they return after the device work completed and its
+ *     status was checked, so host outputs are valid on return;
+ *   - a failed route status or device error poisons the session
+ *     (crates/qwen-llm/src/metal_forward/mod.rs:2161-2170): later calls fail with
+ *     DFL_ERR_POISONED;
+ *   - there is no CPU fallback: without a CUDA device compute calls fail with
+ *     DFL_ERR_NO_DEVICE.
+ */
+#ifndef DFLASH_B200_H
+#define DFLASH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum dfl_status {
+    DFL_OK = 0,
+    DFL_ERR_BAD_ARG = 1,       /* null pointer, out-of-range scalar */
+    DFL_ERR_BAD_SHAPE = 2,     /* DFlashError::BadShape{kernel,detail} */
+    DFL_ERR_UNSUPPORTED = 3,   /* dtype / geometry the kernels do not cover */
+    DFL_ERR_CUDA = 4,          /* a CUDA runtime call or a kernel failed */
+    DFL_ERR_NO_DEVICE = 5,     /* no usable CUDA device: compute refused */
+    DFL_ERR_OOM = 6,
+    DFL_ERR_POISONED = 7,      /* session poisoned by an earlier failure */
+    DFL_ERR_CTX_OVERFLOW = 8,  /* DFlashError::CtxOverflow, metal_dflash.rs:5666 */
+    DFL_ERR_KV_STATE = 9,      /* kv_n_pos / capacity guard wall, metal_dflash.rs:9079-9186 */
+    DFL_ERR_BAD_TOKEN = 10,    /* ForwardError::BadToken, forward.rs:24 */
+    DFL_ERR_SAMPLING = 11,     /* SamplingError / DFlashAcceptError */
+    DFL_ERR_TIMEOUT = 12,      /* a bounded device-side wait gave up */
+    DFL_ERR_MISSING_TENSOR = 13
+} dfl_status;
+
+/* ggml type ids (crates/qwen-llm/src/tensor.rs:159 `storage_layout`). */
+typedef enum dfl_dtype {
+    DFL_F32 = 0,
+    DFL_F16 = 1,
+    DFL_Q8_0 = 8,   /* 34 B / 32 weights  */
+    DFL_Q4_K = 12,  /* 144 B / 256 weights */
+    DFL_Q5_K = 13,  /* 176 B / 256 weights */
+    DFL_Q6_K = 14,  /* 210 B / 256 weights */
+    DFL_BF16 = 30
+} dfl_dtype;
+
+/* One named tensor in ggml storage order (ne[0] fastest).  Mirrors TensorDesc,
+ * crates/qwen-llm/src/tensor.rs.  `data` is a host pointer unless
+ * `on_device` != 0, in which case it is a device pointer on the model's GPU. */
+typedef struct dfl_tensor {
+    const char* name;
+    int32_t dtype;       /* dfl_dtype */
+    int32_t n_dims;      /* 1..3 */
+    uint64_t shape[4];   /* ne[0..n_dims) */
+    const void* data;
+    uint64_t n_bytes;
+    int32_t on_device;
+    int32_t _pad;
+} dfl_tensor;
+
+/* Architecture of the hybrid target.  Mirrors `Arch`,
+ * crates/qwen-llm/src/model.rs:40-70. */
+typedef struct dfl_arch {
+    uint32_t n_layer;
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t vocab_size;
+    uint32_t full_attention_interval;
+    uint32_t n_q_heads;
+    uint32_t n_kv_heads;
+    uint32_t attn_head_dim;
+    float rope_theta;
+    float partial_rotary_factor;
+    uint32_t gdn_n_v_heads;
+    uint32_t gdn_n_k_heads;
+    uint32_t gdn_head_dim;
+    uint32_t gdn_conv_kernel;
+    uint32_t expert_count;                       /* 0 on dense models */
+    uint32_t expert_used_count;
+    uint32_t expert_feed_forward_length;
+    uint32_t expert_shared_feed_forward_length;
+} dfl_arch;
+
+#define DFL_MAX_TARGET_LAYERS 8
+#define DFL_MAX_BLOCK 16
+#define DFL_MAX_DRAFTER_LAYERS 16
+
+/* Drafter description.  Mirrors `DFlashConfig` + `DFlashHead.target_layer_ids` +
+ * per-layer `is_swa`, crates/qwen-llm/src/loader.rs:340-409. */
+typedef struct dfl_dflash_config {
+    uint32_t n_layer;
+    uint32_t hidden_size;
+    uint32_t intermediate_size;
+    uint32_t n_q_heads;
+    uint32_t n_kv_heads;
+    uint32_t head_dim;
+    float rope_theta;
+    float rms_norm_eps;
+    uint32_t causal;
+    uint32_t swa_window;
+    uint32_t block_size;
+    int32_t mask_token_id;
+    uint32_t n_target_layers;                          /* K */
+    uint32_t target_layer_ids[DFL_MAX_TARGET_LAYERS];
+    uint32_t layer_is_swa[DFL_MAX_DRAFTER_LAYERS];
+} dfl_dflash_config;
+
+typedef struct dfl_model dfl_model;       /* MetalModel          metal_forward/mod.rs:443  */
+typedef struct dfl_session dfl_session;   /* MetalSession        metal_forward/mod.rs:2095 */
+typedef struct dfl_drafter dfl_drafter;   /* MetalDFlashHead     metal_dflash.rs:4944      */
+typedef struct dfl_dsession dfl_dsession; /* MetalDFlashSession  metal_dflash.rs:5492      */
+typedef struct dfl_scratch dfl_scratch;   /* MetalDFlashVerifyScratch + LayerMajorScratch
+                                             metal_dflash.rs:6003, :8025                   */
+typedef struct dfl_qmatrix dfl_qmatrix;   /* one resident quantised matrix (MetalTensor)   */
+typedef struct dfl_sampler dfl_sampler;   /* Sampler             sampling.rs:305           */
+
+/* ---- library / diagnostics --------------------------------------------- */
+const char* dfl_version(void);
+const char* dfl_last_error(void);
+/* Number of usable CUDA devices (0 when the driver or a device is missing). */
+int32_t dfl_device_count(void);
+/* Kernel launches this library issued on the calling process since load. */
+uint64_t dfl_launch_count(void);
+
+/* ---- few-row quantised GEMM (the weight-streaming hot kernel) ----------
+ * Replaces encode_mat_mat_dispatch / kernel_mat_mat_*_fewrow_gen,
+ * crates/qwen-llm/src/metal_forward/dispatch.rs:345-433,
+ * kernels/mat_mat_fewrow_gen.metal:374-474.
+ * W is row-major [n_out][n_in] in ggml blocks; y[r, o] = sum_i x[r, i] W[o, i]. */
+dfl_status dfl_qmatrix_create(int32_t device, int32_t dtype, uint64_t n_in, uint64_t n_out,
+                              const void* data, uint64_t n_bytes, int32_t on_device,
+                              dfl_qmatrix** out);
+void dfl_qmatrix_destroy(dfl_qmatrix* m);
+/* Decode the resident (re-tiled) matrix back to f32 [n_out][n_in] on the host:
+ * proves the integer unpack equals ggml's (codec.rs:287 dequant_to_f32). */
+dfl_status dfl_qmatrix_dequant(const dfl_qmatrix* m, float* out_host, uint64_t n_floats);
+/* x_host [n_rows][n_in] f32, y_host [n_rows][n_out] f32, 1 <= n_rows <= 16. */
+dfl_status dfl_fewrow_matmul(const dfl_qmatrix* m, const float* x_host, int32_t n_rows,
+                             float* y_host);
+/* Row argmax with lowest-index ties and (top1 - top2) gap; replaces
+ * encode_argmax_top2_f32, kernels/elementwise.metal:1231-1286. */
+dfl_status dfl_argmax_top2(int32_t device, const float* logits_host, int32_t n_rows,
+                           uint64_t vocab, int32_t* argmax_out, float* gap_out);
+
+/* ---- BASELINE config 1: two chained few-row GEMMs + greedy acceptance ---
+ * logits = head(x W1^T); argmax per row; greedy prefix accept against drafts.
+ * Device-resident pipeline object so the timed region has no allocation. */
+typedef struct dfl_c1 dfl_c1;
+dfl_status dfl_c1_create(const dfl_qmatrix* w1, const dfl_qmatrix* head, dfl_c1** out);
+void dfl_c1_destroy(dfl_c1* p);
+/* Host-to-host call: copies x in, runs both GEMMs + argmax, copies results out.
+ * logits_host may be NULL.  n_accepted = longest j with draft[j]==argmax[j]. */
+dfl_status dfl_c1_step(dfl_c1* p, const float* x_host, int32_t n_rows, const int32_t* draft_ids,
+                       int32_t* argmax_out, float* gap_out, int32_t* n_accepted,
+                       float* logits_host);
+/* Same work with x already resident (uploaded by dfl_c1_upload); returns the
+ * device time of the kernels alone in milliseconds (CUDA events). */
+dfl_status dfl_c1_upload(dfl_c1* p, const float* x_host, int32_t n_rows);
+dfl_status dfl_c1_run_resident(dfl_c1* p, int32_t n_rows, int32_t iters, float* ms_total);
+
+/* ---- model / drafter / sessions ---------------------------------------- */
+/* MetalModel::load  metal_forward/mod.rs:443-454 (tensor names follow
+ * crates/qwen-llm/src/loader.rs:438-611). */
+dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors,
+                            uint64_t n_tensors, dfl_model** out);
+void dfl_model_destroy(dfl_model* m);
+/* Bytes of quantised weights one verify step streams (the roofline numerator). */
+uint64_t dfl_model_verify_weight_bytes(const dfl_model* m);
+
+/* MetalDFlashHead::load  metal_dflash.rs:4944-5050 (names loader.rs:1179-1230). */
+dfl_status dfl_drafter_create(const dfl_model* target, const dfl_dflash_config* cfg,
+                              const dfl_tensor* tensors, uint64_t n_tensors, dfl_drafter** out);
+void dfl_drafter_destroy(dfl_drafter* d);
+uint64_t dfl_drafter_weight_bytes(const dfl_drafter* d);
+
+/* MetalSession::fresh(ctx, model, kv_capacity)  metal_forward/mod.rs:2238-2391.
+ * kv_f16 != 0 stores K/V as fp16 (the reference GPU layout, mod.rs:2330-2341);
+ * 0 stores f32 (the CPU oracle's layout, forward.rs:1142-1151). */
+dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t kv_f16,
+                              dfl_session** out);
+void dfl_session_destroy(dfl_session* s);
+uint32_t dfl_session_kv_n_pos(const dfl_session* s);
+int32_t dfl_session_poisoned(const dfl_session* s);
+/* Test hook mirroring completion::fail_next_completion_check
+ * (metal/completion.rs:41-66): the next completion check on this session
+ * reports failure without touching the GPU. */
+void dfl_session_fail_next_completion(dfl_session* s);
+/* Read back recurrent state for bitwise comparisons (tests.rs:7049-7094). */
+dfl_status dfl_session_read_gdn_state(const dfl_session* s, uint32_t gdn_index, float* ssm_out,
+                                      uint64_t n_ssm, float* conv_out, uint64_t n_conv);
+dfl_status dfl_session_read_kv(const dfl_session* s, uint32_t attn_index, uint32_t pos,
+                               float* k_out, float* v_out, uint64_t n);
+
+/* MetalDFlashVerifyScratch::fresh + MetalDFlashLayerMajorScratch::fresh
+ * metal_dflash.rs:6003-6075, :8025. */
+dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t n_capture_layers,
+                              dfl_scratch** out);
+void dfl_scratch_destroy(dfl_scratch* s);
+
+/* encode_packed_verify_layer_major_inner  metal_dflash.rs:10696-10719.
+ * tokens[n] = [carry, drafts...]; requires kv_n_pos == start_position and
+ * start_position + n <= kv_capacity.  Writes argmax_out[n], gap_out[n]
+ * (top1 - top2), optional logits_host[n * vocab]; captures hidden rows of
+ * `layer_ids` into the scratch as [n][k][H]. */
+dfl_status dfl_packed_verify(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
+                             const uint32_t* layer_ids, uint32_t n_layer_ids,
+                             const int32_t* tokens, uint32_t n, uint32_t start_position,
+                             int32_t* argmax_out, float* gap_out, float* logits_host);
+/* Copy captured hidden rows [n][k][H] of the last verify to the host. */
+dfl_status dfl_scratch_read_capture(const dfl_scratch* sc, uint32_t n, float* out_host,
+                                    uint64_t n_floats);
+
+/* encode_restore_after_partial_accept_inner  metal_dflash.rs:15649-15777:
+ * n_keep in [1, n]; GDN state / conv := state after n_keep tokens of the last
+ * verify block; kv_n_pos := start_position + n_keep. */
+dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
+                               uint32_t n_keep, uint32_t start_position);
+/* encode_restore_to_pre_block  metal_dflash.rs:15789. */
+dfl_status dfl_restore_pre_block(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
+                                 uint32_t start_position);
+
+/* MetalForward::single_token_with_multi_hidden  metal_forward/token.rs:984. */
+dfl_status dfl_single_token(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
+                            const uint32_t* layer_ids, uint32_t n_layer_ids, int32_t token,
+                            uint32_t position, float* logits_host, float* hidden_host);
+/* prefill_tokens_with_multi_hidden  metal_dflash.rs:10779-10787: feeds ids in
+ * blocks of <=16 through the verify path; hidden_host (optional) [n][k][H];
+ * last_logits_host (optional) [vocab]. */
+dfl_status dfl_prefill(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
+                       const uint32_t* layer_ids, uint32_t n_layer_ids, const int32_t* ids,
+                       uint64_t n, uint32_t start_position, dfl_dsession* feed_drafter,
+                       float* hidden_host, float* last_logits_host);
+
+/* MetalDFlashSession::fresh(ctx, head, target_h, vocab, ctx_capacity)
+ * metal_dflash.rs:5492. */
+dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_dsession** out);
+void dfl_dsession_destroy(dfl_dsession* ds);
+uint32_t dfl_dsession_ctx_len(const dfl_dsession* ds);
+/* append_target_ctx_columns_now  metal_dflash.rs:5798-5816: append `count`
+ * columns of K*H f32 from the host (cols_host != NULL) ... */
+dfl_status dfl_dsession_append_columns_host(dfl_dsession* ds, const float* cols_host,
+                                            const uint32_t* positions, uint32_t count);
+/* ... or rows [first_row, first_row+count) of the last verify capture. */
+dfl_status dfl_dsession_append_from_scratch(dfl_dsession* ds, const dfl_scratch* sc,
+                                            uint32_t first_row, uint32_t count,
+                                            uint32_t first_position);
+/* Drop all context columns (new request). */
+dfl_status dfl_dsession_reset(dfl_dsession* ds);
+
+/* DFlashDecoder::draft_block(carry, noise_start_pos) -> [N] tokens
+ * metal_dflash.rs:15915; `_with_logits` :17499.  out_tokens[0] = carry,
+ * out_tokens[1..N) = per-row argmax; logits_host optional [N * vocab]. */
+dfl_status dfl_draft_block(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos,
+                           int32_t* out_tokens, float* logits_host);
+
+/* ---- sampling + acceptance (host, f64) --------------------------------- */
+typedef struct dfl_sampling_config { /* SamplingConfig  sampling.rs:17-30 */
+    float temperature;
+    uint32_t top_k;
+    float top_p;
+    float min_p;
+    uint64_t seed;
+} dfl_sampling_config;
+
+dfl_status dfl_sampler_create(const dfl_sampling_config* cfg, dfl_sampler** out);
+/* Sampler::at_draw  sampling.rs:359 */
+dfl_status dfl_sampler_create_at_draw(const dfl_sampling_config* cfg, uint64_t draws,
+                                      dfl_sampler** out);
+void dfl_sampler_destroy(dfl_sampler* s);
+uint64_t dfl_sampler_draws(const dfl_sampler* s);
+void dfl_sampler_rng_state(const dfl_sampler* s, uint64_t out_state[4]);
+/* Sampler::sample  sampling.rs:530 */
+dfl_status dfl_sampler_sample(dfl_sampler* s, const float* logits, uint64_t vocab,
+                              int32_t* token_out, uint64_t* candidate_index_out);
+/* greedy_token  sampling.rs:1159-1181 */
+dfl_status dfl_greedy_token(const float* logits, uint64_t vocab, int32_t* token_out);
+/* raw generator access for golden-vector checks (sampling.rs:1621-1670) */
+uint64_t dfl_splitmix64_next(uint64_t* state);
+uint64_t dfl_sampler_next_u64(dfl_sampler* s);
+double dfl_sampler_next_unit_f64(dfl_sampler* s);
+
+/* SparseProposal rows, flattened: row r owns candidates
+ * [cand_offsets[r], cand_offsets[r+1]).  sampling.rs:185-197. */
+typedef struct dfl_sparse_proposals {
+    uint32_t n_rows;
+    const int32_t* tokens;        /* [n_rows] sampled proposal token per row */
+    const uint32_t* cand_offsets; /* [n_rows + 1] */
+    const int32_t* cand_tokens;
+    const double* cand_weights;
+} dfl_sparse_proposals;
+
+enum { DFL_CARRY_NONE = 0, DFL_CARRY_CORRECTION = 1, DFL_CARRY_BONUS = 2 };
+enum { DFL_STOP_NONE = 0, DFL_STOP_EOS = 1, DFL_STOP_TOKEN_LIMIT = 2 };
+
+typedef struct dfl_accept_decision { /* DFlashAcceptDecision  accept.rs:17-32 */
+    uint32_t n_accepted;
+    int32_t accepted_drafts[DFL_MAX_BLOCK];
+    int32_t next_carry_kind;
+    int32_t next_carry;
+    int32_t stop_reason;
+    uint32_t retain_input_count;
+    int32_t error_row; /* row of a Sampling error, else -1 */
+} dfl_accept_decision;
+
+/* decide_dflash_accept_prefix  metal_dflash/accept.rs:76-183.  On any error the
+ * sampler is left unchanged. */
+dfl_status dfl_accept_prefix(const int32_t* verified_tokens, uint32_t n_tokens,
+                             const float* target_logits, uint64_t n_logits, uint64_t vocab,
+                             const dfl_sparse_proposals* proposals /* NULL = deterministic */,
+                             dfl_sampler* sampler, uint64_t remaining_output_budget,
+                             const int32_t* stop_ids, uint32_t n_stop_ids,
+                             dfl_accept_decision* out);
+/* Sampler::couple_sparse_proposal  sampling.rs:708-790; decision 1 = accepted,
+ * 0 = rejected with *correction set. */
+dfl_status dfl_sampler_couple_sparse(dfl_sampler* s, const float* logits, uint64_t vocab,
+                                     int32_t proposal_token, const int32_t* cand_tokens,
+                                     const double* cand_weights, uint32_t n_cand,
+                                     int32_t* accepted, int32_t* correction);
+
+/* ---- the outer loop ----------------------------------------------------- */
+typedef struct dfl_generate_params {
+    uint32_t max_tokens;
+    const int32_t* stop_ids;
+    uint32_t n_stop_ids;
+    /* "replayed drafts" (dflash_prefix_replay_drafts, qwen/dflash.rs:351-376):
+     * when non-NULL the drafter is bypassed and drafts are taken from this
+     * history wherever it agrees with what was emitted. */
+    const int32_t* replay_history;
+    uint32_t n_replay_history;
+    /* sampled mode: build sparse proposals from the drafter's top-16
+     * (draft_block_sampled, metal_dflash.rs:17268-17415) instead of one-hot. */
+    int32_t sparse_proposals;
+    /* margin guard (qwen/dflash.rs:93-121): committed rows with gap < margin are
+     * replayed through single-token steps.  0 disables. */
+    float verify_margin;
+} dfl_generate_params;
+
+typedef struct dfl_generate_stats { /* DflashDecodeStats  qwen/dflash.rs:380-418 */
+    uint32_t spec_steps;
+    uint32_t drafter_calls;
+    uint32_t verify_calls;
+    uint32_t restore_calls;
+    uint32_t fallback_steps;
+    uint64_t drafts_scored;
+    uint64_t accepted_drafts;
+    uint64_t tokens_emitted;
+    double draft_ms;    /* device time, CUDA events */
+    double verify_ms;
+    double restore_ms;
+    double accept_ms;   /* host */
+    double append_ms;
+    double wall_ms;
+} dfl_generate_stats;
+
+/* generate_dflash  crates/qwen-cli/src/qwen/dflash.rs:484-1263.  `first_logits`
+ * [vocab] are the logits of the last prompt position; tokens_out has room for
+ * max_tokens ids; *n_out receives the count. */
+dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl_dsession* ds,
+                        dfl_sampler* sampler, const float* first_logits,
+                        const dfl_generate_params* params, int32_t* tokens_out, uint32_t* n_out,
+                        dfl_generate_stats* stats);
+
+/* ---- synthetic weights (no reference counterpart: the reference loads GGUF
+ * files; benchmarks here use seeded N(0, std) weights quantised on the GPU) -- */
+/* Fills a device buffer with a [n_out][n_in] tensor of `dtype` in ggml block
+ * layout from a counter-based generator; *dev_ptr must be freed with
+ * dfl_device_free. */
+dfl_status dfl_synth_tensor(int32_t device, int32_t dtype, uint64_t n_in, uint64_t n_out,
+                            uint64_t seed, float std_dev, void** dev_ptr, uint64_t* n_bytes);
+dfl_status dfl_device_free(int32_t device, void* dev_ptr);
+dfl_status dfl_device_to_host(int32_t device, const void* dev_ptr, void* host, uint64_t n_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DFLASH_B200_H */
