@@ -1,0 +1,204 @@
+"""Host-side Python mirror of the dflash_b200 C ABI (include/dflash_b200.h).
+
+The package is a thin ctypes layer: every call goes through the `extern "C"` entry
+points of libdflash_b200.so, the same ones a Rust/cgo/JNI binding would use.  There is
+no CPU fallback: if the CUDA library has not been built, importing a compute symbol
+raises; if no GPU is present the library returns DFL_ERR_NO_DEVICE.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libdflash_b200.so")
+
+F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 12, 13, 14, 30
+MAX_BLOCK = 16
+MAX_TARGET_LAYERS = 8
+MAX_DRAFTER_LAYERS = 16
+
+STATUS_NAMES = {0: "OK", 1: "BAD_ARG", 2: "BAD_SHAPE", 3: "UNSUPPORTED", 4: "CUDA", 5: "NO_DEVICE", 6: "OOM", 7: "POISONED",
+                8: "CTX_OVERFLOW", 9: "KV_STATE", 10: "BAD_TOKEN", 11: "SAMPLING", 12: "TIMEOUT", 13: "MISSING_TENSOR"}
+
+
+class DflError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"DFL_ERR_{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+        self.name = STATUS_NAMES.get(status, str(status))
+
+
+class Tensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int32), ("n_dims", C.c_int32), ("shape", C.c_uint64 * 4),
+                ("data", C.c_void_p), ("n_bytes", C.c_uint64), ("on_device", C.c_int32), ("_pad", C.c_int32)]
+
+
+class Arch(C.Structure):
+    _fields_ = [("n_layer", C.c_uint32), ("hidden_size", C.c_uint32), ("intermediate_size", C.c_uint32),
+                ("vocab_size", C.c_uint32), ("full_attention_interval", C.c_uint32), ("n_q_heads", C.c_uint32),
+                ("n_kv_heads", C.c_uint32), ("attn_head_dim", C.c_uint32), ("rope_theta", C.c_float),
+                ("partial_rotary_factor", C.c_float), ("gdn_n_v_heads", C.c_uint32), ("gdn_n_k_heads", C.c_uint32),
+                ("gdn_head_dim", C.c_uint32), ("gdn_conv_kernel", C.c_uint32), ("expert_count", C.c_uint32),
+                ("expert_used_count", C.c_uint32), ("expert_feed_forward_length", C.c_uint32),
+                ("expert_shared_feed_forward_length", C.c_uint32)]
+
+
+class DFlashConfig(C.Structure):
+    _fields_ = [("n_layer", C.c_uint32), ("hidden_size", C.c_uint32), ("intermediate_size", C.c_uint32),
+                ("n_q_heads", C.c_uint32), ("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("rope_theta", C.c_float),
+                ("rms_norm_eps", C.c_float), ("causal", C.c_uint32), ("swa_window", C.c_uint32), ("block_size", C.c_uint32),
+                ("mask_token_id", C.c_int32), ("n_target_layers", C.c_uint32),
+                ("target_layer_ids", C.c_uint32 * MAX_TARGET_LAYERS), ("layer_is_swa", C.c_uint32 * MAX_DRAFTER_LAYERS)]
+
+
+class SamplingConfig(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("min_p", C.c_float),
+                ("seed", C.c_uint64)]
+
+
+class SparseProposals(C.Structure):
+    _fields_ = [("n_rows", C.c_uint32), ("tokens", C.POINTER(C.c_int32)), ("cand_offsets", C.POINTER(C.c_uint32)),
+                ("cand_tokens", C.POINTER(C.c_int32)), ("cand_weights", C.POINTER(C.c_double))]
+
+
+class AcceptDecision(C.Structure):
+    _fields_ = [("n_accepted", C.c_uint32), ("accepted_drafts", C.c_int32 * MAX_BLOCK), ("next_carry_kind", C.c_int32),
+                ("next_carry", C.c_int32), ("stop_reason", C.c_int32), ("retain_input_count", C.c_uint32),
+                ("error_row", C.c_int32)]
+
+
+class GenerateParams(C.Structure):
+    _fields_ = [("max_tokens", C.c_uint32), ("stop_ids", C.POINTER(C.c_int32)), ("n_stop_ids", C.c_uint32),
+                ("replay_history", C.POINTER(C.c_int32)), ("n_replay_history", C.c_uint32), ("sparse_proposals", C.c_int32),
+                ("verify_margin", C.c_float)]
+
+
+class GenerateStats(C.Structure):
+    _fields_ = [("spec_steps", C.c_uint32), ("drafter_calls", C.c_uint32), ("verify_calls", C.c_uint32),
+                ("restore_calls", C.c_uint32), ("fallback_steps", C.c_uint32), ("drafts_scored", C.c_uint64),
+                ("accepted_drafts", C.c_uint64), ("tokens_emitted", C.c_uint64), ("draft_ms", C.c_double),
+                ("verify_ms", C.c_double), ("restore_ms", C.c_double), ("accept_ms", C.c_double), ("append_ms", C.c_double),
+                ("wall_ms", C.c_double)]
+
+
+_LIB = None
+
+
+def lib():
+    """The loaded C ABI.  Raises if the CUDA library was not built (no fallback)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python qwen-llm_b200/build.py` (needs nvcc). "
+                              "There is no CPU implementation to fall back to.")
+        L = C.CDLL(LIB_PATH)
+        L.dfl_version.restype = C.c_char_p
+        L.dfl_last_error.restype = C.c_char_p
+        L.dfl_device_count.restype = C.c_int32
+        L.dfl_launch_count.restype = C.c_uint64
+        for name in ("dfl_model_verify_weight_bytes", "dfl_drafter_weight_bytes", "dfl_sampler_draws",
+                     "dfl_splitmix64_next", "dfl_sampler_next_u64"):
+            if hasattr(L, name):
+                getattr(L, name).restype = C.c_uint64
+        for name in ("dfl_session_kv_n_pos", "dfl_dsession_ctx_len"):
+            if hasattr(L, name):
+                getattr(L, name).restype = C.c_uint32
+        if hasattr(L, "dfl_sampler_next_unit_f64"):
+            L.dfl_sampler_next_unit_f64.restype = C.c_double
+        _LIB = L
+    return _LIB
+
+
+def check(status):
+    if status != 0:
+        raise DflError(status, lib().dfl_last_error().decode(errors="replace"))
+
+
+def _ptr(a, t=C.c_void_p):
+    return a.ctypes.data_as(t)
+
+
+def device_count():
+    return int(lib().dfl_device_count())
+
+
+def launch_count():
+    return int(lib().dfl_launch_count())
+
+
+class QMatrix:
+    """A resident quantised matrix W[n_out][n_in] (ggml bytes in, stream tiles on the GPU)."""
+
+    def __init__(self, dtype, n_in, n_out, raw, device=0):
+        raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        self.dtype, self.n_in, self.n_out, self.device = dtype, n_in, n_out, device
+        self.h = C.c_void_p()
+        check(lib().dfl_qmatrix_create(C.c_int32(device), C.c_int32(dtype), C.c_uint64(n_in), C.c_uint64(n_out), _ptr(raw),
+                                       C.c_uint64(raw.size), C.c_int32(0), C.byref(self.h)))
+
+    def close(self):
+        if self.h:
+            lib().dfl_qmatrix_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def dequant(self):
+        out = np.zeros((self.n_out, self.n_in), dtype=np.float32)
+        check(lib().dfl_qmatrix_dequant(self.h, _ptr(out), C.c_uint64(out.size)))
+        return out
+
+    def matmul(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.n_in)
+        y = np.zeros((x.shape[0], self.n_out), dtype=np.float32)
+        check(lib().dfl_fewrow_matmul(self.h, _ptr(x), C.c_int32(x.shape[0]), _ptr(y)))
+        return y
+
+
+def argmax_top2(logits, device=0):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    n, v = logits.shape
+    am = np.zeros(n, dtype=np.int32)
+    gap = np.zeros(n, dtype=np.float32)
+    check(lib().dfl_argmax_top2(C.c_int32(device), _ptr(logits), C.c_int32(n), C.c_uint64(v), _ptr(am), _ptr(gap)))
+    return am, gap
+
+
+class C1Pipeline:
+    """BASELINE config 1: logits = head(x W1^T), row argmax, greedy prefix acceptance."""
+
+    def __init__(self, w1: QMatrix, head: QMatrix):
+        self.w1, self.head = w1, head
+        self.h = C.c_void_p()
+        check(lib().dfl_c1_create(w1.h, head.h, C.byref(self.h)))
+
+    def close(self):
+        if self.h:
+            lib().dfl_c1_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def step(self, x, draft_ids, want_logits=False):
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.w1.n_in)
+        n = x.shape[0]
+        draft = np.ascontiguousarray(draft_ids, dtype=np.int32)
+        am = np.zeros(n, dtype=np.int32)
+        gap = np.zeros(n, dtype=np.float32)
+        nacc = C.c_int32(0)
+        logits = np.zeros((n, self.head.n_out), dtype=np.float32) if want_logits else None
+        check(lib().dfl_c1_step(self.h, _ptr(x), C.c_int32(n), _ptr(draft), _ptr(am), _ptr(gap), C.byref(nacc),
+                                _ptr(logits) if want_logits else None))
+        return am, gap, int(nacc.value), logits
+
+    def upload(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.w1.n_in)
+        check(lib().dfl_c1_upload(self.h, _ptr(x), C.c_int32(x.shape[0])))
+
+    def run_resident(self, n_rows, iters):
+        ms = C.c_float(0)
+        check(lib().dfl_c1_run_resident(self.h, C.c_int32(n_rows), C.c_int32(iters), C.byref(ms)))
+        return float(ms.value)
