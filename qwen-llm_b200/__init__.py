@@ -202,3 +202,132 @@ class C1Pipeline:
         ms = C.c_float(0)
         check(lib().dfl_c1_run_resident(self.h, C.c_int32(n_rows), C.c_int32(iters), C.byref(ms)))
         return float(ms.value)
+
+
+# ---------------------------------------------------------------------------
+# model / session / scratch
+# ---------------------------------------------------------------------------
+def make_tensor_table(tensors):
+    """tensors: list of (name, dtype, shape(list, ne[0] first), numpy uint8 bytes). Returns (ctypes array, keepalive)."""
+    arr = (Tensor * len(tensors))()
+    keep = []
+    for i, (name, dtype, shape, raw) in enumerate(tensors):
+        raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        nm = name.encode()
+        keep.append((nm, raw))
+        arr[i].name = nm
+        arr[i].dtype = dtype
+        arr[i].n_dims = len(shape)
+        for j, d in enumerate(shape):
+            arr[i].shape[j] = d
+        arr[i].data = raw.ctypes.data
+        arr[i].n_bytes = raw.size
+        arr[i].on_device = 0
+    return arr, keep
+
+
+class Model:
+    def __init__(self, arch: Arch, tensors, device=0):
+        arr, keep = make_tensor_table(tensors)
+        self.arch, self.device = arch, device
+        self.h = C.c_void_p()
+        check(lib().dfl_model_create(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(tensors)), C.byref(self.h)))
+
+    def verify_weight_bytes(self):
+        return int(lib().dfl_model_verify_weight_bytes(self.h))
+
+    def close(self):
+        if self.h:
+            lib().dfl_model_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class Session:
+    def __init__(self, model: Model, kv_capacity, kv_f16=True):
+        self.model = model
+        self.h = C.c_void_p()
+        check(lib().dfl_session_create(model.h, C.c_uint32(kv_capacity), C.c_int32(1 if kv_f16 else 0), C.byref(self.h)))
+
+    @property
+    def kv_n_pos(self):
+        return int(lib().dfl_session_kv_n_pos(self.h))
+
+    @property
+    def poisoned(self):
+        return bool(lib().dfl_session_poisoned(self.h))
+
+    def fail_next_completion(self):
+        lib().dfl_session_fail_next_completion(self.h)
+
+    def read_gdn_state(self, gdn_index):
+        a = self.model.arch
+        ssm = np.zeros(a.gdn_n_v_heads * 128 * 128, dtype=np.float32)
+        conv = np.zeros(3 * (2 * a.gdn_n_k_heads + a.gdn_n_v_heads) * 128, dtype=np.float32)
+        check(lib().dfl_session_read_gdn_state(self.h, C.c_uint32(gdn_index), _ptr(ssm), C.c_uint64(ssm.size), _ptr(conv),
+                                               C.c_uint64(conv.size)))
+        return ssm, conv
+
+    def read_kv(self, attn_index, pos):
+        a = self.model.arch
+        n = a.n_kv_heads * a.attn_head_dim
+        k = np.zeros(n, dtype=np.float32)
+        v = np.zeros(n, dtype=np.float32)
+        check(lib().dfl_session_read_kv(self.h, C.c_uint32(attn_index), C.c_uint32(pos), _ptr(k), _ptr(v), C.c_uint64(n)))
+        return k, v
+
+    def close(self):
+        if self.h:
+            lib().dfl_session_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class Scratch:
+    def __init__(self, model: Model, block_size=16, n_capture_layers=0):
+        self.model, self.block_size, self.k = model, block_size, max(1, n_capture_layers)
+        self.h = C.c_void_p()
+        check(lib().dfl_scratch_create(model.h, C.c_uint32(block_size), C.c_uint32(n_capture_layers), C.byref(self.h)))
+
+    def read_capture(self, n):
+        out = np.zeros((n, self.k, self.model.arch.hidden_size), dtype=np.float32)
+        check(lib().dfl_scratch_read_capture(self.h, C.c_uint32(n), _ptr(out), C.c_uint64(out.size)))
+        return out
+
+    def close(self):
+        if self.h:
+            lib().dfl_scratch_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+def _u32(a):
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def packed_verify(model, session, scratch, layer_ids, tokens, start_position, want_logits=False):
+    tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+    n = tokens.size
+    ids = _u32(layer_ids)
+    am = np.zeros(n, dtype=np.int32)
+    gap = np.zeros(n, dtype=np.float32)
+    logits = np.zeros((n, model.arch.vocab_size), dtype=np.float32) if want_logits else None
+    check(lib().dfl_packed_verify(model.h, session.h, scratch.h, _ptr(ids) if ids.size else None, C.c_uint32(ids.size), _ptr(tokens),
+                                  C.c_uint32(n), C.c_uint32(start_position), _ptr(am), _ptr(gap),
+                                  _ptr(logits) if want_logits else None))
+    return am, gap, logits
+
+
+def restore_partial(model, session, scratch, n_keep, start_position):
+    check(lib().dfl_restore_partial(model.h, session.h, scratch.h, C.c_uint32(n_keep), C.c_uint32(start_position)))
+
+
+def restore_pre_block(model, session, scratch, start_position):
+    check(lib().dfl_restore_pre_block(model.h, session.h, scratch.h, C.c_uint32(start_position)))
+
+
+def single_token(model, session, scratch, layer_ids, token, position, want_hidden=True):
+    ids = _u32(layer_ids)
+    logits = np.zeros(model.arch.vocab_size, dtype=np.float32)
+    hidden = np.zeros((scratch.k, model.arch.hidden_size), dtype=np.float32) if (want_hidden and ids.size) else None
+    check(lib().dfl_single_token(model.h, session.h, scratch.h, _ptr(ids) if ids.size else None, C.c_uint32(ids.size),
+                                 C.c_int32(int(token)), C.c_uint32(position), _ptr(logits),
+                                 _ptr(hidden) if hidden is not None else None))
+    return logits, hidden

@@ -1,0 +1,292 @@
+// Gated full-attention block of the verify pass (oracle: Forward::attn_step,
+// crates/qwen-llm/src/forward.rs:834-932; reference GPU path metal_dflash.rs:9823-10099,
+// kernels/attn.metal:137-196,266-336, kernels/attn_v4.metal:65-265).
+//
+// Unlike the reference, which scans the KV cache once per query row, all query rows of the
+// block and all query heads of a GQA group share ONE pass over each 64-position KV chunk
+// (row r attends to positions <= start + r), with per-chunk partial softmax results combined
+// afterwards.  Q stays f32; scores, exp and sums are f32 with accurate expf.
+#include "ops.cuh"
+
+namespace dfl {
+
+// ---- front: reduce GEMM partials, per-head RMSNorm, partial NeoX RoPE, KV append ---------
+// grid (heads = n_q + 2 n_kv, n_rows), block = 128 threads (4 warps cooperate on one head).
+__global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, const float* __restrict__ part, int splits,
+                                                         int ld_part, const float* __restrict__ q_norm_w,
+                                                         const float* __restrict__ k_norm_w, uint32_t start, void* k_cache,
+                                                         void* v_cache, int kv_f16, float* __restrict__ q_rot,
+                                                         float* __restrict__ gate, const uint32_t* __restrict__ pos_override) {
+    extern __shared__ float sh[];  // [hd] values, then 4 partial sums
+    const int head = blockIdx.x, tok = blockIdx.y, hd = g.hd;
+    const int q_stride = gated ? 2 * hd : hd;
+    const int q_cols = g.n_q * q_stride, kv_cols = g.n_kv * hd;
+    int kind, h, col0;  // 0 = q, 1 = k, 2 = v
+    if (head < g.n_q) { kind = 0; h = head; col0 = h * q_stride; }
+    else if (head < g.n_q + g.n_kv) { kind = 1; h = head - g.n_q; col0 = q_cols + h * hd; }
+    else { kind = 2; h = head - g.n_q - g.n_kv; col0 = q_cols + kv_cols + h * hd; }
+    const uint32_t pos = pos_override ? pos_override[tok] : start + (uint32_t)tok;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float v = 0.f, gt = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float* row = part + ((uint64_t)s * MAX_ROWS + tok) * ld_part;
+            v += row[col0 + d];
+            if (kind == 0 && gated) gt += row[col0 + hd + d];
+        }
+        sh[d] = v;
+        ss += v * v;
+        if (kind == 0 && gated) gate[(uint64_t)tok * (g.n_q * hd) + h * hd + d] = gt;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) sh[hd + (threadIdx.x >> 5)] = ss;
+    __syncthreads();
+    if (kind == 2) {
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            const uint64_t o = ((uint64_t)pos * g.n_kv + h) * hd + d;
+            if (kv_f16) reinterpret_cast<__half*>(v_cache)[o] = __float2half_rn(sh[d]);
+            else reinterpret_cast<float*>(v_cache)[o] = sh[d];
+        }
+        return;
+    }
+    const float total = sh[hd] + sh[hd + 1] + sh[hd + 2] + sh[hd + 3];
+    const float scale = 1.0f / sqrtf(total / (float)hd + g.eps);
+    const float* nw = kind == 0 ? q_norm_w : k_norm_w;
+    __syncthreads();
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) sh[d] = sh[d] * scale * nw[d];
+    __syncthreads();
+    const int half = g.n_rot / 2;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float out = sh[d];
+        if (d < g.n_rot) {
+            const int i = d < half ? d : d - half;
+            const float exponent = (float)(2 * i) / (float)g.n_rot;
+            const float freq = (float)pos / powf(g.theta, exponent);
+            float sn, cs;
+            sincosf(freq, &sn, &cs);
+            const float a = sh[i], b = sh[i + half];
+            out = d < half ? (a * cs - b * sn) : (a * sn + b * cs);
+        }
+        if (kind == 0) q_rot[((uint64_t)tok * g.n_q + h) * hd + d] = out;
+        else {
+            const uint64_t o = ((uint64_t)pos * g.n_kv + h) * hd + d;
+            if (kv_f16) reinterpret_cast<__half*>(k_cache)[o] = __float2half_rn(out);
+            else reinterpret_cast<float*>(k_cache)[o] = out;
+        }
+    }
+}
+
+dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, const float* part, int splits, int ld_part,
+                             const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
+                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override) {
+    dim3 grid((unsigned)(g.n_q + 2 * g.n_kv), (unsigned)n_rows);
+    attn_front_kernel<<<grid, 128, (g.hd + 4) * sizeof(float), st>>>(g, gated ? 1 : 0, part, splits, ld_part, q_norm_w, k_norm_w, start,
+                                                                   k_cache, v_cache, kv_f16 ? 1 : 0, q_rot, gate, pos_override);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+// ---- chunk kernel ----------------------------------------------------------------------
+// grid (n_chunks, n_kv), block 256.  partial record per (chunk, kv head, query): [m, l, acc[hd]].
+template <typename KV, int HD>
+__global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float* __restrict__ q_rot, const KV* __restrict__ k_cache,
+                                                         const KV* __restrict__ v_cache, uint32_t start, int n_rows,
+                                                         float* __restrict__ partials) {
+    extern __shared__ float sm[];
+    constexpr int LD = HD + 1;
+    float* ks = sm;                      // [64][LD]
+    float* vs = ks + ATTN_CHUNK * LD;    // [64][LD]
+    float* qs = vs + ATTN_CHUNK * LD;    // [8 warps][HD]
+    float* ps = qs + 8 * HD;             // [8 warps][64]
+    const int chunk = blockIdx.x, kvh = blockIdx.y;
+    const int group = g.n_q / g.n_kv;
+    const uint32_t n_pos = start + (uint32_t)n_rows;
+    const uint32_t p0 = (uint32_t)chunk * ATTN_CHUNK;
+    const int n_here = (int)min((uint32_t)ATTN_CHUNK, n_pos - p0);
+    for (int idx = threadIdx.x; idx < ATTN_CHUNK * HD; idx += blockDim.x) {
+        const int kp = idx / HD, d = idx % HD;
+        float kv = 0.f, vv = 0.f;
+        if (kp < n_here) {
+            const uint64_t o = ((uint64_t)(p0 + kp) * g.n_kv + kvh) * HD + d;
+            kv = (float)k_cache[o];
+            vv = (float)v_cache[o];
+        }
+        ks[kp * LD + d] = kv;
+        vs[kp * LD + d] = vv;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float scale = 1.0f / sqrtf((float)HD);
+    const int n_queries = n_rows * group;
+    float* myq = qs + warp * HD;
+    float* myp = ps + warp * ATTN_CHUNK;
+    for (int qi = warp; qi < n_queries; qi += 8) {
+        const int row = qi / group, qh = kvh * group + qi % group;
+        const float* qsrc = q_rot + ((uint64_t)row * g.n_q + qh) * HD;
+        for (int d = lane; d < HD; d += 32) myq[d] = qsrc[d];
+        __syncwarp();
+        const uint32_t last = start + (uint32_t)row;  // last visible position
+        float s0 = 0.f, s1 = 0.f;
+        const float* k0 = ks + lane * LD;
+        const float* k1 = ks + (lane + 32) * LD;
+#pragma unroll 8
+        for (int d = 0; d < HD; ++d) {
+            const float qv = myq[d];
+            s0 = fmaf(qv, k0[d], s0);
+            s1 = fmaf(qv, k1[d], s1);
+        }
+        s0 *= scale;
+        s1 *= scale;
+        const bool ok0 = lane < n_here && p0 + lane <= last;
+        const bool ok1 = lane + 32 < n_here && p0 + lane + 32 <= last;
+        if (!ok0) s0 = -INFINITY;
+        if (!ok1) s1 = -INFINITY;
+        const float m = warp_max(fmaxf(s0, s1));
+        float e0 = 0.f, e1 = 0.f;
+        if (m > -INFINITY) {
+            e0 = ok0 ? expf(s0 - m) : 0.f;
+            e1 = ok1 ? expf(s1 - m) : 0.f;
+        }
+        const float l = warp_sum(e0 + e1);
+        myp[lane] = e0;
+        myp[lane + 32] = e1;
+        __syncwarp();
+        float acc[HD / 32];
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) acc[j] = 0.f;
+        for (int kp = 0; kp < n_here; ++kp) {
+            const float pw = myp[kp];
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) acc[j] = fmaf(pw, vs[kp * LD + lane + 32 * j], acc[j]);
+        }
+        float* rec = partials + (((uint64_t)chunk * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
+        if (lane == 0) { rec[0] = m; rec[1] = l; }
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) rec[2 + lane + 32 * j] = acc[j];
+        __syncwarp();
+    }
+}
+
+// ---- combine + sigmoid gate + activation packing ---------------------------------------------
+// grid (n_q, n_rows), block 32: one warp per (row, q head); lane owns hd/32 consecutive dims.
+template <int HD>
+__global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* __restrict__ partials, int n_chunks_total,
+                                                       const float* __restrict__ gate, uint32_t start, uint8_t* acts, int bf3,
+                                                       float* out_f32, int* err) {
+    constexpr int PER = HD / 32;  // 4 or 8
+    const int qh = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
+    const int group = g.n_q / g.n_kv, kvh = qh / group, qi = row * group + qh % group;
+    const int n_chunks = (int)((start + (uint32_t)row) / ATTN_CHUNK) + 1;  // chunks holding visible positions
+    (void)n_chunks_total;
+    float M = -INFINITY;
+    for (int c = lane; c < n_chunks; c += 32) {
+        const float* rec = partials + (((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
+        M = fmaxf(M, rec[0]);
+    }
+    M = warp_max(M);
+    float acc[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) acc[j] = 0.f;
+    float L = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+        const float* rec = partials + (((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
+        const float m = rec[0];
+        if (m == -INFINITY) continue;
+        const float f = expf(m - M);
+        L = fmaf(rec[1], f, L);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) acc[j] = fmaf(rec[2 + lane * PER + j], f, acc[j]);
+    }
+    const float inv = 1.0f / L;
+    const int col0 = qh * HD + lane * PER;
+    float v[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        v[j] = acc[j] * inv;
+        if (gate) v[j] *= sigmoid_f(gate[(uint64_t)row * (g.n_q * HD) + col0 + j]);
+    }
+    if (out_f32)
+#pragma unroll
+        for (int j = 0; j < PER; ++j) out_f32[(uint64_t)row * (g.n_q * HD) + col0 + j] = v[j];
+    if (acts) {
+        bool over = false;
+        float sum = 0.f;
+#pragma unroll
+        for (int q4 = 0; q4 < PER / 4; ++q4) {
+            const int col = col0 + 4 * q4;
+            uint8_t* chunk = acts + (uint64_t)(col >> 8) * (bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
+            const float quad[4] = {v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]};
+            pack_quad(chunk, bf3 != 0, row, col & 255, quad, over);
+            sum += quad[0] + quad[1] + quad[2] + quad[3];
+        }
+        if (!bf3) {
+            // 32-column sub-block sums: 32 / PER lanes each
+            constexpr int LANES = 32 / PER;
+#pragma unroll
+            for (int o = LANES / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if ((lane % LANES) == 0) {
+                uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * ACT16_CHUNK;
+                reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[row * 8 + ((col0 & 255) >> 5)] = sum;
+            }
+        }
+        if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
+    }
+}
+
+// zero the activation rows of padded tokens (rows n_rows..15) and the plane padding
+__global__ void acts_clear_kernel(uint8_t* acts, uint64_t bytes) {
+    const uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 16;
+    if (i < bytes) *reinterpret_cast<uint4*>(acts + i) = make_uint4(0, 0, 0, 0);
+}
+dfl_status launch_acts_clear(cudaStream_t st, uint8_t* acts, uint64_t bytes) {
+    acts_clear_kernel<<<(unsigned)((bytes / 16 + 255) / 256), 256, 0, st>>>(acts, bytes);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+uint64_t attn_partials_floats(const AttnGeom& g, uint32_t max_positions) {
+    const uint64_t chunks = (max_positions + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    return chunks * g.n_kv * (uint64_t)(MAX_ROWS * (g.n_q / g.n_kv)) * (g.hd + 2);
+}
+
+template <typename KV, int HD>
+static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* k_cache, const void* v_cache,
+                               uint32_t start, int n_rows, float* partials, int n_chunks) {
+    const size_t smem = (size_t)(2 * ATTN_CHUNK * (HD + 1) + 8 * HD + 8 * ATTN_CHUNK) * sizeof(float);
+    static bool set = false;
+    if (!set) {
+        DFL_CUDA(cudaFuncSetAttribute(attn_chunk_kernel<KV, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        set = true;
+    }
+    attn_chunk_kernel<KV, HD><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(
+        g, q_rot, reinterpret_cast<const KV*>(k_cache), reinterpret_cast<const KV*>(v_cache), start, n_rows, partials);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
+                              const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts, bool bf3,
+                              float* out_f32, int* err) {
+    if (g.hd != 128 && g.hd != 256) return fail(DFL_ERR_UNSUPPORTED, "attention: head_dim must be 128 or 256");
+    const int n_chunks = (int)((start + (uint32_t)n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK);
+    dfl_status s;
+    if (g.hd == 128) s = kv_f16 ? launch_chunk<__half, 128>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks)
+                                : launch_chunk<float, 128>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks);
+    else s = kv_f16 ? launch_chunk<__half, 256>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks)
+                    : launch_chunk<float, 256>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks);
+    DFL_CHECK(s);
+    if (acts && n_rows < MAX_ROWS) {
+        // rows of absent tokens must read as zero in the next GEMM
+        DFL_CHECK(launch_acts_clear(st, acts, acts_bytes(bf3 ? DFL_BF16 : DFL_Q4_K, (uint64_t)g.n_q * g.hd)));
+    }
+    if (g.hd == 128) attn_post_kernel<128><<<dim3((unsigned)g.n_q, (unsigned)n_rows), 32, 0, st>>>(g, partials, n_chunks, gate, start, acts, bf3 ? 1 : 0, out_f32, err);
+    else attn_post_kernel<256><<<dim3((unsigned)g.n_q, (unsigned)n_rows), 32, 0, st>>>(g, partials, n_chunks, gate, start, acts, bf3 ? 1 : 0, out_f32, err);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+}  // namespace dfl

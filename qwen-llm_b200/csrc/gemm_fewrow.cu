@@ -36,7 +36,8 @@ struct GemmParams {
     int n_sumsq;
     float norm_k, eps, out_scale;
     int kblocks, splits;
-    uint32_t n_out;
+    uint32_t n_out;   // rows of this matrix
+    uint32_t ld_out;  // row length of the partial buffer (>= n_out when several matrices share it)
     int* err;
 };
 
@@ -484,14 +485,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
         const int row = threadIdx.x & (TILE_R - 1), th = threadIdx.x >> 7;
         const uint32_t orow = (uint32_t)rt * TILE_R + row;
         if (orow < p.n_out) {
-            float* dst = p.out + (uint64_t)sp * MAX_ROWS * p.n_out + orow;
+            float* dst = p.out + (uint64_t)sp * MAX_ROWS * p.ld_out + orow;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int tok = th * 8 + j;
                 float v = 0.f;
 #pragma unroll
                 for (int wv = 0; wv < CONSUMER_WARPS; ++wv) v += red[wv * (MAX_ROWS * RED_LD) + tok * RED_LD + row];
-                dst[(uint64_t)tok * p.n_out] = v * tok_scale[tok];
+                dst[(uint64_t)tok * p.ld_out] = v * tok_scale[tok];
             }
         }
     }
@@ -532,7 +533,7 @@ static dfl_status launch_t(cudaStream_t st, const GemmParams& p, int grid, bool 
 }
 
 dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits,
-                              const GemmEpilogue& ep, int* dev_err, bool pdl) {
+                              const GemmEpilogue& ep, int* dev_err, bool pdl, uint32_t ld_out) {
     if (splits < 1 || splits > m.kblocks) return fail(DFL_ERR_BAD_ARG, "gemm: bad split count");
     GemmParams p;
     p.w = m.tiles;
@@ -546,6 +547,7 @@ dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* 
     p.kblocks = m.kblocks;
     p.splits = splits;
     p.n_out = (uint32_t)m.n_out;
+    p.ld_out = ld_out ? ld_out : (uint32_t)m.n_out;
     p.err = dev_err;
     const int grid = m.row_tiles * splits;
     switch (m.dtype) {

@@ -1,0 +1,632 @@
+// Target model residency, per-sequence session, verify scratch and the packed verify pass
+// (reference: encode_packed_verify_layer_major_inner, crates/qwen-llm/src/metal_dflash.rs:9045-10719;
+// restore: :15649-15905; oracle: Forward::single_token_capture_layers, forward.rs:173-220).
+#include <cstring>
+
+#include "model.cuh"
+
+namespace dfl {
+
+dfl_status launch_group(cudaStream_t st, const MatGroup& g, const uint8_t* acts, float* part, const GemmEpilogue& ep, int* err) {
+    for (size_t i = 0; i < g.mats.size(); ++i)
+        DFL_CHECK(launch_gemm_fewrow(st, g.mats[i], acts, part + g.col_off[i], g.splits, ep, err, false, g.total_cols));
+    return DFL_OK;
+}
+
+static uint64_t tensor_elems(const dfl_tensor* t) {
+    uint64_t n = 1;
+    for (int i = 0; i < t->n_dims; ++i) n *= t->shape[i];
+    return n;
+}
+
+dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const std::vector<std::string>& names, uint64_t n_in,
+                       const std::vector<uint64_t>& n_outs, MatGroup* out) {
+    out->n_in = n_in;
+    out->total_cols = 0;
+    size_t i = 0;
+    while (i < names.size()) {
+        const dfl_tensor* t0 = tm.find(names[i]);
+        if (!t0) return fail(DFL_ERR_MISSING_TENSOR, "missing tensor " + names[i]);
+        // run of same-dtype tensors -> one concatenated matrix
+        size_t j = i;
+        uint64_t rows = 0, bytes = 0;
+        while (j < names.size()) {
+            const dfl_tensor* t = tm.find(names[j]);
+            if (!t) return fail(DFL_ERR_MISSING_TENSOR, "missing tensor " + names[j]);
+            if (t->dtype != t0->dtype || t->on_device != t0->on_device) break;
+            if (t->n_dims < 2 || t->shape[0] != n_in || tensor_elems(t) != n_in * n_outs[j])
+                return fail(DFL_ERR_BAD_SHAPE, "tensor " + names[j] + " has unexpected shape");
+            const uint64_t want = n_outs[j] * (n_in / 256) * (uint64_t)ggml_bytes_per_256(t->dtype);
+            if (n_in % 256 || ggml_bytes_per_256(t->dtype) == 0 || t->n_bytes != want)
+                return fail(DFL_ERR_BAD_SHAPE, "tensor " + names[j] + ": byte count does not match dtype/shape (n_in must be a multiple of 256)");
+            rows += n_outs[j];
+            bytes += t->n_bytes;
+            ++j;
+        }
+        QMatrix qm;
+        if (j - i == 1) {
+            DFL_CHECK(qmatrix_create(device, t0->dtype, n_in, rows, t0->data, t0->n_bytes, t0->on_device != 0, st, &qm));
+        } else {
+            uint8_t* cat = nullptr;
+            DFL_CUDA(cudaMalloc(&cat, bytes));
+            uint64_t off = 0;
+            for (size_t k = i; k < j; ++k) {
+                const dfl_tensor* t = tm.find(names[k]);
+                cudaMemcpyAsync(cat + off, t->data, t->n_bytes, t->on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st);
+                off += t->n_bytes;
+            }
+            dfl_status s = qmatrix_create(device, t0->dtype, n_in, rows, cat, bytes, true, st, &qm);
+            cudaStreamSynchronize(st);
+            cudaFree(cat);
+            DFL_CHECK(s);
+        }
+        out->mats.push_back(qm);
+        out->col_off.push_back(out->total_cols);
+        out->total_cols += (uint32_t)rows;
+        i = j;
+    }
+    // one split count for the whole group so that every partial slice is fully written
+    QMatrix whole;
+    whole.row_tiles = 0;
+    for (auto& m : out->mats) whole.row_tiles += m.row_tiles;
+    whole.kblocks = (int)(n_in / 256);
+    out->splits = gemm_choose_splits(whole);
+    return DFL_OK;
+}
+
+__global__ void decode_small_kernel(int dtype, const uint8_t* __restrict__ src, uint64_t n, float* __restrict__ out) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (dtype == DFL_F32) out[i] = reinterpret_cast<const float*>(src)[i];
+    else if (dtype == DFL_F16) out[i] = __half2float(reinterpret_cast<const __half*>(src)[i]);
+    else out[i] = __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(src)[i] << 16);
+}
+
+dfl_status upload_f32(int device, cudaStream_t st, const TensorMap& tm, const std::string& name, uint64_t n_expected, float** out) {
+    const dfl_tensor* t = tm.find(name);
+    if (!t) return fail(DFL_ERR_MISSING_TENSOR, "missing tensor " + name);
+    const uint64_t n = tensor_elems(t);
+    if (n != n_expected) return fail(DFL_ERR_BAD_SHAPE, "tensor " + name + " has unexpected element count");
+    if (t->dtype != DFL_F32 && t->dtype != DFL_F16 && t->dtype != DFL_BF16)
+        return fail(DFL_ERR_UNSUPPORTED, "tensor " + name + " must be f32, f16 or bf16");
+    const uint64_t esz = t->dtype == DFL_F32 ? 4 : 2;
+    if (t->n_bytes != n * esz) return fail(DFL_ERR_BAD_SHAPE, "tensor " + name + " byte count mismatch");
+    DFL_CUDA(cudaMalloc(out, n * 4));
+    if (t->dtype == DFL_F32) {
+        DFL_CUDA(cudaMemcpyAsync(*out, t->data, n * 4, t->on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st));
+        DFL_CUDA(cudaStreamSynchronize(st));
+    } else {
+        uint8_t* tmp = nullptr;
+        DFL_CUDA(cudaMalloc(&tmp, t->n_bytes));
+        cudaMemcpyAsync(tmp, t->data, t->n_bytes, t->on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st);
+        decode_small_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(t->dtype, tmp, n, *out);
+        count_launch();
+        cudaStreamSynchronize(st);
+        cudaFree(tmp);
+    }
+    return DFL_OK;
+}
+
+dfl_status session_guard(const dfl_model* m, dfl_session* s, const char* what) {
+    if (!m || !s) return fail(DFL_ERR_BAD_ARG, std::string(what) + ": null handle");
+    if (s->m != m) return fail(DFL_ERR_BAD_ARG, std::string(what) + ": session belongs to another model");
+    if (s->poisoned) return fail(DFL_ERR_POISONED, std::string(what) + ": session is poisoned by an earlier failure");
+    return use_device(m->device);
+}
+
+static bool layer_is_attn(const dfl_arch& a, uint32_t il) {
+    const uint32_t iv = a.full_attention_interval ? a.full_attention_interval : 1;
+    return il % iv == iv - 1;
+}
+
+// After the stream has drained: completion check (metal/completion.rs:18) incl. the injected failure.
+static dfl_status completion_check(dfl_session* s) {
+    if (s->fail_next) {
+        s->fail_next = false;
+        s->poisoned = true;
+        return fail(DFL_ERR_CUDA, "completion check failed (injected): command discarded; session poisoned");
+    }
+    dfl_status st = check_dev_err(s->st, s->err);
+    if (st != DFL_OK) s->poisoned = true;
+    return st;
+}
+
+dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, const uint32_t* layer_ids, uint32_t n_ids,
+                       const int32_t* tokens, uint32_t n, uint32_t start, bool want_head) {
+    const dfl_arch& a = m->arch;
+    cudaStream_t st = s->st;
+    const uint64_t H = a.hidden_size, F = a.intermediate_size;
+    const AttnGeom ag = m->attn_geom();
+    const GdnGeom gg = m->gdn_geom();
+    const int kb_h = (int)(H / 256);
+    GemmEpilogue ep_norm;
+    ep_norm.sumsq = sc->sumsq;
+    ep_norm.n_sumsq = kb_h;
+    ep_norm.norm_k = (float)H;
+    ep_norm.eps = 1e-6f;
+
+    memcpy(sc->pinned_i, tokens, n * sizeof(int32_t));
+    DFL_CUDA(cudaMemcpyAsync(sc->tokens_dev, sc->pinned_i, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
+    DFL_CHECK(launch_embed_rows(st, m->embd_dtype, m->embd_ggml, H, sc->tokens_dev, (int)n, sc->x, (int)H));
+
+    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* norm_w, bool want_xn, float* capture) -> dfl_status {
+        GlueParams p;
+        p.mode = GLUE_RESID;
+        p.part = part; p.splits = splits; p.ld_part = ld_part;
+        p.x = sc->x; p.ld_x = (int)H;
+        p.mul_w = norm_w;
+        p.acts = sc->acts_h; p.bf3 = 0;
+        if (want_xn) { p.xn = sc->xn; p.ld_xn = (int)H; }
+        p.sumsq = sc->sumsq;
+        p.capture = capture; p.ld_capture = (int)(sc->k_layers * H);
+        p.n_rows = (int)n; p.err = s->err;
+        return launch_glue(st, p, H);
+    };
+    DFL_CHECK(norm_glue(nullptr, 0, 0, m->layers[0].attn_norm_w, !m->layers[0].is_attn, nullptr));
+
+    int gi = 0, ai = 0;
+    for (uint32_t il = 0; il < a.n_layer; ++il) {
+        const LayerW& L = m->layers[il];
+        const MatGroup* out_proj;
+        if (L.is_attn) {
+            DFL_CHECK(launch_group(st, L.qkv, sc->acts_h, sc->part, ep_norm, s->err));
+            DFL_CHECK(launch_attn_front(st, ag, true, sc->part, L.qkv.splits, (int)L.qkv.total_cols, L.q_norm_w, L.k_norm_w, start, (int)n,
+                                        s->k_cache[ai], s->v_cache[ai], s->kv_f16, sc->q_rot, sc->gate, nullptr));
+            DFL_CHECK(launch_attn_verify(st, ag, sc->q_rot, sc->gate, s->k_cache[ai], s->v_cache[ai], s->kv_f16, start, (int)n,
+                                         s->attn_partials, sc->acts_v, false, nullptr, s->err));
+            out_proj = &L.wo;
+            ++ai;
+        } else {
+            const int cd = gg.conv_dim();
+            DFL_CHECK(launch_group(st, L.in_qkv_z, sc->acts_h, sc->part, ep_norm, s->err));
+            DFL_CHECK(launch_small_matmul(st, L.w_ab, sc->xn, (int)H, (int)n, H, 2 * gg.n_v, ep_norm, sc->ab[gi], 2 * gg.n_v));
+            DFL_CUDA(cudaMemcpyAsync(sc->conv_pre[gi], s->conv[gi], (size_t)3 * cd * 4, cudaMemcpyDeviceToDevice, st));
+            DFL_CHECK(launch_gdn_front(st, gg, sc->part, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, (int)n, L.conv_w, s->conv[gi],
+                                       sc->qkv_raw[gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi]));
+            const int cur = s->ssm_cur[gi];
+            DFL_CHECK(launch_gdn_scan(st, gg, s->ssm[cur][gi], s->ssm[cur ^ 1][gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->ab[gi],
+                                      L.dt_bias, L.a_log, (int)n, sc->o));
+            s->ssm_cur[gi] = cur ^ 1;
+            DFL_CHECK(launch_gdn_post(st, gg, sc->o, sc->part + cd, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, L.ssm_norm_w, (int)n,
+                                      sc->acts_v, false, s->err));
+            out_proj = &L.w_out;
+            ++gi;
+        }
+        DFL_CHECK(launch_group(st, *out_proj, sc->acts_v, sc->part, GemmEpilogue{}, s->err));
+        DFL_CHECK(norm_glue(sc->part, out_proj->splits, (int)out_proj->total_cols, L.post_norm_w, false, nullptr));
+        // dense SwiGLU FFN (forward.rs:725-747)
+        DFL_CHECK(launch_group(st, L.gate_up, sc->acts_h, sc->part, ep_norm, s->err));
+        {
+            GlueParams p;
+            p.mode = GLUE_SWIGLU;
+            p.part = sc->part; p.splits = L.gate_up.splits; p.ld_part = (int)L.gate_up.total_cols;
+            p.swiglu_f = (int)F;
+            p.pre_scale = 1.0f / 64.0f;  // keeps silu(g)*u inside the f16 operand range; undone in the GEMM epilogue
+            p.acts = sc->acts_f; p.bf3 = 0;
+            p.n_rows = (int)n; p.err = s->err;
+            DFL_CHECK(launch_glue(st, p, F));
+        }
+        GemmEpilogue ep_down;
+        ep_down.out_scale = 64.0f;
+        DFL_CHECK(launch_group(st, L.down, sc->acts_f, sc->part, ep_down, s->err));
+        float* cap = nullptr;
+        for (uint32_t k = 0; k < n_ids; ++k)
+            if (layer_ids[k] == il) cap = sc->capture + (uint64_t)k * H;
+        const bool last = il + 1 == a.n_layer;
+        const float* next_w = last ? m->out_norm_w : m->layers[il + 1].attn_norm_w;
+        const bool next_gdn = !last && !m->layers[il + 1].is_attn;
+        DFL_CHECK(norm_glue(sc->part, L.down.splits, (int)L.down.total_cols, next_w, next_gdn, cap));
+        if (cap) {
+            // duplicate slots (same layer listed twice) get a device copy of the first one
+            bool first = true;
+            for (uint32_t k = 0; k < n_ids; ++k) {
+                if (layer_ids[k] != il) continue;
+                if (first) { first = false; continue; }
+                DFL_CUDA(cudaMemcpy2DAsync(sc->capture + (uint64_t)k * H, sc->k_layers * H * 4, cap, sc->k_layers * H * 4, H * 4, n,
+                                           cudaMemcpyDeviceToDevice, st));
+            }
+        }
+    }
+    if (want_head) {
+        const uint64_t V = a.vocab_size;
+        const MatGroup& lm = m->lm_head;
+        float* logits = sc->logits;
+        if (lm.splits == 1) {
+            DFL_CHECK(launch_group(st, lm, sc->acts_h, logits, ep_norm, s->err));
+        } else {
+            DFL_CHECK(launch_group(st, lm, sc->acts_h, sc->part, ep_norm, s->err));
+            DFL_CHECK(launch_reduce_partials(st, sc->part, lm.splits, (int)n, V, logits, (int)V));
+        }
+        DFL_CHECK(launch_argmax_top2(st, logits, (int)n, V, V, sc->argmax, sc->gap, sc->am_scratch));
+    }
+    s->kv_n_pos = start + n;
+    sc->last_n = n;
+    sc->last_start = start;
+    sc->have_block = true;
+    return DFL_OK;
+}
+
+}  // namespace dfl
+
+using namespace dfl;
+
+extern "C" {
+
+dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors, uint64_t n_tensors, dfl_model** out) {
+    if (!arch || !tensors || !out) return fail(DFL_ERR_BAD_ARG, "model_create: null argument");
+    *out = nullptr;
+    DFL_CHECK(use_device(device));
+    const dfl_arch& a = *arch;
+    if (a.n_layer == 0 || a.hidden_size % 256 || a.hidden_size == 0) return fail(DFL_ERR_BAD_SHAPE, "model_create: hidden size must be a positive multiple of 256");
+    if (a.expert_count > 0) return fail(DFL_ERR_UNSUPPORTED, "model_create: routed-expert FFN is not built yet");
+    if (a.intermediate_size % 256) return fail(DFL_ERR_BAD_SHAPE, "model_create: FFN width must be a multiple of 256");
+    if (a.gdn_head_dim != 128 || a.gdn_conv_kernel != 4) return fail(DFL_ERR_UNSUPPORTED, "model_create: GDN head_dim must be 128 and conv kernel 4");
+    if (a.attn_head_dim != 128 && a.attn_head_dim != 256) return fail(DFL_ERR_UNSUPPORTED, "model_create: attention head_dim must be 128 or 256");
+    if (a.n_kv_heads == 0 || a.n_q_heads % a.n_kv_heads || a.gdn_n_k_heads == 0 || a.gdn_n_v_heads % a.gdn_n_k_heads)
+        return fail(DFL_ERR_BAD_SHAPE, "model_create: head counts");
+    if (((uint64_t)a.n_q_heads * a.attn_head_dim) % 256 || ((uint64_t)a.gdn_n_v_heads * 128) % 256)
+        return fail(DFL_ERR_BAD_SHAPE, "model_create: projection widths must be multiples of 256");
+    TensorMap tm;
+    for (uint64_t i = 0; i < n_tensors; ++i) {
+        if (!tensors[i].name || !tensors[i].data) return fail(DFL_ERR_BAD_ARG, "model_create: tensor without name or data");
+        tm.t[tensors[i].name] = &tensors[i];
+    }
+    auto* m = new dfl_model();
+    m->device = device;
+    m->arch = a;
+    cudaStream_t st = 0;
+    const uint64_t H = a.hidden_size, F = a.intermediate_size, V = a.vocab_size;
+    const uint64_t hd = a.attn_head_dim, q_dim = a.n_q_heads * hd, kv_dim = a.n_kv_heads * hd;
+    const uint64_t conv_dim = (2ull * a.gdn_n_k_heads + a.gdn_n_v_heads) * 128, v_dim = a.gdn_n_v_heads * 128ull;
+    dfl_status s = DFL_OK;
+    auto blk = [](uint32_t il, const char* suffix) { return "blk." + std::to_string(il) + "." + suffix; };
+#define MC(expr)                      \
+    do {                              \
+        s = (expr);                   \
+        if (s != DFL_OK) goto failed; \
+    } while (0)
+    {
+        const dfl_tensor* te = tm.find("token_embd.weight");
+        if (!te) { s = fail(DFL_ERR_MISSING_TENSOR, "missing tensor token_embd.weight"); goto failed; }
+        const uint64_t want = V * (H / 256) * (uint64_t)ggml_bytes_per_256(te->dtype);
+        if (ggml_bytes_per_256(te->dtype) == 0 || te->n_bytes != want) { s = fail(DFL_ERR_BAD_SHAPE, "token_embd.weight: byte count"); goto failed; }
+        if (cudaMalloc(&m->embd_ggml, te->n_bytes) != cudaSuccess) { s = fail(DFL_ERR_OOM, "token_embd"); goto failed; }
+        cudaMemcpy(m->embd_ggml, te->data, te->n_bytes, te->on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice);
+        m->embd_dtype = te->dtype;
+        const char* head_name = tm.find("output.weight") ? "output.weight" : "token_embd.weight";  // tied embeddings, loader.rs:445
+        MC(build_group(device, st, tm, {head_name}, H, {V}, &m->lm_head));
+        MC(upload_f32(device, st, tm, "output_norm.weight", H, &m->out_norm_w));
+        m->verify_weight_bytes = m->lm_head.ggml_bytes();
+    }
+    m->layers.resize(a.n_layer);
+    for (uint32_t il = 0; il < a.n_layer; ++il) {
+        LayerW& L = m->layers[il];
+        L.is_attn = layer_is_attn(a, il);
+        MC(upload_f32(device, st, tm, blk(il, "attn_norm.weight"), H, &L.attn_norm_w));
+        MC(upload_f32(device, st, tm, blk(il, "post_attention_norm.weight"), H, &L.post_norm_w));
+        if (L.is_attn) {
+            ++m->n_attn;
+            MC(build_group(device, st, tm, {blk(il, "attn_q.weight"), blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H,
+                           {2 * q_dim, kv_dim, kv_dim}, &L.qkv));
+            MC(build_group(device, st, tm, {blk(il, "attn_output.weight")}, q_dim, {H}, &L.wo));
+            MC(upload_f32(device, st, tm, blk(il, "attn_q_norm.weight"), hd, &L.q_norm_w));
+            MC(upload_f32(device, st, tm, blk(il, "attn_k_norm.weight"), hd, &L.k_norm_w));
+            m->verify_weight_bytes += L.qkv.ggml_bytes() + L.wo.ggml_bytes();
+        } else {
+            ++m->n_gdn;
+            MC(build_group(device, st, tm, {blk(il, "attn_qkv.weight"), blk(il, "attn_gate.weight")}, H, {conv_dim, v_dim}, &L.in_qkv_z));
+            MC(build_group(device, st, tm, {blk(il, "ssm_out.weight")}, v_dim, {H}, &L.w_out));
+            {
+                float *al = nullptr, *be = nullptr;
+                MC(upload_f32(device, st, tm, blk(il, "ssm_alpha.weight"), H * a.gdn_n_v_heads, &al));
+                s = upload_f32(device, st, tm, blk(il, "ssm_beta.weight"), H * a.gdn_n_v_heads, &be);
+                if (s != DFL_OK) { cudaFree(al); goto failed; }
+                cudaMalloc(&L.w_ab, 2 * H * a.gdn_n_v_heads * 4);
+                cudaMemcpy(L.w_ab, al, H * a.gdn_n_v_heads * 4, cudaMemcpyDeviceToDevice);
+                cudaMemcpy(L.w_ab + H * a.gdn_n_v_heads, be, H * a.gdn_n_v_heads * 4, cudaMemcpyDeviceToDevice);
+                cudaFree(al);
+                cudaFree(be);
+            }
+            MC(upload_f32(device, st, tm, blk(il, "ssm_a"), a.gdn_n_v_heads, &L.a_log));
+            MC(upload_f32(device, st, tm, blk(il, "ssm_dt.bias"), a.gdn_n_v_heads, &L.dt_bias));
+            MC(upload_f32(device, st, tm, blk(il, "ssm_conv1d.weight"), conv_dim * 4, &L.conv_w));
+            MC(upload_f32(device, st, tm, blk(il, "ssm_norm.weight"), 128, &L.ssm_norm_w));
+            m->verify_weight_bytes += L.in_qkv_z.ggml_bytes() + L.w_out.ggml_bytes() + 2 * H * a.gdn_n_v_heads * 4;
+        }
+        MC(build_group(device, st, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up));
+        MC(build_group(device, st, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down));
+        m->verify_weight_bytes += L.gate_up.ggml_bytes() + L.down.ggml_bytes();
+    }
+#undef MC
+    cudaDeviceSynchronize();
+    *out = m;
+    return DFL_OK;
+failed:
+    dfl_model_destroy(m);
+    return s;
+}
+
+void dfl_model_destroy(dfl_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    for (auto& L : m->layers) {
+        L.qkv.release(); L.wo.release(); L.in_qkv_z.release(); L.w_out.release(); L.gate_up.release(); L.down.release();
+        for (float* p : {L.attn_norm_w, L.post_norm_w, L.q_norm_w, L.k_norm_w, L.w_ab, L.a_log, L.dt_bias, L.conv_w, L.ssm_norm_w})
+            if (p) cudaFree(p);
+    }
+    m->lm_head.release();
+    if (m->embd_ggml) cudaFree(m->embd_ggml);
+    if (m->out_norm_w) cudaFree(m->out_norm_w);
+    delete m;
+}
+
+uint64_t dfl_model_verify_weight_bytes(const dfl_model* m) { return m ? m->verify_weight_bytes : 0; }
+
+dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t kv_f16, dfl_session** out) {
+    if (!m || !out) return fail(DFL_ERR_BAD_ARG, "session_create: null argument");
+    *out = nullptr;
+    if (kv_capacity == 0) return fail(DFL_ERR_BAD_ARG, "session_create: kv_capacity must be positive");
+    DFL_CHECK(use_device(m->device));
+    auto* s = new dfl_session();
+    s->m = m;
+    s->kv_capacity = kv_capacity;
+    s->kv_f16 = kv_f16 != 0;
+    const dfl_arch& a = m->arch;
+    const size_t kv_elems = (size_t)kv_capacity * a.n_kv_heads * a.attn_head_dim;
+    const size_t kv_bytes = kv_elems * (s->kv_f16 ? 2 : 4);
+    const size_t conv_bytes = (size_t)3 * m->gdn_geom().conv_dim() * 4;
+    const size_t ssm_bytes = (size_t)a.gdn_n_v_heads * 128 * 128 * 4;
+    bool ok = cudaStreamCreateWithFlags(&s->st, cudaStreamNonBlocking) == cudaSuccess;
+    for (int i = 0; i < m->n_attn && ok; ++i) {
+        void *k = nullptr, *v = nullptr;
+        ok = cudaMalloc(&k, kv_bytes) == cudaSuccess && cudaMalloc(&v, kv_bytes) == cudaSuccess;
+        s->k_cache.push_back(k);
+        s->v_cache.push_back(v);
+    }
+    for (int i = 0; i < m->n_gdn && ok; ++i) {
+        float *c = nullptr, *s0 = nullptr, *s1 = nullptr;
+        ok = cudaMalloc(&c, conv_bytes) == cudaSuccess && cudaMalloc(&s0, ssm_bytes) == cudaSuccess && cudaMalloc(&s1, ssm_bytes) == cudaSuccess;
+        if (ok) { cudaMemset(c, 0, conv_bytes); cudaMemset(s0, 0, ssm_bytes); cudaMemset(s1, 0, ssm_bytes); }
+        s->conv.push_back(c);
+        s->ssm[0].push_back(s0);
+        s->ssm[1].push_back(s1);
+        s->ssm_cur.push_back(0);
+    }
+    if (ok && m->n_attn) ok = cudaMalloc(&s->attn_partials, attn_partials_floats(m->attn_geom(), kv_capacity) * 4) == cudaSuccess;
+    ok = ok && cudaMalloc(&s->err, 4) == cudaSuccess;
+    ok = ok && cudaEventCreate(&s->ev0) == cudaSuccess && cudaEventCreate(&s->ev1) == cudaSuccess;
+    if (!ok) {
+        std::string why = cudaGetErrorString(cudaGetLastError());
+        dfl_session_destroy(s);
+        return fail(DFL_ERR_OOM, "session_create: allocation failed: " + why);
+    }
+    cudaMemset(s->err, 0, 4);
+    cudaDeviceSynchronize();
+    *out = s;
+    return DFL_OK;
+}
+
+void dfl_session_destroy(dfl_session* s) {
+    if (!s) return;
+    cudaSetDevice(s->m->device);
+    for (void* p : s->k_cache) cudaFree(p);
+    for (void* p : s->v_cache) cudaFree(p);
+    for (float* p : s->conv) cudaFree(p);
+    for (float* p : s->ssm[0]) cudaFree(p);
+    for (float* p : s->ssm[1]) cudaFree(p);
+    cudaFree(s->attn_partials);
+    cudaFree(s->err);
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
+    if (s->st) cudaStreamDestroy(s->st);
+    delete s;
+}
+
+uint32_t dfl_session_kv_n_pos(const dfl_session* s) { return s ? s->kv_n_pos : 0; }
+int32_t dfl_session_poisoned(const dfl_session* s) { return s && s->poisoned ? 1 : 0; }
+void dfl_session_fail_next_completion(dfl_session* s) { if (s) s->fail_next = true; }
+
+dfl_status dfl_session_read_gdn_state(const dfl_session* s, uint32_t gdn_index, float* ssm_out, uint64_t n_ssm, float* conv_out, uint64_t n_conv) {
+    if (!s) return fail(DFL_ERR_BAD_ARG, "read_gdn_state: null session");
+    if (gdn_index >= s->conv.size()) return fail(DFL_ERR_BAD_ARG, "read_gdn_state: layer index");
+    DFL_CHECK(use_device(s->m->device));
+    const uint64_t want_ssm = (uint64_t)s->m->arch.gdn_n_v_heads * 128 * 128, want_conv = 3ull * s->m->gdn_geom().conv_dim();
+    DFL_CUDA(cudaStreamSynchronize(s->st));
+    if (ssm_out) {
+        if (n_ssm != want_ssm) return fail(DFL_ERR_BAD_SHAPE, "read_gdn_state: ssm size");
+        DFL_CUDA(cudaMemcpy(ssm_out, s->ssm[s->ssm_cur[gdn_index]][gdn_index], want_ssm * 4, cudaMemcpyDeviceToHost));
+    }
+    if (conv_out) {
+        if (n_conv != want_conv) return fail(DFL_ERR_BAD_SHAPE, "read_gdn_state: conv size");
+        DFL_CUDA(cudaMemcpy(conv_out, s->conv[gdn_index], want_conv * 4, cudaMemcpyDeviceToHost));
+    }
+    return DFL_OK;
+}
+
+dfl_status dfl_session_read_kv(const dfl_session* s, uint32_t attn_index, uint32_t pos, float* k_out, float* v_out, uint64_t n) {
+    if (!s || !k_out || !v_out) return fail(DFL_ERR_BAD_ARG, "read_kv: null argument");
+    if (attn_index >= s->k_cache.size() || pos >= s->kv_n_pos) return fail(DFL_ERR_BAD_ARG, "read_kv: index");
+    const uint64_t stride = (uint64_t)s->m->arch.n_kv_heads * s->m->arch.attn_head_dim;
+    if (n != stride) return fail(DFL_ERR_BAD_SHAPE, "read_kv: row size");
+    DFL_CHECK(use_device(s->m->device));
+    DFL_CUDA(cudaStreamSynchronize(s->st));
+    if (s->kv_f16) {
+        std::vector<__half> hk(stride), hv(stride);
+        DFL_CUDA(cudaMemcpy(hk.data(), (const __half*)s->k_cache[attn_index] + pos * stride, stride * 2, cudaMemcpyDeviceToHost));
+        DFL_CUDA(cudaMemcpy(hv.data(), (const __half*)s->v_cache[attn_index] + pos * stride, stride * 2, cudaMemcpyDeviceToHost));
+        for (uint64_t i = 0; i < stride; ++i) { k_out[i] = __half2float(hk[i]); v_out[i] = __half2float(hv[i]); }
+    } else {
+        DFL_CUDA(cudaMemcpy(k_out, (const float*)s->k_cache[attn_index] + pos * stride, stride * 4, cudaMemcpyDeviceToHost));
+        DFL_CUDA(cudaMemcpy(v_out, (const float*)s->v_cache[attn_index] + pos * stride, stride * 4, cudaMemcpyDeviceToHost));
+    }
+    return DFL_OK;
+}
+
+dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t n_capture_layers, dfl_scratch** out) {
+    if (!m || !out) return fail(DFL_ERR_BAD_ARG, "scratch_create: null argument");
+    *out = nullptr;
+    if (block_size < 1 || block_size > MAX_ROWS) return fail(DFL_ERR_BAD_SHAPE, "scratch_create: block_size must be in [1, 16]");
+    if (n_capture_layers > DFL_MAX_TARGET_LAYERS) return fail(DFL_ERR_BAD_SHAPE, "scratch_create: too many capture layers");
+    DFL_CHECK(use_device(m->device));
+    auto* sc = new dfl_scratch();
+    sc->m = m;
+    sc->block_size = block_size;
+    sc->k_layers = n_capture_layers ? n_capture_layers : 1;
+    const dfl_arch& a = m->arch;
+    const uint64_t H = a.hidden_size, F = a.intermediate_size, V = a.vocab_size;
+    const GdnGeom gg = m->gdn_geom();
+    const uint64_t q_dim = (uint64_t)a.n_q_heads * a.attn_head_dim, v_dim = (uint64_t)gg.n_v * 128;
+    uint64_t part = 0;
+    auto upd = [&](const MatGroup& g) { part = std::max<uint64_t>(part, (uint64_t)g.splits * MAX_ROWS * g.total_cols); };
+    for (auto& L : m->layers) { upd(L.qkv); upd(L.wo); upd(L.in_qkv_z); upd(L.w_out); upd(L.gate_up); upd(L.down); }
+    if (m->lm_head.splits > 1) upd(m->lm_head);
+    sc->part_floats = part;
+    bool ok = true;
+    auto alloc = [&](auto** p, size_t bytes) {
+        if (!ok) return;
+        void* q = nullptr;
+        ok = cudaMalloc(&q, bytes ? bytes : 16) == cudaSuccess;
+        if (ok) { cudaMemset(q, 0, bytes ? bytes : 16); sc->allocs.push_back(q); }
+        *p = reinterpret_cast<std::remove_reference_t<decltype(**p)>*>(q);
+    };
+    alloc(&sc->x, MAX_ROWS * H * 4);
+    alloc(&sc->xn, MAX_ROWS * H * 4);
+    alloc(&sc->part, part * 4);
+    alloc(&sc->sumsq, (H / 256) * MAX_ROWS * 4);
+    alloc(&sc->acts_h, acts_bytes(DFL_Q4_K, H));
+    alloc(&sc->acts_f, acts_bytes(DFL_Q4_K, F));
+    alloc(&sc->acts_v, acts_bytes(DFL_Q4_K, std::max(q_dim, v_dim)));
+    alloc(&sc->q_rot, MAX_ROWS * q_dim * 4);
+    alloc(&sc->gate, MAX_ROWS * q_dim * 4);
+    alloc(&sc->o, MAX_ROWS * v_dim * 4);
+    for (int i = 0; i < m->n_gdn; ++i) {
+        float *a0, *a1, *a2, *a3, *a4, *a5;
+        alloc(&a0, (size_t)MAX_ROWS * gg.conv_dim() * 4);
+        alloc(&a1, (size_t)3 * gg.conv_dim() * 4);
+        alloc(&a2, (size_t)MAX_ROWS * gg.n_k * 128 * 4);
+        alloc(&a3, (size_t)MAX_ROWS * gg.n_k * 128 * 4);
+        alloc(&a4, (size_t)MAX_ROWS * gg.n_v * 128 * 4);
+        alloc(&a5, (size_t)MAX_ROWS * 2 * gg.n_v * 4);
+        sc->qkv_raw.push_back(a0); sc->conv_pre.push_back(a1); sc->q_n.push_back(a2); sc->k_n.push_back(a3); sc->v.push_back(a4); sc->ab.push_back(a5);
+    }
+    alloc(&sc->logits, MAX_ROWS * V * 4);
+    alloc(&sc->gap, MAX_ROWS * 4);
+    alloc(&sc->argmax, MAX_ROWS * 4);
+    { uint8_t* am = nullptr; alloc(&am, MAX_ROWS * ARGMAX_PARTS * 16); sc->am_scratch = am; }
+    alloc(&sc->capture, (size_t)MAX_ROWS * sc->k_layers * H * 4);
+    alloc(&sc->tokens_dev, MAX_ROWS * 4);
+    ok = ok && cudaMallocHost(&sc->pinned_i, 2 * MAX_ROWS * 4) == cudaSuccess && cudaMallocHost(&sc->pinned_f, MAX_ROWS * 4) == cudaSuccess;
+    if (!ok) {
+        std::string why = cudaGetErrorString(cudaGetLastError());
+        dfl_scratch_destroy(sc);
+        return fail(DFL_ERR_OOM, "scratch_create: allocation failed: " + why);
+    }
+    cudaDeviceSynchronize();
+    *out = sc;
+    return DFL_OK;
+}
+
+void dfl_scratch_destroy(dfl_scratch* sc) {
+    if (!sc) return;
+    cudaSetDevice(sc->m->device);
+    for (void* p : sc->allocs) cudaFree(p);
+    if (sc->pinned_i) cudaFreeHost(sc->pinned_i);
+    if (sc->pinned_f) cudaFreeHost(sc->pinned_f);
+    delete sc;
+}
+
+static dfl_status verify_guards(const dfl_model* m, dfl_session* s, dfl_scratch* sc, const uint32_t* layer_ids, uint32_t n_ids,
+                                const int32_t* tokens, uint32_t n, uint32_t start, const char* what) {
+    DFL_CHECK(session_guard(m, s, what));
+    if (!sc || sc->m != m) return fail(DFL_ERR_BAD_ARG, std::string(what) + ": scratch belongs to another model");
+    if (!tokens) return fail(DFL_ERR_BAD_ARG, std::string(what) + ": tokens is null");
+    if (n < 1 || n > sc->block_size) return fail(DFL_ERR_BAD_SHAPE, std::string(what) + ": token count must be in [1, block_size]");
+    if (n_ids > sc->k_layers || (n_ids && !layer_ids)) return fail(DFL_ERR_BAD_SHAPE, std::string(what) + ": capture layer count exceeds the scratch");
+    for (uint32_t k = 0; k < n_ids; ++k)
+        if (layer_ids[k] >= m->arch.n_layer) return fail(DFL_ERR_BAD_SHAPE, std::string(what) + ": capture layer id out of range");
+    // guard wall of the reference (metal_dflash.rs:9079-9186)
+    if (s->kv_n_pos != start) return fail(DFL_ERR_KV_STATE, std::string(what) + ": kv_n_pos " + std::to_string(s->kv_n_pos) + " != start_position " + std::to_string(start));
+    if ((uint64_t)start + n > s->kv_capacity) return fail(DFL_ERR_KV_STATE, std::string(what) + ": start_position + n exceeds kv_capacity");
+    for (uint32_t i = 0; i < n; ++i)
+        if (tokens[i] < 0 || (uint32_t)tokens[i] >= m->arch.vocab_size) return fail(DFL_ERR_BAD_TOKEN, std::string(what) + ": token id out of range");
+    return DFL_OK;
+}
+
+dfl_status dfl_packed_verify(const dfl_model* m, dfl_session* s, dfl_scratch* sc, const uint32_t* layer_ids, uint32_t n_layer_ids,
+                             const int32_t* tokens, uint32_t n, uint32_t start_position, int32_t* argmax_out, float* gap_out,
+                             float* logits_host) {
+    DFL_CHECK(verify_guards(m, s, sc, layer_ids, n_layer_ids, tokens, n, start_position, "packed_verify"));
+    if (!argmax_out) return fail(DFL_ERR_BAD_ARG, "packed_verify: argmax_out is null");
+    dfl_status st = verify_core(m, s, sc, layer_ids, n_layer_ids, tokens, n, start_position, true);
+    if (st != DFL_OK) { s->poisoned = true; return st; }
+    cudaMemcpyAsync(sc->pinned_i + MAX_ROWS, sc->argmax, n * 4, cudaMemcpyDeviceToHost, s->st);
+    cudaMemcpyAsync(sc->pinned_f, sc->gap, n * 4, cudaMemcpyDeviceToHost, s->st);
+    if (logits_host) cudaMemcpyAsync(logits_host, sc->logits, (size_t)n * m->arch.vocab_size * 4, cudaMemcpyDeviceToHost, s->st);
+    DFL_CHECK(completion_check(s));
+    memcpy(argmax_out, sc->pinned_i + MAX_ROWS, n * 4);
+    if (gap_out) memcpy(gap_out, sc->pinned_f, n * 4);
+    return DFL_OK;
+}
+
+dfl_status dfl_scratch_read_capture(const dfl_scratch* sc, uint32_t n, float* out_host, uint64_t n_floats) {
+    if (!sc || !out_host) return fail(DFL_ERR_BAD_ARG, "read_capture: null argument");
+    const uint64_t want = (uint64_t)n * sc->k_layers * sc->m->arch.hidden_size;
+    if (n > MAX_ROWS || n_floats != want) return fail(DFL_ERR_BAD_SHAPE, "read_capture: size");
+    DFL_CHECK(use_device(sc->m->device));
+    DFL_CUDA(cudaDeviceSynchronize());
+    DFL_CUDA(cudaMemcpy(out_host, sc->capture, want * 4, cudaMemcpyDeviceToHost));
+    return DFL_OK;
+}
+
+dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t n_keep, uint32_t start_position) {
+    DFL_CHECK(session_guard(m, s, "restore_partial"));
+    if (!sc || sc->m != m || !sc->have_block) return fail(DFL_ERR_BAD_ARG, "restore_partial: scratch holds no verify block");
+    if (start_position != sc->last_start) return fail(DFL_ERR_KV_STATE, "restore_partial: start_position differs from the last verify");
+    if (n_keep < 1 || n_keep > sc->last_n) return fail(DFL_ERR_BAD_SHAPE, "restore_partial: n_keep must be in [1, n]");
+    if (s->kv_n_pos != sc->last_start + sc->last_n) return fail(DFL_ERR_KV_STATE, "restore_partial: kv_n_pos != start_position + n");
+    if (n_keep == sc->last_n) return DFL_OK;  // nothing to undo (metal_dflash.rs:15751)
+    const GdnGeom gg = m->gdn_geom();
+    int gi = 0;
+    for (uint32_t il = 0; il < m->arch.n_layer; ++il) {
+        const LayerW& L = m->layers[il];
+        if (L.is_attn) continue;
+        const int cur = s->ssm_cur[gi];  // advanced state; cur ^ 1 still holds the pre-block state
+        dfl_status st = launch_gdn_scan(s->st, gg, s->ssm[cur ^ 1][gi], s->ssm[cur][gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->ab[gi],
+                                        L.dt_bias, L.a_log, (int)n_keep, nullptr);
+        if (st == DFL_OK) st = launch_gdn_conv_restore(s->st, gg, sc->conv_pre[gi], sc->qkv_raw[gi], (int)n_keep, s->conv[gi]);
+        if (st != DFL_OK) { s->poisoned = true; return st; }
+        ++gi;
+    }
+    s->kv_n_pos = start_position + n_keep;  // KV rows beyond stay and are overwritten by the next block
+    sc->last_n = n_keep;
+    DFL_CUDA(cudaStreamSynchronize(s->st));
+    return completion_check(s);
+}
+
+dfl_status dfl_restore_pre_block(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t start_position) {
+    DFL_CHECK(session_guard(m, s, "restore_pre_block"));
+    if (!sc || sc->m != m || !sc->have_block) return fail(DFL_ERR_BAD_ARG, "restore_pre_block: scratch holds no verify block");
+    if (start_position != sc->last_start) return fail(DFL_ERR_KV_STATE, "restore_pre_block: start_position differs from the last verify");
+    const GdnGeom gg = m->gdn_geom();
+    for (size_t gi = 0; gi < s->conv.size(); ++gi) {
+        s->ssm_cur[gi] ^= 1;
+        DFL_CUDA(cudaMemcpyAsync(s->conv[gi], sc->conv_pre[gi], (size_t)3 * gg.conv_dim() * 4, cudaMemcpyDeviceToDevice, s->st));
+    }
+    s->kv_n_pos = start_position;
+    sc->have_block = false;
+    DFL_CUDA(cudaStreamSynchronize(s->st));
+    return completion_check(s);
+}
+
+dfl_status dfl_single_token(const dfl_model* m, dfl_session* s, dfl_scratch* sc, const uint32_t* layer_ids, uint32_t n_layer_ids,
+                            int32_t token, uint32_t position, float* logits_host, float* hidden_host) {
+    DFL_CHECK(verify_guards(m, s, sc, layer_ids, n_layer_ids, &token, 1, position, "single_token"));
+    dfl_status st = verify_core(m, s, sc, layer_ids, n_layer_ids, &token, 1, position, true);
+    if (st != DFL_OK) { s->poisoned = true; return st; }
+    if (logits_host) cudaMemcpyAsync(logits_host, sc->logits, (size_t)m->arch.vocab_size * 4, cudaMemcpyDeviceToHost, s->st);
+    if (hidden_host && n_layer_ids)
+        cudaMemcpyAsync(hidden_host, sc->capture, (size_t)sc->k_layers * m->arch.hidden_size * 4, cudaMemcpyDeviceToHost, s->st);
+    return completion_check(s);
+}
+
+}  // extern "C"

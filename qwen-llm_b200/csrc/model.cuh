@@ -1,0 +1,132 @@
+// Host-side objects behind the opaque C handles: resident target model, per-sequence session,
+// verify scratch, drafter and drafter session.  They mirror the reference's MetalModel /
+// MetalSession / MetalDFlashVerifyScratch / MetalDFlashHead / MetalDFlashSession
+// (crates/qwen-llm/src/metal_forward/mod.rs:443,2095; crates/qwen-llm/src/metal_dflash.rs:4944,5492,6003).
+#pragma once
+#include <map>
+#include <string>
+#include <vector>
+
+#include "ops.cuh"
+
+namespace dfl {
+
+dfl_status use_device(int device);
+dfl_status check_dev_err(cudaStream_t st, int* dev_err);
+dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, const void* data, uint64_t n_bytes, bool on_device,
+                          cudaStream_t st, QMatrix* m);
+void qmatrix_release(QMatrix* m);
+
+// Several matrices that consume the same activations and write side by side into one
+// partial buffer [splits][16][total_cols].
+struct MatGroup {
+    std::vector<QMatrix> mats;
+    std::vector<uint32_t> col_off;
+    uint32_t total_cols = 0;
+    uint64_t n_in = 0;
+    int splits = 1;
+    uint64_t ggml_bytes() const { uint64_t b = 0; for (auto& m : mats) b += m.ggml_bytes(); return b; }
+    void release() { for (auto& m : mats) qmatrix_release(&m); mats.clear(); }
+};
+dfl_status launch_group(cudaStream_t st, const MatGroup& g, const uint8_t* acts, float* part, const GemmEpilogue& ep, int* err);
+
+struct TensorMap {
+    std::map<std::string, const dfl_tensor*> t;
+    const dfl_tensor* find(const std::string& n) const { auto it = t.find(n); return it == t.end() ? nullptr : it->second; }
+};
+// Builds a MatGroup from named tensors [n_in, n_out]; consecutive tensors of one dtype are
+// concatenated row-wise into one resident matrix (one kernel launch instead of several).
+dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const std::vector<std::string>& names, uint64_t n_in,
+                       const std::vector<uint64_t>& n_outs, MatGroup* out);
+// Uploads a small tensor as f32 (norm weights, biases, f32 projections); any ggml dtype.
+dfl_status upload_f32(int device, cudaStream_t st, const TensorMap& tm, const std::string& name, uint64_t n_expected, float** out);
+
+struct LayerW {
+    bool is_attn = false;
+    float *attn_norm_w = nullptr, *post_norm_w = nullptr;
+    // full attention
+    MatGroup qkv;  // q (interleaved q|gate per head), k, v
+    MatGroup wo;
+    float *q_norm_w = nullptr, *k_norm_w = nullptr;
+    // gated delta net
+    MatGroup in_qkv_z;  // attn_qkv then attn_gate
+    MatGroup w_out;
+    float *w_ab = nullptr;  // [2 n_v][H]: ssm_alpha rows, then ssm_beta rows
+    float *a_log = nullptr, *dt_bias = nullptr, *conv_w = nullptr, *ssm_norm_w = nullptr;
+    // dense FFN
+    MatGroup gate_up;
+    MatGroup down;
+};
+
+}  // namespace dfl
+
+struct dfl_model {
+    int device = 0;
+    dfl_arch arch{};
+    std::vector<dfl::LayerW> layers;
+    uint8_t* embd_ggml = nullptr;  // token_embd in ggml layout (row gather)
+    int embd_dtype = 0;
+    dfl::MatGroup lm_head;
+    float* out_norm_w = nullptr;
+    uint64_t verify_weight_bytes = 0;
+    std::vector<void*> allocs;
+    int n_gdn = 0, n_attn = 0;
+    dfl::AttnGeom attn_geom() const {
+        dfl::AttnGeom g;
+        g.n_q = (int)arch.n_q_heads; g.n_kv = (int)arch.n_kv_heads; g.hd = (int)arch.attn_head_dim;
+        g.n_rot = (int)((float)arch.attn_head_dim * arch.partial_rotary_factor);
+        g.theta = arch.rope_theta; g.eps = 1e-6f;
+        return g;
+    }
+    dfl::GdnGeom gdn_geom() const {
+        dfl::GdnGeom g;
+        g.n_v = (int)arch.gdn_n_v_heads; g.n_k = (int)arch.gdn_n_k_heads; g.hd = (int)arch.gdn_head_dim; g.conv_k = (int)arch.gdn_conv_kernel;
+        return g;
+    }
+};
+
+struct dfl_session {
+    const dfl_model* m = nullptr;
+    uint32_t kv_capacity = 0;
+    bool kv_f16 = false;
+    uint32_t kv_n_pos = 0;
+    bool poisoned = false;
+    bool fail_next = false;
+    std::vector<void*> k_cache, v_cache;  // per attention layer: [capacity][n_kv][hd]
+    std::vector<float*> conv;             // per GDN layer: [3][conv_dim]
+    std::vector<float*> ssm[2];           // per GDN layer, double buffered: [n_v][128][128]
+    std::vector<int> ssm_cur;
+    float* attn_partials = nullptr;
+    cudaStream_t st = nullptr;
+    int* err = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+struct dfl_scratch {
+    const dfl_model* m = nullptr;
+    uint32_t block_size = 0, k_layers = 0;
+    float *x = nullptr, *xn = nullptr, *part = nullptr, *sumsq = nullptr;
+    uint8_t *acts_h = nullptr, *acts_f = nullptr, *acts_v = nullptr;
+    float *q_rot = nullptr, *gate = nullptr, *o = nullptr;
+    // per GDN layer, kept for rollback
+    std::vector<float*> qkv_raw, conv_pre, q_n, k_n, v, ab;
+    float *logits = nullptr, *gap = nullptr;
+    int32_t* argmax = nullptr;
+    void* am_scratch = nullptr;
+    float* capture = nullptr;  // [16][k][H]
+    int32_t* tokens_dev = nullptr;
+    int32_t* pinned_i = nullptr;  // [16] tokens in, [16] argmax out
+    float* pinned_f = nullptr;    // [16] gaps
+    uint32_t last_n = 0, last_start = 0;
+    bool have_block = false;
+    uint64_t part_floats = 0;
+    std::vector<void*> allocs;
+};
+
+namespace dfl {
+// One packed forward of n <= 16 tokens at positions start..start+n-1 (the body shared by
+// dfl_packed_verify, dfl_single_token and dfl_prefill).  Leaves argmax/gap/logits/capture on the device.
+dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, const uint32_t* layer_ids, uint32_t n_ids,
+                       const int32_t* tokens, uint32_t n, uint32_t start, bool want_head);
+dfl_status session_guard(const dfl_model* m, dfl_session* s, const char* what);
+}  // namespace dfl

@@ -1,0 +1,137 @@
+// Launchers of the element-wise / recurrent / attention kernels that sit between the
+// weight-streaming GEMMs of one verify or draft pass.  All of them work on the whole block
+// of <= 16 token rows at once and never touch the host.
+#pragma once
+#include "tiles.cuh"
+
+namespace dfl {
+
+#ifdef __CUDACC__
+// Packs four consecutive columns k..k+3 (k % 4 == 0, inside one 256-column block) of one
+// token row into the activation chunk the few-row GEMM consumes.
+__device__ __forceinline__ void pack_quad(uint8_t* chunk, bool bf3, int tok, int k, const float (&v)[4], bool& overflow) {
+    const int pos = act_pos(k);
+    if (!bf3) {
+        uint16_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float f = v[e];
+            overflow |= (fabsf(f) >= 65504.f) && (fabsf(f) < INFINITY);
+            const __half h = __float2half_rn(f);
+            hi[e] = __half_as_ushort(h);
+            lo[e] = __half_as_ushort(__float2half_rn(f - __half2float(h)));
+        }
+        *reinterpret_cast<uint2*>(chunk + (tok * ACT_ROW_HALFS + pos) * 2) =
+            make_uint2((uint32_t)hi[0] | ((uint32_t)hi[1] << 16), (uint32_t)hi[2] | ((uint32_t)hi[3] << 16));
+        *reinterpret_cast<uint2*>(chunk + ACT_PLANE + (tok * ACT_ROW_HALFS + pos) * 2) =
+            make_uint2((uint32_t)lo[0] | ((uint32_t)lo[1] << 16), (uint32_t)lo[2] | ((uint32_t)lo[3] << 16));
+    } else {
+        uint16_t b[3][4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float f = v[e];
+#pragma unroll
+            for (int p = 0; p < 3; ++p) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(f);
+                b[p][e] = __bfloat16_as_ushort(h);
+                f -= __bfloat162float(h);
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < 3; ++p)
+            *reinterpret_cast<uint2*>(chunk + p * ACT_PLANE + (tok * ACT_ROW_HALFS + pos) * 2) =
+                make_uint2((uint32_t)b[p][0] | ((uint32_t)b[p][1] << 16), (uint32_t)b[p][2] | ((uint32_t)b[p][3] << 16));
+    }
+}
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) {
+    if (x > 20.0f) return x;
+    if (x < -20.0f) return expf(x);
+    return logf(1.0f + expf(x));
+}
+#endif
+
+enum GlueMode : int {
+    GLUE_RESID = 0,   // v = x + sum_s part[s]        (x updated in place when x != nullptr)
+    GLUE_SWIGLU = 1,  // v = silu(sum part[:, c]) * sum part[:, F + c]
+    GLUE_COPY = 2     // v = x (read only)
+};
+
+struct GlueParams {
+    int mode = GLUE_RESID;
+    const float* part = nullptr;  // [splits][16][ld_part]
+    int splits = 0;
+    int ld_part = 0;
+    float* x = nullptr;           // [16][ld_x]
+    int ld_x = 0;
+    const float* mul_w = nullptr; // per-column multiplier (a folded RMSNorm weight)
+    float pre_scale = 1.f;
+    uint8_t* acts = nullptr;      // packed output, optional
+    int bf3 = 0;
+    float* xn = nullptr;          // optional f32 copy of the packed value [16][ld_xn]
+    int ld_xn = 0;
+    float* sumsq = nullptr;       // optional [kblocks][16] partial sums of v*v
+    float* capture = nullptr;     // optional copy of v: capture[tok * ld_capture + col]
+    int ld_capture = 0;
+    int swiglu_f = 0;
+    int n_rows = 0;
+    int* err = nullptr;
+};
+// k = number of columns (multiple of 256)
+dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k);
+
+// x[tok][0..h) = decoded row tokens[tok] of a ggml matrix [vocab][h] (kernel_get_rows_*,
+// kernels/elementwise.metal:727-958).  tokens live on the device.
+dfl_status launch_embed_rows(cudaStream_t st, int dtype, const uint8_t* ggml, uint64_t h, const int32_t* tokens, int n_rows,
+                             float* x, int ld);
+
+// out[tok][j] = rs[tok] * sum_k xn[tok][k] * w[j][k] for small f32 matrices (GDN alpha/beta, MoE router).
+dfl_status launch_small_matmul(cudaStream_t st, const float* w, const float* xn, int ld_xn, int n_rows, uint64_t k, int n_out,
+                               const GemmEpilogue& ep, float* out, int ld_out);
+
+// ---- attention (attn.cu) -------------------------------------------------------
+struct AttnGeom {
+    int n_q, n_kv, hd, n_rot;
+    float theta, eps;
+};
+constexpr int ATTN_CHUNK = 64;
+// Reduces the fused q|k|v GEMM partials, applies per-head RMSNorm + partial NeoX RoPE, appends K/V
+// at positions start..start+n_rows-1 and leaves rotated Q and the raw gate for the attention kernel.
+// gated: q rows are interleaved (q, gate) per head as in the target; otherwise plain q.
+dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, const float* part, int splits, int ld_part,
+                             const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
+                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override);
+// Causal attention of the n_rows query rows over cache positions [0, start + row]; partials per
+// 64-position chunk, then combine, sigmoid gate and activation packing for the o-projection.
+dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
+                              const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts,
+                              bool bf3, float* out_f32, int* err);
+uint64_t attn_partials_floats(const AttnGeom& g, uint32_t max_positions);
+
+// ---- gated delta net (gdn.cu) --------------------------------------------------
+struct GdnGeom {
+    int n_v, n_k, hd, conv_k;  // hd must be 128, conv_k 4
+    __host__ __device__ int conv_dim() const { return (2 * n_k + n_v) * hd; }
+};
+// conv1d + SiLU over the block, q/k L2 norm; keeps raw qkv rows for rollback; updates conv state in place.
+dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
+                            const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v);
+// Sequential delta-rule scan over n_rows tokens from state_in to state_out (different buffers).
+dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state_in, float* state_out, const float* q_n,
+                           const float* k_n, const float* v, const float* ab, const float* dt_bias, const float* a_log,
+                           int n_rows, float* o);
+// y = rmsnorm(o; eps*hd) * w * silu(z), z = sum of the z-GEMM partials; packs activations for out_proj.
+dfl_status launch_gdn_post(cudaStream_t st, const GdnGeom& g, const float* o, const float* part_z, int splits, int ld_part,
+                           const float* norm_w, int n_rows, uint8_t* acts, bool bf3, int* err);
+// conv state := last (conv_k-1) rows of {pre-block conv rows, raw qkv rows 0..n_keep-1}
+dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const float* conv_pre, const float* qkv_raw, int n_keep,
+                                   float* conv_state);
+
+// ---- drafter attention (drafter_attn.cu) ---------------------------------------
+dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
+                               const int32_t* pos_ctx, int ctx_begin, int ctx_len, const float* k_noise, const float* v_noise,
+                               uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts,
+                               bool bf3, int* err);
+
+}  // namespace dfl

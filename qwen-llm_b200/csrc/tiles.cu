@@ -6,30 +6,6 @@
 
 namespace dfl {
 
-// ---- integer quant of weight i (0..255) of one ggml block -------------------
-// Q4_K block: {f16 d, f16 dmin, u8 scales[12], u8 qs[128]}  (kernels/mat_vec_q4_k.metal:13-20)
-__device__ __forceinline__ uint32_t q4k_src_q(const uint8_t* blk, int i) {
-    const int c = i >> 6, l = i & 31, hi = (i >> 5) & 1;
-    const uint8_t b = blk[16 + 32 * c + l];
-    return hi ? (b >> 4) : (b & 15);
-}
-// Q5_K block: {d, dmin, scales[12], qh[32], qs[128]}  (kernels/mat_mat_fewrow_gen.metal:72-106)
-__device__ __forceinline__ uint32_t q5k_src_q(const uint8_t* blk, int i) {
-    const int c = i >> 6, l = i & 31, hi = (i >> 5) & 1;
-    const uint8_t b = blk[48 + 32 * c + l];
-    const uint32_t nib = hi ? (b >> 4) : (b & 15);
-    const uint32_t hb = (blk[16 + l] >> (2 * c + hi)) & 1;
-    return nib | (hb << 4);
-}
-// Q6_K block: {ql[128], qh[64], i8 scales[16], f16 d}  (kernels/mat_vec_q6_k.metal:5-12)
-__device__ __forceinline__ uint32_t q6k_src_q(const uint8_t* blk, int i) {
-    const int n = i >> 7, rem = i & 127, quarter = rem >> 5, l = rem & 31;
-    const uint8_t qlb = blk[64 * n + l + ((quarter & 1) ? 32 : 0)];
-    const uint32_t nib = quarter >= 2 ? (qlb >> 4) : (qlb & 15);
-    const uint32_t h2 = (blk[128 + 32 * n + l] >> (2 * quarter)) & 3;
-    return nib | (h2 << 4);
-}
-
 // One thread per (row in tile, warp slot w, lane slot t): the 8 weights
 // k = 32w + 16s + 4t + e of one 256-column block.
 template <int DT>
@@ -149,11 +125,6 @@ dfl_status retile_matrix(cudaStream_t st, int dtype, const uint8_t* ggml_dev, ui
 }
 
 // ---- decode: resident tiles -> f32, ggml operation order ----------------------
-__device__ __forceinline__ void k4_scale_min(const uint8_t* q, int j, uint32_t& sc, uint32_t& m) {
-    if (j < 4) { sc = q[j] & 63; m = q[j + 4] & 63; }
-    else { sc = (q[j + 4] & 0x0f) | ((q[j - 4] >> 6) << 4); m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
-}
-
 __global__ void decode_tiles_kernel(const uint8_t* __restrict__ tiles, int dtype, uint64_t n_in, uint64_t n_out, int kblocks,
                                     float* __restrict__ out) {
     const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;

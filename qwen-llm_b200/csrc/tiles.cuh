@@ -89,6 +89,67 @@ __host__ __device__ inline int act_pos(int k) {
     return 32 * w + 8 * t + 4 * s + e;
 }
 
+#ifdef __CUDACC__
+// ---- integer quant of weight i (0..255) of one ggml block -------------------
+// Q4_K block: {f16 d, f16 dmin, u8 scales[12], u8 qs[128]}  (kernels/mat_vec_q4_k.metal:13-20)
+__device__ __forceinline__ uint32_t q4k_src_q(const uint8_t* blk, int i) {
+    const int c = i >> 6, l = i & 31, hi = (i >> 5) & 1;
+    const uint8_t b = blk[16 + 32 * c + l];
+    return hi ? (b >> 4) : (b & 15);
+}
+// Q5_K block: {d, dmin, scales[12], qh[32], qs[128]}  (kernels/mat_mat_fewrow_gen.metal:72-106)
+__device__ __forceinline__ uint32_t q5k_src_q(const uint8_t* blk, int i) {
+    const int c = i >> 6, l = i & 31, hi = (i >> 5) & 1;
+    const uint8_t b = blk[48 + 32 * c + l];
+    const uint32_t nib = hi ? (b >> 4) : (b & 15);
+    const uint32_t hb = (blk[16 + l] >> (2 * c + hi)) & 1;
+    return nib | (hb << 4);
+}
+// Q6_K block: {ql[128], qh[64], i8 scales[16], f16 d}  (kernels/mat_vec_q6_k.metal:5-12)
+__device__ __forceinline__ uint32_t q6k_src_q(const uint8_t* blk, int i) {
+    const int n = i >> 7, rem = i & 127, quarter = rem >> 5, l = rem & 31;
+    const uint8_t qlb = blk[64 * n + l + ((quarter & 1) ? 32 : 0)];
+    const uint32_t nib = quarter >= 2 ? (qlb >> 4) : (qlb & 15);
+    const uint32_t h2 = (blk[128 + 32 * n + l] >> (2 * quarter)) & 3;
+    return nib | (h2 << 4);
+}
+
+__device__ __forceinline__ void k4_scale_min(const uint8_t* q, int j, uint32_t& sc, uint32_t& m) {
+    if (j < 4) { sc = q[j] & 63; m = q[j + 4] & 63; }
+    else { sc = (q[j + 4] & 0x0f) | ((q[j - 4] >> 6) << 4); m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+}
+
+// Decoded f32 value of element k (0..255) of one ggml block segment, ggml operation order
+// (kernels/mat_vec_q4_k.metal:13-20, mat_vec_q6_k.metal:5-12, mat_vec_q8_0.metal:3-9).
+__device__ __forceinline__ float ggml_decode_elem(int dtype, const uint8_t* seg256, int k) {
+    switch (dtype) {
+        case DFL_Q4_K:
+        case DFL_Q5_K: {
+            const float d = __half2float(__ushort_as_half((unsigned short)(seg256[0] | (seg256[1] << 8))));
+            const float dmin = __half2float(__ushort_as_half((unsigned short)(seg256[2] | (seg256[3] << 8))));
+            uint32_t sc, m;
+            k4_scale_min(seg256 + 4, k >> 5, sc, m);
+            const uint32_t q = dtype == DFL_Q4_K ? q4k_src_q(seg256, k) : q5k_src_q(seg256, k);
+            return __fsub_rn(__fmul_rn(d * (float)sc, (float)q), dmin * (float)m);
+        }
+        case DFL_Q6_K: {
+            const float d = __half2float(__ushort_as_half((unsigned short)(seg256[208] | (seg256[209] << 8))));
+            const int8_t sc = (int8_t)seg256[192 + (k >> 4)];
+            return __fmul_rn(__fmul_rn(d, (float)sc), (float)((int)q6k_src_q(seg256, k) - 32));
+        }
+        case DFL_Q8_0: {
+            const uint8_t* b = seg256 + 34 * (k >> 5);
+            const float d = __half2float(__ushort_as_half((unsigned short)(b[0] | (b[1] << 8))));
+            return __fmul_rn((float)(int8_t)b[2 + (k & 31)], d);
+        }
+        case DFL_BF16: return __uint_as_float(((uint32_t)seg256[2 * k] | ((uint32_t)seg256[2 * k + 1] << 8)) << 16);
+        case DFL_F16: return __half2float(__ushort_as_half((unsigned short)(seg256[2 * k] | (seg256[2 * k + 1] << 8))));
+        case DFL_F32: return reinterpret_cast<const float*>(seg256)[k];
+        default: return 0.f;
+    }
+}
+#endif  // __CUDACC__
+
 // A resident matrix.
 struct QMatrix {
     int device = 0;
@@ -122,8 +183,10 @@ struct GemmEpilogue {
 };
 int gemm_choose_splits(const QMatrix& m);
 // out: [splits][16][n_out] f32 partial sums (sum over the first axis in order 0..splits-1).
+// ld_out: row length of `out` (0 = n_out); a wider buffer lets several matrices with the
+// same input write side by side (out then points at this matrix's first column).
 dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits,
-                              const GemmEpilogue& ep, int* dev_err, bool pdl);
+                              const GemmEpilogue& ep, int* dev_err, bool pdl, uint32_t ld_out = 0);
 // x [n_rows][ld] f32 -> packed activations for a matrix of `dtype`; rows >= n_rows are zero.
 // pre_scale multiplies x before the f16 split (a power of two keeps it exact).
 dfl_status launch_prep_acts(cudaStream_t st, int weight_dtype, const float* x, int ld, int n_rows, uint64_t k,

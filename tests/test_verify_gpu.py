@@ -1,0 +1,166 @@
+"""Packed verify / single token / rollback of the hybrid target against the CPU oracle
+(the reference's model-witness tests, crates/qwen-llm/src/metal_dflash/tests.rs:5887-7700, restated on a
+seeded synthetic model)."""
+import numpy as np
+import pytest
+
+import modelgen
+import orc
+from dflb import pkg
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-2, 1e-3  # logits contract
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    arch = modelgen.tiny_arch()
+    T = modelgen.target_tensors(arch, seed=3)
+    om = modelgen.OracleModel(arch, T)
+    gm = pkg.Model(arch, T)
+    yield arch, om, gm
+    gm.close()
+
+
+def oracle_block(om, st, tokens, start, layer_ids):
+    logits, caps = [], []
+    for i, t in enumerate(tokens):
+        l, c = om.single_token(st, t, start + i, layer_ids)
+        logits.append(l)
+        caps.append(c)
+    return np.stack(logits), np.stack(caps)
+
+
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_packed_verify_matches_oracle(tiny, kv_f16):
+    arch, om, gm = tiny
+    rng = np.random.default_rng(1)
+    layer_ids = [0, 2, 3]
+    sess = pkg.Session(gm, 64, kv_f16)
+    scr = pkg.Scratch(gm, 16, len(layer_ids))
+    ost = om.new_state(64, kv_f16)
+    start = 0
+    for n in (16, 5, 16, 1):
+        tokens = rng.integers(0, arch.vocab_size, size=n)
+        want_logits, want_cap = oracle_block(om, ost, tokens, start, layer_ids)
+        am, gap, logits = pkg.packed_verify(gm, sess, scr, layer_ids, tokens, start, want_logits=True)
+        np.testing.assert_allclose(logits, want_logits, rtol=RTOL, atol=ATOL)
+        cap = scr.read_capture(n)
+        np.testing.assert_allclose(cap, want_cap, rtol=RTOL, atol=ATOL)
+        want_arg = np.array([orc.greedy_token(r) for r in want_logits])
+        s = np.sort(want_logits, axis=1)
+        safe = (s[:, -1] - s[:, -2]) > 1e-4       # rows whose argmax is not a near tie in the oracle
+        assert np.array_equal(am[safe], want_arg[safe])
+        np.testing.assert_allclose(gap, s[:, -1] - s[:, -2], rtol=0, atol=2e-3)
+        start += n
+        assert sess.kv_n_pos == start
+    # state parity
+    for gi in range(3):
+        ssm, conv = sess.read_gdn_state(gi)
+        wssm, wconv = om.read_gdn(ost, gi)
+        np.testing.assert_allclose(ssm, wssm, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(conv, wconv, rtol=RTOL, atol=ATOL)
+    k, v = sess.read_kv(0, start - 1)
+    wk, wv = om.read_kv(ost, 0, start - 1)
+    np.testing.assert_allclose(k, wk, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(v, wv, rtol=RTOL, atol=ATOL)
+    sess.close(); scr.close()
+
+
+def test_packed_verify_equals_single_token_steps_bitwise(tiny):
+    # tests.rs:5887+: packed verify argmax == N single tokens, bitwise state
+    arch, om, gm = tiny
+    rng = np.random.default_rng(2)
+    tokens = rng.integers(0, arch.vocab_size, size=16)
+    a, sa = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 1)
+    b, sb = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 1)
+    _, _, packed = pkg.packed_verify(gm, a, sa, [3], tokens, 0, want_logits=True)
+    for i, t in enumerate(tokens):
+        logits, _ = pkg.single_token(gm, b, sb, [3], t, i)
+        assert logits.tobytes() == packed[i].tobytes(), f"row {i}"
+    for gi in range(3):
+        s1, c1 = a.read_gdn_state(gi)
+        s2, c2 = b.read_gdn_state(gi)
+        assert s1.tobytes() == s2.tobytes() and c1.tobytes() == c2.tobytes()
+    for x in (a, sa, b, sb):
+        x.close()
+
+
+@pytest.mark.parametrize("n_keep", [1, 8, 15, 16])
+def test_restore_then_marker_equals_sequential(tiny, n_keep):
+    # tests.rs:6949-7110: restore(n_keep) then one marker token == n_keep sequential tokens then marker
+    arch, om, gm = tiny
+    rng = np.random.default_rng(5)
+    warm = rng.integers(0, arch.vocab_size, size=7)
+    tokens = rng.integers(0, arch.vocab_size, size=16)
+    marker = 17
+    a, sa = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 0)
+    b, sb = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 0)
+    pkg.packed_verify(gm, a, sa, [], warm, 0)
+    pkg.packed_verify(gm, b, sb, [], warm, 0)
+    pkg.packed_verify(gm, a, sa, [], tokens, 7)
+    pkg.restore_partial(gm, a, sa, n_keep, 7)
+    assert a.kv_n_pos == 7 + n_keep
+    pkg.packed_verify(gm, b, sb, [], tokens[:n_keep], 7)
+    la, _ = pkg.single_token(gm, a, sa, [], marker, 7 + n_keep)
+    lb, _ = pkg.single_token(gm, b, sb, [], marker, 7 + n_keep)
+    assert la.tobytes() == lb.tobytes()
+    for gi in range(3):
+        s1, c1 = a.read_gdn_state(gi)
+        s2, c2 = b.read_gdn_state(gi)
+        assert s1.tobytes() == s2.tobytes() and c1.tobytes() == c2.tobytes()
+    for x in (a, sa, b, sb):
+        x.close()
+
+
+def test_restore_pre_block_and_guard_walls(tiny):
+    arch, om, gm = tiny
+    rng = np.random.default_rng(6)
+    tokens = rng.integers(0, arch.vocab_size, size=16)
+    a, sa = pkg.Session(gm, 32), pkg.Scratch(gm, 16, 0)
+    s0, c0 = a.read_gdn_state(0)
+    _, _, l1 = pkg.packed_verify(gm, a, sa, [], tokens, 0, want_logits=True)
+    pkg.restore_pre_block(gm, a, sa, 0)
+    assert a.kv_n_pos == 0
+    s1, c1 = a.read_gdn_state(0)
+    assert s0.tobytes() == s1.tobytes() and c0.tobytes() == c1.tobytes()
+    _, _, l2 = pkg.packed_verify(gm, a, sa, [], tokens, 0, want_logits=True)
+    assert l1.tobytes() == l2.tobytes()
+    # guard wall: start must equal kv_n_pos, capacity, token range, n_keep range
+    for bad_start in (0, 17):
+        with pytest.raises(pkg.DflError) as e:
+            pkg.packed_verify(gm, a, sa, [], tokens, bad_start)
+        assert e.value.name == "KV_STATE"
+    with pytest.raises(pkg.DflError) as e:
+        pkg.packed_verify(gm, a, sa, [], np.r_[tokens, [1]], 16)
+    assert e.value.name == "BAD_SHAPE"
+    bad = tokens.copy()
+    bad[3] = arch.vocab_size
+    with pytest.raises(pkg.DflError) as e:
+        pkg.packed_verify(gm, a, sa, [], bad, 16)
+    assert e.value.name == "BAD_TOKEN"
+    pkg.packed_verify(gm, a, sa, [], tokens, 16)         # 16 + 16 == capacity: fits
+    with pytest.raises(pkg.DflError) as e:
+        pkg.packed_verify(gm, a, sa, [], tokens[:1], 32)  # one past capacity
+    assert e.value.name == "KV_STATE"
+    for bad_keep in (0, 17):
+        with pytest.raises(pkg.DflError) as e:
+            pkg.restore_partial(gm, a, sa, bad_keep, 16)
+        assert e.value.name == "BAD_SHAPE"
+    assert not a.poisoned and a.kv_n_pos == 32
+    a.close(); sa.close()
+
+
+def test_injected_completion_failure_poisons_session(tiny):
+    # metal/completion.rs:41-66 + metal_forward/mod.rs:2161-2170
+    arch, om, gm = tiny
+    a, sa = pkg.Session(gm, 32), pkg.Scratch(gm, 16, 0)
+    a.fail_next_completion()
+    with pytest.raises(pkg.DflError):
+        pkg.packed_verify(gm, a, sa, [], [1, 2, 3], 0)
+    assert a.poisoned
+    with pytest.raises(pkg.DflError) as e:
+        pkg.packed_verify(gm, a, sa, [], [1, 2, 3], 3)
+    assert e.value.name == "POISONED"
+    a.close(); sa.close()
