@@ -282,11 +282,20 @@ dfl_status dfl_sampler_create(const dfl_sampling_config* cfg, dfl_sampler** out)
 dfl_status dfl_sampler_create_at_draw(const dfl_sampling_config* cfg, uint64_t draws,
                                       dfl_sampler** out);
 void dfl_sampler_destroy(dfl_sampler* s);
+/* Sampler::config  sampling.rs:369 */
+void dfl_sampler_get_config(const dfl_sampler* s, dfl_sampling_config* out);
 uint64_t dfl_sampler_draws(const dfl_sampler* s);
 void dfl_sampler_rng_state(const dfl_sampler* s, uint64_t out_state[4]);
 /* Sampler::sample  sampling.rs:530 */
 dfl_status dfl_sampler_sample(dfl_sampler* s, const float* logits, uint64_t vocab,
                               int32_t* token_out, uint64_t* candidate_index_out);
+/* Sampler::sample_with_distribution  sampling.rs:437-452: samples and also returns the
+ * filtered categorical distribution (tokens / unnormalised weights in categorical order,
+ * at most `cap` entries; *count receives the full length). */
+dfl_status dfl_sampler_sample_with_distribution(dfl_sampler* s, const float* logits, uint64_t vocab,
+                                                int32_t* token_out, uint64_t* candidate_index_out,
+                                                int32_t* dist_tokens, double* dist_weights,
+                                                uint64_t cap, uint64_t* count, double* total_weight);
 /* greedy_token  sampling.rs:1159-1181 */
 dfl_status dfl_greedy_token(const float* logits, uint64_t vocab, int32_t* token_out);
 /* raw generator access for golden-vector checks (sampling.rs:1621-1670) */

@@ -331,3 +331,192 @@ def single_token(model, session, scratch, layer_ids, token, position, want_hidde
                                  C.c_int32(int(token)), C.c_uint32(position), _ptr(logits),
                                  _ptr(hidden) if hidden is not None else None))
     return logits, hidden
+
+
+# ---------------------------------------------------------------------------
+# sampler + acceptance (host)
+# ---------------------------------------------------------------------------
+class Sampler:
+    def __init__(self, temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, seed=0, at_draw=None):
+        self.cfg = SamplingConfig(temperature, top_k, top_p, min_p, seed & ((1 << 64) - 1))
+        self.h = C.c_void_p()
+        if at_draw is None:
+            check(lib().dfl_sampler_create(C.byref(self.cfg), C.byref(self.h)))
+        else:
+            check(lib().dfl_sampler_create_at_draw(C.byref(self.cfg), C.c_uint64(at_draw), C.byref(self.h)))
+
+    def close(self):
+        if self.h:
+            lib().dfl_sampler_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def draws(self):
+        return int(lib().dfl_sampler_draws(self.h))
+
+    def rng_state(self):
+        st = (C.c_uint64 * 4)()
+        lib().dfl_sampler_rng_state(self.h, st)
+        return list(st)
+
+    def next_u64(self):
+        return int(lib().dfl_sampler_next_u64(self.h))
+
+    def next_unit_f64(self):
+        return float(lib().dfl_sampler_next_unit_f64(self.h))
+
+    def sample(self, logits):
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        tok, idx = C.c_int32(0), C.c_uint64(0)
+        check(lib().dfl_sampler_sample(self.h, _ptr(logits), C.c_uint64(logits.size), C.byref(tok), C.byref(idx)))
+        return int(tok.value), int(idx.value)
+
+    def couple_sparse(self, logits, token, candidates):
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        ct = np.ascontiguousarray([c[0] for c in candidates], dtype=np.int32)
+        cw = np.ascontiguousarray([c[1] for c in candidates], dtype=np.float64)
+        acc, corr = C.c_int32(0), C.c_int32(0)
+        check(lib().dfl_sampler_couple_sparse(self.h, _ptr(logits), C.c_uint64(logits.size), C.c_int32(token), _ptr(ct), _ptr(cw),
+                                              C.c_uint32(ct.size), C.byref(acc), C.byref(corr)))
+        return ("accepted", None) if acc.value else ("rejected", int(corr.value))
+
+
+def splitmix64_stream(seed, n):
+    st = C.c_uint64(seed)
+    return [int(lib().dfl_splitmix64_next(C.byref(st))) for _ in range(n)]
+
+
+def greedy_token(logits):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    tok = C.c_int32(0)
+    check(lib().dfl_greedy_token(_ptr(logits), C.c_uint64(logits.size), C.byref(tok)))
+    return int(tok.value)
+
+
+def accept_prefix(verified_tokens, target_logits, vocab, proposals, sampler, remaining_output_budget, stop_ids):
+    """proposals: None or list of (token, [(cand_token, weight), ...]).  Returns AcceptDecision as a dict."""
+    vt = np.ascontiguousarray(verified_tokens, dtype=np.int32)
+    tl = np.ascontiguousarray(target_logits, dtype=np.float32).reshape(-1)
+    stops = np.ascontiguousarray(stop_ids, dtype=np.int32)
+    sp = None
+    keep = []
+    if proposals is not None:
+        toks = np.ascontiguousarray([p[0] for p in proposals], dtype=np.int32)
+        offs = np.zeros(len(proposals) + 1, dtype=np.uint32)
+        ct, cw = [], []
+        for i, p in enumerate(proposals):
+            for t, w in p[1]:
+                ct.append(t)
+                cw.append(w)
+            offs[i + 1] = len(ct)
+        ct = np.ascontiguousarray(ct, dtype=np.int32)
+        cw = np.ascontiguousarray(cw, dtype=np.float64)
+        keep = [toks, offs, ct, cw]
+        sp = SparseProposals(len(proposals), _ptr(toks, C.POINTER(C.c_int32)), _ptr(offs, C.POINTER(C.c_uint32)),
+                             _ptr(ct, C.POINTER(C.c_int32)), _ptr(cw, C.POINTER(C.c_double)))
+    out = AcceptDecision()
+    vocab = int(vocab) & ((1 << 64) - 1)
+    check(lib().dfl_accept_prefix(_ptr(vt) if vt.size else None, C.c_uint32(vt.size), _ptr(tl) if tl.size else None, C.c_uint64(tl.size),
+                                  C.c_uint64(vocab), C.byref(sp) if sp is not None else None, sampler.h,
+                                  C.c_uint64(remaining_output_budget), _ptr(stops) if stops.size else None, C.c_uint32(stops.size),
+                                  C.byref(out)))
+    kinds = {0: None, 1: "correction", 2: "bonus"}
+    stopsn = {0: None, 1: "eos", 2: "token_limit"}
+    return {"accepted_drafts": list(out.accepted_drafts[:out.n_accepted]),
+            "next_carry": (kinds[out.next_carry_kind], out.next_carry) if out.next_carry_kind else None,
+            "stop_reason": stopsn[out.stop_reason], "retain_input_count": int(out.retain_input_count), "error_row": out.error_row}
+
+
+# ---------------------------------------------------------------------------
+# drafter / drafter session / outer loop
+# ---------------------------------------------------------------------------
+class Drafter:
+    def __init__(self, target: Model, cfg: DFlashConfig, tensors):
+        arr, keep = make_tensor_table(tensors)
+        self.target, self.cfg = target, cfg
+        self.h = C.c_void_p()
+        check(lib().dfl_drafter_create(target.h, C.byref(cfg), arr, C.c_uint64(len(tensors)), C.byref(self.h)))
+
+    def weight_bytes(self):
+        return int(lib().dfl_drafter_weight_bytes(self.h))
+
+    def layer_ids(self):
+        return [int(self.cfg.target_layer_ids[i]) for i in range(self.cfg.n_target_layers)]
+
+    def close(self):
+        if self.h:
+            lib().dfl_drafter_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class DSession:
+    def __init__(self, drafter: Drafter, ctx_capacity):
+        self.drafter = drafter
+        self.h = C.c_void_p()
+        check(lib().dfl_dsession_create(drafter.h, C.c_uint32(ctx_capacity), C.byref(self.h)))
+
+    @property
+    def ctx_len(self):
+        return int(lib().dfl_dsession_ctx_len(self.h))
+
+    def append_columns(self, cols, positions):
+        cols = np.ascontiguousarray(cols, dtype=np.float32)
+        pos = np.ascontiguousarray(positions, dtype=np.uint32)
+        check(lib().dfl_dsession_append_columns_host(self.h, _ptr(cols), _ptr(pos), C.c_uint32(pos.size)))
+
+    def append_from_scratch(self, scratch, first_row, count, first_position):
+        check(lib().dfl_dsession_append_from_scratch(self.h, scratch.h, C.c_uint32(first_row), C.c_uint32(count), C.c_uint32(first_position)))
+
+    def reset(self):
+        check(lib().dfl_dsession_reset(self.h))
+
+    def draft_block(self, carry, noise_start_pos, want_logits=False):
+        n = self.drafter.cfg.block_size
+        out = np.zeros(n, dtype=np.int32)
+        logits = np.zeros((n, self.drafter.target.arch.vocab_size), dtype=np.float32) if want_logits else None
+        check(lib().dfl_draft_block(self.h, C.c_int32(int(carry)), C.c_uint32(noise_start_pos), _ptr(out),
+                                    _ptr(logits) if want_logits else None))
+        return out, logits
+
+    def close(self):
+        if self.h:
+            lib().dfl_dsession_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+def prefill(model, session, scratch, layer_ids, ids, start_position=0, feed_drafter=None, want_hidden=False, want_logits=True):
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    lids = _u32(layer_ids)
+    hidden = np.zeros((ids.size, scratch.k, model.arch.hidden_size), dtype=np.float32) if want_hidden else None
+    logits = np.zeros(model.arch.vocab_size, dtype=np.float32) if want_logits else None
+    check(lib().dfl_prefill(model.h, session.h, scratch.h, _ptr(lids) if lids.size else None, C.c_uint32(lids.size), _ptr(ids),
+                            C.c_uint64(ids.size), C.c_uint32(start_position), feed_drafter.h if feed_drafter is not None else None,
+                            _ptr(hidden) if want_hidden else None, _ptr(logits) if want_logits else None))
+    return logits, hidden
+
+
+def generate(model, session, scratch, dsession, sampler, first_logits, max_tokens, stop_ids=(), replay_history=None,
+             sparse_proposals=False, verify_margin=0.0):
+    first_logits = np.ascontiguousarray(first_logits, dtype=np.float32)
+    stops = np.ascontiguousarray(stop_ids, dtype=np.int32)
+    hist = np.ascontiguousarray(replay_history, dtype=np.int32) if replay_history is not None else None
+    p = GenerateParams()
+    p.max_tokens = max_tokens
+    p.stop_ids = _ptr(stops, C.POINTER(C.c_int32)) if stops.size else None
+    p.n_stop_ids = stops.size
+    p.replay_history = _ptr(hist, C.POINTER(C.c_int32)) if hist is not None else None
+    p.n_replay_history = hist.size if hist is not None else 0
+    p.sparse_proposals = 1 if sparse_proposals else 0
+    p.verify_margin = verify_margin
+    out = np.zeros(max_tokens, dtype=np.int32)
+    n = C.c_uint32(0)
+    stats = GenerateStats()
+    check(lib().dfl_generate(model.h, session.h, scratch.h, dsession.h, sampler.h, _ptr(first_logits), C.byref(p), _ptr(out), C.byref(n),
+                             C.byref(stats)))
+    return out[:n.value].copy(), stats

@@ -16,7 +16,7 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
                                                          int ld_part, const float* __restrict__ q_norm_w,
                                                          const float* __restrict__ k_norm_w, uint32_t start, void* k_cache,
                                                          void* v_cache, int kv_f16, float* __restrict__ q_rot,
-                                                         float* __restrict__ gate, const uint32_t* __restrict__ pos_override) {
+                                                         float* __restrict__ gate, const uint32_t* __restrict__ pos_override, long long cache_row0) {
     extern __shared__ float sh[];  // [hd] values, then 4 partial sums
     const int head = blockIdx.x, tok = blockIdx.y, hd = g.hd;
     const int q_stride = gated ? 2 * hd : hd;
@@ -25,7 +25,8 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
     if (head < g.n_q) { kind = 0; h = head; col0 = h * q_stride; }
     else if (head < g.n_q + g.n_kv) { kind = 1; h = head - g.n_q; col0 = q_cols + h * hd; }
     else { kind = 2; h = head - g.n_q - g.n_kv; col0 = q_cols + kv_cols + h * hd; }
-    const uint32_t pos = pos_override ? pos_override[tok] : start + (uint32_t)tok;
+    const uint32_t pos = pos_override ? pos_override[tok] : start + (uint32_t)tok;  // RoPE position
+    const uint64_t crow = cache_row0 >= 0 ? (uint64_t)cache_row0 + tok : pos;         // cache row
     float ss = 0.f;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float v = 0.f, gt = 0.f;
@@ -43,7 +44,7 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
     __syncthreads();
     if (kind == 2) {
         for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-            const uint64_t o = ((uint64_t)pos * g.n_kv + h) * hd + d;
+            const uint64_t o = (crow * g.n_kv + h) * hd + d;
             if (kv_f16) reinterpret_cast<__half*>(v_cache)[o] = __float2half_rn(sh[d]);
             else reinterpret_cast<float*>(v_cache)[o] = sh[d];
         }
@@ -69,7 +70,7 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
         }
         if (kind == 0) q_rot[((uint64_t)tok * g.n_q + h) * hd + d] = out;
         else {
-            const uint64_t o = ((uint64_t)pos * g.n_kv + h) * hd + d;
+            const uint64_t o = (crow * g.n_kv + h) * hd + d;
             if (kv_f16) reinterpret_cast<__half*>(k_cache)[o] = __float2half_rn(out);
             else reinterpret_cast<float*>(k_cache)[o] = out;
         }
@@ -78,10 +79,10 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
 
 dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, const float* part, int splits, int ld_part,
                              const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
-                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override) {
+                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override, long long cache_row0) {
     dim3 grid((unsigned)(g.n_q + 2 * g.n_kv), (unsigned)n_rows);
     attn_front_kernel<<<grid, 128, (g.hd + 4) * sizeof(float), st>>>(g, gated ? 1 : 0, part, splits, ld_part, q_norm_w, k_norm_w, start,
-                                                                   k_cache, v_cache, kv_f16 ? 1 : 0, q_rot, gate, pos_override);
+                                                                   k_cache, v_cache, kv_f16 ? 1 : 0, q_rot, gate, pos_override, cache_row0);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -1,0 +1,617 @@
+// DFlash block-diffusion drafter: resident head, per-request drafter session and one draft
+// pass (reference: MetalDFlashHead::load / MetalDFlashSession / draft_block_inner,
+// crates/qwen-llm/src/metal_dflash.rs:4944-5050, :5492-5816, :15952-17164; oracle
+// Forward::dflash_draft, crates/qwen-llm/src/forward.rs:380-662; attention mask
+// kernels/dflash_attn.metal:99-103).
+//
+// The context side is incremental, as in the reference (watermark ctx_h_ready_n / kv_ctx_ready_n,
+// metal_dflash.rs:16045-16143): fc + hidden_norm and every layer's K/V projection, K-norm and
+// RoPE run once per appended context column and are kept in per-layer caches; a draft call only
+// projects what was appended since the last call.
+#include <algorithm>
+#include <cstring>
+
+#include "model.cuh"
+
+namespace dfl {
+
+struct DLayerW {
+    float *attn_norm_w = nullptr, *post_norm_w = nullptr, *q_norm_w = nullptr, *k_norm_w = nullptr;
+    MatGroup qkv, kv, wo, gate_up, down;
+    bool is_swa = false;
+};
+
+// ---- drafter attention: queries = noise rows, keys = context cache || noise rows -----------
+// allowed(q_pos, k_pos) = (!causal || k_pos <= q_pos) && (!swa || window == 0 || |q - k| < window)
+template <int HD>
+__global__ void __launch_bounds__(256) dattn_chunk_kernel(AttnGeom g, const float* __restrict__ q_rot, const float* __restrict__ k_ctx,
+                                                          const float* __restrict__ v_ctx, const uint32_t* __restrict__ pos_ctx, int ctx_begin,
+                                                          int n_ctx, const float* __restrict__ k_noise, const float* __restrict__ v_noise,
+                                                          uint32_t noise_start, int n_rows, int causal, uint32_t window,
+                                                          float* __restrict__ partials) {
+    extern __shared__ float sm[];
+    constexpr int LD = HD + 1;
+    float* ks = sm;
+    float* vs = ks + ATTN_CHUNK * LD;
+    float* qs = vs + ATTN_CHUNK * LD;
+    float* ps = qs + 8 * HD;
+    __shared__ uint32_t kpos[ATTN_CHUNK];
+    const int chunk = blockIdx.x, kvh = blockIdx.y;
+    const int group = g.n_q / g.n_kv;
+    const int n_keys = n_ctx + n_rows;
+    const int j0 = chunk * ATTN_CHUNK;
+    const int n_here = min(ATTN_CHUNK, n_keys - j0);
+    for (int idx = threadIdx.x; idx < ATTN_CHUNK * HD; idx += blockDim.x) {
+        const int kp = idx / HD, d = idx % HD;
+        float kv = 0.f, vv = 0.f;
+        if (kp < n_here) {
+            const int j = j0 + kp;
+            if (j < n_ctx) {
+                const uint64_t o = ((uint64_t)(ctx_begin + j) * g.n_kv + kvh) * HD + d;
+                kv = k_ctx[o];
+                vv = v_ctx[o];
+            } else {
+                const uint64_t o = ((uint64_t)(j - n_ctx) * g.n_kv + kvh) * HD + d;
+                kv = k_noise[o];
+                vv = v_noise[o];
+            }
+        }
+        ks[kp * LD + d] = kv;
+        vs[kp * LD + d] = vv;
+    }
+    if (threadIdx.x < ATTN_CHUNK) {
+        const int j = j0 + threadIdx.x;
+        kpos[threadIdx.x] = j < n_ctx ? pos_ctx[ctx_begin + j] : noise_start + (uint32_t)(j - n_ctx);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float scale = 1.0f / sqrtf((float)HD);
+    const int n_queries = n_rows * group;
+    float* myq = qs + warp * HD;
+    float* myp = ps + warp * ATTN_CHUNK;
+    for (int qi = warp; qi < n_queries; qi += 8) {
+        const int row = qi / group, qh = kvh * group + qi % group;
+        const float* qsrc = q_rot + ((uint64_t)row * g.n_q + qh) * HD;
+        for (int d = lane; d < HD; d += 32) myq[d] = qsrc[d];
+        __syncwarp();
+        const uint32_t q_pos = noise_start + (uint32_t)row;
+        float s0 = 0.f, s1 = 0.f;
+        const float* k0 = ks + lane * LD;
+        const float* k1 = ks + (lane + 32) * LD;
+#pragma unroll 8
+        for (int d = 0; d < HD; ++d) {
+            const float qv = myq[d];
+            s0 = fmaf(qv, k0[d], s0);
+            s1 = fmaf(qv, k1[d], s1);
+        }
+        s0 *= scale;
+        s1 *= scale;
+        auto allowed = [&](int kp) {
+            if (kp >= n_here) return false;
+            const uint32_t kpv = kpos[kp];
+            const uint32_t diff = q_pos > kpv ? q_pos - kpv : kpv - q_pos;
+            return (!causal || kpv <= q_pos) && (window == 0 || diff < window);
+        };
+        const bool ok0 = allowed(lane), ok1 = allowed(lane + 32);
+        if (!ok0) s0 = -INFINITY;
+        if (!ok1) s1 = -INFINITY;
+        const float m = warp_max(fmaxf(s0, s1));
+        float e0 = 0.f, e1 = 0.f;
+        if (m > -INFINITY) {
+            e0 = ok0 ? expf(s0 - m) : 0.f;
+            e1 = ok1 ? expf(s1 - m) : 0.f;
+        }
+        const float l = warp_sum(e0 + e1);
+        myp[lane] = e0;
+        myp[lane + 32] = e1;
+        __syncwarp();
+        float acc[HD / 32];
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) acc[j] = 0.f;
+        for (int kp = 0; kp < n_here; ++kp) {
+            const float pw = myp[kp];
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) acc[j] = fmaf(pw, vs[kp * LD + lane + 32 * j], acc[j]);
+        }
+        float* rec = partials + (((uint64_t)chunk * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
+        if (lane == 0) { rec[0] = m; rec[1] = l; }
+#pragma unroll
+        for (int j = 0; j < HD / 32; ++j) rec[2 + lane + 32 * j] = acc[j];
+        __syncwarp();
+    }
+}
+
+// combine over a fixed number of chunks + activation packing (rows >= n_rows packed as zeros)
+template <int HD>
+__global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float* __restrict__ partials, int n_chunks, int n_rows, uint8_t* acts,
+                                                        int bf3, int* err) {
+    constexpr int PER = HD / 32;
+    const int qh = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
+    const int group = g.n_q / g.n_kv, kvh = qh / group, qi = row * group + qh % group;
+    float v[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) v[j] = 0.f;
+    if (row < n_rows) {
+        float M = -INFINITY;
+        for (int c = lane; c < n_chunks; c += 32)
+            M = fmaxf(M, partials[(((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2)]);
+        M = warp_max(M);
+        float L = 0.f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const float* rec = partials + (((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
+            const float m = rec[0];
+            if (m == -INFINITY) continue;
+            const float f = expf(m - M);
+            L = fmaf(rec[1], f, L);
+#pragma unroll
+            for (int j = 0; j < PER; ++j) v[j] = fmaf(rec[2 + lane * PER + j], f, v[j]);
+        }
+        const float inv = 1.0f / L;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) v[j] *= inv;
+    }
+    const int col0 = qh * HD + lane * PER;
+    bool over = false;
+    float sum = 0.f;
+#pragma unroll
+    for (int q4 = 0; q4 < PER / 4; ++q4) {
+        const int col = col0 + 4 * q4;
+        uint8_t* chunk = acts + (uint64_t)(col >> 8) * (bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
+        const float quad[4] = {v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]};
+        pack_quad(chunk, bf3 != 0, row, col & 255, quad, over);
+        sum += quad[0] + quad[1] + quad[2] + quad[3];
+    }
+    if (!bf3) {
+        constexpr int LANES = 32 / PER;
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if ((lane % LANES) == 0)
+            reinterpret_cast<float*>(acts + (uint64_t)(col0 >> 8) * ACT16_CHUNK + 2 * ACT_PLANE)[row * 8 + ((col0 & 255) >> 5)] = sum;
+    }
+    if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
+}
+
+dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
+                               const int32_t* pos_ctx, int ctx_begin, int ctx_len, const float* k_noise, const float* v_noise,
+                               uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts, bool bf3,
+                               int* err) {
+    const int n_ctx = ctx_len - ctx_begin;
+    const int n_chunks = (n_ctx + n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    const uint32_t* pc = reinterpret_cast<const uint32_t*>(pos_ctx);
+    if (g.hd == 128) {
+        const size_t smem = (size_t)(2 * ATTN_CHUNK * 129 + 8 * 128 + 8 * ATTN_CHUNK) * sizeof(float);
+        static bool set = false;
+        if (!set) { DFL_CUDA(cudaFuncSetAttribute(dattn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
+        dattn_chunk_kernel<128><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
+                                                                                          noise_start, n_rows, causal ? 1 : 0, window, partials);
+        dattn_post_kernel<128><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3 ? 1 : 0, err);
+    } else if (g.hd == 256) {
+        const size_t smem = (size_t)(2 * ATTN_CHUNK * 257 + 8 * 256 + 8 * ATTN_CHUNK) * sizeof(float);
+        static bool set = false;
+        if (!set) { DFL_CUDA(cudaFuncSetAttribute(dattn_chunk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
+        dattn_chunk_kernel<256><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
+                                                                                          noise_start, n_rows, causal ? 1 : 0, window, partials);
+        dattn_post_kernel<256><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3 ? 1 : 0, err);
+    } else {
+        return fail(DFL_ERR_UNSUPPORTED, "drafter attention: head_dim must be 128 or 256");
+    }
+    count_launch(2);
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+}  // namespace dfl
+
+using namespace dfl;
+
+struct dfl_drafter {
+    const dfl_model* target = nullptr;
+    dfl_dflash_config cfg{};
+    MatGroup fc;
+    float *hidden_norm_w = nullptr, *out_norm_w = nullptr;
+    std::vector<DLayerW> layers;
+    uint64_t weight_bytes = 0;
+    AttnGeom geom(int n_q) const {
+        AttnGeom g;
+        g.n_q = n_q; g.n_kv = (int)cfg.n_kv_heads; g.hd = (int)cfg.head_dim; g.n_rot = (int)cfg.head_dim;
+        g.theta = cfg.rope_theta; g.eps = cfg.rms_norm_eps;
+        return g;
+    }
+};
+
+constexpr uint32_t kPendingCap = 256;  // appended-but-unprojected context columns kept in staging
+
+struct dfl_dsession {
+    const dfl_drafter* d = nullptr;
+    uint32_t ctx_capacity = 0, ctx_len = 0, ready = 0;
+    uint32_t pending_base = 0;          // column index of staging row 0
+    float* staging = nullptr;           // [kPendingCap][K*H]
+    uint32_t* pos_ctx_dev = nullptr;    // [capacity]
+    std::vector<uint32_t> pos_host;
+    std::vector<float*> k_ctx, v_ctx;   // per layer [capacity][n_kv][hd]
+    // scratch
+    float *x = nullptr, *part = nullptr, *sumsq = nullptr, *q_rot = nullptr, *k_noise = nullptr, *v_noise = nullptr, *attn_part = nullptr;
+    uint8_t *acts_h = nullptr, *acts_f = nullptr, *acts_q = nullptr, *acts_fc = nullptr, *acts_lm = nullptr;
+    float *logits = nullptr, *gap = nullptr;
+    int32_t *argmax = nullptr, *tokens_dev = nullptr;
+    void* am_scratch = nullptr;
+    int32_t* pinned_i = nullptr;
+    cudaStream_t st = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int* err = nullptr;
+    std::vector<void*> allocs;
+};
+
+namespace dfl {
+dfl_status dsession_project_pending(dfl_dsession* ds);
+dfl_status dsession_append_dev(dfl_dsession* ds, const float* rows_dev, cudaMemcpyKind kind, const uint32_t* positions, uint32_t count);
+}
+
+extern "C" {
+
+dfl_status dfl_drafter_create(const dfl_model* target, const dfl_dflash_config* cfg, const dfl_tensor* tensors, uint64_t n_tensors,
+                              dfl_drafter** out) {
+    if (!target || !cfg || !tensors || !out) return fail(DFL_ERR_BAD_ARG, "drafter_create: null argument");
+    *out = nullptr;
+    DFL_CHECK(use_device(target->device));
+    const dfl_dflash_config& c = *cfg;
+    if (c.hidden_size != target->arch.hidden_size) return fail(DFL_ERR_BAD_SHAPE, "drafter requires H_drafter == H_target");
+    if (c.n_layer == 0 || c.n_layer > DFL_MAX_DRAFTER_LAYERS) return fail(DFL_ERR_BAD_SHAPE, "drafter_create: layer count");
+    if (c.block_size < 1 || c.block_size > MAX_ROWS) return fail(DFL_ERR_BAD_SHAPE, "drafter_create: block_size must be in [1, 16]");
+    if (c.n_target_layers < 1 || c.n_target_layers > DFL_MAX_TARGET_LAYERS) return fail(DFL_ERR_BAD_SHAPE, "drafter_create: target layer count");
+    if (c.head_dim != 128 && c.head_dim != 256) return fail(DFL_ERR_UNSUPPORTED, "drafter_create: head_dim must be 128 or 256");
+    if (c.n_kv_heads == 0 || c.n_q_heads % c.n_kv_heads || ((uint64_t)c.n_q_heads * c.head_dim) % 256 || c.intermediate_size % 256)
+        return fail(DFL_ERR_BAD_SHAPE, "drafter_create: head counts / widths");
+    if (c.mask_token_id < 0 || (uint32_t)c.mask_token_id >= target->arch.vocab_size) return fail(DFL_ERR_BAD_TOKEN, "drafter_create: mask token id");
+    for (uint32_t k = 0; k < c.n_target_layers; ++k)
+        if (c.target_layer_ids[k] >= target->arch.n_layer) return fail(DFL_ERR_BAD_SHAPE, "drafter_create: target layer id out of range");
+    TensorMap tm;
+    for (uint64_t i = 0; i < n_tensors; ++i) {
+        if (!tensors[i].name || !tensors[i].data) return fail(DFL_ERR_BAD_ARG, "drafter_create: tensor without name or data");
+        tm.t[tensors[i].name] = &tensors[i];
+    }
+    auto* d = new dfl_drafter();
+    d->target = target;
+    d->cfg = c;
+    const int dev = target->device;
+    const uint64_t H = c.hidden_size, F = c.intermediate_size, q_dim = (uint64_t)c.n_q_heads * c.head_dim, kv_dim = (uint64_t)c.n_kv_heads * c.head_dim;
+    const uint64_t KH = (uint64_t)c.n_target_layers * H;
+    dfl_status s = DFL_OK;
+    auto blk = [](uint32_t il, const char* suffix) { return "blk." + std::to_string(il) + "." + suffix; };
+#define DC(expr)                      \
+    do {                              \
+        s = (expr);                   \
+        if (s != DFL_OK) goto failed; \
+    } while (0)
+    DC(build_group(dev, 0, tm, {"dflash_fc.weight"}, KH, {H}, &d->fc));
+    DC(upload_f32(dev, 0, tm, "dflash_hidden_norm.weight", H, &d->hidden_norm_w));
+    DC(upload_f32(dev, 0, tm, "output_norm.weight", H, &d->out_norm_w));
+    d->weight_bytes = d->fc.ggml_bytes();
+    d->layers.resize(c.n_layer);
+    for (uint32_t il = 0; il < c.n_layer; ++il) {
+        DLayerW& L = d->layers[il];
+        L.is_swa = c.layer_is_swa[il] != 0;
+        DC(upload_f32(dev, 0, tm, blk(il, "attn_norm.weight"), H, &L.attn_norm_w));
+        DC(upload_f32(dev, 0, tm, blk(il, "post_attention_norm.weight"), H, &L.post_norm_w));
+        DC(upload_f32(dev, 0, tm, blk(il, "attn_q_norm.weight"), c.head_dim, &L.q_norm_w));
+        DC(upload_f32(dev, 0, tm, blk(il, "attn_k_norm.weight"), c.head_dim, &L.k_norm_w));
+        DC(build_group(dev, 0, tm, {blk(il, "attn_q.weight"), blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H, {q_dim, kv_dim, kv_dim}, &L.qkv));
+        DC(build_group(dev, 0, tm, {blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H, {kv_dim, kv_dim}, &L.kv));
+        DC(build_group(dev, 0, tm, {blk(il, "attn_output.weight")}, q_dim, {H}, &L.wo));
+        DC(build_group(dev, 0, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up));
+        DC(build_group(dev, 0, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down));
+        d->weight_bytes += L.qkv.ggml_bytes() + L.wo.ggml_bytes() + L.gate_up.ggml_bytes() + L.down.ggml_bytes();
+    }
+#undef DC
+    d->weight_bytes += target->lm_head.ggml_bytes();
+    cudaDeviceSynchronize();
+    *out = d;
+    return DFL_OK;
+failed:
+    dfl_drafter_destroy(d);
+    return s;
+}
+
+void dfl_drafter_destroy(dfl_drafter* d) {
+    if (!d) return;
+    cudaSetDevice(d->target->device);
+    d->fc.release();
+    for (auto& L : d->layers) {
+        L.qkv.release(); L.kv.release(); L.wo.release(); L.gate_up.release(); L.down.release();
+        for (float* p : {L.attn_norm_w, L.post_norm_w, L.q_norm_w, L.k_norm_w})
+            if (p) cudaFree(p);
+    }
+    if (d->hidden_norm_w) cudaFree(d->hidden_norm_w);
+    if (d->out_norm_w) cudaFree(d->out_norm_w);
+    delete d;
+}
+
+uint64_t dfl_drafter_weight_bytes(const dfl_drafter* d) { return d ? d->weight_bytes : 0; }
+
+dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_dsession** out) {
+    if (!d || !out) return fail(DFL_ERR_BAD_ARG, "dsession_create: null argument");
+    *out = nullptr;
+    if (ctx_capacity == 0) return fail(DFL_ERR_BAD_ARG, "dsession_create: ctx_capacity must be positive");
+    DFL_CHECK(use_device(d->target->device));
+    auto* ds = new dfl_dsession();
+    ds->d = d;
+    ds->ctx_capacity = ctx_capacity;
+    const dfl_dflash_config& c = d->cfg;
+    const uint64_t H = c.hidden_size, F = c.intermediate_size, V = d->target->arch.vocab_size;
+    const uint64_t q_dim = (uint64_t)c.n_q_heads * c.head_dim, kv_dim = (uint64_t)c.n_kv_heads * c.head_dim, KH = (uint64_t)c.n_target_layers * H;
+    uint64_t part = 0;
+    auto upd = [&](const MatGroup& g) { part = std::max<uint64_t>(part, (uint64_t)g.splits * MAX_ROWS * g.total_cols); };
+    upd(d->fc);
+    for (auto& L : d->layers) { upd(L.qkv); upd(L.kv); upd(L.wo); upd(L.gate_up); upd(L.down); }
+    if (d->target->lm_head.splits > 1) upd(d->target->lm_head);
+    bool ok = cudaStreamCreateWithFlags(&ds->st, cudaStreamNonBlocking) == cudaSuccess;
+    auto alloc = [&](size_t bytes) -> void* {
+        if (!ok) return nullptr;
+        void* q = nullptr;
+        ok = cudaMalloc(&q, bytes ? bytes : 16) == cudaSuccess;
+        if (ok) { cudaMemset(q, 0, bytes ? bytes : 16); ds->allocs.push_back(q); }
+        return q;
+    };
+    const AttnGeom g = d->geom((int)c.n_q_heads);
+    ds->staging = (float*)alloc((size_t)kPendingCap * KH * 4);
+    ds->pos_ctx_dev = (uint32_t*)alloc((size_t)ctx_capacity * 4);
+    for (uint32_t il = 0; il < c.n_layer; ++il) {
+        ds->k_ctx.push_back((float*)alloc((size_t)ctx_capacity * kv_dim * 4));
+        ds->v_ctx.push_back((float*)alloc((size_t)ctx_capacity * kv_dim * 4));
+    }
+    ds->x = (float*)alloc(MAX_ROWS * H * 4);
+    ds->part = (float*)alloc(part * 4);
+    ds->sumsq = (float*)alloc((H / 256) * MAX_ROWS * 4);
+    ds->q_rot = (float*)alloc(MAX_ROWS * q_dim * 4);
+    ds->k_noise = (float*)alloc(MAX_ROWS * kv_dim * 4);
+    ds->v_noise = (float*)alloc(MAX_ROWS * kv_dim * 4);
+    ds->attn_part = (float*)alloc(attn_partials_floats(g, ctx_capacity + MAX_ROWS) * 4);
+    ds->acts_h = (uint8_t*)alloc(acts_bytes(DFL_BF16, H));
+    ds->acts_f = (uint8_t*)alloc(acts_bytes(DFL_BF16, F));
+    ds->acts_q = (uint8_t*)alloc(acts_bytes(DFL_BF16, q_dim));
+    ds->acts_fc = (uint8_t*)alloc(acts_bytes(DFL_BF16, KH));
+    ds->acts_lm = (uint8_t*)alloc(acts_bytes(DFL_BF16, H));
+    ds->logits = (float*)alloc(MAX_ROWS * V * 4);
+    ds->gap = (float*)alloc(MAX_ROWS * 4);
+    ds->argmax = (int32_t*)alloc(MAX_ROWS * 4);
+    ds->tokens_dev = (int32_t*)alloc(MAX_ROWS * 4);
+    ds->am_scratch = alloc(MAX_ROWS * ARGMAX_PARTS * 16);
+    ds->err = (int*)alloc(4);
+    ok = ok && cudaMallocHost(&ds->pinned_i, 2 * MAX_ROWS * 4) == cudaSuccess;
+    ok = ok && cudaEventCreate(&ds->ev0) == cudaSuccess && cudaEventCreate(&ds->ev1) == cudaSuccess;
+    if (!ok) {
+        std::string why = cudaGetErrorString(cudaGetLastError());
+        dfl_dsession_destroy(ds);
+        return fail(DFL_ERR_OOM, "dsession_create: allocation failed: " + why);
+    }
+    ds->pos_host.reserve(ctx_capacity);
+    cudaDeviceSynchronize();
+    *out = ds;
+    return DFL_OK;
+}
+
+void dfl_dsession_destroy(dfl_dsession* ds) {
+    if (!ds) return;
+    cudaSetDevice(ds->d->target->device);
+    for (void* p : ds->allocs) cudaFree(p);
+    if (ds->pinned_i) cudaFreeHost(ds->pinned_i);
+    if (ds->ev0) cudaEventDestroy(ds->ev0);
+    if (ds->ev1) cudaEventDestroy(ds->ev1);
+    if (ds->st) cudaStreamDestroy(ds->st);
+    delete ds;
+}
+
+uint32_t dfl_dsession_ctx_len(const dfl_dsession* ds) { return ds ? ds->ctx_len : 0; }
+
+// Internal view for the outer loop (generate.cu); not part of the public header.
+struct dfl_dsession_view {
+    cudaStream_t st;
+    cudaEvent_t ev0, ev1;
+    int* err;
+    const int32_t* argmax_dev;
+    const float* logits_dev;
+    int32_t* pinned_i;
+    uint32_t block_size, n_target_layers;
+    const uint32_t* target_layer_ids;
+    const dfl_model* target;
+};
+void dfl_dsession_view_get(dfl_dsession* ds, dfl_dsession_view* out) {
+    out->st = ds->st; out->ev0 = ds->ev0; out->ev1 = ds->ev1; out->err = ds->err;
+    out->argmax_dev = ds->argmax; out->logits_dev = ds->logits; out->pinned_i = ds->pinned_i;
+    out->block_size = ds->d->cfg.block_size; out->n_target_layers = ds->d->cfg.n_target_layers;
+    out->target_layer_ids = ds->d->cfg.target_layer_ids; out->target = ds->d->target;
+}
+
+dfl_status dfl_dsession_reset(dfl_dsession* ds) {
+    if (!ds) return fail(DFL_ERR_BAD_ARG, "dsession_reset: null session");
+    ds->ctx_len = ds->ready = ds->pending_base = 0;
+    ds->pos_host.clear();
+    return DFL_OK;
+}
+
+}  // extern "C"
+
+namespace dfl {
+
+// Projects every appended-but-unprojected column: fc + hidden_norm, then per layer K/V + K-norm + RoPE.
+dfl_status dsession_project_pending(dfl_dsession* ds) {
+    const dfl_drafter* d = ds->d;
+    const dfl_dflash_config& c = d->cfg;
+    const uint64_t H = c.hidden_size, KH = (uint64_t)c.n_target_layers * H;
+    cudaStream_t st = ds->st;
+    GemmEpilogue ep_norm;
+    ep_norm.sumsq = ds->sumsq;
+    ep_norm.n_sumsq = (int)(H / 256);
+    ep_norm.norm_k = (float)H;
+    ep_norm.eps = c.rms_norm_eps;
+    const AttnGeom gkv = d->geom(0);
+    while (ds->ready < ds->ctx_len) {
+        const uint32_t c0 = ds->ready, nb = std::min<uint32_t>(MAX_ROWS, ds->ctx_len - c0);
+        GlueParams p;
+        p.mode = GLUE_COPY;
+        p.x = ds->staging + (uint64_t)(c0 - ds->pending_base) * KH;
+        p.ld_x = (int)KH;
+        p.acts = ds->acts_fc; p.bf3 = dtype_uses_bf16_acts(d->fc.mats[0].dtype) ? 1 : 0;
+        p.n_rows = (int)nb; p.err = ds->err;
+        DFL_CHECK(launch_glue(st, p, KH));
+        DFL_CHECK(launch_group(st, d->fc, ds->acts_fc, ds->part, GemmEpilogue{}, ds->err));
+        GlueParams q;
+        q.mode = GLUE_RESID;
+        q.part = ds->part; q.splits = d->fc.splits; q.ld_part = (int)d->fc.total_cols;
+        q.mul_w = d->hidden_norm_w;
+        q.sumsq = ds->sumsq;
+        q.acts = ds->acts_h; q.bf3 = dtype_uses_bf16_acts(d->layers[0].kv.mats[0].dtype) ? 1 : 0;
+        q.n_rows = (int)nb; q.err = ds->err;
+        DFL_CHECK(launch_glue(st, q, H));
+        for (uint32_t il = 0; il < c.n_layer; ++il) {
+            const DLayerW& L = d->layers[il];
+            DFL_CHECK(launch_group(st, L.kv, ds->acts_h, ds->part, ep_norm, ds->err));
+            DFL_CHECK(launch_attn_front(st, gkv, false, ds->part, L.kv.splits, (int)L.kv.total_cols, nullptr, L.k_norm_w, 0, (int)nb, ds->k_ctx[il],
+                                        ds->v_ctx[il], false, nullptr, nullptr, ds->pos_ctx_dev + c0, (long long)c0));
+        }
+        ds->ready += nb;
+    }
+    ds->pending_base = ds->ready;
+    return DFL_OK;
+}
+
+dfl_status dsession_append_dev(dfl_dsession* ds, const float* rows, cudaMemcpyKind kind, const uint32_t* positions, uint32_t count) {
+    const dfl_dflash_config& c = ds->d->cfg;
+    const uint64_t KH = (uint64_t)c.n_target_layers * c.hidden_size;
+    if ((uint64_t)ds->ctx_len + count > ds->ctx_capacity)
+        return fail(DFL_ERR_CTX_OVERFLOW, "drafter context is full: " + std::to_string(ds->ctx_len) + " + " + std::to_string(count) + " > " +
+                                              std::to_string(ds->ctx_capacity));
+    uint32_t done = 0;
+    while (done < count) {
+        if (ds->ctx_len - ds->pending_base >= kPendingCap) DFL_CHECK(dsession_project_pending(ds));
+        const uint32_t room = kPendingCap - (ds->ctx_len - ds->pending_base);
+        const uint32_t nb = std::min(room, count - done);
+        DFL_CUDA(cudaMemcpyAsync(ds->staging + (uint64_t)(ds->ctx_len - ds->pending_base) * KH, rows + (uint64_t)done * KH, (size_t)nb * KH * 4, kind, ds->st));
+        for (uint32_t i = 0; i < nb; ++i) ds->pos_host.push_back(positions[done + i]);
+        DFL_CUDA(cudaMemcpyAsync(ds->pos_ctx_dev + ds->ctx_len, ds->pos_host.data() + ds->ctx_len, (size_t)nb * 4, cudaMemcpyHostToDevice, ds->st));
+        // pos_host may reallocate later: the copy above must finish first
+        DFL_CUDA(cudaStreamSynchronize(ds->st));
+        ds->ctx_len += nb;
+        done += nb;
+    }
+    return DFL_OK;
+}
+
+// One draft pass; leaves logits / argmax on the device.
+dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start) {
+    const dfl_drafter* d = ds->d;
+    const dfl_model* tgt = d->target;
+    const dfl_dflash_config& c = d->cfg;
+    const uint64_t H = c.hidden_size, F = c.intermediate_size, V = tgt->arch.vocab_size;
+    const int n = (int)c.block_size;
+    cudaStream_t st = ds->st;
+    DFL_CHECK(dsession_project_pending(ds));
+    GemmEpilogue ep_norm;
+    ep_norm.sumsq = ds->sumsq;
+    ep_norm.n_sumsq = (int)(H / 256);
+    ep_norm.norm_k = (float)H;
+    ep_norm.eps = c.rms_norm_eps;
+    ds->pinned_i[0] = carry;
+    for (int i = 1; i < n; ++i) ds->pinned_i[i] = c.mask_token_id;
+    DFL_CUDA(cudaMemcpyAsync(ds->tokens_dev, ds->pinned_i, n * 4, cudaMemcpyHostToDevice, st));
+    DFL_CHECK(launch_embed_rows(st, tgt->embd_dtype, tgt->embd_ggml, H, ds->tokens_dev, n, ds->x, (int)H));
+    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* w, uint8_t* acts, bool bf3) -> dfl_status {
+        GlueParams p;
+        p.mode = GLUE_RESID;
+        p.part = part; p.splits = splits; p.ld_part = ld_part;
+        p.x = ds->x; p.ld_x = (int)H;
+        p.mul_w = w;
+        p.acts = acts; p.bf3 = bf3 ? 1 : 0;
+        p.sumsq = ds->sumsq;
+        p.n_rows = n; p.err = ds->err;
+        return launch_glue(st, p, H);
+    };
+    auto bf = [](const MatGroup& g) { return dtype_uses_bf16_acts(g.mats[0].dtype); };
+    DFL_CHECK(norm_glue(nullptr, 0, 0, d->layers[0].attn_norm_w, ds->acts_h, bf(d->layers[0].qkv)));
+    const AttnGeom g = d->geom((int)c.n_q_heads);
+    // context columns an all-SWA layer can see start at the first position >= noise_start - (window - 1)
+    bool monotonic = true;
+    for (size_t i = 1; i < ds->pos_host.size() && monotonic; ++i) monotonic = ds->pos_host[i] >= ds->pos_host[i - 1];
+    for (uint32_t il = 0; il < c.n_layer; ++il) {
+        const DLayerW& L = d->layers[il];
+        DFL_CHECK(launch_group(st, L.qkv, ds->acts_h, ds->part, ep_norm, ds->err));
+        DFL_CHECK(launch_attn_front(st, g, false, ds->part, L.qkv.splits, (int)L.qkv.total_cols, L.q_norm_w, L.k_norm_w, noise_start, n, ds->k_noise,
+                                    ds->v_noise, false, ds->q_rot, nullptr, nullptr, 0));
+        const uint32_t window = L.is_swa ? c.swa_window : 0;
+        int ctx_begin = 0;
+        if (window > 0 && monotonic) {  // dflash_swa_ctx_scan_start, metal_dflash.rs:570-594
+            const uint32_t min_pos = noise_start >= window - 1 ? noise_start - (window - 1) : 0;
+            ctx_begin = (int)(std::lower_bound(ds->pos_host.begin(), ds->pos_host.begin() + ds->ctx_len, min_pos) - ds->pos_host.begin());
+        }
+        DFL_CHECK(launch_drafter_attn(st, g, ds->q_rot, ds->k_ctx[il], ds->v_ctx[il], reinterpret_cast<const int32_t*>(ds->pos_ctx_dev), ctx_begin,
+                                      (int)ds->ctx_len, ds->k_noise, ds->v_noise, noise_start, n, c.causal != 0, window, ds->attn_part, ds->acts_q,
+                                      bf(L.wo), ds->err));
+        DFL_CHECK(launch_group(st, L.wo, ds->acts_q, ds->part, GemmEpilogue{}, ds->err));
+        DFL_CHECK(norm_glue(ds->part, L.wo.splits, (int)L.wo.total_cols, L.post_norm_w, ds->acts_h, bf(L.gate_up)));
+        DFL_CHECK(launch_group(st, L.gate_up, ds->acts_h, ds->part, ep_norm, ds->err));
+        GlueParams p;
+        p.mode = GLUE_SWIGLU;
+        p.part = ds->part; p.splits = L.gate_up.splits; p.ld_part = (int)L.gate_up.total_cols;
+        p.swiglu_f = (int)F;
+        const bool down_bf = bf(L.down);
+        p.pre_scale = down_bf ? 1.0f : 1.0f / 64.0f;
+        p.acts = ds->acts_f; p.bf3 = down_bf ? 1 : 0;
+        p.n_rows = n; p.err = ds->err;
+        DFL_CHECK(launch_glue(st, p, F));
+        GemmEpilogue ep_down;
+        ep_down.out_scale = down_bf ? 1.0f : 64.0f;
+        DFL_CHECK(launch_group(st, L.down, ds->acts_f, ds->part, ep_down, ds->err));
+        const bool last = il + 1 == c.n_layer;
+        if (last) DFL_CHECK(norm_glue(ds->part, L.down.splits, (int)L.down.total_cols, d->out_norm_w, ds->acts_lm, bf(tgt->lm_head)));
+        else DFL_CHECK(norm_glue(ds->part, L.down.splits, (int)L.down.total_cols, d->layers[il + 1].attn_norm_w, ds->acts_h, bf(d->layers[il + 1].qkv)));
+    }
+    const MatGroup& lm = tgt->lm_head;
+    if (lm.splits == 1) {
+        DFL_CHECK(launch_group(st, lm, ds->acts_lm, ds->logits, ep_norm, ds->err));
+    } else {
+        DFL_CHECK(launch_group(st, lm, ds->acts_lm, ds->part, ep_norm, ds->err));
+        DFL_CHECK(launch_reduce_partials(st, ds->part, lm.splits, n, V, ds->logits, (int)V));
+    }
+    DFL_CHECK(launch_argmax_top2(st, ds->logits, n, V, V, ds->argmax, ds->gap, ds->am_scratch));
+    return DFL_OK;
+}
+
+}  // namespace dfl
+
+extern "C" {
+
+dfl_status dfl_dsession_append_columns_host(dfl_dsession* ds, const float* cols_host, const uint32_t* positions, uint32_t count) {
+    if (!ds || !cols_host || !positions) return fail(DFL_ERR_BAD_ARG, "append_columns: null argument");
+    DFL_CHECK(use_device(ds->d->target->device));
+    return dsession_append_dev(ds, cols_host, cudaMemcpyHostToDevice, positions, count);
+}
+
+dfl_status dfl_dsession_append_from_scratch(dfl_dsession* ds, const dfl_scratch* sc, uint32_t first_row, uint32_t count, uint32_t first_position) {
+    if (!ds || !sc) return fail(DFL_ERR_BAD_ARG, "append_from_scratch: null argument");
+    if (sc->m != ds->d->target) return fail(DFL_ERR_BAD_ARG, "append_from_scratch: scratch belongs to another model");
+    if (sc->k_layers != ds->d->cfg.n_target_layers) return fail(DFL_ERR_BAD_SHAPE, "append_from_scratch: capture layer count differs from the drafter's");
+    if (!sc->have_block || first_row + count > MAX_ROWS) return fail(DFL_ERR_BAD_SHAPE, "append_from_scratch: rows outside the captured block");
+    DFL_CHECK(use_device(ds->d->target->device));
+    uint32_t pos[MAX_ROWS];
+    for (uint32_t i = 0; i < count; ++i) pos[i] = first_position + i;
+    const uint64_t KH = (uint64_t)sc->k_layers * sc->m->arch.hidden_size;
+    // the capture was written on the target session's stream, which the verify call has already synchronised
+    return dsession_append_dev(ds, sc->capture + (uint64_t)first_row * KH, cudaMemcpyDeviceToDevice, pos, count);
+}
+
+dfl_status dfl_draft_block(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos, int32_t* out_tokens, float* logits_host) {
+    if (!ds || !out_tokens) return fail(DFL_ERR_BAD_ARG, "draft_block: null argument");
+    const dfl_model* tgt = ds->d->target;
+    DFL_CHECK(use_device(tgt->device));
+    if (carry < 0 || (uint32_t)carry >= tgt->arch.vocab_size) return fail(DFL_ERR_BAD_TOKEN, "draft_block: carry token out of range");
+    const uint32_t n = ds->d->cfg.block_size;
+    DFL_CHECK(draft_core(ds, carry, noise_start_pos));
+    DFL_CUDA(cudaMemcpyAsync(ds->pinned_i + MAX_ROWS, ds->argmax, n * 4, cudaMemcpyDeviceToHost, ds->st));
+    if (logits_host) DFL_CUDA(cudaMemcpyAsync(logits_host, ds->logits, (size_t)n * tgt->arch.vocab_size * 4, cudaMemcpyDeviceToHost, ds->st));
+    DFL_CHECK(check_dev_err(ds->st, ds->err));
+    out_tokens[0] = carry;
+    for (uint32_t i = 1; i < n; ++i) out_tokens[i] = ds->pinned_i[MAX_ROWS + i];
+    return DFL_OK;
+}
+
+}  // extern "C"

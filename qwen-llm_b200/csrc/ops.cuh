@@ -99,9 +99,12 @@ constexpr int ATTN_CHUNK = 64;
 // Reduces the fused q|k|v GEMM partials, applies per-head RMSNorm + partial NeoX RoPE, appends K/V
 // at positions start..start+n_rows-1 and leaves rotated Q and the raw gate for the attention kernel.
 // gated: q rows are interleaved (q, gate) per head as in the target; otherwise plain q.
+// pos_override[tok] (device) replaces start + tok as the RoPE position; cache_row0 >= 0 stores
+// K/V at rows cache_row0 + tok instead of at the position (the drafter's context cache).
 dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, const float* part, int splits, int ld_part,
                              const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
-                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override);
+                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override,
+                             long long cache_row0 = -1);
 // Causal attention of the n_rows query rows over cache positions [0, start + row]; partials per
 // 64-position chunk, then combine, sigmoid gate and activation packing for the o-projection.
 dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,

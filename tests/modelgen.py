@@ -122,3 +122,73 @@ class OracleModel:
         p = lambda x: x.ctypes.data_as(C.c_void_p)
         assert self.L.orc_state_read_kv(self.h, st, C.c_uint32(ai), C.c_uint32(pos), p(k), p(v)) == 0
         return k, v
+
+
+def tiny_dflash_config(arch, **kw):
+    c = pkg.DFlashConfig()
+    d = dict(n_layer=2, hidden_size=arch.hidden_size, intermediate_size=512, n_q_heads=2, n_kv_heads=1, head_dim=128,
+             rope_theta=1000000.0, rms_norm_eps=1e-6, causal=0, swa_window=8, block_size=16, mask_token_id=7, n_target_layers=2)
+    d.update(kw)
+    for k, v in d.items():
+        setattr(c, k, v)
+    ids = kw.get("ids", [1, arch.n_layer - 1])
+    for i, l in enumerate(ids[:c.n_target_layers]):
+        c.target_layer_ids[i] = l
+    swa = kw.get("swa", [1] * (c.n_layer - 1) + [0])     # sliding window on all but the last layer
+    for i, v in enumerate(swa[:c.n_layer]):
+        c.layer_is_swa[i] = v
+    return c
+
+
+def drafter_tensors(arch, cfg, seed=1, std=0.02, dtype=orc.BF16):
+    rng = np.random.default_rng(seed)
+    H, F = cfg.hidden_size, cfg.intermediate_size
+    q_dim, kv_dim = cfg.n_q_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+    KH = cfg.n_target_layers * arch.hidden_size
+    T = []
+
+    def mat(name, n_in, n_out, s=std):
+        w = (rng.standard_normal((n_out, n_in)) * s).astype(np.float32)
+        T.append((name, dtype, [n_in, n_out], orc.quantize(dtype, w)))
+
+    def norm(name, n):
+        T.append((name, orc.F32, [n], (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32).view(np.uint8)))
+
+    mat("dflash_fc.weight", KH, H)
+    norm("dflash_hidden_norm.weight", H)
+    norm("output_norm.weight", H)
+    for il in range(cfg.n_layer):
+        b = f"blk.{il}."
+        norm(b + "attn_norm.weight", H)
+        norm(b + "post_attention_norm.weight", H)
+        norm(b + "attn_q_norm.weight", cfg.head_dim)
+        norm(b + "attn_k_norm.weight", cfg.head_dim)
+        mat(b + "attn_q.weight", H, q_dim)
+        mat(b + "attn_k.weight", H, kv_dim)
+        mat(b + "attn_v.weight", H, kv_dim)
+        mat(b + "attn_output.weight", q_dim, H)
+        mat(b + "ffn_gate.weight", H, F)
+        mat(b + "ffn_up.weight", H, F)
+        mat(b + "ffn_down.weight", F, H)
+    return T
+
+
+class OracleDrafter:
+    def __init__(self, cfg, tensors):
+        import ctypes as C
+        self.cfg = cfg
+        arr, self._keep = pkg.make_tensor_table(tensors)
+        self.L = orc.lib()
+        self.h = C.c_void_p(self.L.orc_drafter_create(C.byref(cfg), arr, C.c_uint64(len(tensors))))
+        assert self.h, self.L.orc_last_error()
+
+    def draft(self, target: "OracleModel", noise_ids, ctx_stacked, pos_ctx, noise_start):
+        import ctypes as C
+        noise = np.ascontiguousarray(noise_ids, dtype=np.int32)
+        ctx = np.ascontiguousarray(ctx_stacked, dtype=np.float32)
+        pos = np.ascontiguousarray(pos_ctx, dtype=np.uint32)
+        out = np.zeros((noise.size, target.arch.vocab_size), dtype=np.float32)
+        p = lambda a: a.ctypes.data_as(C.c_void_p)
+        orc.check(self.L.orc_dflash_draft(self.h, target.h, p(noise), C.c_uint32(noise.size), p(ctx), C.c_uint32(pos.size), p(pos),
+                                          C.c_uint32(noise_start), p(out)))
+        return out
