@@ -1,0 +1,308 @@
+"""Workload c2 of bench.py: greedy DFlash decode, 9B-class hybrid Q4_K_M target + 5-layer bf16 drafter,
+batch 1, prompt 512 random ids, block 16 (BASELINE config 2).
+
+One bench "step" is one DFlash outer step: draft 16 -> packed verify of 16 rows -> accept prefix ->
+context append -> rollback.  Random-init weights make the drafter's own acceptance ~0, so acceptance
+is controlled with the reference's replayed-draft mode (dflash_prefix_replay_drafts, qwen/dflash.rs:351-376):
+drafts come from the true greedy continuation with seeded corruption, while the drafter still runs every
+step so that no work is skipped.  The headline schedule accepts 3,3,4,3,4 drafts per step (mean emitted 4.4
+tokens per step, the reference's measured acceptance, docs/PERF-LOG.md:22184-22187); the natural (alpha ~ 0) and
+full-accept schedules are reported beside it.
+"""
+import ctypes as C
+import importlib
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+PROMPT = 512
+PATTERN = [3, 3, 4, 3, 4]     # accepted drafts per step -> emitted 4,4,5,4,5 (mean 4.4)
+KV_CAP = 4096
+
+
+def _pkg():
+    return importlib.import_module("qwen-llm_b200")
+
+
+def _syn():
+    return importlib.import_module("qwen-llm_b200.synthetic")
+
+
+def schedule_history(cont, pattern, vocab):
+    """Replay history that makes step k accept pattern[k % len] drafts: corrupt the draft after them."""
+    hist = np.array(cont, dtype=np.int32).copy()
+    e, k = 1, 0
+    while True:
+        a = pattern[k % len(pattern)]
+        if e + a >= hist.size:
+            break
+        if a < 15:
+            hist[e + a] = (hist[e + a] + 1) % vocab
+        e += a + 1
+        k += 1
+    return hist
+
+
+def tokens_for_steps(pattern, first_step, n_steps):
+    return 1 + sum(pattern[(first_step + i) % len(pattern)] + 1 for i in range(n_steps))
+
+
+class World:
+    def __init__(self, device, seed):
+        pkg, syn = _pkg(), _syn()
+        self.pkg = pkg
+        self.arch = syn.arch_9b()
+        t0 = time.perf_counter()
+        ents = syn.target_entries(self.arch, seed=seed, device=device)
+        self.model = syn.build_model(self.arch, ents, device)
+        self.sample_entries = None
+        syn.free_entries(ents, device)
+        self.cfg = syn.dflash_config_9b(self.arch)
+        dents = syn.drafter_entries(self.arch, self.cfg, seed=seed + 1, device=device)
+        self.drafter = syn.build_drafter(self.model, self.cfg, dents)
+        syn.free_entries(dents, device)
+        self.build_s = time.perf_counter() - t0
+        self.layer_ids = self.drafter.layer_ids()
+        self.prompt = np.random.default_rng(seed + 2).integers(0, self.arch.vocab_size, size=PROMPT).astype(np.int32)
+        self.sess = self.scr = self.ds = None
+
+    def fresh(self):
+        pkg = self.pkg
+        for x in (self.sess, self.scr, self.ds):
+            if x is not None:
+                x.close()
+        self.sess = pkg.Session(self.model, KV_CAP, True)
+        self.scr = pkg.Scratch(self.model, 16, len(self.layer_ids))
+        self.ds = pkg.DSession(self.drafter, KV_CAP)
+        t0 = time.perf_counter()
+        logits, _ = pkg.prefill(self.model, self.sess, self.scr, self.layer_ids, self.prompt, 0, feed_drafter=self.ds)
+        self.prefill_s = time.perf_counter() - t0
+        return logits
+
+    def gen(self, first_logits, max_tokens, **kw):
+        return self.pkg.generate(self.model, self.sess, self.scr, self.ds, self.pkg.Sampler(), first_logits, max_tokens, **kw)
+
+
+def one_hot(vocab, tok):
+    l = np.full(vocab, -1.0, dtype=np.float32)
+    l[tok] = 1.0
+    return l
+
+
+def run_schedule(w, cont, pattern, warm_steps, steps, runs_drafter=True):
+    """Returns dict with device / wall timings of exactly `steps` outer steps after `warm_steps` warm-up steps."""
+    V = w.arch.vocab_size
+    hist = schedule_history(cont, pattern, V)
+    logits = w.fresh()
+    n_a = tokens_for_steps(pattern, 0, warm_steps)
+    toks_a, _ = w.gen(logits, n_a, replay_history=hist, replay_runs_drafter=runs_drafter, replay_unchecked=True)
+    assert np.array_equal(toks_a, cont[:n_a]), "warm-up output differs from the greedy continuation"
+    n_b = tokens_for_steps(pattern, warm_steps, steps)
+    launches0 = w.pkg.launch_count()
+    t0 = time.perf_counter()
+    toks_b, st = w.gen(one_hot(V, int(toks_a[-1])), n_b, replay_history=hist[n_a - 1:], replay_runs_drafter=runs_drafter,
+                       replay_unchecked=True)
+    wall = time.perf_counter() - t0
+    launches = w.pkg.launch_count() - launches0
+    assert np.array_equal(toks_b, cont[n_a - 1:n_a - 1 + n_b]), "timed output differs from the greedy continuation"
+    assert st.spec_steps == steps, (st.spec_steps, steps)
+    emitted = n_b - 1
+    dev_ms = st.draft_ms + st.verify_ms + st.restore_ms
+    return {"emitted": emitted, "steps": steps, "dev_ms": dev_ms, "wall_ms": wall * 1e3, "draft_ms": st.draft_ms, "verify_ms": st.verify_ms,
+            "restore_ms": st.restore_ms, "accept_ms": st.accept_ms, "append_ms": st.append_ms, "launches": launches,
+            "restore_calls": st.restore_calls, "accepted": int(st.accepted_drafts)}
+
+
+def cpu_sample(arch, tensors, threads_hint=None):
+    """Times the oracle on a 4-layer (3 GDN + 1 attention) + lm_head slice with the real widths.
+    Returns (seconds per full 32-layer verify of 16 rows, threads, description)."""
+    import modelgen
+    import orc
+    a4 = _pkg().Arch()
+    for f, _ in arch._fields_:
+        setattr(a4, f, getattr(arch, f))
+    a4.n_layer = 4
+    om = modelgen.OracleModel(a4, tensors)
+    st = om.new_state(64, True)
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, arch.vocab_size, size=17)
+    om.single_token(st, toks[0], 0, (), want_logits=True)          # dequantises every weight once (not timed)
+    t0 = time.perf_counter()
+    for i in range(1, 9):
+        om.single_token(st, toks[i], i, (), want_logits=False)
+    t_layers = (time.perf_counter() - t0) / 8                       # 4 layers, one row
+    t0 = time.perf_counter()
+    for i in range(9, 13):
+        om.single_token(st, toks[i], i, (), want_logits=True)
+    t_full = (time.perf_counter() - t0) / 4
+    t_head = max(t_full - t_layers, 0.0)
+    per_verify = 16 * (t_layers * (arch.n_layer / 4.0) + t_head)
+    threads = int(orc.lib().orc_num_threads())
+    desc = ("oracle port, 12 single-token passes through a 4-layer (3 GDN + 1 attention) + lm_head slice with config-2 widths; "
+            "scaled to 32 layers x 16 rows; drafter not included")
+    return per_verify, threads, desc
+
+
+def host_random_entries(arch, layers=(0, 1, 2, 3), seed=0):
+    """Random valid quantised blocks generated on the host (fast): timing does not depend on the values."""
+    import orc
+    rng = np.random.default_rng(seed)
+    H, F, V = arch.hidden_size, arch.intermediate_size, arch.vocab_size
+    hd = arch.attn_head_dim
+    q_dim, kv_dim = arch.n_q_heads * hd, arch.n_kv_heads * hd
+    n_v, n_k = arch.gdn_n_v_heads, arch.gdn_n_k_heads
+    conv_dim, v_dim = (2 * n_k + n_v) * 128, n_v * 128
+    T = []
+    blk_bytes = {orc.Q4_K: 144, orc.Q5_K: 176, orc.Q6_K: 210}
+
+    def mat(name, dtype, n_in, n_out):
+        nb = n_in * n_out // 256
+        raw = rng.integers(0, 256, size=(nb, blk_bytes[dtype]), dtype=np.uint8)
+        scale = np.frombuffer(np.float16(2e-4).tobytes(), dtype=np.uint8)
+        if dtype == orc.Q6_K:
+            raw[:, 208:210] = scale
+        else:
+            raw[:, 0:2] = scale
+            raw[:, 2:4] = scale
+        T.append((name, dtype, [n_in, n_out], raw.reshape(-1)))
+
+    def vec(name, v, shape=None):
+        a = np.ascontiguousarray(v, dtype=np.float32)
+        T.append((name, orc.F32, shape or [a.size], a.view(np.uint8)))
+
+    mat("token_embd.weight", orc.Q4_K, H, V)
+    mat("output.weight", orc.Q6_K, H, V)
+    vec("output_norm.weight", np.ones(H))
+    for il in layers:
+        b = f"blk.{il}."
+        vec(b + "attn_norm.weight", np.ones(H))
+        vec(b + "post_attention_norm.weight", np.ones(H))
+        if il % 4 == 3:
+            mat(b + "attn_q.weight", orc.Q4_K, H, 2 * q_dim)
+            mat(b + "attn_k.weight", orc.Q4_K, H, kv_dim)
+            mat(b + "attn_v.weight", orc.Q4_K, H, kv_dim)
+            mat(b + "attn_output.weight", orc.Q4_K, q_dim, H)
+            vec(b + "attn_q_norm.weight", np.ones(hd))
+            vec(b + "attn_k_norm.weight", np.ones(hd))
+        else:
+            mat(b + "attn_qkv.weight", orc.Q6_K, H, conv_dim)
+            mat(b + "attn_gate.weight", orc.Q4_K, H, v_dim)
+            mat(b + "ssm_out.weight", orc.Q5_K, v_dim, H)
+            vec(b + "ssm_alpha.weight", rng.standard_normal((n_v, H)) * 0.02, [H, n_v])
+            vec(b + "ssm_beta.weight", rng.standard_normal((n_v, H)) * 0.02, [H, n_v])
+            vec(b + "ssm_a", -rng.uniform(0.1, 2.0, n_v))
+            vec(b + "ssm_dt.bias", rng.uniform(-1.0, 1.0, n_v))
+            vec(b + "ssm_conv1d.weight", rng.standard_normal((conv_dim, 4)) * 0.3, [4, conv_dim])
+            vec(b + "ssm_norm.weight", np.ones(128))
+        mat(b + "ffn_gate.weight", orc.Q4_K, H, F)
+        mat(b + "ffn_up.weight", orc.Q4_K, H, F)
+        mat(b + "ffn_down.weight", orc.Q6_K, F, H)
+    return T
+
+
+def reference_arm(args):
+    """bench.py --impl reference: the reference's CPU algorithm on the host cores (bounded sample, scaled)."""
+    arch = _syn().arch_9b()
+    per_verify, threads, desc = cpu_sample(arch, host_random_entries(arch))
+    emitted = sum(a + 1 for a in PATTERN) / len(PATTERN)
+    return emitted / per_verify, per_verify, threads, desc
+
+
+def run(args, rank, world, device):
+    import torch
+    bench = importlib.import_module("bench")
+    pkg = _pkg()
+    w = World(device, seed=100 + rank)
+    V = w.arch.vocab_size
+    steps, warm = args.steps, max(args.warmup, 3)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+
+    # pass 0: the true greedy continuation (also the natural, alpha ~ 0 schedule)
+    need = tokens_for_steps([15], 0, warm + steps) + 16
+    logits = w.fresh()
+    t0 = time.perf_counter()
+    n_nat = min(need, 1 + 2 * (warm + steps))
+    cont_nat, st_nat = w.gen(logits, n_nat)
+    nat_wall = time.perf_counter() - t0
+    # extend the continuation cheaply with full-accept replay of itself is impossible before it is known:
+    # decode the rest with plain replay-free steps only as far as the schedules need
+    cont = cont_nat
+    if cont.size < need:
+        logits = w.fresh()
+        cont, _ = w.gen(logits, need, replay_history=cont_nat)   # replays what is known, then drafts naturally
+    sampler = bench.ClockSampler(device)
+    sampler.start()
+    barrier()
+    head = run_schedule(w, cont, PATTERN, warm, steps)
+    barrier()
+    clocks = sampler.stop()
+    full = run_schedule(w, cont, [15], warm, steps)
+    natural = {"emitted": int(st_nat.tokens_emitted) - 1, "steps": int(st_nat.spec_steps),
+               "dev_ms": st_nat.draft_ms + st_nat.verify_ms + st_nat.restore_ms, "wall_ms": nat_wall * 1e3}
+    # kernel-only timing of the dominant kernel on a few extra steps
+    pkg.gemm_timing_begin()
+    extra = run_schedule(w, cont, PATTERN, 1, 4)
+    gemm_ms, gemm_n, gemm_bytes = pkg.gemm_timing_end()
+    t = torch.tensor([head["dev_ms"], head["wall_ms"], full["dev_ms"], full["wall_ms"]], dtype=torch.float64, device=f"cuda:{device}")
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    dev_ms, wall_ms = float(t[0]), float(t[1])
+    peak, peak_kind = bench.measured_peaks()
+    vbytes = w.model.verify_weight_bytes()
+    dbytes = w.drafter.weight_bytes()
+    verify_ms = head["verify_ms"] / steps
+    draft_ms = head["draft_ms"] / steps
+    gemm_gbs = gemm_bytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else 0.0
+    line = {
+        "metric": bench.METRIC, "value": head["emitted"] * world / (dev_ms * 1e-3), "unit": bench.UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warm, "ms_per_step": dev_ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u4/u5/u6 weights x f16 hi+lo activations, f32 accumulate; bf16 drafter", "data": "synthetic",
+        "config": {"workload": "c2: 9B-class hybrid Q4_K_M target (32 layers, GDN:attn 3:1, H 4096, FFN 12288, V 151936) + 5-layer bf16 DFlash drafter, "
+                               "greedy, batch 1, prompt 512, block 16; replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step",
+                   "l2": "5.1 GB of weights per verify >> 126 MB L2", "parallelism": f"dp{world}: one independent sequence per GPU, no collective"},
+        "roofline": {"bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s", "frac": gemm_gbs / peak, "traffic": None,
+                     "peak_kind": peak_kind, "kernel": "gemm_fewrow_kernel, all launches of 5 outer steps (verify + draft), CUDA events per launch",
+                     "launches_timed": gemm_n, "algorithmic_bytes_timed": gemm_bytes,
+                     "verify_step": {"weight_bytes": vbytes, "ms": verify_ms, "GBps": vbytes / (verify_ms * 1e-3) / 1e9,
+                                     "frac": vbytes / (verify_ms * 1e-3) / 1e9 / peak},
+                     "draft_step": {"weight_bytes": dbytes, "ms": draft_ms, "GBps": dbytes / (draft_ms * 1e-3) / 1e9 if draft_ms > 0 else None}},
+        "e2e": {"value": head["emitted"] * world / (wall_ms * 1e-3), "unit": bench.UNIT, "h2d_bytes_per_step": 2 * 16 * 4,
+                "d2h_bytes_per_step": 3 * 16 * 4},
+        "gpu_launches": int(head["launches"]), "clocks": clocks,
+        "schedules": {
+            "reference_like_4.4": {"tok_per_s": head["emitted"] / (head["dev_ms"] * 1e-3), "e2e_tok_per_s": head["emitted"] / (head["wall_ms"] * 1e-3),
+                                   "ms_per_step": head["dev_ms"] / steps, "draft_ms": draft_ms, "verify_ms": verify_ms,
+                                   "restore_ms": head["restore_ms"] / steps, "host_accept_ms": head["accept_ms"] / steps},
+            "full_accept_16": {"tok_per_s": full["emitted"] / (full["dev_ms"] * 1e-3), "e2e_tok_per_s": full["emitted"] / (full["wall_ms"] * 1e-3),
+                               "ms_per_step": full["dev_ms"] / steps},
+            "natural_drafter": {"tok_per_s": natural["emitted"] / (natural["dev_ms"] * 1e-3) if natural["dev_ms"] else None,
+                                "e2e_tok_per_s": natural["emitted"] / (natural["wall_ms"] * 1e-3), "steps": natural["steps"],
+                                "mean_emitted": natural["emitted"] / max(natural["steps"], 1)}},
+        "setup": {"build_s": w.build_s, "prefill_s": w.prefill_s},
+    }
+    if rank == 0 and world == 1:
+        try:
+            syn = _syn()
+            ents = syn.target_entries(w.arch, seed=100, device=device, layers=[0, 1, 2, 3])
+            host = []
+            for (name, dtype, shape, data, nb) in ents:
+                raw = pkg.device_to_host(data, nb, device) if isinstance(data, int) else np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+                host.append((name, dtype, shape, raw))
+            syn.free_entries(ents, device)
+            per_verify, threads, desc = cpu_sample(w.arch, host)
+            emitted = sum(a + 1 for a in PATTERN) / len(PATTERN)
+            line["cpu_baseline"] = {"value": emitted / per_verify, "unit": bench.UNIT, "cores": threads, "kind": "port", "sample": desc,
+                                    "cpu_verify_s": per_verify}
+        except Exception as e:  # the baseline is a reported extra; never lose the GPU line over it
+            line["cpu_baseline"] = {"value": None, "unit": bench.UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    return line

@@ -136,6 +136,12 @@ const char* dfl_last_error(void);
 int32_t dfl_device_count(void);
 /* Kernel launches this library issued on the calling process since load. */
 uint64_t dfl_launch_count(void);
+/* Per-kernel device timing of the few-row GEMM (the reference reads per-phase GPU time from
+ * GPUStartTime/GPUEndTime, metal_dflash.rs:5608-5634).  Between begin and end every GEMM launch is
+ * bracketed by CUDA events on its own stream; end synchronises them and returns the summed kernel
+ * time, the launch count and the ggml weight bytes those launches streamed. */
+void dfl_gemm_timing_begin(void);
+dfl_status dfl_gemm_timing_end(double* ms_total, uint64_t* n_launches, uint64_t* weight_bytes);
 
 /* ---- few-row quantised GEMM (the weight-streaming hot kernel) ----------
  * Replaces encode_mat_mat_dispatch / kernel_mat_mat_*_fewrow_gen,
@@ -357,6 +363,13 @@ typedef struct dfl_generate_params {
     /* margin guard (qwen/dflash.rs:93-121): committed rows with gap < margin are
      * replayed through single-token steps.  0 disables. */
     float verify_margin;
+    /* with replay_history: still run the drafter every step (its tokens are discarded) so that a
+     * replayed-acceptance schedule pays the full draft cost. */
+    int32_t replay_runs_drafter;
+    /* with replay_history: take drafts from history[emitted ...] even where the history disagrees
+     * with what was emitted (the reference stops replaying at the first divergence).  Lets a caller
+     * script an acceptance schedule by corrupting chosen draft positions. */
+    int32_t replay_unchecked;
 } dfl_generate_params;
 
 typedef struct dfl_generate_stats { /* DflashDecodeStats  qwen/dflash.rs:380-418 */

@@ -71,7 +71,7 @@ class AcceptDecision(C.Structure):
 class GenerateParams(C.Structure):
     _fields_ = [("max_tokens", C.c_uint32), ("stop_ids", C.POINTER(C.c_int32)), ("n_stop_ids", C.c_uint32),
                 ("replay_history", C.POINTER(C.c_int32)), ("n_replay_history", C.c_uint32), ("sparse_proposals", C.c_int32),
-                ("verify_margin", C.c_float)]
+                ("verify_margin", C.c_float), ("replay_runs_drafter", C.c_int32), ("replay_unchecked", C.c_int32)]
 
 
 class GenerateStats(C.Structure):
@@ -502,7 +502,7 @@ def prefill(model, session, scratch, layer_ids, ids, start_position=0, feed_draf
 
 
 def generate(model, session, scratch, dsession, sampler, first_logits, max_tokens, stop_ids=(), replay_history=None,
-             sparse_proposals=False, verify_margin=0.0):
+             sparse_proposals=False, verify_margin=0.0, replay_runs_drafter=False, replay_unchecked=False):
     first_logits = np.ascontiguousarray(first_logits, dtype=np.float32)
     stops = np.ascontiguousarray(stop_ids, dtype=np.int32)
     hist = np.ascontiguousarray(replay_history, dtype=np.int32) if replay_history is not None else None
@@ -514,9 +514,64 @@ def generate(model, session, scratch, dsession, sampler, first_logits, max_token
     p.n_replay_history = hist.size if hist is not None else 0
     p.sparse_proposals = 1 if sparse_proposals else 0
     p.verify_margin = verify_margin
+    p.replay_runs_drafter = 1 if replay_runs_drafter else 0
+    p.replay_unchecked = 1 if replay_unchecked else 0
     out = np.zeros(max_tokens, dtype=np.int32)
     n = C.c_uint32(0)
     stats = GenerateStats()
     check(lib().dfl_generate(model.h, session.h, scratch.h, dsession.h, sampler.h, _ptr(first_logits), C.byref(p), _ptr(out), C.byref(n),
                              C.byref(stats)))
     return out[:n.value].copy(), stats
+
+
+def gemm_timing_begin():
+    lib().dfl_gemm_timing_begin()
+
+
+def gemm_timing_end():
+    ms, n, b = C.c_double(0), C.c_uint64(0), C.c_uint64(0)
+    check(lib().dfl_gemm_timing_end(C.byref(ms), C.byref(n), C.byref(b)))
+    return float(ms.value), int(n.value), int(b.value)
+
+
+def synth_tensor(name, dtype, n_in, n_out, seed, std, device=0, shape=None):
+    """A seeded N(0, std) tensor quantised on the GPU.  Returns (name, dtype, shape, device_ptr, n_bytes)."""
+    ptr, nb = C.c_void_p(), C.c_uint64(0)
+    check(lib().dfl_synth_tensor(C.c_int32(device), C.c_int32(dtype), C.c_uint64(n_in), C.c_uint64(n_out), C.c_uint64(seed),
+                                 C.c_float(std), C.byref(ptr), C.byref(nb)))
+    return (name, dtype, shape or [n_in, n_out], ptr.value, int(nb.value))
+
+
+def device_free(ptr, device=0):
+    check(lib().dfl_device_free(C.c_int32(device), C.c_void_p(ptr)))
+
+
+def device_to_host(ptr, n_bytes, device=0):
+    out = np.zeros(n_bytes, dtype=np.uint8)
+    check(lib().dfl_device_to_host(C.c_int32(device), C.c_void_p(ptr), _ptr(out), C.c_uint64(n_bytes)))
+    return out
+
+
+def make_device_tensor_table(entries):
+    """entries: (name, dtype, shape, ptr_or_ndarray, n_bytes or None); ints are device pointers, arrays host data."""
+    arr = (Tensor * len(entries))()
+    keep = []
+    for i, (name, dtype, shape, data, nb) in enumerate(entries):
+        nm = name.encode()
+        arr[i].name = nm
+        arr[i].dtype = dtype
+        arr[i].n_dims = len(shape)
+        for j, d in enumerate(shape):
+            arr[i].shape[j] = d
+        if isinstance(data, int):
+            arr[i].data = data
+            arr[i].n_bytes = nb
+            arr[i].on_device = 1
+            keep.append(nm)
+        else:
+            raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+            arr[i].data = raw.ctypes.data
+            arr[i].n_bytes = raw.size
+            arr[i].on_device = 0
+            keep.append((nm, raw))
+    return arr, keep

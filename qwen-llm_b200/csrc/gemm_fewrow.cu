@@ -18,6 +18,8 @@
 //   * per-warp partial tiles are summed in a fixed order through shared memory and the
 //     split-K partial [16][n_out] is written coalesced.  No atomics: results are
 //     deterministic and each activation row's result is independent of the other rows.
+#include <vector>
+
 #include "tiles.cuh"
 
 namespace dfl {
@@ -532,6 +534,13 @@ static dfl_status launch_t(cudaStream_t st, const GemmParams& p, int grid, bool 
     return DFL_OK;
 }
 
+// ---- optional per-launch timing ---------------------------------------------------------
+struct TimedLaunch { cudaEvent_t e0, e1; uint64_t bytes; };
+static bool g_timing = false;
+static std::vector<TimedLaunch> g_timed;
+
+static dfl_status launch_gemm_dispatch(cudaStream_t st, const QMatrix& m, const GemmParams& p, int grid, bool pdl);
+
 dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits,
                               const GemmEpilogue& ep, int* dev_err, bool pdl, uint32_t ld_out) {
     if (splits < 1 || splits > m.kblocks) return fail(DFL_ERR_BAD_ARG, "gemm: bad split count");
@@ -550,6 +559,19 @@ dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* 
     p.ld_out = ld_out ? ld_out : (uint32_t)m.n_out;
     p.err = dev_err;
     const int grid = m.row_tiles * splits;
+    if (!g_timing) return launch_gemm_dispatch(st, m, p, grid, pdl);
+    TimedLaunch t{};
+    t.bytes = m.ggml_bytes();
+    DFL_CUDA(cudaEventCreate(&t.e0));
+    DFL_CUDA(cudaEventCreate(&t.e1));
+    DFL_CUDA(cudaEventRecord(t.e0, st));
+    dfl_status rc = launch_gemm_dispatch(st, m, p, grid, pdl);
+    DFL_CUDA(cudaEventRecord(t.e1, st));
+    g_timed.push_back(t);
+    return rc;
+}
+
+static dfl_status launch_gemm_dispatch(cudaStream_t st, const QMatrix& m, const GemmParams& p, int grid, bool pdl) {
     switch (m.dtype) {
         case DFL_Q4_K: return launch_t<DFL_Q4_K>(st, p, grid, pdl);
         case DFL_Q5_K: return launch_t<DFL_Q5_K>(st, p, grid, pdl);
@@ -758,3 +780,29 @@ dfl_status launch_argmax_top2(cudaStream_t st, const float* logits, int n_rows, 
 }
 
 }  // namespace dfl
+
+extern "C" {
+void dfl_gemm_timing_begin(void) {
+    for (auto& t : dfl::g_timed) { cudaEventDestroy(t.e0); cudaEventDestroy(t.e1); }
+    dfl::g_timed.clear();
+    dfl::g_timing = true;
+}
+dfl_status dfl_gemm_timing_end(double* ms_total, uint64_t* n_launches, uint64_t* weight_bytes) {
+    dfl::g_timing = false;
+    double ms = 0;
+    uint64_t bytes = 0;
+    for (auto& t : dfl::g_timed) {
+        float one = 0;
+        cudaEventSynchronize(t.e1);
+        if (cudaEventElapsedTime(&one, t.e0, t.e1) == cudaSuccess) ms += one;
+        bytes += t.bytes;
+        cudaEventDestroy(t.e0);
+        cudaEventDestroy(t.e1);
+    }
+    if (ms_total) *ms_total = ms;
+    if (n_launches) *n_launches = dfl::g_timed.size();
+    if (weight_bytes) *weight_bytes = bytes;
+    dfl::g_timed.clear();
+    return DFL_OK;
+}
+}

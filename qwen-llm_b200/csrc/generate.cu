@@ -122,7 +122,8 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         const int32_t* replay = nullptr;
         if (params->replay_history && !sampled) {  // dflash_prefix_replay_drafts, qwen/dflash.rs:351-360
             const size_t emitted = tokens.size();
-            if (emitted + (N - 1) <= params->n_replay_history && std::memcmp(params->replay_history, tokens.data(), emitted * 4) == 0)
+            if (emitted + (N - 1) <= params->n_replay_history &&
+                (params->replay_unchecked || std::memcmp(params->replay_history, tokens.data(), emitted * 4) == 0))
                 replay = params->replay_history + emitted;
         }
         std::vector<int32_t> prop_tok;
@@ -130,6 +131,18 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         std::vector<int32_t> prop_ct;
         std::vector<double> prop_cw;
         if (replay) {
+            if (params->replay_runs_drafter) {
+                int32_t discard[MAX_ROWS];
+                cudaEventRecord(dv.ev0, dv.st);
+                rc = dfl_draft_block(ds, carry, position, discard, nullptr);
+                cudaEventRecord(dv.ev1, dv.st);
+                if (rc != DFL_OK) break;
+                cudaEventSynchronize(dv.ev1);
+                float ms = 0;
+                cudaEventElapsedTime(&ms, dv.ev0, dv.ev1);
+                st.draft_ms += ms;
+                ++st.drafter_calls;
+            }
             draft[0] = carry;
             for (uint32_t i = 1; i < N; ++i) draft[i] = replay[i - 1];
         } else {
