@@ -256,6 +256,8 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     if args.workload == "c1":
         line = run_c1(args, rank, world, local)
+    elif args.workload == "c2v":
+        line = importlib.import_module("bench_c2").run_verify_only(args, rank, world, local)
     else:
         c2 = importlib.import_module("bench_c2")
         line = c2.run(args, rank, world, local)

@@ -306,3 +306,37 @@ def run(args, rank, world, device):
         except Exception as e:  # the baseline is a reported extra; never lose the GPU line over it
             line["cpu_baseline"] = {"value": None, "unit": bench.UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
     return line
+
+
+def run_verify_only(args, rank, world, device):
+    """Workload c2v: packed verify steps only (16 rows, context 16..), for kernel profiling on the real shapes."""
+    bench = importlib.import_module("bench")
+    pkg, syn = _pkg(), _syn()
+    arch = syn.arch_9b()
+    ents = syn.target_entries(arch, seed=100, device=device)
+    model = syn.build_model(arch, ents, device)
+    syn.free_entries(ents, device)
+    sess, scr = pkg.Session(model, 1024, True), pkg.Scratch(model, 16, 5)
+    ids = [5, 12, 18, 25, 31]
+    rng = np.random.default_rng(0)
+    pos = 0
+    for _ in range(max(args.warmup, 1)):
+        pkg.packed_verify(model, sess, scr, ids, rng.integers(0, arch.vocab_size, size=16), pos)
+        pos += 16
+    launches0 = pkg.launch_count()
+    pkg.gemm_timing_begin() if os.environ.get("DFL_GEMM_TIMING") else None
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        pkg.packed_verify(model, sess, scr, ids, rng.integers(0, arch.vocab_size, size=16), pos)
+        pos += 16
+    wall = (time.perf_counter() - t0) / args.steps
+    extra = {}
+    if os.environ.get("DFL_GEMM_TIMING"):
+        ms, n, b = pkg.gemm_timing_end()
+        extra = {"gemm_ms_per_step": ms / args.steps, "gemm_launches": n, "gemm_GBps": b / (ms * 1e-3) / 1e9}
+    peak, kind = bench.measured_peaks()
+    vb = model.verify_weight_bytes()
+    return {"metric": "verify_ms", "value": wall * 1e3, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": wall * 1e3, "higher_is_better": False, "config": {"workload": "c2v: packed verify only, 16 rows"},
+            "roofline": {"bound": "hbm", "achieved": vb / wall / 1e9, "peak": peak, "unit": "GB/s", "frac": vb / wall / 1e9 / peak,
+                         "traffic": None, "peak_kind": kind}, "gpu_launches": int(pkg.launch_count() - launches0), **extra}
