@@ -5,16 +5,18 @@
 //
 // Design (HBM-bound: every weight byte is read exactly once):
 //   * one CTA owns a 128-row tile and a contiguous range of 256-column blocks; a producer
-//     warp streams the tile stages with 1-D bulk copies (TMA) into a 2-3 deep shared-memory
+//     warp streams the tile stages with 1-D bulk copies (TMA) into a multi-stage shared-memory
 //     ring guarded by mbarriers, weights first (they do not depend on the previous kernel,
 //     so under programmatic dependent launch they prefetch while it still runs), the packed
 //     activations after griddepcontrol.wait;
-//   * eight consumer warps split the 256 columns (32 each).  The *integer* quants go
-//     straight from shared memory through a few logic ops into f16 MMA A-fragments
-//     (magic-number int->half conversion, exact), the activations are the B operand as an
-//     exact hi+lo f16 pair, and mma.sync m16n8k16 accumulates sum(x*q) in f32.  Block scales
-//     (d*sc, dmin*m) are applied in f32 per 16/32 columns, so no dequantised weight is ever
-//     rounded: a one-hot activation row reproduces ggml's decoded weight bit for bit;
+//   * sixteen consumer warps: warp (ks, mh) owns columns [32 ks, 32 ks + 32) of the stage and
+//     the four 16-row m-tiles 4 mh .. 4 mh + 3.  The *integer* quants go straight from shared
+//     memory through a few logic ops into f16 MMA A-fragments (magic-number int->half
+//     conversion, exact), the activations are the B operand as an exact hi+lo f16 pair, and
+//     mma.sync m16n8k16 accumulates sum(x*q) in f32, two m-tiles interleaved so that four
+//     independent accumulator chains are in flight.  Block scales (d*sc, dmin*m) are applied
+//     in f32 per 16/32 columns, so no dequantised weight is ever rounded: a one-hot activation
+//     row reproduces ggml's decoded weight bit for bit;
 //   * per-warp partial tiles are summed in a fixed order through shared memory and the
 //     split-K partial [16][n_out] is written coalesced.  No atomics: results are
 //     deterministic and each activation row's result is independent of the other rows.
@@ -24,11 +26,13 @@
 
 namespace dfl {
 
-constexpr int CONSUMER_WARPS = 8;
-constexpr int GEMM_THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int K_SLICES = 8;                                         // warps along the 256 columns of a stage
+constexpr int M_HALVES = 2;                                         // warps along the 128 rows
+constexpr int CONSUMER_WARPS = K_SLICES * M_HALVES;                 // 16
+constexpr int GEMM_THREADS = (CONSUMER_WARPS + 1) * 32;             // + producer warp
 constexpr int RED_LD = TILE_R + 4;                                  // padded row length of the reduce buffer
-constexpr int RED_BYTES = CONSUMER_WARPS * MAX_ROWS * RED_LD * 4;   // 67584
-constexpr int WARP_SCRATCH = TILE_R * 8;                            // float2 per row, per warp
+constexpr int RED_BYTES = K_SLICES * MAX_ROWS * RED_LD * 4;         // 67584
+constexpr int WARP_SCRATCH = (TILE_R / M_HALVES) * 8;               // float2 per row of the warp's 64 rows
 
 struct GemmParams {
     const uint8_t* w;
@@ -82,91 +86,131 @@ constexpr uint32_t H2_M96 = 0xd600d600u;    // half2(-96, -96)
 // Activation fragments of one consumer warp for one stage (f16 hi/lo variant).
 struct ActFrag16 {
     uint4 hi0, hi1, lo0, lo1;  // token g / g+8; .x,.y = step 0 (b0,b1); .z,.w = step 1
-    __device__ __forceinline__ void load(const uint8_t* ast, int w, int g, int t) {
-        const int off = (32 * w + 8 * t) * 2;
+    __device__ __forceinline__ void load(const uint8_t* ast, int ks, int g, int t) {
+        const int off = (32 * ks + 8 * t) * 2;
         hi0 = *reinterpret_cast<const uint4*>(ast + g * (ACT_ROW_HALFS * 2) + off);
         hi1 = *reinterpret_cast<const uint4*>(ast + (g + 8) * (ACT_ROW_HALFS * 2) + off);
         lo0 = *reinterpret_cast<const uint4*>(ast + ACT_PLANE + g * (ACT_ROW_HALFS * 2) + off);
         lo1 = *reinterpret_cast<const uint4*>(ast + ACT_PLANE + (g + 8) * (ACT_ROW_HALFS * 2) + off);
     }
 };
-// d0 += A(step) x tokens 0-7, d1 += A(step) x tokens 8-15, hi and lo parts.
-__device__ __forceinline__ void mma_step0(float (&d0)[4], float (&d1)[4], const ActFrag16& f, uint32_t a0, uint32_t a1,
-                                          uint32_t a2, uint32_t a3) {
-    mma_f16(d0, a0, a1, a2, a3, f.hi0.x, f.hi0.y);
-    mma_f16(d1, a0, a1, a2, a3, f.hi1.x, f.hi1.y);
-    mma_f16(d0, a0, a1, a2, a3, f.lo0.x, f.lo0.y);
-    mma_f16(d1, a0, a1, a2, a3, f.lo1.x, f.lo1.y);
+
+// A[m][0..3] = step-0 fragment (a0,a1,a2,a3) of m-tile m, A[m][4..7] = step-1 fragment.
+// Both steps into the same accumulators d[m][token half]: four independent chains of four MMAs.
+__device__ __forceinline__ void mma_pair_same_scale(float (&d)[2][2][4], const uint32_t (&A)[2][8], const ActFrag16& f) {
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        mma_f16(d[m][0], A[m][0], A[m][1], A[m][2], A[m][3], f.hi0.x, f.hi0.y);
+        mma_f16(d[m][1], A[m][0], A[m][1], A[m][2], A[m][3], f.hi1.x, f.hi1.y);
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        mma_f16(d[m][0], A[m][4], A[m][5], A[m][6], A[m][7], f.hi0.z, f.hi0.w);
+        mma_f16(d[m][1], A[m][4], A[m][5], A[m][6], A[m][7], f.hi1.z, f.hi1.w);
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        mma_f16(d[m][0], A[m][0], A[m][1], A[m][2], A[m][3], f.lo0.x, f.lo0.y);
+        mma_f16(d[m][1], A[m][0], A[m][1], A[m][2], A[m][3], f.lo1.x, f.lo1.y);
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        mma_f16(d[m][0], A[m][4], A[m][5], A[m][6], A[m][7], f.lo0.z, f.lo0.w);
+        mma_f16(d[m][1], A[m][4], A[m][5], A[m][6], A[m][7], f.lo1.z, f.lo1.w);
+    }
 }
-__device__ __forceinline__ void mma_step1(float (&d0)[4], float (&d1)[4], const ActFrag16& f, uint32_t a0, uint32_t a1,
-                                          uint32_t a2, uint32_t a3) {
-    mma_f16(d0, a0, a1, a2, a3, f.hi0.z, f.hi0.w);
-    mma_f16(d1, a0, a1, a2, a3, f.hi1.z, f.hi1.w);
-    mma_f16(d0, a0, a1, a2, a3, f.lo0.z, f.lo0.w);
-    mma_f16(d1, a0, a1, a2, a3, f.lo1.z, f.lo1.w);
+// Separate accumulators per step (per-16-column scales): d[m][step][token half].
+__device__ __forceinline__ void mma_pair_step_scale(float (&d)[2][2][2][4], const uint32_t (&A)[2][8], const ActFrag16& f) {
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        mma_f16(d[m][0][0], A[m][0], A[m][1], A[m][2], A[m][3], f.hi0.x, f.hi0.y);
+        mma_f16(d[m][0][1], A[m][0], A[m][1], A[m][2], A[m][3], f.hi1.x, f.hi1.y);
+        mma_f16(d[m][1][0], A[m][4], A[m][5], A[m][6], A[m][7], f.hi0.z, f.hi0.w);
+        mma_f16(d[m][1][1], A[m][4], A[m][5], A[m][6], A[m][7], f.hi1.z, f.hi1.w);
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        mma_f16(d[m][0][0], A[m][0], A[m][1], A[m][2], A[m][3], f.lo0.x, f.lo0.y);
+        mma_f16(d[m][0][1], A[m][0], A[m][1], A[m][2], A[m][3], f.lo1.x, f.lo1.y);
+        mma_f16(d[m][1][0], A[m][4], A[m][5], A[m][6], A[m][7], f.lo0.z, f.lo0.w);
+        mma_f16(d[m][1][1], A[m][4], A[m][5], A[m][6], A[m][7], f.lo1.z, f.lo1.w);
+    }
 }
 
-// ---- per-format stage consumers ----------------------------------------------
-// acc[mt][c]: c0,c1 = (row 16mt+g, tokens 2t,2t+1), c2,c3 = (row 16mt+g+8, same tokens),
-//             c4..c7 the same for tokens 8+2t, 9+2t.
+// acc[mt][c] (mt = 0..3 local m-tile of this warp): c0,c1 = (row 16mt+g, tokens 2t,2t+1),
+// c2,c3 = (row 16mt+g+8, same tokens), c4..c7 the same for tokens 8+2t, 9+2t.
+// sa / sb: (scale, min) of rows g / g+8;  s0..s3: activation sub-block sums of the lane's four tokens.
+__device__ __forceinline__ void apply_scale_min(float (&acc)[8], const float (&d0)[4], const float (&d1)[4], float2 sa, float2 sb,
+                                                float s0, float s1, float s2, float s3) {
+    acc[0] = fmaf(-sa.y, s0, fmaf(sa.x, d0[0], acc[0]));
+    acc[1] = fmaf(-sa.y, s1, fmaf(sa.x, d0[1], acc[1]));
+    acc[2] = fmaf(-sb.y, s0, fmaf(sb.x, d0[2], acc[2]));
+    acc[3] = fmaf(-sb.y, s1, fmaf(sb.x, d0[3], acc[3]));
+    acc[4] = fmaf(-sa.y, s2, fmaf(sa.x, d1[0], acc[4]));
+    acc[5] = fmaf(-sa.y, s3, fmaf(sa.x, d1[1], acc[5]));
+    acc[6] = fmaf(-sb.y, s2, fmaf(sb.x, d1[2], acc[6]));
+    acc[7] = fmaf(-sb.y, s3, fmaf(sb.x, d1[3], acc[7]));
+}
+// K-quant header {f16 d, f16 dmin, 12 B of 6-bit (scale, min)} -> (d*sc, dmin*m) of sub-block j.
+__device__ __forceinline__ float2 k4_header_scale(const uint4 h, int j) {
+    const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+    uint32_t s, m;
+    if (j < 4) {
+        s = (h.y >> (8 * j)) & 63u;
+        m = (h.z >> (8 * j)) & 63u;
+    } else {
+        const int jj = j - 4;
+        s = ((h.w >> (8 * jj)) & 0xfu) | (((h.y >> (8 * jj + 6)) & 3u) << 4);
+        m = ((h.w >> (8 * jj + 4)) & 0xfu) | (((h.z >> (8 * jj + 6)) & 3u) << 4);
+    }
+    return make_float2(d * (float)s, dmin * (float)m);
+}
+
 template <int DT>
 struct Fmt;
 
 template <>
 struct Fmt<DFL_Q4_K> {
-    static constexpr int STAGE = STAGE_Q4_K, ACT = ACT16_CHUNK, STAGES = 3;
-    static constexpr bool HAS_HI = false;
-    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[8][8],
-                                                   int w, int lane) {
+    static constexpr int STAGE = STAGE_Q4_K, ACT = ACT16_CHUNK, STAGES = 4;
+    __device__ static __forceinline__ void unpack(uint32_t wq, uint32_t wq8, uint32_t (&A)[8]) {
+        A[0] = h2_sub((wq & 0x000f000fu) | H2_1024, H2_1024);
+        A[1] = h2_sub((wq8 & 0x000f000fu) | H2_1024, H2_1024);
+        A[2] = h2_fma((wq & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64);
+        A[3] = h2_fma((wq8 & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64);
+        const uint32_t v = wq >> 8, v8 = wq8 >> 8;
+        A[4] = h2_sub((v & 0x000f000fu) | H2_1024, H2_1024);
+        A[5] = h2_sub((v8 & 0x000f000fu) | H2_1024, H2_1024);
+        A[6] = h2_fma((v & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64);
+        A[7] = h2_fma((v8 & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64);
+    }
+    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[4][8], int ks,
+                                                   int mh, int lane) {
         const int g = lane >> 2, t = lane & 3;
-        // (d*sc_w, dmin*m_w) of this warp's 32-column sub-block for all 128 rows
+        // (d*sc, dmin*m) of this warp's 32-column sub-block for its 64 rows
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
             const int r = lane + 32 * i;
-            const uint4 h = reinterpret_cast<const uint4*>(wst)[r];
-            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
-            const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-            uint32_t s, m;
-            if (w < 4) {
-                s = (h.y >> (8 * w)) & 63u;
-                m = (h.z >> (8 * w)) & 63u;
-            } else {
-                const int jj = w - 4;
-                s = ((h.w >> (8 * jj)) & 0xfu) | (((h.y >> (8 * jj + 6)) & 3u) << 4);
-                m = ((h.w >> (8 * jj + 4)) & 0xfu) | (((h.z >> (8 * jj + 6)) & 3u) << 4);
-            }
-            sc[r] = make_float2(d * (float)s, dmin * (float)m);
+            sc[r] = k4_header_scale(reinterpret_cast<const uint4*>(wst)[64 * mh + r], ks);
         }
         __syncwarp();
         ActFrag16 f;
-        f.load(ast, w, g, t);
+        f.load(ast, ks, g, t);
         const float* S = reinterpret_cast<const float*>(ast + 2 * ACT_PLANE);
-        const float s0 = S[(2 * t) * 8 + w], s1 = S[(2 * t + 1) * 8 + w], s2 = S[(2 * t + 8) * 8 + w], s3 = S[(2 * t + 9) * 8 + w];
-        const uint4* q = reinterpret_cast<const uint4*>(wst + Q4K_OFF_QS) + (w * 4) * 32 + lane;
+        const float s0 = S[(2 * t) * 8 + ks], s1 = S[(2 * t + 1) * 8 + ks], s2 = S[(2 * t + 8) * 8 + ks], s3 = S[(2 * t + 9) * 8 + ks];
+        const uint4* q = reinterpret_cast<const uint4*>(wst + Q4K_OFF_QS) + (ks * 4 + 2 * mh) * 32 + lane;
 #pragma unroll
-        for (int mtp = 0; mtp < 4; ++mtp) {
-            const uint4 qq = q[mtp * 32];
+        for (int p = 0; p < 2; ++p) {
+            const uint4 qq = q[p * 32];  // x,y = m-tile 2p rows g,g+8;  z,w = m-tile 2p+1
+            uint32_t A[2][8];
+            unpack(qq.x, qq.y, A[0]);
+            unpack(qq.z, qq.w, A[1]);
+            float d[2][2][4] = {};
+            mma_pair_same_scale(d, A, f);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int mt = 2 * mtp + h;
-                const uint32_t wg = h ? qq.z : qq.x, wg8 = h ? qq.w : qq.y;
-                const uint32_t l0 = h2_sub((wg & 0x000f000fu) | H2_1024, H2_1024), l1 = h2_sub((wg8 & 0x000f000fu) | H2_1024, H2_1024);
-                const uint32_t h0 = h2_fma((wg & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64), h1 = h2_fma((wg8 & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64);
-                const uint32_t vg = wg >> 8, vg8 = wg8 >> 8;
-                const uint32_t l2 = h2_sub((vg & 0x000f000fu) | H2_1024, H2_1024), l3 = h2_sub((vg8 & 0x000f000fu) | H2_1024, H2_1024);
-                const uint32_t h2 = h2_fma((vg & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64), h3 = h2_fma((vg8 & 0x00f000f0u) | H2_1024, H2_16TH, H2_M64);
-                float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_step0(d0, d1, f, l0, l1, h0, h1);
-                mma_step1(d0, d1, f, l2, l3, h2, h3);
-                const float2 a = sc[16 * mt + g], b = sc[16 * mt + g + 8];
-                acc[mt][0] = fmaf(-a.y, s0, fmaf(a.x, d0[0], acc[mt][0]));
-                acc[mt][1] = fmaf(-a.y, s1, fmaf(a.x, d0[1], acc[mt][1]));
-                acc[mt][2] = fmaf(-b.y, s0, fmaf(b.x, d0[2], acc[mt][2]));
-                acc[mt][3] = fmaf(-b.y, s1, fmaf(b.x, d0[3], acc[mt][3]));
-                acc[mt][4] = fmaf(-a.y, s2, fmaf(a.x, d1[0], acc[mt][4]));
-                acc[mt][5] = fmaf(-a.y, s3, fmaf(a.x, d1[1], acc[mt][5]));
-                acc[mt][6] = fmaf(-b.y, s2, fmaf(b.x, d1[2], acc[mt][6]));
-                acc[mt][7] = fmaf(-b.y, s3, fmaf(b.x, d1[3], acc[mt][7]));
+            for (int m = 0; m < 2; ++m) {
+                const int mt = 2 * p + m;
+                apply_scale_min(acc[mt], d[m][0], d[m][1], sc[16 * mt + g], sc[16 * mt + g + 8], s0, s1, s2, s3);
             }
         }
         __syncwarp();
@@ -175,65 +219,45 @@ struct Fmt<DFL_Q4_K> {
 
 template <>
 struct Fmt<DFL_Q5_K> {
-    static constexpr int STAGE = STAGE_Q5_K, ACT = ACT16_CHUNK, STAGES = 2;
-    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[8][8],
-                                                   int w, int lane) {
+    static constexpr int STAGE = STAGE_Q5_K, ACT = ACT16_CHUNK, STAGES = 4;
+    __device__ static __forceinline__ void unpack(uint32_t wq, uint32_t hb, uint32_t& a_l0, uint32_t& a_h0, uint32_t& a_l1, uint32_t& a_h1) {
+        const uint32_t X = (hb & 0xfu) | ((hb & 0xf0u) << 12);
+        const uint32_t v = wq >> 8;
+        a_l0 = h2_sub((wq & 0x000f000fu) | ((X << 4) & 0x00100010u) | H2_1024, H2_1024);
+        a_h0 = h2_fma((wq & 0x00f000f0u) | ((X << 7) & 0x01000100u) | H2_1024, H2_16TH, H2_M64);
+        a_l1 = h2_sub((v & 0x000f000fu) | ((X << 2) & 0x00100010u) | H2_1024, H2_1024);
+        a_h1 = h2_fma((v & 0x00f000f0u) | ((X << 5) & 0x01000100u) | H2_1024, H2_16TH, H2_M64);
+    }
+    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[4][8], int ks,
+                                                   int mh, int lane) {
         const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
             const int r = lane + 32 * i;
-            const uint4 h = reinterpret_cast<const uint4*>(wst)[r];
-            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
-            const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-            uint32_t s, m;
-            if (w < 4) {
-                s = (h.y >> (8 * w)) & 63u;
-                m = (h.z >> (8 * w)) & 63u;
-            } else {
-                const int jj = w - 4;
-                s = ((h.w >> (8 * jj)) & 0xfu) | (((h.y >> (8 * jj + 6)) & 3u) << 4);
-                m = ((h.w >> (8 * jj + 4)) & 0xfu) | (((h.z >> (8 * jj + 6)) & 3u) << 4);
-            }
-            sc[r] = make_float2(d * (float)s, dmin * (float)m);
+            sc[r] = k4_header_scale(reinterpret_cast<const uint4*>(wst)[64 * mh + r], ks);
         }
         __syncwarp();
         ActFrag16 f;
-        f.load(ast, w, g, t);
+        f.load(ast, ks, g, t);
         const float* S = reinterpret_cast<const float*>(ast + 2 * ACT_PLANE);
-        const float s0 = S[(2 * t) * 8 + w], s1 = S[(2 * t + 1) * 8 + w], s2 = S[(2 * t + 8) * 8 + w], s3 = S[(2 * t + 9) * 8 + w];
-        const uint4* q = reinterpret_cast<const uint4*>(wst + Q5K_OFF_QS) + (w * 4) * 32 + lane;
-        const uint32_t* qh = reinterpret_cast<const uint32_t*>(wst + Q5K_OFF_QH) + (w * 4) * 32 + lane;
+        const float s0 = S[(2 * t) * 8 + ks], s1 = S[(2 * t + 1) * 8 + ks], s2 = S[(2 * t + 8) * 8 + ks], s3 = S[(2 * t + 9) * 8 + ks];
+        const uint4* q = reinterpret_cast<const uint4*>(wst + Q5K_OFF_QS) + (ks * 4 + 2 * mh) * 32 + lane;
+        const uint32_t* qh = reinterpret_cast<const uint32_t*>(wst + Q5K_OFF_QH) + (ks * 4 + 2 * mh) * 32 + lane;
 #pragma unroll
-        for (int mtp = 0; mtp < 4; ++mtp) {
-            const uint4 qq = q[mtp * 32];
-            const uint32_t hb4 = qh[mtp * 32];
+        for (int p = 0; p < 2; ++p) {
+            const uint4 qq = q[p * 32];
+            const uint32_t hb4 = qh[p * 32];  // bytes: (mt 2p, g), (mt 2p, g+8), (mt 2p+1, g), (mt 2p+1, g+8)
+            uint32_t A[2][8];
+            unpack(qq.x, hb4 & 0xffu, A[0][0], A[0][2], A[0][4], A[0][6]);
+            unpack(qq.y, (hb4 >> 8) & 0xffu, A[0][1], A[0][3], A[0][5], A[0][7]);
+            unpack(qq.z, (hb4 >> 16) & 0xffu, A[1][0], A[1][2], A[1][4], A[1][6]);
+            unpack(qq.w, hb4 >> 24, A[1][1], A[1][3], A[1][5], A[1][7]);
+            float d[2][2][4] = {};
+            mma_pair_same_scale(d, A, f);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int mt = 2 * mtp + h;
-                uint32_t a[2][4];  // [row half][l(step0), h(step0), l(step1), h(step1)]
-#pragma unroll
-                for (int rh = 0; rh < 2; ++rh) {
-                    const uint32_t wq = h ? (rh ? qq.w : qq.z) : (rh ? qq.y : qq.x);
-                    const uint32_t hb = (hb4 >> (8 * (2 * h + rh))) & 0xffu;
-                    const uint32_t X = (hb & 0xfu) | ((hb & 0xf0u) << 12);
-                    const uint32_t v = wq >> 8;
-                    a[rh][0] = h2_sub((wq & 0x000f000fu) | ((X << 4) & 0x00100010u) | H2_1024, H2_1024);
-                    a[rh][1] = h2_fma((wq & 0x00f000f0u) | ((X << 7) & 0x01000100u) | H2_1024, H2_16TH, H2_M64);
-                    a[rh][2] = h2_sub((v & 0x000f000fu) | ((X << 2) & 0x00100010u) | H2_1024, H2_1024);
-                    a[rh][3] = h2_fma((v & 0x00f000f0u) | ((X << 5) & 0x01000100u) | H2_1024, H2_16TH, H2_M64);
-                }
-                float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_step0(d0, d1, f, a[0][0], a[1][0], a[0][1], a[1][1]);
-                mma_step1(d0, d1, f, a[0][2], a[1][2], a[0][3], a[1][3]);
-                const float2 sa = sc[16 * mt + g], sb = sc[16 * mt + g + 8];
-                acc[mt][0] = fmaf(-sa.y, s0, fmaf(sa.x, d0[0], acc[mt][0]));
-                acc[mt][1] = fmaf(-sa.y, s1, fmaf(sa.x, d0[1], acc[mt][1]));
-                acc[mt][2] = fmaf(-sb.y, s0, fmaf(sb.x, d0[2], acc[mt][2]));
-                acc[mt][3] = fmaf(-sb.y, s1, fmaf(sb.x, d0[3], acc[mt][3]));
-                acc[mt][4] = fmaf(-sa.y, s2, fmaf(sa.x, d1[0], acc[mt][4]));
-                acc[mt][5] = fmaf(-sa.y, s3, fmaf(sa.x, d1[1], acc[mt][5]));
-                acc[mt][6] = fmaf(-sb.y, s2, fmaf(sb.x, d1[2], acc[mt][6]));
-                acc[mt][7] = fmaf(-sb.y, s3, fmaf(sb.x, d1[3], acc[mt][7]));
+            for (int m = 0; m < 2; ++m) {
+                const int mt = 2 * p + m;
+                apply_scale_min(acc[mt], d[m][0], d[m][1], sc[16 * mt + g], sc[16 * mt + g + 8], s0, s1, s2, s3);
             }
         }
         __syncwarp();
@@ -242,55 +266,55 @@ struct Fmt<DFL_Q5_K> {
 
 template <>
 struct Fmt<DFL_Q6_K> {
-    static constexpr int STAGE = STAGE_Q6_K, ACT = ACT16_CHUNK, STAGES = 2;
-    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[8][8],
-                                                   int w, int lane) {
+    static constexpr int STAGE = STAGE_Q6_K, ACT = ACT16_CHUNK, STAGES = 4;
+    // wq: low nibbles, X: the 2-bit high fields spread as byte0 -> bits 0-7, byte1 -> bits 16-23
+    __device__ static __forceinline__ void unpack(uint32_t wq, uint32_t X, uint32_t& a_l0, uint32_t& a_h0, uint32_t& a_l1, uint32_t& a_h1) {
+        const uint32_t v = wq >> 8;
+        a_l0 = h2_sub((wq & 0x000f000fu) | ((X << 4) & 0x00300030u) | H2_1024, H2_1056);
+        a_h0 = h2_fma((wq & 0x00f000f0u) | ((X << 6) & 0x03000300u) | H2_1024, H2_16TH, H2_M96);
+        a_l1 = h2_sub((v & 0x000f000fu) | (X & 0x00300030u) | H2_1024, H2_1056);
+        a_h1 = h2_fma((v & 0x00f000f0u) | ((X << 2) & 0x03000300u) | H2_1024, H2_16TH, H2_M96);
+    }
+    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[4][8], int ks,
+                                                   int mh, int lane) {
         const int g = lane >> 2, t = lane & 3;
-        // d*sc of the two 16-column sub-blocks (2w, 2w+1) this warp owns
+        // d*sc of the two 16-column sub-blocks (2ks, 2ks+1) this warp owns, for its 64 rows
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = lane + 32 * i;
-            const uint16_t two = *reinterpret_cast<const uint16_t*>(wst + r * 16 + 2 * w);
-            const float d = __half2float(__ushort_as_half(reinterpret_cast<const uint16_t*>(wst + Q6K_OFF_D)[r]));
+        for (int i = 0; i < 2; ++i) {
+            const int r = lane + 32 * i, row = 64 * mh + r;
+            const uint16_t two = *reinterpret_cast<const uint16_t*>(wst + row * 16 + 2 * ks);
+            const float d = __half2float(__ushort_as_half(reinterpret_cast<const uint16_t*>(wst + Q6K_OFF_D)[row]));
             sc[r] = make_float2(d * (float)(int8_t)(two & 0xff), d * (float)(int8_t)(two >> 8));
         }
         __syncwarp();
         ActFrag16 f;
-        f.load(ast, w, g, t);
-        const uint4* ql = reinterpret_cast<const uint4*>(wst + Q6K_OFF_QL) + (w * 4) * 32 + lane;
-        const uint2* qh = reinterpret_cast<const uint2*>(wst + Q6K_OFF_QH) + (w * 4) * 32 + lane;
+        f.load(ast, ks, g, t);
+        const uint4* ql = reinterpret_cast<const uint4*>(wst + Q6K_OFF_QL) + (ks * 4 + 2 * mh) * 32 + lane;
+        const uint2* qh = reinterpret_cast<const uint2*>(wst + Q6K_OFF_QH) + (ks * 4 + 2 * mh) * 32 + lane;
 #pragma unroll
-        for (int mtp = 0; mtp < 4; ++mtp) {
-            const uint4 qq = ql[mtp * 32];
-            const uint2 hh2 = qh[mtp * 32];
+        for (int p = 0; p < 2; ++p) {
+            const uint4 qq = ql[p * 32];
+            const uint2 hh = qh[p * 32];  // x: m-tile 2p (row g low 16 bits, row g+8 high 16 bits), y: m-tile 2p+1
+            uint32_t A[2][8];
+            unpack(qq.x, prmt(hh.x, 0u, 0x4140u), A[0][0], A[0][2], A[0][4], A[0][6]);
+            unpack(qq.y, prmt(hh.x, 0u, 0x4342u), A[0][1], A[0][3], A[0][5], A[0][7]);
+            unpack(qq.z, prmt(hh.y, 0u, 0x4140u), A[1][0], A[1][2], A[1][4], A[1][6]);
+            unpack(qq.w, prmt(hh.y, 0u, 0x4342u), A[1][1], A[1][3], A[1][5], A[1][7]);
+            float d[2][2][2][4] = {};
+            mma_pair_step_scale(d, A, f);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int mt = 2 * mtp + h;
-                const uint32_t hh = h ? hh2.y : hh2.x;
-                uint32_t a[2][4];
-#pragma unroll
-                for (int rh = 0; rh < 2; ++rh) {
-                    const uint32_t wq = h ? (rh ? qq.w : qq.z) : (rh ? qq.y : qq.x);
-                    const uint32_t X = prmt(hh, 0u, rh ? 0x4342u : 0x4140u);  // byte0 -> bits 0-7, byte1 -> bits 16-23
-                    const uint32_t v = wq >> 8;
-                    a[rh][0] = h2_sub((wq & 0x000f000fu) | ((X << 4) & 0x00300030u) | H2_1024, H2_1056);
-                    a[rh][1] = h2_fma((wq & 0x00f000f0u) | ((X << 6) & 0x03000300u) | H2_1024, H2_16TH, H2_M96);
-                    a[rh][2] = h2_sub((v & 0x000f000fu) | (X & 0x00300030u) | H2_1024, H2_1056);
-                    a[rh][3] = h2_fma((v & 0x00f000f0u) | ((X << 2) & 0x03000300u) | H2_1024, H2_16TH, H2_M96);
-                }
-                float d00[4] = {0.f, 0.f, 0.f, 0.f}, d01[4] = {0.f, 0.f, 0.f, 0.f};
-                float d10[4] = {0.f, 0.f, 0.f, 0.f}, d11[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_step0(d00, d01, f, a[0][0], a[1][0], a[0][1], a[1][1]);
-                mma_step1(d10, d11, f, a[0][2], a[1][2], a[0][3], a[1][3]);
+            for (int m = 0; m < 2; ++m) {
+                const int mt = 2 * p + m;
                 const float2 sa = sc[16 * mt + g], sb = sc[16 * mt + g + 8];
-                acc[mt][0] = fmaf(sa.y, d10[0], fmaf(sa.x, d00[0], acc[mt][0]));
-                acc[mt][1] = fmaf(sa.y, d10[1], fmaf(sa.x, d00[1], acc[mt][1]));
-                acc[mt][2] = fmaf(sb.y, d10[2], fmaf(sb.x, d00[2], acc[mt][2]));
-                acc[mt][3] = fmaf(sb.y, d10[3], fmaf(sb.x, d00[3], acc[mt][3]));
-                acc[mt][4] = fmaf(sa.y, d11[0], fmaf(sa.x, d01[0], acc[mt][4]));
-                acc[mt][5] = fmaf(sa.y, d11[1], fmaf(sa.x, d01[1], acc[mt][5]));
-                acc[mt][6] = fmaf(sb.y, d11[2], fmaf(sb.x, d01[2], acc[mt][6]));
-                acc[mt][7] = fmaf(sb.y, d11[3], fmaf(sb.x, d01[3], acc[mt][7]));
+                float(&a)[8] = acc[mt];
+                a[0] = fmaf(sa.y, d[m][1][0][0], fmaf(sa.x, d[m][0][0][0], a[0]));
+                a[1] = fmaf(sa.y, d[m][1][0][1], fmaf(sa.x, d[m][0][0][1], a[1]));
+                a[2] = fmaf(sb.y, d[m][1][0][2], fmaf(sb.x, d[m][0][0][2], a[2]));
+                a[3] = fmaf(sb.y, d[m][1][0][3], fmaf(sb.x, d[m][0][0][3], a[3]));
+                a[4] = fmaf(sa.y, d[m][1][1][0], fmaf(sa.x, d[m][0][1][0], a[4]));
+                a[5] = fmaf(sa.y, d[m][1][1][1], fmaf(sa.x, d[m][0][1][1], a[5]));
+                a[6] = fmaf(sb.y, d[m][1][1][2], fmaf(sb.x, d[m][0][1][2], a[6]));
+                a[7] = fmaf(sb.y, d[m][1][1][3], fmaf(sb.x, d[m][0][1][3], a[7]));
             }
         }
         __syncwarp();
@@ -299,39 +323,51 @@ struct Fmt<DFL_Q6_K> {
 
 template <>
 struct Fmt<DFL_Q8_0> {
-    static constexpr int STAGE = STAGE_Q8_0, ACT = ACT16_CHUNK, STAGES = 2;
-    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[8][8],
-                                                   int w, int lane) {
+    static constexpr int STAGE = STAGE_Q8_0, ACT = ACT16_CHUNK, STAGES = 4;
+    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[4][8], int ks,
+                                                   int mh, int lane) {
         const int g = lane >> 2, t = lane & 3;
         float* scf = reinterpret_cast<float*>(sc);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
             const int r = lane + 32 * i;
-            scf[r] = __half2float(__ushort_as_half(reinterpret_cast<const uint16_t*>(wst)[r * 8 + w]));
+            scf[r] = __half2float(__ushort_as_half(reinterpret_cast<const uint16_t*>(wst)[(64 * mh + r) * 8 + ks]));
         }
         __syncwarp();
         ActFrag16 f;
-        f.load(ast, w, g, t);
-        const uint4* q = reinterpret_cast<const uint4*>(wst + Q80_OFF_QS) + (w * 8) * 32 + lane;
+        f.load(ast, ks, g, t);
+        const uint4* q = reinterpret_cast<const uint4*>(wst + Q80_OFF_QS) + (ks * 8 + 4 * mh) * 32 + lane;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            const uint4 qq = q[mt * 32];  // x: row g step0, y: row g step1, z: row g+8 step0, w: row g+8 step1
-            const uint32_t a00 = h2_sub(prmt(qq.x, H2_1024, 0x5150u), H2_1152), a02 = h2_sub(prmt(qq.x, H2_1024, 0x5352u), H2_1152);
-            const uint32_t a01 = h2_sub(prmt(qq.z, H2_1024, 0x5150u), H2_1152), a03 = h2_sub(prmt(qq.z, H2_1024, 0x5352u), H2_1152);
-            const uint32_t a10 = h2_sub(prmt(qq.y, H2_1024, 0x5150u), H2_1152), a12 = h2_sub(prmt(qq.y, H2_1024, 0x5352u), H2_1152);
-            const uint32_t a11 = h2_sub(prmt(qq.w, H2_1024, 0x5150u), H2_1152), a13 = h2_sub(prmt(qq.w, H2_1024, 0x5352u), H2_1152);
-            float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_step0(d0, d1, f, a00, a01, a02, a03);
-            mma_step1(d0, d1, f, a10, a11, a12, a13);
-            const float da = scf[16 * mt + g], db = scf[16 * mt + g + 8];
-            acc[mt][0] = fmaf(da, d0[0], acc[mt][0]);
-            acc[mt][1] = fmaf(da, d0[1], acc[mt][1]);
-            acc[mt][2] = fmaf(db, d0[2], acc[mt][2]);
-            acc[mt][3] = fmaf(db, d0[3], acc[mt][3]);
-            acc[mt][4] = fmaf(da, d1[0], acc[mt][4]);
-            acc[mt][5] = fmaf(da, d1[1], acc[mt][5]);
-            acc[mt][6] = fmaf(db, d1[2], acc[mt][6]);
-            acc[mt][7] = fmaf(db, d1[3], acc[mt][7]);
+        for (int p = 0; p < 2; ++p) {
+            uint32_t A[2][8];
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const uint4 qq = q[(2 * p + m) * 32];  // x: row g step0, y: row g step1, z: row g+8 step0, w: row g+8 step1
+                A[m][0] = h2_sub(prmt(qq.x, H2_1024, 0x5150u), H2_1152);
+                A[m][1] = h2_sub(prmt(qq.z, H2_1024, 0x5150u), H2_1152);
+                A[m][2] = h2_sub(prmt(qq.x, H2_1024, 0x5352u), H2_1152);
+                A[m][3] = h2_sub(prmt(qq.z, H2_1024, 0x5352u), H2_1152);
+                A[m][4] = h2_sub(prmt(qq.y, H2_1024, 0x5150u), H2_1152);
+                A[m][5] = h2_sub(prmt(qq.w, H2_1024, 0x5150u), H2_1152);
+                A[m][6] = h2_sub(prmt(qq.y, H2_1024, 0x5352u), H2_1152);
+                A[m][7] = h2_sub(prmt(qq.w, H2_1024, 0x5352u), H2_1152);
+            }
+            float d[2][2][4] = {};
+            mma_pair_same_scale(d, A, f);
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const int mt = 2 * p + m;
+                const float da = scf[16 * mt + g], db = scf[16 * mt + g + 8];
+                float(&a)[8] = acc[mt];
+                a[0] = fmaf(da, d[m][0][0], a[0]);
+                a[1] = fmaf(da, d[m][0][1], a[1]);
+                a[2] = fmaf(db, d[m][0][2], a[2]);
+                a[3] = fmaf(db, d[m][0][3], a[3]);
+                a[4] = fmaf(da, d[m][1][0], a[4]);
+                a[5] = fmaf(da, d[m][1][1], a[5]);
+                a[6] = fmaf(db, d[m][1][2], a[6]);
+                a[7] = fmaf(db, d[m][1][3], a[7]);
+            }
         }
         __syncwarp();
     }
@@ -340,26 +376,37 @@ struct Fmt<DFL_Q8_0> {
 template <>
 struct Fmt<DFL_BF16> {
     static constexpr int STAGE = STAGE_B16, ACT = ACTB3_CHUNK, STAGES = 2;
-    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2*, float (&acc)[8][8], int w,
+    __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2*, float (&acc)[4][8], int ks, int mh,
                                                    int lane) {
         const int g = lane >> 2, t = lane & 3;
-        const int off = (32 * w + 8 * t) * 2;
+        const int off = (32 * ks + 8 * t) * 2;
         uint4 b0[3], b1[3];
 #pragma unroll
-        for (int p = 0; p < 3; ++p) {
-            b0[p] = *reinterpret_cast<const uint4*>(ast + p * ACT_PLANE + g * (ACT_ROW_HALFS * 2) + off);
-            b1[p] = *reinterpret_cast<const uint4*>(ast + p * ACT_PLANE + (g + 8) * (ACT_ROW_HALFS * 2) + off);
+        for (int pl = 0; pl < 3; ++pl) {
+            b0[pl] = *reinterpret_cast<const uint4*>(ast + pl * ACT_PLANE + g * (ACT_ROW_HALFS * 2) + off);
+            b1[pl] = *reinterpret_cast<const uint4*>(ast + pl * ACT_PLANE + (g + 8) * (ACT_ROW_HALFS * 2) + off);
         }
-        const uint4* q = reinterpret_cast<const uint4*>(wst) + (w * 8) * 64 + lane;
+        const uint4* q = reinterpret_cast<const uint4*>(wst) + (ks * 8 + 4 * mh) * 64 + lane;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            const uint4 ra = q[mt * 64], rb = q[mt * 64 + 32];  // rows g, g+8: x,y = step0 (e01,e23), z,w = step1
+        for (int p = 0; p < 2; ++p) {
+            uint4 ra[2], rb[2];  // rows g, g+8: x,y = step0 (e01,e23), z,w = step1
 #pragma unroll
-            for (int p = 0; p < 3; ++p) {
-                mma_bf16(&acc[mt][0], ra.x, rb.x, ra.y, rb.y, b0[p].x, b0[p].y);
-                mma_bf16(&acc[mt][4], ra.x, rb.x, ra.y, rb.y, b1[p].x, b1[p].y);
-                mma_bf16(&acc[mt][0], ra.z, rb.z, ra.w, rb.w, b0[p].z, b0[p].w);
-                mma_bf16(&acc[mt][4], ra.z, rb.z, ra.w, rb.w, b1[p].z, b1[p].w);
+            for (int m = 0; m < 2; ++m) {
+                ra[m] = q[(2 * p + m) * 64];
+                rb[m] = q[(2 * p + m) * 64 + 32];
+            }
+#pragma unroll
+            for (int pl = 0; pl < 3; ++pl) {
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    mma_bf16(&acc[2 * p + m][0], ra[m].x, rb[m].x, ra[m].y, rb[m].y, b0[pl].x, b0[pl].y);
+                    mma_bf16(&acc[2 * p + m][4], ra[m].x, rb[m].x, ra[m].y, rb[m].y, b1[pl].x, b1[pl].y);
+                }
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    mma_bf16(&acc[2 * p + m][0], ra[m].z, rb[m].z, ra[m].w, rb[m].w, b0[pl].z, b0[pl].w);
+                    mma_bf16(&acc[2 * p + m][4], ra[m].z, rb[m].z, ra[m].w, rb[m].w, b1[pl].z, b1[pl].w);
+                }
             }
         }
     }
@@ -401,9 +448,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
     // Let the next kernel in the stream start its own weight prefetch as early as possible.
     pdl_launch_dependents();
 
-    float acc[8][8];
+    float acc[4][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
@@ -440,28 +487,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
         }
     } else {
         // ---------------- consumers ----------------
-        float2* sc = scratch + warp * TILE_R;
+        const int ks = warp & (K_SLICES - 1), mh = warp >> 3;
+        float2* sc = scratch + warp * (TILE_R / M_HALVES);
         bool ok = true;
         for (int i = 0; i < n_it; ++i) {
             const int s = i % STAGES;
             ok = mbar_wait_bounded(&full[s], (i / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
             if (!ok) break;
-            F::consume(ring + s * SLOT, ring + s * SLOT + F::STAGE, sc, acc, warp, lane);
+            F::consume(ring + s * SLOT, ring + s * SLOT + F::STAGE, sc, acc, ks, mh, lane);
             if (lane == 0) mbar_arrive(&empty[s]);
         }
         if (!ok) atomicExch(&abort_flag, 1);
     }
-    if (warp == CONSUMER_WARPS) pdl_wait();  // lanes 1..31 (and lane 0 again): harmless, keeps the wait on every path
+    if (warp == CONSUMER_WARPS) pdl_wait();  // every thread of the producer warp has passed the dependency wait
     __syncthreads();
     if (abort_flag) return;  // error word already set; outputs are left untouched
 
-    // ---------------- epilogue: fixed-order cross-warp sum ----------------
+    // ---------------- epilogue: fixed-order sum over the eight column slices ----------------
     float* red = reinterpret_cast<float*>(ring);
     if (warp < CONSUMER_WARPS) {
+        const int ks = warp & (K_SLICES - 1), mh = warp >> 3;
         const int g = lane >> 2, t = lane & 3;
-        float* mine = red + warp * (MAX_ROWS * RED_LD);
+        float* mine = red + ks * (MAX_ROWS * RED_LD) + 64 * mh;
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
+        for (int mt = 0; mt < 4; ++mt) {
             const int r0 = 16 * mt + g;
             mine[(2 * t) * RED_LD + r0] = acc[mt][0];
             mine[(2 * t + 1) * RED_LD + r0] = acc[mt][1];
@@ -473,41 +522,52 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
             mine[(2 * t + 9) * RED_LD + r0 + 8] = acc[mt][7];
         }
     }
-    if (threadIdx.x < MAX_ROWS) {
-        float sc = p.out_scale;
-        if (p.sumsq) {
-            float ss = 0.f;
-            for (int i = 0; i < p.n_sumsq; ++i) ss += p.sumsq[i * MAX_ROWS + threadIdx.x];
-            sc *= 1.0f / sqrtf(ss / p.norm_k + p.eps);
-        }
-        tok_scale[threadIdx.x] = sc;
+    if (threadIdx.x < 256) {
+        // per-token output scale; 16 threads per token add the sum-of-squares partials in a fixed tree
+        const int tok = threadIdx.x >> 4, part = threadIdx.x & 15;
+        float ss = 0.f;
+        if (p.sumsq)
+            for (int i = part; i < p.n_sumsq; i += 16) ss += p.sumsq[i * MAX_ROWS + tok];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (part == 0) tok_scale[tok] = p.sumsq ? p.out_scale * (1.0f / sqrtf(ss / p.norm_k + p.eps)) : p.out_scale;
     }
     __syncthreads();
-    if (threadIdx.x < 256) {
-        const int row = threadIdx.x & (TILE_R - 1), th = threadIdx.x >> 7;
+    if (threadIdx.x < 512) {
+        const int row = threadIdx.x & (TILE_R - 1), tg = threadIdx.x >> 7;
         const uint32_t orow = (uint32_t)rt * TILE_R + row;
         if (orow < p.n_out) {
             float* dst = p.out + (uint64_t)sp * MAX_ROWS * p.ld_out + orow;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int tok = th * 8 + j;
+            for (int j = 0; j < 4; ++j) {
+                const int tok = tg * 4 + j;
                 float v = 0.f;
 #pragma unroll
-                for (int wv = 0; wv < CONSUMER_WARPS; ++wv) v += red[wv * (MAX_ROWS * RED_LD) + tok * RED_LD + row];
+                for (int wv = 0; wv < K_SLICES; ++wv) v += red[wv * (MAX_ROWS * RED_LD) + tok * RED_LD + row];
                 dst[(uint64_t)tok * p.ld_out] = v * tok_scale[tok];
             }
         }
     }
 }
 
+// Split count: enough CTAs to fill the 148 SMs (one CTA per SM) in whole waves, but no finer than
+// two column blocks per CTA where that is possible.
 int gemm_choose_splits(const QMatrix& m) {
-    // Aim at roughly two co-resident CTAs per SM; never split finer than one block per CTA.
-    constexpr int kTargetCtas = 2 * 148;
-    int s = kTargetCtas / (m.row_tiles > 0 ? m.row_tiles : 1);
-    if (s < 1) s = 1;
-    if (s > m.kblocks) s = m.kblocks;
-    if (s > 16) s = 16;
-    return s;
+    constexpr int kSms = 148;
+    const int tiles = m.row_tiles > 0 ? m.row_tiles : 1;
+    int best = 1;
+    double best_score = -1.0;
+    const int max_s = m.kblocks < 16 ? m.kblocks : 16;
+    for (int s = 1; s <= max_s; ++s) {
+        const int ctas = tiles * s;
+        const int waves = (ctas + kSms - 1) / kSms;
+        const double fill = (double)ctas / (double)(waves * kSms);       // fraction of SM-slots doing work
+        const double per_cta = (double)m.kblocks / s;                     // stages per CTA
+        const double overhead = per_cta / (per_cta + 1.5);                // fixed prologue/epilogue ~ 1.5 stages
+        const double score = fill * overhead - 0.01 * s;                  // mild preference for fewer partials
+        if (score > best_score) { best_score = score; best = s; }
+    }
+    return best;
 }
 
 template <int DT>
@@ -539,7 +599,16 @@ struct TimedLaunch { cudaEvent_t e0, e1; uint64_t bytes; };
 static bool g_timing = false;
 static std::vector<TimedLaunch> g_timed;
 
-static dfl_status launch_gemm_dispatch(cudaStream_t st, const QMatrix& m, const GemmParams& p, int grid, bool pdl);
+static dfl_status launch_gemm_dispatch(cudaStream_t st, const QMatrix& m, const GemmParams& p, int grid, bool pdl) {
+    switch (m.dtype) {
+        case DFL_Q4_K: return launch_t<DFL_Q4_K>(st, p, grid, pdl);
+        case DFL_Q5_K: return launch_t<DFL_Q5_K>(st, p, grid, pdl);
+        case DFL_Q6_K: return launch_t<DFL_Q6_K>(st, p, grid, pdl);
+        case DFL_Q8_0: return launch_t<DFL_Q8_0>(st, p, grid, pdl);
+        case DFL_BF16: return launch_t<DFL_BF16>(st, p, grid, pdl);
+        default: return fail(DFL_ERR_UNSUPPORTED, "gemm: weight dtype has no few-row kernel");
+    }
+}
 
 dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits,
                               const GemmEpilogue& ep, int* dev_err, bool pdl, uint32_t ld_out) {
@@ -571,25 +640,13 @@ dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* 
     return rc;
 }
 
-static dfl_status launch_gemm_dispatch(cudaStream_t st, const QMatrix& m, const GemmParams& p, int grid, bool pdl) {
-    switch (m.dtype) {
-        case DFL_Q4_K: return launch_t<DFL_Q4_K>(st, p, grid, pdl);
-        case DFL_Q5_K: return launch_t<DFL_Q5_K>(st, p, grid, pdl);
-        case DFL_Q6_K: return launch_t<DFL_Q6_K>(st, p, grid, pdl);
-        case DFL_Q8_0: return launch_t<DFL_Q8_0>(st, p, grid, pdl);
-        case DFL_BF16: return launch_t<DFL_BF16>(st, p, grid, pdl);
-        default: return fail(DFL_ERR_UNSUPPORTED, "gemm: weight dtype has no few-row kernel");
-    }
-}
-
-// ---- activation packing ------------------------------------------------------
+// ---- activation packing (standalone; the model path packs inside its glue kernels) ------------
 // One CTA per 256-column block; thread = (token = tid/16, 16 consecutive columns).
 template <bool BF3>
 __global__ void prep_acts_kernel(const float* __restrict__ x, int ld, int n_rows, float pre_scale, uint8_t* __restrict__ acts,
                                  int* err) {
     constexpr int CH = BF3 ? ACTB3_CHUNK : ACT16_CHUNK;
     const int kb = blockIdx.x, tok = threadIdx.x >> 4, seg = threadIdx.x & 15;
-    const int w = seg >> 1, s = seg & 1;
     uint8_t* chunk = acts + (uint64_t)kb * CH;
     float v[16];
     if (tok < n_rows) {
@@ -603,44 +660,32 @@ __global__ void prep_acts_kernel(const float* __restrict__ x, int ld, int n_rows
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = 0.f;
     }
-    if (!BF3) {
-        float sum = 0.f;
-        bool over = false;
+    float sum = 0.f;
+    bool over = false;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            __half hi[4], lo[4];
+    for (int q4 = 0; q4 < 4; ++q4) {
+        const int k = seg * 16 + 4 * q4;
+        const int pos = act_pos(k);
+        if (!BF3) {
+            uint16_t hi[4], lo[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float f = v[4 * t + e];
+                const float f = v[4 * q4 + e];
                 over |= (fabsf(f) >= 65504.f) && (fabsf(f) < INFINITY);
-                hi[e] = __float2half_rn(f);
-                lo[e] = __float2half_rn(f - __half2float(hi[e]));
+                const __half h = __float2half_rn(f);
+                hi[e] = __half_as_ushort(h);
+                lo[e] = __half_as_ushort(__float2half_rn(f - __half2float(h)));
                 sum += f;
             }
-            const int pos = 32 * w + 8 * t + 4 * s;
-            uint2 ph, pl;
-            ph.x = (uint32_t)__half_as_ushort(hi[0]) | ((uint32_t)__half_as_ushort(hi[1]) << 16);
-            ph.y = (uint32_t)__half_as_ushort(hi[2]) | ((uint32_t)__half_as_ushort(hi[3]) << 16);
-            pl.x = (uint32_t)__half_as_ushort(lo[0]) | ((uint32_t)__half_as_ushort(lo[1]) << 16);
-            pl.y = (uint32_t)__half_as_ushort(lo[2]) | ((uint32_t)__half_as_ushort(lo[3]) << 16);
-            *reinterpret_cast<uint2*>(chunk + (tok * ACT_ROW_HALFS + pos) * 2) = ph;
-            *reinterpret_cast<uint2*>(chunk + ACT_PLANE + (tok * ACT_ROW_HALFS + pos) * 2) = pl;
-        }
-        // sum over the 32-column sub-block = this thread (16 columns) + its neighbour
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        if (s == 0) reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[tok * 8 + w] = sum;
-        if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
-        if (seg == 0) {  // zero the 8 padding halfs of both planes
-            *reinterpret_cast<uint4*>(chunk + (tok * ACT_ROW_HALFS + 256) * 2) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(chunk + ACT_PLANE + (tok * ACT_ROW_HALFS + 256) * 2) = make_uint4(0, 0, 0, 0);
-        }
-    } else {
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
+            *reinterpret_cast<uint2*>(chunk + (tok * ACT_ROW_HALFS + pos) * 2) =
+                make_uint2((uint32_t)hi[0] | ((uint32_t)hi[1] << 16), (uint32_t)hi[2] | ((uint32_t)hi[3] << 16));
+            *reinterpret_cast<uint2*>(chunk + ACT_PLANE + (tok * ACT_ROW_HALFS + pos) * 2) =
+                make_uint2((uint32_t)lo[0] | ((uint32_t)lo[1] << 16), (uint32_t)lo[2] | ((uint32_t)lo[3] << 16));
+        } else {
             uint16_t b[3][4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float f = v[4 * t + e];
+                float f = v[4 * q4 + e];
 #pragma unroll
                 for (int pl = 0; pl < 3; ++pl) {
                     const __nv_bfloat16 h = __float2bfloat16_rn(f);
@@ -648,19 +693,17 @@ __global__ void prep_acts_kernel(const float* __restrict__ x, int ld, int n_rows
                     f -= __bfloat162float(h);
                 }
             }
-            const int pos = 32 * w + 8 * t + 4 * s;
-#pragma unroll
-            for (int pl = 0; pl < 3; ++pl) {
-                uint2 pk;
-                pk.x = (uint32_t)b[pl][0] | ((uint32_t)b[pl][1] << 16);
-                pk.y = (uint32_t)b[pl][2] | ((uint32_t)b[pl][3] << 16);
-                *reinterpret_cast<uint2*>(chunk + pl * ACT_PLANE + (tok * ACT_ROW_HALFS + pos) * 2) = pk;
-            }
-        }
-        if (seg == 0)
 #pragma unroll
             for (int pl = 0; pl < 3; ++pl)
-                *reinterpret_cast<uint4*>(chunk + pl * ACT_PLANE + (tok * ACT_ROW_HALFS + 256) * 2) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint2*>(chunk + pl * ACT_PLANE + (tok * ACT_ROW_HALFS + pos) * 2) =
+                    make_uint2((uint32_t)b[pl][0] | ((uint32_t)b[pl][1] << 16), (uint32_t)b[pl][2] | ((uint32_t)b[pl][3] << 16));
+        }
+    }
+    if (!BF3) {
+        // sum over the 32-column sub-block = this thread (16 columns) + its neighbour
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if ((seg & 1) == 0) reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[tok * 8 + (seg >> 1)] = sum;
+        if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
     }
 }
 
@@ -712,8 +755,7 @@ __device__ __forceinline__ void top2_merge(Top2& a, const Top2& b) {
         a.k2 = second;
     }
 }
-__device__ __forceinline__ Top2 top2_block_reduce(Top2 a) {
-    __shared__ Top2 sh[32];
+__device__ __forceinline__ Top2 top2_warp_reduce(Top2 a) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         Top2 b;
@@ -722,19 +764,17 @@ __device__ __forceinline__ Top2 top2_block_reduce(Top2 a) {
         b.k2 = __shfl_xor_sync(0xffffffffu, a.k2, o);
         top2_merge(a, b);
     }
+    return a;
+}
+__device__ __forceinline__ Top2 top2_block_reduce(Top2 a) {
+    __shared__ Top2 sh[32];
+    a = top2_warp_reduce(a);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     if (lane == 0) sh[warp] = a;
     __syncthreads();
     if (warp == 0) {
         a = lane < nw ? sh[lane] : Top2{INT32_MIN, INT32_MAX, INT32_MIN, 0};
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            Top2 b;
-            b.k1 = __shfl_xor_sync(0xffffffffu, a.k1, o);
-            b.i1 = __shfl_xor_sync(0xffffffffu, a.i1, o);
-            b.k2 = __shfl_xor_sync(0xffffffffu, a.k2, o);
-            top2_merge(a, b);
-        }
+        a = top2_warp_reduce(a);
     }
     return a;
 }
