@@ -105,24 +105,42 @@ __global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float
     const uint32_t n_pos = start + (uint32_t)n_rows;
     const uint32_t p0 = (uint32_t)chunk * ATTN_CHUNK;
     const int n_here = (int)min((uint32_t)ATTN_CHUNK, n_pos - p0);
-    for (int idx = threadIdx.x; idx < ATTN_CHUNK * HD; idx += blockDim.x) {
-        const int kp = idx / HD, d = idx % HD;
-        float kv = 0.f, vv = 0.f;
+    // 16-byte vector loads, all issued before the first use (one latency round per CTA)
+    constexpr int EPV = 16 / (int)sizeof(KV);          // elements per vector
+    constexpr int VPR = HD / EPV;                      // vectors per cache row
+    constexpr int ITERS = ATTN_CHUNK * VPR / 256;
+    uint4 kreg[ITERS], vreg[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int idx = threadIdx.x + it * 256, kp = idx / VPR, vv = idx % VPR;
+        kreg[it] = make_uint4(0, 0, 0, 0);
+        vreg[it] = make_uint4(0, 0, 0, 0);
         if (kp < n_here) {
-            const uint64_t o = ((uint64_t)(p0 + kp) * g.n_kv + kvh) * HD + d;
-            kv = (float)k_cache[o];
-            vv = (float)v_cache[o];
+            const uint64_t o = ((uint64_t)(p0 + kp) * g.n_kv + kvh) * HD + vv * EPV;
+            kreg[it] = *reinterpret_cast<const uint4*>(k_cache + o);
+            vreg[it] = *reinterpret_cast<const uint4*>(v_cache + o);
         }
-        ks[kp * LD + d] = kv;
-        vs[kp * LD + d] = vv;
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int idx = threadIdx.x + it * 256, kp = idx / VPR, vv = idx % VPR;
+        const KV* ke = reinterpret_cast<const KV*>(&kreg[it]);
+        const KV* ve = reinterpret_cast<const KV*>(&vreg[it]);
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) {
+            ks[kp * LD + vv * EPV + e] = (float)ke[e];
+            vs[kp * LD + vv * EPV + e] = (float)ve[e];
+        }
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float scale = 1.0f / sqrtf((float)HD);
-    const int n_queries = n_rows * group;
+    // blockIdx.z selects a group of ATTN_ROW_GROUP query rows, so that short contexts still fill the GPU
+    const int q_lo = blockIdx.z * ATTN_ROW_GROUP * group;
+    const int q_hi = min(n_rows, ((int)blockIdx.z + 1) * ATTN_ROW_GROUP) * group;
     float* myq = qs + warp * HD;
     float* myp = ps + warp * ATTN_CHUNK;
-    for (int qi = warp; qi < n_queries; qi += 8) {
+    for (int qi = q_lo + warp; qi < q_hi; qi += 8) {
         const int row = qi / group, qh = kvh * group + qi % group;
         const float* qsrc = q_rot + ((uint64_t)row * g.n_q + qh) * HD;
         for (int d = lane; d < HD; d += 32) myq[d] = qsrc[d];
@@ -261,7 +279,7 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
         DFL_CUDA(cudaFuncSetAttribute(attn_chunk_kernel<KV, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = true;
     }
-    attn_chunk_kernel<KV, HD><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(
+    attn_chunk_kernel<KV, HD><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv, (unsigned)((n_rows + ATTN_ROW_GROUP - 1) / ATTN_ROW_GROUP)), 256, smem, st>>>(
         g, q_rot, reinterpret_cast<const KV*>(k_cache), reinterpret_cast<const KV*>(v_cache), start, n_rows, partials);
     count_launch();
     DFL_CUDA(cudaGetLastError());

@@ -361,7 +361,7 @@ dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_
     }
     ds->x = (float*)alloc(MAX_ROWS * H * 4);
     ds->part = (float*)alloc(part * 4);
-    ds->sumsq = (float*)alloc((H / 256) * MAX_ROWS * 4);
+    ds->sumsq = (float*)alloc((H / GLUE_COLS) * MAX_ROWS * 4);
     ds->q_rot = (float*)alloc(MAX_ROWS * q_dim * 4);
     ds->k_noise = (float*)alloc(MAX_ROWS * kv_dim * 4);
     ds->v_noise = (float*)alloc(MAX_ROWS * kv_dim * 4);
@@ -441,7 +441,7 @@ dfl_status dsession_project_pending(dfl_dsession* ds) {
     cudaStream_t st = ds->st;
     GemmEpilogue ep_norm;
     ep_norm.sumsq = ds->sumsq;
-    ep_norm.n_sumsq = (int)(H / 256);
+    ep_norm.n_sumsq = (int)(H / GLUE_COLS);
     ep_norm.norm_k = (float)H;
     ep_norm.eps = c.rms_norm_eps;
     const AttnGeom gkv = d->geom(0);
@@ -508,7 +508,7 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start) {
     DFL_CHECK(dsession_project_pending(ds));
     GemmEpilogue ep_norm;
     ep_norm.sumsq = ds->sumsq;
-    ep_norm.n_sumsq = (int)(H / 256);
+    ep_norm.n_sumsq = (int)(H / GLUE_COLS);
     ep_norm.norm_k = (float)H;
     ep_norm.eps = c.rms_norm_eps;
     ds->pinned_i[0] = carry;

@@ -14,6 +14,7 @@ namespace dfl {
 
 // ---- front: conv1d(K=4) + SiLU over the block, q/k L2 norm -------------------------------
 // grid = conv_dim / 128 (one q, k or v head per CTA), block 128 (one channel per thread).
+// All global loads are issued before the token recurrence starts.
 __global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* __restrict__ part, int splits, int ld_part, int n_rows,
                                                         const float* __restrict__ conv_w, float* __restrict__ conv_state,
                                                         float* __restrict__ qkv_raw, float* __restrict__ q_n, float* __restrict__ k_n,
@@ -21,39 +22,62 @@ __global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* 
     const int conv_dim = g.conv_dim();
     const int c = blockIdx.x * 128 + threadIdx.x;
     const int head = blockIdx.x;  // heads of 128 channels: [0, n_k) q, [n_k, 2 n_k) k, rest v
-    float w0 = conv_w[c * 4 + 0], w1 = conv_w[c * 4 + 1], w2 = conv_w[c * 4 + 2], w3 = conv_w[c * 4 + 3];
+    const float4 w = *reinterpret_cast<const float4*>(conv_w + c * 4);
     float h0 = conv_state[0 * conv_dim + c], h1 = conv_state[1 * conv_dim + c], h2 = conv_state[2 * conv_dim + c];
-    __shared__ float red[4];
-    const bool is_v = head >= 2 * g.n_k;
-    float* dst = is_v ? v_out + (uint64_t)(head - 2 * g.n_k) * 128 + threadIdx.x
-                      : (head < g.n_k ? q_n + (uint64_t)head * 128 + threadIdx.x : k_n + (uint64_t)(head - g.n_k) * 128 + threadIdx.x);
-    const int dst_ld = is_v ? g.n_v * 128 : g.n_k * 128;
-    for (int i = 0; i < n_rows; ++i) {
-        float x = 0.f;
-        for (int s = 0; s < splits; ++s) x += part[((uint64_t)s * MAX_ROWS + i) * ld_part + c];
-        qkv_raw[(uint64_t)i * conv_dim + c] = x;
-        // s = sum_k w[k] * window[k], k ascending (forward.rs:1000-1010)
-        float sacc = 0.f;
-        sacc += w0 * h0;
-        sacc += w1 * h1;
-        sacc += w2 * h2;
-        sacc += w3 * x;
-        float y = silu_f(sacc);
-        h0 = h1; h1 = h2; h2 = x;
-        if (!is_v) {
-            // y / max(||y||, eps) over the head's 128 channels (forward.rs:1269-1275)
-            float sq = warp_sum(y * y);
-            __syncthreads();
-            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
-            __syncthreads();
-            const float tot = red[0] + red[1] + red[2] + red[3];
-            y *= 1.0f / fmaxf(sqrtf(tot), 1e-6f);
+    float x[MAX_ROWS];
+#pragma unroll
+    for (int i = 0; i < MAX_ROWS; ++i) x[i] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* base = part + (uint64_t)s * MAX_ROWS * ld_part + c;
+#pragma unroll
+        for (int i = 0; i < MAX_ROWS; ++i)
+            if (i < n_rows) x[i] += base[(uint64_t)i * ld_part];
+    }
+    float y[MAX_ROWS];
+#pragma unroll
+    for (int i = 0; i < MAX_ROWS; ++i) {
+        y[i] = 0.f;
+        if (i < n_rows) {
+            qkv_raw[(uint64_t)i * conv_dim + c] = x[i];
+            // s = sum_k w[k] * window[k], k ascending (forward.rs:1000-1010)
+            float sacc = 0.f;
+            sacc += w.x * h0;
+            sacc += w.y * h1;
+            sacc += w.z * h2;
+            sacc += w.w * x[i];
+            y[i] = silu_f(sacc);
+            h0 = h1; h1 = h2; h2 = x[i];
         }
-        dst[(uint64_t)i * dst_ld] = y;
     }
     conv_state[0 * conv_dim + c] = h0;
     conv_state[1 * conv_dim + c] = h1;
     conv_state[2 * conv_dim + c] = h2;
+    const bool is_v = head >= 2 * g.n_k;
+    if (!is_v) {
+        // y / max(||y||, eps) over the head's 128 channels, all tokens at once (forward.rs:1269-1275)
+        __shared__ float red[4][MAX_ROWS];
+        __shared__ float inv[MAX_ROWS];
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+        for (int i = 0; i < MAX_ROWS; ++i) {
+            const float sq = warp_sum(y[i] * y[i]);
+            if (lane == 0) red[warp][i] = sq;
+        }
+        __syncthreads();
+        if (threadIdx.x < MAX_ROWS) {
+            const float tot = red[0][threadIdx.x] + red[1][threadIdx.x] + red[2][threadIdx.x] + red[3][threadIdx.x];
+            inv[threadIdx.x] = 1.0f / fmaxf(sqrtf(tot), 1e-6f);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < MAX_ROWS; ++i) y[i] *= inv[i];
+    }
+    float* dst = is_v ? v_out + (uint64_t)(head - 2 * g.n_k) * 128 + threadIdx.x
+                      : (head < g.n_k ? q_n + (uint64_t)head * 128 + threadIdx.x : k_n + (uint64_t)(head - g.n_k) * 128 + threadIdx.x);
+    const int dst_ld = is_v ? g.n_v * 128 : g.n_k * 128;
+#pragma unroll
+    for (int i = 0; i < MAX_ROWS; ++i)
+        if (i < n_rows) dst[(uint64_t)i * dst_ld] = y[i];
 }
 
 dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
@@ -87,33 +111,48 @@ dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const floa
 
 // ---- scan --------------------------------------------------------------------------------
 // grid (n_v, 4), block 256: warp owns 4 state rows (dv), lane owns columns dk = lane + 32 j.
-// Per token (forward.rs:1054-1091): sk = S k (state before decay), coeff = beta (v - g sk),
-// S = g S + coeff k, o = S q.
+// The block's q, k, v rows and gate scalars are staged in shared memory first, so that the
+// sequential part touches no global memory.  Per token (forward.rs:1054-1091): sk = S k (state
+// before decay), coeff = beta (v - g sk), S = g S + coeff k, o = S q.
 __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* __restrict__ state_in, float* __restrict__ state_out,
                                                        const float* __restrict__ q_n, const float* __restrict__ k_n,
                                                        const float* __restrict__ v, const float* __restrict__ ab,
                                                        const float* __restrict__ dt_bias, const float* __restrict__ a_log, int n_rows,
                                                        float* __restrict__ o) {
+    __shared__ float qs[MAX_ROWS][128], ks[MAX_ROWS][128], vs[MAX_ROWS][32], gs[MAX_ROWS], bs[MAX_ROWS], os[MAX_ROWS][32];
     const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hk = h % g.n_k;
-    const int dv0 = blockIdx.y * 32 + warp * 4;
+    const int dv_cta = blockIdx.y * 32, dv0 = dv_cta + warp * 4;
+    for (int idx = threadIdx.x; idx < n_rows * 128; idx += 256) {
+        const int i = idx >> 7, d = idx & 127;
+        qs[i][d] = q_n[((uint64_t)i * g.n_k + hk) * 128 + d];
+        ks[i][d] = k_n[((uint64_t)i * g.n_k + hk) * 128 + d];
+    }
+    for (int idx = threadIdx.x; idx < n_rows * 32; idx += 256) {
+        const int i = idx >> 5, d = idx & 31;
+        vs[i][d] = v[((uint64_t)i * g.n_v + h) * 128 + dv_cta + d];
+    }
+    if (threadIdx.x < n_rows) {
+        // gate inputs: ab[i][0..n_v) = alpha projection, ab[i][n_v..2 n_v) = beta projection
+        const int i = threadIdx.x;
+        const float alpha = ab[(uint64_t)i * (2 * g.n_v) + h] + dt_bias[h];
+        gs[i] = expf(softplus_f(alpha) * a_log[h]);
+        bs[i] = sigmoid_f(ab[(uint64_t)i * (2 * g.n_v) + g.n_v + h]);
+    }
     float S[4][4];
     const float* sin = state_in + ((uint64_t)h * 128 + dv0) * 128;
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
         for (int j = 0; j < 4; ++j) S[r][j] = sin[r * 128 + lane + 32 * j];
-    const float dtb = dt_bias[h], al = a_log[h];
+    __syncthreads();
     for (int i = 0; i < n_rows; ++i) {
-        // gate inputs: ab[i][0..n_v) = alpha projection, ab[i][n_v..2 n_v) = beta projection
-        const float alpha = ab[(uint64_t)i * (2 * g.n_v) + h] + dtb;
-        const float gexp = expf(softplus_f(alpha) * al);
-        const float beta = sigmoid_f(ab[(uint64_t)i * (2 * g.n_v) + g.n_v + h]);
+        const float gexp = gs[i], beta = bs[i];
         float kk[4], qq[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            kk[j] = k_n[((uint64_t)i * g.n_k + hk) * 128 + lane + 32 * j];
-            qq[j] = q_n[((uint64_t)i * g.n_k + hk) * 128 + lane + 32 * j];
+            kk[j] = ks[i][lane + 32 * j];
+            qq[j] = qs[i][lane + 32 * j];
         }
         float sk[4];
 #pragma unroll
@@ -121,28 +160,42 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* _
             float p = 0.f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) p = fmaf(S[r][j], kk[j], p);
-            sk[r] = warp_sum(p);
+            sk[r] = p;
         }
+#pragma unroll
+        for (int of = 16; of > 0; of >>= 1)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) sk[r] += __shfl_xor_sync(0xffffffffu, sk[r], of);
         float oo[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            const float vv = v[((uint64_t)i * g.n_v + h) * 128 + dv0 + r];
-            const float coeff = beta * (vv - gexp * sk[r]);
+            const float coeff = beta * (vs[i][warp * 4 + r] - gexp * sk[r]);
             float p = 0.f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 S[r][j] = __fadd_rn(__fmul_rn(gexp, S[r][j]), __fmul_rn(coeff, kk[j]));
                 p = fmaf(S[r][j], qq[j], p);
             }
-            oo[r] = warp_sum(p);
+            oo[r] = p;
         }
-        if (o && lane < 4) o[((uint64_t)i * g.n_v + h) * 128 + dv0 + lane] = lane == 0 ? oo[0] : lane == 1 ? oo[1] : lane == 2 ? oo[2] : oo[3];
+#pragma unroll
+        for (int of = 16; of > 0; of >>= 1)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], of);
+        if (lane < 4) os[i][warp * 4 + lane] = lane == 0 ? oo[0] : lane == 1 ? oo[1] : lane == 2 ? oo[2] : oo[3];
     }
     float* sout = state_out + ((uint64_t)h * 128 + dv0) * 128;
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
         for (int j = 0; j < 4; ++j) sout[r * 128 + lane + 32 * j] = S[r][j];
+    if (o) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n_rows * 32; idx += 256) {
+            const int i = idx >> 5, d = idx & 31;
+            o[((uint64_t)i * g.n_v + h) * 128 + dv_cta + d] = os[i][d];
+        }
+    }
 }
 
 dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state_in, float* state_out, const float* q_n,
@@ -165,6 +218,7 @@ __global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* __
     if (tok < n_rows) {
         const float4 ov = *reinterpret_cast<const float4*>(o + (uint64_t)tok * (g.n_v * 128) + col0);
         float z[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
         for (int s = 0; s < splits; ++s) {
             const float4 zz = *reinterpret_cast<const float4*>(part_z + ((uint64_t)s * MAX_ROWS + tok) * ld_part + col0);
             z[0] += zz.x; z[1] += zz.y; z[2] += zz.z; z[3] += zz.w;

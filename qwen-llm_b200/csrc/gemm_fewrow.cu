@@ -29,7 +29,7 @@ namespace dfl {
 constexpr int K_SLICES = 8;                                         // warps along the 256 columns of a stage
 constexpr int M_HALVES = 2;                                         // warps along the 128 rows
 constexpr int CONSUMER_WARPS = K_SLICES * M_HALVES;                 // 16
-constexpr int GEMM_THREADS = (CONSUMER_WARPS + 1) * 32;             // + producer warp
+constexpr int GEMM_THREADS = CONSUMER_WARPS * 32;                   // thread 0 also issues the bulk copies
 constexpr int RED_LD = TILE_R + 4;                                  // padded row length of the reduce buffer
 constexpr int RED_BYTES = K_SLICES * MAX_ROWS * RED_LD * 4;         // 67584
 constexpr int WARP_SCRATCH = (TILE_R / M_HALVES) * 8;               // float2 per row of the warp's 64 rows
@@ -454,43 +454,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
-    if (warp == CONSUMER_WARPS) {
-        // ---------------- producer ----------------
-        if (lane == 0) {
-            const uint8_t* wsrc = p.w + ((uint64_t)rt * p.kblocks + kb0) * F::STAGE;
-            const uint8_t* asrc = p.acts + (uint64_t)kb0 * F::ACT;
-            const int pre = n_it < STAGES ? n_it : STAGES;
-            // weights of the first stages do not depend on the previous kernel
-            for (int i = 0; i < pre; ++i) {
-                mbar_arrive_expect_tx(&full[i], F::STAGE + F::ACT);
-                bulk_g2s(ring + i * SLOT, wsrc + (uint64_t)i * F::STAGE, F::STAGE, &full[i]);
-            }
-            pdl_wait();
-            for (int i = 0; i < pre; ++i) bulk_g2s(ring + i * SLOT + F::STAGE, asrc + (uint64_t)i * F::ACT, F::ACT, &full[i]);
-            bool ok = true;
-            int issued = pre;
-            for (int i = STAGES; i < n_it && ok; ++i) {
-                const int s = i % STAGES;
-                ok = mbar_wait_bounded(&empty[s], ((i / STAGES) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&full[s], F::STAGE + F::ACT);
-                bulk_g2s(ring + s * SLOT, wsrc + (uint64_t)i * F::STAGE, F::STAGE, &full[s]);
-                bulk_g2s(ring + s * SLOT + F::STAGE, asrc + (uint64_t)i * F::ACT, F::ACT, &full[s]);
-                issued = i + 1;
-            }
-            if (!ok) {
-                // Give the copies still in flight a bounded chance to land before the CTA exits.
-                atomicExch(&abort_flag, 1);
-                for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i)
-                    mbar_wait_bounded(&full[i % STAGES], (i / STAGES) & 1, p.err, DEV_ERR_WAIT_DRAIN);
-            }
+    // Thread 0 doubles as the producer: it arms the first STAGES stages up front and, once per
+    // iteration, refills the slot every warp released one iteration earlier.
+    const bool producer = threadIdx.x == 0;
+    const uint8_t* wsrc = p.w + ((uint64_t)rt * p.kblocks + kb0) * F::STAGE;
+    const uint8_t* asrc = p.acts + (uint64_t)kb0 * F::ACT;
+    if (producer) {
+        const int pre = n_it < STAGES ? n_it : STAGES;
+        // weights of the first stages do not depend on the previous kernel
+        for (int i = 0; i < pre; ++i) {
+            mbar_arrive_expect_tx(&full[i], F::STAGE + F::ACT);
+            bulk_g2s(ring + i * SLOT, wsrc + (uint64_t)i * F::STAGE, F::STAGE, &full[i]);
         }
-    } else {
-        // ---------------- consumers ----------------
+        pdl_wait();
+        for (int i = 0; i < pre; ++i) bulk_g2s(ring + i * SLOT + F::STAGE, asrc + (uint64_t)i * F::ACT, F::ACT, &full[i]);
+    }
+    {
         const int ks = warp & (K_SLICES - 1), mh = warp >> 3;
         float2* sc = scratch + warp * (TILE_R / M_HALVES);
         bool ok = true;
         for (int i = 0; i < n_it; ++i) {
+            if (producer && i >= 1 && i - 1 + STAGES < n_it) {
+                const int j = i - 1, sj = j % STAGES;  // slot consumed in the previous iteration
+                ok = mbar_wait_bounded(&empty[sj], (j / STAGES) & 1, p.err, DEV_ERR_WAIT_EMPTY);
+                if (ok) {
+                    const int nx = j + STAGES;
+                    mbar_arrive_expect_tx(&full[sj], F::STAGE + F::ACT);
+                    bulk_g2s(ring + sj * SLOT, wsrc + (uint64_t)nx * F::STAGE, F::STAGE, &full[sj]);
+                    bulk_g2s(ring + sj * SLOT + F::STAGE, asrc + (uint64_t)nx * F::ACT, F::ACT, &full[sj]);
+                }
+            }
+            if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the producer's verdict, warp-uniform
+            if (!ok) break;
             const int s = i % STAGES;
             ok = mbar_wait_bounded(&full[s], (i / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
             if (!ok) break;
@@ -499,13 +494,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
         }
         if (!ok) atomicExch(&abort_flag, 1);
     }
-    if (warp == CONSUMER_WARPS) pdl_wait();  // every thread of the producer warp has passed the dependency wait
     __syncthreads();
-    if (abort_flag) return;  // error word already set; outputs are left untouched
+    if (abort_flag) {
+        // Error word already set.  Every copy this CTA armed either completed (its full barrier was
+        // waited for) or is given a bounded chance to land before the shared memory is released.
+        if (producer)
+            for (int s = 0; s < STAGES; ++s) {
+                uint32_t spins = 0;
+                while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && ++spins < (1u << 16)) __nanosleep(100);
+            }
+        return;
+    }
 
     // ---------------- epilogue: fixed-order sum over the eight column slices ----------------
     float* red = reinterpret_cast<float*>(ring);
-    if (warp < CONSUMER_WARPS) {
+    {
         const int ks = warp & (K_SLICES - 1), mh = warp >> 3;
         const int g = lane >> 2, t = lane & 3;
         float* mine = red + ks * (MAX_ROWS * RED_LD) + 64 * mh;
@@ -533,7 +536,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
         if (part == 0) tok_scale[tok] = p.sumsq ? p.out_scale * (1.0f / sqrtf(ss / p.norm_k + p.eps)) : p.out_scale;
     }
     __syncthreads();
-    if (threadIdx.x < 512) {
+    {
         const int row = threadIdx.x & (TILE_R - 1), tg = threadIdx.x >> 7;
         const uint32_t orow = (uint32_t)rt * TILE_R + row;
         if (orow < p.n_out) {

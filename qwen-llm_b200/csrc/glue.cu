@@ -4,117 +4,79 @@
 // kernel_rms_norm_batched_f32 launches (kernels/elementwise.metal:89,193; rms_norm.metal:48).
 //
 // RMSNorm is split so that no row-wide reduction sits on the critical path: this kernel
-// multiplies by the norm weight and emits per-256-column partial sums of squares; the
+// multiplies by the norm weight and emits per-64-column partial sums of squares; the
 // consuming GEMM multiplies its result by 1/sqrt(mean(x^2) + eps) per token.
 #include "ops.cuh"
 
 namespace dfl {
 
-// grid = k / 256, block 256: thread = (token = tid / 16, 16 consecutive columns).
+// grid = k / 64, block 256: thread = (token = tid / 16, four consecutive columns).  One float4 per
+// split per thread keeps every global load of the kernel independent (one latency round).
 __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
-    const int kb = blockIdx.x, tok = threadIdx.x >> 4, seg = threadIdx.x & 15;
-    const int col0 = kb * TILE_K + seg * 16;
+    const int cb = blockIdx.x, tok = threadIdx.x >> 4, quad = threadIdx.x & 15;
+    const int col0 = cb * GLUE_COLS + quad * 4;
     const bool live = tok < p.n_rows;
-    float v[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (live) {
         if (p.mode == GLUE_SWIGLU) {
-            float g[16], u[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) { g[j] = 0.f; u[j] = 0.f; }
+            float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
+            const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
+#pragma unroll 4
             for (int s = 0; s < p.splits; ++s) {
-                const float* base = p.part + ((uint64_t)s * MAX_ROWS + tok) * p.ld_part + col0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 a = reinterpret_cast<const float4*>(base)[j];
-                    const float4 b = reinterpret_cast<const float4*>(base + p.swiglu_f)[j];
-                    g[4 * j] += a.x; g[4 * j + 1] += a.y; g[4 * j + 2] += a.z; g[4 * j + 3] += a.w;
-                    u[4 * j] += b.x; u[4 * j + 1] += b.y; u[4 * j + 2] += b.z; u[4 * j + 3] += b.w;
-                }
+                const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
+                const float4 b = *reinterpret_cast<const float4*>(base + s * stride + p.swiglu_f);
+                g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+                u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_f(g[j]) * u[j];
+            for (int j = 0; j < 4; ++j) v[j] = silu_f(g[j]) * u[j];
         } else {
-            if (p.x) {
-                const float4* src = reinterpret_cast<const float4*>(p.x + (uint64_t)tok * p.ld_x + col0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 a = src[j];
-                    v[4 * j] = a.x; v[4 * j + 1] = a.y; v[4 * j + 2] = a.z; v[4 * j + 3] = a.w;
-                }
-            }
+            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.x) xv = *reinterpret_cast<const float4*>(p.x + (uint64_t)tok * p.ld_x + col0);
             if (p.mode == GLUE_RESID && p.part) {
                 // sum the split-K partials first (fixed order), then add to the residual
-                float acc[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
+                const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
+#pragma unroll 4
                 for (int s = 0; s < p.splits; ++s) {
-                    const float4* src = reinterpret_cast<const float4*>(p.part + ((uint64_t)s * MAX_ROWS + tok) * p.ld_part + col0);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float4 a = src[j];
-                        acc[4 * j] += a.x; acc[4 * j + 1] += a.y; acc[4 * j + 2] += a.z; acc[4 * j + 3] += a.w;
-                    }
+                    const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
+                    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
                 }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[j] += acc[j];
-                if (p.x) {
-                    float4* dst = reinterpret_cast<float4*>(p.x + (uint64_t)tok * p.ld_x + col0);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                }
+                v[0] = xv.x + acc[0]; v[1] = xv.y + acc[1]; v[2] = xv.z + acc[2]; v[3] = xv.w + acc[3];
+                if (p.x) *reinterpret_cast<float4*>(p.x + (uint64_t)tok * p.ld_x + col0) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+                v[0] = xv.x; v[1] = xv.y; v[2] = xv.z; v[3] = xv.w;
             }
         }
-        if (p.capture) {
-            float4* dst = reinterpret_cast<float4*>(p.capture + (uint64_t)tok * p.ld_capture + col0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-        }
+        if (p.capture)
+            *reinterpret_cast<float4*>(p.capture + (uint64_t)tok * p.ld_capture + col0) = make_float4(v[0], v[1], v[2], v[3]);
     }
     if (p.sumsq) {
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) ss += v[j] * v[j];
+        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (seg == 0) p.sumsq[kb * MAX_ROWS + tok] = ss;
+        if (quad == 0) p.sumsq[cb * MAX_ROWS + tok] = ss;
     }
     if (p.mul_w) {
-        const float4* w = reinterpret_cast<const float4*>(p.mul_w + col0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float4 a = w[j];
-            v[4 * j] *= a.x; v[4 * j + 1] *= a.y; v[4 * j + 2] *= a.z; v[4 * j + 3] *= a.w;
-        }
+        const float4 w = *reinterpret_cast<const float4*>(p.mul_w + col0);
+        v[0] *= w.x; v[1] *= w.y; v[2] *= w.z; v[3] *= w.w;
     }
     if (p.pre_scale != 1.f) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] *= p.pre_scale;
+        for (int j = 0; j < 4; ++j) v[j] *= p.pre_scale;
     }
-    if (p.xn && live) {
-        float4* dst = reinterpret_cast<float4*>(p.xn + (uint64_t)tok * p.ld_xn + col0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-    }
+    if (p.xn && live) *reinterpret_cast<float4*>(p.xn + (uint64_t)tok * p.ld_xn + col0) = make_float4(v[0], v[1], v[2], v[3]);
     if (p.acts) {
-        uint8_t* chunk = p.acts + (uint64_t)kb * (p.bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
+        uint8_t* chunk = p.acts + (uint64_t)(col0 >> 8) * (p.bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
         bool over = false;
-        float sum = 0.f;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float quad[4] = {v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]};
-            pack_quad(chunk, p.bf3 != 0, tok, seg * 16 + 4 * q, quad, over);
-            sum += quad[0] + quad[1] + quad[2] + quad[3];
-        }
+        pack_quad(chunk, p.bf3 != 0, tok, col0 & 255, v, over);
         if (!p.bf3) {
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // 32-column sub-block = two neighbouring threads
-            if ((seg & 1) == 0) reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[tok * 8 + (seg >> 1)] = sum;
-        }
-        if (seg == 0) {
-            const int planes = p.bf3 ? 3 : 2;
-            for (int pl = 0; pl < planes; ++pl)
-                *reinterpret_cast<uint4*>(chunk + pl * ACT_PLANE + (tok * ACT_ROW_HALFS + 256) * 2) = make_uint4(0, 0, 0, 0);
+            float sum = v[0] + v[1] + v[2] + v[3];  // 32-column sub-block = eight neighbouring threads
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if ((quad & 7) == 0) reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[tok * 8 + ((col0 & 255) >> 5)] = sum;
         }
         if (over) atomicCAS(p.err, 0, DEV_ERR_OVERFLOW);
     }
@@ -122,7 +84,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
 
 dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k) {
     if (k == 0 || k % TILE_K) return fail(DFL_ERR_BAD_SHAPE, "glue: column count must be a positive multiple of 256");
-    glue_kernel<<<(unsigned)(k / TILE_K), 256, 0, st>>>(p);
+    glue_kernel<<<(unsigned)(k / GLUE_COLS), 256, 0, st>>>(p);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -149,7 +111,9 @@ dfl_status launch_embed_rows(cudaStream_t st, int dtype, const uint8_t* ggml, ui
 }
 
 // ---- small f32 matrices --------------------------------------------------------------
-__global__ void __launch_bounds__(128) small_matmul_kernel(const float* __restrict__ w, const float* __restrict__ xn, int ld_xn,
+// One CTA of 512 threads per output column; each thread takes float4 slices of the row so that all
+// of its loads are independent, then a fixed-order block reduction per token.
+__global__ void __launch_bounds__(512) small_matmul_kernel(const float* __restrict__ w, const float* __restrict__ xn, int ld_xn,
                                                            int n_rows, uint64_t k, const float* __restrict__ sumsq, int n_sumsq,
                                                            float norm_k, float eps, float out_scale, float* __restrict__ out,
                                                            int ld_out) {
@@ -158,13 +122,17 @@ __global__ void __launch_bounds__(128) small_matmul_kernel(const float* __restri
 #pragma unroll
     for (int r = 0; r < MAX_ROWS; ++r) acc[r] = 0.f;
     const float* wr = w + (uint64_t)j * k;
-    for (uint64_t c = threadIdx.x; c < k; c += blockDim.x) {
-        const float wv = wr[c];
+    for (uint64_t c = (uint64_t)threadIdx.x * 4; c < k; c += 512 * 4) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + c);
 #pragma unroll
-        for (int r = 0; r < MAX_ROWS; ++r)
-            if (r < n_rows) acc[r] = fmaf(wv, xn[(uint64_t)r * ld_xn + c], acc[r]);
+        for (int r = 0; r < MAX_ROWS; ++r) {
+            if (r < n_rows) {
+                const float4 xv = *reinterpret_cast<const float4*>(xn + (uint64_t)r * ld_xn + c);
+                acc[r] = fmaf(wv.w, xv.w, fmaf(wv.z, xv.z, fmaf(wv.y, xv.y, fmaf(wv.x, xv.x, acc[r]))));
+            }
+        }
     }
-    __shared__ float red[4][MAX_ROWS];
+    __shared__ float red[16][MAX_ROWS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
     for (int r = 0; r < MAX_ROWS; ++r) {
@@ -174,7 +142,9 @@ __global__ void __launch_bounds__(128) small_matmul_kernel(const float* __restri
     __syncthreads();
     if (threadIdx.x < n_rows) {
         const int r = threadIdx.x;
-        float s = red[0][r] + red[1][r] + red[2][r] + red[3][r];
+        float s = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < 16; ++wv) s += red[wv][r];
         float sc = out_scale;
         if (sumsq) {
             float ss = 0.f;
@@ -187,7 +157,8 @@ __global__ void __launch_bounds__(128) small_matmul_kernel(const float* __restri
 
 dfl_status launch_small_matmul(cudaStream_t st, const float* w, const float* xn, int ld_xn, int n_rows, uint64_t k, int n_out,
                                const GemmEpilogue& ep, float* out, int ld_out) {
-    small_matmul_kernel<<<n_out, 128, 0, st>>>(w, xn, ld_xn, n_rows, k, ep.sumsq, ep.n_sumsq, ep.norm_k, ep.eps, ep.out_scale, out,
+    if (k % 4) return fail(DFL_ERR_BAD_SHAPE, "small_matmul: k must be a multiple of 4");
+    small_matmul_kernel<<<n_out, 512, 0, st>>>(w, xn, ld_xn, n_rows, k, ep.sumsq, ep.n_sumsq, ep.norm_k, ep.eps, ep.out_scale, out,
                                                ld_out);
     count_launch();
     DFL_CUDA(cudaGetLastError());

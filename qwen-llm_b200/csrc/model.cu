@@ -138,7 +138,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
     const uint64_t H = a.hidden_size, F = a.intermediate_size;
     const AttnGeom ag = m->attn_geom();
     const GdnGeom gg = m->gdn_geom();
-    const int kb_h = (int)(H / 256);
+    const int kb_h = (int)(H / GLUE_COLS);
     GemmEpilogue ep_norm;
     ep_norm.sumsq = sc->sumsq;
     ep_norm.n_sumsq = kb_h;
@@ -492,7 +492,7 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
     alloc(&sc->x, MAX_ROWS * H * 4);
     alloc(&sc->xn, MAX_ROWS * H * 4);
     alloc(&sc->part, part * 4);
-    alloc(&sc->sumsq, (H / 256) * MAX_ROWS * 4);
+    alloc(&sc->sumsq, (H / GLUE_COLS) * MAX_ROWS * 4);
     alloc(&sc->acts_h, acts_bytes(DFL_Q4_K, H));
     alloc(&sc->acts_f, acts_bytes(DFL_Q4_K, F));
     alloc(&sc->acts_v, acts_bytes(DFL_Q4_K, std::max(q_dim, v_dim)));

@@ -52,6 +52,8 @@ __device__ __forceinline__ float softplus_f(float x) {
 }
 #endif
 
+constexpr int GLUE_COLS = 64;  // columns per glue CTA = granularity of the sum-of-squares partials
+
 enum GlueMode : int {
     GLUE_RESID = 0,   // v = x + sum_s part[s]        (x updated in place when x != nullptr)
     GLUE_SWIGLU = 1,  // v = silu(sum part[:, c]) * sum part[:, F + c]
@@ -71,7 +73,7 @@ struct GlueParams {
     int bf3 = 0;
     float* xn = nullptr;          // optional f32 copy of the packed value [16][ld_xn]
     int ld_xn = 0;
-    float* sumsq = nullptr;       // optional [kblocks][16] partial sums of v*v
+    float* sumsq = nullptr;       // optional [k / GLUE_COLS][16] partial sums of v*v
     float* capture = nullptr;     // optional copy of v: capture[tok * ld_capture + col]
     int ld_capture = 0;
     int swiglu_f = 0;
@@ -96,6 +98,7 @@ struct AttnGeom {
     float theta, eps;
 };
 constexpr int ATTN_CHUNK = 64;
+constexpr int ATTN_ROW_GROUP = 4;  // query rows per attention CTA
 // Reduces the fused q|k|v GEMM partials, applies per-head RMSNorm + partial NeoX RoPE, appends K/V
 // at positions start..start+n_rows-1 and leaves rotated Q and the raw gate for the attention kernel.
 // gated: q rows are interleaved (q, gate) per head as in the target; otherwise plain q.
