@@ -11,7 +11,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libdflash_b200.so")
+LIB_PATH = os.environ.get("DFL_LIB_PATH") or os.path.join(HERE, "libdflash_b200.so")
 
 F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 12, 13, 14, 30
 MAX_BLOCK = 16

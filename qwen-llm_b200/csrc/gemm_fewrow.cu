@@ -108,6 +108,7 @@ __device__ __forceinline__ void mma_pair_same_scale(float (&d)[2][2][4], const u
         mma_f16(d[m][0], A[m][4], A[m][5], A[m][6], A[m][7], f.hi0.z, f.hi0.w);
         mma_f16(d[m][1], A[m][4], A[m][5], A[m][6], A[m][7], f.hi1.z, f.hi1.w);
     }
+#ifndef DFL_EXP_NOLO
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
         mma_f16(d[m][0], A[m][0], A[m][1], A[m][2], A[m][3], f.lo0.x, f.lo0.y);
@@ -118,6 +119,7 @@ __device__ __forceinline__ void mma_pair_same_scale(float (&d)[2][2][4], const u
         mma_f16(d[m][0], A[m][4], A[m][5], A[m][6], A[m][7], f.lo0.z, f.lo0.w);
         mma_f16(d[m][1], A[m][4], A[m][5], A[m][6], A[m][7], f.lo1.z, f.lo1.w);
     }
+#endif
 }
 // Separate accumulators per step (per-16-column scales): d[m][step][token half].
 __device__ __forceinline__ void mma_pair_step_scale(float (&d)[2][2][2][4], const uint32_t (&A)[2][8], const ActFrag16& f) {
@@ -128,6 +130,7 @@ __device__ __forceinline__ void mma_pair_step_scale(float (&d)[2][2][2][4], cons
         mma_f16(d[m][1][0], A[m][4], A[m][5], A[m][6], A[m][7], f.hi0.z, f.hi0.w);
         mma_f16(d[m][1][1], A[m][4], A[m][5], A[m][6], A[m][7], f.hi1.z, f.hi1.w);
     }
+#ifndef DFL_EXP_NOLO
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
         mma_f16(d[m][0][0], A[m][0], A[m][1], A[m][2], A[m][3], f.lo0.x, f.lo0.y);
@@ -135,6 +138,7 @@ __device__ __forceinline__ void mma_pair_step_scale(float (&d)[2][2][2][4], cons
         mma_f16(d[m][1][0], A[m][4], A[m][5], A[m][6], A[m][7], f.lo0.z, f.lo0.w);
         mma_f16(d[m][1][1], A[m][4], A[m][5], A[m][6], A[m][7], f.lo1.z, f.lo1.w);
     }
+#endif
 }
 
 // acc[mt][c] (mt = 0..3 local m-tile of this warp): c0,c1 = (row 16mt+g, tokens 2t,2t+1),
@@ -489,7 +493,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
             const int s = i % STAGES;
             ok = mbar_wait_bounded(&full[s], (i / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
             if (!ok) break;
+#ifndef DFL_EXP_NOCOMPUTE
             F::consume(ring + s * SLOT, ring + s * SLOT + F::STAGE, sc, acc, ks, mh, lane);
+#else
+            acc[0][0] += reinterpret_cast<const float*>(ring + s * SLOT)[threadIdx.x];  // streaming-only experiment build
+            __syncwarp();
+#endif
             if (lane == 0) mbar_arrive(&empty[s]);
         }
         if (!ok) atomicExch(&abort_flag, 1);
