@@ -162,6 +162,26 @@ dfl_status dfl_fewrow_matmul(const dfl_qmatrix* m, const float* x_host, int32_t 
  * encode_argmax_top2_f32, kernels/elementwise.metal:1231-1286. */
 dfl_status dfl_argmax_top2(int32_t device, const float* logits_host, int32_t n_rows,
                            uint64_t vocab, int32_t* argmax_out, float* gap_out);
+/* The same row argmax for a caller that must not allocate device memory or
+ * block: code running inside a host callback of a stream, a thread that holds a
+ * lock the CUDA allocator may also need, or a serving loop with a fixed memory
+ * budget.  This entry point has no counterpart in the reference; it exists for
+ * such callers.  logits_dev [n_rows][ld] f32, argmax_dev [n_rows] and gap_dev
+ * [n_rows] are the caller's own buffers on `device`; `stream` is a
+ * cudaStream_t (NULL = the default stream).  The call enqueues two kernels
+ * on `stream` and returns without waiting: results are valid once the stream
+ * reaches that point.  It calls no allocation or free routine; its per-row
+ * partial results live in one fixed 16 KiB array inside the library, sized
+ * for n_rows <= 16 (larger n_rows is refused with DFL_ERR_BAD_SHAPE).  The
+ * first call on each device also looks up the array's address, so make one
+ * call per device before starting a stream capture.  Every call on a device
+ * shares that array and each call overwrites the part it uses before
+ * reading it, so nothing needs clearing; but two calls whose kernels can
+ * overlap (different streams, or different threads on different streams)
+ * race on it: keep calls on one device in stream order. */
+dfl_status dfl_argmax_top2_static(int32_t device, const float* logits_dev, int32_t n_rows,
+                                  uint64_t vocab, uint64_t ld, int32_t* argmax_dev,
+                                  float* gap_dev, void* stream);
 
 /* ---- BASELINE config 1: two chained few-row GEMMs + greedy acceptance ---
  * logits = head(x W1^T); argmax per row; greedy prefix accept against drafts.

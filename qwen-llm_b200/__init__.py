@@ -169,6 +169,12 @@ def argmax_top2(logits, device=0):
     return am, gap
 
 
+def argmax_top2_static(logits_ptr, n_rows, vocab, ld, argmax_ptr, gap_ptr, stream=0, device=0):
+    """Row argmax over device buffers given as raw addresses; enqueues on `stream` and allocates nothing."""
+    check(lib().dfl_argmax_top2_static(C.c_int32(device), C.c_void_p(logits_ptr), C.c_int32(n_rows), C.c_uint64(vocab),
+                                       C.c_uint64(ld), C.c_void_p(argmax_ptr), C.c_void_p(gap_ptr), C.c_void_p(stream)))
+
+
 class C1Pipeline:
     """BASELINE config 1: logits = head(x W1^T), row argmax, greedy prefix acceptance."""
 

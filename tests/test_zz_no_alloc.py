@@ -1,0 +1,60 @@
+"""dfl_argmax_top2_static (fixed in-library scratch, no allocation) against dfl_argmax_top2.
+
+Named so that it is collected last: it must pass both alone and after every other test has used
+the library in the same process.
+"""
+import numpy as np
+import pytest
+
+from dflb import pkg
+
+
+def _case(seed, n, vocab):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, vocab)).astype(np.float32) * 3.0
+    if n > 1:
+        x[1, 7] = x[1, 11] = x[1].max() + 1.0    # tie: the lowest index wins, gap 0
+    if n > 2:
+        x[2, vocab - 1] = np.float32("nan")       # NaN is reported as ~index
+    return x
+
+
+def _run_static(torch, x, ld=None):
+    n, vocab = x.shape
+    ld = ld or vocab
+    buf = torch.full((n, ld), -1.0e30, dtype=torch.float32, device="cuda:0")
+    buf[:, :vocab] = torch.from_numpy(x).to("cuda:0")
+    am = torch.full((n,), -12345, dtype=torch.int32, device="cuda:0")
+    gap = torch.full((n,), -1.0, dtype=torch.float32, device="cuda:0")
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated(0)
+    st = torch.cuda.current_stream(0).cuda_stream
+    pkg.argmax_top2_static(buf.data_ptr(), n, vocab, ld, am.data_ptr(), gap.data_ptr(), stream=st, device=0)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated(0) == before
+    return am.cpu().numpy(), gap.cpu().numpy()
+
+
+@pytest.mark.gpu
+def test_static_argmax_matches_allocating_entry_point_twice_in_a_row():
+    import torch
+    # two calls back to back with different shapes and data: the second must not see the first's scratch
+    for seed, n, vocab, ld in [(1, 16, 151936, None), (2, 5, 4099, 4112)]:
+        x = _case(seed, n, vocab)
+        want_am, want_gap = pkg.argmax_top2(x, device=0)
+        got_am, got_gap = _run_static(torch, x, ld)
+        np.testing.assert_array_equal(got_am, want_am)
+        np.testing.assert_array_equal(got_gap.view(np.uint32), want_gap.view(np.uint32))
+        assert got_am[1] == 7 and got_gap[1] == 0.0
+        assert got_am[2] == ~(vocab - 1)
+
+
+@pytest.mark.gpu
+def test_static_argmax_refuses_more_rows_than_its_scratch_holds():
+    import torch
+    buf = torch.zeros((17, 256), dtype=torch.float32, device="cuda:0")
+    am = torch.zeros((17,), dtype=torch.int32, device="cuda:0")
+    gap = torch.zeros((17,), dtype=torch.float32, device="cuda:0")
+    with pytest.raises(pkg.DflError) as e:
+        pkg.argmax_top2_static(buf.data_ptr(), 17, 256, 256, am.data_ptr(), gap.data_ptr())
+    assert e.value.name == "BAD_SHAPE" and "16" in str(e.value)
