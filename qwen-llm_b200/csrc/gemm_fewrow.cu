@@ -31,7 +31,6 @@ constexpr int M_HALVES = 2;                                         // warps alo
 constexpr int CONSUMER_WARPS = K_SLICES * M_HALVES;                 // 16
 constexpr int GEMM_THREADS = CONSUMER_WARPS * 32;                   // thread 0 also issues the bulk copies
 constexpr int RED_LD = TILE_R + 4;                                  // padded row length of the reduce buffer
-constexpr int RED_BYTES = K_SLICES * MAX_ROWS * RED_LD * 4;         // 67584
 constexpr int WARP_SCRATCH = (TILE_R / M_HALVES) * 8;               // float2 per row of the warp's 64 rows
 
 struct GemmParams {
@@ -42,6 +41,7 @@ struct GemmParams {
     int n_sumsq;
     float norm_k, eps, out_scale;
     int kblocks, splits;
+    int row_tiles, ctas_per_split;
     uint32_t n_out;   // rows of this matrix
     uint32_t ld_out;  // row length of the partial buffer (>= n_out when several matrices share it)
     int* err;
@@ -176,7 +176,7 @@ struct Fmt;
 
 template <>
 struct Fmt<DFL_Q4_K> {
-    static constexpr int STAGE = STAGE_Q4_K, ACT = ACT16_CHUNK, STAGES = 4;
+    static constexpr int STAGE = STAGE_Q4_K, ACT = ACT16_CHUNK, STAGES = 4, KC = 6;
     __device__ static __forceinline__ void unpack(uint32_t wq, uint32_t wq8, uint32_t (&A)[8]) {
         A[0] = h2_sub((wq & 0x000f000fu) | H2_1024, H2_1024);
         A[1] = h2_sub((wq8 & 0x000f000fu) | H2_1024, H2_1024);
@@ -223,7 +223,7 @@ struct Fmt<DFL_Q4_K> {
 
 template <>
 struct Fmt<DFL_Q5_K> {
-    static constexpr int STAGE = STAGE_Q5_K, ACT = ACT16_CHUNK, STAGES = 4;
+    static constexpr int STAGE = STAGE_Q5_K, ACT = ACT16_CHUNK, STAGES = 3, KC = 6;
     __device__ static __forceinline__ void unpack(uint32_t wq, uint32_t hb, uint32_t& a_l0, uint32_t& a_h0, uint32_t& a_l1, uint32_t& a_h1) {
         const uint32_t X = (hb & 0xfu) | ((hb & 0xf0u) << 12);
         const uint32_t v = wq >> 8;
@@ -270,7 +270,7 @@ struct Fmt<DFL_Q5_K> {
 
 template <>
 struct Fmt<DFL_Q6_K> {
-    static constexpr int STAGE = STAGE_Q6_K, ACT = ACT16_CHUNK, STAGES = 4;
+    static constexpr int STAGE = STAGE_Q6_K, ACT = ACT16_CHUNK, STAGES = 3, KC = 6;
     // wq: low nibbles, X: the 2-bit high fields spread as byte0 -> bits 0-7, byte1 -> bits 16-23
     __device__ static __forceinline__ void unpack(uint32_t wq, uint32_t X, uint32_t& a_l0, uint32_t& a_h0, uint32_t& a_l1, uint32_t& a_h1) {
         const uint32_t v = wq >> 8;
@@ -327,7 +327,7 @@ struct Fmt<DFL_Q6_K> {
 
 template <>
 struct Fmt<DFL_Q8_0> {
-    static constexpr int STAGE = STAGE_Q8_0, ACT = ACT16_CHUNK, STAGES = 4;
+    static constexpr int STAGE = STAGE_Q8_0, ACT = ACT16_CHUNK, STAGES = 3, KC = 4;
     __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2* sc, float (&acc)[4][8], int ks,
                                                    int mh, int lane) {
         const int g = lane >> 2, t = lane & 3;
@@ -379,7 +379,7 @@ struct Fmt<DFL_Q8_0> {
 
 template <>
 struct Fmt<DFL_BF16> {
-    static constexpr int STAGE = STAGE_B16, ACT = ACTB3_CHUNK, STAGES = 2;
+    static constexpr int STAGE = STAGE_B16, ACT = ACTB3_CHUNK, STAGES = 2, KC = 2;
     __device__ static __forceinline__ void consume(const uint8_t* wst, const uint8_t* ast, float2*, float (&acc)[4][8], int ks, int mh,
                                                    int lane) {
         const int g = lane >> 2, t = lane & 3;
@@ -416,35 +416,51 @@ struct Fmt<DFL_BF16> {
     }
 };
 
+constexpr int RED_HALF_BYTES = K_SLICES * (MAX_ROWS / 2) * RED_LD * 4;   // eight slices x eight tokens x 132 floats = 33792
+
 template <int DT>
 constexpr int gemm_smem_bytes() {
-    return Fmt<DT>::STAGES * (Fmt<DT>::STAGE + Fmt<DT>::ACT) + CONSUMER_WARPS * WARP_SCRATCH + 128;
+    return Fmt<DT>::KC * Fmt<DT>::ACT + Fmt<DT>::STAGES * Fmt<DT>::STAGE + RED_HALF_BYTES + CONSUMER_WARPS * WARP_SCRATCH + 128;
 }
 
+// One CTA = one split (a range of at most KC column blocks, whose packed activations stay
+// resident in shared memory) and every `ctas_per_split`-th row tile.  The weight stages of its
+// tiles stream back to back through the ring, so the copy pipeline stays full across tile
+// boundaries; after the last column block of a tile the eight column-slice partials are summed
+// in a fixed order and the tile's [16][128] partial result is written.
 template <int DT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const GemmParams p) {
     using F = Fmt<DT>;
     constexpr int STAGES = F::STAGES;
-    constexpr int SLOT = F::STAGE + F::ACT;
-    static_assert(STAGES * SLOT >= RED_BYTES, "stage ring must be able to hold the reduce buffer");
+    constexpr int OFF_RING = F::KC * F::ACT;
+    constexpr int OFF_RED = OFF_RING + STAGES * F::STAGE;
+    constexpr int OFF_SCR = OFF_RED + RED_HALF_BYTES;
+    constexpr int OFF_BAR = OFF_SCR + CONSUMER_WARPS * WARP_SCRATCH;
+    static_assert(OFF_BAR + 128 <= 227 * 1024, "shared memory budget");
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* ring = smem;
-    float2* scratch = reinterpret_cast<float2*>(smem + STAGES * SLOT);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * SLOT + CONSUMER_WARPS * WARP_SCRATCH);
+    uint8_t* acts_res = smem;
+    uint8_t* ring = smem + OFF_RING;
+    float* red = reinterpret_cast<float*>(smem + OFF_RED);
+    float2* scratch = reinterpret_cast<float2*>(smem + OFF_SCR);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* empty = full + STAGES;
+    uint64_t* acts_bar = empty + STAGES;
     __shared__ float tok_scale[MAX_ROWS];
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rt = blockIdx.x / p.splits, sp = blockIdx.x % p.splits;
+    const int sp = blockIdx.x % p.splits, c = blockIdx.x / p.splits;
     const int kb0 = (int)((long long)sp * p.kblocks / p.splits), kb1 = (int)((long long)(sp + 1) * p.kblocks / p.splits);
-    const int n_it = kb1 - kb0;
+    const int n_kb = kb1 - kb0;
+    const int n_my = (p.row_tiles - c + p.ctas_per_split - 1) / p.ctas_per_split;   // row tiles c, c + cps, ...
+    const int n_it = n_my * n_kb;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], CONSUMER_WARPS);
         }
+        mbar_init(acts_bar, 1);
         abort_flag = 0;
         mbar_fence_init();
     }
@@ -458,126 +474,147 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
-    // Thread 0 doubles as the producer: it arms the first STAGES stages up front and, once per
-    // iteration, refills the slot every warp released one iteration earlier.
+    // Thread 0 doubles as the producer.  (pt, pk) = tile / column block of the next stage to issue.
     const bool producer = threadIdx.x == 0;
-    const uint8_t* wsrc = p.w + ((uint64_t)rt * p.kblocks + kb0) * F::STAGE;
-    const uint8_t* asrc = p.acts + (uint64_t)kb0 * F::ACT;
+    const uint64_t tile_stride = (uint64_t)p.kblocks * F::STAGE;
+    const uint8_t* wbase = p.w + (uint64_t)kb0 * F::STAGE;
+    int pt = 0, pk = 0, issued = 0;
+    auto issue = [&](int slot) {
+        const uint8_t* src = wbase + (uint64_t)(c + pt * p.ctas_per_split) * tile_stride + (uint64_t)pk * F::STAGE;
+        mbar_arrive_expect_tx(&full[slot], F::STAGE);
+        bulk_g2s(ring + slot * F::STAGE, src, F::STAGE, &full[slot]);
+        ++issued;
+        if (++pk == n_kb) { pk = 0; ++pt; }
+    };
     if (producer) {
+        // weights do not depend on the previous kernel: the ring fills while that kernel still runs
         const int pre = n_it < STAGES ? n_it : STAGES;
-        // weights of the first stages do not depend on the previous kernel
-        for (int i = 0; i < pre; ++i) {
-            mbar_arrive_expect_tx(&full[i], F::STAGE + F::ACT);
-            bulk_g2s(ring + i * SLOT, wsrc + (uint64_t)i * F::STAGE, F::STAGE, &full[i]);
-        }
+        for (int i = 0; i < pre; ++i) issue(i);
         pdl_wait();
-        for (int i = 0; i < pre; ++i) bulk_g2s(ring + i * SLOT + F::STAGE, asrc + (uint64_t)i * F::ACT, F::ACT, &full[i]);
+        mbar_arrive_expect_tx(acts_bar, (uint32_t)n_kb * F::ACT);
+        for (int k = 0; k < n_kb; ++k)
+            bulk_g2s(acts_res + k * F::ACT, p.acts + (uint64_t)(kb0 + k) * F::ACT, F::ACT, acts_bar);
     }
-    {
-        const int ks = warp & (K_SLICES - 1), mh = warp >> 3;
-        float2* sc = scratch + warp * (TILE_R / M_HALVES);
-        bool ok = true;
-        for (int i = 0; i < n_it; ++i) {
-            if (producer && i >= 1 && i - 1 + STAGES < n_it) {
-                const int j = i - 1, sj = j % STAGES;  // slot consumed in the previous iteration
-                ok = mbar_wait_bounded(&empty[sj], (j / STAGES) & 1, p.err, DEV_ERR_WAIT_EMPTY);
-                if (ok) {
-                    const int nx = j + STAGES;
-                    mbar_arrive_expect_tx(&full[sj], F::STAGE + F::ACT);
-                    bulk_g2s(ring + sj * SLOT, wsrc + (uint64_t)nx * F::STAGE, F::STAGE, &full[sj]);
-                    bulk_g2s(ring + sj * SLOT + F::STAGE, asrc + (uint64_t)nx * F::ACT, F::ACT, &full[sj]);
-                }
-            }
-            if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the producer's verdict, warp-uniform
-            if (!ok) break;
-            const int s = i % STAGES;
-            ok = mbar_wait_bounded(&full[s], (i / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
-            if (!ok) break;
+
+    const int ks = warp & (K_SLICES - 1), mh = warp >> 3;
+    const int g = lane >> 2, t = lane & 3;
+    float2* sc = scratch + warp * (TILE_R / M_HALVES);
+    bool ok = n_it == 0 || mbar_wait_bounded(acts_bar, 0, p.err, DEV_ERR_WAIT_FULL);
+    int kb = 0, tile = 0;
+    for (int i = 0; i < n_it; ++i) {
+        if (producer && ok && i >= 1 && issued < n_it) {
+            const int j = i - 1, sj = j % STAGES;  // slot consumed in the previous iteration
+            ok = mbar_wait_bounded(&empty[sj], (j / STAGES) & 1, p.err, DEV_ERR_WAIT_EMPTY);
+            if (ok) issue(sj);
+        }
+        if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the producer's verdict, warp-uniform
+        const int s = i % STAGES;
+        if (ok) ok = mbar_wait_bounded(&full[s], (i / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
+        if (ok) {
 #ifndef DFL_EXP_NOCOMPUTE
-            F::consume(ring + s * SLOT, ring + s * SLOT + F::STAGE, sc, acc, ks, mh, lane);
+            F::consume(ring + s * F::STAGE, acts_res + kb * F::ACT, sc, acc, ks, mh, lane);
 #else
-            acc[0][0] += reinterpret_cast<const float*>(ring + s * SLOT)[threadIdx.x];  // streaming-only experiment build
+            acc[0][0] += reinterpret_cast<const float*>(ring + s * F::STAGE)[threadIdx.x];  // streaming-only experiment build
             __syncwarp();
 #endif
             if (lane == 0) mbar_arrive(&empty[s]);
+        } else {
+            abort_flag = 1;  // keep walking the loop so that every warp meets the same barriers
         }
-        if (!ok) atomicExch(&abort_flag, 1);
-    }
-    __syncthreads();
-    if (abort_flag) {
-        // Error word already set.  Every copy this CTA armed either completed (its full barrier was
-        // waited for) or is given a bounded chance to land before the shared memory is released.
-        if (producer)
-            for (int s = 0; s < STAGES; ++s) {
-                uint32_t spins = 0;
-                while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && ++spins < (1u << 16)) __nanosleep(100);
-            }
-        return;
-    }
+        if (++kb < n_kb) continue;
+        kb = 0;
 
-    // ---------------- epilogue: fixed-order sum over the eight column slices ----------------
-    float* red = reinterpret_cast<float*>(ring);
-    {
-        const int ks = warp & (K_SLICES - 1), mh = warp >> 3;
-        const int g = lane >> 2, t = lane & 3;
-        float* mine = red + ks * (MAX_ROWS * RED_LD) + 64 * mh;
+        // ---- tile finished: fixed-order sum over the eight column slices, tokens 0-7 then 8-15 ----
+        if (tile == 0 && threadIdx.x < 256) {
+            // per-token output scale; 16 threads per token add the sum-of-squares partials in a fixed tree
+            const int tok = threadIdx.x >> 4, part = threadIdx.x & 15;
+            float ss = 0.f;
+            if (p.sumsq)
+                for (int q = part; q < p.n_sumsq; q += 16) ss += p.sumsq[q * MAX_ROWS + tok];
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-            const int r0 = 16 * mt + g;
-            mine[(2 * t) * RED_LD + r0] = acc[mt][0];
-            mine[(2 * t + 1) * RED_LD + r0] = acc[mt][1];
-            mine[(2 * t) * RED_LD + r0 + 8] = acc[mt][2];
-            mine[(2 * t + 1) * RED_LD + r0 + 8] = acc[mt][3];
-            mine[(2 * t + 8) * RED_LD + r0] = acc[mt][4];
-            mine[(2 * t + 9) * RED_LD + r0] = acc[mt][5];
-            mine[(2 * t + 8) * RED_LD + r0 + 8] = acc[mt][6];
-            mine[(2 * t + 9) * RED_LD + r0 + 8] = acc[mt][7];
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (part == 0) tok_scale[tok] = p.sumsq ? p.out_scale * (1.0f / sqrtf(ss / p.norm_k + p.eps)) : p.out_scale;
         }
-    }
-    if (threadIdx.x < 256) {
-        // per-token output scale; 16 threads per token add the sum-of-squares partials in a fixed tree
-        const int tok = threadIdx.x >> 4, part = threadIdx.x & 15;
-        float ss = 0.f;
-        if (p.sumsq)
-            for (int i = part; i < p.n_sumsq; i += 16) ss += p.sumsq[i * MAX_ROWS + tok];
+        const uint32_t rt = (uint32_t)(c + tile * p.ctas_per_split);
+        const int row = threadIdx.x & (TILE_R - 1), tq = threadIdx.x >> 7;
+        const uint32_t orow = rt * TILE_R + row;
+        float* dst = p.out + (uint64_t)sp * MAX_ROWS * p.ld_out + orow;
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (part == 0) tok_scale[tok] = p.sumsq ? p.out_scale * (1.0f / sqrtf(ss / p.norm_k + p.eps)) : p.out_scale;
+        for (int h = 0; h < 2; ++h) {
+            float* mine = red + ks * ((MAX_ROWS / 2) * RED_LD) + 64 * mh;
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                const int r0 = 16 * mt + g;
+                mine[(2 * t) * RED_LD + r0] = acc[mt][4 * h + 0];
+                mine[(2 * t + 1) * RED_LD + r0] = acc[mt][4 * h + 1];
+                mine[(2 * t) * RED_LD + r0 + 8] = acc[mt][4 * h + 2];
+                mine[(2 * t + 1) * RED_LD + r0 + 8] = acc[mt][4 * h + 3];
+                acc[mt][4 * h + 0] = acc[mt][4 * h + 1] = acc[mt][4 * h + 2] = acc[mt][4 * h + 3] = 0.f;
+            }
+            __syncthreads();
+            if (orow < p.n_out && !abort_flag) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int tl = 2 * tq + j, tok = 8 * h + tl;
+                    float v = 0.f;
+#pragma unroll
+                    for (int wv = 0; wv < K_SLICES; ++wv) v += red[wv * ((MAX_ROWS / 2) * RED_LD) + tl * RED_LD + row];
+                    dst[(uint64_t)tok * p.ld_out] = v * tok_scale[tok];
+                }
+            }
+            __syncthreads();
+        }
+        ++tile;
     }
     __syncthreads();
-    {
-        const int row = threadIdx.x & (TILE_R - 1), tg = threadIdx.x >> 7;
-        const uint32_t orow = (uint32_t)rt * TILE_R + row;
-        if (orow < p.n_out) {
-            float* dst = p.out + (uint64_t)sp * MAX_ROWS * p.ld_out + orow;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int tok = tg * 4 + j;
-                float v = 0.f;
-#pragma unroll
-                for (int wv = 0; wv < K_SLICES; ++wv) v += red[wv * (MAX_ROWS * RED_LD) + tok * RED_LD + row];
-                dst[(uint64_t)tok * p.ld_out] = v * tok_scale[tok];
-            }
+    if (abort_flag && producer) {
+        // Error word already set.  Give every copy this CTA armed a bounded chance to land before
+        // the shared memory is released.
+        for (int s = 0; s < STAGES; ++s) {
+            uint32_t spins = 0;
+            while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && ++spins < (1u << 16)) __nanosleep(100);
         }
+        uint32_t spins = 0;
+        while (!mbar_try_wait(acts_bar, 0) && ++spins < (1u << 16)) __nanosleep(100);
     }
 }
 
-// Split count: enough CTAs to fill the 148 SMs (one CTA per SM) in whole waves, but no finer than
-// two column blocks per CTA where that is possible.
+constexpr int kSmCount = 148;
+
+int gemm_max_kblocks_per_cta(int dtype) {
+    switch (dtype) {
+        case DFL_Q4_K: return Fmt<DFL_Q4_K>::KC;
+        case DFL_Q5_K: return Fmt<DFL_Q5_K>::KC;
+        case DFL_Q6_K: return Fmt<DFL_Q6_K>::KC;
+        case DFL_Q8_0: return Fmt<DFL_Q8_0>::KC;
+        case DFL_BF16: return Fmt<DFL_BF16>::KC;
+        default: return 1;
+    }
+}
+
+static int ctas_per_split(int row_tiles, int splits) {
+    int cps = kSmCount / splits;
+    if (cps < 1) cps = 1;
+    return cps < row_tiles ? cps : row_tiles;
+}
+
+// Split count: every split must fit the resident activation window; beyond that, the count that
+// minimises the longest CTA (rounds of row tiles x column blocks per split, plus a per-tile
+// epilogue and a per-launch prologue measured in stage times).
 int gemm_choose_splits(const QMatrix& m) {
-    constexpr int kSms = 148;
     const int tiles = m.row_tiles > 0 ? m.row_tiles : 1;
-    int best = 1;
-    double best_score = -1.0;
-    const int max_s = m.kblocks < 16 ? m.kblocks : 16;
-    for (int s = 1; s <= max_s; ++s) {
-        const int ctas = tiles * s;
-        const int waves = (ctas + kSms - 1) / kSms;
-        const double fill = (double)ctas / (double)(waves * kSms);       // fraction of SM-slots doing work
-        const double per_cta = (double)m.kblocks / s;                     // stages per CTA
-        const double overhead = per_cta / (per_cta + 1.5);                // fixed prologue/epilogue ~ 1.5 stages
-        const double score = fill * overhead - 0.01 * s;                  // mild preference for fewer partials
-        if (score > best_score) { best_score = score; best = s; }
+    const int kc = gemm_max_kblocks_per_cta(m.dtype);
+    const int s_min = (m.kblocks + kc - 1) / kc;
+    int s_max = m.kblocks < 24 ? m.kblocks : 24;
+    if (s_max < s_min) s_max = s_min;
+    int best = s_min;
+    double best_cost = 1e30;
+    for (int s = s_min; s <= s_max; ++s) {
+        const int cps = ctas_per_split(tiles, s);
+        const int rounds = (tiles + cps - 1) / cps;
+        const double unit = (double)((m.kblocks + s - 1) / s) + 1.0;
+        const double cost = rounds * unit + 1.5 + 0.05 * s;
+        if (cost < best_cost) { best_cost = cost; best = s; }
     }
     return best;
 }
@@ -639,7 +676,11 @@ dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* 
     p.n_out = (uint32_t)m.n_out;
     p.ld_out = ld_out ? ld_out : (uint32_t)m.n_out;
     p.err = dev_err;
-    const int grid = m.row_tiles * splits;
+    if ((m.kblocks + splits - 1) / splits > gemm_max_kblocks_per_cta(m.dtype))
+        return fail(DFL_ERR_BAD_ARG, "gemm: too few splits for the resident activation window");
+    p.row_tiles = m.row_tiles;
+    p.ctas_per_split = ctas_per_split(m.row_tiles, splits);
+    const int grid = p.ctas_per_split * splits;
     if (!g_timing) return launch_gemm_dispatch(st, m, p, grid, pdl);
     TimedLaunch t{};
     t.bytes = m.ggml_bytes();

@@ -68,7 +68,11 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
     // one split count for the whole group so that every partial slice is fully written
     QMatrix whole;
     whole.row_tiles = 0;
-    for (auto& m : out->mats) whole.row_tiles += m.row_tiles;
+    whole.dtype = out->mats[0].dtype;
+    for (auto& m : out->mats) {
+        whole.row_tiles += m.row_tiles;
+        if (gemm_max_kblocks_per_cta(m.dtype) < gemm_max_kblocks_per_cta(whole.dtype)) whole.dtype = m.dtype;
+    }
     whole.kblocks = (int)(n_in / 256);
     out->splits = gemm_choose_splits(whole);
     return DFL_OK;

@@ -182,6 +182,7 @@ struct GemmEpilogue {
     float out_scale = 1.f;
 };
 int gemm_choose_splits(const QMatrix& m);
+int gemm_max_kblocks_per_cta(int dtype);  // column blocks one CTA can keep resident
 // out: [splits][16][n_out] f32 partial sums (sum over the first axis in order 0..splits-1).
 // ld_out: row length of `out` (0 = n_out); a wider buffer lets several matrices with the
 // same input write side by side (out then points at this matrix's first column).
