@@ -3,7 +3,7 @@
 #include <mutex>
 #include <vector>
 
-#include "tiles.cuh"
+#include "gemm_ts.cuh"
 
 namespace dfl {
 
@@ -47,7 +47,7 @@ dfl_status check_dev_err(cudaStream_t st, int* dev_err) {
 }
 
 dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, const void* data, uint64_t n_bytes,
-                          bool on_device, cudaStream_t st, QMatrix* m) {
+                          bool on_device, cudaStream_t st, QMatrix* m, bool allow_ts) {
     DFL_CHECK(use_device(device));
     if (!data || n_in == 0 || n_out == 0) return fail(DFL_ERR_BAD_ARG, "qmatrix: null data or empty shape");
     m->device = device;
@@ -80,7 +80,11 @@ dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, 
         if (tmp) cudaFree(tmp);
         return fail(DFL_ERR_OOM, std::string("qmatrix: cudaMalloc: ") + cudaGetErrorString(e));
     }
-    dfl_status s = retile_matrix(st, dtype, src, n_in, n_out, m->tiles);
+    // DFL_GEMM_PATH=legacy keeps every matrix on the mma.sync kernel (A/B runs)
+    const char* path = getenv("DFL_GEMM_PATH");
+    m->layout = (allow_ts && ts_supported(dtype) && !(path && std::string(path) == "legacy")) ? LAYOUT_TS : LAYOUT_FRAG;
+    dfl_status s = m->layout == LAYOUT_TS ? retile_matrix_ts(st, dtype, src, n_in, n_out, m->tiles)
+                                          : retile_matrix(st, dtype, src, n_in, n_out, m->tiles);
     cudaError_t e2 = cudaStreamSynchronize(st);
     if (tmp) cudaFree(tmp);
     if (s != DFL_OK) return s;
@@ -137,7 +141,7 @@ dfl_status dfl_qmatrix_create(int32_t device, int32_t dtype, uint64_t n_in, uint
     if (!out) return fail(DFL_ERR_BAD_ARG, "qmatrix_create: out is null");
     *out = nullptr;
     auto* q = new dfl_qmatrix();
-    dfl_status s = qmatrix_create(device, dtype, n_in, n_out, data, n_bytes, on_device != 0, 0, &q->m);
+    dfl_status s = qmatrix_create(device, dtype, n_in, n_out, data, n_bytes, on_device != 0, 0, &q->m, true);
     if (s != DFL_OK) {
         qmatrix_release(&q->m);
         delete q;
@@ -163,7 +167,7 @@ dfl_status dfl_qmatrix_dequant(const dfl_qmatrix* m, float* out_host, uint64_t n
     }
     float* d = nullptr;
     DFL_CUDA(cudaMalloc(&d, n_floats * 4));
-    dfl_status s = decode_tiles(0, m->m, d);
+    dfl_status s = m->m.layout == LAYOUT_TS ? decode_tiles_ts(0, m->m, d) : decode_tiles(0, m->m, d);
     cudaError_t e = cudaMemcpy(out_host, d, n_floats * 4, cudaMemcpyDeviceToHost);
     cudaFree(d);
     if (s != DFL_OK) return s;
@@ -184,14 +188,14 @@ dfl_status dfl_fewrow_matmul(const dfl_qmatrix* m, const float* x_host, int32_t 
     dfl_status s = DFL_OK;
     auto cleanup = [&]() { cudaFree(x); cudaFree(part); cudaFree(y); cudaFree(acts); cudaFree(err); };
     if (cudaMalloc(&x, (size_t)n_rows * q.n_in * 4) != cudaSuccess || cudaMalloc(&part, (size_t)splits * MAX_ROWS * q.n_out * 4) != cudaSuccess ||
-        cudaMalloc(&y, (size_t)n_rows * q.n_out * 4) != cudaSuccess || cudaMalloc(&acts, acts_bytes(q.dtype, q.n_in)) != cudaSuccess ||
+        cudaMalloc(&y, (size_t)n_rows * q.n_out * 4) != cudaSuccess || cudaMalloc(&acts, acts_bytes_for(q)) != cudaSuccess ||
         cudaMalloc(&err, 4) != cudaSuccess) {
         cleanup();
         return fail(DFL_ERR_OOM, "fewrow_matmul: cudaMalloc failed");
     }
     cudaMemset(err, 0, 4);
     cudaMemcpy(x, x_host, (size_t)n_rows * q.n_in * 4, cudaMemcpyHostToDevice);
-    s = launch_prep_acts(0, q.dtype, x, (int)q.n_in, n_rows, q.n_in, 1.0f, acts, err);
+    s = launch_prep_acts_for(0, q, x, (int)q.n_in, n_rows, 1.0f, acts, err);
     if (s == DFL_OK) s = launch_gemm_fewrow(0, q, acts, part, splits, GemmEpilogue{}, err, false);
     if (s == DFL_OK) s = launch_reduce_partials(0, part, splits, n_rows, q.n_out, y, (int)q.n_out);
     if (s == DFL_OK) s = check_dev_err(0, err);
@@ -249,8 +253,8 @@ dfl_status dfl_c1_create(const dfl_qmatrix* w1, const dfl_qmatrix* head, dfl_c1*
     ok = ok && cudaMalloc(&p->logits, MAX_ROWS * v * 4) == cudaSuccess;
     ok = ok && cudaMalloc(&p->gap, MAX_ROWS * 4) == cudaSuccess;
     ok = ok && cudaMalloc(&p->argmax, MAX_ROWS * 4) == cudaSuccess;
-    ok = ok && cudaMalloc(&p->acts1, acts_bytes(w1->m.dtype, k1)) == cudaSuccess;
-    ok = ok && cudaMalloc(&p->acts2, acts_bytes(head->m.dtype, n1)) == cudaSuccess;
+    ok = ok && cudaMalloc(&p->acts1, acts_bytes_for(w1->m)) == cudaSuccess;
+    ok = ok && cudaMalloc(&p->acts2, acts_bytes_for(head->m)) == cudaSuccess;
     ok = ok && cudaMalloc(&p->am_scratch, MAX_ROWS * ARGMAX_PARTS * 16) == cudaSuccess;
     ok = ok && cudaMalloc(&p->err, 4) == cudaSuccess;
     ok = ok && cudaEventCreate(&p->e0) == cudaSuccess && cudaEventCreate(&p->e1) == cudaSuccess;
@@ -280,10 +284,10 @@ void dfl_c1_destroy(dfl_c1* p) {
 static dfl_status c1_enqueue(dfl_c1* p, int n_rows) {
     const QMatrix& a = p->w1->m;
     const QMatrix& b = p->head->m;
-    DFL_CHECK(launch_prep_acts(p->st, a.dtype, p->x, (int)a.n_in, n_rows, a.n_in, 1.0f, p->acts1, p->err));
+    DFL_CHECK(launch_prep_acts_for(p->st, a, p->x, (int)a.n_in, n_rows, 1.0f, p->acts1, p->err));
     DFL_CHECK(launch_gemm_fewrow(p->st, a, p->acts1, p->part1, p->splits1, GemmEpilogue{}, p->err, false));
     DFL_CHECK(launch_reduce_partials(p->st, p->part1, p->splits1, n_rows, a.n_out, p->h, (int)a.n_out));
-    DFL_CHECK(launch_prep_acts(p->st, b.dtype, p->h, (int)a.n_out, n_rows, a.n_out, 1.0f, p->acts2, p->err));
+    DFL_CHECK(launch_prep_acts_for(p->st, b, p->h, (int)a.n_out, n_rows, 1.0f, p->acts2, p->err));
     DFL_CHECK(launch_gemm_fewrow(p->st, b, p->acts2, p->part2, p->splits2, GemmEpilogue{}, p->err, false));
     DFL_CHECK(launch_reduce_partials(p->st, p->part2, p->splits2, n_rows, b.n_out, p->logits, (int)b.n_out));
     DFL_CHECK(launch_argmax_top2(p->st, p->logits, n_rows, b.n_out, b.n_out, p->argmax, p->gap, p->am_scratch));

@@ -22,7 +22,7 @@
 //     deterministic and each activation row's result is independent of the other rows.
 #include <vector>
 
-#include "tiles.cuh"
+#include "gemm_ts.cuh"
 
 namespace dfl {
 
@@ -602,6 +602,7 @@ static int ctas_per_split(int row_tiles, int splits) {
 // minimises the longest CTA (rounds of row tiles x column blocks per split, plus a per-tile
 // epilogue and a per-launch prologue measured in stage times).
 int gemm_choose_splits(const QMatrix& m) {
+    if (m.layout == LAYOUT_TS) return gemm_ts_choose_splits(m);
     const int tiles = m.row_tiles > 0 ? m.row_tiles : 1;
     const int kc = gemm_max_kblocks_per_cta(m.dtype);
     const int s_min = (m.kblocks + kc - 1) / kc;
@@ -662,6 +663,18 @@ static dfl_status launch_gemm_dispatch(cudaStream_t st, const QMatrix& m, const 
 dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits,
                               const GemmEpilogue& ep, int* dev_err, bool pdl, uint32_t ld_out) {
     if (splits < 1 || splits > m.kblocks) return fail(DFL_ERR_BAD_ARG, "gemm: bad split count");
+    if (m.layout == LAYOUT_TS) {
+        if (!g_timing) return launch_gemm_ts(st, m, acts, out, splits, ep, dev_err, pdl, ld_out);
+        TimedLaunch t{};
+        t.bytes = m.ggml_bytes();
+        DFL_CUDA(cudaEventCreate(&t.e0));
+        DFL_CUDA(cudaEventCreate(&t.e1));
+        DFL_CUDA(cudaEventRecord(t.e0, st));
+        dfl_status rc = launch_gemm_ts(st, m, acts, out, splits, ep, dev_err, pdl, ld_out);
+        DFL_CUDA(cudaEventRecord(t.e1, st));
+        g_timed.push_back(t);
+        return rc;
+    }
     GemmParams p;
     p.w = m.tiles;
     p.acts = acts;
@@ -769,6 +782,12 @@ dfl_status launch_prep_acts(cudaStream_t st, int weight_dtype, const float* x, i
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
+}
+
+dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* x, int ld, int n_rows, float pre_scale, uint8_t* acts,
+                                int* dev_err) {
+    if (m.layout == LAYOUT_TS) return launch_prep_acts_ts(st, x, ld, n_rows, m.n_in, pre_scale, acts, dev_err);
+    return launch_prep_acts(st, m.dtype, x, ld, n_rows, m.n_in, pre_scale, acts, dev_err);
 }
 
 __global__ void reduce_partials_kernel(const float* __restrict__ part, int splits, int n_rows, uint64_t n_out, float* __restrict__ y,

@@ -1,0 +1,367 @@
+// Few-row weight-streaming GEMM on the fifth-generation tensor cores.
+//
+// Same contract as the mma.sync kernel (gemm_fewrow.cu: y[r, o] = sum_i x[r, i] W[o, i], <= 16
+// activation rows, split-K partials, deterministic), different engine:
+//   * a producer thread streams 128-row x 256-column stages of packed weights with bulk copies
+//     into a shared-memory ring; the packed activations of the CTA's column range are copied
+//     once and stay resident as the B operand;
+//   * sixteen unpacking warps turn the integer quants into exact f16 integers q * sc (the
+//     6-bit sub-block scale folded in, still exact: q * sc < 2048) and store them with
+//     tcgen05.st into tensor memory, thread = (row, quarter of the columns), row = TMEM lane;
+//   * one thread issues tcgen05.mma (A from tensor memory, B = activations hi / lo planes from
+//     shared memory, M = 128, N = 32, K = 16 per instruction), sixteen per stage, accumulating
+//     the whole 256-column block in tensor memory; a seventeenth MMA multiplies the sub-block
+//     mins with the per-sub-block activation sums (the K-quant "min" term);
+//   * two stages later the unpacking threads read their row's 8 + 12 accumulator columns back
+//     (tcgen05.ld), apply the per-row f16 super-block scales d and dmin in f32 and add to four
+//     register accumulators per thread (row x 4 tokens); at the end of a row tile they write
+//     the partial result straight to global memory.  No shared-memory reduction, no atomics.
+// A and the accumulators are double-buffered in tensor memory so that unpacking stage i + 1
+// overlaps the MMAs of stage i.
+#include "gemm_ts.cuh"
+
+namespace dfl {
+
+// Q6_K packing lives in gemm_ts_q6k.cuh (included further down, after the primitives it uses)
+__global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks);
+__device__ float decode_ts_q6k_elem(const uint8_t* stage, int r, int k);
+
+// ---------------------------------------------------------------------------------------------
+// Re-tiling into row-lane tiles and the inverse decode.
+// ---------------------------------------------------------------------------------------------
+template <int DT>
+__global__ void retile_ts_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks) {
+    constexpr int SRC_BLK = DT == DFL_Q4_K ? 144 : DT == DFL_Q5_K ? 176 : 210;
+    constexpr int STAGE = DT == DFL_Q4_K ? STAGE_Q4_K : DT == DFL_Q5_K ? STAGE_Q5_K : STAGE_Q6_K;
+    const uint64_t tile_id = blockIdx.x;
+    const int kb = (int)(tile_id % kblocks);
+    const uint64_t rt = tile_id / kblocks;
+    uint8_t* stage = dst + tile_id * STAGE;
+    // one item = 16 destination bytes
+    for (int idx = threadIdx.x; idx < STAGE / 16; idx += blockDim.x) {
+        uint8_t out[16];
+#pragma unroll
+        for (int b = 0; b < 16; ++b) out[b] = 0;
+        const int off = idx * 16;
+        if (DT == DFL_Q4_K || DT == DFL_Q5_K) {
+            const int qs_src = DT == DFL_Q4_K ? 16 : 48;
+            int r, src_off;
+            if (off < TSQ4_OFF_QS) { r = idx; src_off = 0; }                                  // header
+            else if (off < TSQ4_OFF_QS + 16384) {                                             // qs [kp][half][row]
+                const int i = idx - TSQ4_OFF_QS / 16;
+                r = i & 127;
+                src_off = qs_src + 32 * (i >> 8) + 16 * ((i >> 7) & 1);
+            } else {                                                                          // Q5_K qh [half][row]
+                const int i = idx - TSQ5_OFF_QH / 16;
+                r = i & 127;
+                src_off = 16 + 16 * (i >> 7);
+            }
+            const uint64_t row = rt * TILE_R + r;
+            if (row < n_out) {
+                const uint8_t* blk = src + (row * kblocks + kb) * (uint64_t)SRC_BLK + src_off;
+#pragma unroll
+                for (int b = 0; b < 16; ++b) out[b] = blk[b];
+            }
+        }
+        *reinterpret_cast<uint4*>(stage + off) = *reinterpret_cast<const uint4*>(out);
+    }
+}
+
+dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, uint8_t* dst_tiles) {
+    if (n_in % TILE_K) return fail(DFL_ERR_BAD_SHAPE, "retile: n_in must be a multiple of 256");
+    const int kblocks = (int)(n_in / TILE_K);
+    const uint64_t n_tiles = (uint64_t)kblocks * ((n_out + TILE_R - 1) / TILE_R);
+    if (n_tiles == 0 || n_tiles > 0x7fffffffu) return fail(DFL_ERR_BAD_SHAPE, "retile: tile count out of range");
+    dim3 grid((unsigned)n_tiles), block(256);
+    switch (dtype) {
+        case DFL_Q4_K: retile_ts_kernel<DFL_Q4_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
+        case DFL_Q5_K: retile_ts_kernel<DFL_Q5_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
+        case DFL_Q6_K: retile_ts_q6k_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
+        default: return fail(DFL_ERR_UNSUPPORTED, "retile: dtype has no row-lane tile layout");
+    }
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+__global__ void decode_tiles_ts_kernel(const uint8_t* __restrict__ tiles, int dtype, uint64_t n_in, uint64_t n_out, int kblocks,
+                                       float* __restrict__ out) {
+    const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_in * n_out) return;
+    const uint64_t row = idx / n_in;
+    const int kk = (int)(idx % n_in);
+    const int kb = kk >> 8, k = kk & 255;
+    const uint64_t rt = row / TILE_R;
+    const int r = (int)(row % TILE_R);
+    const uint8_t* stage = tiles + (rt * kblocks + kb) * (uint64_t)stage_bytes_of(dtype);
+    float v = 0.f;
+    if (dtype == DFL_Q4_K || dtype == DFL_Q5_K) {
+        const uint8_t* h = stage + r * 16;
+        const float d = __half2float(__ushort_as_half((unsigned short)(h[0] | (h[1] << 8))));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(h[2] | (h[3] << 8))));
+        uint32_t sc, m;
+        k4_scale_min(h + 4, k >> 5, sc, m);
+        const int kp = k >> 6, hi = (k >> 5) & 1, l = k & 31;
+        const uint8_t byte = stage[TSQ4_OFF_QS + ((kp * 2 + (l >> 4)) * 128 + r) * 16 + (l & 15)];
+        uint32_t q = hi ? (byte >> 4) : (byte & 15);
+        if (dtype == DFL_Q5_K) q |= ((stage[TSQ5_OFF_QH + ((l >> 4) * 128 + r) * 16 + (l & 15)] >> (2 * kp + hi)) & 1u) << 4;
+        v = __fsub_rn(__fmul_rn(d * (float)sc, (float)q), dmin * (float)m);
+    } else if (dtype == DFL_Q6_K) {
+        v = decode_ts_q6k_elem(stage, r, k);
+    }
+    out[idx] = v;
+}
+
+dfl_status decode_tiles_ts(cudaStream_t st, const QMatrix& m, float* out_dev) {
+    const uint64_t n = m.n_in * m.n_out;
+    decode_tiles_ts_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m.tiles, m.dtype, m.n_in, m.n_out, m.kblocks, out_dev);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Standalone activation packing (the model path packs inside its glue kernels).
+// One CTA per 256-column block; thread = (token = tid / 16, 16 consecutive columns).
+// ---------------------------------------------------------------------------------------------
+__global__ void prep_acts_ts_kernel(const float* __restrict__ x, int ld, int n_rows, float pre_scale, uint8_t* __restrict__ acts,
+                                    int* err) {
+    const int kb = blockIdx.x, tok = threadIdx.x >> 4, seg = threadIdx.x & 15;
+    uint8_t* chunk = acts + (uint64_t)kb * ACTTS_CHUNK;
+    // the zero half of the small operand (sub-block index 8..15)
+    for (int i = threadIdx.x; i < 768 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(chunk + TS_BMIN_OFF + 768)[i] = 0u;
+    float v[16];
+    if (tok < n_rows) {
+        const float4* src = reinterpret_cast<const float4*>(x + (uint64_t)tok * ld + (uint64_t)kb * TILE_K + seg * 16);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 q = src[j];
+            v[4 * j] = q.x * pre_scale; v[4 * j + 1] = q.y * pre_scale; v[4 * j + 2] = q.z * pre_scale; v[4 * j + 3] = q.w * pre_scale;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+    }
+    bool over = false;
+    float sum = 0.f;
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+        const float quad[4] = {v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]};
+        pack_quad_ts(chunk, tok, seg * 16 + 4 * q4, quad, over);
+        sum += (quad[0] + quad[1]) + (quad[2] + quad[3]);
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // 32-column sub-block = this thread and its neighbour
+    if ((seg & 1) == 0) pack_subsum_ts(chunk, tok, seg >> 1, sum, over);
+    if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
+}
+
+dfl_status launch_prep_acts_ts(cudaStream_t st, const float* x, int ld, int n_rows, uint64_t k, float pre_scale, uint8_t* acts,
+                               int* dev_err) {
+    if (k % TILE_K || n_rows < 0 || n_rows > MAX_ROWS) return fail(DFL_ERR_BAD_SHAPE, "prep_acts: shape");
+    prep_acts_ts_kernel<<<(unsigned)(k / TILE_K), 256, 0, st>>>(x, ld, n_rows, pre_scale, acts, dev_err);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05 / tensor-memory primitives (sm_100a).
+// ---------------------------------------------------------------------------------------------
+namespace ts {
+
+constexpr int UNPACK_WARPS = 16;
+constexpr int UNPACK_THREADS = UNPACK_WARPS * 32;       // 512: thread = (row = 32 * (warp % 4) + lane, kp = warp / 4)
+constexpr int PRODUCER_WARP = 16, MMA_WARP = 17;
+constexpr int THREADS = (UNPACK_WARPS + 2) * 32;        // 576
+constexpr int KC = 8;                                   // column blocks whose activations stay resident
+
+// tensor-memory columns (32-bit each, 128 lanes): two A buffers of 128 columns (256 f16 per row),
+// two 32-column accumulators, two 8-column A operands and 48-column accumulators of the min term
+constexpr uint32_t TM_A = 0, TM_D = 256, TM_AM = 320, TM_DM = 336, TM_COLS = 512;
+
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// mbarrier arrive once every MMA this thread issued before has completed
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor]; M x N x 16, f16 inputs, f32 accumulate
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero)
+        : "memory");
+}
+// K-major, no swizzle: 8-row groups 128 B apart (stride offset), the two k-cores `lbo` bytes apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46);
+}
+// f16 x f16 -> f32, A and B K-major, M = 128
+__host__ __device__ constexpr uint32_t instr_desc(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24); }
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
+    uint32_t r[4];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ uint32_t h2sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2mul(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+constexpr uint32_t MAGIC = 0x64006400u;      // half2(1024, 1024): 1024 + small integer in the mantissa
+constexpr uint32_t H2_NEG1024 = 0xe400e400u; // half2(-1024)
+constexpr uint32_t H2_16TH = 0x2c002c00u;    // half2(1/16)
+constexpr uint32_t H2_NEG64 = 0xd400d400u;   // half2(-64)
+// (a, b) small non-negative integers -> half2(a, b), exact
+__device__ __forceinline__ uint32_t int_pair_h2(uint32_t a, uint32_t b) { return h2sub((a | (b << 16)) | MAGIC, MAGIC); }
+
+// 6-bit (scale, min) of sub-block j from a K-quant header {f16 d, f16 dmin, 12 packed bytes}
+__device__ __forceinline__ void k4_sc_m(const uint4 h, int j, uint32_t& sc, uint32_t& m) {
+    if (j < 4) {
+        sc = (h.y >> (8 * j)) & 63u;
+        m = (h.z >> (8 * j)) & 63u;
+    } else {
+        const int jj = j - 4;
+        sc = ((h.w >> (8 * jj)) & 0xfu) | (((h.y >> (8 * jj + 6)) & 3u) << 4);
+        m = ((h.w >> (8 * jj + 4)) & 0xfu) | (((h.z >> (8 * jj + 6)) & 3u) << 4);
+    }
+}
+
+struct UnitScales {
+    float d, dmin;
+};
+
+template <int DT>
+struct Fmt;
+
+// Q4_K / Q5_K: one unit per stage.  Thread (row, kp) unpacks sub-blocks 2kp (low nibbles) and
+// 2kp + 1 (high nibbles) of its row into r[0..15] / r[16..31]; r[c] = half2 of k-positions 2c, 2c + 1.
+template <int DT>
+struct FmtK45 {
+    static constexpr int STAGE = DT == DFL_Q4_K ? STAGE_Q4_K : STAGE_Q5_K;
+    static constexpr int STAGES = DT == DFL_Q4_K ? 4 : 3;
+    static constexpr int UNITS = 1;
+    static constexpr bool HAS_MIN = true;
+    // MMA step j of a unit multiplies tensor-memory columns [8j, 8j + 8) with 16-column slice j of the block
+    __device__ static __forceinline__ uint32_t b_kstep(int /*unit*/, int j) { return (uint32_t)j; }
+    __device__ static __forceinline__ uint32_t accumulate(int j) { return j > 0 ? 1u : 0u; }
+    __device__ static __forceinline__ void store(uint32_t a_base, int kp, const uint32_t (&r)[32]) { tmem_st32(a_base + 32 * kp, r); }
+    __device__ static __forceinline__ void unpack(const uint8_t* st, int /*unit*/, int row, int kp, uint32_t (&r)[32], uint32_t (&am)[8],
+                                                  UnitScales& us) {
+        const uint4 h = reinterpret_cast<const uint4*>(st)[row];
+        const uint4* qs = reinterpret_cast<const uint4*>(st + TSQ4_OFF_QS);
+        const uint4 qa = qs[(kp * 2 + 0) * 128 + row], qb = qs[(kp * 2 + 1) * 128 + row];
+        us.d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+        us.dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+        uint32_t sc0, m0, sc1, m1;
+        k4_sc_m(h, 2 * kp, sc0, m0);
+        k4_sc_m(h, 2 * kp + 1, sc1, m1);
+        const uint32_t s0 = int_pair_h2(sc0, sc0), s1 = int_pair_h2(sc1, sc1);
+        const uint32_t cml = s0, cal = h2mul(s0, H2_NEG1024);                      // (1024 + q) * sc - 1024 sc
+        const uint32_t cmh = h2mul(s1, H2_16TH), cah = h2mul(s1, H2_NEG64);        // (1024 + 16 q) * sc / 16 - 64 sc
+        const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        if (DT == DFL_Q4_K) {
+#pragma unroll
+            for (int wi = 0; wi < 8; ++wi) {
+                const uint32_t v = w[wi], v8 = v >> 8;
+                r[2 * wi] = h2fma((v & 0x000f000fu) | MAGIC, cml, cal);
+                r[2 * wi + 1] = h2fma((v8 & 0x000f000fu) | MAGIC, cml, cal);
+                r[16 + 2 * wi] = h2fma((v & 0x00f000f0u) | MAGIC, cmh, cah);
+                r[16 + 2 * wi + 1] = h2fma((v8 & 0x00f000f0u) | MAGIC, cmh, cah);
+            }
+        } else {
+            const uint4* qh = reinterpret_cast<const uint4*>(st + TSQ5_OFF_QH);
+            const uint4 ha = qh[row], hb = qh[128 + row];
+            const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+            for (int wi = 0; wi < 8; ++wi) {
+                const uint32_t v = w[wi], v8 = v >> 8, t = hw[wi] >> (2 * kp);
+                r[2 * wi] = h2fma((v & 0x000f000fu) | ((t << 4) & 0x00100010u) | MAGIC, cml, cal);
+                r[2 * wi + 1] = h2fma((v8 & 0x000f000fu) | ((t >> 4) & 0x00100010u) | MAGIC, cml, cal);
+                r[16 + 2 * wi] = h2fma((v & 0x00f000f0u) | ((t << 7) & 0x01000100u) | MAGIC, cmh, cah);
+                r[16 + 2 * wi + 1] = h2fma((v8 & 0x00f000f0u) | ((t >> 1) & 0x01000100u) | MAGIC, cmh, cah);
+            }
+        }
+        if (kp == 0) {
+            // the eight sub-block mins of the row as the 16-wide A operand of the min-term MMA
+            uint32_t m[8], s_unused;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) k4_sc_m(h, j, s_unused, m[j]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                am[j] = int_pair_h2(m[2 * j], m[2 * j + 1]);
+                am[4 + j] = 0u;
+            }
+        }
+    }
+};
+template <>
+struct Fmt<DFL_Q4_K> : FmtK45<DFL_Q4_K> {};
+template <>
+struct Fmt<DFL_Q5_K> : FmtK45<DFL_Q5_K> {};
+
+}  // namespace ts
+
+}  // namespace dfl
+
+#include "gemm_ts_q6k.cuh"
+#include "gemm_ts_kernel.cuh"

@@ -14,7 +14,7 @@ namespace dfl {
 dfl_status use_device(int device);
 dfl_status check_dev_err(cudaStream_t st, int* dev_err);
 dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, const void* data, uint64_t n_bytes, bool on_device,
-                          cudaStream_t st, QMatrix* m);
+                          cudaStream_t st, QMatrix* m, bool allow_ts = false);
 void qmatrix_release(QMatrix* m);
 
 // Several matrices that consume the same activations and write side by side into one

@@ -83,6 +83,13 @@ __host__ __device__ inline int ggml_bytes_per_256(int dtype) {
 }
 __host__ __device__ inline bool dtype_uses_bf16_acts(int dtype) { return dtype == DFL_BF16; }
 
+// Two resident tile layouts / kernels: per-lane MMA fragments for the mma.sync kernel (this file),
+// row-lane tiles for the tensor-memory kernel (gemm_ts.cuh).  The packed activation format
+// follows the kernel that consumes it.
+constexpr int LAYOUT_FRAG = 0, LAYOUT_TS = 1;
+constexpr int ACT_F16 = 0, ACT_BF3 = 1, ACT_TS = 2;
+constexpr int ACTTS_CHUNK = 16384 + 1536;  // tensor-memory kernel: B operand + min-term operand per 256 columns
+
 // position of column k (0..255) inside an activation plane row
 __host__ __device__ inline int act_pos(int k) {
     const int w = k >> 5, s = (k >> 4) & 1, t = (k >> 2) & 3, e = k & 3;
@@ -154,6 +161,7 @@ __device__ __forceinline__ float ggml_decode_elem(int dtype, const uint8_t* seg2
 struct QMatrix {
     int device = 0;
     int dtype = 0;
+    int layout = LAYOUT_FRAG;
     uint64_t n_in = 0, n_out = 0;
     int kblocks = 0;    // n_in / 256
     int row_tiles = 0;  // ceil(n_out / 128)
@@ -195,6 +203,12 @@ dfl_status launch_prep_acts(cudaStream_t st, int weight_dtype, const float* x, i
 inline uint64_t acts_bytes(int weight_dtype, uint64_t k) {
     return (k / TILE_K) * (uint64_t)(dtype_uses_bf16_acts(weight_dtype) ? ACTB3_CHUNK : ACT16_CHUNK);
 }
+inline int act_layout_of(const QMatrix& m) { return m.layout == LAYOUT_TS ? ACT_TS : dtype_uses_bf16_acts(m.dtype) ? ACT_BF3 : ACT_F16; }
+inline int act_chunk_bytes(int act_layout) { return act_layout == ACT_TS ? ACTTS_CHUNK : act_layout == ACT_BF3 ? ACTB3_CHUNK : ACT16_CHUNK; }
+inline uint64_t acts_bytes_for(const QMatrix& m) { return (m.n_in / TILE_K) * (uint64_t)act_chunk_bytes(act_layout_of(m)); }
+// Packs x for the kernel that will consume matrix m.
+dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* x, int ld, int n_rows, float pre_scale, uint8_t* acts,
+                                int* dev_err);
 // Sum split-K partials: y[r][o] = sum_s part[s][r][o], r < n_rows.
 dfl_status launch_reduce_partials(cudaStream_t st, const float* part, int splits, int n_rows, uint64_t n_out,
                                   float* y, int ld_y);
