@@ -234,19 +234,19 @@ __global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* 
 #pragma unroll
         for (int q4 = 0; q4 < PER / 4; ++q4) {
             const int col = col0 + 4 * q4;
-            uint8_t* chunk = acts + (uint64_t)(col >> 8) * (bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
+            uint8_t* chunk = acts + (uint64_t)(col >> 8) * act_chunk_dev(bf3);
             const float quad[4] = {v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]};
-            pack_quad(chunk, bf3 != 0, row, col & 255, quad, over);
+            pack_quad_any(chunk, bf3, row, col & 255, quad, over);
             sum += quad[0] + quad[1] + quad[2] + quad[3];
         }
-        if (!bf3) {
+        if (bf3 != ACT_BF3) {
             // 32-column sub-block sums: 32 / PER lanes each
             constexpr int LANES = 32 / PER;
 #pragma unroll
             for (int o = LANES / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             if ((lane % LANES) == 0) {
-                uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * ACT16_CHUNK;
-                reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[row * 8 + ((col0 & 255) >> 5)] = sum;
+                uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * act_chunk_dev(bf3);
+                store_subsum(chunk, bf3, row, (col0 & 255) >> 5, sum, over);
             }
         }
         if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
@@ -287,7 +287,7 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
 }
 
 dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
-                              const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts, bool bf3,
+                              const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts, int bf3,
                               float* out_f32, int* err) {
     if (g.hd != 128 && g.hd != 256) return fail(DFL_ERR_UNSUPPORTED, "attention: head_dim must be 128 or 256");
     const int n_chunks = (int)((start + (uint32_t)n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK);
@@ -299,10 +299,10 @@ dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q
     DFL_CHECK(s);
     if (acts && n_rows < MAX_ROWS) {
         // rows of absent tokens must read as zero in the next GEMM
-        DFL_CHECK(launch_acts_clear(st, acts, acts_bytes(bf3 ? DFL_BF16 : DFL_Q4_K, (uint64_t)g.n_q * g.hd)));
+        DFL_CHECK(launch_acts_clear(st, acts, (uint64_t)g.n_q * g.hd / TILE_K * (uint64_t)act_chunk_bytes(bf3)));
     }
-    if (g.hd == 128) attn_post_kernel<128><<<dim3((unsigned)g.n_q, (unsigned)n_rows), 32, 0, st>>>(g, partials, n_chunks, gate, start, acts, bf3 ? 1 : 0, out_f32, err);
-    else attn_post_kernel<256><<<dim3((unsigned)g.n_q, (unsigned)n_rows), 32, 0, st>>>(g, partials, n_chunks, gate, start, acts, bf3 ? 1 : 0, out_f32, err);
+    if (g.hd == 128) attn_post_kernel<128><<<dim3((unsigned)g.n_q, (unsigned)n_rows), 32, 0, st>>>(g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
+    else attn_post_kernel<256><<<dim3((unsigned)g.n_q, (unsigned)n_rows), 32, 0, st>>>(g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

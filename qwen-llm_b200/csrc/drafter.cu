@@ -156,24 +156,24 @@ __global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float*
 #pragma unroll
     for (int q4 = 0; q4 < PER / 4; ++q4) {
         const int col = col0 + 4 * q4;
-        uint8_t* chunk = acts + (uint64_t)(col >> 8) * (bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
+        uint8_t* chunk = acts + (uint64_t)(col >> 8) * act_chunk_dev(bf3);
         const float quad[4] = {v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]};
-        pack_quad(chunk, bf3 != 0, row, col & 255, quad, over);
+        pack_quad_any(chunk, bf3, row, col & 255, quad, over);
         sum += quad[0] + quad[1] + quad[2] + quad[3];
     }
-    if (!bf3) {
+    if (bf3 != ACT_BF3) {
         constexpr int LANES = 32 / PER;
 #pragma unroll
         for (int o = LANES / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if ((lane % LANES) == 0)
-            reinterpret_cast<float*>(acts + (uint64_t)(col0 >> 8) * ACT16_CHUNK + 2 * ACT_PLANE)[row * 8 + ((col0 & 255) >> 5)] = sum;
+            store_subsum(acts + (uint64_t)(col0 >> 8) * act_chunk_dev(bf3), bf3, row, (col0 & 255) >> 5, sum, over);
     }
     if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
 }
 
 dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
                                const int32_t* pos_ctx, int ctx_begin, int ctx_len, const float* k_noise, const float* v_noise,
-                               uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts, bool bf3,
+                               uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts, int bf3,
                                int* err) {
     const int n_ctx = ctx_len - ctx_begin;
     const int n_chunks = (n_ctx + n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK;
@@ -184,14 +184,14 @@ dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* 
         if (!set) { DFL_CUDA(cudaFuncSetAttribute(dattn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
         dattn_chunk_kernel<128><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
                                                                                           noise_start, n_rows, causal ? 1 : 0, window, partials);
-        dattn_post_kernel<128><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3 ? 1 : 0, err);
+        dattn_post_kernel<128><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3, err);
     } else if (g.hd == 256) {
         const size_t smem = (size_t)(2 * ATTN_CHUNK * 257 + 8 * 256 + 8 * ATTN_CHUNK) * sizeof(float);
         static bool set = false;
         if (!set) { DFL_CUDA(cudaFuncSetAttribute(dattn_chunk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
         dattn_chunk_kernel<256><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
                                                                                           noise_start, n_rows, causal ? 1 : 0, window, partials);
-        dattn_post_kernel<256><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3 ? 1 : 0, err);
+        dattn_post_kernel<256><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3, err);
     } else {
         return fail(DFL_ERR_UNSUPPORTED, "drafter attention: head_dim must be 128 or 256");
     }
@@ -451,7 +451,7 @@ dfl_status dsession_project_pending(dfl_dsession* ds) {
         p.mode = GLUE_COPY;
         p.x = ds->staging + (uint64_t)(c0 - ds->pending_base) * KH;
         p.ld_x = (int)KH;
-        p.acts = ds->acts_fc; p.bf3 = dtype_uses_bf16_acts(d->fc.mats[0].dtype) ? 1 : 0;
+        p.acts = ds->acts_fc; p.bf3 = act_layout_of(d->fc.mats[0]);
         p.n_rows = (int)nb; p.err = ds->err;
         DFL_CHECK(launch_glue(st, p, KH));
         DFL_CHECK(launch_group(st, d->fc, ds->acts_fc, ds->part, GemmEpilogue{}, ds->err));
@@ -460,7 +460,7 @@ dfl_status dsession_project_pending(dfl_dsession* ds) {
         q.part = ds->part; q.splits = d->fc.splits; q.ld_part = (int)d->fc.total_cols;
         q.mul_w = d->hidden_norm_w;
         q.sumsq = ds->sumsq;
-        q.acts = ds->acts_h; q.bf3 = dtype_uses_bf16_acts(d->layers[0].kv.mats[0].dtype) ? 1 : 0;
+        q.acts = ds->acts_h; q.bf3 = act_layout_of(d->layers[0].kv.mats[0]);
         q.n_rows = (int)nb; q.err = ds->err;
         DFL_CHECK(launch_glue(st, q, H));
         for (uint32_t il = 0; il < c.n_layer; ++il) {
@@ -515,18 +515,18 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start) {
     for (int i = 1; i < n; ++i) ds->pinned_i[i] = c.mask_token_id;
     DFL_CUDA(cudaMemcpyAsync(ds->tokens_dev, ds->pinned_i, n * 4, cudaMemcpyHostToDevice, st));
     DFL_CHECK(launch_embed_rows(st, tgt->embd_dtype, tgt->embd_ggml, H, ds->tokens_dev, n, ds->x, (int)H));
-    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* w, uint8_t* acts, bool bf3) -> dfl_status {
+    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* w, uint8_t* acts, int layout) -> dfl_status {
         GlueParams p;
         p.mode = GLUE_RESID;
         p.part = part; p.splits = splits; p.ld_part = ld_part;
         p.x = ds->x; p.ld_x = (int)H;
         p.mul_w = w;
-        p.acts = acts; p.bf3 = bf3 ? 1 : 0;
+        p.acts = acts; p.bf3 = layout;
         p.sumsq = ds->sumsq;
         p.n_rows = n; p.err = ds->err;
         return launch_glue(st, p, H);
     };
-    auto bf = [](const MatGroup& g) { return dtype_uses_bf16_acts(g.mats[0].dtype); };
+    auto bf = [](const MatGroup& g) { return act_layout_of(g.mats[0]); };
     DFL_CHECK(norm_glue(nullptr, 0, 0, d->layers[0].attn_norm_w, ds->acts_h, bf(d->layers[0].qkv)));
     const AttnGeom g = d->geom((int)c.n_q_heads);
     // context columns an all-SWA layer can see start at the first position >= noise_start - (window - 1)
@@ -553,9 +553,10 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start) {
         p.mode = GLUE_SWIGLU;
         p.part = ds->part; p.splits = L.gate_up.splits; p.ld_part = (int)L.gate_up.total_cols;
         p.swiglu_f = (int)F;
-        const bool down_bf = bf(L.down);
+        const int down_layout = bf(L.down);
+        const bool down_bf = down_layout == ACT_BF3;
         p.pre_scale = down_bf ? 1.0f : 1.0f / 64.0f;
-        p.acts = ds->acts_f; p.bf3 = down_bf ? 1 : 0;
+        p.acts = ds->acts_f; p.bf3 = down_layout;
         p.n_rows = n; p.err = ds->err;
         DFL_CHECK(launch_glue(st, p, F));
         GemmEpilogue ep_down;

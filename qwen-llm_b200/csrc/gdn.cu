@@ -231,21 +231,21 @@ __global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* __
         v[2] = ov.z * scale * nw.z * silu_f(z[2]);
         v[3] = ov.w * scale * nw.w * silu_f(z[3]);
     }
-    uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * (bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
+    uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * act_chunk_dev(bf3);
     bool over = false;
-    pack_quad(chunk, bf3 != 0, tok, col0 & 255, v, over);
-    if (!bf3) {
+    pack_quad_any(chunk, bf3, tok, col0 & 255, v, over);
+    if (bf3 != ACT_BF3) {
         float sum = v[0] + v[1] + v[2] + v[3];
 #pragma unroll
         for (int of = 4; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);
-        if ((lane & 7) == 0) reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[tok * 8 + ((col0 & 255) >> 5)] = sum;
+        if ((lane & 7) == 0) store_subsum(chunk, bf3, tok, (col0 & 255) >> 5, sum, over);
     }
     if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
 }
 
 dfl_status launch_gdn_post(cudaStream_t st, const GdnGeom& g, const float* o, const float* part_z, int splits, int ld_part,
-                           const float* norm_w, int n_rows, uint8_t* acts, bool bf3, int* err) {
-    gdn_post_kernel<<<dim3((unsigned)g.n_v, MAX_ROWS), 32, 0, st>>>(g, o, part_z, splits, ld_part, norm_w, n_rows, acts, bf3 ? 1 : 0, err);
+                           const float* norm_w, int n_rows, uint8_t* acts, int bf3, int* err) {
+    gdn_post_kernel<<<dim3((unsigned)g.n_v, MAX_ROWS), 32, 0, st>>>(g, o, part_z, splits, ld_part, norm_w, n_rows, acts, bf3, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

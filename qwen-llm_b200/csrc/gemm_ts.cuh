@@ -67,6 +67,7 @@ __device__ __forceinline__ void pack_subsum_ts(uint8_t* chunk, int tok, int j, f
     for (int pl = 0; pl < 3; ++pl) {
         const __half h = __float2half_rn(f);
         *reinterpret_cast<__half*>(chunk + ts_bmin_offset(3 * tok + pl, j)) = h;
+        *reinterpret_cast<__half*>(chunk + ts_bmin_offset(3 * tok + pl, j + 8)) = __ushort_as_half((unsigned short)0);  // K padding
         f -= __half2float(h);
     }
 }

@@ -69,14 +69,14 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
     }
     if (p.xn && live) *reinterpret_cast<float4*>(p.xn + (uint64_t)tok * p.ld_xn + col0) = make_float4(v[0], v[1], v[2], v[3]);
     if (p.acts) {
-        uint8_t* chunk = p.acts + (uint64_t)(col0 >> 8) * (p.bf3 ? ACTB3_CHUNK : ACT16_CHUNK);
+        uint8_t* chunk = p.acts + (uint64_t)(col0 >> 8) * act_chunk_dev(p.bf3);
         bool over = false;
-        pack_quad(chunk, p.bf3 != 0, tok, col0 & 255, v, over);
-        if (!p.bf3) {
+        pack_quad_any(chunk, p.bf3, tok, col0 & 255, v, over);
+        if (p.bf3 != ACT_BF3) {
             float sum = v[0] + v[1] + v[2] + v[3];  // 32-column sub-block = eight neighbouring threads
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if ((quad & 7) == 0) reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[tok * 8 + ((col0 & 255) >> 5)] = sum;
+            if ((quad & 7) == 0) store_subsum(chunk, p.bf3, tok, (col0 & 255) >> 5, sum, over);
         }
         if (over) atomicCAS(p.err, 0, DEV_ERR_OVERFLOW);
     }

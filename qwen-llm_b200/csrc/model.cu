@@ -20,7 +20,7 @@ static uint64_t tensor_elems(const dfl_tensor* t) {
 }
 
 dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const std::vector<std::string>& names, uint64_t n_in,
-                       const std::vector<uint64_t>& n_outs, MatGroup* out) {
+                       const std::vector<uint64_t>& n_outs, MatGroup* out, bool allow_ts) {
     out->n_in = n_in;
     out->total_cols = 0;
     size_t i = 0;
@@ -45,7 +45,7 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
         }
         QMatrix qm;
         if (j - i == 1) {
-            DFL_CHECK(qmatrix_create(device, t0->dtype, n_in, rows, t0->data, t0->n_bytes, t0->on_device != 0, st, &qm));
+            DFL_CHECK(qmatrix_create(device, t0->dtype, n_in, rows, t0->data, t0->n_bytes, t0->on_device != 0, st, &qm, allow_ts));
         } else {
             uint8_t* cat = nullptr;
             DFL_CUDA(cudaMalloc(&cat, bytes));
@@ -55,7 +55,7 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
                 cudaMemcpyAsync(cat + off, t->data, t->n_bytes, t->on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st);
                 off += t->n_bytes;
             }
-            dfl_status s = qmatrix_create(device, t0->dtype, n_in, rows, cat, bytes, true, st, &qm);
+            dfl_status s = qmatrix_create(device, t0->dtype, n_in, rows, cat, bytes, true, st, &qm, allow_ts);
             cudaStreamSynchronize(st);
             cudaFree(cat);
             DFL_CHECK(s);
@@ -69,6 +69,7 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
     QMatrix whole;
     whole.row_tiles = 0;
     whole.dtype = out->mats[0].dtype;
+    whole.layout = out->mats[0].layout;
     for (auto& m : out->mats) {
         whole.row_tiles += m.row_tiles;
         if (gemm_max_kblocks_per_cta(m.dtype) < gemm_max_kblocks_per_cta(whole.dtype)) whole.dtype = m.dtype;
@@ -159,7 +160,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         p.part = part; p.splits = splits; p.ld_part = ld_part;
         p.x = sc->x; p.ld_x = (int)H;
         p.mul_w = norm_w;
-        p.acts = sc->acts_h; p.bf3 = 0;
+        p.acts = sc->acts_h; p.bf3 = m->act_layout;
         if (want_xn) { p.xn = sc->xn; p.ld_xn = (int)H; }
         p.sumsq = sc->sumsq;
         p.capture = capture; p.ld_capture = (int)(sc->k_layers * H);
@@ -177,7 +178,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             DFL_CHECK(launch_attn_front(st, ag, true, sc->part, L.qkv.splits, (int)L.qkv.total_cols, L.q_norm_w, L.k_norm_w, start, (int)n,
                                         s->k_cache[ai], s->v_cache[ai], s->kv_f16, sc->q_rot, sc->gate, nullptr));
             DFL_CHECK(launch_attn_verify(st, ag, sc->q_rot, sc->gate, s->k_cache[ai], s->v_cache[ai], s->kv_f16, start, (int)n,
-                                         s->attn_partials, sc->acts_v, false, nullptr, s->err));
+                                         s->attn_partials, sc->acts_v, m->act_layout, nullptr, s->err));
             out_proj = &L.wo;
             ++ai;
         } else {
@@ -192,7 +193,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
                                       L.dt_bias, L.a_log, (int)n, sc->o));
             s->ssm_cur[gi] = cur ^ 1;
             DFL_CHECK(launch_gdn_post(st, gg, sc->o, sc->part + cd, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, L.ssm_norm_w, (int)n,
-                                      sc->acts_v, false, s->err));
+                                      sc->acts_v, m->act_layout, s->err));
             out_proj = &L.w_out;
             ++gi;
         }
@@ -206,7 +207,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             p.part = sc->part; p.splits = L.gate_up.splits; p.ld_part = (int)L.gate_up.total_cols;
             p.swiglu_f = (int)F;
             p.pre_scale = 1.0f / 64.0f;  // keeps silu(g)*u inside the f16 operand range; undone in the GEMM epilogue
-            p.acts = sc->acts_f; p.bf3 = 0;
+            p.acts = sc->acts_f; p.bf3 = m->act_layout;
             p.n_rows = (int)n; p.err = s->err;
             DFL_CHECK(launch_glue(st, p, F));
         }
@@ -277,6 +278,17 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
     }
     auto* m = new dfl_model();
     m->device = device;
+    // One kernel family per model: the tensor-memory GEMM when every 2-D quantised tensor has a
+    // row-lane layout (Q4_K / Q5_K / Q6_K), else the mma.sync kernel for all of them, so that every
+    // packed-activation buffer has a single format.  DFL_GEMM_PATH=legacy forces the latter.
+    bool allow_ts = true;
+    for (uint64_t i = 0; i < n_tensors; ++i)
+        if (tensors[i].n_dims >= 2 && stage_bytes_of(tensors[i].dtype) != 0 && !ts_supported(tensors[i].dtype)) allow_ts = false;
+    {
+        const char* path = getenv("DFL_GEMM_PATH");
+        if (path && std::string(path) == "legacy") allow_ts = false;
+    }
+    m->act_layout = allow_ts ? ACT_TS : ACT_F16;
     m->arch = a;
     cudaStream_t st = 0;
     const uint64_t H = a.hidden_size, F = a.intermediate_size, V = a.vocab_size;
@@ -298,7 +310,7 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
         cudaMemcpy(m->embd_ggml, te->data, te->n_bytes, te->on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice);
         m->embd_dtype = te->dtype;
         const char* head_name = tm.find("output.weight") ? "output.weight" : "token_embd.weight";  // tied embeddings, loader.rs:445
-        MC(build_group(device, st, tm, {head_name}, H, {V}, &m->lm_head));
+        MC(build_group(device, st, tm, {head_name}, H, {V}, &m->lm_head, allow_ts));
         MC(upload_f32(device, st, tm, "output_norm.weight", H, &m->out_norm_w));
         m->verify_weight_bytes = m->lm_head.ggml_bytes();
     }
@@ -311,15 +323,15 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
         if (L.is_attn) {
             ++m->n_attn;
             MC(build_group(device, st, tm, {blk(il, "attn_q.weight"), blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H,
-                           {2 * q_dim, kv_dim, kv_dim}, &L.qkv));
-            MC(build_group(device, st, tm, {blk(il, "attn_output.weight")}, q_dim, {H}, &L.wo));
+                           {2 * q_dim, kv_dim, kv_dim}, &L.qkv, allow_ts));
+            MC(build_group(device, st, tm, {blk(il, "attn_output.weight")}, q_dim, {H}, &L.wo, allow_ts));
             MC(upload_f32(device, st, tm, blk(il, "attn_q_norm.weight"), hd, &L.q_norm_w));
             MC(upload_f32(device, st, tm, blk(il, "attn_k_norm.weight"), hd, &L.k_norm_w));
             m->verify_weight_bytes += L.qkv.ggml_bytes() + L.wo.ggml_bytes();
         } else {
             ++m->n_gdn;
-            MC(build_group(device, st, tm, {blk(il, "attn_qkv.weight"), blk(il, "attn_gate.weight")}, H, {conv_dim, v_dim}, &L.in_qkv_z));
-            MC(build_group(device, st, tm, {blk(il, "ssm_out.weight")}, v_dim, {H}, &L.w_out));
+            MC(build_group(device, st, tm, {blk(il, "attn_qkv.weight"), blk(il, "attn_gate.weight")}, H, {conv_dim, v_dim}, &L.in_qkv_z, allow_ts));
+            MC(build_group(device, st, tm, {blk(il, "ssm_out.weight")}, v_dim, {H}, &L.w_out, allow_ts));
             {
                 float *al = nullptr, *be = nullptr;
                 MC(upload_f32(device, st, tm, blk(il, "ssm_alpha.weight"), H * a.gdn_n_v_heads, &al));
@@ -337,8 +349,8 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
             MC(upload_f32(device, st, tm, blk(il, "ssm_norm.weight"), 128, &L.ssm_norm_w));
             m->verify_weight_bytes += L.in_qkv_z.ggml_bytes() + L.w_out.ggml_bytes() + 2 * H * a.gdn_n_v_heads * 4;
         }
-        MC(build_group(device, st, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up));
-        MC(build_group(device, st, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down));
+        MC(build_group(device, st, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up, allow_ts));
+        MC(build_group(device, st, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down, allow_ts));
         m->verify_weight_bytes += L.gate_up.ggml_bytes() + L.down.ggml_bytes();
     }
 #undef MC
@@ -497,9 +509,10 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
     alloc(&sc->xn, MAX_ROWS * H * 4);
     alloc(&sc->part, part * 4);
     alloc(&sc->sumsq, (H / GLUE_COLS) * MAX_ROWS * 4);
-    alloc(&sc->acts_h, acts_bytes(DFL_Q4_K, H));
-    alloc(&sc->acts_f, acts_bytes(DFL_Q4_K, F));
-    alloc(&sc->acts_v, acts_bytes(DFL_Q4_K, std::max(q_dim, v_dim)));
+    const uint64_t chunk = (uint64_t)std::max(act_chunk_bytes(ACT_F16), act_chunk_bytes(ACT_TS));
+    alloc(&sc->acts_h, H / TILE_K * chunk);
+    alloc(&sc->acts_f, F / TILE_K * chunk);
+    alloc(&sc->acts_v, std::max(q_dim, v_dim) / TILE_K * chunk);
     alloc(&sc->q_rot, MAX_ROWS * q_dim * 4);
     alloc(&sc->gate, MAX_ROWS * q_dim * 4);
     alloc(&sc->o, MAX_ROWS * v_dim * 4);

@@ -37,7 +37,7 @@ struct TensorMap {
 // Builds a MatGroup from named tensors [n_in, n_out]; consecutive tensors of one dtype are
 // concatenated row-wise into one resident matrix (one kernel launch instead of several).
 dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const std::vector<std::string>& names, uint64_t n_in,
-                       const std::vector<uint64_t>& n_outs, MatGroup* out);
+                       const std::vector<uint64_t>& n_outs, MatGroup* out, bool allow_ts = false);
 // Uploads a small tensor as f32 (norm weights, biases, f32 projections); any ggml dtype.
 dfl_status upload_f32(int device, cudaStream_t st, const TensorMap& tm, const std::string& name, uint64_t n_expected, float** out);
 
@@ -62,6 +62,7 @@ struct LayerW {
 
 struct dfl_model {
     int device = 0;
+    int act_layout = dfl::ACT_F16;  // packed-activation format all its GEMMs consume (follows the kernel family)
     dfl_arch arch{};
     std::vector<dfl::LayerW> layers;
     uint8_t* embd_ggml = nullptr;  // token_embd in ggml layout (row gather)

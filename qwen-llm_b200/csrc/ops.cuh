@@ -2,7 +2,7 @@
 // weight-streaming GEMMs of one verify or draft pass.  All of them work on the whole block
 // of <= 16 token rows at once and never touch the host.
 #pragma once
-#include "tiles.cuh"
+#include "gemm_ts.cuh"
 
 namespace dfl {
 
@@ -42,6 +42,17 @@ __device__ __forceinline__ void pack_quad(uint8_t* chunk, bool bf3, int tok, int
             *reinterpret_cast<uint2*>(chunk + p * ACT_PLANE + (tok * ACT_ROW_HALFS + pos) * 2) =
                 make_uint2((uint32_t)b[p][0] | ((uint32_t)b[p][1] << 16), (uint32_t)b[p][2] | ((uint32_t)b[p][3] << 16));
     }
+}
+// Layout-agnostic forms: `layout` is ACT_F16, ACT_BF3 or ACT_TS (the kernel family of the consuming GEMM).
+__device__ __forceinline__ int act_chunk_dev(int layout) { return layout == ACT_TS ? ACTTS_CHUNK : layout == ACT_BF3 ? ACTB3_CHUNK : ACT16_CHUNK; }
+__device__ __forceinline__ void pack_quad_any(uint8_t* chunk, int layout, int tok, int k, const float (&v)[4], bool& overflow) {
+    if (layout == ACT_TS) pack_quad_ts(chunk, tok, k, v, overflow);
+    else pack_quad(chunk, layout == ACT_BF3, tok, k, v, overflow);
+}
+// sum of one token's activations over the 32-column sub-block `sub` (the K-quant "min" term input)
+__device__ __forceinline__ void store_subsum(uint8_t* chunk, int layout, int tok, int sub, float sum, bool& overflow) {
+    if (layout == ACT_F16) reinterpret_cast<float*>(chunk + 2 * ACT_PLANE)[tok * 8 + sub] = sum;
+    else if (layout == ACT_TS) pack_subsum_ts(chunk, tok, sub, sum, overflow);
 }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -112,7 +123,7 @@ dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, con
 // 64-position chunk, then combine, sigmoid gate and activation packing for the o-projection.
 dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
                               const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts,
-                              bool bf3, float* out_f32, int* err);
+                              int act_layout, float* out_f32, int* err);
 uint64_t attn_partials_floats(const AttnGeom& g, uint32_t max_positions);
 
 // ---- gated delta net (gdn.cu) --------------------------------------------------
@@ -129,7 +140,7 @@ dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state
                            int n_rows, float* o);
 // y = rmsnorm(o; eps*hd) * w * silu(z), z = sum of the z-GEMM partials; packs activations for out_proj.
 dfl_status launch_gdn_post(cudaStream_t st, const GdnGeom& g, const float* o, const float* part_z, int splits, int ld_part,
-                           const float* norm_w, int n_rows, uint8_t* acts, bool bf3, int* err);
+                           const float* norm_w, int n_rows, uint8_t* acts, int act_layout, int* err);
 // conv state := last (conv_k-1) rows of {pre-block conv rows, raw qkv rows 0..n_keep-1}
 dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const float* conv_pre, const float* qkv_raw, int n_keep,
                                    float* conv_state);
@@ -138,6 +149,6 @@ dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const floa
 dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
                                const int32_t* pos_ctx, int ctx_begin, int ctx_len, const float* k_noise, const float* v_noise,
                                uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts,
-                               bool bf3, int* err);
+                               int act_layout, int* err);
 
 }  // namespace dfl
