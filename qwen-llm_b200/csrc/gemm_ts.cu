@@ -61,6 +61,18 @@ __global__ void retile_ts_kernel(const uint8_t* __restrict__ src, uint8_t* __res
                 const uint8_t* blk = src + (row * kblocks + kb) * (uint64_t)SRC_BLK + src_off;
 #pragma unroll
                 for (int b = 0; b < 16; ++b) out[b] = blk[b];
+                if (off < TSQ4_OFF_QS) {
+                    // header: d, dmin, then the eight (scale, min) pairs as 12-bit fields, pair j at bit 12 j
+                    uint32_t f[3] = {0, 0, 0};
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t sc, m;
+                        k4_scale_min(blk + 4, j, sc, m);
+                        const uint64_t v = (uint64_t)(sc | (m << 6)) << ((12 * j) & 31);
+                        f[(12 * j) >> 5] |= (uint32_t)v;
+                        if (((12 * j) >> 5) < 2) f[((12 * j) >> 5) + 1] |= (uint32_t)(v >> 32);
+                    }
+                    for (int b = 0; b < 12; ++b) out[4 + b] = (uint8_t)(f[b >> 2] >> (8 * (b & 3)));
+                }
             }
         }
         *reinterpret_cast<uint4*>(stage + off) = *reinterpret_cast<const uint4*>(out);
@@ -99,8 +111,10 @@ __global__ void decode_tiles_ts_kernel(const uint8_t* __restrict__ tiles, int dt
         const uint8_t* h = stage + r * 16;
         const float d = __half2float(__ushort_as_half((unsigned short)(h[0] | (h[1] << 8))));
         const float dmin = __half2float(__ushort_as_half((unsigned short)(h[2] | (h[3] << 8))));
-        uint32_t sc, m;
-        k4_scale_min(h + 4, k >> 5, sc, m);
+        const uint32_t* f = reinterpret_cast<const uint32_t*>(h + 4);
+        const int bit = 12 * (k >> 5);
+        const uint64_t two = (uint64_t)f[bit >> 5] | ((uint64_t)((bit >> 5) < 2 ? f[(bit >> 5) + 1] : 0u) << 32);
+        const uint32_t pair = (uint32_t)(two >> (bit & 31)) & 0xfffu, sc = pair & 63u, m = pair >> 6;
         const int kp = k >> 6, hi = (k >> 5) & 1, l = k & 31;
         const uint8_t byte = stage[TSQ4_OFF_QS + ((kp * 2 + (l >> 4)) * 128 + r) * 16 + (l & 15)];
         uint32_t q = hi ? (byte >> 4) : (byte & 15);
@@ -169,15 +183,21 @@ dfl_status launch_prep_acts_ts(cudaStream_t st, const float* x, int ld, int n_ro
 // ---------------------------------------------------------------------------------------------
 namespace ts {
 
-constexpr int UNPACK_WARPS = 16;
-constexpr int UNPACK_THREADS = UNPACK_WARPS * 32;       // 512: thread = (row = 32 * (warp % 4) + lane, kp = warp / 4)
-constexpr int PRODUCER_WARP = 16, MMA_WARP = 17;
-constexpr int THREADS = (UNPACK_WARPS + 2) * 32;        // 576
-constexpr int KC = 8;                                   // column blocks whose activations stay resident
+constexpr int GROUP_WARPS = 8;                          // unpacking warps per group; thread = (row = 32 * (warp % 4) + lane, kp2)
+constexpr int GROUP_THREADS = GROUP_WARPS * 32;
+constexpr int UNPACK_WARPS = 2 * GROUP_WARPS;
+constexpr int PRODUCER_WARP = 16, MMA_WARP0 = 17, MMA_WARP1 = 18;
+constexpr int THREADS = 19 * 32;                        // 608
+#ifndef DFL_TS_KC
+#define DFL_TS_KC 6
+#endif
+constexpr int KC = DFL_TS_KC;                           // column blocks whose activations stay resident
 
-// tensor-memory columns (32-bit each, 128 lanes): two A buffers of 128 columns (256 f16 per row),
-// two 32-column accumulators, two 8-column A operands and 48-column accumulators of the min term
-constexpr uint32_t TM_A = 0, TM_D = 256, TM_AM = 320, TM_DM = 336, TM_COLS = 512;
+// tensor-memory columns (32-bit each, 128 lanes) of one group: two pass buffers of 64 columns
+// (128 f16 per row), two 32-column accumulators (even / odd MMA steps: two short dependency chains
+// instead of one long one), the 8-column A operand and the 48-column accumulator of the min term;
+// the second group starts 256 columns further
+constexpr uint32_t TM_A = 0, TM_D = 128, TM_AM = 192, TM_DM = 200, TM_GROUP = 256, TM_COLS = 512;
 
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -189,6 +209,12 @@ __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
 }
 __device__ __forceinline__ void tmem_free(uint32_t taddr, uint32_t cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 // mbarrier arrive once every MMA this thread issued before has completed
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
@@ -228,6 +254,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r) : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -241,6 +273,17 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
                  : "memory");
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
     uint32_t r[4];
@@ -274,18 +317,6 @@ constexpr uint32_t H2_NEG64 = 0xd400d400u;   // half2(-64)
 // (a, b) small non-negative integers -> half2(a, b), exact
 __device__ __forceinline__ uint32_t int_pair_h2(uint32_t a, uint32_t b) { return h2sub((a | (b << 16)) | MAGIC, MAGIC); }
 
-// 6-bit (scale, min) of sub-block j from a K-quant header {f16 d, f16 dmin, 12 packed bytes}
-__device__ __forceinline__ void k4_sc_m(const uint4 h, int j, uint32_t& sc, uint32_t& m) {
-    if (j < 4) {
-        sc = (h.y >> (8 * j)) & 63u;
-        m = (h.z >> (8 * j)) & 63u;
-    } else {
-        const int jj = j - 4;
-        sc = ((h.w >> (8 * jj)) & 0xfu) | (((h.y >> (8 * jj + 6)) & 3u) << 4);
-        m = ((h.w >> (8 * jj + 4)) & 0xfu) | (((h.z >> (8 * jj + 6)) & 3u) << 4);
-    }
-}
-
 struct UnitScales {
     float d, dmin;
 };
@@ -293,28 +324,29 @@ struct UnitScales {
 template <int DT>
 struct Fmt;
 
-// Q4_K / Q5_K: one unit per stage.  Thread (row, kp) unpacks sub-blocks 2kp (low nibbles) and
-// 2kp + 1 (high nibbles) of its row into r[0..15] / r[16..31]; r[c] = half2 of k-positions 2c, 2c + 1.
+// Q4_K / Q5_K: two passes of 128 columns per stage.  In pass ps thread (row, kp2) takes the 64
+// columns of kp = 2 ps + kp2: sub-blocks 2kp (low nibbles) and 2kp + 1 (high nibbles) of its row
+// into r[0..15] / r[16..31]; r[c] = half2 of k-positions 2c, 2c + 1.
 template <int DT>
 struct FmtK45 {
     static constexpr int STAGE = DT == DFL_Q4_K ? STAGE_Q4_K : STAGE_Q5_K;
-    static constexpr int STAGES = DT == DFL_Q4_K ? 4 : 3;
-    static constexpr int UNITS = 1;
+    static constexpr int STAGES = KC == 4 ? (DT == DFL_Q4_K ? 7 : 6) : (DT == DFL_Q4_K ? 5 : 4);
+    static constexpr int PASSES = 2;
     static constexpr bool HAS_MIN = true;
-    // MMA step j of a unit multiplies tensor-memory columns [8j, 8j + 8) with 16-column slice j of the block
-    __device__ static __forceinline__ uint32_t b_kstep(int /*unit*/, int j) { return (uint32_t)j; }
-    __device__ static __forceinline__ uint32_t accumulate(int j) { return j > 0 ? 1u : 0u; }
-    __device__ static __forceinline__ void store(uint32_t a_base, int kp, const uint32_t (&r)[32]) { tmem_st32(a_base + 32 * kp, r); }
-    __device__ static __forceinline__ void unpack(const uint8_t* st, int /*unit*/, int row, int kp, uint32_t (&r)[32], uint32_t (&am)[8],
+    // MMA step j of pass ps multiplies pass-buffer columns [8j, 8j + 8) with this 16-column slice of the block
+    __device__ static __forceinline__ uint32_t b_slice(int ps, int j) { return (uint32_t)(8 * ps + j); }
+    __device__ static __forceinline__ void store(uint32_t buf, int kp2, const uint32_t (&r)[32]) { tmem_st32(buf + 32 * kp2, r); }
+    __device__ static __forceinline__ void unpack(const uint8_t* st, int ps, int row, int kp2, uint32_t (&r)[32], uint32_t (&am)[8],
                                                   UnitScales& us) {
+        const int kp = 2 * ps + kp2;
         const uint4 h = reinterpret_cast<const uint4*>(st)[row];
         const uint4* qs = reinterpret_cast<const uint4*>(st + TSQ4_OFF_QS);
         const uint4 qa = qs[(kp * 2 + 0) * 128 + row], qb = qs[(kp * 2 + 1) * 128 + row];
         us.d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
         us.dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-        uint32_t sc0, m0, sc1, m1;
-        k4_sc_m(h, 2 * kp, sc0, m0);
-        k4_sc_m(h, 2 * kp + 1, sc1, m1);
+        // (scale, min) pairs of sub-blocks 2kp and 2kp + 1: 24 bits at bit 24 kp of the 96-bit field h.y, h.z, h.w
+        const uint32_t t = (ps == 0 ? (kp2 ? __funnelshift_r(h.y, h.z, 24) : h.y) : (kp2 ? (h.w >> 8) : __funnelshift_r(h.z, h.w, 16)));
+        const uint32_t sc0 = t & 63u, m0 = (t >> 6) & 63u, sc1 = (t >> 12) & 63u, m1 = (t >> 18) & 63u;
         const uint32_t s0 = int_pair_h2(sc0, sc0), s1 = int_pair_h2(sc1, sc1);
         const uint32_t cml = s0, cal = h2mul(s0, H2_NEG1024);                      // (1024 + q) * sc - 1024 sc
         const uint32_t cmh = h2mul(s1, H2_16TH), cah = h2mul(s1, H2_NEG64);        // (1024 + 16 q) * sc / 16 - 64 sc
@@ -341,17 +373,8 @@ struct FmtK45 {
                 r[16 + 2 * wi + 1] = h2fma((v8 & 0x00f000f0u) | ((t >> 1) & 0x01000100u) | MAGIC, cmh, cah);
             }
         }
-        if (kp == 0) {
-            // the eight sub-block mins of the row as the 16-wide A operand of the min-term MMA
-            uint32_t m[8], s_unused;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) k4_sc_m(h, j, s_unused, m[j]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                am[j] = int_pair_h2(m[2 * j], m[2 * j + 1]);
-                am[4 + j] = 0u;
-            }
-        }
+        // column kp of the min-term A operand: the mins of this thread's two sub-blocks
+        am[0] = int_pair_h2(m0, m1);
     }
 };
 template <>

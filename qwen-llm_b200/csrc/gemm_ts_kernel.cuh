@@ -1,4 +1,17 @@
 // Kernel body and launcher of the tensor-memory few-row GEMM; included by gemm_ts.cu only.
+//
+// CTA = one split (at most KC column blocks, activations resident) x every ctas_per_split-th
+// row tile.  Its work is the sequence of entries e = (tile, column block); the weight stage of
+// entry e travels through ring slot e % STAGES.  Two groups of eight unpacking warps take the
+// entries alternately (group = e & 1), each with its own tensor-memory buffers, MMA-issuing
+// thread and barriers, so that one group's unpacking overlaps the other's waits; the groups
+// meet only at the end of a row tile, where group 1 hands its partial sums to group 0 through
+// shared memory and group 0 writes the tile.
+//
+// Inside a group an entry is processed in PASSES passes of 64 tensor-memory columns (Q4_K/Q5_K:
+// 128 weight columns per pass, Q6_K: 64, twice, as the even/odd scale parts); the two pass
+// buffers alternate, eight MMAs per pass accumulate into the group's single accumulator, which
+// the group reads back while it already holds the next entry's first pass in registers.
 #pragma once
 
 namespace dfl {
@@ -16,52 +29,76 @@ struct Params {
     int* err;
 };
 
+#ifdef DFL_TS_TRACE
+// development build only: SM-clock timestamps of CTA 0, [role][slot]; role 0 = group-0 warp 0, 1 = group-1 warp 8,
+// 2 = MMA thread 0, 3 = MMA thread 1, 4 = producer
+__device__ long long g_ts_trace[5][512];
+#define TS_TRACE(role, slot)                                                                         \
+    do {                                                                                             \
+        if (blockIdx.x == 0 && (slot) < 512) g_ts_trace[role][slot] = clock64();                       \
+    } while (0)
+#else
+#define TS_TRACE(role, slot) do { } while (0)
+#endif
+
+constexpr int XBUF_BYTES = GROUP_THREADS * 8 * 4;   // one tile's partial sums of a group: 8 tokens per thread
+
 template <int DT>
 constexpr int smem_bytes() {
-    return KC * ACTTS_CHUNK + Fmt<DT>::STAGES * Fmt<DT>::STAGE + 256;
+    return KC * ACTTS_CHUNK + Fmt<DT>::STAGES * Fmt<DT>::STAGE + 2 * XBUF_BYTES + 256;
 }
+
+// named barrier 1: start-up of the unpacking warps (every one of them reaches it unconditionally)
+__device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
 template <int DT>
 __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     using F = Fmt<DT>;
-    constexpr int STAGES = F::STAGES, UNITS = F::UNITS;
+    constexpr int STAGES = F::STAGES, PASSES = F::PASSES;
     constexpr int OFF_RING = KC * ACTTS_CHUNK;
-    constexpr int OFF_BAR = OFF_RING + STAGES * F::STAGE;
+    constexpr int OFF_XBUF = OFF_RING + STAGES * F::STAGE;
+    constexpr int OFF_BAR = OFF_XBUF + 2 * XBUF_BYTES;
     static_assert(OFF_BAR + 256 <= 227 * 1024, "shared memory budget");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* acts_res = smem;
     uint8_t* ring = smem + OFF_RING;
+    float* xbuf = reinterpret_cast<float*>(smem + OFF_XBUF);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* empty = full + STAGES;
     uint64_t* acts_bar = empty + STAGES;
-    uint64_t* a_ready = acts_bar + 1;   // [2] the unpacked A operand of a unit is in tensor memory
-    uint64_t* mma_done = a_ready + 2;   // [2] the unit's MMAs have completed
+    uint64_t* a_ready = acts_bar + 1;   // [group][buffer] a pass of unpacked weights is in tensor memory
+    uint64_t* a_free = a_ready + 4;     // [group][buffer] the MMAs of that pass have completed
+    uint64_t* x_full = a_free + 4;      // [tile & 1] group 1 has put its partial sums of the tile into the exchange buffer
+    uint64_t* x_free = x_full + 2;      // [tile & 1] group 0 has read them
     __shared__ uint32_t tmem_slot;
     __shared__ float tok_scale[MAX_ROWS];
     __shared__ int abort_flag;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // warp-uniform by construction
     const int sp = blockIdx.x % p.splits, c = blockIdx.x / p.splits;
     const int kb0 = (int)((long long)sp * p.kblocks / p.splits), kb1 = (int)((long long)(sp + 1) * p.kblocks / p.splits);
     const int n_kb = kb1 - kb0;
     const int n_my = (p.row_tiles - c + p.ctas_per_split - 1) / p.ctas_per_split;   // row tiles c, c + cps, ...
-    const int n_it = n_my * n_kb;            // stages
-    const int n_units = n_it * UNITS;
+    const int n_it = n_my * n_kb;            // entries
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], UNPACK_WARPS);
+            mbar_init(&empty[s], GROUP_WARPS);
         }
         mbar_init(acts_bar, 1);
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(&a_ready[a], UNPACK_WARPS);
-            mbar_init(&mma_done[a], 1);
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&a_ready[i], GROUP_WARPS);
+            mbar_init(&a_free[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&x_full[i], GROUP_WARPS);
+            mbar_init(&x_free[i], GROUP_WARPS);
         }
         abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == MMA_WARP) tmem_alloc(&tmem_slot, TM_COLS);
+    if (warp == MMA_WARP0) tmem_alloc(&tmem_slot, TM_COLS);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -75,15 +112,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
             const uint8_t* wbase = p.w + (uint64_t)kb0 * F::STAGE;
             int pt = 0, pk = 0;
             bool ok = true;
-            for (int it = 0; it < n_it && ok; ++it) {
-                const int s = it % STAGES;
-                if (it >= STAGES) ok = mbar_wait_bounded(&empty[s], ((it / STAGES) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
+            for (int e = 0; e < n_it; ++e) {
+                const int s = e % STAGES;
+                if (e >= STAGES) ok = mbar_wait_bounded(&empty[s], ((e / STAGES) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
                 if (!ok) break;
                 const uint8_t* src = wbase + (uint64_t)(c + pt * p.ctas_per_split) * tile_stride + (uint64_t)pk * F::STAGE;
                 mbar_arrive_expect_tx(&full[s], F::STAGE);
                 bulk_g2s(ring + s * F::STAGE, src, F::STAGE, &full[s]);
+                TS_TRACE(4, e);
                 if (++pk == n_kb) { pk = 0; ++pt; }
-                if (it == (STAGES < n_it ? STAGES : n_it) - 1) {
+                if (e == (STAGES < n_it ? STAGES : n_it) - 1) {
                     // the ring is primed with weights (independent of the previous kernel); now the activations
                     pdl_wait();
                     mbar_arrive_expect_tx(acts_bar, (uint32_t)n_kb * ACTTS_CHUNK);
@@ -93,34 +131,52 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
             }
             if (!ok) abort_flag = 1;
         }
-    } else if (warp == MMA_WARP) {
-        // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0 && n_units > 0) {
-            constexpr uint32_t IDESC_MAIN = instr_desc(32), IDESC_MIN = instr_desc(48);
+    } else if (warp == MMA_WARP0 || warp == MMA_WARP1) {
+        // ------------------------------ MMA issuer of one group ------------------------------
+        // The whole warp walks the loop so that addresses and descriptors stay warp-uniform; one elected
+        // lane issues the instructions.
+        const int g = warp - MMA_WARP0;
+        if (n_it > g) {
+#ifndef DFL_TS_EXP_N
+#define DFL_TS_EXP_N 32
+#endif
+            constexpr uint32_t IDESC_MAIN = instr_desc(DFL_TS_EXP_N), IDESC_MIN = instr_desc(48);
             bool ok = mbar_wait_bounded(acts_bar, 0, p.err, DEV_ERR_WAIT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
             const uint32_t acts_addr = smem_u32(acts_res);
-            int kb = 0, u = 0;
-            for (int i = 0; i < n_units && ok; ++i) {
-                const int a = i & 1;
-                ok = mbar_wait_bounded(&a_ready[a], (i >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
-                if (!ok) break;
-                fence_after_sync();
-                const uint32_t chunk = acts_addr + kb * ACTTS_CHUNK;
-                const uint32_t a_col = tmem + TM_A + a * 128, d_col = tmem + TM_D + a * 32;
+            const uint32_t tm_g = tmem + g * TM_GROUP;
+            uint32_t pc = 0;   // running pass count of this group
+            for (int e = g; e < n_it && ok; e += 2) {
+                const uint32_t chunk = acts_addr + (e % n_kb) * ACTTS_CHUNK;
+#pragma unroll
+                for (int ps = 0; ps < PASSES; ++ps, ++pc) {
+                    const uint32_t b = pc & 1;
+                    if (ok) {
+                        ok = mbar_wait_bounded(&a_ready[2 * g + b], (pc >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+                        ok = __all_sync(0xffffffffu, ok);
+                    }
+                    if (ok) {
+                        if (lane == 0) TS_TRACE(2 + g, 2 * pc);
+                        fence_after_sync();
+                        if (elect_one()) {
 #ifndef DFL_TS_EXP_NOMMA
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint32_t bk = F::b_kstep(u, j);   // which 16-column slice of the block this step multiplies with
-                    mma_ts(d_col, a_col + 8 * j, smem_desc(chunk + bk * 1024, 512, 128), IDESC_MAIN, F::accumulate(j));
-                }
+                            for (int j = 0; j < 8; ++j)
+                                mma_ts(tm_g + TM_D + 32 * (j & 1), tm_g + TM_A + b * 64 + 8 * j,
+                                       smem_desc(chunk + F::b_slice(ps, j) * 1024, 512, 128), IDESC_MAIN, (ps | (j >> 1)) ? 1u : 0u);
 #endif
-                if (F::HAS_MIN) mma_ts(tmem + TM_DM + a * 48, tmem + TM_AM + a * 8, smem_desc(chunk + TS_BMIN_OFF, 768, 128), IDESC_MIN, 0);
-                mma_commit(&mma_done[a]);
-                if (++u == UNITS) { u = 0; if (++kb == n_kb) kb = 0; }
+                            if (F::HAS_MIN && ps == PASSES - 1)   // every pass has stored its column of the min operand by now
+                                mma_ts(tm_g + TM_DM, tm_g + TM_AM, smem_desc(chunk + TS_BMIN_OFF, 768, 128), IDESC_MIN, 0);
+                            mma_commit(&a_free[2 * g + b]);
+                        }
+                        __syncwarp();
+                        if (lane == 0) TS_TRACE(2 + g, 2 * pc + 1);
+                    }
+                }
             }
             if (!ok) abort_flag = 1;
         }
-    } else {
+    } else if (warp < UNPACK_WARPS) {
         // ------------------------------ unpack + drain warps ------------------------------
         pdl_wait();
         if (threadIdx.x < 256) {
@@ -133,96 +189,155 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
             for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             if (part == 0) tok_scale[tok] = p.sumsq ? p.out_scale * (1.0f / sqrtf(ss / p.norm_k + p.eps)) : p.out_scale;
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(UNPACK_THREADS) : "memory");
+        named_sync(1, UNPACK_WARPS * 32);
 
-        const int q4 = warp & 3, kp = warp >> 2;
-        const int row = 32 * q4 + lane;
-        const uint32_t lane_base = tmem + ((uint32_t)(32 * q4) << 16);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        UnitScales us_even{0.f, 0.f}, us_odd{0.f, 0.f};
-        int dkb = 0, du = 0, dtile = 0;   // column block / unit / tile of the next unit to drain
+        const int g = warp >> 3, q4 = warp & 3, kp2 = (warp >> 2) & 1;
+        const int row = 32 * q4 + lane, gtid = threadIdx.x & (GROUP_THREADS - 1);
+        const uint32_t tm_g = tmem + g * TM_GROUP + ((uint32_t)(32 * q4) << 16);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        // K padding of the min-term operand (sub-block index 8..15): written once, never touched again
+        if (F::HAS_MIN && kp2 == 0) tmem_st4(tm_g + TM_AM + 4, 0u, 0u, 0u, 0u);
         bool ok = true;
+        uint32_t pc = 0;            // running pass count of this group
+        int next_close = 0;         // next row tile this group has to close
+        bool pending = false;       // an entry whose accumulator has not been read back yet
+        int pend_tile = 0;
+        bool pend_last = false;
+        UnitScales pend_us{0.f, 0.f};
 
-        // read back unit `i` (accumulators of buffer i & 1), scale and add; write the tile out after its last unit
-        auto drain = [&](int i) {
-            const int a = i & 1;
-            ok = mbar_wait_bounded(&mma_done[a], (i >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+        // hand over (group 1) or finish (group 0) the partial sums of tile t
+        auto close_tile = [&](int t) {
+            float* xb = xbuf + (t & 1) * (XBUF_BYTES / 4) + gtid * 8;
+            const uint32_t use = (uint32_t)t >> 1;   // how often this exchange buffer has been used before
+            if (g == 1) {
+                if (t >= 2) {
+                    ok = mbar_wait_bounded(&x_free[t & 1], (use - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) return;
+                }
+                *reinterpret_cast<float4*>(xb) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(xb + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&x_full[t & 1]);
+            } else {
+                ok = mbar_wait_bounded(&x_full[t & 1], use & 1, p.err, DEV_ERR_WAIT_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) return;
+                const float4 o0 = *reinterpret_cast<const float4*>(xb), o1 = *reinterpret_cast<const float4*>(xb + 4);
+                const float other[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&x_free[t & 1]);
+                const uint32_t orow = (uint32_t)(c + t * p.ctas_per_split) * TILE_R + row;
+                if (orow < p.n_out) {
+                    float* dst = p.out + ((uint64_t)sp * MAX_ROWS + 8 * kp2) * p.ld_out + orow;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dst[(uint64_t)j * p.ld_out] = (acc[j] + other[j]) * tok_scale[8 * kp2 + j];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        };
+        // read back the accumulator of the pending entry (its last pass was pass pc - 1), scale, add
+        auto drain_pending = [&]() {
+            const uint32_t lp = pc - 1;
+            ok = mbar_wait_bounded(&a_free[2 * g + (lp & 1)], (lp >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) return;
             fence_after_sync();
-            float v[8];
-            tmem_ld8(lane_base + TM_D + a * 32 + 8 * kp, v);
-            float s[3][4];
-            if (F::HAS_MIN) {
+            {
+                float v[16], t[8];
+                tmem_ld16(tm_g + TM_D + 16 * kp2, v);        // even MMA steps
+                wait_ld();
 #pragma unroll
-                for (int j = 0; j < 3; ++j) tmem_ld4(lane_base + TM_DM + a * 48 + 12 * kp + 4 * j, s[j]);
+                for (int j = 0; j < 8; ++j) t[j] = v[2 * j] + v[2 * j + 1];
+                tmem_ld16(tm_g + TM_D + 32 + 16 * kp2, v);   // odd MMA steps
+                wait_ld();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = fmaf(pend_us.d, t[j] + (v[2 * j] + v[2 * j + 1]), acc[j]);
             }
-            wait_ld();
-            const UnitScales us = a ? us_odd : us_even;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] = fmaf(us.d, v[2 * j] + v[2 * j + 1], acc[j]);
             if (F::HAS_MIN) {
-                // s[..] flattened = 12 columns: token j -> planes 3j, 3j + 1, 3j + 2
-                const float* f = &s[0][0];
+                float s0[8], s1[8], s2[8];   // 8 tokens x 3 planes, token j = flattened columns 3j .. 3j + 2
+                tmem_ld8(tm_g + TM_DM + 24 * kp2, s0);
+                tmem_ld8(tm_g + TM_DM + 24 * kp2 + 8, s1);
+                tmem_ld8(tm_g + TM_DM + 24 * kp2 + 16, s2);
+                wait_ld();
+                auto col = [&](int i) { return i < 8 ? s0[i] : i < 16 ? s1[i - 8] : s2[i - 16]; };
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[j] = fmaf(-us.dmin, (f[3 * j] + f[3 * j + 1]) + f[3 * j + 2], acc[j]);
+                for (int j = 0; j < 8; ++j) acc[j] = fmaf(-pend_us.dmin, (col(3 * j) + col(3 * j + 1)) + col(3 * j + 2), acc[j]);
             }
-            if (++du == UNITS) {
-                du = 0;
-                if (++dkb == n_kb) {
-                    dkb = 0;
-                    const uint32_t orow = (uint32_t)(c + dtile * p.ctas_per_split) * TILE_R + row;
-                    if (orow < p.n_out) {
-                        float* dst = p.out + ((uint64_t)sp * MAX_ROWS + 4 * kp) * p.ld_out + orow;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) dst[(uint64_t)j * p.ld_out] = acc[j] * tok_scale[4 * kp + j];
-                    }
-                    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-                    ++dtile;
-                }
+            fence_before_sync();
+            pending = false;
+            if (pend_last) {
+                close_tile(pend_tile);   // every earlier tile was closed when this entry was started
+                next_close = pend_tile + 1;
             }
         };
 
-        int u = 0;
-        for (int i = 0; i < n_units; ++i) {
-            const int it = i / UNITS, s = it % STAGES, a = i & 1;
-            if (u == 0) {
-                ok = mbar_wait_bounded(&full[s], (it / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
-            uint32_t r[32], am[8];
-            UnitScales us;
+        for (int e = g; e < n_it && ok; e += 2) {
+            const int s = e % STAGES, tile = e / n_kb;
+            const bool tracer = (warp & 7) == 0 && lane == 0;
+            if (tracer) TS_TRACE(g, 16 * (e >> 1));
+            ok = mbar_wait_bounded(&full[s], (e / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
+            if (tracer) TS_TRACE(g, 16 * (e >> 1) + 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint8_t* st = ring + s * F::STAGE;
+            UnitScales us{0.f, 0.f};
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ++ps, ++pc) {
+                uint32_t r[32], am[8];
+                if (ok) {
 #ifndef DFL_TS_EXP_NOUNPACK
-            F::unpack(ring + s * F::STAGE, u, row, kp, r, am, us);
+                    F::unpack(st, ps, row, kp2, r, am, us);
 #else
-            us.d = us.dmin = 0.f;
 #pragma unroll
-            for (int q = 0; q < 32; ++q) r[q] = 0u;
+                    for (int q = 0; q < 32; ++q) r[q] = 0u;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) am[q] = 0u;
+                    for (int q = 0; q < 8; ++q) am[q] = 0u;
 #endif
-            if (i >= 2) {
-                drain(i - 2);
-                if (!ok) break;
+                }
+                if (tracer) TS_TRACE(g, 16 * (e >> 1) + 2 + 3 * ps);
+                if (ok && ps == 0) {
+                    if (pending) drain_pending();
+                    if (tracer) TS_TRACE(g, 16 * (e >> 1) + 14);
+                    // tiles in which this group had no entry carry no partial sums of its own
+                    while (ok && next_close < tile) close_tile(next_close++);
+                }
+                const uint32_t b = pc & 1;
+                // The pass buffer was last read by pass pc - 2.  If that pass belongs to the previous entry, the
+                // read-back above (or, for this group's first entries, nothing) already waited for it.
+                if (ok && ps >= 2) {
+                    ok = mbar_wait_bounded(&a_free[2 * g + b], ((pc >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (ok) fence_after_sync();
+                }
+                if (tracer) TS_TRACE(g, 16 * (e >> 1) + 3 + 3 * ps);
+                if (ok) {
+                    F::store(tm_g + TM_A + b * 64, kp2, r);
+                    if (F::HAS_MIN) tmem_st1(tm_g + TM_AM + 2 * ps + kp2, am[0]);
+                    wait_st();
+                    fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&a_ready[2 * g + b]);
+                        if (ps == PASSES - 1) mbar_arrive(&empty[s]);
+                    }
+                    if (tracer) TS_TRACE(g, 16 * (e >> 1) + 4 + 3 * ps);
+                }
             }
-            if (a) us_odd = us; else us_even = us;
-#ifndef DFL_TS_EXP_NOSTORE
-            F::store(lane_base + TM_A + a * 128, kp, r);
-#endif
-            if (F::HAS_MIN && kp == 0) tmem_st8(lane_base + TM_AM + a * 8, am);
-            wait_st();
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&a_ready[a]);
-                if (u == UNITS - 1) mbar_arrive(&empty[s]);
-            }
-            if (++u == UNITS) u = 0;
+            if (!ok) break;
+            pending = true;
+            pend_tile = tile;
+            pend_last = e + 2 >= (tile + 1) * n_kb;   // this group's last entry of the tile
+            pend_us = us;
         }
-        if (ok && n_units >= 2) drain(n_units - 2);
-        if (ok && n_units >= 1) drain(n_units - 1);
-        if (!ok) abort_flag = 1;
+        if (ok && pending) drain_pending();
+        while (ok && next_close < n_my) close_tile(next_close++);
+        if (!ok) {
+            abort_flag = 1;
+        }
     }
 
     fence_before_sync();
@@ -238,7 +353,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
         while (!mbar_try_wait(acts_bar, 0) && ++spins < (1u << 16)) __nanosleep(100);
     }
     __syncthreads();
-    if (warp == MMA_WARP) {
+    if (warp == MMA_WARP0) {
         fence_after_sync();
         tmem_free(tmem, TM_COLS);
     }
@@ -326,3 +441,9 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
 }
 
 }  // namespace dfl
+
+#ifdef DFL_TS_TRACE
+extern "C" int dfl_ts_trace_read(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, dfl::ts::g_ts_trace, sizeof(long long) * 5 * 512);
+}
+#endif
