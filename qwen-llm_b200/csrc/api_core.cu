@@ -10,6 +10,14 @@ namespace dfl {
 static thread_local std::string t_last_error;
 std::atomic<uint64_t> g_launches{0};
 
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("DFL_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 void set_error(const std::string& msg) { t_last_error = msg; }
 dfl_status fail(dfl_status st, const std::string& msg) {
     t_last_error = msg;

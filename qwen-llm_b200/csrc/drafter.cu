@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(256) dattn_chunk_kernel(AttnGeom g, const floa
                                                           int n_ctx, const float* __restrict__ k_noise, const float* __restrict__ v_noise,
                                                           uint32_t noise_start, int n_rows, int causal, uint32_t window,
                                                           float* __restrict__ partials) {
+    pdl_prologue();
     extern __shared__ float sm[];
     constexpr int LD = HD + 1;
     float* ks = sm;
@@ -125,6 +126,7 @@ __global__ void __launch_bounds__(256) dattn_chunk_kernel(AttnGeom g, const floa
 template <int HD>
 __global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float* __restrict__ partials, int n_chunks, int n_rows, uint8_t* acts,
                                                         int bf3, int* err) {
+    pdl_prologue();
     constexpr int PER = HD / 32;
     const int qh = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
     const int group = g.n_q / g.n_kv, kvh = qh / group, qi = row * group + qh % group;
@@ -182,16 +184,16 @@ dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* 
         const size_t smem = (size_t)(2 * ATTN_CHUNK * 129 + 8 * 128 + 8 * ATTN_CHUNK) * sizeof(float);
         static bool set = false;
         if (!set) { DFL_CUDA(cudaFuncSetAttribute(dattn_chunk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-        dattn_chunk_kernel<128><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
+        launch_k(dattn_chunk_kernel<128>, dim3(dim3((unsigned)n_chunks, (unsigned)g.n_kv)), dim3(256), smem, st, g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
                                                                                           noise_start, n_rows, causal ? 1 : 0, window, partials);
-        dattn_post_kernel<128><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3, err);
+        launch_k(dattn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, MAX_ROWS)), dim3(32), 0, st, g, partials, n_chunks, n_rows, acts, bf3, err);
     } else if (g.hd == 256) {
         const size_t smem = (size_t)(2 * ATTN_CHUNK * 257 + 8 * 256 + 8 * ATTN_CHUNK) * sizeof(float);
         static bool set = false;
         if (!set) { DFL_CUDA(cudaFuncSetAttribute(dattn_chunk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-        dattn_chunk_kernel<256><<<dim3((unsigned)n_chunks, (unsigned)g.n_kv), 256, smem, st>>>(g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
+        launch_k(dattn_chunk_kernel<256>, dim3(dim3((unsigned)n_chunks, (unsigned)g.n_kv)), dim3(256), smem, st, g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise,
                                                                                           noise_start, n_rows, causal ? 1 : 0, window, partials);
-        dattn_post_kernel<256><<<dim3((unsigned)g.n_q, MAX_ROWS), 32, 0, st>>>(g, partials, n_chunks, n_rows, acts, bf3, err);
+        launch_k(dattn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, MAX_ROWS)), dim3(32), 0, st, g, partials, n_chunks, n_rows, acts, bf3, err);
     } else {
         return fail(DFL_ERR_UNSUPPORTED, "drafter attention: head_dim must be 128 or 256");
     }

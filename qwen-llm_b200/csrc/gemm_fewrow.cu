@@ -792,6 +792,7 @@ dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* 
 
 __global__ void reduce_partials_kernel(const float* __restrict__ part, int splits, int n_rows, uint64_t n_out, float* __restrict__ y,
                                        int ld_y) {
+    pdl_prologue();
     const uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int r = blockIdx.y;
     if (o >= n_out || r >= n_rows) return;
@@ -802,7 +803,7 @@ __global__ void reduce_partials_kernel(const float* __restrict__ part, int split
 
 dfl_status launch_reduce_partials(cudaStream_t st, const float* part, int splits, int n_rows, uint64_t n_out, float* y, int ld_y) {
     dim3 grid((unsigned)((n_out + 255) / 256), (unsigned)n_rows);
-    reduce_partials_kernel<<<grid, 256, 0, st>>>(part, splits, n_rows, n_out, y, ld_y);
+    launch_k(reduce_partials_kernel, dim3(grid), dim3(256), 0, st, part, splits, n_rows, n_out, y, ld_y);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -853,6 +854,7 @@ __device__ __forceinline__ Top2 top2_block_reduce(Top2 a) {
 __device__ __forceinline__ float key_to_float(int32_t k) { return __int_as_float(k < 0 ? (k ^ 0x7fffffff) : k); }
 
 __global__ void argmax_part_kernel(const float* __restrict__ logits, uint64_t vocab, uint64_t ld, Top2* __restrict__ parts) {
+    pdl_prologue();
     const int row = blockIdx.y, part = blockIdx.x;
     const uint64_t per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
     const uint64_t lo = part * per, hi = lo + per < vocab ? lo + per : vocab;
@@ -867,6 +869,7 @@ __global__ void argmax_part_kernel(const float* __restrict__ logits, uint64_t vo
     if (threadIdx.x == 0) parts[row * ARGMAX_PARTS + part] = a;
 }
 __global__ void argmax_final_kernel(const Top2* __restrict__ parts, int32_t* __restrict__ argmax, float* __restrict__ gap) {
+    pdl_prologue();
     const int row = blockIdx.x;
     Top2 a = threadIdx.x < ARGMAX_PARTS ? parts[row * ARGMAX_PARTS + threadIdx.x] : Top2{INT32_MIN, INT32_MAX, INT32_MIN, 0};
     a = top2_block_reduce(a);
@@ -884,8 +887,8 @@ __global__ void argmax_final_kernel(const Top2* __restrict__ parts, int32_t* __r
 dfl_status launch_argmax_top2(cudaStream_t st, const float* logits, int n_rows, uint64_t vocab, uint64_t ld, int32_t* argmax,
                               float* gap, void* scratch) {
     if (n_rows < 1 || vocab == 0) return fail(DFL_ERR_BAD_SHAPE, "argmax: shape");
-    argmax_part_kernel<<<dim3(ARGMAX_PARTS, n_rows), 256, 0, st>>>(logits, vocab, ld, reinterpret_cast<Top2*>(scratch));
-    argmax_final_kernel<<<n_rows, 64, 0, st>>>(reinterpret_cast<const Top2*>(scratch), argmax, gap);
+    launch_k(argmax_part_kernel, dim3(dim3(ARGMAX_PARTS, n_rows)), dim3(256), 0, st, logits, vocab, ld, reinterpret_cast<Top2*>(scratch));
+    launch_k(argmax_final_kernel, dim3(n_rows), dim3(64), 0, st, reinterpret_cast<const Top2*>(scratch), argmax, gap);
     count_launch(2);
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -80,5 +80,6 @@ dfl_status launch_prep_acts_ts(cudaStream_t st, const float* x, int ld, int n_ro
 dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits, const GemmEpilogue& ep,
                           int* dev_err, bool pdl, uint32_t ld_out);
 int gemm_ts_choose_splits(const QMatrix& m);
+int gemm_ts_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks);
 
 }  // namespace dfl

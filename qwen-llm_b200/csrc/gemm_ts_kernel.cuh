@@ -396,16 +396,25 @@ static int ctas_per_split(int row_tiles, int splits) {
 // and a per-launch overhead measured in stage times).
 int gemm_ts_choose_splits(const QMatrix& m) {
     const int tiles = m.row_tiles > 0 ? m.row_tiles : 1;
-    const int s_min = (m.kblocks + ts::KC - 1) / ts::KC;
-    int s_max = m.kblocks < 24 ? m.kblocks : 24;
+    return gemm_ts_choose_splits_multi(&tiles, 1, m.kblocks);
+}
+// Several matrices that share their input and their partial buffer are launched one after the other
+// with one common split count: minimise the sum of their longest-CTA times.
+int gemm_ts_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks) {
+    const int s_min = (kblocks + ts::KC - 1) / ts::KC;
+    int s_max = kblocks < 24 ? kblocks : 24;
     if (s_max < s_min) s_max = s_min;
     int best = s_min;
     double best_cost = 1e30;
     for (int s = s_min; s <= s_max; ++s) {
-        const int cps = ts::ctas_per_split(tiles, s);
-        const int rounds = (tiles + cps - 1) / cps;
-        const double unit = (double)((m.kblocks + s - 1) / s) + 0.25;
-        const double cost = rounds * unit + 3.0 + 0.05 * s;
+        double cost = 0.0;
+        for (int i = 0; i < n_mats; ++i) {
+            const int tiles = row_tiles[i] > 0 ? row_tiles[i] : 1;
+            cost += 0.05 * s + 0.0054 * s * tiles;   // partial slices to write and to sum again
+            const int cps = ts::ctas_per_split(tiles, s);
+            const int rounds = (tiles + cps - 1) / cps;
+            cost += rounds * ((double)((kblocks + s - 1) / s) + 0.25);
+        }
         if (cost < best_cost) { best_cost = cost; best = s; }
     }
     return best;

@@ -13,6 +13,7 @@ namespace dfl {
 // grid = k / 64, block 256: thread = (token = tid / 16, four consecutive columns).  One float4 per
 // split per thread keeps every global load of the kernel independent (one latency round).
 __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
+    pdl_prologue();
     const int cb = blockIdx.x, tok = threadIdx.x >> 4, quad = threadIdx.x & 15;
     const int col0 = cb * GLUE_COLS + quad * 4;
     const bool live = tok < p.n_rows;
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
 
 dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k) {
     if (k == 0 || k % TILE_K) return fail(DFL_ERR_BAD_SHAPE, "glue: column count must be a positive multiple of 256");
-    glue_kernel<<<(unsigned)(k / GLUE_COLS), 256, 0, st>>>(p);
+    launch_k(glue_kernel, dim3((unsigned)(k / GLUE_COLS)), dim3(256), 0, st, p);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -93,6 +94,7 @@ dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k) {
 // ---- embedding rows ---------------------------------------------------------------
 __global__ void embed_rows_kernel(int dtype, const uint8_t* __restrict__ ggml, uint64_t h, const int32_t* __restrict__ tokens,
                                   float* __restrict__ x, int ld) {
+    pdl_prologue();
     const int tok = blockIdx.y;
     const uint64_t col = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (col >= h) return;
@@ -104,7 +106,7 @@ __global__ void embed_rows_kernel(int dtype, const uint8_t* __restrict__ ggml, u
 dfl_status launch_embed_rows(cudaStream_t st, int dtype, const uint8_t* ggml, uint64_t h, const int32_t* tokens, int n_rows,
                              float* x, int ld) {
     if (h % 256 || ggml_bytes_per_256(dtype) == 0) return fail(DFL_ERR_UNSUPPORTED, "embed_rows: dtype or width");
-    embed_rows_kernel<<<dim3((unsigned)((h + 255) / 256), (unsigned)n_rows), 256, 0, st>>>(dtype, ggml, h, tokens, x, ld);
+    launch_k(embed_rows_kernel, dim3(dim3((unsigned)((h + 255) / 256), (unsigned)n_rows)), dim3(256), 0, st, dtype, ggml, h, tokens, x, ld);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -117,6 +119,7 @@ __global__ void __launch_bounds__(512) small_matmul_kernel(const float* __restri
                                                            int n_rows, uint64_t k, const float* __restrict__ sumsq, int n_sumsq,
                                                            float norm_k, float eps, float out_scale, float* __restrict__ out,
                                                            int ld_out) {
+    pdl_prologue();
     const int j = blockIdx.x;
     float acc[MAX_ROWS];
 #pragma unroll
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(512) small_matmul_kernel(const float* __restri
 dfl_status launch_small_matmul(cudaStream_t st, const float* w, const float* xn, int ld_xn, int n_rows, uint64_t k, int n_out,
                                const GemmEpilogue& ep, float* out, int ld_out) {
     if (k % 4) return fail(DFL_ERR_BAD_SHAPE, "small_matmul: k must be a multiple of 4");
-    small_matmul_kernel<<<n_out, 512, 0, st>>>(w, xn, ld_xn, n_rows, k, ep.sumsq, ep.n_sumsq, ep.norm_k, ep.eps, ep.out_scale, out,
+    launch_k(small_matmul_kernel, dim3(n_out), dim3(512), 0, st, w, xn, ld_xn, n_rows, k, ep.sumsq, ep.n_sumsq, ep.norm_k, ep.eps, ep.out_scale, out,
                                                ld_out);
     count_launch();
     DFL_CUDA(cudaGetLastError());

@@ -9,7 +9,7 @@ namespace dfl {
 
 dfl_status launch_group(cudaStream_t st, const MatGroup& g, const uint8_t* acts, float* part, const GemmEpilogue& ep, int* err) {
     for (size_t i = 0; i < g.mats.size(); ++i)
-        DFL_CHECK(launch_gemm_fewrow(st, g.mats[i], acts, part + g.col_off[i], g.splits, ep, err, false, g.total_cols));
+        DFL_CHECK(launch_gemm_fewrow(st, g.mats[i], acts, part + g.col_off[i], g.splits, ep, err, pdl_enabled(), g.total_cols));
     return DFL_OK;
 }
 
@@ -75,7 +75,13 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
         if (gemm_max_kblocks_per_cta(m.dtype) < gemm_max_kblocks_per_cta(whole.dtype)) whole.dtype = m.dtype;
     }
     whole.kblocks = (int)(n_in / 256);
-    out->splits = gemm_choose_splits(whole);
+    if (whole.layout == LAYOUT_TS) {
+        std::vector<int> tiles;
+        for (auto& m : out->mats) tiles.push_back(m.row_tiles);
+        out->splits = gemm_ts_choose_splits_multi(tiles.data(), (int)tiles.size(), whole.kblocks);
+    } else {
+        out->splits = gemm_choose_splits(whole);
+    }
     return DFL_OK;
 }
 
