@@ -193,7 +193,7 @@ def run_c1(args, rank, world, device):
         "config": {"workload": "c1: 16x4096 . Q4_K 4096x4096 -> Q6_K 4096x32000 head, greedy prefix accept, 5 tok/step",
                    "l2": f"{n_rep} weight replicas cycled (468 MB > L2)", "parallelism": f"dp{world} independent sequences"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemm_fewrow_kernel (both GEMMs of the step)",
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "few-row GEMM (gemm_ts_kernel Q4_K + Q6_K head; both GEMMs of the step)",
                      "algorithmic_bytes_per_step": C1_BYTES},
         "e2e": {"value": emitted_per_step * args.steps * world / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int(x.nbytes + draft.nbytes), "d2h_bytes_per_step": int(C1_N * 8)},

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* 
             pack_quad_any(chunk, bf3, row, col & 255, quad, over);
             sum += quad[0] + quad[1] + quad[2] + quad[3];
         }
-        if (bf3 != ACT_BF3) {
+        if ((bf3 == ACT_F16 || bf3 == ACT_TS)) {
             // 32-column sub-block sums: 32 / PER lanes each
             constexpr int LANES = 32 / PER;
 #pragma unroll

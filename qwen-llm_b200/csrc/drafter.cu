@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float*
         pack_quad_any(chunk, bf3, row, col & 255, quad, over);
         sum += quad[0] + quad[1] + quad[2] + quad[3];
     }
-    if (bf3 != ACT_BF3) {
+    if ((bf3 == ACT_F16 || bf3 == ACT_TS)) {
         constexpr int LANES = 32 / PER;
 #pragma unroll
         for (int o = LANES / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -285,7 +285,7 @@ dfl_status dfl_drafter_create(const dfl_model* target, const dfl_dflash_config* 
         s = (expr);                   \
         if (s != DFL_OK) goto failed; \
     } while (0)
-    DC(build_group(dev, 0, tm, {"dflash_fc.weight"}, KH, {H}, &d->fc));
+    DC(build_group(dev, 0, tm, {"dflash_fc.weight"}, KH, {H}, &d->fc, true));
     DC(upload_f32(dev, 0, tm, "dflash_hidden_norm.weight", H, &d->hidden_norm_w));
     DC(upload_f32(dev, 0, tm, "output_norm.weight", H, &d->out_norm_w));
     d->weight_bytes = d->fc.ggml_bytes();
@@ -297,11 +297,11 @@ dfl_status dfl_drafter_create(const dfl_model* target, const dfl_dflash_config* 
         DC(upload_f32(dev, 0, tm, blk(il, "post_attention_norm.weight"), H, &L.post_norm_w));
         DC(upload_f32(dev, 0, tm, blk(il, "attn_q_norm.weight"), c.head_dim, &L.q_norm_w));
         DC(upload_f32(dev, 0, tm, blk(il, "attn_k_norm.weight"), c.head_dim, &L.k_norm_w));
-        DC(build_group(dev, 0, tm, {blk(il, "attn_q.weight"), blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H, {q_dim, kv_dim, kv_dim}, &L.qkv));
-        DC(build_group(dev, 0, tm, {blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H, {kv_dim, kv_dim}, &L.kv));
-        DC(build_group(dev, 0, tm, {blk(il, "attn_output.weight")}, q_dim, {H}, &L.wo));
-        DC(build_group(dev, 0, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up));
-        DC(build_group(dev, 0, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down));
+        DC(build_group(dev, 0, tm, {blk(il, "attn_q.weight"), blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H, {q_dim, kv_dim, kv_dim}, &L.qkv, true));
+        DC(build_group(dev, 0, tm, {blk(il, "attn_k.weight"), blk(il, "attn_v.weight")}, H, {kv_dim, kv_dim}, &L.kv, true));
+        DC(build_group(dev, 0, tm, {blk(il, "attn_output.weight")}, q_dim, {H}, &L.wo, true));
+        DC(build_group(dev, 0, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up, true));
+        DC(build_group(dev, 0, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down, true));
         d->weight_bytes += L.qkv.ggml_bytes() + L.wo.ggml_bytes() + L.gate_up.ggml_bytes() + L.down.ggml_bytes();
     }
 #undef DC
@@ -556,7 +556,7 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start) {
         p.part = ds->part; p.splits = L.gate_up.splits; p.ld_part = (int)L.gate_up.total_cols;
         p.swiglu_f = (int)F;
         const int down_layout = bf(L.down);
-        const bool down_bf = down_layout == ACT_BF3;
+        const bool down_bf = down_layout == ACT_BF3 || down_layout == ACT_TSB;
         p.pre_scale = down_bf ? 1.0f : 1.0f / 64.0f;
         p.acts = ds->acts_f; p.bf3 = down_layout;
         p.n_rows = n; p.err = ds->err;

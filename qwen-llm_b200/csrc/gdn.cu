@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* __
     uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * act_chunk_dev(bf3);
     bool over = false;
     pack_quad_any(chunk, bf3, tok, col0 & 255, v, over);
-    if (bf3 != ACT_BF3) {
+    if ((bf3 == ACT_F16 || bf3 == ACT_TS)) {
         float sum = v[0] + v[1] + v[2] + v[3];
 #pragma unroll
         for (int of = 4; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);

@@ -602,7 +602,10 @@ static int ctas_per_split(int row_tiles, int splits) {
 // minimises the longest CTA (rounds of row tiles x column blocks per split, plus a per-tile
 // epilogue and a per-launch prologue measured in stage times).
 int gemm_choose_splits(const QMatrix& m) {
-    if (m.layout == LAYOUT_TS) return gemm_ts_choose_splits(m);
+    if (m.layout == LAYOUT_TS) {
+        const int tiles = m.row_tiles;
+        return m.dtype == DFL_BF16 ? gemm_tsb_choose_splits_multi(&tiles, 1, m.kblocks) : gemm_ts_choose_splits(m);
+    }
     const int tiles = m.row_tiles > 0 ? m.row_tiles : 1;
     const int kc = gemm_max_kblocks_per_cta(m.dtype);
     const int s_min = (m.kblocks + kc - 1) / kc;
@@ -664,13 +667,14 @@ dfl_status launch_gemm_fewrow(cudaStream_t st, const QMatrix& m, const uint8_t* 
                               const GemmEpilogue& ep, int* dev_err, bool pdl, uint32_t ld_out) {
     if (splits < 1 || splits > m.kblocks) return fail(DFL_ERR_BAD_ARG, "gemm: bad split count");
     if (m.layout == LAYOUT_TS) {
-        if (!g_timing) return launch_gemm_ts(st, m, acts, out, splits, ep, dev_err, pdl, ld_out);
+        auto* launch = m.dtype == DFL_BF16 ? launch_gemm_tsb : launch_gemm_ts;
+        if (!g_timing) return launch(st, m, acts, out, splits, ep, dev_err, pdl, ld_out);
         TimedLaunch t{};
         t.bytes = m.ggml_bytes();
         DFL_CUDA(cudaEventCreate(&t.e0));
         DFL_CUDA(cudaEventCreate(&t.e1));
         DFL_CUDA(cudaEventRecord(t.e0, st));
-        dfl_status rc = launch_gemm_ts(st, m, acts, out, splits, ep, dev_err, pdl, ld_out);
+        dfl_status rc = launch(st, m, acts, out, splits, ep, dev_err, pdl, ld_out);
         DFL_CUDA(cudaEventRecord(t.e1, st));
         g_timed.push_back(t);
         return rc;
@@ -786,6 +790,7 @@ dfl_status launch_prep_acts(cudaStream_t st, int weight_dtype, const float* x, i
 
 dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* x, int ld, int n_rows, float pre_scale, uint8_t* acts,
                                 int* dev_err) {
+    if (m.layout == LAYOUT_TS && m.dtype == DFL_BF16) return launch_prep_acts_tsb(st, x, ld, n_rows, m.n_in, pre_scale, acts);
     if (m.layout == LAYOUT_TS) return launch_prep_acts_ts(st, x, ld, n_rows, m.n_in, pre_scale, acts, dev_err);
     return launch_prep_acts(st, m.dtype, x, ld, n_rows, m.n_in, pre_scale, acts, dev_err);
 }

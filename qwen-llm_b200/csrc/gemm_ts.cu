@@ -25,6 +25,8 @@ namespace dfl {
 // Q6_K packing lives in gemm_ts_q6k.cuh (included further down, after the primitives it uses)
 __global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks);
 __device__ float decode_ts_q6k_elem(const uint8_t* stage, int r, int k);
+__global__ void retile_tsb_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_in, uint64_t n_out, int kblocks);
+__device__ float decode_tsb_elem(const uint8_t* stage, int r, int k);
 
 // ---------------------------------------------------------------------------------------------
 // Re-tiling into row-lane tiles and the inverse decode.
@@ -89,6 +91,7 @@ dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev,
         case DFL_Q4_K: retile_ts_kernel<DFL_Q4_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
         case DFL_Q5_K: retile_ts_kernel<DFL_Q5_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
         case DFL_Q6_K: retile_ts_q6k_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
+        case DFL_BF16: retile_tsb_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_in, n_out, kblocks); break;
         default: return fail(DFL_ERR_UNSUPPORTED, "retile: dtype has no row-lane tile layout");
     }
     count_launch();
@@ -122,6 +125,8 @@ __global__ void decode_tiles_ts_kernel(const uint8_t* __restrict__ tiles, int dt
         v = __fsub_rn(__fmul_rn(d * (float)sc, (float)q), dmin * (float)m);
     } else if (dtype == DFL_Q6_K) {
         v = decode_ts_q6k_elem(stage, r, k);
+    } else if (dtype == DFL_BF16) {
+        v = decode_tsb_elem(stage, r, k);
     }
     out[idx] = v;
 }
@@ -387,4 +392,5 @@ struct Fmt<DFL_Q5_K> : FmtK45<DFL_Q5_K> {};
 }  // namespace dfl
 
 #include "gemm_ts_q6k.cuh"
+#include "gemm_tsb.cuh"
 #include "gemm_ts_kernel.cuh"

@@ -20,6 +20,8 @@
 // the activations over each 32-column sub-block as an exact three-way f16 split, K padded from 8
 // to 16 with zeros (the second k-core is never written after the buffer was cleared).
 #pragma once
+#include <cuda_bf16.h>
+
 #include "tiles.cuh"
 
 namespace dfl {
@@ -39,7 +41,9 @@ __host__ __device__ inline int ts_act_kpos(int k) { return (k & ~3) + (((k & 1) 
 __host__ __device__ inline int ts_b_offset(int n, int kpos) { return (kpos >> 3) * 512 + (n >> 3) * 128 + (n & 7) * 16 + (kpos & 7) * 2; }
 __host__ __device__ inline int ts_bmin_offset(int n2, int j) { return TS_BMIN_OFF + (j >> 3) * 768 + (n2 >> 3) * 128 + (n2 & 7) * 16 + (j & 7) * 2; }
 
-inline bool ts_supported(int dtype) { return dtype == DFL_Q4_K || dtype == DFL_Q5_K || dtype == DFL_Q6_K; }
+inline bool ts_supported(int dtype) { return dtype == DFL_Q4_K || dtype == DFL_Q5_K || dtype == DFL_Q6_K || dtype == DFL_BF16; }
+// bf16-weight operand (gemm_tsb.cuh): n = 3 * token + plane (x = b1 + b2 + b3), natural column order
+__host__ __device__ inline int tsb_b_offset(int n, int k) { return (k >> 3) * 768 + (n >> 3) * 128 + (n & 7) * 16 + (k & 7) * 2; }
 
 #ifdef __CUDACC__
 // Four consecutive columns k..k+3 (k % 4 == 0) of one token -> hi / lo operand rows.
@@ -58,6 +62,23 @@ __device__ __forceinline__ void pack_quad_ts(uint8_t* chunk, int tok, int k, con
         make_uint2((uint32_t)hi[0] | ((uint32_t)hi[2] << 16), (uint32_t)hi[1] | ((uint32_t)hi[3] << 16));
     *reinterpret_cast<uint2*>(chunk + ts_b_offset(2 * tok + 1, k)) =
         make_uint2((uint32_t)lo[0] | ((uint32_t)lo[2] << 16), (uint32_t)lo[1] | ((uint32_t)lo[3] << 16));
+}
+__device__ __forceinline__ void pack_quad_tsb(uint8_t* chunk, int tok, int k, const float (&v)[4]) {
+    uint16_t b[3][4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        float f = v[e];
+#pragma unroll
+        for (int pl = 0; pl < 3; ++pl) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(f);
+            b[pl][e] = __bfloat16_as_ushort(h);
+            f -= __bfloat162float(h);
+        }
+    }
+#pragma unroll
+    for (int pl = 0; pl < 3; ++pl)
+        *reinterpret_cast<uint2*>(chunk + tsb_b_offset(3 * tok + pl, k)) =
+            make_uint2((uint32_t)b[pl][0] | ((uint32_t)b[pl][1] << 16), (uint32_t)b[pl][2] | ((uint32_t)b[pl][3] << 16));
 }
 // Sum of one token's activations over sub-block j (32 columns) -> three f16 planes.
 __device__ __forceinline__ void pack_subsum_ts(uint8_t* chunk, int tok, int j, float sum, bool& overflow) {
@@ -81,5 +102,9 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
                           int* dev_err, bool pdl, uint32_t ld_out);
 int gemm_ts_choose_splits(const QMatrix& m);
 int gemm_ts_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks);
+int gemm_tsb_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks);
+dfl_status launch_gemm_tsb(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits, const GemmEpilogue& ep,
+                           int* dev_err, bool pdl, uint32_t ld_out);
+dfl_status launch_prep_acts_tsb(cudaStream_t st, const float* x, int ld, int n_rows, uint64_t k, float pre_scale, uint8_t* acts);
 
 }  // namespace dfl

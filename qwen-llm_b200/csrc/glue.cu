@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
         uint8_t* chunk = p.acts + (uint64_t)(col0 >> 8) * act_chunk_dev(p.bf3);
         bool over = false;
         pack_quad_any(chunk, p.bf3, tok, col0 & 255, v, over);
-        if (p.bf3 != ACT_BF3) {
+        if ((p.bf3 == ACT_F16 || p.bf3 == ACT_TS)) {
             float sum = v[0] + v[1] + v[2] + v[3];  // 32-column sub-block = eight neighbouring threads
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);

@@ -23,6 +23,17 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
                        const std::vector<uint64_t>& n_outs, MatGroup* out, bool allow_ts) {
     out->n_in = n_in;
     out->total_cols = 0;
+    if (allow_ts) {
+        // every member must consume the same packed-activation format, else the whole group stays on mma.sync
+        int fmt = -1;
+        for (auto& nm : names) {
+            const dfl_tensor* t = tm.find(nm);
+            if (!t) continue;
+            const int f = !ts_supported(t->dtype) ? -2 : (t->dtype == DFL_BF16 ? ACT_TSB : ACT_TS);
+            if (f == -2 || (fmt != -1 && f != fmt)) allow_ts = false;
+            fmt = f;
+        }
+    }
     size_t i = 0;
     while (i < names.size()) {
         const dfl_tensor* t0 = tm.find(names[i]);
@@ -78,7 +89,8 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
     if (whole.layout == LAYOUT_TS) {
         std::vector<int> tiles;
         for (auto& m : out->mats) tiles.push_back(m.row_tiles);
-        out->splits = gemm_ts_choose_splits_multi(tiles.data(), (int)tiles.size(), whole.kblocks);
+        out->splits = whole.dtype == DFL_BF16 ? gemm_tsb_choose_splits_multi(tiles.data(), (int)tiles.size(), whole.kblocks)
+                                              : gemm_ts_choose_splits_multi(tiles.data(), (int)tiles.size(), whole.kblocks);
     } else {
         out->splits = gemm_choose_splits(whole);
     }
@@ -289,7 +301,9 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
     // packed-activation buffer has a single format.  DFL_GEMM_PATH=legacy forces the latter.
     bool allow_ts = true;
     for (uint64_t i = 0; i < n_tensors; ++i)
-        if (tensors[i].n_dims >= 2 && stage_bytes_of(tensors[i].dtype) != 0 && !ts_supported(tensors[i].dtype)) allow_ts = false;
+        if (tensors[i].n_dims >= 2 && stage_bytes_of(tensors[i].dtype) != 0 &&
+            !(tensors[i].dtype == DFL_Q4_K || tensors[i].dtype == DFL_Q5_K || tensors[i].dtype == DFL_Q6_K))
+            allow_ts = false;
     {
         const char* path = getenv("DFL_GEMM_PATH");
         if (path && std::string(path) == "legacy") allow_ts = false;

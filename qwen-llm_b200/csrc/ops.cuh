@@ -44,9 +44,12 @@ __device__ __forceinline__ void pack_quad(uint8_t* chunk, bool bf3, int tok, int
     }
 }
 // Layout-agnostic forms: `layout` is ACT_F16, ACT_BF3 or ACT_TS (the kernel family of the consuming GEMM).
-__device__ __forceinline__ int act_chunk_dev(int layout) { return layout == ACT_TS ? ACTTS_CHUNK : layout == ACT_BF3 ? ACTB3_CHUNK : ACT16_CHUNK; }
+__device__ __forceinline__ int act_chunk_dev(int layout) {
+    return layout == ACT_TS ? ACTTS_CHUNK : layout == ACT_TSB ? ACTTSB_CHUNK : layout == ACT_BF3 ? ACTB3_CHUNK : ACT16_CHUNK;
+}
 __device__ __forceinline__ void pack_quad_any(uint8_t* chunk, int layout, int tok, int k, const float (&v)[4], bool& overflow) {
     if (layout == ACT_TS) pack_quad_ts(chunk, tok, k, v, overflow);
+    else if (layout == ACT_TSB) pack_quad_tsb(chunk, tok, k, v);
     else pack_quad(chunk, layout == ACT_BF3, tok, k, v, overflow);
 }
 // sum of one token's activations over the 32-column sub-block `sub` (the K-quant "min" term input)

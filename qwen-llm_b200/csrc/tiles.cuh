@@ -87,8 +87,9 @@ __host__ __device__ inline bool dtype_uses_bf16_acts(int dtype) { return dtype =
 // row-lane tiles for the tensor-memory kernel (gemm_ts.cuh).  The packed activation format
 // follows the kernel that consumes it.
 constexpr int LAYOUT_FRAG = 0, LAYOUT_TS = 1;
-constexpr int ACT_F16 = 0, ACT_BF3 = 1, ACT_TS = 2;
+constexpr int ACT_F16 = 0, ACT_BF3 = 1, ACT_TS = 2, ACT_TSB = 3;
 constexpr int ACTTS_CHUNK = 16384 + 1536;  // tensor-memory kernel: B operand + min-term operand per 256 columns
+constexpr int ACTTSB_CHUNK = 32 * 768;     // bf16-weight tensor-core kernel: three bf16 planes as one 48-row B operand
 
 // position of column k (0..255) inside an activation plane row
 __host__ __device__ inline int act_pos(int k) {
@@ -203,8 +204,13 @@ dfl_status launch_prep_acts(cudaStream_t st, int weight_dtype, const float* x, i
 inline uint64_t acts_bytes(int weight_dtype, uint64_t k) {
     return (k / TILE_K) * (uint64_t)(dtype_uses_bf16_acts(weight_dtype) ? ACTB3_CHUNK : ACT16_CHUNK);
 }
-inline int act_layout_of(const QMatrix& m) { return m.layout == LAYOUT_TS ? ACT_TS : dtype_uses_bf16_acts(m.dtype) ? ACT_BF3 : ACT_F16; }
-inline int act_chunk_bytes(int act_layout) { return act_layout == ACT_TS ? ACTTS_CHUNK : act_layout == ACT_BF3 ? ACTB3_CHUNK : ACT16_CHUNK; }
+inline int act_layout_of(const QMatrix& m) {
+    if (m.layout == LAYOUT_TS) return dtype_uses_bf16_acts(m.dtype) ? ACT_TSB : ACT_TS;
+    return dtype_uses_bf16_acts(m.dtype) ? ACT_BF3 : ACT_F16;
+}
+inline int act_chunk_bytes(int act_layout) {
+    return act_layout == ACT_TS ? ACTTS_CHUNK : act_layout == ACT_TSB ? ACTTSB_CHUNK : act_layout == ACT_BF3 ? ACTB3_CHUNK : ACT16_CHUNK;
+}
 inline uint64_t acts_bytes_for(const QMatrix& m) { return (m.n_in / TILE_K) * (uint64_t)act_chunk_bytes(act_layout_of(m)); }
 // Packs x for the kernel that will consume matrix m.
 dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* x, int ld, int n_rows, float pre_scale, uint8_t* acts,
