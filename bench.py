@@ -130,6 +130,62 @@ def c1_cpu(orc, raw1, raw2, x, steps):
     return dt / steps, arg, int(L.orc_num_threads())
 
 
+def run_gemm(args, device):
+    """One weight matrix, 16 activation rows: the few-row GEMM alone against the HBM roofline.
+    The pipeline object chains dtype[n_in -> n_out] with dtype[n_out -> n_in]; both launches are timed with
+    CUDA events on the launching stream and replicas larger than L2 are cycled."""
+    pkg = importlib.import_module("qwen-llm_b200")
+    name, n_in, n_out = args.gemm.split(":")
+    n_in, n_out = int(n_in), int(n_out)
+    dt = {"q4_k": pkg.Q4_K, "q5_k": pkg.Q5_K, "q6_k": pkg.Q6_K, "q8_0": pkg.Q8_0, "bf16": pkg.BF16}[name]
+    blk = {pkg.Q4_K: 144, pkg.Q5_K: 176, pkg.Q6_K: 210, pkg.Q8_0: 272, pkg.BF16: 512}[dt]
+    rng = np.random.default_rng(7)
+
+    def raw(k, n):
+        nb = n * (k // 256)
+        if dt == pkg.BF16:
+            w = rng.standard_normal((n, k)).astype(np.float32) * 0.02
+            return (w.view(np.uint32) >> 16).astype(np.uint16).view(np.uint8).reshape(-1)
+        b = rng.integers(0, 256, size=(nb, blk), dtype=np.uint8)
+        d = np.full(nb, 1e-4, dtype=np.float16).view(np.uint8).reshape(nb, 2)   # sane f16 block scales
+        if dt == pkg.Q6_K:
+            b[:, 208:210] = d
+        elif dt == pkg.Q8_0:
+            for j in range(8):
+                b[:, 34 * j:34 * j + 2] = d
+        else:
+            b[:, 0:2] = d
+            b[:, 2:4] = d
+        return b.reshape(-1)
+
+    bytes_one = (n_in // 256) * n_out * blk
+    n_rep = max(2, int(300e6 // (2 * bytes_one)) + 1)
+    pipes = []
+    for _ in range(n_rep):
+        a, b = pkg.QMatrix(dt, n_in, n_out, raw(n_in, n_out), device), pkg.QMatrix(dt, n_out, n_in, raw(n_out, n_in), device)
+        pipes.append((a, b, pkg.C1Pipeline(a, b)))
+    x = (rng.standard_normal((16, n_in)) * 0.1).astype(np.float32)
+    for _, _, p in pipes:
+        p.upload(x)
+    for i in range(max(3, args.warmup)):
+        pipes[i % n_rep][2].run_resident(16, 1)
+    sampler = ClockSampler(device)
+    sampler.start()
+    pkg.gemm_timing_begin()
+    for i in range(args.steps):
+        pipes[i % n_rep][2].run_resident(16, 1)
+    ms, n, nbytes = pkg.gemm_timing_end()
+    clocks = sampler.stop()
+    peak, kind = measured_peaks()
+    gbs = nbytes / ms / 1e6
+    return {"metric": "gemm_GBps", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "dtype": name, "data": "synthetic",
+            "config": {"workload": f"gemm: 16 rows x {name} {n_in}x{n_out} then {n_out}x{n_in}", "l2": f"{n_rep} replicas cycled, > 126 MB"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                         "peak_kind": kind, "launches_timed": n, "us_per_launch": ms / n * 1e3},
+            "gpu_launches": n, "clocks": clocks}
+
+
 def run_c1(args, rank, world, device):
     import orc
     pkg = importlib.import_module("qwen-llm_b200")
@@ -239,6 +295,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=os.environ.get("DFL_BENCH_WORKLOAD", "auto"))
     ap.add_argument("--impl", default="b200")
+    ap.add_argument("--gemm", default="q4_k:4096:24576", help="workload gemm only: dtype:n_in:n_out")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -256,6 +313,8 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     if args.workload == "c1":
         line = run_c1(args, rank, world, local)
+    elif args.workload == "gemm":
+        line = run_gemm(args, local)
     elif args.workload == "c2v":
         line = importlib.import_module("bench_c2").run_verify_only(args, rank, world, local)
     else:
