@@ -18,6 +18,14 @@ bool pdl_enabled() {
     return on;
 }
 
+bool pdl_enabled_for(int family) {
+    static const int off = [] {
+        const char* e = getenv("DFL_PDL_OFF");
+        return e ? atoi(e) : 0;
+    }();
+    return pdl_enabled() && !(off & family);
+}
+
 void set_error(const std::string& msg) { t_last_error = msg; }
 dfl_status fail(dfl_status st, const std::string& msg) {
     t_last_error = msg;
@@ -55,7 +63,7 @@ dfl_status check_dev_err(cudaStream_t st, int* dev_err) {
 }
 
 dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, const void* data, uint64_t n_bytes,
-                          bool on_device, cudaStream_t st, QMatrix* m, bool allow_ts) {
+                          bool on_device, cudaStream_t st, QMatrix* m, bool allow_ts, int kb_group) {
     DFL_CHECK(use_device(device));
     if (!data || n_in == 0 || n_out == 0) return fail(DFL_ERR_BAD_ARG, "qmatrix: null data or empty shape");
     m->device = device;
@@ -91,7 +99,13 @@ dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, 
     // DFL_GEMM_PATH=legacy keeps every matrix on the mma.sync kernel (A/B runs)
     const char* path = getenv("DFL_GEMM_PATH");
     m->layout = (allow_ts && ts_supported(dtype) && !(path && std::string(path) == "legacy")) ? LAYOUT_TS : LAYOUT_FRAG;
-    dfl_status s = m->layout == LAYOUT_TS ? retile_matrix_ts(st, dtype, src, n_in, n_out, m->tiles)
+    if (kb_group > 0 && m->layout != LAYOUT_TS) {
+        if (tmp) cudaFree(tmp);
+        cudaFree(m->tiles);
+        m->tiles = nullptr;
+        return fail(DFL_ERR_UNSUPPORTED, "qmatrix: expert-grouped matrices need the tensor-memory GEMM (Q4_K / Q5_K / Q6_K)");
+    }
+    dfl_status s = m->layout == LAYOUT_TS ? retile_matrix_ts(st, dtype, src, n_in, n_out, m->tiles, kb_group)
                                           : retile_matrix(st, dtype, src, n_in, n_out, m->tiles);
     cudaError_t e2 = cudaStreamSynchronize(st);
     if (tmp) cudaFree(tmp);
@@ -149,7 +163,7 @@ dfl_status dfl_qmatrix_create(int32_t device, int32_t dtype, uint64_t n_in, uint
     if (!out) return fail(DFL_ERR_BAD_ARG, "qmatrix_create: out is null");
     *out = nullptr;
     auto* q = new dfl_qmatrix();
-    dfl_status s = qmatrix_create(device, dtype, n_in, n_out, data, n_bytes, on_device != 0, 0, &q->m, true);
+    dfl_status s = qmatrix_create(device, dtype, n_in, n_out, data, n_bytes, on_device != 0, 0, &q->m, true, 0);
     if (s != DFL_OK) {
         qmatrix_release(&q->m);
         delete q;

@@ -12,11 +12,11 @@ namespace dfl {
 
 // ---- front: reduce GEMM partials, per-head RMSNorm, partial NeoX RoPE, KV append ---------
 // grid (heads = n_q + 2 n_kv, n_rows), block = 128 threads (4 warps cooperate on one head).
-__global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, const float* __restrict__ part, int splits,
-                                                         int ld_part, const float* __restrict__ q_norm_w,
-                                                         const float* __restrict__ k_norm_w, uint32_t start, void* k_cache,
-                                                         void* v_cache, int kv_f16, float* __restrict__ q_rot,
-                                                         float* __restrict__ gate, const uint32_t* __restrict__ pos_override, long long cache_row0) {
+__global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, const float* part, int splits,
+                                                         int ld_part, const float* q_norm_w,
+                                                         const float* k_norm_w, uint32_t start, void* k_cache,
+                                                         void* v_cache, int kv_f16, float* q_rot,
+                                                         float* gate, const uint32_t* pos_override, long long cache_row0) {
     pdl_prologue();
     extern __shared__ float sh[];  // [hd] values, then 4 partial sums
     const int head = blockIdx.x, tok = blockIdx.y, hd = g.hd;
@@ -82,7 +82,7 @@ dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, con
                              const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
                              void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override, long long cache_row0) {
     dim3 grid((unsigned)(g.n_q + 2 * g.n_kv), (unsigned)n_rows);
-    launch_k(attn_front_kernel, dim3(grid), dim3(128), (g.hd + 4) * sizeof(float), st, g, gated ? 1 : 0, part, splits, ld_part, q_norm_w, k_norm_w, start,
+    launch_kf(4, attn_front_kernel, dim3(grid), dim3(128), (g.hd + 4) * sizeof(float), st, g, gated ? 1 : 0, part, splits, ld_part, q_norm_w, k_norm_w, start,
                                                                    k_cache, v_cache, kv_f16 ? 1 : 0, q_rot, gate, pos_override, cache_row0);
     count_launch();
     DFL_CUDA(cudaGetLastError());
@@ -92,9 +92,9 @@ dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, con
 // ---- chunk kernel ----------------------------------------------------------------------
 // grid (n_chunks, n_kv), block 256.  partial record per (chunk, kv head, query): [m, l, acc[hd]].
 template <typename KV, int HD>
-__global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float* __restrict__ q_rot, const KV* __restrict__ k_cache,
-                                                         const KV* __restrict__ v_cache, uint32_t start, int n_rows,
-                                                         float* __restrict__ partials) {
+__global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float* q_rot, const KV* k_cache,
+                                                         const KV* v_cache, uint32_t start, int n_rows,
+                                                         float* partials) {
     pdl_prologue();
     extern __shared__ float sm[];
     constexpr int LD = HD + 1;
@@ -192,8 +192,8 @@ __global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float
 // ---- combine + sigmoid gate + activation packing ---------------------------------------------
 // grid (n_q, n_rows), block 32: one warp per (row, q head); lane owns hd/32 consecutive dims.
 template <int HD>
-__global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* __restrict__ partials, int n_chunks_total,
-                                                       const float* __restrict__ gate, uint32_t start, uint8_t* acts, int bf3,
+__global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* partials, int n_chunks_total,
+                                                       const float* gate, uint32_t start, uint8_t* acts, int bf3,
                                                        float* out_f32, int* err) {
     pdl_prologue();
     constexpr int PER = HD / 32;  // 4 or 8
@@ -263,7 +263,7 @@ __global__ void acts_clear_kernel(uint8_t* acts, uint64_t bytes) {
     if (i < bytes) *reinterpret_cast<uint4*>(acts + i) = make_uint4(0, 0, 0, 0);
 }
 dfl_status launch_acts_clear(cudaStream_t st, uint8_t* acts, uint64_t bytes) {
-    launch_k(acts_clear_kernel, dim3((unsigned)((bytes / 16 + 255) / 256)), dim3(256), 0, st, acts, bytes);
+    launch_kf(4, acts_clear_kernel, dim3((unsigned)((bytes / 16 + 255) / 256)), dim3(256), 0, st, acts, bytes);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -283,7 +283,7 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
         DFL_CUDA(cudaFuncSetAttribute(attn_chunk_kernel<KV, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = true;
     }
-    launch_k(attn_chunk_kernel<KV, HD>, dim3(dim3((unsigned)n_chunks, (unsigned)g.n_kv, (unsigned)((n_rows + ATTN_ROW_GROUP - 1) / ATTN_ROW_GROUP))), dim3(256), smem, st, 
+    launch_kf(4, attn_chunk_kernel<KV, HD>, dim3(dim3((unsigned)n_chunks, (unsigned)g.n_kv, (unsigned)((n_rows + ATTN_ROW_GROUP - 1) / ATTN_ROW_GROUP))), dim3(256), smem, st, 
         g, q_rot, reinterpret_cast<const KV*>(k_cache), reinterpret_cast<const KV*>(v_cache), start, n_rows, partials);
     count_launch();
     DFL_CUDA(cudaGetLastError());
@@ -305,8 +305,8 @@ dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q
         // rows of absent tokens must read as zero in the next GEMM
         DFL_CHECK(launch_acts_clear(st, acts, (uint64_t)g.n_q * g.hd / TILE_K * (uint64_t)act_chunk_bytes(bf3)));
     }
-    if (g.hd == 128) launch_k(attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
-    else launch_k(attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
+    if (g.hd == 128) launch_kf(4, attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
+    else launch_kf(4, attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -107,7 +107,22 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // first global-memory access and pdl_launch_dependents() at its top, so that launch latency and
 // block scheduling overlap the predecessor.  DFL_PDL=0 turns the attribute off.
 bool pdl_enabled();
+bool pdl_enabled_for(int family);   // development switch: DFL_PDL_OFF=<bit mask of kernel families>
 #ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kf(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled_for(family) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
@@ -122,7 +137,10 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
-// first statements of every kernel launched through launch_k
+// first statements of every kernel launched through launch_k.  Such a kernel starts its life before its
+// predecessor has finished writing, so inputs the predecessor produces must not be declared
+// `const T* __restrict__` (that licenses non-coherent read-only-cache loads, which may return stale lines);
+// only genuinely immutable inputs (weights) keep the qualifier.
 __device__ __forceinline__ void pdl_prologue() {
     pdl_launch_dependents();
     pdl_wait();

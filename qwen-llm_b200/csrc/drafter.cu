@@ -24,11 +24,11 @@ struct DLayerW {
 // ---- drafter attention: queries = noise rows, keys = context cache || noise rows -----------
 // allowed(q_pos, k_pos) = (!causal || k_pos <= q_pos) && (!swa || window == 0 || |q - k| < window)
 template <int HD>
-__global__ void __launch_bounds__(256) dattn_chunk_kernel(AttnGeom g, const float* __restrict__ q_rot, const float* __restrict__ k_ctx,
-                                                          const float* __restrict__ v_ctx, const uint32_t* __restrict__ pos_ctx, int ctx_begin,
-                                                          int n_ctx, const float* __restrict__ k_noise, const float* __restrict__ v_noise,
+__global__ void __launch_bounds__(256) dattn_chunk_kernel(AttnGeom g, const float* q_rot, const float* k_ctx,
+                                                          const float* v_ctx, const uint32_t* pos_ctx, int ctx_begin,
+                                                          int n_ctx, const float* k_noise, const float* v_noise,
                                                           uint32_t noise_start, int n_rows, int causal, uint32_t window,
-                                                          float* __restrict__ partials) {
+                                                          float* partials) {
     pdl_prologue();
     extern __shared__ float sm[];
     constexpr int LD = HD + 1;
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) dattn_chunk_kernel(AttnGeom g, const floa
 
 // combine over a fixed number of chunks + activation packing (rows >= n_rows packed as zeros)
 template <int HD>
-__global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float* __restrict__ partials, int n_chunks, int n_rows, uint8_t* acts,
+__global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float* partials, int n_chunks, int n_rows, uint8_t* acts,
                                                         int bf3, int* err) {
     pdl_prologue();
     constexpr int PER = HD / 32;

@@ -15,10 +15,10 @@ namespace dfl {
 // ---- front: conv1d(K=4) + SiLU over the block, q/k L2 norm -------------------------------
 // grid = conv_dim / 128 (one q, k or v head per CTA), block 128 (one channel per thread).
 // All global loads are issued before the token recurrence starts.
-__global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* __restrict__ part, int splits, int ld_part, int n_rows,
-                                                        const float* __restrict__ conv_w, float* __restrict__ conv_state,
-                                                        float* __restrict__ qkv_raw, float* __restrict__ q_n, float* __restrict__ k_n,
-                                                        float* __restrict__ v_out) {
+__global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* part, int splits, int ld_part, int n_rows,
+                                                        const float* conv_w, float* conv_state,
+                                                        float* qkv_raw, float* q_n, float* k_n,
+                                                        float* v_out) {
     pdl_prologue();
     const int conv_dim = g.conv_dim();
     const int c = blockIdx.x * 128 + threadIdx.x;
@@ -84,14 +84,14 @@ __global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* 
 dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
                             const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v) {
     if (g.hd != 128 || g.conv_k != 4) return fail(DFL_ERR_UNSUPPORTED, "gdn: head_dim must be 128 and conv kernel 4");
-    launch_k(gdn_front_kernel, dim3(g.conv_dim() / 128), dim3(128), 0, st, g, part_qkv, splits, ld_part, n_rows, conv_w, conv_state, qkv_raw, q_n, k_n, v);
+    launch_kf(8, gdn_front_kernel, dim3(g.conv_dim() / 128), dim3(128), 0, st, g, part_qkv, splits, ld_part, n_rows, conv_w, conv_state, qkv_raw, q_n, k_n, v);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
 }
 
-__global__ void gdn_conv_restore_kernel(int conv_dim, const float* __restrict__ conv_pre, const float* __restrict__ qkv_raw, int n_keep,
-                                        float* __restrict__ conv_state) {
+__global__ void gdn_conv_restore_kernel(int conv_dim, const float* conv_pre, const float* qkv_raw, int n_keep,
+                                        float* conv_state) {
     pdl_prologue();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= conv_dim) return;
@@ -105,7 +105,7 @@ __global__ void gdn_conv_restore_kernel(int conv_dim, const float* __restrict__ 
 dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const float* conv_pre, const float* qkv_raw, int n_keep,
                                    float* conv_state) {
     const int cd = g.conv_dim();
-    launch_k(gdn_conv_restore_kernel, dim3((cd + 255) / 256), dim3(256), 0, st, cd, conv_pre, qkv_raw, n_keep, conv_state);
+    launch_kf(8, gdn_conv_restore_kernel, dim3((cd + 255) / 256), dim3(256), 0, st, cd, conv_pre, qkv_raw, n_keep, conv_state);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -116,11 +116,11 @@ dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const floa
 // The block's q, k, v rows and gate scalars are staged in shared memory first, so that the
 // sequential part touches no global memory.  Per token (forward.rs:1054-1091): sk = S k (state
 // before decay), coeff = beta (v - g sk), S = g S + coeff k, o = S q.
-__global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* __restrict__ state_in, float* __restrict__ state_out,
-                                                       const float* __restrict__ q_n, const float* __restrict__ k_n,
-                                                       const float* __restrict__ v, const float* __restrict__ ab,
-                                                       const float* __restrict__ dt_bias, const float* __restrict__ a_log, int n_rows,
-                                                       float* __restrict__ o) {
+__global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* state_in, float* state_out,
+                                                       const float* q_n, const float* k_n,
+                                                       const float* v, const float* ab,
+                                                       const float* dt_bias, const float* a_log, int n_rows,
+                                                       float* o) {
     pdl_prologue();
     __shared__ float qs[MAX_ROWS][128], ks[MAX_ROWS][128], vs[MAX_ROWS][32], gs[MAX_ROWS], bs[MAX_ROWS], os[MAX_ROWS][32];
     const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* _
 dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state_in, float* state_out, const float* q_n,
                            const float* k_n, const float* v, const float* ab, const float* dt_bias, const float* a_log, int n_rows,
                            float* o) {
-    launch_k(gdn_scan_kernel, dim3(dim3((unsigned)g.n_v, 4)), dim3(256), 0, st, g, state_in, state_out, q_n, k_n, v, ab, dt_bias, a_log, n_rows, o);
+    launch_kf(8, gdn_scan_kernel, dim3(dim3((unsigned)g.n_v, 4)), dim3(256), 0, st, g, state_in, state_out, q_n, k_n, v, ab, dt_bias, a_log, n_rows, o);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -212,8 +212,8 @@ dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state
 
 // ---- post: gated RMSNorm + activation packing ----------------------------------------------
 // grid (n_v, 16), block 32: one warp per (head, token); lane owns 4 consecutive channels.
-__global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* __restrict__ o, const float* __restrict__ part_z, int splits,
-                                                      int ld_part, const float* __restrict__ norm_w, int n_rows, uint8_t* acts, int bf3,
+__global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* o, const float* part_z, int splits,
+                                                      int ld_part, const float* norm_w, int n_rows, uint8_t* acts, int bf3,
                                                       int* err) {
     pdl_prologue();
     const int h = blockIdx.x, tok = blockIdx.y, lane = threadIdx.x;
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* __
 
 dfl_status launch_gdn_post(cudaStream_t st, const GdnGeom& g, const float* o, const float* part_z, int splits, int ld_part,
                            const float* norm_w, int n_rows, uint8_t* acts, int bf3, int* err) {
-    launch_k(gdn_post_kernel, dim3(dim3((unsigned)g.n_v, MAX_ROWS)), dim3(32), 0, st, g, o, part_z, splits, ld_part, norm_w, n_rows, acts, bf3, err);
+    launch_kf(8, gdn_post_kernel, dim3(dim3((unsigned)g.n_v, MAX_ROWS)), dim3(32), 0, st, g, o, part_z, splits, ld_part, norm_w, n_rows, acts, bf3, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

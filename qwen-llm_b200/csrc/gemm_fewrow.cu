@@ -795,7 +795,7 @@ dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* 
     return launch_prep_acts(st, m.dtype, x, ld, n_rows, m.n_in, pre_scale, acts, dev_err);
 }
 
-__global__ void reduce_partials_kernel(const float* __restrict__ part, int splits, int n_rows, uint64_t n_out, float* __restrict__ y,
+__global__ void reduce_partials_kernel(const float* part, int splits, int n_rows, uint64_t n_out, float* y,
                                        int ld_y) {
     pdl_prologue();
     const uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -858,7 +858,7 @@ __device__ __forceinline__ Top2 top2_block_reduce(Top2 a) {
 }
 __device__ __forceinline__ float key_to_float(int32_t k) { return __int_as_float(k < 0 ? (k ^ 0x7fffffff) : k); }
 
-__global__ void argmax_part_kernel(const float* __restrict__ logits, uint64_t vocab, uint64_t ld, Top2* __restrict__ parts) {
+__global__ void argmax_part_kernel(const float* logits, uint64_t vocab, uint64_t ld, Top2* parts) {
     pdl_prologue();
     const int row = blockIdx.y, part = blockIdx.x;
     const uint64_t per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
@@ -873,7 +873,7 @@ __global__ void argmax_part_kernel(const float* __restrict__ logits, uint64_t vo
     a = top2_block_reduce(a);
     if (threadIdx.x == 0) parts[row * ARGMAX_PARTS + part] = a;
 }
-__global__ void argmax_final_kernel(const Top2* __restrict__ parts, int32_t* __restrict__ argmax, float* __restrict__ gap) {
+__global__ void argmax_final_kernel(const Top2* parts, int32_t* argmax, float* gap) {
     pdl_prologue();
     const int row = blockIdx.x;
     Top2 a = threadIdx.x < ARGMAX_PARTS ? parts[row * ARGMAX_PARTS + threadIdx.x] : Top2{INT32_MIN, INT32_MAX, INT32_MIN, 0};

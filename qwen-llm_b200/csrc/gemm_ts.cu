@@ -23,7 +23,8 @@
 namespace dfl {
 
 // Q6_K packing lives in gemm_ts_q6k.cuh (included further down, after the primitives it uses)
-__global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks);
+__device__ __forceinline__ uint64_t src_block_index(uint64_t row, int kb, int kblocks, uint64_t n_out, int kb_group);
+__global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks, int kb_group);
 __device__ float decode_ts_q6k_elem(const uint8_t* stage, int r, int k);
 __global__ void retile_tsb_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_in, uint64_t n_out, int kblocks);
 __device__ float decode_tsb_elem(const uint8_t* stage, int r, int k);
@@ -31,8 +32,16 @@ __device__ float decode_tsb_elem(const uint8_t* stage, int r, int k);
 // ---------------------------------------------------------------------------------------------
 // Re-tiling into row-lane tiles and the inverse decode.
 // ---------------------------------------------------------------------------------------------
+// Index of the ggml block (row, kb) in the source.  kb_group = 0: plain row-major [n_out][kblocks].  kb_group > 0: the
+// source is [kblocks / kb_group] matrices of [n_out][kb_group] blocks one after the other (the experts of
+// ffn_down_exps), viewed as one matrix whose columns are the experts' columns side by side.
+__device__ __forceinline__ uint64_t src_block_index(uint64_t row, int kb, int kblocks, uint64_t n_out, int kb_group) {
+    if (kb_group <= 0) return row * kblocks + kb;
+    return ((uint64_t)(kb / kb_group) * n_out + row) * kb_group + kb % kb_group;
+}
+
 template <int DT>
-__global__ void retile_ts_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks) {
+__global__ void retile_ts_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks, int kb_group) {
     constexpr int SRC_BLK = DT == DFL_Q4_K ? 144 : DT == DFL_Q5_K ? 176 : 210;
     constexpr int STAGE = DT == DFL_Q4_K ? STAGE_Q4_K : DT == DFL_Q5_K ? STAGE_Q5_K : STAGE_Q6_K;
     const uint64_t tile_id = blockIdx.x;
@@ -60,7 +69,7 @@ __global__ void retile_ts_kernel(const uint8_t* __restrict__ src, uint8_t* __res
             }
             const uint64_t row = rt * TILE_R + r;
             if (row < n_out) {
-                const uint8_t* blk = src + (row * kblocks + kb) * (uint64_t)SRC_BLK + src_off;
+                const uint8_t* blk = src + src_block_index(row, kb, kblocks, n_out, kb_group) * (uint64_t)SRC_BLK + src_off;
 #pragma unroll
                 for (int b = 0; b < 16; ++b) out[b] = blk[b];
                 if (off < TSQ4_OFF_QS) {
@@ -81,17 +90,21 @@ __global__ void retile_ts_kernel(const uint8_t* __restrict__ src, uint8_t* __res
     }
 }
 
-dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, uint8_t* dst_tiles) {
+dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, uint8_t* dst_tiles,
+                            int kb_group) {
     if (n_in % TILE_K) return fail(DFL_ERR_BAD_SHAPE, "retile: n_in must be a multiple of 256");
     const int kblocks = (int)(n_in / TILE_K);
     const uint64_t n_tiles = (uint64_t)kblocks * ((n_out + TILE_R - 1) / TILE_R);
     if (n_tiles == 0 || n_tiles > 0x7fffffffu) return fail(DFL_ERR_BAD_SHAPE, "retile: tile count out of range");
     dim3 grid((unsigned)n_tiles), block(256);
     switch (dtype) {
-        case DFL_Q4_K: retile_ts_kernel<DFL_Q4_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
-        case DFL_Q5_K: retile_ts_kernel<DFL_Q5_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
-        case DFL_Q6_K: retile_ts_q6k_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks); break;
-        case DFL_BF16: retile_tsb_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_in, n_out, kblocks); break;
+        case DFL_Q4_K: retile_ts_kernel<DFL_Q4_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks, kb_group); break;
+        case DFL_Q5_K: retile_ts_kernel<DFL_Q5_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks, kb_group); break;
+        case DFL_Q6_K: retile_ts_q6k_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks, kb_group); break;
+        case DFL_BF16:
+            if (kb_group > 0) return fail(DFL_ERR_UNSUPPORTED, "retile: grouped column blocks are not built for bf16");
+            retile_tsb_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_in, n_out, kblocks);
+            break;
         default: return fail(DFL_ERR_UNSUPPORTED, "retile: dtype has no row-lane tile layout");
     }
     count_launch();

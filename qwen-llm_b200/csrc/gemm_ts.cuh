@@ -94,7 +94,8 @@ __device__ __forceinline__ void pack_subsum_ts(uint8_t* chunk, int tok, int j, f
 }
 #endif
 
-dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, uint8_t* dst_tiles);
+dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, uint8_t* dst_tiles,
+                            int kb_group = 0);
 dfl_status decode_tiles_ts(cudaStream_t st, const QMatrix& m, float* out_dev);
 dfl_status launch_prep_acts_ts(cudaStream_t st, const float* x, int ld, int n_rows, uint64_t k, float pre_scale, uint8_t* acts,
                                int* dev_err);

@@ -21,7 +21,7 @@ __host__ __device__ inline int tsq6_slot_of_kprime(int within8) { return (within
 __host__ __device__ inline int tsq6_hi2_bit(int wi, int slot) { return (wi & 1) * 8 + 2 * (slot & 3) + 16 * (slot >> 2); }
 
 // one thread per (row, unit, kp)
-__global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks) {
+__global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks, int kb_group) {
     const uint64_t tile_id = blockIdx.x;
     const int kb = (int)(tile_id % kblocks);
     const uint64_t rt = tile_id / kblocks;
@@ -30,7 +30,7 @@ __global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* _
         const int r = idx & 127, kp = (idx >> 7) & 3, u = idx >> 9;
         const uint64_t row = rt * TILE_R + r;
         const bool valid = row < n_out;
-        const uint8_t* blk = src + (row * kblocks + kb) * 210ull;
+        const uint8_t* blk = src + src_block_index(row, kb, kblocks, n_out, kb_group) * 210ull;
         uint32_t nib[4] = {0, 0, 0, 0}, hi2[2] = {0, 0};
         if (valid) {
 #pragma unroll

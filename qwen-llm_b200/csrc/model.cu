@@ -9,7 +9,7 @@ namespace dfl {
 
 dfl_status launch_group(cudaStream_t st, const MatGroup& g, const uint8_t* acts, float* part, const GemmEpilogue& ep, int* err) {
     for (size_t i = 0; i < g.mats.size(); ++i)
-        DFL_CHECK(launch_gemm_fewrow(st, g.mats[i], acts, part + g.col_off[i], g.splits, ep, err, pdl_enabled(), g.total_cols));
+        DFL_CHECK(launch_gemm_fewrow(st, g.mats[i], acts, part + g.col_off[i], g.splits, ep, err, pdl_enabled_for(1), g.total_cols));
     return DFL_OK;
 }
 
@@ -20,7 +20,7 @@ static uint64_t tensor_elems(const dfl_tensor* t) {
 }
 
 dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const std::vector<std::string>& names, uint64_t n_in,
-                       const std::vector<uint64_t>& n_outs, MatGroup* out, bool allow_ts) {
+                       const std::vector<uint64_t>& n_outs, MatGroup* out, bool allow_ts, int kb_group) {
     out->n_in = n_in;
     out->total_cols = 0;
     if (allow_ts) {
@@ -45,7 +45,8 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
             const dfl_tensor* t = tm.find(names[j]);
             if (!t) return fail(DFL_ERR_MISSING_TENSOR, "missing tensor " + names[j]);
             if (t->dtype != t0->dtype || t->on_device != t0->on_device) break;
-            if (t->n_dims < 2 || t->shape[0] != n_in || tensor_elems(t) != n_in * n_outs[j])
+            if (kb_group > 0 && names.size() != 1) return fail(DFL_ERR_BAD_ARG, "build_group: an expert-grouped matrix stands alone");
+            if (t->n_dims < 2 || (kb_group == 0 && t->shape[0] != n_in) || tensor_elems(t) != n_in * n_outs[j])
                 return fail(DFL_ERR_BAD_SHAPE, "tensor " + names[j] + " has unexpected shape");
             const uint64_t want = n_outs[j] * (n_in / 256) * (uint64_t)ggml_bytes_per_256(t->dtype);
             if (n_in % 256 || ggml_bytes_per_256(t->dtype) == 0 || t->n_bytes != want)
@@ -56,7 +57,7 @@ dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const s
         }
         QMatrix qm;
         if (j - i == 1) {
-            DFL_CHECK(qmatrix_create(device, t0->dtype, n_in, rows, t0->data, t0->n_bytes, t0->on_device != 0, st, &qm, allow_ts));
+            DFL_CHECK(qmatrix_create(device, t0->dtype, n_in, rows, t0->data, t0->n_bytes, t0->on_device != 0, st, &qm, allow_ts, kb_group));
         } else {
             uint8_t* cat = nullptr;
             DFL_CUDA(cudaMalloc(&cat, bytes));
@@ -216,7 +217,33 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             ++gi;
         }
         DFL_CHECK(launch_group(st, *out_proj, sc->acts_v, sc->part, GemmEpilogue{}, s->err));
-        DFL_CHECK(norm_glue(sc->part, out_proj->splits, (int)out_proj->total_cols, L.post_norm_w, false, nullptr));
+        const bool moe = a.expert_count > 0;
+        DFL_CHECK(norm_glue(sc->part, out_proj->splits, (int)out_proj->total_cols, L.post_norm_w, moe, nullptr));
+        int down_splits;
+        if (moe) {
+            // routed experts + shared expert (forward.rs:749-824): route, then every expert of the layer as two large
+            // few-row GEMMs; the glue zeroes the inner columns of the experts a token did not choose
+            const int E = (int)a.expert_count, Fe = (int)a.expert_feed_forward_length, Fs = (int)a.expert_shared_feed_forward_length;
+            const int inner = E * Fe + Fs;
+            DFL_CHECK(launch_small_matmul(st, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
+            DFL_CHECK(launch_moe_route(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
+            DFL_CHECK(launch_group(st, L.moe_gate_up, sc->acts_h, sc->part, ep_norm, s->err));
+            GlueParams p;
+            p.mode = GLUE_SWIGLU;
+            p.part = sc->part; p.splits = L.moe_gate_up.splits; p.ld_part = (int)L.moe_gate_up.total_cols;
+            p.swiglu_f = inner;
+            p.route_w = sc->route_w; p.route_sg = sc->route_sg; p.route_e = E; p.route_f = Fe;
+            p.pre_scale = 1.0f / 64.0f;
+            p.acts = sc->acts_f; p.bf3 = m->act_layout;
+            p.n_rows = (int)n; p.err = s->err;
+            DFL_CHECK(launch_glue(st, p, (uint64_t)inner));
+            GemmEpilogue ep_down;
+            ep_down.out_scale = 64.0f;
+            DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part, ep_down, s->err));
+            DFL_CHECK(launch_group(st, L.moe_down_sh, sc->acts_f + (uint64_t)(E * Fe / TILE_K) * act_chunk_bytes(m->act_layout),
+                                   sc->part + (uint64_t)L.moe_down.splits * MAX_ROWS * H, ep_down, s->err));
+            down_splits = L.moe_down.splits + L.moe_down_sh.splits;
+        } else {
         // dense SwiGLU FFN (forward.rs:725-747)
         DFL_CHECK(launch_group(st, L.gate_up, sc->acts_h, sc->part, ep_norm, s->err));
         {
@@ -232,13 +259,15 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         GemmEpilogue ep_down;
         ep_down.out_scale = 64.0f;
         DFL_CHECK(launch_group(st, L.down, sc->acts_f, sc->part, ep_down, s->err));
+        down_splits = L.down.splits;
+        }
         float* cap = nullptr;
         for (uint32_t k = 0; k < n_ids; ++k)
             if (layer_ids[k] == il) cap = sc->capture + (uint64_t)k * H;
         const bool last = il + 1 == a.n_layer;
         const float* next_w = last ? m->out_norm_w : m->layers[il + 1].attn_norm_w;
         const bool next_gdn = !last && !m->layers[il + 1].is_attn;
-        DFL_CHECK(norm_glue(sc->part, L.down.splits, (int)L.down.total_cols, next_w, next_gdn, cap));
+        DFL_CHECK(norm_glue(sc->part, down_splits, (int)H, next_w, next_gdn, cap));
         if (cap) {
             // duplicate slots (same layer listed twice) get a device copy of the first one
             bool first = true;
@@ -281,7 +310,9 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
     DFL_CHECK(use_device(device));
     const dfl_arch& a = *arch;
     if (a.n_layer == 0 || a.hidden_size % 256 || a.hidden_size == 0) return fail(DFL_ERR_BAD_SHAPE, "model_create: hidden size must be a positive multiple of 256");
-    if (a.expert_count > 0) return fail(DFL_ERR_UNSUPPORTED, "model_create: routed-expert FFN is not built yet");
+    if (a.expert_count > 0 && (a.expert_feed_forward_length == 0 || a.expert_feed_forward_length % 256 || a.expert_shared_feed_forward_length == 0 ||
+                               a.expert_shared_feed_forward_length % 256 || a.expert_used_count == 0 || a.expert_used_count > a.expert_count))
+        return fail(DFL_ERR_BAD_SHAPE, "model_create: expert FFN widths must be positive multiples of 256 and 1 <= used <= count");
     if (a.intermediate_size % 256) return fail(DFL_ERR_BAD_SHAPE, "model_create: FFN width must be a multiple of 256");
     if (a.gdn_head_dim != 128 || a.gdn_conv_kernel != 4) return fail(DFL_ERR_UNSUPPORTED, "model_create: GDN head_dim must be 128 and conv kernel 4");
     if (a.attn_head_dim != 128 && a.attn_head_dim != 256) return fail(DFL_ERR_UNSUPPORTED, "model_create: attention head_dim must be 128 or 256");
@@ -369,9 +400,31 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
             MC(upload_f32(device, st, tm, blk(il, "ssm_norm.weight"), 128, &L.ssm_norm_w));
             m->verify_weight_bytes += L.in_qkv_z.ggml_bytes() + L.w_out.ggml_bytes() + 2 * H * a.gdn_n_v_heads * 4;
         }
-        MC(build_group(device, st, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up, allow_ts));
-        MC(build_group(device, st, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down, allow_ts));
-        m->verify_weight_bytes += L.gate_up.ggml_bytes() + L.down.ggml_bytes();
+        if (a.expert_count > 0) {
+            // forward.rs:749-824; tensor shapes as in loader.rs (experts stacked along the last ggml dimension)
+            if (!allow_ts) { s = fail(DFL_ERR_UNSUPPORTED, "model_create: the routed-expert FFN needs Q4_K / Q5_K / Q6_K matrices"); goto failed; }
+            const uint64_t E = a.expert_count, Fe = a.expert_feed_forward_length, Fs = a.expert_shared_feed_forward_length;
+            MC(build_group(device, st, tm, {blk(il, "ffn_gate_exps.weight"), blk(il, "ffn_gate_shexp.weight"), blk(il, "ffn_up_exps.weight"),
+                                           blk(il, "ffn_up_shexp.weight")}, H, {E * Fe, Fs, E * Fe, Fs}, &L.moe_gate_up, allow_ts));
+            MC(build_group(device, st, tm, {blk(il, "ffn_down_exps.weight")}, E * Fe, {H}, &L.moe_down, allow_ts, (int)(Fe / 256)));
+            MC(build_group(device, st, tm, {blk(il, "ffn_down_shexp.weight")}, Fs, {H}, &L.moe_down_sh, allow_ts));
+            {
+                float *rw = nullptr, *sgw = nullptr;
+                MC(upload_f32(device, st, tm, blk(il, "ffn_gate_inp.weight"), H * E, &rw));
+                s = upload_f32(device, st, tm, blk(il, "ffn_gate_inp_shexp.weight"), H, &sgw);
+                if (s != DFL_OK) { cudaFree(rw); goto failed; }
+                cudaMalloc(&L.router_w, (E + 1) * H * 4);
+                cudaMemcpy(L.router_w, rw, E * H * 4, cudaMemcpyDeviceToDevice);
+                cudaMemcpy(L.router_w + E * H, sgw, H * 4, cudaMemcpyDeviceToDevice);
+                cudaFree(rw);
+                cudaFree(sgw);
+            }
+            m->verify_weight_bytes += L.moe_gate_up.ggml_bytes() + L.moe_down.ggml_bytes() + L.moe_down_sh.ggml_bytes() + (E + 1) * H * 4;
+        } else {
+            MC(build_group(device, st, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up, allow_ts));
+            MC(build_group(device, st, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down, allow_ts));
+            m->verify_weight_bytes += L.gate_up.ggml_bytes() + L.down.ggml_bytes();
+        }
     }
 #undef MC
     cudaDeviceSynchronize();
@@ -387,6 +440,8 @@ void dfl_model_destroy(dfl_model* m) {
     cudaSetDevice(m->device);
     for (auto& L : m->layers) {
         L.qkv.release(); L.wo.release(); L.in_qkv_z.release(); L.w_out.release(); L.gate_up.release(); L.down.release();
+        L.moe_gate_up.release(); L.moe_down.release(); L.moe_down_sh.release();
+        cudaFree(L.router_w);
         for (float* p : {L.attn_norm_w, L.post_norm_w, L.q_norm_w, L.k_norm_w, L.w_ab, L.a_log, L.dt_bias, L.conv_w, L.ssm_norm_w})
             if (p) cudaFree(p);
     }
@@ -514,7 +569,11 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
     const uint64_t q_dim = (uint64_t)a.n_q_heads * a.attn_head_dim, v_dim = (uint64_t)gg.n_v * 128;
     uint64_t part = 0;
     auto upd = [&](const MatGroup& g) { part = std::max<uint64_t>(part, (uint64_t)g.splits * MAX_ROWS * g.total_cols); };
-    for (auto& L : m->layers) { upd(L.qkv); upd(L.wo); upd(L.in_qkv_z); upd(L.w_out); upd(L.gate_up); upd(L.down); }
+    for (auto& L : m->layers) {
+        upd(L.qkv); upd(L.wo); upd(L.in_qkv_z); upd(L.w_out); upd(L.gate_up); upd(L.down); upd(L.moe_gate_up);
+        // the experts' and the shared expert's down projections write their partial slices one after the other
+        part = std::max<uint64_t>(part, (uint64_t)(L.moe_down.splits + L.moe_down_sh.splits) * MAX_ROWS * H);
+    }
     if (m->lm_head.splits > 1) upd(m->lm_head);
     sc->part_floats = part;
     bool ok = true;
@@ -531,7 +590,14 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
     alloc(&sc->sumsq, (H / GLUE_COLS) * MAX_ROWS * 4);
     const uint64_t chunk = (uint64_t)std::max(act_chunk_bytes(ACT_F16), act_chunk_bytes(ACT_TS));
     alloc(&sc->acts_h, H / TILE_K * chunk);
-    alloc(&sc->acts_f, F / TILE_K * chunk);
+    const uint64_t f_inner = a.expert_count > 0 ? (uint64_t)a.expert_count * a.expert_feed_forward_length + a.expert_shared_feed_forward_length : F;
+    alloc(&sc->acts_f, f_inner / TILE_K * chunk);
+    if (a.expert_count > 0) {
+        alloc(&sc->route_logits, (size_t)MAX_ROWS * (a.expert_count + 1) * 4);
+        alloc(&sc->route_w, (size_t)MAX_ROWS * a.expert_count * 4);
+        alloc(&sc->route_sg, MAX_ROWS * 4);
+        alloc(&sc->route_idx, (size_t)MAX_ROWS * a.expert_used_count * 4);
+    }
     alloc(&sc->acts_v, std::max(q_dim, v_dim) / TILE_K * chunk);
     alloc(&sc->q_rot, MAX_ROWS * q_dim * 4);
     alloc(&sc->gate, MAX_ROWS * q_dim * 4);

@@ -14,7 +14,7 @@ namespace dfl {
 dfl_status use_device(int device);
 dfl_status check_dev_err(cudaStream_t st, int* dev_err);
 dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, const void* data, uint64_t n_bytes, bool on_device,
-                          cudaStream_t st, QMatrix* m, bool allow_ts = false);
+                          cudaStream_t st, QMatrix* m, bool allow_ts = false, int kb_group = 0);
 void qmatrix_release(QMatrix* m);
 
 // Several matrices that consume the same activations and write side by side into one
@@ -37,7 +37,7 @@ struct TensorMap {
 // Builds a MatGroup from named tensors [n_in, n_out]; consecutive tensors of one dtype are
 // concatenated row-wise into one resident matrix (one kernel launch instead of several).
 dfl_status build_group(int device, cudaStream_t st, const TensorMap& tm, const std::vector<std::string>& names, uint64_t n_in,
-                       const std::vector<uint64_t>& n_outs, MatGroup* out, bool allow_ts = false);
+                       const std::vector<uint64_t>& n_outs, MatGroup* out, bool allow_ts = false, int kb_group = 0);
 // Uploads a small tensor as f32 (norm weights, biases, f32 projections); any ggml dtype.
 dfl_status upload_f32(int device, cudaStream_t st, const TensorMap& tm, const std::string& name, uint64_t n_expected, float** out);
 
@@ -56,6 +56,12 @@ struct LayerW {
     // dense FFN
     MatGroup gate_up;
     MatGroup down;
+    // routed experts + shared expert (arch.expert_count > 0): gate|up of all experts and of the shared expert in
+    // one group (columns: E*F' expert gates, F_sh shared gate, E*F' expert ups, F_sh shared up), the experts' down
+    // projections as one matrix over n_in = E*F', the shared expert's down, and the f32 router with the shared
+    // expert's gate vector as its last row [E + 1][H]
+    MatGroup moe_gate_up, moe_down, moe_down_sh;
+    float* router_w = nullptr;
 };
 
 }  // namespace dfl
@@ -113,6 +119,9 @@ struct dfl_scratch {
     std::vector<float*> qkv_raw, conv_pre, q_n, k_n, v, ab;
     float *logits = nullptr, *gap = nullptr;
     int32_t* argmax = nullptr;
+    // routed experts: router logits [16][E + 1], dense route weights [16][E], shared-expert gates [16], chosen ids [16][k]
+    float *route_logits = nullptr, *route_w = nullptr, *route_sg = nullptr;
+    int32_t* route_idx = nullptr;
     void* am_scratch = nullptr;
     float* capture = nullptr;  // [16][k][H]
     int32_t* tokens_dev = nullptr;

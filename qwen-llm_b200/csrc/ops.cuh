@@ -91,11 +91,21 @@ struct GlueParams {
     float* capture = nullptr;     // optional copy of v: capture[tok * ld_capture + col]
     int ld_capture = 0;
     int swiglu_f = 0;
+    // routed experts (GLUE_SWIGLU only): column c < route_e * route_f belongs to expert c / route_f and is
+    // multiplied by route_w[tok][expert]; the columns after them (the shared expert) by route_sg[tok]
+    const float* route_w = nullptr;
+    const float* route_sg = nullptr;
+    int route_e = 0, route_f = 0;
     int n_rows = 0;
     int* err = nullptr;
 };
 // k = number of columns (multiple of 256)
 dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k);
+// Softmax + top-k routing of n_rows tokens over n_expert experts; logits[tok][n_expert] is the extra router row of
+// the shared expert's gate.  Writes route_w[16][n_expert] (zeros for experts not chosen), shared_gate[16],
+// route_idx[16][n_used].
+dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_expert, int n_used, int n_rows, float* route_w,
+                            float* shared_gate, int32_t* route_idx);
 
 // x[tok][0..h) = decoded row tokens[tok] of a ggml matrix [vocab][h] (kernel_get_rows_*,
 // kernels/elementwise.metal:727-958).  tokens live on the device.

@@ -70,9 +70,23 @@ def target_tensors(arch, seed=0, std=0.02, embd_dtype=orc.Q4_K, head_dtype=orc.Q
             vec(b + "ssm_dt.bias", rng.uniform(-1.0, 1.0, n_v))
             T.append((b + "ssm_conv1d.weight", orc.F32, [4, conv_dim], (rng.standard_normal((conv_dim, 4)) * 0.3).astype(np.float32).view(np.uint8)))
             norm(b + "ssm_norm.weight", 128)
-        mat(b + "ffn_gate.weight", orc.Q4_K, H, F)
-        mat(b + "ffn_up.weight", orc.Q4_K, H, F)
-        mat(b + "ffn_down.weight", orc.Q6_K, F, H)
+        if arch.expert_count > 0:
+            # routed experts stacked along the last ggml dimension (expert-major contiguous) + one shared expert
+            E, Fe, Fs = arch.expert_count, arch.expert_feed_forward_length, arch.expert_shared_feed_forward_length
+            T.append((b + "ffn_gate_inp.weight", orc.F32, [H, E], (rng.standard_normal((E, H)) * 0.5).astype(np.float32).view(np.uint8)))
+            for nm in ("ffn_gate_exps.weight", "ffn_up_exps.weight"):
+                w = (rng.standard_normal((E * Fe, H)) * std).astype(np.float32)
+                T.append((b + nm, orc.Q4_K, [H, Fe, E], orc.quantize(orc.Q4_K, w)))
+            w = (rng.standard_normal((E * H, Fe)) * std).astype(np.float32)
+            T.append((b + "ffn_down_exps.weight", orc.Q6_K, [Fe, H, E], orc.quantize(orc.Q6_K, w)))
+            vec(b + "ffn_gate_inp_shexp.weight", rng.standard_normal(H) * 0.1)
+            mat(b + "ffn_gate_shexp.weight", orc.Q4_K, H, Fs)
+            mat(b + "ffn_up_shexp.weight", orc.Q4_K, H, Fs)
+            mat(b + "ffn_down_shexp.weight", orc.Q6_K, Fs, H)
+        else:
+            mat(b + "ffn_gate.weight", orc.Q4_K, H, F)
+            mat(b + "ffn_up.weight", orc.Q4_K, H, F)
+            mat(b + "ffn_down.weight", orc.Q6_K, F, H)
     return T
 
 

@@ -164,3 +164,34 @@ def test_injected_completion_failure_poisons_session(tiny):
         pkg.packed_verify(gm, a, sa, [], [1, 2, 3], 3)
     assert e.value.name == "POISONED"
     a.close(); sa.close()
+
+
+def test_routed_expert_ffn_matches_oracle():
+    # forward.rs:749-824 (softmax over all experts, top-k by probability then index, renormalised weights, shared
+    # expert behind a sigmoid gate) on a small MoE hybrid; also the packed rows against single-token steps, bitwise
+    arch = modelgen.tiny_arch(expert_count=8, expert_used_count=2, expert_feed_forward_length=256,
+                              expert_shared_feed_forward_length=256)
+    T = modelgen.target_tensors(arch, seed=11)
+    om = modelgen.OracleModel(arch, T)
+    gm = pkg.Model(arch, T)
+    rng = np.random.default_rng(5)
+    sess, scr = pkg.Session(gm, 64, False), pkg.Scratch(gm, 16, 1)
+    ost = om.new_state(64, False)
+    start = 0
+    for n in (16, 3):
+        tokens = rng.integers(0, arch.vocab_size, size=n)
+        want_logits, _ = oracle_block(om, ost, tokens, start, [arch.n_layer - 1])
+        am, gap, logits = pkg.packed_verify(gm, sess, scr, [arch.n_layer - 1], tokens, start, want_logits=True)
+        np.testing.assert_allclose(logits, want_logits, rtol=RTOL, atol=ATOL)
+        start += n
+    # packed == sequential single-token steps, bitwise
+    sess2, scr2 = pkg.Session(gm, 64, False), pkg.Scratch(gm, 16, 1)
+    tokens = rng.integers(0, arch.vocab_size, size=6)
+    _, _, packed = pkg.packed_verify(gm, sess2, scr2, [0], tokens, 0, want_logits=True)
+    sess3 = pkg.Session(gm, 64, False)
+    for i, t in enumerate(tokens):
+        row, _ = pkg.single_token(gm, sess3, scr2, [0], int(t), i)
+        assert row.tobytes() == packed[i].tobytes()
+    for o in (sess, sess2, sess3, scr, scr2):
+        o.close()
+    gm.close()
