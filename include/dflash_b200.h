@@ -201,7 +201,11 @@ dfl_status dfl_c1_run_resident(dfl_c1* p, int32_t n_rows, int32_t iters, float* 
 
 /* ---- model / drafter / sessions ---------------------------------------- */
 /* MetalModel::load  metal_forward/mod.rs:443-454 (tensor names follow
- * crates/qwen-llm/src/loader.rs:438-611). */
+ * crates/qwen-llm/src/loader.rs:438-611).  With arch.expert_count > 0 every
+ * layer's FFN is the routed-expert block of forward.rs:749-824 and the table
+ * must hold ffn_gate_inp, ffn_{gate,up,down}_exps (experts stacked along the
+ * last ggml dimension), ffn_gate_inp_shexp and ffn_{gate,up,down}_shexp;
+ * expert widths must be multiples of 256 and the matrices Q4_K / Q5_K / Q6_K. */
 dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors,
                             uint64_t n_tensors, dfl_model** out);
 void dfl_model_destroy(dfl_model* m);
