@@ -315,7 +315,7 @@ def main():
         line = run_c1(args, rank, world, local)
     elif args.workload == "gemm":
         line = run_gemm(args, local)
-    elif args.workload == "c2v":
+    elif args.workload in ("c2v", "c4v"):
         line = importlib.import_module("bench_c2").run_verify_only(args, rank, world, local)
     else:
         c2 = importlib.import_module("bench_c2")

@@ -309,15 +309,17 @@ def run(args, rank, world, device):
 
 
 def run_verify_only(args, rank, world, device):
-    """Workload c2v: packed verify steps only (16 rows, context 16..), for kernel profiling on the real shapes."""
+    """Workloads c2v / c4v: packed verify steps only (16 rows, context 16..), for kernel profiling on the real shapes
+    of config 2 (dense 9B-class hybrid) or config 4 (35B-A3B-shaped routed-expert hybrid, all experts on one GPU)."""
     bench = importlib.import_module("bench")
     pkg, syn = _pkg(), _syn()
-    arch = syn.arch_9b()
+    moe = args.workload == "c4v"
+    arch = syn.arch_35b_a3b() if moe else syn.arch_9b()
     ents = syn.target_entries(arch, seed=100, device=device)
     model = syn.build_model(arch, ents, device)
     syn.free_entries(ents, device)
     sess, scr = pkg.Session(model, 1024, True), pkg.Scratch(model, 16, 5)
-    ids = [5, 12, 18, 25, 31]
+    ids = [7, 15, 23, 31, 39] if moe else [5, 12, 18, 25, 31]
     rng = np.random.default_rng(0)
     pos = 0
     for _ in range(max(args.warmup, 1)):
@@ -337,6 +339,7 @@ def run_verify_only(args, rank, world, device):
     peak, kind = bench.measured_peaks()
     vb = model.verify_weight_bytes()
     return {"metric": "verify_ms", "value": wall * 1e3, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": wall * 1e3, "higher_is_better": False, "config": {"workload": "c2v: packed verify only, 16 rows"},
+            "ms_per_step": wall * 1e3, "higher_is_better": False, "config": {"workload": ("c4v: packed verify only, 16 rows, 256 experts top-8 + shared, every expert streamed" if moe
+                                    else "c2v: packed verify only, 16 rows")},
             "roofline": {"bound": "hbm", "achieved": vb / wall / 1e9, "peak": peak, "unit": "GB/s", "frac": vb / wall / 1e9 / peak,
                          "traffic": None, "peak_kind": kind}, "gpu_launches": int(pkg.launch_count() - launches0), **extra}

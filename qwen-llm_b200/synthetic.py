@@ -25,6 +25,17 @@ def arch_9b():
     return a
 
 
+def arch_35b_a3b():
+    """BASELINE config 4: 35B-A3B-shaped qwen35moe hybrid (256 routed experts top-8 + one shared expert)."""
+    a = pkg.Arch()
+    for k, v in dict(n_layer=40, hidden_size=2048, intermediate_size=0, vocab_size=151936, full_attention_interval=4,
+                     n_q_heads=16, n_kv_heads=2, attn_head_dim=256, rope_theta=10000000.0, partial_rotary_factor=0.25,
+                     gdn_n_v_heads=32, gdn_n_k_heads=16, gdn_head_dim=128, gdn_conv_kernel=4, expert_count=256, expert_used_count=8,
+                     expert_feed_forward_length=512, expert_shared_feed_forward_length=512).items():
+        setattr(a, k, v)
+    return a
+
+
 def dflash_config_9b(arch):
     """5-layer DFlash-1 shaped drafter: block 16, K=5 evenly spaced tap layers, SWA 2048 on all but the last layer."""
     c = pkg.DFlashConfig()
@@ -56,9 +67,9 @@ def target_entries(arch, seed=0, std=0.02, device=0, layers=None):
     E = []
     counter = [seed * 1000003 + 17]
 
-    def mat(name, dtype, n_in, n_out, s=std):
+    def mat(name, dtype, n_in, n_out, s=std, shape=None):
         counter[0] += 1
-        E.append(pkg.synth_tensor(name, dtype, n_in, n_out, counter[0], s, device))
+        E.append(pkg.synth_tensor(name, dtype, n_in, n_out, counter[0], s, device, shape))
 
     def vec(name, values, shape=None):
         a = np.ascontiguousarray(values, dtype=np.float32)
@@ -88,9 +99,21 @@ def target_entries(arch, seed=0, std=0.02, device=0, layers=None):
             vec(b + "ssm_dt.bias", rng.uniform(-1.0, 1.0, n_v))
             vec(b + "ssm_conv1d.weight", rng.standard_normal((conv_dim, 4)) * 0.3, [4, conv_dim])
             vec(b + "ssm_norm.weight", np.ones(128))
-        mat(b + "ffn_gate.weight", Q4_K, H, F)
-        mat(b + "ffn_up.weight", Q4_K, H, F)
-        mat(b + "ffn_down.weight", Q6_K, F, H)
+        if arch.expert_count > 0:
+            # experts stacked along the last ggml dimension: expert gate/up Q4_K, down Q6_K, router f32 (SURVEY 8d mix)
+            ne, fe, fs = arch.expert_count, arch.expert_feed_forward_length, arch.expert_shared_feed_forward_length
+            mat(b + "ffn_gate_inp.weight", F32, H, ne, 0.5)
+            mat(b + "ffn_gate_exps.weight", Q4_K, H, ne * fe, shape=[H, fe, ne])
+            mat(b + "ffn_up_exps.weight", Q4_K, H, ne * fe, shape=[H, fe, ne])
+            mat(b + "ffn_down_exps.weight", Q6_K, fe, ne * H, shape=[fe, H, ne])
+            vec(b + "ffn_gate_inp_shexp.weight", rng.standard_normal(H) * 0.1)
+            mat(b + "ffn_gate_shexp.weight", Q4_K, H, fs)
+            mat(b + "ffn_up_shexp.weight", Q4_K, H, fs)
+            mat(b + "ffn_down_shexp.weight", Q6_K, fs, H)
+        else:
+            mat(b + "ffn_gate.weight", Q4_K, H, F)
+            mat(b + "ffn_up.weight", Q4_K, H, F)
+            mat(b + "ffn_down.weight", Q6_K, F, H)
     return E
 
 
