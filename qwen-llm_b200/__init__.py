@@ -232,12 +232,26 @@ def make_tensor_table(tensors):
     return arr, keep
 
 
+def ep_unique_id():
+    """128-byte NCCL id (call on one rank, hand to every rank of the expert-parallel group)."""
+    buf = (C.c_uint8 * 128)()
+    check(lib().dfl_ep_unique_id(buf))
+    return bytes(buf)
+
+
 class Model:
-    def __init__(self, arch: Arch, tensors, device=0):
+    def __init__(self, arch: Arch, tensors, device=0, ep=None):
+        """ep = (rank, world, nccl_id) builds the expert-parallel slice of a routed-expert model."""
         arr, keep = make_tensor_table(tensors)
         self.arch, self.device = arch, device
         self.h = C.c_void_p()
-        check(lib().dfl_model_create(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(tensors)), C.byref(self.h)))
+        if ep is None:
+            check(lib().dfl_model_create(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(tensors)), C.byref(self.h)))
+        else:
+            rank, world, nccl_id = ep
+            idb = (C.c_uint8 * 128).from_buffer_copy(nccl_id)
+            check(lib().dfl_model_create_ep(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(tensors)), C.c_int32(rank),
+                                            C.c_int32(world), idb, C.byref(self.h)))
 
     def verify_weight_bytes(self):
         return int(lib().dfl_model_verify_weight_bytes(self.h))

@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = silu_f(g[j]) * u[j];
             if (p.route_w) {
-                const float w = col0 < p.route_e * p.route_f ? p.route_w[tok * p.route_e + col0 / p.route_f] : p.route_sg[tok];
+                const float w = col0 < p.route_n * p.route_f ? p.route_w[tok * p.route_e + p.route_e0 + col0 / p.route_f] : p.route_sg[tok];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) v[j] *= w;
             }

@@ -220,11 +220,12 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         const bool moe = a.expert_count > 0;
         DFL_CHECK(norm_glue(sc->part, out_proj->splits, (int)out_proj->total_cols, L.post_norm_w, moe, nullptr));
         int down_splits;
+        const float* moe_part = sc->part;
         if (moe) {
             // routed experts + shared expert (forward.rs:749-824): route, then every expert of the layer as two large
             // few-row GEMMs; the glue zeroes the inner columns of the experts a token did not choose
-            const int E = (int)a.expert_count, Fe = (int)a.expert_feed_forward_length, Fs = (int)a.expert_shared_feed_forward_length;
-            const int inner = E * Fe + Fs;
+            const int E = (int)a.expert_count, Fe = (int)a.expert_feed_forward_length, Fs = (int)m->ep_fs, En = (int)m->ep_n;
+            const int inner = En * Fe + Fs;
             DFL_CHECK(launch_small_matmul(st, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
             DFL_CHECK(launch_moe_route(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
             DFL_CHECK(launch_group(st, L.moe_gate_up, sc->acts_h, sc->part, ep_norm, s->err));
@@ -233,6 +234,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             p.part = sc->part; p.splits = L.moe_gate_up.splits; p.ld_part = (int)L.moe_gate_up.total_cols;
             p.swiglu_f = inner;
             p.route_w = sc->route_w; p.route_sg = sc->route_sg; p.route_e = E; p.route_f = Fe;
+            p.route_e0 = (int)m->ep_e0; p.route_n = En;
             p.pre_scale = 1.0f / 64.0f;
             p.acts = sc->acts_f; p.bf3 = m->act_layout;
             p.n_rows = (int)n; p.err = s->err;
@@ -240,9 +242,19 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             GemmEpilogue ep_down;
             ep_down.out_scale = 64.0f;
             DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part, ep_down, s->err));
-            DFL_CHECK(launch_group(st, L.moe_down_sh, sc->acts_f + (uint64_t)(E * Fe / TILE_K) * act_chunk_bytes(m->act_layout),
-                                   sc->part + (uint64_t)L.moe_down.splits * MAX_ROWS * H, ep_down, s->err));
-            down_splits = L.moe_down.splits + L.moe_down_sh.splits;
+            down_splits = L.moe_down.splits;
+            if (Fs > 0) {
+                DFL_CHECK(launch_group(st, L.moe_down_sh, sc->acts_f + (uint64_t)(En * Fe / TILE_K) * act_chunk_bytes(m->act_layout),
+                                       sc->part + (uint64_t)L.moe_down.splits * MAX_ROWS * H, ep_down, s->err));
+                down_splits += L.moe_down_sh.splits;
+            }
+            if (m->ep_world > 1) {
+                // sum this rank's slices, then over the ranks: every rank continues with the same [16][H] block output
+                DFL_CHECK(launch_reduce_partials(st, sc->part, down_splits, MAX_ROWS, H, sc->moe_out, (int)H));
+                DFL_CHECK(ep_all_reduce_sum(m->ep_comm, sc->moe_out, (size_t)MAX_ROWS * H, st));
+                moe_part = sc->moe_out;
+                down_splits = 1;
+            }
         } else {
         // dense SwiGLU FFN (forward.rs:725-747)
         DFL_CHECK(launch_group(st, L.gate_up, sc->acts_h, sc->part, ep_norm, s->err));
@@ -267,7 +279,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         const bool last = il + 1 == a.n_layer;
         const float* next_w = last ? m->out_norm_w : m->layers[il + 1].attn_norm_w;
         const bool next_gdn = !last && !m->layers[il + 1].is_attn;
-        DFL_CHECK(norm_glue(sc->part, down_splits, (int)H, next_w, next_gdn, cap));
+        DFL_CHECK(norm_glue(moe_part, down_splits, (int)H, next_w, next_gdn, cap));
         if (cap) {
             // duplicate slots (same layer listed twice) get a device copy of the first one
             bool first = true;
@@ -304,9 +316,15 @@ using namespace dfl;
 
 extern "C" {
 
-dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors, uint64_t n_tensors, dfl_model** out) {
+}  // extern "C"
+
+static dfl_status model_create_impl(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors, uint64_t n_tensors, int ep_rank,
+                                    int ep_world, const uint8_t* nccl_id, dfl_model** out) {
     if (!arch || !tensors || !out) return fail(DFL_ERR_BAD_ARG, "model_create: null argument");
     *out = nullptr;
+    if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world) return fail(DFL_ERR_BAD_ARG, "model_create: expert-parallel rank / world");
+    if (ep_world > 1 && (arch->expert_count == 0 || arch->expert_count % ep_world || !nccl_id))
+        return fail(DFL_ERR_BAD_ARG, "model_create: expert parallelism needs a routed-expert model whose expert count divides by the world size");
     DFL_CHECK(use_device(device));
     const dfl_arch& a = *arch;
     if (a.n_layer == 0 || a.hidden_size % 256 || a.hidden_size == 0) return fail(DFL_ERR_BAD_SHAPE, "model_create: hidden size must be a positive multiple of 256");
@@ -327,6 +345,13 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
     }
     auto* m = new dfl_model();
     m->device = device;
+    m->ep_rank = ep_rank;
+    m->ep_world = ep_world;
+    m->ep_n = arch->expert_count / (uint32_t)ep_world;
+    m->ep_e0 = (uint32_t)ep_rank * m->ep_n;
+    m->ep_fs = ep_rank == 0 ? arch->expert_shared_feed_forward_length : 0;
+    std::vector<dfl_tensor> sliced;   // this rank's views of the stacked expert tensors
+    sliced.reserve(3 * (size_t)arch->n_layer);
     // One kernel family per model: the tensor-memory GEMM when every 2-D quantised tensor has a
     // row-lane layout (Q4_K / Q5_K / Q6_K), else the mma.sync kernel for all of them, so that every
     // packed-activation buffer has a single format.  DFL_GEMM_PATH=legacy forces the latter.
@@ -403,11 +428,30 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
         if (a.expert_count > 0) {
             // forward.rs:749-824; tensor shapes as in loader.rs (experts stacked along the last ggml dimension)
             if (!allow_ts) { s = fail(DFL_ERR_UNSUPPORTED, "model_create: the routed-expert FFN needs Q4_K / Q5_K / Q6_K matrices"); goto failed; }
-            const uint64_t E = a.expert_count, Fe = a.expert_feed_forward_length, Fs = a.expert_shared_feed_forward_length;
-            MC(build_group(device, st, tm, {blk(il, "ffn_gate_exps.weight"), blk(il, "ffn_gate_shexp.weight"), blk(il, "ffn_up_exps.weight"),
-                                           blk(il, "ffn_up_shexp.weight")}, H, {E * Fe, Fs, E * Fe, Fs}, &L.moe_gate_up, allow_ts));
-            MC(build_group(device, st, tm, {blk(il, "ffn_down_exps.weight")}, E * Fe, {H}, &L.moe_down, allow_ts, (int)(Fe / 256)));
-            MC(build_group(device, st, tm, {blk(il, "ffn_down_shexp.weight")}, Fs, {H}, &L.moe_down_sh, allow_ts));
+            const uint64_t E = a.expert_count, Fe = a.expert_feed_forward_length, Fs = m->ep_fs, En = m->ep_n;
+            if (ep_world > 1) {
+                // experts are stacked along the last ggml dimension: this rank's range is one contiguous byte range
+                for (const char* nm : {"ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"}) {
+                    const dfl_tensor* t = tm.find(blk(il, nm));
+                    if (!t) { s = fail(DFL_ERR_MISSING_TENSOR, "missing tensor " + blk(il, nm)); goto failed; }
+                    if (t->n_dims != 3 || t->shape[2] != E || t->n_bytes % E) { s = fail(DFL_ERR_BAD_SHAPE, blk(il, nm) + ": expected [.., .., n_expert]"); goto failed; }
+                    dfl_tensor v = *t;
+                    v.shape[2] = En;
+                    v.n_bytes = t->n_bytes / E * En;
+                    v.data = static_cast<const uint8_t*>(t->data) + t->n_bytes / E * m->ep_e0;
+                    sliced.push_back(v);
+                    tm.t[blk(il, nm)] = &sliced.back();
+                }
+            }
+            if (Fs > 0) {
+                MC(build_group(device, st, tm, {blk(il, "ffn_gate_exps.weight"), blk(il, "ffn_gate_shexp.weight"), blk(il, "ffn_up_exps.weight"),
+                                               blk(il, "ffn_up_shexp.weight")}, H, {En * Fe, Fs, En * Fe, Fs}, &L.moe_gate_up, allow_ts));
+                MC(build_group(device, st, tm, {blk(il, "ffn_down_shexp.weight")}, Fs, {H}, &L.moe_down_sh, allow_ts));
+            } else {
+                MC(build_group(device, st, tm, {blk(il, "ffn_gate_exps.weight"), blk(il, "ffn_up_exps.weight")}, H, {En * Fe, En * Fe},
+                               &L.moe_gate_up, allow_ts));
+            }
+            MC(build_group(device, st, tm, {blk(il, "ffn_down_exps.weight")}, En * Fe, {H}, &L.moe_down, allow_ts, (int)(Fe / 256)));
             {
                 float *rw = nullptr, *sgw = nullptr;
                 MC(upload_f32(device, st, tm, blk(il, "ffn_gate_inp.weight"), H * E, &rw));
@@ -428,11 +472,29 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
     }
 #undef MC
     cudaDeviceSynchronize();
+    if (ep_world > 1) {
+        s = ep_comm_create(ep_rank, ep_world, nccl_id, &m->ep_comm);
+        if (s != DFL_OK) goto failed;
+    }
     *out = m;
     return DFL_OK;
 failed:
     dfl_model_destroy(m);
     return s;
+}
+
+extern "C" {
+
+dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors, uint64_t n_tensors, dfl_model** out) {
+    return model_create_impl(device, arch, tensors, n_tensors, 0, 1, nullptr, out);
+}
+dfl_status dfl_ep_unique_id(uint8_t* id_out) {
+    if (!id_out) return fail(DFL_ERR_BAD_ARG, "ep_unique_id: null argument");
+    return ep_unique_id(id_out);
+}
+dfl_status dfl_model_create_ep(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors, uint64_t n_tensors, int32_t ep_rank,
+                               int32_t ep_world, const uint8_t* nccl_id, dfl_model** out) {
+    return model_create_impl(device, arch, tensors, n_tensors, ep_rank, ep_world, nccl_id, out);
 }
 
 void dfl_model_destroy(dfl_model* m) {
@@ -446,6 +508,7 @@ void dfl_model_destroy(dfl_model* m) {
             if (p) cudaFree(p);
     }
     m->lm_head.release();
+    ep_comm_destroy(m->ep_comm);
     if (m->embd_ggml) cudaFree(m->embd_ggml);
     if (m->out_norm_w) cudaFree(m->out_norm_w);
     delete m;
@@ -590,12 +653,13 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
     alloc(&sc->sumsq, (H / GLUE_COLS) * MAX_ROWS * 4);
     const uint64_t chunk = (uint64_t)std::max(act_chunk_bytes(ACT_F16), act_chunk_bytes(ACT_TS));
     alloc(&sc->acts_h, H / TILE_K * chunk);
-    const uint64_t f_inner = a.expert_count > 0 ? (uint64_t)a.expert_count * a.expert_feed_forward_length + a.expert_shared_feed_forward_length : F;
+    const uint64_t f_inner = a.expert_count > 0 ? (uint64_t)m->ep_n * a.expert_feed_forward_length + m->ep_fs : F;
     alloc(&sc->acts_f, f_inner / TILE_K * chunk);
     if (a.expert_count > 0) {
         alloc(&sc->route_logits, (size_t)MAX_ROWS * (a.expert_count + 1) * 4);
         alloc(&sc->route_w, (size_t)MAX_ROWS * a.expert_count * 4);
         alloc(&sc->route_sg, MAX_ROWS * 4);
+        alloc(&sc->moe_out, MAX_ROWS * H * 4);
         alloc(&sc->route_idx, (size_t)MAX_ROWS * a.expert_used_count * 4);
     }
     alloc(&sc->acts_v, std::max(q_dim, v_dim) / TILE_K * chunk);

@@ -66,8 +66,21 @@ struct LayerW {
 
 }  // namespace dfl
 
+namespace dfl {
+// expert parallelism (ep_nccl.cpp)
+dfl_status ep_unique_id(uint8_t* id_out);
+dfl_status ep_comm_create(int rank, int world, const uint8_t* id_bytes, void** comm_out);
+void ep_comm_destroy(void* comm);
+dfl_status ep_all_reduce_sum(void* comm, float* buf, size_t count, cudaStream_t st);
+}  // namespace dfl
+
 struct dfl_model {
     int device = 0;
+    // expert parallelism: this rank holds experts [ep_e0, ep_e0 + ep_n) of every layer (all of them when ep_world == 1)
+    // and, on rank 0 only, the shared expert; each block's output is summed over the ranks
+    int ep_rank = 0, ep_world = 1;
+    uint32_t ep_e0 = 0, ep_n = 0, ep_fs = 0;
+    void* ep_comm = nullptr;
     int act_layout = dfl::ACT_F16;  // packed-activation format all its GEMMs consume (follows the kernel family)
     dfl_arch arch{};
     std::vector<dfl::LayerW> layers;
@@ -120,7 +133,7 @@ struct dfl_scratch {
     float *logits = nullptr, *gap = nullptr;
     int32_t* argmax = nullptr;
     // routed experts: router logits [16][E + 1], dense route weights [16][E], shared-expert gates [16], chosen ids [16][k]
-    float *route_logits = nullptr, *route_w = nullptr, *route_sg = nullptr;
+    float *route_logits = nullptr, *route_w = nullptr, *route_sg = nullptr, *moe_out = nullptr;
     int32_t* route_idx = nullptr;
     void* am_scratch = nullptr;
     float* capture = nullptr;  // [16][k][H]

@@ -96,6 +96,7 @@ struct GlueParams {
     const float* route_w = nullptr;
     const float* route_sg = nullptr;
     int route_e = 0, route_f = 0;
+    int route_e0 = 0, route_n = 0;   // the inner columns hold experts route_e0 .. route_e0 + route_n - 1
     int n_rows = 0;
     int* err = nullptr;
 };
