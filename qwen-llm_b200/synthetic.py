@@ -159,13 +159,20 @@ class _Handle:
     pass
 
 
-def build_model(arch, entries, device=0):
+def build_model(arch, entries, device=0, ep=None):
+    """ep = (rank, world, nccl_id): the expert-parallel slice of a routed-expert model (see pkg.Model)."""
     import ctypes as C
     arr, keep = pkg.make_device_tensor_table(entries)
     m = pkg.Model.__new__(pkg.Model)
     m.arch, m.device = arch, device
     m.h = C.c_void_p()
-    pkg.check(pkg.lib().dfl_model_create(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(entries)), C.byref(m.h)))
+    if ep is None:
+        pkg.check(pkg.lib().dfl_model_create(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(entries)), C.byref(m.h)))
+    else:
+        rank, world, nccl_id = ep
+        idb = (C.c_uint8 * 128).from_buffer_copy(nccl_id)
+        pkg.check(pkg.lib().dfl_model_create_ep(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(entries)), C.c_int32(rank),
+                                                C.c_int32(world), idb, C.byref(m.h)))
     return m
 
 
