@@ -270,8 +270,11 @@ def run(args, rank, world, device):
         "config": {"workload": "c2: 9B-class hybrid Q4_K_M target (32 layers, GDN:attn 3:1, H 4096, FFN 12288, V 151936) + 5-layer bf16 DFlash drafter, "
                                "greedy, batch 1, prompt 512, block 16; replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step",
                    "l2": "5.1 GB of weights per verify >> 126 MB L2", "parallelism": f"dp{world}: one independent sequence per GPU, no collective"},
-        "roofline": {"bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s", "frac": gemm_gbs / peak, "traffic": None,
-                     "peak_kind": peak_kind, "kernel": "few-row GEMMs (gemm_ts_kernel for the Q4_K/Q5_K/Q6_K target, gemm_fewrow_kernel for the bf16 drafter), all launches of 5 outer steps (verify + draft), CUDA events per launch",
+        # DRAM bytes per launch: algorithmic bytes x 1.04, the dram-bytes / ggml-bytes ratio ncu measured for this kernel
+        # (profiles/gemm_ts_c1_ncu_full.md; the traffic grows with the bytes streamed)
+        "roofline": {"bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s", "frac": gemm_gbs / peak,
+                     "traffic": 1.04 * gemm_bytes / max(gemm_n, 1), "algorithmic_bytes_per_launch": gemm_bytes / max(gemm_n, 1),
+                     "peak_kind": peak_kind, "kernel": "few-row GEMMs (gemm_ts_kernel for the Q4_K/Q5_K/Q6_K target, gemm_tsb_kernel for the bf16 drafter), all launches of 5 outer steps (verify + draft), CUDA events per launch",
                      "launches_timed": gemm_n, "algorithmic_bytes_timed": gemm_bytes,
                      "verify_step": {"weight_bytes": vbytes, "ms": verify_ms, "GBps": vbytes / (verify_ms * 1e-3) / 1e9,
                                      "frac": vbytes / (verify_ms * 1e-3) / 1e9 / peak},

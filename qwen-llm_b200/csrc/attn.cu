@@ -13,8 +13,8 @@ namespace dfl {
 // ---- front: reduce GEMM partials, per-head RMSNorm, partial NeoX RoPE, KV append ---------
 // grid (heads = n_q + 2 n_kv, n_rows), block = 128 threads (4 warps cooperate on one head).
 __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, const float* part, int splits,
-                                                         int ld_part, const float* q_norm_w,
-                                                         const float* k_norm_w, uint32_t start, void* k_cache,
+                                                         int ld_part, const float* __restrict__ q_norm_w,
+                                                         const float* __restrict__ k_norm_w, uint32_t start, void* k_cache,
                                                          void* v_cache, int kv_f16, float* q_rot,
                                                          float* gate, const uint32_t* pos_override, long long cache_row0) {
     pdl_prologue();

@@ -16,7 +16,7 @@ namespace dfl {
 // grid = conv_dim / 128 (one q, k or v head per CTA), block 128 (one channel per thread).
 // All global loads are issued before the token recurrence starts.
 __global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* part, int splits, int ld_part, int n_rows,
-                                                        const float* conv_w, float* conv_state,
+                                                        const float* __restrict__ conv_w, float* conv_state,
                                                         float* qkv_raw, float* q_n, float* k_n,
                                                         float* v_out) {
     pdl_prologue();
@@ -119,7 +119,7 @@ dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const floa
 __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* state_in, float* state_out,
                                                        const float* q_n, const float* k_n,
                                                        const float* v, const float* ab,
-                                                       const float* dt_bias, const float* a_log, int n_rows,
+                                                       const float* __restrict__ dt_bias, const float* __restrict__ a_log, int n_rows,
                                                        float* o) {
     pdl_prologue();
     __shared__ float qs[MAX_ROWS][128], ks[MAX_ROWS][128], vs[MAX_ROWS][32], gs[MAX_ROWS], bs[MAX_ROWS], os[MAX_ROWS][32];
@@ -213,7 +213,7 @@ dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state
 // ---- post: gated RMSNorm + activation packing ----------------------------------------------
 // grid (n_v, 16), block 32: one warp per (head, token); lane owns 4 consecutive channels.
 __global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* o, const float* part_z, int splits,
-                                                      int ld_part, const float* norm_w, int n_rows, uint8_t* acts, int bf3,
+                                                      int ld_part, const float* __restrict__ norm_w, int n_rows, uint8_t* acts, int bf3,
                                                       int* err) {
     pdl_prologue();
     const int h = blockIdx.x, tok = blockIdx.y, lane = threadIdx.x;

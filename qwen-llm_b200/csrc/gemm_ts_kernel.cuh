@@ -51,8 +51,13 @@ constexpr int smem_bytes() {
 // named barrier 1: start-up of the unpacking warps (every one of them reaches it unconditionally)
 __device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
+#ifdef DFL_TS_MAXNREG
+#define TS_KERNEL_ATTR __maxnreg__(DFL_TS_MAXNREG)
+#else
+#define TS_KERNEL_ATTR __launch_bounds__(THREADS, 1)
+#endif
 template <int DT>
-__global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
+__global__ void TS_KERNEL_ATTR gemm_ts_kernel(const Params p) {
     using F = Fmt<DT>;
     constexpr int STAGES = F::STAGES, PASSES = F::PASSES;
     constexpr int OFF_RING = KC * ACTTS_CHUNK;
