@@ -195,3 +195,36 @@ def test_routed_expert_ffn_matches_oracle():
     for o in (sess, sess2, sess3, scr, scr2):
         o.close()
     gm.close()
+
+
+@pytest.mark.parametrize("kv_f16", [False, True])
+def test_verify_over_a_multi_chunk_kv_cache_with_rollback(tiny, kv_f16):
+    # long-context shape of the step in miniature: the block attends over several 64-position KV chunks (partial
+    # softmax per chunk + combine), a partial accept rolls KV and GDN state back, and the next block still matches
+    # the oracle fed with the accepted tokens only
+    arch, om, gm = tiny
+    rng = np.random.default_rng(9)
+    cap = 384
+    sess, scr = pkg.Session(gm, cap, kv_f16), pkg.Scratch(gm, 16, 1)
+    ost = om.new_state(cap, kv_f16)
+    pos = 0
+    while pos < 304:                                  # fill 4.75 chunks through the packed path
+        toks = rng.integers(0, arch.vocab_size, size=16)
+        pkg.packed_verify(gm, sess, scr, [3], toks, pos)
+        for i, t in enumerate(toks):
+            om.single_token(ost, t, pos + i, (), want_logits=False)
+        pos += 16
+    toks = rng.integers(0, arch.vocab_size, size=16)
+    want, _ = oracle_block(om, om.clone_state(ost), toks, pos, [3])
+    _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=True)
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+    n_keep = 5
+    pkg.restore_partial(gm, sess, scr, n_keep, pos)
+    for i in range(n_keep):
+        om.single_token(ost, toks[i], pos + i, (), want_logits=False)
+    pos += n_keep
+    toks = rng.integers(0, arch.vocab_size, size=16)
+    want, _ = oracle_block(om, ost, toks, pos, [3])
+    _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=True)
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+    sess.close(); scr.close()
