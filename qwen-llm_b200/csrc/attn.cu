@@ -94,7 +94,7 @@ dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, con
 template <typename KV, int HD>
 __global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float* q_rot, const KV* k_cache,
                                                          const KV* v_cache, uint32_t start, int n_rows,
-                                                         float* partials) {
+                                                         float* partials, int rows_per_cta) {
     pdl_prologue();
     extern __shared__ float sm[];
     constexpr int LD = HD + 1;
@@ -137,9 +137,10 @@ __global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float scale = 1.0f / sqrtf((float)HD);
-    // blockIdx.z selects a group of ATTN_ROW_GROUP query rows, so that short contexts still fill the GPU
-    const int q_lo = blockIdx.z * ATTN_ROW_GROUP * group;
-    const int q_hi = min(n_rows, ((int)blockIdx.z + 1) * ATTN_ROW_GROUP) * group;
+    // blockIdx.z selects a group of query rows: four per CTA at short context so that the GPU still fills, all sixteen
+    // once there are enough KV chunks (every row group re-reads the chunk, which is what long contexts must avoid)
+    const int q_lo = blockIdx.z * rows_per_cta * group;
+    const int q_hi = min(n_rows, ((int)blockIdx.z + 1) * rows_per_cta) * group;
     float* myq = qs + warp * HD;
     float* myp = ps + warp * ATTN_CHUNK;
     for (int qi = q_lo + warp; qi < q_hi; qi += 8) {
@@ -283,8 +284,13 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
         DFL_CUDA(cudaFuncSetAttribute(attn_chunk_kernel<KV, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = true;
     }
-    launch_kf(4, attn_chunk_kernel<KV, HD>, dim3(dim3((unsigned)n_chunks, (unsigned)g.n_kv, (unsigned)((n_rows + ATTN_ROW_GROUP - 1) / ATTN_ROW_GROUP))), dim3(256), smem, st, 
-        g, q_rot, reinterpret_cast<const KV*>(k_cache), reinterpret_cast<const KV*>(v_cache), start, n_rows, partials);
+    int rows_per_cta = (long long)n_chunks * g.n_kv >= 2 * 148 ? MAX_ROWS : ATTN_ROW_GROUP;
+    if (const char* e = getenv("DFL_ATTN_ROWS_PER_CTA")) {   // test hook: results must not depend on the grouping
+        const int v = atoi(e);
+        if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) rows_per_cta = v;
+    }
+    launch_kf(4, attn_chunk_kernel<KV, HD>, dim3((unsigned)n_chunks, (unsigned)g.n_kv, (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta)), dim3(256), smem, st,
+              g, q_rot, reinterpret_cast<const KV*>(k_cache), reinterpret_cast<const KV*>(v_cache), start, n_rows, partials, rows_per_cta);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

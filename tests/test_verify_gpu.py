@@ -228,3 +228,21 @@ def test_verify_over_a_multi_chunk_kv_cache_with_rollback(tiny, kv_f16):
     _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=True)
     np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
     sess.close(); scr.close()
+
+
+def test_attention_row_grouping_does_not_change_a_bit(tiny, monkeypatch):
+    # long contexts put all 16 rows of a block in one attention CTA per KV chunk, short ones four: same bits
+    arch, om, gm = tiny
+    rng = np.random.default_rng(13)
+    blocks = [rng.integers(0, arch.vocab_size, size=16) for _ in range(6)]
+    outs = []
+    for rows in ("4", "16"):
+        monkeypatch.setenv("DFL_ATTN_ROWS_PER_CTA", rows)
+        sess, scr = pkg.Session(gm, 128, True), pkg.Scratch(gm, 16, 1)
+        got = []
+        for i, b in enumerate(blocks):
+            _, _, lg = pkg.packed_verify(gm, sess, scr, [3], b, 16 * i, want_logits=True)
+            got.append(lg)
+        outs.append(np.concatenate(got))
+        sess.close(); scr.close()
+    assert outs[0].tobytes() == outs[1].tobytes()
