@@ -296,6 +296,7 @@ def main():
     ap.add_argument("--workload", default=os.environ.get("DFL_BENCH_WORKLOAD", "auto"))
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--gemm", default="q4_k:4096:24576", help="workload gemm only: dtype:n_in:n_out")
+    ap.add_argument("--ctx", type=int, default=131072, help="workload c5v only: context length filled before timing")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -315,7 +316,7 @@ def main():
         line = run_c1(args, rank, world, local)
     elif args.workload == "gemm":
         line = run_gemm(args, local)
-    elif args.workload in ("c2v", "c4v"):
+    elif args.workload in ("c2v", "c4v", "c5v"):
         line = importlib.import_module("bench_c2").run_verify_only(args, rank, world, local)
     else:
         c2 = importlib.import_module("bench_c2")

@@ -330,10 +330,14 @@ def run_verify_only(args, rank, world, device):
         ep = (rank, world, idt.cpu().numpy().tobytes())
     model = syn.build_model(arch, ents, device, ep)
     syn.free_entries(ents, device)
-    sess, scr = pkg.Session(model, 1024, True), pkg.Scratch(model, 16, 5)
+    ctx = int(getattr(args, "ctx", 0) or 0) if args.workload == "c5v" else 0
+    sess, scr = pkg.Session(model, max(1024, ctx + 16 * (args.steps + args.warmup + 2)), True), pkg.Scratch(model, 16, 5)
     ids = [7, 15, 23, 31, 39] if moe else [5, 12, 18, 25, 31]
     rng = np.random.default_rng(0)
     pos = 0
+    while pos < ctx:   # c5v: fill the fp16 KV cache (and the GDN state) with `ctx` random ids through the packed path
+        pkg.packed_verify(model, sess, scr, ids, rng.integers(0, arch.vocab_size, size=16), pos)
+        pos += 16
     for _ in range(max(args.warmup, 1)):
         pkg.packed_verify(model, sess, scr, ids, rng.integers(0, arch.vocab_size, size=16), pos)
         pos += 16
@@ -355,8 +359,14 @@ def run_verify_only(args, rank, world, device):
         extra = {"gemm_ms_per_step": ms / args.steps, "gemm_launches": n, "gemm_GBps": b / (ms * 1e-3) / 1e9}
     peak, kind = bench.measured_peaks()
     vb = model.verify_weight_bytes()
+    if ctx:   # the KV bytes one verify reads: attention layers x positions x (K + V) x n_kv x head_dim x 2 B
+        n_attn = sum(1 for il in range(arch.n_layer) if syn.is_attn(arch, il))
+        kvb = n_attn * (ctx + 16 * args.warmup) * 2 * arch.n_kv_heads * arch.attn_head_dim * 2
+        extra = {**extra, "kv_bytes_per_verify": kvb, "weight_bytes_per_verify": vb}
+        vb += kvb
     return {"metric": "verify_ms", "value": wall * 1e3, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": wall * 1e3, "higher_is_better": False, "config": {"workload": ("c4v: packed verify only, 16 rows, 256 experts top-8 + shared, every expert streamed" if moe
+                                    else f"c5v: packed verify only, 16 rows over a context of {ctx} positions (fp16 KV)" if ctx
                                     else "c2v: packed verify only, 16 rows")},
             "roofline": {"bound": "hbm", "achieved": vb / wall / 1e9, "peak": peak, "unit": "GB/s", "frac": vb / wall / 1e9 / peak,
                          "traffic": None, "peak_kind": kind}, "gpu_launches": int(pkg.launch_count() - launches0), **extra}
