@@ -193,15 +193,15 @@ __global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float
 // ---- combine + sigmoid gate + activation packing ---------------------------------------------
 // grid (n_q, n_rows), block 32: one warp per (row, q head); lane owns hd/32 consecutive dims.
 template <int HD>
-__global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* partials, int n_chunks_total,
+__global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* partials, int chunks_per_record,
                                                        const float* gate, uint32_t start, uint8_t* acts, int bf3,
                                                        float* out_f32, int* err) {
     pdl_prologue();
     constexpr int PER = HD / 32;  // 4 or 8
     const int qh = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
     const int group = g.n_q / g.n_kv, kvh = qh / group, qi = row * group + qh % group;
-    const int n_chunks = (int)((start + (uint32_t)row) / ATTN_CHUNK) + 1;  // chunks holding visible positions
-    (void)n_chunks_total;
+    // records holding visible positions: one per 64-position chunk (scalar kernel) or per span of chunks (tensor-core kernel)
+    const int n_chunks = (int)((start + (uint32_t)row) / ATTN_CHUNK) / chunks_per_record + 1;
     float M = -INFINITY;
     for (int c = lane; c < n_chunks; c += 32) {
         const float* rec = partials + (((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
@@ -298,11 +298,16 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
 
 dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
                               const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts, int bf3,
-                              float* out_f32, int* err) {
+                              float* out_f32, int* err, uint32_t kv_capacity) {
     if (g.hd != 128 && g.hd != 256) return fail(DFL_ERR_UNSUPPORTED, "attention: head_dim must be 128 or 256");
     const int n_chunks = (int)((start + (uint32_t)n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK);
     dfl_status s;
-    if (g.hd == 128) s = kv_f16 ? launch_chunk<__half, 128>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks)
+    int chunks_per_record = 1;
+    const char* tc_env = getenv("DFL_ATTN_TC");
+    if (attn_tc_supported(g, kv_f16) && !(tc_env && tc_env[0] == '0')) {
+        chunks_per_record = attn_tc_chunks_per_span(g, kv_capacity);
+        s = launch_attn_span_tc(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, chunks_per_record);
+    } else if (g.hd == 128) s = kv_f16 ? launch_chunk<__half, 128>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks)
                                 : launch_chunk<float, 128>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks);
     else s = kv_f16 ? launch_chunk<__half, 256>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks)
                     : launch_chunk<float, 256>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks);
@@ -311,8 +316,9 @@ dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q
         // rows of absent tokens must read as zero in the next GEMM
         DFL_CHECK(launch_acts_clear(st, acts, (uint64_t)g.n_q * g.hd / TILE_K * (uint64_t)act_chunk_bytes(bf3)));
     }
-    if (g.hd == 128) launch_kf(4, attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
-    else launch_kf(4, attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, n_chunks, gate, start, acts, bf3, out_f32, err);
+    (void)n_chunks;
+    if (g.hd == 128) launch_kf(4, attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
+    else launch_kf(4, attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

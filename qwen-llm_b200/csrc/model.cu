@@ -197,7 +197,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             DFL_CHECK(launch_attn_front(st, ag, true, sc->part, L.qkv.splits, (int)L.qkv.total_cols, L.q_norm_w, L.k_norm_w, start, (int)n,
                                         s->k_cache[ai], s->v_cache[ai], s->kv_f16, sc->q_rot, sc->gate, nullptr));
             DFL_CHECK(launch_attn_verify(st, ag, sc->q_rot, sc->gate, s->k_cache[ai], s->v_cache[ai], s->kv_f16, start, (int)n,
-                                         s->attn_partials, sc->acts_v, m->act_layout, nullptr, s->err));
+                                         s->attn_partials, sc->acts_v, m->act_layout, nullptr, s->err, s->kv_capacity));
             out_proj = &L.wo;
             ++ai;
         } else {

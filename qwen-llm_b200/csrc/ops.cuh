@@ -137,7 +137,12 @@ dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, con
 // 64-position chunk, then combine, sigmoid gate and activation packing for the o-projection.
 dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
                               const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts,
-                              int act_layout, float* out_f32, int* err);
+                              int act_layout, float* out_f32, int* err, uint32_t kv_capacity = 0);
+// tensor-core span kernel over an fp16 cache (attn_tc.cu)
+bool attn_tc_supported(const AttnGeom& g, bool kv_f16);
+int attn_tc_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity);
+dfl_status launch_attn_span_tc(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* k_cache, const void* v_cache,
+                               uint32_t start, int n_rows, float* partials, int chunks_per_span);
 uint64_t attn_partials_floats(const AttnGeom& g, uint32_t max_positions);
 
 // ---- gated delta net (gdn.cu) --------------------------------------------------

@@ -246,3 +246,51 @@ def test_attention_row_grouping_does_not_change_a_bit(tiny, monkeypatch):
         outs.append(np.concatenate(got))
         sess.close(); scr.close()
     assert outs[0].tobytes() == outs[1].tobytes()
+
+
+@pytest.fixture(scope="module")
+def tiny_g4():
+    # GQA group of four 128-wide heads over an fp16 cache: the geometry of the tensor-core attention kernel
+    arch = modelgen.tiny_arch(n_q_heads=4)
+    T = modelgen.target_tensors(arch, seed=21)
+    om = modelgen.OracleModel(arch, T)
+    gm = pkg.Model(arch, T)
+    yield arch, om, gm
+    gm.close()
+
+
+@pytest.mark.parametrize("cap", [384, 40000])
+def test_tensor_core_attention_matches_oracle_and_single_token_steps(tiny_g4, cap):
+    # cap 384: one 64-position chunk per record; cap 40000: several chunks per span (online softmax inside the CTA)
+    arch, om, gm = tiny_g4
+    rng = np.random.default_rng(31)
+    sess, scr = pkg.Session(gm, cap, True), pkg.Scratch(gm, 16, 1)
+    single, scr1 = pkg.Session(gm, cap, True), pkg.Scratch(gm, 16, 1)
+    ost = om.new_state(cap, True)
+    pos = 0
+    for blk_i in range(14):                          # 224 positions = 3.5 chunks
+        toks = rng.integers(0, arch.vocab_size, size=16)
+        check = blk_i in (0, 5, 13)
+        _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=check)
+        if check:
+            want, _ = oracle_block(om, om.clone_state(ost), toks, pos, [3])
+            np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+        for i, t in enumerate(toks):
+            om.single_token(ost, t, pos + i, (), want_logits=False)
+            row, _ = pkg.single_token(gm, single, scr1, [3], int(t), pos + i)
+            if check:
+                assert row.tobytes() == got[i].tobytes(), f"block {blk_i} row {i}"
+        pos += 16
+    # partial accept, then the next block still matches the oracle
+    toks = rng.integers(0, arch.vocab_size, size=16)
+    pkg.packed_verify(gm, sess, scr, [3], toks, pos)
+    pkg.restore_partial(gm, sess, scr, 7, pos)
+    for i in range(7):
+        om.single_token(ost, toks[i], pos + i, (), want_logits=False)
+    pos += 7
+    toks = rng.integers(0, arch.vocab_size, size=16)
+    want, _ = oracle_block(om, ost, toks, pos, [3])
+    _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=True)
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+    for o in (sess, scr, single, scr1):
+        o.close()
