@@ -18,13 +18,18 @@ namespace dfl {
 __global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* part, int splits, int ld_part, int n_rows,
                                                         const float* __restrict__ conv_w, float* conv_state,
                                                         float* qkv_raw, float* q_n, float* k_n,
-                                                        float* v_out) {
+                                                        float* v_out, float* conv_pre) {
     pdl_prologue();
     const int conv_dim = g.conv_dim();
     const int c = blockIdx.x * 128 + threadIdx.x;
     const int head = blockIdx.x;  // heads of 128 channels: [0, n_k) q, [n_k, 2 n_k) k, rest v
     const float4 w = *reinterpret_cast<const float4*>(conv_w + c * 4);
     float h0 = conv_state[0 * conv_dim + c], h1 = conv_state[1 * conv_dim + c], h2 = conv_state[2 * conv_dim + c];
+    if (conv_pre) {   // the pre-block rows a partial accept restores from
+        conv_pre[0 * conv_dim + c] = h0;
+        conv_pre[1 * conv_dim + c] = h1;
+        conv_pre[2 * conv_dim + c] = h2;
+    }
     float x[MAX_ROWS];
 #pragma unroll
     for (int i = 0; i < MAX_ROWS; ++i) x[i] = 0.f;
@@ -82,9 +87,10 @@ __global__ void __launch_bounds__(128) gdn_front_kernel(GdnGeom g, const float* 
 }
 
 dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
-                            const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v) {
+                            const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v, float* conv_pre) {
     if (g.hd != 128 || g.conv_k != 4) return fail(DFL_ERR_UNSUPPORTED, "gdn: head_dim must be 128 and conv kernel 4");
-    launch_kf(8, gdn_front_kernel, dim3(g.conv_dim() / 128), dim3(128), 0, st, g, part_qkv, splits, ld_part, n_rows, conv_w, conv_state, qkv_raw, q_n, k_n, v);
+    launch_kf(8, gdn_front_kernel, dim3(g.conv_dim() / 128), dim3(128), 0, st, g, part_qkv, splits, ld_part, n_rows, conv_w, conv_state, qkv_raw, q_n, k_n, v,
+              conv_pre);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

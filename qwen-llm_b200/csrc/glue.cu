@@ -126,6 +126,17 @@ __global__ void __launch_bounds__(512) small_matmul_kernel(const float* __restri
                                                            int ld_out) {
     pdl_prologue();
     const int j = blockIdx.x;
+    // per-token output scale first (16 threads per token, fixed tree), so that it overlaps the weight loads
+    __shared__ float scale_s[MAX_ROWS];
+    if (threadIdx.x < 256) {
+        const int tok = threadIdx.x >> 4, part = threadIdx.x & 15;
+        float ss = 0.f;
+        if (sumsq)
+            for (int i = part; i < n_sumsq; i += 16) ss += sumsq[i * MAX_ROWS + tok];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (part == 0) scale_s[tok] = sumsq ? out_scale * (1.0f / sqrtf(ss / norm_k + eps)) : out_scale;
+    }
     float acc[MAX_ROWS];
 #pragma unroll
     for (int r = 0; r < MAX_ROWS; ++r) acc[r] = 0.f;
@@ -153,13 +164,7 @@ __global__ void __launch_bounds__(512) small_matmul_kernel(const float* __restri
         float s = 0.f;
 #pragma unroll
         for (int wv = 0; wv < 16; ++wv) s += red[wv][r];
-        float sc = out_scale;
-        if (sumsq) {
-            float ss = 0.f;
-            for (int i = 0; i < n_sumsq; ++i) ss += sumsq[i * MAX_ROWS + r];
-            sc *= 1.0f / sqrtf(ss / norm_k + eps);
-        }
-        out[(uint64_t)r * ld_out + j] = s * sc;
+        out[(uint64_t)r * ld_out + j] = s * scale_s[r];
     }
 }
 

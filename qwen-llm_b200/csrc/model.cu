@@ -204,9 +204,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             const int cd = gg.conv_dim();
             DFL_CHECK(launch_group(st, L.in_qkv_z, sc->acts_h, sc->part, ep_norm, s->err));
             DFL_CHECK(launch_small_matmul(st, L.w_ab, sc->xn, (int)H, (int)n, H, 2 * gg.n_v, ep_norm, sc->ab[gi], 2 * gg.n_v));
-            DFL_CUDA(cudaMemcpyAsync(sc->conv_pre[gi], s->conv[gi], (size_t)3 * cd * 4, cudaMemcpyDeviceToDevice, st));
             DFL_CHECK(launch_gdn_front(st, gg, sc->part, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, (int)n, L.conv_w, s->conv[gi],
-                                       sc->qkv_raw[gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi]));
+                                       sc->qkv_raw[gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->conv_pre[gi]));
             const int cur = s->ssm_cur[gi];
             DFL_CHECK(launch_gdn_scan(st, gg, s->ssm[cur][gi], s->ssm[cur ^ 1][gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->ab[gi],
                                       L.dt_bias, L.a_log, (int)n, sc->o));

@@ -152,7 +152,7 @@ struct GdnGeom {
 };
 // conv1d + SiLU over the block, q/k L2 norm; keeps raw qkv rows for rollback; updates conv state in place.
 dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
-                            const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v);
+                            const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v, float* conv_pre = nullptr);
 // Sequential delta-rule scan over n_rows tokens from state_in to state_out (different buffers).
 dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state_in, float* state_out, const float* q_n,
                            const float* k_n, const float* v, const float* ab, const float* dt_bias, const float* a_log,
