@@ -118,6 +118,11 @@ typedef struct dfl_dflash_config {
     uint32_t n_target_layers;                          /* K */
     uint32_t target_layer_ids[DFL_MAX_TARGET_LAYERS];
     uint32_t layer_is_swa[DFL_MAX_DRAFTER_LAYERS];
+    /* DFlash 2 path selector (loader.rs:371-376, metadata dflash.selector_rank / dflash.selector_top_k); both 0 on
+     * a DFlash 1 drafter.  With a selector the tensor table must hold selector_hidden.weight [H, rank],
+     * selector_predecessor.weight and selector_successor.weight [rank, vocab] (loader.rs:1182-1230). */
+    uint32_t selector_rank;
+    uint32_t selector_top_k;   /* only 16 is supported, as in the reference (metal_dflash.rs:5011-5017) */
 } dfl_dflash_config;
 
 typedef struct dfl_model dfl_model;       /* MetalModel          metal_forward/mod.rs:443  */
@@ -128,6 +133,7 @@ typedef struct dfl_scratch dfl_scratch;   /* MetalDFlashVerifyScratch + LayerMaj
                                              metal_dflash.rs:6003, :8025                   */
 typedef struct dfl_qmatrix dfl_qmatrix;   /* one resident quantised matrix (MetalTensor)   */
 typedef struct dfl_sampler dfl_sampler;   /* Sampler             sampling.rs:305           */
+typedef struct dfl_codebook dfl_codebook; /* DFlash2Codebook     metal_dflash.rs:3163      */
 
 /* ---- library / diagnostics --------------------------------------------- */
 const char* dfl_version(void);
@@ -309,6 +315,54 @@ dfl_status dfl_dsession_reset(dfl_dsession* ds);
  * out_tokens[1..N) = per-row argmax; logits_host optional [N * vocab]. */
 dfl_status dfl_draft_block(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos,
                            int32_t* out_tokens, float* logits_host);
+/* On a drafter with a DFlash 2 selector dfl_draft_block returns the selector's greedy path
+ * (select_draft_path, metal_dflash.rs:17176-17251) instead of the per-row argmax. */
+
+/* ---- DFlash 2 path selector ---------------------------------------------- */
+/* kernel_topk16_f32 (kernels/dflash2.metal:96-170): per row the 16 best (id, value) pairs in
+ * descending order under the f32 total order, ties to the lower index; rows shorter than 16
+ * keep the sentinel (id -1, -inf) in the unfilled slots.  Host-to-host test entry. */
+dfl_status dfl_topk16(int32_t device, const float* x_host, int32_t n_rows, uint64_t n,
+                      int32_t* ids_out /* [n_rows][16] */, float* vals_out /* [n_rows][16] */);
+/* DFlash2Codebook::from_gguf (metal_dflash.rs:3180-3273): host copy of a [rank, n_rows]
+ * codebook, dtype Q4_K (rank 256 only) / Q8_0 / F32 / F16 / BF16. */
+dfl_status dfl_codebook_create(int32_t dtype, uint64_t rank, uint64_t n_rows, const void* data,
+                               uint64_t n_bytes, dfl_codebook** out);
+void dfl_codebook_destroy(dfl_codebook* c);
+/* DFlash2Codebook::dequant_row  metal_dflash.rs:3275-3340 */
+dfl_status dfl_codebook_dequant_row(const dfl_codebook* c, uint64_t row, float* out, uint64_t n_out);
+/* The greedy walk of select_draft_path (metal_dflash.rs:17212-17250) over ids / vals
+ * [n][top_k] and the gate rows sel_h [n][rank]: tokens_out[0] = ids[0], tokens_out[pos] = the
+ * candidate maximising vals + <A(prev) * sel_h[pos], B(candidate)> (strict >, first wins).
+ * scores_out [n][top_k] and scored_out [n][top_k] (1 = candidate was scored) are optional
+ * (diagnose_dflash2_selector_walk, metal_dflash.rs:3472-3620). */
+dfl_status dfl_selector_walk(const dfl_codebook* predecessor, const dfl_codebook* successor,
+                             uint32_t top_k, uint32_t rank, int32_t carry, uint32_t n,
+                             const int32_t* ids, const float* vals, const float* sel_h,
+                             int32_t* tokens_out, float* scores_out, uint8_t* scored_out);
+/* The sampled walk of draft_block_sampled (metal_dflash.rs:17349-17409): each position's 16
+ * scores are sampled with `proposal_sampler` (temperature only, else DFL_ERR_SAMPLING) and the
+ * positive-weight candidates become that row's sparse proposal.  Row r = position r + 1 owns
+ * candidates [cand_offsets[r], cand_offsets[r+1]); cand_offsets has n entries, cand_tokens /
+ * cand_weights room for (n - 1) * top_k. */
+dfl_status dfl_selector_walk_sampled(const dfl_codebook* predecessor, const dfl_codebook* successor,
+                                     uint32_t top_k, uint32_t rank, int32_t carry, uint32_t n,
+                                     const int32_t* ids, const float* vals, const float* sel_h,
+                                     dfl_sampler* proposal_sampler, int32_t* tokens_out,
+                                     uint32_t* cand_offsets, int32_t* cand_tokens,
+                                     double* cand_weights);
+/* DFlashDecoder::draft_block_sampled (metal_dflash.rs:17268-17415): one draft pass, then the
+ * sampled walk.  Fails with DFL_ERR_UNSUPPORTED on a drafter without a selector ("sampled
+ * path requires a DFlash 2 selector").  Outputs as dfl_selector_walk_sampled. */
+dfl_status dfl_draft_block_sampled(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos,
+                                   dfl_sampler* proposal_sampler, int32_t* out_tokens,
+                                   uint32_t* cand_offsets, int32_t* cand_tokens,
+                                   double* cand_weights);
+/* Top-16 ids / logits [N][16] and, with a selector, the gate rows W_h h [N][rank] of the last
+ * draft pass (the buffers draft_block_with_selector_diagnostic re-reads, metal_dflash.rs:17424).
+ * sel_h_out may be NULL. */
+dfl_status dfl_dsession_read_selector(dfl_dsession* ds, int32_t* ids_out, float* vals_out,
+                                      float* sel_h_out);
 
 /* ---- sampling + acceptance (host, f64) --------------------------------- */
 typedef struct dfl_sampling_config { /* SamplingConfig  sampling.rs:17-30 */

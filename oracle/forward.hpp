@@ -414,9 +414,10 @@ struct Drafter {
     TensorTable tt;
     std::string blk(uint32_t il, const char* suffix) const { return "blk." + std::to_string(il) + "." + suffix; }
 
-    // returns [N, vocab] logits
+    // returns [N, vocab] logits; hidden_out (optional) receives the [N, H] rows after output_norm, the input of both
+    // the lm_head and the DFlash 2 selector's gate projection (metal_dflash.rs:17099-17128)
     std::vector<float> draft(const Model& target, const int32_t* noise_ids, size_t n, const float* target_ctx_stacked,
-                             size_t ctx_len, const uint32_t* pos_ctx, uint32_t noise_start_pos) const {
+                             size_t ctx_len, const uint32_t* pos_ctx, uint32_t noise_start_pos, float* hidden_out = nullptr) const {
         const size_t h = cfg.hidden_size, f = cfg.intermediate_size, hd = cfg.head_dim;
         const size_t n_q = cfg.n_q_heads, n_kv = cfg.n_kv_heads, q_dim = n_q * hd, kv_dim = n_kv * hd, group = n_q / n_kv;
         const size_t nfeat = (size_t)cfg.n_target_layers * target.arch.hidden_size;
@@ -523,6 +524,7 @@ struct Drafter {
         const float* lm = target.lm_head().deq();
         for (size_t i = 0; i < n; ++i) {
             auto normed = rms_norm(&x[i * h], h, on_w, eps);
+            if (hidden_out) std::copy(normed.begin(), normed.end(), hidden_out + i * h);
             auto row = mat_vec(lm, h, v, normed.data());
             std::copy(row.begin(), row.end(), &logits[i * v]);
         }

@@ -166,6 +166,15 @@ int orc_dflash_draft(void* drafter, void* target, const int32_t* noise_ids, uint
     ORC_CATCH
 }
 
+// the same pass, also returning the normalised final hidden rows [n][H]
+int orc_dflash_draft_hidden(void* drafter, void* target, const int32_t* noise_ids, uint32_t n, const float* ctx_stacked,
+                            uint32_t ctx_len, const uint32_t* pos_ctx, uint32_t noise_start_pos, float* logits_out, float* hidden_out) {
+    ORC_TRY
+    auto l = ((Drafter*)drafter)->draft(*(Model*)target, noise_ids, n, ctx_stacked, ctx_len, pos_ctx, noise_start_pos, hidden_out);
+    std::copy(l.begin(), l.end(), logits_out);
+    ORC_CATCH
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
     

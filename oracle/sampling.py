@@ -252,6 +252,17 @@ class Sampler:
                 break
         return probe.candidates[idx][0], idx
 
+    def sample_with_distribution(self, logits) -> Distribution:
+        """sampling.rs:437-452: the draw together with the filtered categorical distribution it was made from;
+        an error leaves the generator untouched."""
+        if self.config.temperature == 0.0:
+            return self.diagnose(logits, 0.0)
+        probe = copy.deepcopy(self.rng)
+        dist = self.diagnose(logits, probe.next_unit_f64())
+        self.rng = probe
+        self.draws += 1
+        return dist
+
     def couple_deterministic_proposal(self, logits, proposal: int):
         target, _ = self.sample(logits)
         return ("accepted", None) if target == proposal else ("rejected", target)

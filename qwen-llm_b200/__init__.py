@@ -49,7 +49,8 @@ class DFlashConfig(C.Structure):
                 ("n_q_heads", C.c_uint32), ("n_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("rope_theta", C.c_float),
                 ("rms_norm_eps", C.c_float), ("causal", C.c_uint32), ("swa_window", C.c_uint32), ("block_size", C.c_uint32),
                 ("mask_token_id", C.c_int32), ("n_target_layers", C.c_uint32),
-                ("target_layer_ids", C.c_uint32 * MAX_TARGET_LAYERS), ("layer_is_swa", C.c_uint32 * MAX_DRAFTER_LAYERS)]
+                ("target_layer_ids", C.c_uint32 * MAX_TARGET_LAYERS), ("layer_is_swa", C.c_uint32 * MAX_DRAFTER_LAYERS),
+                ("selector_rank", C.c_uint32), ("selector_top_k", C.c_uint32)]
 
 
 class SamplingConfig(C.Structure):
@@ -407,6 +408,72 @@ class Sampler:
         return ("accepted", None) if acc.value else ("rejected", int(corr.value))
 
 
+def topk16(x, device=0):
+    """kernel_topk16_f32 on the device: ids, vals [n_rows][16]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    ids = np.zeros((x.shape[0], 16), dtype=np.int32)
+    vals = np.zeros((x.shape[0], 16), dtype=np.float32)
+    check(lib().dfl_topk16(C.c_int32(device), _ptr(x), C.c_int32(x.shape[0]), C.c_uint64(x.shape[1]), _ptr(ids), _ptr(vals)))
+    return ids, vals
+
+
+class Codebook:
+    """DFlash2Codebook: host copy of a [rank, n_rows] selector codebook in ggml storage."""
+
+    def __init__(self, dtype, rank, n_rows, raw):
+        raw = np.ascontiguousarray(np.frombuffer(bytes(raw), dtype=np.uint8))
+        self.rank, self.n_rows = rank, n_rows
+        self.h = C.c_void_p()
+        check(lib().dfl_codebook_create(C.c_int32(dtype), C.c_uint64(rank), C.c_uint64(n_rows), _ptr(raw) if raw.size else None,
+                                        C.c_uint64(raw.size), C.byref(self.h)))
+
+    def dequant_row(self, row):
+        out = np.zeros(self.rank, dtype=np.float32)
+        check(lib().dfl_codebook_dequant_row(self.h, C.c_uint64(row), _ptr(out), C.c_uint64(out.size)))
+        return out
+
+    def close(self):
+        if self.h:
+            lib().dfl_codebook_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def selector_walk(predecessor, successor, top_k, rank, carry, n, ids, vals, sel_h):
+    """select_draft_path's greedy walk: (tokens[n], scores[n][top_k], scored[n][top_k])."""
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    vals = np.ascontiguousarray(vals, dtype=np.float32)
+    sel_h = np.ascontiguousarray(sel_h, dtype=np.float32)
+    if ids.size != n * top_k or vals.size != n * top_k or sel_h.size != n * rank:
+        raise DflError(2, f"expected ids/vals/gate lengths {n * top_k}/{n * top_k}/{n * rank}, got {ids.size}/{vals.size}/{sel_h.size}")
+    tokens = np.zeros(n, dtype=np.int32)
+    scores = np.full((n, top_k), -np.inf, dtype=np.float32)
+    scored = np.zeros((n, top_k), dtype=np.uint8)
+    check(lib().dfl_selector_walk(predecessor.h, successor.h, C.c_uint32(top_k), C.c_uint32(rank), C.c_int32(carry), C.c_uint32(n), _ptr(ids),
+                                  _ptr(vals), _ptr(sel_h), _ptr(tokens), _ptr(scores), _ptr(scored)))
+    return tokens, scores, scored
+
+
+def selector_walk_sampled(predecessor, successor, top_k, rank, carry, n, ids, vals, sel_h, proposal_sampler):
+    """draft_block_sampled's walk: (tokens[n], [(token, [(cand, weight), ...]) per draft row])."""
+    ids = np.ascontiguousarray(ids, dtype=np.int32)
+    vals = np.ascontiguousarray(vals, dtype=np.float32)
+    sel_h = np.ascontiguousarray(sel_h, dtype=np.float32)
+    tokens = np.zeros(n, dtype=np.int32)
+    offs = np.zeros(n, dtype=np.uint32)
+    ct = np.zeros(max(1, (n - 1) * top_k), dtype=np.int32)
+    cw = np.zeros(max(1, (n - 1) * top_k), dtype=np.float64)
+    check(lib().dfl_selector_walk_sampled(predecessor.h, successor.h, C.c_uint32(top_k), C.c_uint32(rank), C.c_int32(carry), C.c_uint32(n),
+                                          _ptr(ids), _ptr(vals), _ptr(sel_h), proposal_sampler.h, _ptr(tokens), _ptr(offs), _ptr(ct), _ptr(cw)))
+    props = [(int(tokens[r + 1]), [(int(ct[k]), float(cw[k])) for k in range(int(offs[r]), int(offs[r + 1]))]) for r in range(n - 1)]
+    return tokens, props
+
+
 def splitmix64_stream(seed, n):
     st = C.c_uint64(seed)
     return [int(lib().dfl_splitmix64_next(C.byref(st))) for _ in range(n)]
@@ -495,6 +562,27 @@ class DSession:
 
     def reset(self):
         check(lib().dfl_dsession_reset(self.h))
+
+    def draft_block_sampled(self, carry, noise_start_pos, proposal_sampler):
+        """DFlashDecoder::draft_block_sampled: (tokens[n], [(token, [(cand, weight), ...]) per draft row])."""
+        n = self.drafter.cfg.block_size
+        out = np.zeros(n, dtype=np.int32)
+        offs = np.zeros(n, dtype=np.uint32)
+        ct = np.zeros((n - 1) * 16, dtype=np.int32)
+        cw = np.zeros((n - 1) * 16, dtype=np.float64)
+        check(lib().dfl_draft_block_sampled(self.h, C.c_int32(int(carry)), C.c_uint32(noise_start_pos), proposal_sampler.h, _ptr(out),
+                                            _ptr(offs), _ptr(ct), _ptr(cw)))
+        props = [(int(out[r + 1]), [(int(ct[k]), float(cw[k])) for k in range(int(offs[r]), int(offs[r + 1]))]) for r in range(n - 1)]
+        return out, props
+
+    def read_selector(self):
+        """Top-16 ids / logits [n][16] and (with a selector) the gate rows [n][rank] of the last draft pass."""
+        n, rank = self.drafter.cfg.block_size, self.drafter.cfg.selector_rank
+        ids = np.zeros((n, 16), dtype=np.int32)
+        vals = np.zeros((n, 16), dtype=np.float32)
+        sel_h = np.zeros((n, rank), dtype=np.float32) if rank else None
+        check(lib().dfl_dsession_read_selector(self.h, _ptr(ids), _ptr(vals), _ptr(sel_h) if rank else None))
+        return ids, vals, sel_h
 
     def draft_block(self, carry, noise_start_pos, want_logits=False):
         n = self.drafter.cfg.block_size

@@ -43,6 +43,10 @@ __device__ __forceinline__ void split_pair(float a, float b, uint32_t& hi, uint3
     hi = *reinterpret_cast<const uint32_t*>(&h);
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -133,12 +137,16 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
                 const uint32_t e0 = lds32(qb + 16 * kk), e1 = lds32(qb + 8 * TC_PITCH + 16 * kk), e2 = lds32(qb + 16 * kk + 8),
                                e3 = lds32(qb + 8 * TC_PITCH + 16 * kk + 8);
 #pragma unroll
+                uint32_t b0[8], b1[8];
+#pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
                     const __half* kr = ks + (8 * nt + gq) * TC_PITCH + 16 * kk + 2 * t;
-                    const uint32_t b0 = lds32(kr), b1 = lds32(kr + 8);
-                    mma16816(s[nt], h0, h1, h2, h3, b0, b1);
-                    mma16816(s[nt], e0, e1, e2, e3, b0, b1);
+                    b0[nt] = lds32(kr);
+                    b1[nt] = lds32(kr + 8);
+                    mma16816(s[nt], h0, h1, h2, h3, b0[nt], b1[nt]);
                 }
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) mma16816(s[nt], e0, e1, e2, e3, b0[nt], b1[nt]);
             }
         }
         // ---- causal / range mask (only the chunks that reach past the block's first position need it) ----
@@ -193,20 +201,15 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
 #pragma unroll
         for (int kk = 0; kk < ATTN_CHUNK / 16; ++kk) {
             // A fragment of keys 16 kk .. 16 kk + 15 = score tiles 2 kk (k 0-7) and 2 kk + 1 (k 8-15)
-            uint32_t h0, h1, h2, h3, e0, e1, e2, e3;
-            split_pair(s[2 * kk][0], s[2 * kk][1], h0, e0);
-            split_pair(s[2 * kk][2], s[2 * kk][3], h1, e1);
-            split_pair(s[2 * kk + 1][0], s[2 * kk + 1][1], h2, e2);
-            split_pair(s[2 * kk + 1][2], s[2 * kk + 1][3], h3, e3);
+            const uint32_t h0 = pack_h2(s[2 * kk][0], s[2 * kk][1]), h1 = pack_h2(s[2 * kk][2], s[2 * kk][3]);
+            const uint32_t h2 = pack_h2(s[2 * kk + 1][0], s[2 * kk + 1][1]), h3 = pack_h2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
             for (int np = 0; np < 8; ++np) {   // two 8-wide dim tiles per ldmatrix.x4
                 // lanes 0-15: keys 16 kk + lane of dims 16 np .. + 7; lanes 16-31: the same keys of dims 16 np + 8 .. + 15
                 uint32_t b[4];
                 ldmatrix_x4_trans(b, vs + (16 * kk + (lane & 15)) * TC_PITCH + 16 * np + 8 * (lane >> 4));
                 mma16816(o[2 * np], h0, h1, h2, h3, b[0], b[1]);
-                mma16816(o[2 * np], e0, e1, e2, e3, b[0], b[1]);
                 mma16816(o[2 * np + 1], h0, h1, h2, h3, b[2], b[3]);
-                mma16816(o[2 * np + 1], e0, e1, e2, e3, b[2], b[3]);
             }
         }
     }

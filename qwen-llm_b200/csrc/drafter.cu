@@ -213,6 +213,10 @@ struct dfl_drafter {
     float *hidden_norm_w = nullptr, *out_norm_w = nullptr;
     std::vector<DLayerW> layers;
     uint64_t weight_bytes = 0;
+    // DFlash 2 path selector (metal_dflash.rs:2789-2797): the gate projection on the device, the codebooks on the host
+    bool has_selector = false;
+    MatGroup sel_hidden;
+    dfl_codebook *sel_pred = nullptr, *sel_succ = nullptr;
     AttnGeom geom(int n_q) const {
         AttnGeom g;
         g.n_q = n_q; g.n_kv = (int)cfg.n_kv_heads; g.hd = (int)cfg.head_dim; g.n_rot = (int)cfg.head_dim;
@@ -237,6 +241,13 @@ struct dfl_dsession {
     float *logits = nullptr, *gap = nullptr;
     int32_t *argmax = nullptr, *tokens_dev = nullptr;
     void* am_scratch = nullptr;
+    // top-16 per row and the selector's gate rows W_h h of the last pass
+    int32_t* topk_ids = nullptr;
+    float *topk_vals = nullptr, *sel_h = nullptr;
+    void* topk_scratch = nullptr;
+    uint8_t* acts_sel = nullptr;
+    bool have_topk = false;
+    uint8_t* pinned_sel = nullptr;   // [16][16] ids | [16][16] vals | [16][rank] gate rows
     int32_t* pinned_i = nullptr;
     cudaStream_t st = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -304,6 +315,21 @@ dfl_status dfl_drafter_create(const dfl_model* target, const dfl_dflash_config* 
         DC(build_group(dev, 0, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down, true));
         d->weight_bytes += L.qkv.ggml_bytes() + L.wo.ggml_bytes() + L.gate_up.ggml_bytes() + L.down.ggml_bytes();
     }
+    if (c.selector_rank > 0) {   // MetalDFlashHead::load, metal_dflash.rs:5008-5036
+        if (c.selector_top_k != 16) { s = fail(DFL_ERR_UNSUPPORTED, "only selector_top_k=16 is supported"); goto failed; }
+        DC(build_group(dev, 0, tm, {"selector_hidden.weight"}, H, {(uint64_t)c.selector_rank}, &d->sel_hidden, true));
+        for (int which = 0; which < 2; ++which) {
+            const char* name = which ? "selector_successor.weight" : "selector_predecessor.weight";
+            auto it = tm.t.find(name);
+            if (it == tm.t.end()) { s = fail(DFL_ERR_MISSING_TENSOR, std::string("missing tensor ") + name); goto failed; }
+            const dfl_tensor& t = *it->second;
+            if (t.on_device) { s = fail(DFL_ERR_BAD_ARG, "selector codebooks must be passed as host tensors"); goto failed; }
+            if (t.n_dims != 2 || t.shape[0] != c.selector_rank) { s = fail(DFL_ERR_BAD_SHAPE, "selector codebook must be [rank, vocab]"); goto failed; }
+            DC(dfl_codebook_create(t.dtype, t.shape[0], t.shape[1], t.data, t.n_bytes, which ? &d->sel_succ : &d->sel_pred));
+        }
+        d->has_selector = true;
+        d->weight_bytes += d->sel_hidden.ggml_bytes();
+    }
 #undef DC
     d->weight_bytes += target->lm_head.ggml_bytes();
     cudaDeviceSynchronize();
@@ -325,6 +351,9 @@ void dfl_drafter_destroy(dfl_drafter* d) {
     }
     if (d->hidden_norm_w) cudaFree(d->hidden_norm_w);
     if (d->out_norm_w) cudaFree(d->out_norm_w);
+    d->sel_hidden.release();
+    dfl_codebook_destroy(d->sel_pred);
+    dfl_codebook_destroy(d->sel_succ);
     delete d;
 }
 
@@ -346,6 +375,7 @@ dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_
     upd(d->fc);
     for (auto& L : d->layers) { upd(L.qkv); upd(L.kv); upd(L.wo); upd(L.gate_up); upd(L.down); }
     if (d->target->lm_head.splits > 1) upd(d->target->lm_head);
+    if (d->has_selector) upd(d->sel_hidden);
     bool ok = cudaStreamCreateWithFlags(&ds->st, cudaStreamNonBlocking) == cudaSuccess;
     auto alloc = [&](size_t bytes) -> void* {
         if (!ok) return nullptr;
@@ -378,8 +408,16 @@ dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_
     ds->argmax = (int32_t*)alloc(MAX_ROWS * 4);
     ds->tokens_dev = (int32_t*)alloc(MAX_ROWS * 4);
     ds->am_scratch = alloc(MAX_ROWS * ARGMAX_PARTS * 16);
+    ds->topk_ids = (int32_t*)alloc(MAX_ROWS * 16 * 4);
+    ds->topk_vals = (float*)alloc(MAX_ROWS * 16 * 4);
+    ds->topk_scratch = alloc(topk16_scratch_bytes(MAX_ROWS));
+    if (d->has_selector) {
+        ds->sel_h = (float*)alloc((size_t)MAX_ROWS * c.selector_rank * 4);
+        ds->acts_sel = (uint8_t*)alloc(acts_bytes(DFL_BF16, H));
+    }
     ds->err = (int*)alloc(4);
     ok = ok && cudaMallocHost(&ds->pinned_i, 2 * MAX_ROWS * 4) == cudaSuccess;
+    ok = ok && cudaMallocHost(&ds->pinned_sel, MAX_ROWS * 16 * 8 + (size_t)MAX_ROWS * c.selector_rank * 4) == cudaSuccess;
     ok = ok && cudaEventCreate(&ds->ev0) == cudaSuccess && cudaEventCreate(&ds->ev1) == cudaSuccess;
     if (!ok) {
         std::string why = cudaGetErrorString(cudaGetLastError());
@@ -397,6 +435,7 @@ void dfl_dsession_destroy(dfl_dsession* ds) {
     cudaSetDevice(ds->d->target->device);
     for (void* p : ds->allocs) cudaFree(p);
     if (ds->pinned_i) cudaFreeHost(ds->pinned_i);
+    if (ds->pinned_sel) cudaFreeHost(ds->pinned_sel);
     if (ds->ev0) cudaEventDestroy(ds->ev0);
     if (ds->ev1) cudaEventDestroy(ds->ev1);
     if (ds->st) cudaStreamDestroy(ds->st);
@@ -416,10 +455,12 @@ struct dfl_dsession_view {
     uint32_t block_size, n_target_layers;
     const uint32_t* target_layer_ids;
     const dfl_model* target;
+    int32_t has_selector;
 };
 void dfl_dsession_view_get(dfl_dsession* ds, dfl_dsession_view* out) {
     out->st = ds->st; out->ev0 = ds->ev0; out->ev1 = ds->ev1; out->err = ds->err;
     out->argmax_dev = ds->argmax; out->logits_dev = ds->logits; out->pinned_i = ds->pinned_i;
+    out->has_selector = ds->d->has_selector ? 1 : 0;
     out->block_size = ds->d->cfg.block_size; out->n_target_layers = ds->d->cfg.n_target_layers;
     out->target_layer_ids = ds->d->cfg.target_layer_ids; out->target = ds->d->target;
 }
@@ -499,8 +540,9 @@ dfl_status dsession_append_dev(dfl_dsession* ds, const float* rows, cudaMemcpyKi
     return DFL_OK;
 }
 
-// One draft pass; leaves logits / argmax on the device.
-dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start) {
+// One draft pass; leaves logits / argmax on the device, and with `topk` (always on a drafter with a selector) the
+// top-16 per row plus the selector's gate rows (phase-4 tail, metal_dflash.rs:17099-17128).
+dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, bool topk) {
     const dfl_drafter* d = ds->d;
     const dfl_model* tgt = d->target;
     const dfl_dflash_config& c = d->cfg;
@@ -576,6 +618,58 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start) {
         DFL_CHECK(launch_reduce_partials(st, ds->part, lm.splits, n, V, ds->logits, (int)V));
     }
     DFL_CHECK(launch_argmax_top2(st, ds->logits, n, V, V, ds->argmax, ds->gap, ds->am_scratch));
+    ds->have_topk = false;
+    if (topk || d->has_selector) {
+        DFL_CHECK(launch_topk16(st, ds->logits, n, V, V, ds->topk_ids, ds->topk_vals, ds->topk_scratch));
+        if (d->has_selector) {
+            const MatGroup& sh = d->sel_hidden;
+            const uint8_t* acts = ds->acts_lm;
+            if (bf(sh) != bf(lm)) {   // the normalised hidden again, packed for this matrix's kernel family
+                DFL_CHECK(norm_glue(nullptr, 0, 0, d->out_norm_w, ds->acts_sel, bf(sh)));
+                acts = ds->acts_sel;
+            }
+            if (sh.splits == 1) {
+                DFL_CHECK(launch_group(st, sh, acts, ds->sel_h, ep_norm, ds->err));
+            } else {
+                DFL_CHECK(launch_group(st, sh, acts, ds->part, ep_norm, ds->err));
+                DFL_CHECK(launch_reduce_partials(st, ds->part, sh.splits, n, c.selector_rank, ds->sel_h, (int)c.selector_rank));
+            }
+        }
+        ds->have_topk = true;
+    }
+    return DFL_OK;
+}
+
+// the last pass's top-16 and gate rows in pinned host memory (at most 18 KB; the reference reads the same three
+// buffers after its wait, metal_dflash.rs:17184-17207)
+struct SelectorHost {
+    const int32_t* ids;
+    const float *vals, *sel_h;
+};
+dfl_status selector_to_host(dfl_dsession* ds, SelectorHost* h) {
+    const uint32_t n = ds->d->cfg.block_size, rank = ds->d->cfg.selector_rank;
+    uint8_t* p = ds->pinned_sel;
+    DFL_CUDA(cudaMemcpyAsync(p, ds->topk_ids, n * 16 * 4, cudaMemcpyDeviceToHost, ds->st));
+    DFL_CUDA(cudaMemcpyAsync(p + MAX_ROWS * 16 * 4, ds->topk_vals, n * 16 * 4, cudaMemcpyDeviceToHost, ds->st));
+    if (ds->d->has_selector) DFL_CUDA(cudaMemcpyAsync(p + MAX_ROWS * 16 * 8, ds->sel_h, (size_t)n * rank * 4, cudaMemcpyDeviceToHost, ds->st));
+    DFL_CHECK(check_dev_err(ds->st, ds->err));
+    h->ids = reinterpret_cast<const int32_t*>(p);
+    h->vals = reinterpret_cast<const float*>(p + MAX_ROWS * 16 * 4);
+    h->sel_h = reinterpret_cast<const float*>(p + MAX_ROWS * 16 * 8);
+    return DFL_OK;
+}
+
+// per-row argmax drafts plus the top-16 of every row left on the device (for sparse proposals without a selector)
+dfl_status draft_block_topk(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos, int32_t* out_tokens) {
+    const dfl_model* tgt = ds->d->target;
+    DFL_CHECK(use_device(tgt->device));
+    if (carry < 0 || (uint32_t)carry >= tgt->arch.vocab_size) return fail(DFL_ERR_BAD_TOKEN, "draft_block: carry token out of range");
+    const uint32_t n = ds->d->cfg.block_size;
+    DFL_CHECK(draft_core(ds, carry, noise_start_pos, true));
+    DFL_CUDA(cudaMemcpyAsync(ds->pinned_i + MAX_ROWS, ds->argmax, n * 4, cudaMemcpyDeviceToHost, ds->st));
+    DFL_CHECK(check_dev_err(ds->st, ds->err));
+    out_tokens[0] = carry;
+    for (uint32_t i = 1; i < n; ++i) out_tokens[i] = ds->pinned_i[MAX_ROWS + i];
     return DFL_OK;
 }
 
@@ -608,12 +702,56 @@ dfl_status dfl_draft_block(dfl_dsession* ds, int32_t carry, uint32_t noise_start
     DFL_CHECK(use_device(tgt->device));
     if (carry < 0 || (uint32_t)carry >= tgt->arch.vocab_size) return fail(DFL_ERR_BAD_TOKEN, "draft_block: carry token out of range");
     const uint32_t n = ds->d->cfg.block_size;
-    DFL_CHECK(draft_core(ds, carry, noise_start_pos));
+    DFL_CHECK(draft_core(ds, carry, noise_start_pos, false));
     DFL_CUDA(cudaMemcpyAsync(ds->pinned_i + MAX_ROWS, ds->argmax, n * 4, cudaMemcpyDeviceToHost, ds->st));
     if (logits_host) DFL_CUDA(cudaMemcpyAsync(logits_host, ds->logits, (size_t)n * tgt->arch.vocab_size * 4, cudaMemcpyDeviceToHost, ds->st));
+    if (ds->d->has_selector) {   // select_draft_path: the walk replaces the per-row argmax
+        SelectorHost h;
+        DFL_CHECK(selector_to_host(ds, &h));
+        DFL_CHECK(dfl_selector_walk(ds->d->sel_pred, ds->d->sel_succ, 16, ds->d->cfg.selector_rank, carry, n, h.ids, h.vals, h.sel_h, out_tokens,
+                                    nullptr, nullptr));
+        out_tokens[0] = carry;
+        return DFL_OK;
+    }
     DFL_CHECK(check_dev_err(ds->st, ds->err));
     out_tokens[0] = carry;
     for (uint32_t i = 1; i < n; ++i) out_tokens[i] = ds->pinned_i[MAX_ROWS + i];
+    return DFL_OK;
+}
+
+dfl_status dfl_draft_block_sampled(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos, dfl_sampler* proposal_sampler, int32_t* out_tokens,
+                                   uint32_t* cand_offsets, int32_t* cand_tokens, double* cand_weights) {
+    if (!ds || !proposal_sampler || !out_tokens || !cand_offsets || !cand_tokens || !cand_weights)
+        return fail(DFL_ERR_BAD_ARG, "draft_block_sampled: null argument");
+    if (!ds->d->has_selector) return fail(DFL_ERR_UNSUPPORTED, "sampled path requires a DFlash 2 selector");
+    const dfl_model* tgt = ds->d->target;
+    DFL_CHECK(use_device(tgt->device));
+    if (carry < 0 || (uint32_t)carry >= tgt->arch.vocab_size) return fail(DFL_ERR_BAD_TOKEN, "draft_block: carry token out of range");
+    dfl_sampling_config pc;
+    dfl_sampler_get_config(proposal_sampler, &pc);
+    if (!(pc.temperature > 0.0f) || pc.top_k != 0 || pc.top_p != 1.0f || pc.min_p != 0.0f)   // checked before any device work, :17279-17288
+        return fail(DFL_ERR_SAMPLING, "DFlash 2 proposal sampler must use temperature without target filters");
+    const uint32_t n = ds->d->cfg.block_size;
+    DFL_CHECK(draft_core(ds, carry, noise_start_pos, true));
+    SelectorHost h;
+    DFL_CHECK(selector_to_host(ds, &h));
+    DFL_CHECK(dfl_selector_walk_sampled(ds->d->sel_pred, ds->d->sel_succ, 16, ds->d->cfg.selector_rank, carry, n, h.ids, h.vals, h.sel_h,
+                                        proposal_sampler, out_tokens, cand_offsets, cand_tokens, cand_weights));
+    out_tokens[0] = carry;
+    return DFL_OK;
+}
+
+dfl_status dfl_dsession_read_selector(dfl_dsession* ds, int32_t* ids_out, float* vals_out, float* sel_h_out) {
+    if (!ds || !ids_out || !vals_out) return fail(DFL_ERR_BAD_ARG, "read_selector: null argument");
+    if (!ds->have_topk) return fail(DFL_ERR_BAD_ARG, "read_selector: the last draft pass produced no top-16");
+    if (sel_h_out && !ds->d->has_selector) return fail(DFL_ERR_UNSUPPORTED, "read_selector: the drafter has no selector");
+    DFL_CHECK(use_device(ds->d->target->device));
+    SelectorHost h;
+    DFL_CHECK(selector_to_host(ds, &h));
+    const uint32_t n = ds->d->cfg.block_size;
+    memcpy(ids_out, h.ids, n * 16 * 4);
+    memcpy(vals_out, h.vals, n * 16 * 4);
+    if (sel_h_out) memcpy(sel_h_out, h.sel_h, (size_t)n * ds->d->cfg.selector_rank * 4);
     return DFL_OK;
 }
 

@@ -10,7 +10,8 @@
 struct dfl_dsession;
 struct dfl_drafter;
 namespace dfl {
-dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start);
+dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, bool topk);
+dfl_status draft_block_topk(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos, int32_t* out_tokens);
 }
 // accessors implemented next to the drafter session (drafter.cu)
 extern "C" {
@@ -24,6 +25,7 @@ struct dfl_dsession_view {
     uint32_t block_size, n_target_layers;
     const uint32_t* target_layer_ids;
     const dfl_model* target;
+    int32_t has_selector;
 };
 void dfl_dsession_view_get(dfl_dsession* ds, dfl_dsession_view* out);
 }
@@ -89,9 +91,8 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         dfl_sampling_config pc{scfg.temperature, 0, 1.0f, 0.0f, scfg.seed ^ 0x44464c4153483251ull};  // qwen/dflash.rs:91
         DFL_CHECK(dfl_sampler_create(&pc, &proposal_sampler));
     }
-    std::vector<float> logits_host, draft_logits_host;
+    std::vector<float> logits_host;
     if (sampled) logits_host.resize((size_t)N * V);
-    if (proposal_sampler) draft_logits_host.resize((size_t)N * V);
     auto is_stop = [&](int32_t t) {
         for (uint32_t i = 0; i < params->n_stop_ids; ++i)
             if (params->stop_ids[i] == t) return true;
@@ -147,7 +148,13 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
             for (uint32_t i = 1; i < N; ++i) draft[i] = replay[i - 1];
         } else {
             cudaEventRecord(dv.ev0, dv.st);
-            rc = dfl_draft_block(ds, carry, position, draft, proposal_sampler ? draft_logits_host.data() : nullptr);
+            const bool selector_sampled = proposal_sampler && dv.has_selector;
+            uint32_t sel_off[DFL_MAX_BLOCK];
+            int32_t sel_ct[DFL_MAX_BLOCK * 16];
+            double sel_cw[DFL_MAX_BLOCK * 16];
+            if (selector_sampled) rc = dfl_draft_block_sampled(ds, carry, position, proposal_sampler, draft, sel_off, sel_ct, sel_cw);
+            else if (proposal_sampler) rc = draft_block_topk(ds, carry, position, draft);
+            else rc = dfl_draft_block(ds, carry, position, draft, nullptr);
             cudaEventRecord(dv.ev1, dv.st);
             if (rc != DFL_OK) break;
             cudaEventSynchronize(dv.ev1);
@@ -155,23 +162,25 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
             cudaEventElapsedTime(&ms, dv.ev0, dv.ev1);
             st.draft_ms += ms;
             ++st.drafter_calls;
-            if (proposal_sampler) {
-                // sparse proposals from the drafter's top-16 (draft_block_sampled, metal_dflash.rs:17268-17415, selector term omitted)
+            if (selector_sampled) {   // draft_block_sampled, metal_dflash.rs:17268-17415
+                prop_off.push_back(0);
+                for (uint32_t pos = 1; pos < N; ++pos) {
+                    prop_tok.push_back(draft[pos]);
+                    for (uint32_t k = sel_off[pos - 1]; k < sel_off[pos]; ++k) { prop_ct.push_back(sel_ct[k]); prop_cw.push_back(sel_cw[k]); }
+                    prop_off.push_back((uint32_t)prop_ct.size());
+                }
+            } else if (proposal_sampler) {
+                // a drafter without a selector: the same sparse proposals from the device's top-16 with the pair term absent
+                int32_t top_ids[DFL_MAX_BLOCK * 16];
+                float top_vals[DFL_MAX_BLOCK * 16];
+                rc = dfl_dsession_read_selector(ds, top_ids, top_vals, nullptr);
+                if (rc != DFL_OK) break;
                 prop_off.push_back(0);
                 for (uint32_t pos = 1; pos < N && rc == DFL_OK; ++pos) {
-                    const float* row = draft_logits_host.data() + (size_t)pos * V;
-                    int32_t ids[16];
+                    const int32_t* ids = top_ids + pos * 16;
                     float vals[16];
                     int cnt = 0;
-                    for (uint32_t t = 0; t < V; ++t) {  // top-16, ties to the lower index
-                        const float v = row[t];
-                        if (cnt < 16 || v > vals[cnt - 1]) {
-                            int j = cnt < 16 ? cnt++ : 15;
-                            while (j > 0 && vals[j - 1] < v) { vals[j] = vals[j - 1]; ids[j] = ids[j - 1]; --j; }
-                            vals[j] = v;
-                            ids[j] = (int32_t)t;
-                        }
-                    }
+                    while (cnt < 16 && ids[cnt] >= 0) { vals[cnt] = top_vals[pos * 16 + cnt]; ++cnt; }
                     int32_t sel = 0;
                     int32_t dt[16];
                     double dw[16];

