@@ -1,14 +1,18 @@
 #!/usr/bin/env python
 """Benchmark of the DFlash speculative-decoding step on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c2v|c4v|c5v|gemm] [--impl reference]
 
 Prints ONE JSON line on rank 0.  A "step" is one pass of the hot path over one batch of
 seeded synthetic input:
   * workload c2 (default): one DFlash outer step (draft 16 -> packed verify -> greedy accept ->
     rollback) of the 9B-class hybrid Q4_K_M target with the 5-layer bf16 drafter, batch 1;
   * workload c1: the CPU-runnable verify/accept step (16x4096 . Q4_K 4096x4096, Q6_K head to
-    32000, greedy prefix acceptance).
+    32000, greedy prefix acceptance);
+  * workload c3: the same target and drafter with sampled acceptance (T 0.7, top-p 0.95), 32 independent
+    sequences split over the GPUs (strong scaling);
+  * workloads c2v / c4v / c5v (packed verify only: dense, routed-expert, long context) and gemm are
+    kernel-level side benches.
 `value` is accepted tokens per second with inputs resident in HBM; `e2e` is the same metric
 through the host-buffer C-ABI call (copies inside the timed region).  With N > 1 each rank
 drives its own GPU on independent sequences (no collective on the data path): weak scaling.
@@ -318,6 +322,8 @@ def main():
         line = run_gemm(args, local)
     elif args.workload in ("c2v", "c4v", "c5v"):
         line = importlib.import_module("bench_c2").run_verify_only(args, rank, world, local)
+    elif args.workload == "c3":
+        line = importlib.import_module("bench_c2").run_c3(args, rank, world, local)
     else:
         c2 = importlib.import_module("bench_c2")
         line = c2.run(args, rank, world, local)

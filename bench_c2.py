@@ -54,7 +54,7 @@ def tokens_for_steps(pattern, first_step, n_steps):
 
 
 class World:
-    def __init__(self, device, seed):
+    def __init__(self, device, seed, prompt_len=PROMPT):
         pkg, syn = _pkg(), _syn()
         self.pkg = pkg
         self.arch = syn.arch_9b()
@@ -69,7 +69,7 @@ class World:
         syn.free_entries(dents, device)
         self.build_s = time.perf_counter() - t0
         self.layer_ids = self.drafter.layer_ids()
-        self.prompt = np.random.default_rng(seed + 2).integers(0, self.arch.vocab_size, size=PROMPT).astype(np.int32)
+        self.prompt = np.random.default_rng(seed + 2).integers(0, self.arch.vocab_size, size=prompt_len).astype(np.int32)
         self.sess = self.scr = self.ds = None
 
     def fresh(self):
@@ -370,3 +370,143 @@ def run_verify_only(args, rank, world, device):
                                     else "c2v: packed verify only, 16 rows")},
             "roofline": {"bound": "hbm", "achieved": vb / wall / 1e9, "peak": peak, "unit": "GB/s", "frac": vb / wall / 1e9 / peak,
                          "traffic": None, "peak_kind": kind}, "gpu_launches": int(pkg.launch_count() - launches0), **extra}
+
+
+# ---------------------------------------------------------------------------
+# workload c3: sampled acceptance, 32 independent sequences, data parallel
+# ---------------------------------------------------------------------------
+C3_SEQS, C3_PROMPT, C3_T, C3_TOP_P, C3_SEED, C3_KV = 32, 1024, 0.7, 0.95, 0xC3, 2048
+
+
+class Seq:
+    """One independent sequence: its own target session, drafter session and request sampler."""
+
+    def __init__(self, w, index):
+        self.w, self.index = w, index
+        self.prompt = np.random.default_rng(5000 + index).integers(0, w.arch.vocab_size, size=C3_PROMPT).astype(np.int32)
+        self.seed = C3_SEED * 1000 + index
+        self.sess = self.ds = None
+
+    def fresh(self):
+        pkg, w = self.w.pkg, self.w
+        self.close()
+        self.sess = pkg.Session(w.model, C3_KV, True)
+        self.ds = pkg.DSession(w.drafter, C3_KV)
+        logits, _ = pkg.prefill(w.model, self.sess, w.scr, w.layer_ids, self.prompt, 0, feed_drafter=self.ds)
+        return logits
+
+    def sampler(self, at_draw=None):
+        return self.w.pkg.Sampler(temperature=C3_T, top_p=C3_TOP_P, seed=self.seed, at_draw=at_draw)
+
+    def gen(self, sampler, first_logits, max_tokens, **kw):
+        return self.w.pkg.generate(self.w.model, self.sess, self.w.scr, self.ds, sampler, first_logits, max_tokens, **kw)
+
+    def close(self):
+        for x in (self.sess, self.ds):
+            if x is not None:
+                x.close()
+        self.sess = self.ds = None
+
+
+def forced(vocab, tok):
+    """logits whose only sampled outcome is `tok` (the draw is still consumed)"""
+    l = np.full(vocab, -np.inf, dtype=np.float32)
+    l[tok] = 0.0
+    return l
+
+
+def run_c3(args, rank, world, device):
+    """BASELINE config 3: the config-2 target and drafter, sampled acceptance (temperature 0.7, top-p 0.95, fixed
+    seeds, rejection sampling with one-hot coupling of the greedy drafts as the reference does for a drafter without
+    selector, qwen/dflash.rs:508-522), 32 independent sequences with 1024-id prompts split round-robin over the GPUs.
+    A step is one outer step of every sequence this rank owns.  Acceptance is controlled as in workload c2: the drafts
+    replay the sequence's own sampled continuation (one-hot coupling keeps the serial sampler stream, so that
+    continuation is exactly what plain sampled decoding emits) with seeded corruption, 3,3,4,3,4 accepted per step."""
+    import torch
+    bench = importlib.import_module("bench")
+    w = World(device, seed=100, prompt_len=16)   # the same weights on every rank: data parallel replicas
+    pkg = w.pkg
+    V = w.arch.vocab_size
+    steps, warm = args.steps, max(args.warmup, 3)
+    w.scr = pkg.Scratch(w.model, 16, len(w.layer_ids))
+    seqs = [Seq(w, i) for i in range(C3_SEQS) if i % world == rank]
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+
+    # pass 0 per sequence: the sampled continuation itself (natural drafter, acceptance ~ 0 with random weights)
+    need = tokens_for_steps(PATTERN, 0, warm + steps) + 16
+    nat = {"emitted": 0, "steps": 0, "dev_ms": 0.0, "wall_ms": 0.0}
+    state = []
+    t_setup = time.perf_counter()
+    for q in seqs:
+        logits = q.fresh()
+        t0 = time.perf_counter()
+        cont, st = q.gen(q.sampler(), logits, need)
+        nat["wall_ms"] += (time.perf_counter() - t0) * 1e3
+        nat["emitted"] += int(st.tokens_emitted) - 1
+        nat["steps"] += int(st.spec_steps)
+        nat["dev_ms"] += st.draft_ms + st.verify_ms + st.restore_ms
+        hist = schedule_history(cont, PATTERN, V)
+        logits = q.fresh()
+        n_a = tokens_for_steps(PATTERN, 0, warm)
+        toks_a, _ = q.gen(q.sampler(), logits, n_a, replay_history=hist, replay_runs_drafter=True, replay_unchecked=True)
+        assert np.array_equal(toks_a, cont[:n_a]), "warm-up output differs from the plain sampled continuation"
+        state.append((cont, hist, n_a, int(toks_a[-1])))
+    setup_s = time.perf_counter() - t_setup
+    n_b = tokens_for_steps(PATTERN, warm, steps)
+    clock = bench.ClockSampler(device)
+    clock.start()
+    barrier()
+    launches0 = pkg.launch_count()
+    tot = {"emitted": 0, "dev_ms": 0.0, "draft_ms": 0.0, "verify_ms": 0.0, "restore_ms": 0.0, "accept_ms": 0.0}
+    t0 = time.perf_counter()
+    for q, (cont, hist, n_a, last) in zip(seqs, state):
+        toks_b, st = q.gen(q.sampler(at_draw=n_a - 1), forced(V, last), n_b, replay_history=hist[n_a - 1:], replay_runs_drafter=True,
+                           replay_unchecked=True)
+        assert np.array_equal(toks_b, cont[n_a - 1:n_a - 1 + n_b]), "timed output differs from the plain sampled continuation"
+        assert st.spec_steps == steps, (st.spec_steps, steps)
+        tot["emitted"] += n_b - 1
+        for k in ("draft_ms", "verify_ms", "restore_ms", "accept_ms"):
+            tot[k] += getattr(st, k)
+    torch.cuda.synchronize(device)
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    launches = pkg.launch_count() - launches0
+    barrier()
+    clocks = clock.stop()
+    tot["dev_ms"] = tot["draft_ms"] + tot["verify_ms"] + tot["restore_ms"]
+    t = torch.tensor([tot["dev_ms"], wall_ms], dtype=torch.float64, device=f"cuda:{device}")
+    e = torch.tensor([float(tot["emitted"])], dtype=torch.float64, device=f"cuda:{device}")
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(e, op=torch.distributed.ReduceOp.SUM)
+    dev_ms, wall_max, emitted = float(t[0]), float(t[1]), float(e[0])
+    peak, peak_kind = bench.measured_peaks()
+    vbytes = w.model.verify_weight_bytes()
+    n_steps_rank = steps * len(seqs)
+    verify_ms = tot["verify_ms"] / n_steps_rank
+    gbs = vbytes / (verify_ms * 1e-3) / 1e9
+    for q in seqs:
+        q.close()
+    return {
+        "metric": bench.METRIC, "value": emitted / (dev_ms * 1e-3), "unit": bench.UNIT, "n_gpus": world, "steps": steps, "warmup": warm,
+        "ms_per_step": dev_ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "u4/u5/u6 weights x f16 hi+lo activations, f32 accumulate; bf16 drafter; f64 host sampler", "data": "synthetic",
+        "config": {"workload": f"c3: config-2 target + drafter, sampled acceptance T={C3_T} top-p={C3_TOP_P}, fixed seeds, one-hot rejection coupling; "
+                               f"{C3_SEQS} independent sequences, prompt {C3_PROMPT}, block 16; replayed drafts accept 3,3,4,3,4 per step; "
+                               "a step = one outer step of every sequence of the rank",
+                   "l2": "5.1 GB of weights per verify >> 126 MB L2",
+                   "parallelism": f"dp{world}: {C3_SEQS} sequences round-robin over {world} GPU(s), full replica each, no collective in the loop"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "one packed verify (all kernels), weight bytes / CUDA-event time"},
+        "e2e": {"value": emitted / (wall_max * 1e-3), "unit": bench.UNIT, "h2d_bytes_per_step": len(seqs) * 2 * 16 * 4,
+                "d2h_bytes_per_step": len(seqs) * (16 * V * 4 + 3 * 16 * 4)},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "per_outer_step_ms": {"draft": tot["draft_ms"] / n_steps_rank, "verify": verify_ms, "restore": tot["restore_ms"] / n_steps_rank,
+                              "host_accept": tot["accept_ms"] / n_steps_rank, "wall": wall_ms / n_steps_rank},
+        "natural_drafter": {"tok_per_s": nat["emitted"] / (nat["dev_ms"] * 1e-3) if nat["dev_ms"] else None,
+                            "e2e_tok_per_s": nat["emitted"] / (nat["wall_ms"] * 1e-3), "mean_emitted": nat["emitted"] / max(nat["steps"], 1)},
+        "setup": {"build_s": w.build_s, "sequences_on_rank0": len(seqs), "prefill_and_continuation_s": setup_s},
+    }

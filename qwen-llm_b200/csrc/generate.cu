@@ -91,8 +91,14 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         dfl_sampling_config pc{scfg.temperature, 0, 1.0f, 0.0f, scfg.seed ^ 0x44464c4153483251ull};  // qwen/dflash.rs:91
         DFL_CHECK(dfl_sampler_create(&pc, &proposal_sampler));
     }
-    std::vector<float> logits_host;
-    if (sampled) logits_host.resize((size_t)N * V);
+    // the block's logits for the host sampler: pinned, so the 16 x vocab copy runs at link speed
+    struct PinnedLogits {
+        float* p = nullptr;
+        ~PinnedLogits() { if (p) cudaFreeHost(p); }
+        float* data() const { return p; }
+    } logits_host;
+    if (sampled && cudaMallocHost(&logits_host.p, (size_t)N * V * 4) != cudaSuccess)
+        return fail(DFL_ERR_OOM, "generate: pinned logits buffer");
     auto is_stop = [&](int32_t t) {
         for (uint32_t i = 0; i < params->n_stop_ids; ++i)
             if (params->stop_ids[i] == t) return true;
@@ -121,7 +127,7 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         }
         // ---- draft ----
         const int32_t* replay = nullptr;
-        if (params->replay_history && !sampled) {  // dflash_prefix_replay_drafts, qwen/dflash.rs:351-360
+        if (params->replay_history && !proposal_sampler) {  // dflash_prefix_replay_drafts, qwen/dflash.rs:351-360 (one-hot coupling when sampled)
             const size_t emitted = tokens.size();
             if (emitted + (N - 1) <= params->n_replay_history &&
                 (params->replay_unchecked || std::memcmp(params->replay_history, tokens.data(), emitted * 4) == 0))

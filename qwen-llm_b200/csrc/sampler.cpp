@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <thread>
 #include <limits>
 #include <string>
 #include <vector>
@@ -122,9 +123,58 @@ struct dfl_sampler {
     Xoshiro rng;
     uint64_t draws = 0;
     Buffers buf;
+    // Distributions of a block's rows built ahead of the sequential accept loop (one host thread per row): building a
+    // row's distribution draws nothing from the generator, so only the picks have to stay in row order.
+    struct Prepared {
+        const float* logits = nullptr;
+        Dist dist;
+        SErr err = S_OK;
+        uint64_t nan_token = 0;
+        Buffers buf;
+    };
+    std::vector<Prepared> prepared;
+    uint32_t n_prepared = 0;
+
+    void prepare_rows(const float* logits, uint32_t n_rows, uint64_t vocab) {
+        n_prepared = 0;
+        if (cfg.temperature == 0.0f || n_rows < 2 || vocab < 4096) return;
+        const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+        if (hw < 2) return;
+        if (prepared.size() < n_rows) prepared.resize(n_rows);
+        const uint32_t n_threads = std::min<uint32_t>(n_rows, hw);
+        auto work = [&](uint32_t first) {
+            for (uint32_t r = first; r < n_rows; r += n_threads) {
+                Prepared& p = prepared[r];
+                p.logits = logits + (uint64_t)r * vocab;
+                p.err = distribution(p.logits, vocab, p.dist, &p.nan_token, p.buf);
+            }
+        };
+        std::vector<std::thread> pool;
+        for (uint32_t t = 1; t < n_threads; ++t) pool.emplace_back(work, t);
+        work(0);
+        for (auto& t : pool) t.join();
+        n_prepared = n_rows;
+    }
+    // the prepared distribution of this row, if any (moved out: each row is consumed once)
+    bool take_prepared(const float* logits, Dist& d, SErr* e, uint64_t* nan_token) {
+        for (uint32_t r = 0; r < n_prepared; ++r)
+            if (prepared[r].logits == logits) {
+                *e = prepared[r].err;
+                *nan_token = prepared[r].nan_token;
+                std::swap(d, prepared[r].dist);
+                prepared[r].logits = nullptr;
+                return true;
+            }
+        return false;
+    }
 
     // The filtered categorical distribution of sampler-v1 (diagnose_candidates, sampling.rs:1541-1614).
     SErr distribution(const float* logits, uint64_t n, Dist& d, uint64_t* nan_token) {
+        SErr e;
+        if (take_prepared(logits, d, &e, nan_token)) return e;
+        return distribution(logits, n, d, nan_token, buf);
+    }
+    SErr distribution(const float* logits, uint64_t n, Dist& d, uint64_t* nan_token, Buffers& buf) const {
         uint64_t len = 0;
         SErr e = order_keys(logits, n, cfg.top_k, buf, &len, nan_token);
         if (e != S_OK) return e;
@@ -451,6 +501,11 @@ dfl_status dfl_accept_prefix(const int32_t* verified_tokens, uint32_t n_tokens, 
 
     // The request sampler advances in place and is rolled back on any error (accept.rs:147,176).
     dfl_sampler& next = *sampler;
+    next.prepare_rows(target_logits, n_tokens, vocab);
+    struct Unprepare {
+        dfl_sampler& s;
+        ~Unprepare() { s.n_prepared = 0; }
+    } unprepare{next};
     const Xoshiro saved_rng = sampler->rng;
     const uint64_t saved_draws = sampler->draws;
     auto rollback = [&]() { sampler->rng = saved_rng; sampler->draws = saved_draws; };

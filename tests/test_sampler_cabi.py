@@ -206,3 +206,43 @@ def test_accept_prefix_equals_oracle_on_random_blocks():
         w = S.decide_dflash_accept_prefix(verified, [float(x) for x in rows.reshape(-1)], v, None, o, 100, [])
         assert d["accepted_drafts"] == w.accepted_drafts and d["next_carry"] == w.next_carry
         assert d["retain_input_count"] == w.retain_input_count and prod.draws == o.draws and prod.rng_state() == o.rng.state
+
+
+def test_rows_prepared_ahead_on_large_vocab_equal_oracle_and_keep_error_rows():
+    """At vocabularies of 4096 and more the product builds every row's distribution ahead of the sequential accept loop
+    on host threads; decisions, draw counts, generator state and error rows must not change."""
+    rng = np.random.default_rng(21)
+    v = 4608
+    for it in range(6):
+        n = 16 if it < 4 else int(rng.integers(2, 17))
+        rows = (rng.standard_normal((n, v)) * 5).astype(np.float32)
+        rows[:, :8] += 14.0            # a few dominant tokens so that drafts get accepted
+        verified = [int(rng.integers(0, v))]
+        for r in range(n - 1):
+            verified.append(int(np.argmax(rows[r])) if rng.random() < 0.7 else int(rng.integers(0, v)))
+        cfg = dict(temperature=0.7, top_p=0.95)
+        sparse = None
+        if it % 2:    # sparse proposals: the draft plus one other candidate
+            sparse = [(verified[r + 1], [(verified[r + 1], 0.75), ((verified[r + 1] + 1) % v, 0.25)]) for r in range(n - 1)]
+        prod = pkg.Sampler(seed=it, **cfg)
+        o = S.Sampler(S.SamplingConfig(seed=it, **cfg))
+        d = pkg.accept_prefix(verified, rows, v, sparse, prod, 100, [])
+        osparse = None if sparse is None else [S.SparseProposal(t, c) for t, c in sparse]
+        w = S.decide_dflash_accept_prefix(verified, [float(x) for x in rows.reshape(-1)], v, osparse, o, 100, [])
+        assert d["accepted_drafts"] == w.accepted_drafts and d["next_carry"] == w.next_carry
+        assert prod.draws == o.draws and prod.rng_state() == o.rng.state
+    # a NaN in a row the loop never reaches is not an error; in a reached row it is, with the generator untouched
+    rows = np.zeros((4, v), dtype=np.float32)
+    rows[:, 3] = 50.0                   # every row samples token 3
+    verified = [0, 3, 9, 3]             # row 1's draft (9) is rejected
+    rows[2, 100] = NAN
+    req = pkg.Sampler(temperature=1.0, seed=5)
+    d = pkg.accept_prefix(verified, rows, v, None, req, 100, [])
+    assert d["accepted_drafts"] == [3] and d["next_carry"] == ("correction", 3) and req.draws == 2
+    rows[2, 100] = 0.0
+    rows[1, 100] = NAN
+    req = pkg.Sampler(temperature=1.0, seed=5)
+    before = req.rng_state()
+    with pytest.raises(pkg.DflError) as e:
+        pkg.accept_prefix(verified, rows, v, None, req, 100, [])
+    assert "row 1" in str(e.value) and req.rng_state() == before and req.draws == 0
