@@ -12,6 +12,7 @@ struct dfl_drafter;
 namespace dfl {
 dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, bool topk);
 dfl_status draft_block_topk(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos, int32_t* out_tokens);
+dfl_status restore_partial_launch(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t n_keep, uint32_t start_position);
 }
 // accessors implemented next to the drafter session (drafter.cu)
 extern "C" {
@@ -91,14 +92,14 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         dfl_sampling_config pc{scfg.temperature, 0, 1.0f, 0.0f, scfg.seed ^ 0x44464c4153483251ull};  // qwen/dflash.rs:91
         DFL_CHECK(dfl_sampler_create(&pc, &proposal_sampler));
     }
-    // the block's logits for the host sampler: pinned, so the 16 x vocab copy runs at link speed
-    struct PinnedLogits {
-        float* p = nullptr;
-        ~PinnedLogits() { if (p) cudaFreeHost(p); }
-        float* data() const { return p; }
-    } logits_host;
-    if (sampled && cudaMallocHost(&logits_host.p, (size_t)N * V * 4) != cudaSuccess)
+    // the block's logits for the host sampler: pinned (the 16 x vocab copy runs at link speed) and kept with the scratch,
+    // since pinning and unpinning 10 MB costs far more than a step
+    if (sampled && !sc->pinned_logits && cudaMallocHost(&sc->pinned_logits, (size_t)sc->block_size * V * 4) != cudaSuccess) {
+        sc->pinned_logits = nullptr;
+        if (proposal_sampler) dfl_sampler_destroy(proposal_sampler);
         return fail(DFL_ERR_OOM, "generate: pinned logits buffer");
+    }
+    struct { float* p; float* data() const { return p; } } logits_host{sc->pinned_logits};
     auto is_stop = [&](int32_t t) {
         for (uint32_t i = 0; i < params->n_stop_ids; ++i)
             if (params->stop_ids[i] == t) return true;
@@ -109,6 +110,18 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
     dfl_status rc = DFL_OK;
     int32_t draft[MAX_ROWS], verify_in[MAX_ROWS], argmax[MAX_ROWS];
     float gap[MAX_ROWS];
+    // A partial-accept rollback is launched without a wait and runs under the next draft; what is counted as restore
+    // time is the part of it that outlasts that draft (all of it when no draft runs).
+    bool restore_pending = false;
+    auto settle_restore = [&](bool draft_ran) {
+        if (!restore_pending) return;
+        restore_pending = false;
+        cudaEventSynchronize(s->ev1);
+        float ms = 0;
+        if (draft_ran) cudaEventElapsedTime(&ms, dv.ev1, s->ev1);
+        else cudaEventElapsedTime(&ms, s->ev0, s->ev1);
+        if (ms > 0) st.restore_ms += ms;
+    };
     for (;;) {
         tokens.push_back(carry);
         if (is_stop(carry)) break;
@@ -118,6 +131,7 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         if (remaining_ctx < N) {
             // off step (qwen/dflash.rs:629-637): exact single-token decode keeps the loop going near the capacity edge
             if (remaining_ctx == 0) break;
+            settle_restore(false);
             std::vector<float> l(V);
             rc = dfl_single_token(m, s, sc, dv.target_layer_ids, dv.n_target_layers, carry, position, l.data(), nullptr);
             if (rc != DFL_OK) break;
@@ -204,6 +218,7 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
             }
         }
         ++st.spec_steps;
+        settle_restore(!replay || params->replay_runs_drafter);
         // ---- packed verify of [carry, drafts...] ----
         verify_in[0] = carry;
         for (uint32_t i = 1; i < N; ++i) verify_in[i] = draft[i];
@@ -264,13 +279,10 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         st.append_ms += now_ms() - t_app;
         if (n_keep < N) {
             cudaEventRecord(s->ev0, s->st);
-            rc = n_keep == 0 ? dfl_restore_pre_block(m, s, sc, position) : dfl_restore_partial(m, s, sc, n_keep, position);
+            rc = n_keep == 0 ? dfl_restore_pre_block(m, s, sc, position) : restore_partial_launch(m, s, sc, n_keep, position);
             cudaEventRecord(s->ev1, s->st);
             if (rc != DFL_OK) break;
-            cudaEventSynchronize(s->ev1);
-            float ms = 0;
-            cudaEventElapsedTime(&ms, s->ev0, s->ev1);
-            st.restore_ms += ms;
+            restore_pending = true;
             ++st.restore_calls;
         }
         st.accepted_drafts += dec.n_accepted;
@@ -283,6 +295,12 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         carry = dec.next_carry;
     }
     if (proposal_sampler) dfl_sampler_destroy(proposal_sampler);
+    settle_restore(false);
+    if (rc == DFL_OK) {   // nothing of this call is left in flight when it returns
+        if (cudaStreamSynchronize(s->st) != cudaSuccess) rc = fail(DFL_ERR_CUDA, "generate: stream synchronize failed");
+        else rc = check_dev_err(s->st, s->err);
+        if (rc != DFL_OK) s->poisoned = true;
+    }
     const uint32_t n_emit = (uint32_t)std::min<size_t>(tokens.size(), params->max_tokens);
     std::memcpy(tokens_out, tokens.data(), (size_t)n_emit * 4);
     *n_out = n_emit;

@@ -698,6 +698,7 @@ void dfl_scratch_destroy(dfl_scratch* sc) {
     for (void* p : sc->allocs) cudaFree(p);
     if (sc->pinned_i) cudaFreeHost(sc->pinned_i);
     if (sc->pinned_f) cudaFreeHost(sc->pinned_f);
+    if (sc->pinned_logits) cudaFreeHost(sc->pinned_logits);
     delete sc;
 }
 
@@ -744,7 +745,12 @@ dfl_status dfl_scratch_read_capture(const dfl_scratch* sc, uint32_t n, float* ou
     return DFL_OK;
 }
 
-dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t n_keep, uint32_t start_position) {
+}  // extern "C"
+
+namespace dfl {
+// The launches of dfl_restore_partial without the wait: the outer loop lets them run under the next draft (the drafter
+// never reads the target's recurrent state) and the next verify follows them in stream order.
+dfl_status restore_partial_launch(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t n_keep, uint32_t start_position) {
     DFL_CHECK(session_guard(m, s, "restore_partial"));
     if (!sc || sc->m != m || !sc->have_block) return fail(DFL_ERR_BAD_ARG, "restore_partial: scratch holds no verify block");
     if (start_position != sc->last_start) return fail(DFL_ERR_KV_STATE, "restore_partial: start_position differs from the last verify");
@@ -765,6 +771,14 @@ dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* 
     }
     s->kv_n_pos = start_position + n_keep;  // KV rows beyond stay and are overwritten by the next block
     sc->last_n = n_keep;
+    return DFL_OK;
+}
+}  // namespace dfl
+
+extern "C" {
+
+dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t n_keep, uint32_t start_position) {
+    DFL_CHECK(restore_partial_launch(m, s, sc, n_keep, start_position));
     DFL_CUDA(cudaStreamSynchronize(s->st));
     return completion_check(s);
 }

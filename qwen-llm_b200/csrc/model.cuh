@@ -140,6 +140,7 @@ struct dfl_scratch {
     int32_t* tokens_dev = nullptr;
     int32_t* pinned_i = nullptr;  // [16] tokens in, [16] argmax out
     float* pinned_f = nullptr;    // [16] gaps
+    float* pinned_logits = nullptr;  // [block][vocab], made on first use by the sampled outer loop
     uint32_t last_n = 0, last_start = 0;
     bool have_block = false;
     uint64_t part_floats = 0;

@@ -80,22 +80,30 @@ SErr order_keys(const float* logits, uint64_t n, uint64_t top_k, Buffers& b, uin
     if (n == 0) return S_EMPTY;
     if (n > 0x7fffffffull) return S_TOO_LARGE;
     b.keys.resize(n);
+    const bool full = top_k == 0 || top_k >= n;
+    // keys in token order; the four byte histograms of the logit half are taken in the same pass
+    uint32_t hist[4][256];
+    if (full) std::memset(hist, 0, sizeof(hist));
     for (uint64_t t = 0; t < n; ++t) {
         if (std::isnan(logits[t])) { *nan_token = t; return S_NAN; }
-        b.keys[t] = ((uint64_t)descending_bits(logits[t]) << 32) | t;
+        const uint32_t d = descending_bits(logits[t]);
+        b.keys[t] = ((uint64_t)d << 32) | t;
+        if (full) { ++hist[0][d & 255]; ++hist[1][(d >> 8) & 255]; ++hist[2][(d >> 16) & 255]; ++hist[3][d >> 24]; }
     }
-    if (top_k == 0 || top_k >= n) {
-        // stable LSD radix over the logit half (3 digits of 11/11/10 bits); keys were built in token order
+    if (full) {
+        // stable LSD radix over the logit half, one byte per pass (256 write streams stay in the first-level cache);
+        // keys were built in token order, so equal logits keep ascending token order
         if (n >= 2) {
             b.scratch.resize(n);
-            for (int digit = 0; digit < 3; ++digit) {
-                const int shift = 32 + 11 * digit;
-                uint32_t hist[2048] = {0};
-                for (uint64_t i = 0; i < n; ++i) ++hist[(b.keys[i] >> shift) & 2047];
-                if (hist[(b.keys[0] >> shift) & 2047] == n) continue;
+            for (int digit = 0; digit < 4; ++digit) {
+                const int shift = 32 + 8 * digit;
+                uint32_t* h = hist[digit];
+                if (h[(b.keys[0] >> shift) & 255] == n) continue;   // every key has the same byte here
                 uint32_t off = 0;
-                for (auto& h : hist) { const uint32_t c = h; h = off; off += c; }
-                for (uint64_t i = 0; i < n; ++i) b.scratch[hist[(b.keys[i] >> shift) & 2047]++] = b.keys[i];
+                for (int i = 0; i < 256; ++i) { const uint32_t c = h[i]; h[i] = off; off += c; }
+                const uint64_t* src = b.keys.data();
+                uint64_t* dst = b.scratch.data();
+                for (uint64_t i = 0; i < n; ++i) dst[h[(src[i] >> shift) & 255]++] = src[i];
                 b.keys.swap(b.scratch);
             }
         }
@@ -123,8 +131,10 @@ struct dfl_sampler {
     Xoshiro rng;
     uint64_t draws = 0;
     Buffers buf;
-    // Distributions of a block's rows built ahead of the sequential accept loop (one host thread per row): building a
-    // row's distribution draws nothing from the generator, so only the picks have to stay in row order.
+    // Distributions of a block's rows built ahead of the sequential accept loop, one host thread per row: building a
+    // row's distribution draws nothing from the generator, so only the picks have to stay in row order.  Rows are
+    // built in waves as the loop reaches them (the first wave covers a typical accepted prefix), so a block rejected
+    // early does not pay for all of its rows.
     struct Prepared {
         const float* logits = nullptr;
         Dist dist;
@@ -133,39 +143,50 @@ struct dfl_sampler {
         Buffers buf;
     };
     std::vector<Prepared> prepared;
-    uint32_t n_prepared = 0;
+    const float* block_logits = nullptr;
+    uint64_t block_vocab = 0;
+    uint32_t block_rows = 0, n_prepared = 0;
 
     void prepare_rows(const float* logits, uint32_t n_rows, uint64_t vocab) {
-        n_prepared = 0;
-        if (cfg.temperature == 0.0f || n_rows < 2 || vocab < 4096) return;
-        const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
-        if (hw < 2) return;
+        block_logits = nullptr;
+        n_prepared = block_rows = 0;
+        if (cfg.temperature == 0.0f || n_rows < 2 || vocab < 4096 || std::thread::hardware_concurrency() < 2) return;
+        block_logits = logits;
+        block_vocab = vocab;
+        block_rows = n_rows;
         if (prepared.size() < n_rows) prepared.resize(n_rows);
-        const uint32_t n_threads = std::min<uint32_t>(n_rows, hw);
-        auto work = [&](uint32_t first) {
-            for (uint32_t r = first; r < n_rows; r += n_threads) {
+    }
+    void end_block() { block_logits = nullptr; n_prepared = block_rows = 0; }
+    void prepare_wave(uint32_t upto) {
+        const unsigned hw = std::max(2u, std::thread::hardware_concurrency());
+        const uint32_t first = n_prepared, last = std::min(block_rows, std::max(upto + 1, first + std::min<uint32_t>(hw, first == 0 ? 6 : 10)));
+        const uint32_t n_threads = std::min<uint32_t>(last - first, hw);
+        auto work = [&](uint32_t t) {
+            for (uint32_t r = first + t; r < last; r += n_threads) {
                 Prepared& p = prepared[r];
-                p.logits = logits + (uint64_t)r * vocab;
-                p.err = distribution(p.logits, vocab, p.dist, &p.nan_token, p.buf);
+                p.logits = block_logits + (uint64_t)r * block_vocab;
+                p.err = distribution(p.logits, block_vocab, p.dist, &p.nan_token, p.buf);
             }
         };
         std::vector<std::thread> pool;
         for (uint32_t t = 1; t < n_threads; ++t) pool.emplace_back(work, t);
         work(0);
         for (auto& t : pool) t.join();
-        n_prepared = n_rows;
+        n_prepared = last;
     }
-    // the prepared distribution of this row, if any (moved out: each row is consumed once)
+    // the prepared distribution of this row, if it belongs to the current block (moved out: a row is consumed once)
     bool take_prepared(const float* logits, Dist& d, SErr* e, uint64_t* nan_token) {
-        for (uint32_t r = 0; r < n_prepared; ++r)
-            if (prepared[r].logits == logits) {
-                *e = prepared[r].err;
-                *nan_token = prepared[r].nan_token;
-                std::swap(d, prepared[r].dist);
-                prepared[r].logits = nullptr;
-                return true;
-            }
-        return false;
+        if (!block_logits || logits < block_logits) return false;
+        const uint64_t off = (uint64_t)(logits - block_logits);
+        if (off % block_vocab || off / block_vocab >= block_rows) return false;
+        const uint32_t r = (uint32_t)(off / block_vocab);
+        if (r >= n_prepared) prepare_wave(r);
+        if (prepared[r].logits != logits) return false;
+        *e = prepared[r].err;
+        *nan_token = prepared[r].nan_token;
+        std::swap(d, prepared[r].dist);
+        prepared[r].logits = nullptr;
+        return true;
     }
 
     // The filtered categorical distribution of sampler-v1 (diagnose_candidates, sampling.rs:1541-1614).
@@ -204,10 +225,11 @@ struct dfl_sampler {
             const double max_logit = key_logit(keys[0]) / t;
             if (max_logit == -inf) return S_NO_CANDIDATES;
             bool finite = true;
+            double* w = d.weights.data();
+            for (uint64_t i = 0; i < len; ++i) w[i] = key_logit(keys[i]) / t - max_logit;   // vectorisable part first
             for (uint64_t i = 0; i < len; ++i) {
-                const double w = std::exp(key_logit(keys[i]) / t - max_logit);
-                finite &= std::isfinite(w);
-                d.weights[i] = w;
+                w[i] = std::exp(w[i]);
+                finite &= std::isfinite(w[i]);
             }
             if (!finite) return S_NO_CANDIDATES;
         }
@@ -504,7 +526,7 @@ dfl_status dfl_accept_prefix(const int32_t* verified_tokens, uint32_t n_tokens, 
     next.prepare_rows(target_logits, n_tokens, vocab);
     struct Unprepare {
         dfl_sampler& s;
-        ~Unprepare() { s.n_prepared = 0; }
+        ~Unprepare() { s.end_block(); }
     } unprepare{next};
     const Xoshiro saved_rng = sampler->rng;
     const uint64_t saved_draws = sampler->draws;
