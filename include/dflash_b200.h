@@ -134,6 +134,7 @@ typedef struct dfl_scratch dfl_scratch;   /* MetalDFlashVerifyScratch + LayerMaj
 typedef struct dfl_qmatrix dfl_qmatrix;   /* one resident quantised matrix (MetalTensor)   */
 typedef struct dfl_sampler dfl_sampler;   /* Sampler             sampling.rs:305           */
 typedef struct dfl_codebook dfl_codebook; /* DFlash2Codebook     metal_dflash.rs:3163      */
+typedef struct dfl_gguf dfl_gguf;         /* GgufFile            gguf.rs:154               */
 
 /* ---- library / diagnostics --------------------------------------------- */
 const char* dfl_version(void);
@@ -363,6 +364,34 @@ dfl_status dfl_draft_block_sampled(dfl_dsession* ds, int32_t carry, uint32_t noi
  * sel_h_out may be NULL. */
 dfl_status dfl_dsession_read_selector(dfl_dsession* ds, int32_t* ids_out, float* vals_out,
                                       float* sel_h_out);
+
+/* ---- GGUF files (host) --------------------------------------------------- */
+/* GgufFile::open (gguf.rs:154): maps a single-file GGUF (version 2 or 3), validates header, counts,
+ * alignment and every tensor's extent against the file (gguf.rs:1094-1300).  Split files are refused. */
+dfl_status dfl_gguf_open(const char* path, dfl_gguf** out);
+void dfl_gguf_close(dfl_gguf* g);
+uint64_t dfl_gguf_tensor_count(const dfl_gguf* g);
+/* The file's tensors as one table, names and data pointing into the mapping (valid until close):
+ * pass it to dfl_model_create as it is. */
+const dfl_tensor* dfl_gguf_tensors(const dfl_gguf* g);
+/* GgufFile::find (gguf.rs:474); DFL_ERR_MISSING_TENSOR when absent. */
+dfl_status dfl_gguf_find(const dfl_gguf* g, const char* name, dfl_tensor* out);
+/* Typed metadata getters (gguf.rs:514-729).  *found = 0 when the key is absent (or, for u64 / f64 /
+ * str, of another type); get_bool and the array getter fail when the key exists with a wrong type. */
+dfl_status dfl_gguf_get_u64(const dfl_gguf* g, const char* key, uint64_t* out, int32_t* found);
+dfl_status dfl_gguf_get_f64(const dfl_gguf* g, const char* key, double* out, int32_t* found);
+dfl_status dfl_gguf_get_bool(const dfl_gguf* g, const char* key, int32_t* out, int32_t* found);
+dfl_status dfl_gguf_get_str(const dfl_gguf* g, const char* key, char* buf, uint64_t cap, int32_t* found);
+/* integer or bool arrays widened to u64; out may be NULL to query *count */
+dfl_status dfl_gguf_get_u64_array(const dfl_gguf* g, const char* key, uint64_t* out, uint64_t cap,
+                                  uint64_t* count, int32_t* found);
+/* build_arch_from_metadata (loader.rs:1331-1656): `qwen35.*` / `qwen35moe.*` keys -> dfl_arch. */
+dfl_status dfl_gguf_arch(const dfl_gguf* g, dfl_arch* out);
+/* The drafter's DFlashConfig (loader.rs:860-1060) from a "dflash-draft" or "dflash" file. */
+dfl_status dfl_gguf_dflash_config(const dfl_gguf* drafter, const dfl_arch* target, dfl_dflash_config* out);
+/* The drafter file's tensors under the names dfl_drafter_create expects (the "dflash" format's
+ * fc / enc.output_norm / ffn_norm names mapped to the "dflash-draft" ones, loader.rs:876-912). */
+dfl_status dfl_gguf_drafter_tensors(dfl_gguf* g, const dfl_tensor** table, uint64_t* count);
 
 /* ---- sampling + acceptance (host, f64) --------------------------------- */
 typedef struct dfl_sampling_config { /* SamplingConfig  sampling.rs:17-30 */

@@ -105,6 +105,9 @@ def lib():
         for name in ("dfl_session_kv_n_pos", "dfl_dsession_ctx_len"):
             if hasattr(L, name):
                 getattr(L, name).restype = C.c_uint32
+        if hasattr(L, "dfl_gguf_tensors"):
+            L.dfl_gguf_tensors.restype = C.POINTER(Tensor)
+            L.dfl_gguf_tensor_count.restype = C.c_uint64
         if hasattr(L, "dfl_sampler_next_unit_f64"):
             L.dfl_sampler_next_unit_f64.restype = C.c_double
         _LIB = L
@@ -253,6 +256,16 @@ class Model:
             idb = (C.c_uint8 * 128).from_buffer_copy(nccl_id)
             check(lib().dfl_model_create_ep(C.c_int32(device), C.byref(arch), arr, C.c_uint64(len(tensors)), C.c_int32(rank),
                                             C.c_int32(world), idb, C.byref(self.h)))
+
+    @classmethod
+    def from_gguf(cls, gguf, device=0):
+        """Builds the target from an open GGUF: arch from its metadata, weights from its tensor table."""
+        self = cls.__new__(cls)
+        self.arch, self.device = gguf.arch(), device
+        self.h = C.c_void_p()
+        tab, n = gguf.table()
+        check(lib().dfl_model_create(C.c_int32(device), C.byref(self.arch), tab, C.c_uint64(n), C.byref(self.h)))
+        return self
 
     def verify_weight_bytes(self):
         return int(lib().dfl_model_verify_weight_bytes(self.h))
@@ -530,6 +543,15 @@ class Drafter:
         self.h = C.c_void_p()
         check(lib().dfl_drafter_create(target.h, C.byref(cfg), arr, C.c_uint64(len(tensors)), C.byref(self.h)))
 
+    @classmethod
+    def from_gguf(cls, target, gguf):
+        self = cls.__new__(cls)
+        self.target, self.cfg = target, gguf.dflash_config(target.arch)
+        self.h = C.c_void_p()
+        tab, n = gguf.drafter_table()
+        check(lib().dfl_drafter_create(target.h, C.byref(self.cfg), tab, C.c_uint64(n), C.byref(self.h)))
+        return self
+
     def weight_bytes(self):
         return int(lib().dfl_drafter_weight_bytes(self.h))
 
@@ -630,6 +652,90 @@ def generate(model, session, scratch, dsession, sampler, first_logits, max_token
     check(lib().dfl_generate(model.h, session.h, scratch.h, dsession.h, sampler.h, _ptr(first_logits), C.byref(p), _ptr(out), C.byref(n),
                              C.byref(stats)))
     return out[:n.value].copy(), stats
+
+
+class GGUF:
+    """A mapped GGUF file: tensor table, typed metadata, the derived Arch / DFlashConfig."""
+
+    def __init__(self, path):
+        self.h = C.c_void_p()
+        check(lib().dfl_gguf_open(str(path).encode(), C.byref(self.h)))
+
+    def close(self):
+        if self.h:
+            lib().dfl_gguf_close(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def n_tensors(self):
+        return int(lib().dfl_gguf_tensor_count(self.h))
+
+    def table(self):
+        """(pointer to the dfl_tensor table, count): pass to Model.from_table / Drafter.from_table."""
+        return lib().dfl_gguf_tensors(self.h), self.n_tensors
+
+    def drafter_table(self):
+        tab, n = C.POINTER(Tensor)(), C.c_uint64(0)
+        check(lib().dfl_gguf_drafter_tensors(self.h, C.byref(tab), C.byref(n)))
+        return tab, int(n.value)
+
+    def tensors(self):
+        tab, n = self.table()
+        return [tab[i] for i in range(n)]
+
+    def find(self, name):
+        t = Tensor()
+        check(lib().dfl_gguf_find(self.h, name.encode(), C.byref(t)))
+        return t
+
+    @staticmethod
+    def tensor_bytes(t):
+        return np.ctypeslib.as_array(C.cast(t.data, C.POINTER(C.c_uint8)), shape=(int(t.n_bytes),)).copy() if t.n_bytes else np.zeros(0, np.uint8)
+
+    def get_u64(self, key):
+        v, f = C.c_uint64(0), C.c_int32(0)
+        check(lib().dfl_gguf_get_u64(self.h, key.encode(), C.byref(v), C.byref(f)))
+        return int(v.value) if f.value else None
+
+    def get_f64(self, key):
+        v, f = C.c_double(0), C.c_int32(0)
+        check(lib().dfl_gguf_get_f64(self.h, key.encode(), C.byref(v), C.byref(f)))
+        return float(v.value) if f.value else None
+
+    def get_bool(self, key):
+        v, f = C.c_int32(0), C.c_int32(0)
+        check(lib().dfl_gguf_get_bool(self.h, key.encode(), C.byref(v), C.byref(f)))
+        return bool(v.value) if f.value else None
+
+    def get_str(self, key):
+        buf, f = C.create_string_buffer(4096), C.c_int32(0)
+        check(lib().dfl_gguf_get_str(self.h, key.encode(), buf, C.c_uint64(4096), C.byref(f)))
+        return buf.value.decode() if f.value else None
+
+    def get_u64_array(self, key):
+        n, f = C.c_uint64(0), C.c_int32(0)
+        check(lib().dfl_gguf_get_u64_array(self.h, key.encode(), None, C.c_uint64(0), C.byref(n), C.byref(f)))
+        if not f.value:
+            return None
+        out = np.zeros(max(1, int(n.value)), dtype=np.uint64)
+        check(lib().dfl_gguf_get_u64_array(self.h, key.encode(), _ptr(out), C.c_uint64(out.size), C.byref(n), C.byref(f)))
+        return [int(x) for x in out[:int(n.value)]]
+
+    def arch(self):
+        a = Arch()
+        check(lib().dfl_gguf_arch(self.h, C.byref(a)))
+        return a
+
+    def dflash_config(self, target_arch):
+        c = DFlashConfig()
+        check(lib().dfl_gguf_dflash_config(self.h, C.byref(target_arch), C.byref(c)))
+        return c
 
 
 def gemm_timing_begin():

@@ -98,8 +98,6 @@ def test_selector_drafter_matches_oracle_pipeline(world):
             break   # later positions condition on a different predecessor
         agree += 1
     assert agree >= 1
-    # the selector changes the path: it is not simply the per-row argmax
-    assert any(int(np.argmax(got_logits[p])) != toks[p] for p in range(1, 16)) or True
     for x in (sess, scr, ds):
         x.close()
 
