@@ -255,6 +255,36 @@ dfl_status dfl_session_read_gdn_state(const dfl_session* s, uint32_t gdn_index, 
 dfl_status dfl_session_read_kv(const dfl_session* s, uint32_t attn_index, uint32_t pos,
                                float* k_out, float* v_out, uint64_t n);
 
+/* ---- session snapshots (SessionSnapshot, metal_forward/session.rs:13-94) ---- */
+#define DFL_SNAPSHOT_LAYOUT_VERSION 1
+typedef struct dfl_snapshot_identity { /* SnapshotAbi  session.rs:27-37 */
+    uint32_t layout_version;
+    uint32_t n_attn_layers;
+    uint32_t n_gdn_layers;
+    uint32_t kv_dim_elements;
+    uint32_t kv_bytes_per_token;
+    uint32_t kv_storage_kind; /* 0 = f32, 1 = f16 */
+    uint32_t gdn_state_elements_per_layer;
+    uint32_t gdn_conv_elements_per_layer;
+} dfl_snapshot_identity;
+dfl_status dfl_session_snapshot_identity(const dfl_model* m, const dfl_session* s,
+                                         dfl_snapshot_identity* out);
+/* Bytes a snapshot of the session's current prefix takes (with the drafter's context tail when
+ * ds != NULL); 0 on a bad argument. */
+uint64_t dfl_session_snapshot_bytes(const dfl_model* m, const dfl_session* s, const dfl_dsession* ds);
+/* Writes the state after the kv_n_pos tokens consumed so far into `blob`: header with the
+ * identity, K and V packed to the prefix, GDN conv and recurrent state, and (ds != NULL) the
+ * drafter context a restored request can still see (every column, or the last swa_window
+ * columns of an all-sliding-window drafter, metal_dflash.rs:103-140).  Token ids, a pending
+ * token and final logits stay with the caller, as in the reference's prefix cache. */
+dfl_status dfl_session_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession* ds, void* blob,
+                                uint64_t cap, uint64_t* written);
+/* Restores into a session of the same model and KV storage (identity checked, section lengths
+ * checked, prefix <= kv_capacity).  Continuing from the restored session is bitwise equal to
+ * continuing from the session the snapshot was taken from. */
+dfl_status dfl_session_restore_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession* ds,
+                                        const void* blob, uint64_t n_bytes);
+
 /* MetalDFlashVerifyScratch::fresh + MetalDFlashLayerMajorScratch::fresh
  * metal_dflash.rs:6003-6075, :8025. */
 dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t n_capture_layers,

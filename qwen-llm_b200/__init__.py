@@ -349,6 +349,32 @@ def packed_verify(model, session, scratch, layer_ids, tokens, start_position, wa
     return am, gap, logits
 
 
+class SnapshotIdentity(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("layout_version", "n_attn_layers", "n_gdn_layers", "kv_dim_elements", "kv_bytes_per_token",
+                                          "kv_storage_kind", "gdn_state_elements_per_layer", "gdn_conv_elements_per_layer")]
+
+
+def snapshot_identity(model, session):
+    out = SnapshotIdentity()
+    check(lib().dfl_session_snapshot_identity(model.h, session.h, C.byref(out)))
+    return out
+
+
+def session_snapshot(model, session, dsession=None):
+    """SessionSnapshot of the current prefix (and the drafter's visible context) as one byte array."""
+    lib().dfl_session_snapshot_bytes.restype = C.c_uint64
+    n = int(lib().dfl_session_snapshot_bytes(model.h, session.h, dsession.h if dsession is not None else None))
+    blob = np.zeros(n, dtype=np.uint8)
+    written = C.c_uint64(0)
+    check(lib().dfl_session_snapshot(model.h, session.h, dsession.h if dsession is not None else None, _ptr(blob), C.c_uint64(n), C.byref(written)))
+    return blob[:int(written.value)]
+
+
+def session_restore_snapshot(model, session, dsession, blob):
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    check(lib().dfl_session_restore_snapshot(model.h, session.h, dsession.h if dsession is not None else None, _ptr(blob), C.c_uint64(blob.size)))
+
+
 def restore_partial(model, session, scratch, n_keep, start_position):
     check(lib().dfl_restore_partial(model.h, session.h, scratch.h, C.c_uint32(n_keep), C.c_uint32(start_position)))
 

@@ -540,6 +540,59 @@ dfl_status dsession_append_dev(dfl_dsession* ds, const float* rows, cudaMemcpyKi
     return DFL_OK;
 }
 
+// ---- drafter context in a session snapshot -----------------------------------------------------------------------
+// What a restored request needs of the drafter is the context it can still see: every column when a layer has full
+// attention, else the last `swa_window` columns (dflash_capture_window_limit, metal_dflash.rs:110-118).  The reference
+// stores those columns raw (K * H f32 each) and projects them again on restore; this library stores their projected,
+// rotated K / V rows (half the bytes, nothing to recompute), which are exactly what the attention kernels read.
+uint32_t dsession_tail_columns(const dfl_dsession* ds) {
+    const dfl_dflash_config& c = ds->d->cfg;
+    bool all_swa = c.swa_window > 0;
+    for (uint32_t il = 0; il < c.n_layer; ++il) all_swa = all_swa && c.layer_is_swa[il] != 0;
+    return all_swa ? std::min(ds->ctx_len, c.swa_window) : ds->ctx_len;
+}
+uint64_t dsession_snapshot_bytes(const dfl_dsession* ds) {
+    const dfl_dflash_config& c = ds->d->cfg;
+    const uint64_t cols = dsession_tail_columns(ds), kv_dim = (uint64_t)c.n_kv_heads * c.head_dim;
+    return cols * 4 + (uint64_t)c.n_layer * 2 * cols * kv_dim * 4;
+}
+// layout: positions u32[cols], then per layer K rows [cols][kv_dim] f32 and V rows [cols][kv_dim] f32
+dfl_status dsession_snapshot_write(dfl_dsession* ds, uint8_t* dst, uint32_t* cols_out) {
+    DFL_CHECK(dsession_project_pending(ds));
+    const dfl_dflash_config& c = ds->d->cfg;
+    const uint32_t cols = dsession_tail_columns(ds), first = ds->ctx_len - cols;
+    const uint64_t kv_dim = (uint64_t)c.n_kv_heads * c.head_dim, rows = (uint64_t)cols * kv_dim * 4;
+    memcpy(dst, ds->pos_host.data() + first, (size_t)cols * 4);
+    dst += (size_t)cols * 4;
+    for (uint32_t il = 0; il < c.n_layer && cols; ++il) {
+        DFL_CUDA(cudaMemcpyAsync(dst, ds->k_ctx[il] + (uint64_t)first * kv_dim, rows, cudaMemcpyDeviceToHost, ds->st));
+        DFL_CUDA(cudaMemcpyAsync(dst + rows, ds->v_ctx[il] + (uint64_t)first * kv_dim, rows, cudaMemcpyDeviceToHost, ds->st));
+        dst += 2 * rows;
+    }
+    DFL_CHECK(check_dev_err(ds->st, ds->err));
+    *cols_out = cols;
+    return DFL_OK;
+}
+dfl_status dsession_snapshot_read(dfl_dsession* ds, const uint8_t* src, uint32_t cols, uint64_t n_bytes) {
+    const dfl_dflash_config& c = ds->d->cfg;
+    const uint64_t kv_dim = (uint64_t)c.n_kv_heads * c.head_dim, rows = (uint64_t)cols * kv_dim * 4;
+    if (cols > ds->ctx_capacity) return fail(DFL_ERR_CTX_OVERFLOW, "snapshot: drafter context tail exceeds the session's capacity");
+    if (n_bytes != (uint64_t)cols * 4 + (uint64_t)c.n_layer * 2 * rows) return fail(DFL_ERR_BAD_SHAPE, "snapshot: drafter section length mismatch");
+    ds->ctx_len = ds->ready = ds->pending_base = 0;
+    ds->pos_host.assign(reinterpret_cast<const uint32_t*>(src), reinterpret_cast<const uint32_t*>(src) + cols);
+    if (cols) DFL_CUDA(cudaMemcpyAsync(ds->pos_ctx_dev, ds->pos_host.data(), (size_t)cols * 4, cudaMemcpyHostToDevice, ds->st));
+    src += (size_t)cols * 4;
+    for (uint32_t il = 0; il < c.n_layer && cols; ++il) {
+        DFL_CUDA(cudaMemcpyAsync(ds->k_ctx[il], src, rows, cudaMemcpyHostToDevice, ds->st));
+        DFL_CUDA(cudaMemcpyAsync(ds->v_ctx[il], src + rows, rows, cudaMemcpyHostToDevice, ds->st));
+        src += 2 * rows;
+    }
+    DFL_CUDA(cudaStreamSynchronize(ds->st));
+    ds->ctx_len = ds->ready = ds->pending_base = cols;
+    return DFL_OK;
+}
+const dfl_model* dsession_target(const dfl_dsession* ds) { return ds->d->target; }
+
 // One draft pass; leaves logits / argmax on the device, and with `topk` (always on a drafter with a selector) the
 // top-16 per row plus the selector's gate rows (phase-4 tail, metal_dflash.rs:17099-17128).
 dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, bool topk) {

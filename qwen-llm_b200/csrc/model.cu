@@ -783,6 +783,104 @@ dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* 
     return completion_check(s);
 }
 
+// ---- session snapshots (SessionSnapshot, metal_forward/session.rs:13-94) ------------------------------------------
+struct SnapshotHeader {
+    uint32_t magic, header_bytes;
+    dfl_snapshot_identity id;
+    uint32_t prefix_len, drafter_cols;
+    uint64_t kv_bytes /* each of K and V */, conv_bytes, state_bytes, drafter_bytes;
+};
+static constexpr uint32_t kSnapshotMagic = 0x534C4644;   // "DFLS"
+
+dfl_status dfl_session_snapshot_identity(const dfl_model* m, const dfl_session* s, dfl_snapshot_identity* out) {
+    if (!m || !s || !out || s->m != m) return fail(DFL_ERR_BAD_ARG, "snapshot_identity: bad argument");
+    const GdnGeom gg = m->gdn_geom();
+    out->layout_version = DFL_SNAPSHOT_LAYOUT_VERSION;
+    out->n_attn_layers = (uint32_t)s->k_cache.size();
+    out->n_gdn_layers = (uint32_t)s->conv.size();
+    out->kv_dim_elements = m->arch.n_kv_heads * m->arch.attn_head_dim;
+    out->kv_bytes_per_token = out->kv_dim_elements * (s->kv_f16 ? 2u : 4u);
+    out->kv_storage_kind = s->kv_f16 ? 1u : 0u;
+    out->gdn_state_elements_per_layer = (uint32_t)((uint64_t)gg.n_v * 128 * 128);
+    out->gdn_conv_elements_per_layer = (uint32_t)(3 * gg.conv_dim());
+    return DFL_OK;
+}
+
+uint64_t dfl_session_snapshot_bytes(const dfl_model* m, const dfl_session* s, const dfl_dsession* ds) {
+    dfl_snapshot_identity id;
+    if (dfl_session_snapshot_identity(m, s, &id) != DFL_OK) return 0;
+    return sizeof(SnapshotHeader) + 2ull * id.n_attn_layers * s->kv_n_pos * id.kv_bytes_per_token +
+           (uint64_t)id.n_gdn_layers * (id.gdn_conv_elements_per_layer + id.gdn_state_elements_per_layer) * 4 + (ds ? dsession_snapshot_bytes(ds) : 0);
+}
+
+dfl_status dfl_session_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession* ds, void* blob, uint64_t cap, uint64_t* written) {
+    DFL_CHECK(session_guard(m, s, "snapshot"));
+    if (!blob || !written) return fail(DFL_ERR_BAD_ARG, "snapshot: null argument");
+    if (ds && dsession_target(ds) != m) return fail(DFL_ERR_BAD_ARG, "snapshot: drafter session belongs to another model");
+    const uint64_t need = dfl_session_snapshot_bytes(m, s, ds);
+    if (cap < need) return fail(DFL_ERR_BAD_SHAPE, "snapshot: buffer too small, needs " + std::to_string(need) + " bytes");
+    SnapshotHeader h{};
+    h.magic = kSnapshotMagic;
+    h.header_bytes = sizeof(SnapshotHeader);
+    DFL_CHECK(dfl_session_snapshot_identity(m, s, &h.id));
+    h.prefix_len = s->kv_n_pos;
+    h.kv_bytes = (uint64_t)h.id.n_attn_layers * h.prefix_len * h.id.kv_bytes_per_token;
+    h.conv_bytes = (uint64_t)h.id.n_gdn_layers * h.id.gdn_conv_elements_per_layer * 4;
+    h.state_bytes = (uint64_t)h.id.n_gdn_layers * h.id.gdn_state_elements_per_layer * 4;
+    uint8_t* p = (uint8_t*)blob + sizeof(SnapshotHeader);
+    const uint64_t per_layer = (uint64_t)h.prefix_len * h.id.kv_bytes_per_token;
+    for (int which = 0; which < 2; ++which)   // packed to the prefix: the unused tail of the cache is not carried
+        for (size_t ai = 0; ai < s->k_cache.size(); ++ai, p += per_layer)
+            if (per_layer) DFL_CUDA(cudaMemcpyAsync(p, which ? s->v_cache[ai] : s->k_cache[ai], per_layer, cudaMemcpyDeviceToHost, s->st));
+    for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)h.id.gdn_conv_elements_per_layer * 4)
+        DFL_CUDA(cudaMemcpyAsync(p, s->conv[gi], (uint64_t)h.id.gdn_conv_elements_per_layer * 4, cudaMemcpyDeviceToHost, s->st));
+    for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)h.id.gdn_state_elements_per_layer * 4)
+        DFL_CUDA(cudaMemcpyAsync(p, s->ssm[s->ssm_cur[gi]][gi], (uint64_t)h.id.gdn_state_elements_per_layer * 4, cudaMemcpyDeviceToHost, s->st));
+    DFL_CUDA(cudaStreamSynchronize(s->st));
+    DFL_CHECK(completion_check(s));
+    if (ds) {
+        h.drafter_bytes = dsession_snapshot_bytes(ds);
+        DFL_CHECK(dsession_snapshot_write(ds, p, &h.drafter_cols));
+        p += h.drafter_bytes;
+    }
+    memcpy(blob, &h, sizeof(h));
+    *written = (uint64_t)(p - (uint8_t*)blob);
+    return DFL_OK;
+}
+
+dfl_status dfl_session_restore_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession* ds, const void* blob, uint64_t n_bytes) {
+    DFL_CHECK(session_guard(m, s, "restore_snapshot"));
+    if (!blob) return fail(DFL_ERR_BAD_ARG, "restore_snapshot: null argument");
+    if (ds && dsession_target(ds) != m) return fail(DFL_ERR_BAD_ARG, "restore_snapshot: drafter session belongs to another model");
+    SnapshotHeader h;
+    if (n_bytes < sizeof(h)) return fail(DFL_ERR_BAD_SHAPE, "snapshot header length mismatch");
+    memcpy(&h, blob, sizeof(h));
+    if (h.magic != kSnapshotMagic || h.header_bytes != sizeof(h)) return fail(DFL_ERR_BAD_ARG, "restore_snapshot: not a session snapshot");
+    dfl_snapshot_identity id;
+    DFL_CHECK(dfl_session_snapshot_identity(m, s, &id));
+    if (memcmp(&id, &h.id, sizeof(id)) != 0) return fail(DFL_ERR_BAD_SHAPE, "snapshot identity mismatch");   // SnapshotValidationError::IdentityMismatch
+    if (h.prefix_len > s->kv_capacity)
+        return fail(DFL_ERR_KV_STATE, "snapshot prefix length " + std::to_string(h.prefix_len) + " exceeds capacity " + std::to_string(s->kv_capacity));
+    const uint64_t per_layer = (uint64_t)h.prefix_len * id.kv_bytes_per_token;
+    if (h.kv_bytes != per_layer * id.n_attn_layers || h.conv_bytes != (uint64_t)id.n_gdn_layers * id.gdn_conv_elements_per_layer * 4 ||
+        h.state_bytes != (uint64_t)id.n_gdn_layers * id.gdn_state_elements_per_layer * 4 ||
+        n_bytes != sizeof(h) + 2 * h.kv_bytes + h.conv_bytes + h.state_bytes + h.drafter_bytes)
+        return fail(DFL_ERR_BAD_SHAPE, "snapshot section length mismatch");
+    if (ds && h.drafter_bytes == 0 && h.prefix_len > 0) return fail(DFL_ERR_BAD_ARG, "restore_snapshot: the snapshot carries no drafter context");
+    const uint8_t* p = (const uint8_t*)blob + sizeof(h);
+    for (int which = 0; which < 2; ++which)
+        for (size_t ai = 0; ai < s->k_cache.size(); ++ai, p += per_layer)
+            if (per_layer) DFL_CUDA(cudaMemcpyAsync(which ? s->v_cache[ai] : s->k_cache[ai], p, per_layer, cudaMemcpyHostToDevice, s->st));
+    for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)id.gdn_conv_elements_per_layer * 4)
+        DFL_CUDA(cudaMemcpyAsync(s->conv[gi], p, (uint64_t)id.gdn_conv_elements_per_layer * 4, cudaMemcpyHostToDevice, s->st));
+    for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)id.gdn_state_elements_per_layer * 4)
+        DFL_CUDA(cudaMemcpyAsync(s->ssm[s->ssm_cur[gi]][gi], p, (uint64_t)id.gdn_state_elements_per_layer * 4, cudaMemcpyHostToDevice, s->st));
+    DFL_CUDA(cudaStreamSynchronize(s->st));
+    s->kv_n_pos = h.prefix_len;
+    if (ds) DFL_CHECK(dsession_snapshot_read(ds, p, h.drafter_cols, h.drafter_bytes));
+    return completion_check(s);
+}
+
 dfl_status dfl_restore_pre_block(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t start_position) {
     DFL_CHECK(session_guard(m, s, "restore_pre_block"));
     if (!sc || sc->m != m || !sc->have_block) return fail(DFL_ERR_BAD_ARG, "restore_pre_block: scratch holds no verify block");

@@ -153,4 +153,9 @@ namespace dfl {
 dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, const uint32_t* layer_ids, uint32_t n_ids,
                        const int32_t* tokens, uint32_t n, uint32_t start, bool want_head);
 dfl_status session_guard(const dfl_model* m, dfl_session* s, const char* what);
+// the drafter session's part of a session snapshot (drafter.cu)
+uint64_t dsession_snapshot_bytes(const dfl_dsession* ds);
+dfl_status dsession_snapshot_write(dfl_dsession* ds, uint8_t* dst, uint32_t* cols_out);
+dfl_status dsession_snapshot_read(dfl_dsession* ds, const uint8_t* src, uint32_t cols, uint64_t n_bytes);
+const dfl_model* dsession_target(const dfl_dsession* ds);
 }  // namespace dfl
