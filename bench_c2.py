@@ -384,7 +384,7 @@ class Seq:
     def __init__(self, w, index):
         self.w, self.index = w, index
         self.prompt = np.random.default_rng(5000 + index).integers(0, w.arch.vocab_size, size=C3_PROMPT).astype(np.int32)
-        self.seed = C3_SEED * 1000 + index
+        self.seed = importlib.import_module("qwen-llm_b200.dp").per_sequence_seed(C3_SEED, index)   # independent of the rank count
         self.sess = self.ds = None
 
     def fresh(self):
@@ -429,7 +429,8 @@ def run_c3(args, rank, world, device):
     V = w.arch.vocab_size
     steps, warm = args.steps, max(args.warmup, 3)
     w.scr = pkg.Scratch(w.model, 16, len(w.layer_ids))
-    seqs = [Seq(w, i) for i in range(C3_SEQS) if i % world == rank]
+    dp = importlib.import_module("qwen-llm_b200.dp")
+    seqs = [Seq(w, i) for i in dp.partition_sequences(C3_SEQS, world, rank)]
 
     def barrier():
         if world > 1:
@@ -477,12 +478,9 @@ def run_c3(args, rank, world, device):
     barrier()
     clocks = clock.stop()
     tot["dev_ms"] = tot["draft_ms"] + tot["verify_ms"] + tot["restore_ms"]
-    t = torch.tensor([tot["dev_ms"], wall_ms], dtype=torch.float64, device=f"cuda:{device}")
-    e = torch.tensor([float(tot["emitted"])], dtype=torch.float64, device=f"cuda:{device}")
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        torch.distributed.all_reduce(e, op=torch.distributed.ReduceOp.SUM)
-    dev_ms, wall_max, emitted = float(t[0]), float(t[1]), float(e[0])
+    # whole-job counters: times take the max over ranks, emitted tokens the sum
+    g = dp.gather_counters({"dev_ms": tot["dev_ms"], "wall_ms": wall_ms, "emitted": float(tot["emitted"])}, device=f"cuda:{device}")
+    dev_ms, wall_max, emitted = g["dev_ms"], g["wall_ms"], g["emitted"]
     peak, peak_kind = bench.measured_peaks()
     vbytes = w.model.verify_weight_bytes()
     n_steps_rank = steps * len(seqs)
