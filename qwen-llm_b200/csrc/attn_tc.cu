@@ -21,9 +21,8 @@ namespace dfl {
 namespace {
 constexpr int TC_HD = 128, TC_GROUP = 4, TC_Q = MAX_ROWS * TC_GROUP;   // 64 queries per CTA
 constexpr int TC_PITCH = 136;   // halfs per Q / K / V row in shared memory (272 B: conflict-free fragment loads)
-constexpr int TC_KEYS = 32;                        // keys per stage: half a 64-position chunk
-constexpr int TC_STAGE = 2 * TC_KEYS * TC_PITCH;   // halfs per K + V stage
-constexpr int TC_SMEM = (2 * TC_Q * TC_PITCH + 2 * TC_STAGE) * 2;   // 69632: three CTAs per SM
+constexpr int TC_STAGE = 2 * ATTN_CHUNK * TC_PITCH;   // halfs per K + V stage
+constexpr int TC_SMEM = (2 * TC_Q * TC_PITCH + 2 * TC_STAGE) * 2;   // 104448: two CTAs per SM
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -74,25 +73,21 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
     int c_end = (int)((n_pos + ATTN_CHUNK - 1) / ATTN_CHUNK);
     if (c_end > c_begin + chunks_per_span) c_end = c_begin + chunks_per_span;
 
-    // K / V rows of one 32-key unit and head into a stage: 32 x 256 B each, 16 B per copy, zero beyond the last position
-    auto fetch = [&](int u) {
-        __half* kst = kv + (u & 1) * TC_STAGE;
-        const uint32_t p0 = (uint32_t)u * TC_KEYS;
+    // K / V rows of one chunk and head into a stage: 64 x 256 B each, 16 B per copy, zero beyond the last position
+    auto fetch = [&](int c) {
+        __half* kst = kv + (c & 1) * TC_STAGE;
+        const uint32_t p0 = (uint32_t)c * ATTN_CHUNK;
 #pragma unroll
-        for (int i = 0; i < TC_KEYS * 16 / 128; ++i) {
+        for (int i = 0; i < ATTN_CHUNK * 16 / 128; ++i) {
             const int idx = threadIdx.x + 128 * i, kp = idx >> 4, v16 = idx & 15;
             const bool in = p0 + kp < n_pos;
             const uint64_t off = ((uint64_t)(in ? p0 + kp : p0) * g.n_kv + kvh) * TC_HD + v16 * 8;
             cp_async16_zfill(kst + kp * TC_PITCH + v16 * 8, k_cache + off, in);
-            cp_async16_zfill(kst + TC_KEYS * TC_PITCH + kp * TC_PITCH + v16 * 8, v_cache + off, in);
+            cp_async16_zfill(kst + ATTN_CHUNK * TC_PITCH + kp * TC_PITCH + v16 * 8, v_cache + off, in);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    // units of 32 keys: [u_begin, u_end) covers the span's chunks up to the last position
-    const int u_begin = c_begin * (ATTN_CHUNK / TC_KEYS);
-    int u_end = c_end * (ATTN_CHUNK / TC_KEYS);
-    if ((uint32_t)u_end * TC_KEYS >= n_pos + TC_KEYS) u_end = (int)((n_pos + TC_KEYS - 1) / TC_KEYS);
-    if (u_begin < u_end) fetch(u_begin);
+    if (c_begin < c_end) fetch(c_begin);
 
     // queries: pair = row * 4 + head-in-group, scaled by log2(e) / sqrt(hd) (scores live in the exp2 domain), split
     // into an exact f16 hi + lo pair
@@ -119,18 +114,17 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
-    constexpr int NT = TC_KEYS / 8;   // score tiles of 8 keys per unit
-    for (int u = u_begin; u < u_end; ++u) {
-        const uint32_t p0 = (uint32_t)u * TC_KEYS;
+    for (int c = c_begin; c < c_end; ++c) {
+        const uint32_t p0 = (uint32_t)c * ATTN_CHUNK;
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();   // unit u landed for every thread; the other stage is fully consumed (and the query planes written)
-        if (u + 1 < u_end) fetch(u + 1);
-        const __half* ks = kv + (u & 1) * TC_STAGE;
-        const __half* vs = ks + TC_KEYS * TC_PITCH;
-        // ---- S = Q K^T: 16 queries x 32 keys per warp ----
-        float s[NT][4];
+        __syncthreads();   // chunk c landed for every thread; the other stage is fully consumed (and the query planes written)
+        if (c + 1 < c_end) fetch(c + 1);
+        const __half* ks = kv + (c & 1) * TC_STAGE;
+        const __half* vs = ks + ATTN_CHUNK * TC_PITCH;
+        // ---- S = Q K^T: 16 queries x 64 keys per warp ----
+        float s[8][4];
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
         {
@@ -143,26 +137,26 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
                 const uint32_t e0 = lds32(qb + 16 * kk), e1 = lds32(qb + 8 * TC_PITCH + 16 * kk), e2 = lds32(qb + 16 * kk + 8),
                                e3 = lds32(qb + 8 * TC_PITCH + 16 * kk + 8);
 #pragma unroll
-                uint32_t b0[NT], b1[NT];
+                uint32_t b0[8], b1[8];
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
+                for (int nt = 0; nt < 8; ++nt) {
                     const __half* kr = ks + (8 * nt + gq) * TC_PITCH + 16 * kk + 2 * t;
                     b0[nt] = lds32(kr);
                     b1[nt] = lds32(kr + 8);
                     mma16816(s[nt], h0, h1, h2, h3, b0[nt], b1[nt]);
                 }
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) mma16816(s[nt], e0, e1, e2, e3, b0[nt], b1[nt]);
+                for (int nt = 0; nt < 8; ++nt) mma16816(s[nt], e0, e1, e2, e3, b0[nt], b1[nt]);
             }
         }
-        // ---- causal / range mask (only the units that reach past the block's first position need it) ----
-        if (p0 + TC_KEYS > start + 1) {
+        // ---- causal / range mask (only the chunks that reach past the block's first position need it) ----
+        if (p0 + ATTN_CHUNK > start + 1) {
             // keys of this chunk visible to the row: indices below lim (row r sees positions <= start + r; rows
             // beyond the call see nothing)
             const int lim0 = row0 < n_rows ? (int)(start + (uint32_t)row0 + 1 - p0) : 0;
             const int lim1 = row1 < n_rows ? (int)(start + (uint32_t)row1 + 1 - p0) : 0;
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
+            for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const int key = 8 * nt + 2 * t + j;
@@ -173,7 +167,7 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
         // ---- online softmax per query row, in registers ----
         float mc0 = -INFINITY, mc1 = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
+        for (int nt = 0; nt < 8; ++nt) {
             mc0 = fmaxf(mc0, fmaxf(s[nt][0], s[nt][1]));
             mc1 = fmaxf(mc1, fmaxf(s[nt][2], s[nt][3]));
         }
@@ -186,7 +180,7 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
         const float a0 = ex2(m0 - ms0), a1 = ex2(m1 - ms1);
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 s[nt][j] = ex2(s[nt][j] - ms0);
@@ -205,7 +199,7 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
 #pragma unroll
         for (int nt = 0; nt < 16; ++nt) { o[nt][0] *= a0; o[nt][1] *= a0; o[nt][2] *= a1; o[nt][3] *= a1; }
 #pragma unroll
-        for (int kk = 0; kk < TC_KEYS / 16; ++kk) {
+        for (int kk = 0; kk < ATTN_CHUNK / 16; ++kk) {
             // A fragment of keys 16 kk .. 16 kk + 15 = score tiles 2 kk (k 0-7) and 2 kk + 1 (k 8-15)
             const uint32_t h0 = pack_h2(s[2 * kk][0], s[2 * kk][1]), h1 = pack_h2(s[2 * kk][2], s[2 * kk][3]);
             const uint32_t h2 = pack_h2(s[2 * kk + 1][0], s[2 * kk + 1][1]), h3 = pack_h2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
@@ -236,10 +230,10 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
 
 bool attn_tc_supported(const AttnGeom& g, bool kv_f16) { return kv_f16 && g.hd == TC_HD && g.n_q / g.n_kv == TC_GROUP; }
 
-// chunks per span from the session's KV capacity only (never from the call): three CTAs per SM, two waves
+// chunks per span from the session's KV capacity only (never from the call): two CTAs per SM, two waves
 int attn_tc_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity) {
     const uint64_t cap_chunks = ((uint64_t)kv_capacity + ATTN_CHUNK - 1) / ATTN_CHUNK;
-    uint64_t b = (cap_chunks * g.n_kv + 6 * 148 - 1) / (6 * 148);
+    uint64_t b = (cap_chunks * g.n_kv + 4 * 148 - 1) / (4 * 148);
     if (b < 1) b = 1;
     if (b > 64) b = 64;
     return (int)b;
