@@ -376,6 +376,7 @@ def run_verify_only(args, rank, world, device):
 # workload c3: sampled acceptance, 32 independent sequences, data parallel
 # ---------------------------------------------------------------------------
 C3_SEQS, C3_PROMPT, C3_T, C3_TOP_P, C3_SEED, C3_KV = 32, 1024, 0.7, 0.95, 0xC3, 2048
+C3_THREADS = int(os.environ.get("DFL_C3_THREADS", "4"))   # host threads driving a rank's sequences in the end-to-end pass
 
 
 class Seq:
@@ -438,7 +439,7 @@ def run_c3(args, rank, world, device):
         torch.cuda.synchronize(device)
 
     # pass 0 per sequence: the sampled continuation itself (natural drafter, acceptance ~ 0 with random weights)
-    need = tokens_for_steps(PATTERN, 0, warm + steps) + 16
+    need = tokens_for_steps(PATTERN, 0, warm + 2 * steps) + 16   # warm-up, the device-timed pass, the end-to-end pass
     nat = {"emitted": 0, "steps": 0, "dev_ms": 0.0, "wall_ms": 0.0}
     state = []
     t_setup = time.perf_counter()
@@ -473,14 +474,50 @@ def run_c3(args, rank, world, device):
         for k in ("draft_ms", "verify_ms", "restore_ms", "accept_ms"):
             tot[k] += getattr(st, k)
     torch.cuda.synchronize(device)
-    wall_ms = (time.perf_counter() - t0) * 1e3
+    wall_serial_ms = (time.perf_counter() - t0) * 1e3
     launches = pkg.launch_count() - launches0
     barrier()
     clocks = clock.stop()
+    # End-to-end pass: the same number of further steps of every sequence, driven by C3_THREADS host threads, each with
+    # its own scratch and its own share of the sequences (a session is only ever touched by one thread).  While one
+    # thread's sequence is in the host sampler another thread's sequence keeps the GPU busy.
+    import threading
+    n_done = n_b - 1           # tokens emitted by the device-timed pass, after the n_a of the warm-up
+    n_c = tokens_for_steps(PATTERN, warm + steps, steps)
+    threads = max(1, min(C3_THREADS, len(seqs)))
+    scratches = [w.scr] + [pkg.Scratch(w.model, 16, len(w.layer_ids)) for _ in range(threads - 1)]
+    errors, emitted_e2e = [], [0] * threads
+
+    def drive(ti):
+        try:
+            for q, (cont, hist, n_a, last) in list(zip(seqs, state))[ti::threads]:
+                at = n_a - 1 + n_done
+                toks_c, st = pkg.generate(w.model, q.sess, scratches[ti], q.ds, q.sampler(at_draw=at), forced(V, int(cont[at])), n_c,
+                                          replay_history=hist[at:], replay_runs_drafter=True, replay_unchecked=True)
+                assert np.array_equal(toks_c, cont[at:at + n_c]), "end-to-end output differs from the plain sampled continuation"
+                assert st.spec_steps == steps, (st.spec_steps, steps)
+                emitted_e2e[ti] += n_c - 1
+        except Exception as e:   # surfaced after the join
+            errors.append(e)
+
+    barrier()
+    t0 = time.perf_counter()
+    pool = [threading.Thread(target=drive, args=(ti,)) for ti in range(threads)]
+    for t in pool:
+        t.start()
+    for t in pool:
+        t.join()
+    torch.cuda.synchronize(device)
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    if errors:
+        raise errors[0]
+    for sc in scratches[1:]:
+        sc.close()
     tot["dev_ms"] = tot["draft_ms"] + tot["verify_ms"] + tot["restore_ms"]
     # whole-job counters: times take the max over ranks, emitted tokens the sum
-    g = dp.gather_counters({"dev_ms": tot["dev_ms"], "wall_ms": wall_ms, "emitted": float(tot["emitted"])}, device=f"cuda:{device}")
-    dev_ms, wall_max, emitted = g["dev_ms"], g["wall_ms"], g["emitted"]
+    g = dp.gather_counters({"dev_ms": tot["dev_ms"], "wall_ms": wall_ms, "emitted": float(tot["emitted"]), "emitted_e2e": float(sum(emitted_e2e))},
+                           device=f"cuda:{device}")
+    dev_ms, wall_max, emitted, emitted_wall = g["dev_ms"], g["wall_ms"], g["emitted"], g["emitted_e2e"]
     peak, peak_kind = bench.measured_peaks()
     vbytes = w.model.verify_weight_bytes()
     n_steps_rank = steps * len(seqs)
@@ -499,11 +536,13 @@ def run_c3(args, rank, world, device):
                    "parallelism": f"dp{world}: {C3_SEQS} sequences round-robin over {world} GPU(s), full replica each, no collective in the loop"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind,
                      "kernel": "one packed verify (all kernels), weight bytes / CUDA-event time"},
-        "e2e": {"value": emitted / (wall_max * 1e-3), "unit": bench.UNIT, "h2d_bytes_per_step": len(seqs) * 2 * 16 * 4,
-                "d2h_bytes_per_step": len(seqs) * (16 * V * 4 + 3 * 16 * 4)},
+        "e2e": {"value": emitted_wall / (wall_max * 1e-3), "unit": bench.UNIT, "h2d_bytes_per_step": len(seqs) * 2 * 16 * 4,
+                "d2h_bytes_per_step": len(seqs) * (16 * V * 4 + 3 * 16 * 4), "host_threads": threads,
+                "one_thread_tok_per_s": tot["emitted"] / (wall_serial_ms * 1e-3)},
         "gpu_launches": int(launches), "clocks": clocks,
         "per_outer_step_ms": {"draft": tot["draft_ms"] / n_steps_rank, "verify": verify_ms, "restore": tot["restore_ms"] / n_steps_rank,
-                              "host_accept": tot["accept_ms"] / n_steps_rank, "wall": wall_ms / n_steps_rank},
+                              "host_accept": tot["accept_ms"] / n_steps_rank, "wall_one_thread": wall_serial_ms / n_steps_rank,
+                              "wall_threads": wall_ms / n_steps_rank},
         "natural_drafter": {"tok_per_s": nat["emitted"] / (nat["dev_ms"] * 1e-3) if nat["dev_ms"] else None,
                             "e2e_tok_per_s": nat["emitted"] / (nat["wall_ms"] * 1e-3), "mean_emitted": nat["emitted"] / max(nat["steps"], 1)},
         "setup": {"build_s": w.build_s, "sequences_on_rank0": len(seqs), "prefill_and_continuation_s": setup_s},
