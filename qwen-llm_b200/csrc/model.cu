@@ -159,6 +159,21 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
                        const int32_t* tokens, uint32_t n, uint32_t start, bool want_head) {
     const dfl_arch& a = m->arch;
     cudaStream_t st = s->st;
+    // DFL_SIDE_STREAM=0 keeps every launch of the pass on one stream
+    static const bool side_enabled = [] { const char* e = getenv("DFL_SIDE_STREAM"); return !(e && e[0] == '0'); }();
+    cudaStream_t side = side_enabled ? s->st_side : st;
+    auto fork_side = [&]() -> dfl_status {   // the side stream continues from here
+        if (side == st) return DFL_OK;
+        DFL_CUDA(cudaEventRecord(s->ev_fork, st));
+        DFL_CUDA(cudaStreamWaitEvent(side, s->ev_fork, 0));
+        return DFL_OK;
+    };
+    auto join_side = [&]() -> dfl_status {   // the main stream waits for what the side stream was given
+        if (side == st) return DFL_OK;
+        DFL_CUDA(cudaEventRecord(s->ev_join, side));
+        DFL_CUDA(cudaStreamWaitEvent(st, s->ev_join, 0));
+        return DFL_OK;
+    };
     const uint64_t H = a.hidden_size, F = a.intermediate_size;
     const AttnGeom ag = m->attn_geom();
     const GdnGeom gg = m->gdn_geom();
@@ -202,10 +217,18 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             ++ai;
         } else {
             const int cd = gg.conv_dim();
-            DFL_CHECK(launch_group(st, L.in_qkv_z, sc->acts_h, sc->part, ep_norm, s->err));
-            DFL_CHECK(launch_small_matmul(st, L.w_ab, sc->xn, (int)H, (int)n, H, 2 * gg.n_v, ep_norm, sc->ab[gi], 2 * gg.n_v));
+            // qkv -> conv / norms on the main stream; the z projection (its own matrix when its format differs from
+            // qkv's) and the alpha / beta projection beside it: all three read only the layer's normalised input and
+            // write disjoint outputs
+            const MatGroup& G = L.in_qkv_z;
+            DFL_CHECK(fork_side());
+            DFL_CHECK(launch_gemm_fewrow(st, G.mats[0], sc->acts_h, sc->part + G.col_off[0], G.splits, ep_norm, s->err, pdl_enabled_for(1), G.total_cols));
+            for (size_t i = 1; i < G.mats.size(); ++i)
+                DFL_CHECK(launch_gemm_fewrow(side, G.mats[i], sc->acts_h, sc->part + G.col_off[i], G.splits, ep_norm, s->err, pdl_enabled_for(1), G.total_cols));
+            DFL_CHECK(launch_small_matmul(side, L.w_ab, sc->xn, (int)H, (int)n, H, 2 * gg.n_v, ep_norm, sc->ab[gi], 2 * gg.n_v));
             DFL_CHECK(launch_gdn_front(st, gg, sc->part, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, (int)n, L.conv_w, s->conv[gi],
                                        sc->qkv_raw[gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->conv_pre[gi]));
+            DFL_CHECK(join_side());
             const int cur = s->ssm_cur[gi];
             DFL_CHECK(launch_gdn_scan(st, gg, s->ssm[cur][gi], s->ssm[cur ^ 1][gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->ab[gi],
                                       L.dt_bias, L.a_log, (int)n, sc->o));
@@ -225,9 +248,12 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             // few-row GEMMs; the glue zeroes the inner columns of the experts a token did not choose
             const int E = (int)a.expert_count, Fe = (int)a.expert_feed_forward_length, Fs = (int)m->ep_fs, En = (int)m->ep_n;
             const int inner = En * Fe + Fs;
-            DFL_CHECK(launch_small_matmul(st, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
-            DFL_CHECK(launch_moe_route(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
+            // router + selection beside the gate|up GEMM (which reads every expert and needs no routing)
+            DFL_CHECK(fork_side());
+            DFL_CHECK(launch_small_matmul(side, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
+            DFL_CHECK(launch_moe_route(side, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
             DFL_CHECK(launch_group(st, L.moe_gate_up, sc->acts_h, sc->part, ep_norm, s->err));
+            DFL_CHECK(join_side());
             GlueParams p;
             p.mode = GLUE_SWIGLU;
             p.part = sc->part; p.splits = L.moe_gate_up.splits; p.ld_part = (int)L.moe_gate_up.total_cols;
@@ -548,6 +574,9 @@ dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t 
     if (ok && m->n_attn) ok = cudaMalloc(&s->attn_partials, attn_partials_floats(m->attn_geom(), kv_capacity) * 4) == cudaSuccess;
     ok = ok && cudaMalloc(&s->err, 4) == cudaSuccess;
     ok = ok && cudaEventCreate(&s->ev0) == cudaSuccess && cudaEventCreate(&s->ev1) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&s->st_side, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
         std::string why = cudaGetErrorString(cudaGetLastError());
         dfl_session_destroy(s);
@@ -571,6 +600,9 @@ void dfl_session_destroy(dfl_session* s) {
     cudaFree(s->err);
     if (s->ev0) cudaEventDestroy(s->ev0);
     if (s->ev1) cudaEventDestroy(s->ev1);
+    if (s->ev_fork) cudaEventDestroy(s->ev_fork);
+    if (s->ev_join) cudaEventDestroy(s->ev_join);
+    if (s->st_side) cudaStreamDestroy(s->st_side);
     if (s->st) cudaStreamDestroy(s->st);
     delete s;
 }

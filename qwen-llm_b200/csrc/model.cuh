@@ -120,6 +120,10 @@ struct dfl_session {
     cudaStream_t st = nullptr;
     int* err = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    // side stream for the branches of a layer that only depend on the layer's normalised input (the GDN z and
+    // alpha / beta projections, the expert router): they run beside the main projection instead of after it
+    cudaStream_t st_side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 struct dfl_scratch {
