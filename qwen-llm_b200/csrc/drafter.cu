@@ -248,6 +248,12 @@ struct dfl_dsession {
     uint8_t* acts_sel = nullptr;
     bool have_topk = false;
     uint8_t* pinned_sel = nullptr;   // [16][16] ids | [16][16] vals | [16][rank] gate rows
+    // projection of newly appended context columns: its own scratch, so that it can run on a side stream beside the
+    // start of the draft pass (layer l's attention waits for ev_ctx[l])
+    float *part_c = nullptr, *sumsq_c = nullptr;
+    uint8_t* acts_hc = nullptr;
+    cudaStream_t st_side = nullptr;
+    cudaEvent_t ev_ctx[DFL_MAX_DRAFTER_LAYERS] = {};
     int32_t* pinned_i = nullptr;
     cudaStream_t st = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -256,7 +262,7 @@ struct dfl_dsession {
 };
 
 namespace dfl {
-dfl_status dsession_project_pending(dfl_dsession* ds);
+dfl_status dsession_project_pending(dfl_dsession* ds, bool on_side = false);
 dfl_status dsession_append_dev(dfl_dsession* ds, const float* rows_dev, cudaMemcpyKind kind, const uint32_t* positions, uint32_t count);
 }
 
@@ -402,6 +408,13 @@ dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_
     ds->acts_f = (uint8_t*)alloc(acts_bytes(DFL_BF16, F));
     ds->acts_q = (uint8_t*)alloc(acts_bytes(DFL_BF16, q_dim));
     ds->acts_fc = (uint8_t*)alloc(acts_bytes(DFL_BF16, KH));
+    {
+        uint64_t part_c = (uint64_t)d->fc.splits * MAX_ROWS * d->fc.total_cols;
+        for (auto& L : d->layers) part_c = std::max<uint64_t>(part_c, (uint64_t)L.kv.splits * MAX_ROWS * L.kv.total_cols);
+        ds->part_c = (float*)alloc(part_c * 4);
+        ds->sumsq_c = (float*)alloc((H / GLUE_COLS) * MAX_ROWS * 4);
+        ds->acts_hc = (uint8_t*)alloc(acts_bytes(DFL_BF16, H));
+    }
     ds->acts_lm = (uint8_t*)alloc(acts_bytes(DFL_BF16, H));
     ds->logits = (float*)alloc(MAX_ROWS * V * 4);
     ds->gap = (float*)alloc(MAX_ROWS * 4);
@@ -419,6 +432,8 @@ dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_
     ok = ok && cudaMallocHost(&ds->pinned_i, 2 * MAX_ROWS * 4) == cudaSuccess;
     ok = ok && cudaMallocHost(&ds->pinned_sel, MAX_ROWS * 16 * 8 + (size_t)MAX_ROWS * c.selector_rank * 4) == cudaSuccess;
     ok = ok && cudaEventCreate(&ds->ev0) == cudaSuccess && cudaEventCreate(&ds->ev1) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&ds->st_side, cudaStreamNonBlocking) == cudaSuccess;
+    for (uint32_t il = 0; il < c.n_layer; ++il) ok = ok && cudaEventCreateWithFlags(&ds->ev_ctx[il], cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
         std::string why = cudaGetErrorString(cudaGetLastError());
         dfl_dsession_destroy(ds);
@@ -438,6 +453,9 @@ void dfl_dsession_destroy(dfl_dsession* ds) {
     if (ds->pinned_sel) cudaFreeHost(ds->pinned_sel);
     if (ds->ev0) cudaEventDestroy(ds->ev0);
     if (ds->ev1) cudaEventDestroy(ds->ev1);
+    for (auto& e : ds->ev_ctx)
+        if (e) cudaEventDestroy(e);
+    if (ds->st_side) cudaStreamDestroy(ds->st_side);
     if (ds->st) cudaStreamDestroy(ds->st);
     delete ds;
 }
@@ -476,20 +494,24 @@ dfl_status dfl_dsession_reset(dfl_dsession* ds) {
 
 namespace dfl {
 
-// Projects every appended-but-unprojected column: fc + hidden_norm, then per layer K/V + K-norm + RoPE.
-dfl_status dsession_project_pending(dfl_dsession* ds) {
+// Projects every appended-but-unprojected column: fc + hidden_norm, then per layer K/V + K-norm + RoPE.  With on_side
+// the work goes to the session's side stream and layer l's rows are complete when ev_ctx[l] fires (recorded after the
+// last block of columns); its scratch is separate from the draft pass's, the rows it writes are beyond every row a
+// running attention reads.
+dfl_status dsession_project_pending(dfl_dsession* ds, bool on_side) {
     const dfl_drafter* d = ds->d;
     const dfl_dflash_config& c = d->cfg;
     const uint64_t H = c.hidden_size, KH = (uint64_t)c.n_target_layers * H;
-    cudaStream_t st = ds->st;
+    cudaStream_t st = on_side ? ds->st_side : ds->st;
     GemmEpilogue ep_norm;
-    ep_norm.sumsq = ds->sumsq;
+    ep_norm.sumsq = ds->sumsq_c;
     ep_norm.n_sumsq = (int)(H / GLUE_COLS);
     ep_norm.norm_k = (float)H;
     ep_norm.eps = c.rms_norm_eps;
     const AttnGeom gkv = d->geom(0);
     while (ds->ready < ds->ctx_len) {
         const uint32_t c0 = ds->ready, nb = std::min<uint32_t>(MAX_ROWS, ds->ctx_len - c0);
+        const bool last_block = c0 + nb == ds->ctx_len;
         GlueParams p;
         p.mode = GLUE_COPY;
         p.x = ds->staging + (uint64_t)(c0 - ds->pending_base) * KH;
@@ -497,20 +519,21 @@ dfl_status dsession_project_pending(dfl_dsession* ds) {
         p.acts = ds->acts_fc; p.bf3 = act_layout_of(d->fc.mats[0]);
         p.n_rows = (int)nb; p.err = ds->err;
         DFL_CHECK(launch_glue(st, p, KH));
-        DFL_CHECK(launch_group(st, d->fc, ds->acts_fc, ds->part, GemmEpilogue{}, ds->err));
+        DFL_CHECK(launch_group(st, d->fc, ds->acts_fc, ds->part_c, GemmEpilogue{}, ds->err));
         GlueParams q;
         q.mode = GLUE_RESID;
-        q.part = ds->part; q.splits = d->fc.splits; q.ld_part = (int)d->fc.total_cols;
+        q.part = ds->part_c; q.splits = d->fc.splits; q.ld_part = (int)d->fc.total_cols;
         q.mul_w = d->hidden_norm_w;
-        q.sumsq = ds->sumsq;
-        q.acts = ds->acts_h; q.bf3 = act_layout_of(d->layers[0].kv.mats[0]);
+        q.sumsq = ds->sumsq_c;
+        q.acts = ds->acts_hc; q.bf3 = act_layout_of(d->layers[0].kv.mats[0]);
         q.n_rows = (int)nb; q.err = ds->err;
         DFL_CHECK(launch_glue(st, q, H));
         for (uint32_t il = 0; il < c.n_layer; ++il) {
             const DLayerW& L = d->layers[il];
-            DFL_CHECK(launch_group(st, L.kv, ds->acts_h, ds->part, ep_norm, ds->err));
-            DFL_CHECK(launch_attn_front(st, gkv, false, ds->part, L.kv.splits, (int)L.kv.total_cols, nullptr, L.k_norm_w, 0, (int)nb, ds->k_ctx[il],
+            DFL_CHECK(launch_group(st, L.kv, ds->acts_hc, ds->part_c, ep_norm, ds->err));
+            DFL_CHECK(launch_attn_front(st, gkv, false, ds->part_c, L.kv.splits, (int)L.kv.total_cols, nullptr, L.k_norm_w, 0, (int)nb, ds->k_ctx[il],
                                         ds->v_ctx[il], false, nullptr, nullptr, ds->pos_ctx_dev + c0, (long long)c0));
+            if (on_side && last_block) DFL_CUDA(cudaEventRecord(ds->ev_ctx[il], st));
         }
         ds->ready += nb;
     }
@@ -602,7 +625,15 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, boo
     const uint64_t H = c.hidden_size, F = c.intermediate_size, V = tgt->arch.vocab_size;
     const int n = (int)c.block_size;
     cudaStream_t st = ds->st;
-    DFL_CHECK(dsession_project_pending(ds));
+    // the columns appended since the last pass are projected on the side stream while this pass starts
+    // (DFL_SIDE_STREAM=0: before it, on the same stream)
+    static const bool side_enabled = [] { const char* e = getenv("DFL_SIDE_STREAM"); return !(e && e[0] == '0'); }();
+    const bool ctx_on_side = side_enabled && ds->ready < ds->ctx_len;
+    if (ctx_on_side) {   // order the side stream after everything this session has queued on its main stream
+        DFL_CUDA(cudaEventRecord(ds->ev1, st));
+        DFL_CUDA(cudaStreamWaitEvent(ds->st_side, ds->ev1, 0));
+    }
+    DFL_CHECK(dsession_project_pending(ds, ctx_on_side));
     GemmEpilogue ep_norm;
     ep_norm.sumsq = ds->sumsq;
     ep_norm.n_sumsq = (int)(H / GLUE_COLS);
@@ -640,6 +671,7 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, boo
             const uint32_t min_pos = noise_start >= window - 1 ? noise_start - (window - 1) : 0;
             ctx_begin = (int)(std::lower_bound(ds->pos_host.begin(), ds->pos_host.begin() + ds->ctx_len, min_pos) - ds->pos_host.begin());
         }
+        if (ctx_on_side) DFL_CUDA(cudaStreamWaitEvent(st, ds->ev_ctx[il], 0));
         DFL_CHECK(launch_drafter_attn(st, g, ds->q_rot, ds->k_ctx[il], ds->v_ctx[il], reinterpret_cast<const int32_t*>(ds->pos_ctx_dev), ctx_begin,
                                       (int)ds->ctx_len, ds->k_noise, ds->v_noise, noise_start, n, c.causal != 0, window, ds->attn_part, ds->acts_q,
                                       bf(L.wo), ds->err));
