@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the DFlash speculative-decoding step on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c2v|c4v|c5v|gemm] [--impl reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c5|c2v|c4v|c5v|gemm] [--impl reference]
 
 Prints ONE JSON line on rank 0.  A "step" is one pass of the hot path over one batch of
 seeded synthetic input:
@@ -11,6 +11,7 @@ seeded synthetic input:
     32000, greedy prefix acceptance);
   * workload c3: the same target and drafter with sampled acceptance (T 0.7, top-p 0.95), 32 independent
     sequences split over the GPUs (strong scaling);
+  * workload c5: the c2 loop after a long pre-filled context (--ctx, default 131072 positions, fp16 KV);
   * workloads c2v / c4v / c5v (packed verify only: dense, routed-expert, long context) and gemm are
     kernel-level side benches.
 `value` is accepted tokens per second with inputs resident in HBM; `e2e` is the same metric
@@ -300,7 +301,7 @@ def main():
     ap.add_argument("--workload", default=os.environ.get("DFL_BENCH_WORKLOAD", "auto"))
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--gemm", default="q4_k:4096:24576", help="workload gemm only: dtype:n_in:n_out")
-    ap.add_argument("--ctx", type=int, default=131072, help="workload c5v only: context length filled before timing")
+    ap.add_argument("--ctx", type=int, default=131072, help="workloads c5 / c5v: context length filled before timing")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

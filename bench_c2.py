@@ -54,9 +54,11 @@ def tokens_for_steps(pattern, first_step, n_steps):
 
 
 class World:
-    def __init__(self, device, seed, prompt_len=PROMPT):
+    def __init__(self, device, seed, prompt_len=PROMPT, kv_cap=KV_CAP):
         pkg, syn = _pkg(), _syn()
         self.pkg = pkg
+        self.kv_cap = kv_cap
+        self.snapshot = None       # (blob, first logits) of the prefilled prompt: later fresh() calls restore it
         self.arch = syn.arch_9b()
         t0 = time.perf_counter()
         ents = syn.target_entries(self.arch, seed=seed, device=device)
@@ -77,12 +79,19 @@ class World:
         for x in (self.sess, self.scr, self.ds):
             if x is not None:
                 x.close()
-        self.sess = pkg.Session(self.model, KV_CAP, True)
+        self.sess = pkg.Session(self.model, self.kv_cap, True)
         self.scr = pkg.Scratch(self.model, 16, len(self.layer_ids))
-        self.ds = pkg.DSession(self.drafter, KV_CAP)
+        self.ds = pkg.DSession(self.drafter, self.kv_cap)
+        if self.snapshot is not None:   # bitwise the state the prefill left (tests/test_snapshot_gpu.py)
+            t0 = time.perf_counter()
+            pkg.session_restore_snapshot(self.model, self.sess, self.ds, self.snapshot[0])
+            self.restore_s = time.perf_counter() - t0
+            return self.snapshot[1]
         t0 = time.perf_counter()
         logits, _ = pkg.prefill(self.model, self.sess, self.scr, self.layer_ids, self.prompt, 0, feed_drafter=self.ds)
         self.prefill_s = time.perf_counter() - t0
+        self.snapshot = (pkg.session_snapshot(self.model, self.sess, self.ds), logits)
+        self.restore_s = None
         return logits
 
     def gen(self, first_logits, max_tokens, **kw):
@@ -218,7 +227,8 @@ def run(args, rank, world, device):
     import torch
     bench = importlib.import_module("bench")
     pkg = _pkg()
-    w = World(device, seed=100 + rank)
+    long_ctx = int(args.ctx) if args.workload == "c5" else 0   # config 5: the same loop after a long pre-filled context
+    w = World(device, seed=100 + rank, prompt_len=long_ctx, kv_cap=long_ctx + KV_CAP) if long_ctx else World(device, seed=100 + rank)
     V = w.arch.vocab_size
     steps, warm = args.steps, max(args.warmup, 3)
 
@@ -260,6 +270,11 @@ def run(args, rank, world, device):
     peak, peak_kind = bench.measured_peaks()
     vbytes = w.model.verify_weight_bytes()
     dbytes = w.drafter.weight_bytes()
+    kv_bytes = 0
+    if long_ctx:   # K and V rows one verify reads: attention layers x positions x 2 x n_kv x head_dim x 2 B (fp16)
+        n_attn = sum(1 for il in range(w.arch.n_layer) if _syn().is_attn(w.arch, il))
+        kv_bytes = n_attn * long_ctx * 2 * w.arch.n_kv_heads * w.arch.attn_head_dim * 2
+    vbytes += kv_bytes
     verify_ms = head["verify_ms"] / steps
     draft_ms = head["draft_ms"] / steps
     gemm_gbs = gemm_bytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else 0.0
@@ -267,8 +282,11 @@ def run(args, rank, world, device):
         "metric": bench.METRIC, "value": head["emitted"] * world / (dev_ms * 1e-3), "unit": bench.UNIT, "n_gpus": world, "steps": steps,
         "warmup": warm, "ms_per_step": dev_ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u4/u5/u6 weights x f16 hi+lo activations, f32 accumulate; bf16 drafter", "data": "synthetic",
-        "config": {"workload": "c2: 9B-class hybrid Q4_K_M target (32 layers, GDN:attn 3:1, H 4096, FFN 12288, V 151936) + 5-layer bf16 DFlash drafter, "
-                               "greedy, batch 1, prompt 512, block 16; replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step",
+        "config": {"workload": (f"c5: the config-2 target and drafter after a context of {long_ctx} random ids pre-filled into an fp16 KV cache "
+                                f"({kv_bytes / 2**30:.1f} GiB read per verify), greedy, batch 1, block 16; " if long_ctx else
+                                "c2: 9B-class hybrid Q4_K_M target (32 layers, GDN:attn 3:1, H 4096, FFN 12288, V 151936) + 5-layer bf16 DFlash drafter, "
+                                "greedy, batch 1, prompt 512, block 16; ") +
+                               "replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step",
                    "l2": "5.1 GB of weights per verify >> 126 MB L2", "parallelism": f"dp{world}: one independent sequence per GPU, no collective"},
         # DRAM bytes per launch: algorithmic bytes x 1.04, the dram-bytes / ggml-bytes ratio ncu measured for this kernel
         # (profiles/gemm_ts_c1_ncu_full.md; the traffic grows with the bytes streamed)
@@ -291,7 +309,7 @@ def run(args, rank, world, device):
             "natural_drafter": {"tok_per_s": natural["emitted"] / (natural["dev_ms"] * 1e-3) if natural["dev_ms"] else None,
                                 "e2e_tok_per_s": natural["emitted"] / (natural["wall_ms"] * 1e-3), "steps": natural["steps"],
                                 "mean_emitted": natural["emitted"] / max(natural["steps"], 1)}},
-        "setup": {"build_s": w.build_s, "prefill_s": w.prefill_s},
+        "setup": {"build_s": w.build_s, "prefill_s": w.prefill_s, "snapshot_bytes": int(w.snapshot[0].size), "snapshot_restore_s": w.restore_s},
     }
     if rank == 0 and world == 1:
         try:

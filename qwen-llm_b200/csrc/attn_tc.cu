@@ -228,6 +228,232 @@ __global__ void __launch_bounds__(128) attn_span_tc_kernel(AttnGeom g, const flo
     }
 }
 
+// ---- the drafter's attention on the same scheme -----------------------------------------------------------------------
+// Queries = the block's noise rows; keys = the context cache (f32, from column ctx_begin) followed by the noise rows'
+// own K / V; allowed(q, k) = (!causal || k_pos <= q_pos) && (window == 0 || |q_pos - k_pos| < window)
+// (kernels/dflash_attn.metal:99-103).  The f32 rows are split into exact f16 hi + lo pairs while they are copied into
+// shared memory (through registers: 2 CTAs per SM overlap each other's loads), so
+//   S = Qh Kh + Ql Kh + Qh Kl,   O += P Vh + P Vl   (P rounded to f16 as in the verify kernel)
+// keeps f32-class accuracy against the f32 cache.  Same record format and span rule as attn_span_tc_kernel.
+constexpr int DTC_SMEM = 6 * TC_Q * TC_PITCH * 2 + ATTN_CHUNK * 4;   // Q hi/lo, K hi/lo, V hi/lo, key positions: 104704
+
+__global__ void __launch_bounds__(128) dattn_span_tc_kernel(AttnGeom g, const float* q_rot, const float* k_ctx, const float* v_ctx,
+                                                            const uint32_t* pos_ctx, int ctx_begin, int n_ctx, const float* k_noise,
+                                                            const float* v_noise, uint32_t noise_start, int n_rows, int causal,
+                                                            uint32_t window, float* partials, int chunks_per_span) {
+    pdl_prologue();
+    extern __shared__ __align__(16) uint8_t sm_raw[];
+    __half* q_hi = reinterpret_cast<__half*>(sm_raw);
+    __half* q_lo = q_hi + TC_Q * TC_PITCH;
+    __half* k_hi = q_lo + TC_Q * TC_PITCH;
+    __half* k_lo = k_hi + ATTN_CHUNK * TC_PITCH;
+    __half* v_hi = k_lo + ATTN_CHUNK * TC_PITCH;
+    __half* v_lo = v_hi + ATTN_CHUNK * TC_PITCH;
+    uint32_t* kpos = reinterpret_cast<uint32_t*>(v_lo + ATTN_CHUNK * TC_PITCH);
+
+    const int span = blockIdx.x, kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, t = lane & 3;
+    const int n_keys = n_ctx + n_rows;
+    const int c_begin = span * chunks_per_span;
+    int c_end = (n_keys + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    if (c_end > c_begin + chunks_per_span) c_end = c_begin + chunks_per_span;
+
+    const float scale = 1.4426950408889634f / sqrtf((float)TC_HD);
+    for (int idx = threadIdx.x; idx < TC_Q * (TC_HD / 4); idx += 128) {
+        const int pair = idx / (TC_HD / 4), d4 = (idx % (TC_HD / 4)) * 4;
+        const int row = pair / TC_GROUP, qh = kvh * TC_GROUP + pair % TC_GROUP;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < n_rows) q = *reinterpret_cast<const float4*>(q_rot + ((uint64_t)row * g.n_q + qh) * TC_HD + d4);
+        uint32_t h01, l01, h23, l23;
+        split_pair(q.x * scale, q.y * scale, h01, l01);
+        split_pair(q.z * scale, q.w * scale, h23, l23);
+        *reinterpret_cast<uint2*>(q_hi + pair * TC_PITCH + d4) = make_uint2(h01, h23);
+        *reinterpret_cast<uint2*>(q_lo + pair * TC_PITCH + d4) = make_uint2(l01, l23);
+    }
+    const int pair0 = 16 * warp + gq, pair1 = pair0 + 8;
+    const int row0 = pair0 / TC_GROUP, row1 = pair1 / TC_GROUP;
+    const uint32_t qpos0 = noise_start + (uint32_t)row0, qpos1 = noise_start + (uint32_t)row1;
+    const bool live0 = row0 < n_rows, live1 = row1 < n_rows;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+
+    for (int c = c_begin; c < c_end; ++c) {
+        const int j0 = c * ATTN_CHUNK;
+        const int n_here = min(ATTN_CHUNK, n_keys - j0);
+        __syncthreads();   // previous chunk fully consumed (and the query planes written)
+        // K / V rows of the chunk: 64 x 512 B each, one float4 of K and of V per thread and step, split on the way in
+#pragma unroll 4
+        for (int i = 0; i < ATTN_CHUNK * 32 / 128; ++i) {
+            const int idx = threadIdx.x + 128 * i, kp = idx >> 5, d4 = (idx & 31) * 4;
+            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+            if (kp < n_here) {
+                const int j = j0 + kp;
+                if (j < n_ctx) {
+                    const uint64_t off = ((uint64_t)(ctx_begin + j) * g.n_kv + kvh) * TC_HD + d4;
+                    kk = *reinterpret_cast<const float4*>(k_ctx + off);
+                    vv = *reinterpret_cast<const float4*>(v_ctx + off);
+                } else {
+                    const uint64_t off = ((uint64_t)(j - n_ctx) * g.n_kv + kvh) * TC_HD + d4;
+                    kk = *reinterpret_cast<const float4*>(k_noise + off);
+                    vv = *reinterpret_cast<const float4*>(v_noise + off);
+                }
+            }
+            uint32_t h01, l01, h23, l23;
+            split_pair(kk.x, kk.y, h01, l01);
+            split_pair(kk.z, kk.w, h23, l23);
+            *reinterpret_cast<uint2*>(k_hi + kp * TC_PITCH + d4) = make_uint2(h01, h23);
+            *reinterpret_cast<uint2*>(k_lo + kp * TC_PITCH + d4) = make_uint2(l01, l23);
+            split_pair(vv.x, vv.y, h01, l01);
+            split_pair(vv.z, vv.w, h23, l23);
+            *reinterpret_cast<uint2*>(v_hi + kp * TC_PITCH + d4) = make_uint2(h01, h23);
+            *reinterpret_cast<uint2*>(v_lo + kp * TC_PITCH + d4) = make_uint2(l01, l23);
+        }
+        if (threadIdx.x < ATTN_CHUNK) {
+            const int j = j0 + (int)threadIdx.x;
+            kpos[threadIdx.x] = j < n_ctx ? pos_ctx[ctx_begin + j] : noise_start + (uint32_t)(j - n_ctx);
+        }
+        __syncthreads();
+        // ---- S = Qh Kh + Ql Kh + Qh Kl ----
+        float s[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+        {
+            const __half* qa = q_hi + (16 * warp + gq) * TC_PITCH + 2 * t;
+            const __half* qb = q_lo + (16 * warp + gq) * TC_PITCH + 2 * t;
+#pragma unroll
+            for (int kk = 0; kk < TC_HD / 16; ++kk) {
+                const uint32_t h0 = lds32(qa + 16 * kk), h1 = lds32(qa + 8 * TC_PITCH + 16 * kk), h2 = lds32(qa + 16 * kk + 8),
+                               h3 = lds32(qa + 8 * TC_PITCH + 16 * kk + 8);
+                const uint32_t e0 = lds32(qb + 16 * kk), e1 = lds32(qb + 8 * TC_PITCH + 16 * kk), e2 = lds32(qb + 16 * kk + 8),
+                               e3 = lds32(qb + 8 * TC_PITCH + 16 * kk + 8);
+                uint32_t b0[8], b1[8];
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    const __half* kr = k_hi + (8 * nt + gq) * TC_PITCH + 16 * kk + 2 * t;
+                    b0[nt] = lds32(kr);
+                    b1[nt] = lds32(kr + 8);
+                    mma16816(s[nt], h0, h1, h2, h3, b0[nt], b1[nt]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) mma16816(s[nt], e0, e1, e2, e3, b0[nt], b1[nt]);
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    const __half* kr = k_lo + (8 * nt + gq) * TC_PITCH + 16 * kk + 2 * t;
+                    mma16816(s[nt], h0, h1, h2, h3, lds32(kr), lds32(kr + 8));
+                }
+            }
+        }
+        // ---- mask by positions ----
+        const bool plain = !causal && window == 0 && n_here == ATTN_CHUNK && live0 && live1;
+        if (!plain) {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int key = 8 * nt + 2 * t + j;
+                    const uint32_t kp = kpos[key];
+                    const bool in = key < n_here;
+                    const uint32_t d0 = qpos0 > kp ? qpos0 - kp : kp - qpos0, d1 = qpos1 > kp ? qpos1 - kp : kp - qpos1;
+                    const bool ok0 = live0 && in && (!causal || kp <= qpos0) && (window == 0 || d0 < window);
+                    const bool ok1 = live1 && in && (!causal || kp <= qpos1) && (window == 0 || d1 < window);
+                    if (!ok0) s[nt][j] = -INFINITY;
+                    if (!ok1) s[nt][2 + j] = -INFINITY;
+                }
+        }
+        // ---- online softmax per query row, in registers ----
+        float mc0 = -INFINITY, mc1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            mc0 = fmaxf(mc0, fmaxf(s[nt][0], s[nt][1]));
+            mc1 = fmaxf(mc1, fmaxf(s[nt][2], s[nt][3]));
+        }
+        mc0 = fmaxf(mc0, __shfl_xor_sync(0xffffffffu, mc0, 1));
+        mc0 = fmaxf(mc0, __shfl_xor_sync(0xffffffffu, mc0, 2));
+        mc1 = fmaxf(mc1, __shfl_xor_sync(0xffffffffu, mc1, 1));
+        mc1 = fmaxf(mc1, __shfl_xor_sync(0xffffffffu, mc1, 2));
+        const float mn0 = fmaxf(m0, mc0), mn1 = fmaxf(m1, mc1);
+        const float ms0 = mn0 > -INFINITY ? mn0 : 0.f, ms1 = mn1 > -INFINITY ? mn1 : 0.f;
+        const float a0 = ex2(m0 - ms0), a1 = ex2(m1 - ms1);
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[nt][j] = ex2(s[nt][j] - ms0);
+                s[nt][2 + j] = ex2(s[nt][2 + j] - ms1);
+                sum0 += s[nt][j];
+                sum1 += s[nt][2 + j];
+            }
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+        sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+        sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+        m0 = mn0; m1 = mn1;
+        l0 = fmaf(l0, a0, sum0);
+        l1 = fmaf(l1, a1, sum1);
+        // ---- O = O * alpha + P Vh + P Vl ----
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) { o[nt][0] *= a0; o[nt][1] *= a0; o[nt][2] *= a1; o[nt][3] *= a1; }
+#pragma unroll
+        for (int kk = 0; kk < ATTN_CHUNK / 16; ++kk) {
+            const uint32_t h0 = pack_h2(s[2 * kk][0], s[2 * kk][1]), h1 = pack_h2(s[2 * kk][2], s[2 * kk][3]);
+            const uint32_t h2 = pack_h2(s[2 * kk + 1][0], s[2 * kk + 1][1]), h3 = pack_h2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < 8; ++np) {
+                uint32_t b[4], e[4];
+                const int voff = (16 * kk + (lane & 15)) * TC_PITCH + 16 * np + 8 * (lane >> 4);
+                ldmatrix_x4_trans(b, v_hi + voff);
+                ldmatrix_x4_trans(e, v_lo + voff);
+                mma16816(o[2 * np], h0, h1, h2, h3, b[0], b[1]);
+                mma16816(o[2 * np + 1], h0, h1, h2, h3, b[2], b[3]);
+                mma16816(o[2 * np], h0, h1, h2, h3, e[0], e[1]);
+                mma16816(o[2 * np + 1], h0, h1, h2, h3, e[2], e[3]);
+            }
+        }
+    }
+    float* rec0 = partials + (((uint64_t)span * g.n_kv + kvh) * TC_Q + pair0) * (TC_HD + 2);
+    float* rec1 = rec0 + 8 * (TC_HD + 2);
+    if (t == 0) {
+        rec0[0] = m0 * 0.6931471805599453f; rec0[1] = l0;
+        rec1[0] = m1 * 0.6931471805599453f; rec1[1] = l1;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+        const int d = 8 * nt + 2 * t;
+        *reinterpret_cast<float2*>(rec0 + 2 + d) = make_float2(o[nt][0], o[nt][1]);
+        *reinterpret_cast<float2*>(rec1 + 2 + d) = make_float2(o[nt][2], o[nt][3]);
+    }
+}
+
+bool dattn_tc_supported(const AttnGeom& g) { return g.hd == TC_HD && g.n_kv > 0 && g.n_q / g.n_kv == TC_GROUP; }
+
+// launches the span kernel and returns the number of records per (kv head, query) the combine pass has to merge
+dfl_status launch_dattn_span_tc(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
+                                const uint32_t* pos_ctx, int ctx_begin, int n_ctx, const float* k_noise, const float* v_noise,
+                                uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint32_t ctx_capacity,
+                                int* n_spans_out) {
+    static bool set = false;
+    if (!set) {
+        DFL_CUDA(cudaFuncSetAttribute(dattn_span_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DTC_SMEM));
+        set = true;
+    }
+    const int cps = attn_tc_chunks_per_span(g, ctx_capacity + MAX_ROWS);
+    const int n_chunks = (n_ctx + n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK;
+    const int n_spans = (n_chunks + cps - 1) / cps;
+    launch_kf(4, dattn_span_tc_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(128), (size_t)DTC_SMEM, st, g, q_rot, k_ctx, v_ctx, pos_ctx,
+              ctx_begin, n_ctx, k_noise, v_noise, noise_start, n_rows, causal ? 1 : 0, window, partials, cps);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    *n_spans_out = n_spans;
+    return DFL_OK;
+}
+
 bool attn_tc_supported(const AttnGeom& g, bool kv_f16) { return kv_f16 && g.hd == TC_HD && g.n_q / g.n_kv == TC_GROUP; }
 
 // chunks per span from the session's KV capacity only (never from the call): two CTAs per SM, two waves

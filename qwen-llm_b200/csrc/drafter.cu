@@ -176,10 +176,21 @@ __global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float*
 dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
                                const int32_t* pos_ctx, int ctx_begin, int ctx_len, const float* k_noise, const float* v_noise,
                                uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts, int bf3,
-                               int* err) {
+                               int* err, uint32_t ctx_capacity) {
     const int n_ctx = ctx_len - ctx_begin;
     const int n_chunks = (n_ctx + n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK;
     const uint32_t* pc = reinterpret_cast<const uint32_t*>(pos_ctx);
+    // tensor-core span kernel for the usual geometry (DFL_DATTN_TC=0 keeps the scalar kernel)
+    static const bool tc_enabled = [] { const char* e = getenv("DFL_DATTN_TC"); return !(e && e[0] == '0'); }();
+    if (tc_enabled && ctx_capacity > 0 && dattn_tc_supported(g)) {
+        int n_spans = 0;
+        DFL_CHECK(launch_dattn_span_tc(st, g, q_rot, k_ctx, v_ctx, pc, ctx_begin, n_ctx, k_noise, v_noise, noise_start, n_rows, causal, window,
+                                       partials, ctx_capacity, &n_spans));
+        launch_k(dattn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, MAX_ROWS)), dim3(32), 0, st, g, partials, n_spans, n_rows, acts, bf3, err);
+        count_launch();
+        DFL_CUDA(cudaGetLastError());
+        return DFL_OK;
+    }
     if (g.hd == 128) {
         const size_t smem = (size_t)(2 * ATTN_CHUNK * 129 + 8 * 128 + 8 * ATTN_CHUNK) * sizeof(float);
         static bool set = false;
@@ -674,7 +685,10 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, boo
         if (ctx_on_side) DFL_CUDA(cudaStreamWaitEvent(st, ds->ev_ctx[il], 0));
         DFL_CHECK(launch_drafter_attn(st, g, ds->q_rot, ds->k_ctx[il], ds->v_ctx[il], reinterpret_cast<const int32_t*>(ds->pos_ctx_dev), ctx_begin,
                                       (int)ds->ctx_len, ds->k_noise, ds->v_noise, noise_start, n, c.causal != 0, window, ds->attn_part, ds->acts_q,
-                                      bf(L.wo), ds->err));
+                                      bf(L.wo), ds->err,
+                                      // span length follows the keys the layer can see: a sliding-window layer over a
+                                      // monotonic context never scans more than window - 1 + n keys
+                                      window > 0 && monotonic ? std::min<uint32_t>(ds->ctx_capacity, window - 1 + (uint32_t)n) : ds->ctx_capacity));
         DFL_CHECK(launch_group(st, L.wo, ds->acts_q, ds->part, GemmEpilogue{}, ds->err));
         DFL_CHECK(norm_glue(ds->part, L.wo.splits, (int)L.wo.total_cols, L.post_norm_w, ds->acts_h, bf(L.gate_up)));
         DFL_CHECK(launch_group(st, L.gate_up, ds->acts_h, ds->part, ep_norm, ds->err));

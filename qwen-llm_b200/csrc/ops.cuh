@@ -141,6 +141,12 @@ dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q
 // tensor-core span kernel over an fp16 cache (attn_tc.cu)
 bool attn_tc_supported(const AttnGeom& g, bool kv_f16);
 int attn_tc_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity);
+// drafter attention on the tensor cores (f32 context cache split into f16 hi + lo on the way into shared memory)
+bool dattn_tc_supported(const AttnGeom& g);
+dfl_status launch_dattn_span_tc(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
+                                const uint32_t* pos_ctx, int ctx_begin, int n_ctx, const float* k_noise, const float* v_noise,
+                                uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint32_t ctx_capacity,
+                                int* n_spans_out);
 dfl_status launch_attn_span_tc(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* k_cache, const void* v_cache,
                                uint32_t start, int n_rows, float* partials, int chunks_per_span);
 uint64_t attn_partials_floats(const AttnGeom& g, uint32_t max_positions);
@@ -168,7 +174,7 @@ dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const floa
 dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
                                const int32_t* pos_ctx, int ctx_begin, int ctx_len, const float* k_noise, const float* v_noise,
                                uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts,
-                               int act_layout, int* err);
+                               int act_layout, int* err, uint32_t ctx_capacity = 0);
 
 // top-16 (id, value) per row, descending, total order with ties to the lower index (kernel_topk16_f32,
 // kernels/dflash2.metal:96-170); ids / vals [n_rows][16]; scratch of topk16_scratch_bytes(n_rows)

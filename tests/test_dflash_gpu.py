@@ -155,3 +155,39 @@ def test_greedy_loop_matches_oracle_loop(world):
         n_safe += 1
     assert n_safe >= 6, "seed gives an early near tie; pick another"
     assert list(got[:n_safe]) == want[:n_safe]
+
+
+def test_draft_block_with_tensor_core_attention_matches_oracle():
+    """A drafter with the usual head grouping (4 query heads per KV head, 128-wide) takes the tensor-core span kernel:
+    several 64-key chunks of context, a sliding window on the first layer, full attention on the last."""
+    arch = modelgen.tiny_arch()
+    T = modelgen.target_tensors(arch, seed=3)
+    cfg = modelgen.tiny_dflash_config(arch, n_q_heads=4, n_kv_heads=1, swa_window=40)
+    D = modelgen.drafter_tensors(arch, cfg, seed=6)
+    om, gm = modelgen.OracleModel(arch, T), pkg.Model(arch, T)
+    od, gd = modelgen.OracleDrafter(cfg, D), pkg.Drafter(gm, cfg, D)
+    rng = np.random.default_rng(9)
+    layer_ids = gd.layer_ids()
+    n_ctx = 150
+    prompt = rng.integers(0, arch.vocab_size, size=n_ctx)
+    for cap in (256, 20000):      # one chunk per span, then several chunks per span
+        sess, scr, ds = pkg.Session(gm, 256), pkg.Scratch(gm, 16, len(layer_ids)), pkg.DSession(gd, cap)
+        logits, hidden = pkg.prefill(gm, sess, scr, layer_ids, prompt, 0, feed_drafter=ds, want_hidden=True)
+        hidden = hidden.reshape(n_ctx, -1)
+        carry = int(np.argmax(logits))
+        noise = [carry] + [cfg.mask_token_id] * 15
+        want = od.draft(om, noise, hidden, np.arange(n_ctx), n_ctx)
+        toks, got = ds.draft_block(carry, n_ctx, want_logits=True)
+        np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+        cos = (got * want).sum(1) / np.sqrt((got * got).sum(1) * (want * want).sum(1))
+        assert cos.min() > 0.999
+        # a context with a gap in its positions (columns dropped from the middle) still follows the position mask
+        ds2 = pkg.DSession(gd, cap)
+        keep = np.r_[0:60, 100:150]
+        ds2.append_columns(hidden[keep], keep)
+        want2 = od.draft(om, noise, hidden[keep], keep, n_ctx)
+        _, got2 = ds2.draft_block(carry, n_ctx, want_logits=True)
+        np.testing.assert_allclose(got2, want2, rtol=RTOL, atol=ATOL)
+        for x in (sess, scr, ds, ds2):
+            x.close()
+    gd.close(); gm.close()
