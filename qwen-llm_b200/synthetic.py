@@ -100,7 +100,7 @@ def target_entries(arch, seed=0, std=0.02, device=0, layers=None):
             vec(b + "ssm_conv1d.weight", rng.standard_normal((conv_dim, 4)) * 0.3, [4, conv_dim])
             vec(b + "ssm_norm.weight", np.ones(128))
         if arch.expert_count > 0:
-            # experts stacked along the last ggml dimension: expert gate/up Q4_K, down Q6_K, router f32 (SURVEY 8d mix)
+            # experts stacked along the last ggml dimension: expert gate/up Q4_K, down Q6_K, router f32 (the quantisation mix the reference reports for production files)
             ne, fe, fs = arch.expert_count, arch.expert_feed_forward_length, arch.expert_shared_feed_forward_length
             mat(b + "ffn_gate_inp.weight", F32, H, ne, 0.5)
             mat(b + "ffn_gate_exps.weight", Q4_K, H, ne * fe, shape=[H, fe, ne])
