@@ -117,6 +117,44 @@ dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const floa
     return DFL_OK;
 }
 
+// One token of the recurrence for a warp's four state rows (lane owns columns lane + 32 j).
+__device__ __forceinline__ void gdn_token_step(float (&S)[4][4], const float* k_row, const float* q_row, const float* v4, float gexp, float beta,
+                                               int lane, float (&oo)[4]) {
+    float kk[4], qq[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        kk[j] = k_row[lane + 32 * j];
+        qq[j] = q_row[lane + 32 * j];
+    }
+    float sk[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        float p = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) p = fmaf(S[r][j], kk[j], p);
+        sk[r] = p;
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) sk[r] += __shfl_xor_sync(0xffffffffu, sk[r], of);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float coeff = beta * (v4[r] - gexp * sk[r]);
+        float p = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            S[r][j] = __fadd_rn(__fmul_rn(gexp, S[r][j]), __fmul_rn(coeff, kk[j]));
+            p = fmaf(S[r][j], qq[j], p);
+        }
+        oo[r] = p;
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], of);
+}
+
 // ---- scan --------------------------------------------------------------------------------
 // grid (n_v, 4), block 256: warp owns 4 state rows (dv), lane owns columns dk = lane + 32 j.
 // The block's q, k, v rows and gate scalars are staged in shared memory first, so that the
@@ -156,41 +194,8 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* s
         for (int j = 0; j < 4; ++j) S[r][j] = sin[r * 128 + lane + 32 * j];
     __syncthreads();
     for (int i = 0; i < n_rows; ++i) {
-        const float gexp = gs[i], beta = bs[i];
-        float kk[4], qq[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            kk[j] = ks[i][lane + 32 * j];
-            qq[j] = qs[i][lane + 32 * j];
-        }
-        float sk[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            float p = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) p = fmaf(S[r][j], kk[j], p);
-            sk[r] = p;
-        }
-#pragma unroll
-        for (int of = 16; of > 0; of >>= 1)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) sk[r] += __shfl_xor_sync(0xffffffffu, sk[r], of);
         float oo[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const float coeff = beta * (vs[i][warp * 4 + r] - gexp * sk[r]);
-            float p = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                S[r][j] = __fadd_rn(__fmul_rn(gexp, S[r][j]), __fmul_rn(coeff, kk[j]));
-                p = fmaf(S[r][j], qq[j], p);
-            }
-            oo[r] = p;
-        }
-#pragma unroll
-        for (int of = 16; of > 0; of >>= 1)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], of);
+        gdn_token_step(S, ks[i], qs[i], &vs[i][warp * 4], gs[i], bs[i], lane, oo);
         if (lane < 4) os[i][warp * 4 + lane] = lane == 0 ? oo[0] : lane == 1 ? oo[1] : lane == 2 ? oo[2] : oo[3];
     }
     float* sout = state_out + ((uint64_t)h * 128 + dv0) * 128;

@@ -161,17 +161,24 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
     cudaStream_t st = s->st;
     // DFL_SIDE_STREAM=0 keeps every launch of the pass on one stream
     static const bool side_enabled = [] { const char* e = getenv("DFL_SIDE_STREAM"); return !(e && e[0] == '0'); }();
-    cudaStream_t side = side_enabled ? s->st_side : st;
-    auto fork_side = [&]() -> dfl_status {   // the side stream continues from here
+    cudaStream_t side = side_enabled ? s->st_side : st, side2 = side_enabled ? s->st_side2 : st;
+    auto fork_side = [&]() -> dfl_status {   // both side streams continue from here
         if (side == st) return DFL_OK;
         DFL_CUDA(cudaEventRecord(s->ev_fork, st));
         DFL_CUDA(cudaStreamWaitEvent(side, s->ev_fork, 0));
+        DFL_CUDA(cudaStreamWaitEvent(side2, s->ev_fork, 0));
         return DFL_OK;
     };
-    auto join_side = [&]() -> dfl_status {   // the main stream waits for what the side stream was given
+    auto join_side = [&]() -> dfl_status {   // the main stream waits for what the first side stream was given
         if (side == st) return DFL_OK;
         DFL_CUDA(cudaEventRecord(s->ev_join, side));
         DFL_CUDA(cudaStreamWaitEvent(st, s->ev_join, 0));
+        return DFL_OK;
+    };
+    auto join_side2 = [&]() -> dfl_status {   // ... and for the second
+        if (side2 == st) return DFL_OK;
+        DFL_CUDA(cudaEventRecord(s->ev_join2, side2));
+        DFL_CUDA(cudaStreamWaitEvent(st, s->ev_join2, 0));
         return DFL_OK;
     };
     const uint64_t H = a.hidden_size, F = a.intermediate_size;
@@ -217,24 +224,25 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             ++ai;
         } else {
             const int cd = gg.conv_dim();
-            // qkv -> conv / norms on the main stream; the z projection (its own matrix when its format differs from
-            // qkv's) and the alpha / beta projection beside it: all three read only the layer's normalised input and
-            // write disjoint outputs
+            // qkv -> conv / norms on the main stream; the alpha / beta projection and the z projection (its own matrix
+            // when its format differs from qkv's) each on a side stream: all three read only the layer's normalised
+            // input and write disjoint outputs; the scan waits for alpha / beta, the gated norm for z
             const MatGroup& G = L.in_qkv_z;
             DFL_CHECK(fork_side());
             DFL_CHECK(launch_gemm_fewrow(st, G.mats[0], sc->acts_h, sc->part + G.col_off[0], G.splits, ep_norm, s->err, pdl_enabled_for(1), G.total_cols));
-            for (size_t i = 1; i < G.mats.size(); ++i)
-                DFL_CHECK(launch_gemm_fewrow(side, G.mats[i], sc->acts_h, sc->part + G.col_off[i], G.splits, ep_norm, s->err, pdl_enabled_for(1), G.total_cols));
             DFL_CHECK(launch_small_matmul(side, L.w_ab, sc->xn, (int)H, (int)n, H, 2 * gg.n_v, ep_norm, sc->ab[gi], 2 * gg.n_v));
+            for (size_t i = 1; i < G.mats.size(); ++i)
+                DFL_CHECK(launch_gemm_fewrow(side2, G.mats[i], sc->acts_h, sc->part + G.col_off[i], G.splits, ep_norm, s->err, pdl_enabled_for(1), G.total_cols));
+            const int cur = s->ssm_cur[gi];
             DFL_CHECK(launch_gdn_front(st, gg, sc->part, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, (int)n, L.conv_w, s->conv[gi],
                                        sc->qkv_raw[gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->conv_pre[gi]));
-            DFL_CHECK(join_side());
-            const int cur = s->ssm_cur[gi];
+            DFL_CHECK(join_side());    // alpha / beta
             DFL_CHECK(launch_gdn_scan(st, gg, s->ssm[cur][gi], s->ssm[cur ^ 1][gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->ab[gi],
                                       L.dt_bias, L.a_log, (int)n, sc->o));
-            s->ssm_cur[gi] = cur ^ 1;
+            DFL_CHECK(join_side2());   // z
             DFL_CHECK(launch_gdn_post(st, gg, sc->o, sc->part + cd, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, L.ssm_norm_w, (int)n,
                                       sc->acts_v, m->act_layout, s->err));
+            s->ssm_cur[gi] = cur ^ 1;
             out_proj = &L.w_out;
             ++gi;
         }
@@ -328,6 +336,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         }
         DFL_CHECK(launch_argmax_top2(st, logits, (int)n, V, V, sc->argmax, sc->gap, sc->am_scratch));
     }
+    DFL_CHECK(join_side());   // whatever the side streams still hold belongs to this pass
+    DFL_CHECK(join_side2());
     s->kv_n_pos = start + n;
     sc->last_n = n;
     sc->last_start = start;
@@ -574,9 +584,11 @@ dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t 
     if (ok && m->n_attn) ok = cudaMalloc(&s->attn_partials, attn_partials_floats(m->attn_geom(), kv_capacity) * 4) == cudaSuccess;
     ok = ok && cudaMalloc(&s->err, 4) == cudaSuccess;
     ok = ok && cudaEventCreate(&s->ev0) == cudaSuccess && cudaEventCreate(&s->ev1) == cudaSuccess;
-    ok = ok && cudaStreamCreateWithFlags(&s->st_side, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaStreamCreateWithFlags(&s->st_side, cudaStreamNonBlocking) == cudaSuccess &&
+         cudaStreamCreateWithFlags(&s->st_side2, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
-         cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming) == cudaSuccess;
+         cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&s->ev_join2, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
         std::string why = cudaGetErrorString(cudaGetLastError());
         dfl_session_destroy(s);
@@ -602,7 +614,9 @@ void dfl_session_destroy(dfl_session* s) {
     if (s->ev1) cudaEventDestroy(s->ev1);
     if (s->ev_fork) cudaEventDestroy(s->ev_fork);
     if (s->ev_join) cudaEventDestroy(s->ev_join);
+    if (s->ev_join2) cudaEventDestroy(s->ev_join2);
     if (s->st_side) cudaStreamDestroy(s->st_side);
+    if (s->st_side2) cudaStreamDestroy(s->st_side2);
     if (s->st) cudaStreamDestroy(s->st);
     delete s;
 }

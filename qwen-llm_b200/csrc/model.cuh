@@ -122,8 +122,8 @@ struct dfl_session {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     // side stream for the branches of a layer that only depend on the layer's normalised input (the GDN z and
     // alpha / beta projections, the expert router): they run beside the main projection instead of after it
-    cudaStream_t st_side = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaStream_t st_side = nullptr, st_side2 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_join2 = nullptr;
 };
 
 struct dfl_scratch {
