@@ -51,13 +51,8 @@ constexpr int smem_bytes() {
 // named barrier 1: start-up of the unpacking warps (every one of them reaches it unconditionally)
 __device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
-#ifdef DFL_TS_MAXNREG
-#define TS_KERNEL_ATTR __maxnreg__(DFL_TS_MAXNREG)
-#else
-#define TS_KERNEL_ATTR __launch_bounds__(THREADS, 1)
-#endif
 template <int DT>
-__global__ void TS_KERNEL_ATTR gemm_ts_kernel(const Params p) {
+__global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     using F = Fmt<DT>;
     constexpr int STAGES = F::STAGES, PASSES = F::PASSES;
     constexpr int OFF_RING = KC * ACTTS_CHUNK;
@@ -142,10 +137,7 @@ __global__ void TS_KERNEL_ATTR gemm_ts_kernel(const Params p) {
         // lane issues the instructions.
         const int g = warp - MMA_WARP0;
         if (n_it > g) {
-#ifndef DFL_TS_EXP_N
-#define DFL_TS_EXP_N 32
-#endif
-            constexpr uint32_t IDESC_MAIN = instr_desc(DFL_TS_EXP_N), IDESC_MIN = instr_desc(48);
+            constexpr uint32_t IDESC_MAIN = instr_desc(32), IDESC_MIN = instr_desc(48);
             bool ok = mbar_wait_bounded(acts_bar, 0, p.err, DEV_ERR_WAIT_FULL);
             ok = __all_sync(0xffffffffu, ok);
             const uint32_t acts_addr = smem_u32(acts_res);
@@ -164,12 +156,10 @@ __global__ void TS_KERNEL_ATTR gemm_ts_kernel(const Params p) {
                         if (lane == 0) TS_TRACE(2 + g, 2 * pc);
                         fence_after_sync();
                         if (elect_one()) {
-#ifndef DFL_TS_EXP_NOMMA
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
                                 mma_ts(tm_g + TM_D + 32 * (j & 1), tm_g + TM_A + b * 64 + 8 * j,
                                        smem_desc(chunk + F::b_slice(ps, j) * 1024, 512, 128), IDESC_MAIN, (ps | (j >> 1)) ? 1u : 0u);
-#endif
                             if (F::HAS_MIN && ps == PASSES - 1)   // every pass has stored its column of the min operand by now
                                 mma_ts(tm_g + TM_DM, tm_g + TM_AM, smem_desc(chunk + TS_BMIN_OFF, 768, 128), IDESC_MIN, 0);
                             mma_commit(&a_free[2 * g + b]);
@@ -294,14 +284,7 @@ __global__ void TS_KERNEL_ATTR gemm_ts_kernel(const Params p) {
             for (int ps = 0; ps < PASSES; ++ps, ++pc) {
                 uint32_t r[32], am[8];
                 if (ok) {
-#ifndef DFL_TS_EXP_NOUNPACK
                     F::unpack(st, ps, row, kp2, r, am, us);
-#else
-#pragma unroll
-                    for (int q = 0; q < 32; ++q) r[q] = 0u;
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) am[q] = 0u;
-#endif
                 }
                 if (tracer) TS_TRACE(g, 16 * (e >> 1) + 2 + 3 * ps);
                 if (ok && ps == 0) {
