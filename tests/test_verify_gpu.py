@@ -294,3 +294,27 @@ def test_tensor_core_attention_matches_oracle_and_single_token_steps(tiny_g4, ca
     np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
     for o in (sess, scr, single, scr1):
         o.close()
+
+
+def test_repeated_passes_are_bitwise_reproducible():
+    """The pass forks work onto side streams (GDN z / alpha-beta projections) and overlaps launches; twenty fresh sessions
+    fed the same two blocks must give the same bits every time (a missing dependency shows up as a rare mismatch)."""
+    arch = modelgen.tiny_arch()
+    gm = pkg.Model(arch, modelgen.target_tensors(arch, seed=3))
+    rng = np.random.default_rng(17)
+    blocks = [rng.integers(0, arch.vocab_size, size=16), rng.integers(0, arch.vocab_size, size=9)]
+    ref = None
+    for it in range(20):
+        sess, scr = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 2)
+        out = []
+        pos = 0
+        for b in blocks:
+            am, gap, logits = pkg.packed_verify(gm, sess, scr, [1, arch.n_layer - 1], b, pos, want_logits=True)
+            out.append(logits.tobytes() + scr.read_capture(len(b)).tobytes())
+            pos += len(b)
+        out.append(b"".join(np.concatenate(sess.read_gdn_state(g)).tobytes() for g in range(2)))
+        if ref is None:
+            ref = out
+        assert out == ref, f"iteration {it} differs"
+        sess.close(); scr.close()
+    gm.close()
