@@ -265,6 +265,10 @@ struct dfl_dsession {
     uint8_t* acts_hc = nullptr;
     cudaStream_t st_side = nullptr;
     cudaEvent_t ev_ctx[DFL_MAX_DRAFTER_LAYERS] = {};
+    // one-shot hook called when a draft pass has been queued (before anyone waits for it): the outer loop uses it to
+    // queue the target's rollback behind the drafter's launches instead of in front of them
+    void (*after_enqueue)(void*) = nullptr;
+    void* after_enqueue_arg = nullptr;
     int32_t* pinned_i = nullptr;
     cudaStream_t st = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -736,7 +740,16 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, boo
         }
         ds->have_topk = true;
     }
+    if (ds->after_enqueue) {
+        auto fn = ds->after_enqueue;
+        ds->after_enqueue = nullptr;
+        fn(ds->after_enqueue_arg);
+    }
     return DFL_OK;
+}
+void dsession_set_after_enqueue(dfl_dsession* ds, void (*fn)(void*), void* arg) {
+    ds->after_enqueue = fn;
+    ds->after_enqueue_arg = arg;
 }
 
 // the last pass's top-16 and gate rows in pinned host memory (at most 18 KB; the reference reads the same three

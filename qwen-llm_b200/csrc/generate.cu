@@ -13,6 +13,7 @@ namespace dfl {
 dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, bool topk);
 dfl_status draft_block_topk(dfl_dsession* ds, int32_t carry, uint32_t noise_start_pos, int32_t* out_tokens);
 dfl_status restore_partial_launch(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t n_keep, uint32_t start_position);
+void dsession_set_after_enqueue(dfl_dsession* ds, void (*fn)(void*), void* arg);
 }
 // accessors implemented next to the drafter session (drafter.cu)
 extern "C" {
@@ -113,7 +114,31 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
     // A partial-accept rollback is launched without a wait and runs under the next draft; what is counted as restore
     // time is the part of it that outlasts that draft (all of it when no draft runs).
     bool restore_pending = false;
+    // The rollback itself is queued late: behind the next draft's launches when a draft follows (the host then spends
+    // its launch time on the drafter first and the GPU is not left waiting), else right before whatever comes next.
+    struct Deferred {
+        bool on = false;
+        uint32_t n_keep = 0, position = 0;
+        dfl_status rc = DFL_OK;
+        const dfl_model* m;
+        dfl_session* s;
+        dfl_scratch* sc;
+        bool* pending;
+        uint32_t* calls;
+        void launch() {
+            if (!on) return;
+            on = false;
+            cudaEventRecord(s->ev0, s->st);
+            rc = n_keep == 0 ? dfl_restore_pre_block(m, s, sc, position) : restore_partial_launch(m, s, sc, n_keep, position);
+            cudaEventRecord(s->ev1, s->st);
+            if (rc == DFL_OK) { *pending = true; ++*calls; }
+        }
+        static void hook(void* self) { static_cast<Deferred*>(self)->launch(); }
+    } deferred;
+    deferred.m = m; deferred.s = s; deferred.sc = sc; deferred.pending = &restore_pending; deferred.calls = &st.restore_calls;
     auto settle_restore = [&](bool draft_ran) {
+        deferred.launch();
+        if (deferred.rc != DFL_OK && rc == DFL_OK) rc = deferred.rc;
         if (!restore_pending) return;
         restore_pending = false;
         cudaEventSynchronize(s->ev1);
@@ -126,7 +151,8 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         tokens.push_back(carry);
         if (is_stop(carry)) break;
         if (tokens.size() == params->max_tokens) break;
-        const uint32_t position = s->kv_n_pos;
+        // a rollback that is still to be queued has not moved the session's position yet
+        const uint32_t position = deferred.on ? deferred.position + deferred.n_keep : s->kv_n_pos;
         const uint32_t remaining_ctx = s->kv_capacity - position;
         if (remaining_ctx < N) {
             // off step (qwen/dflash.rs:629-637): exact single-token decode keeps the loop going near the capacity edge
@@ -155,7 +181,9 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
             if (params->replay_runs_drafter) {
                 int32_t discard[MAX_ROWS];
                 cudaEventRecord(dv.ev0, dv.st);
+                if (deferred.on) dsession_set_after_enqueue(ds, &Deferred::hook, &deferred);
                 rc = dfl_draft_block(ds, carry, position, discard, nullptr);
+                dsession_set_after_enqueue(ds, nullptr, nullptr);
                 cudaEventRecord(dv.ev1, dv.st);
                 if (rc != DFL_OK) break;
                 cudaEventSynchronize(dv.ev1);
@@ -172,9 +200,11 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
             uint32_t sel_off[DFL_MAX_BLOCK];
             int32_t sel_ct[DFL_MAX_BLOCK * 16];
             double sel_cw[DFL_MAX_BLOCK * 16];
+            if (deferred.on) dsession_set_after_enqueue(ds, &Deferred::hook, &deferred);
             if (selector_sampled) rc = dfl_draft_block_sampled(ds, carry, position, proposal_sampler, draft, sel_off, sel_ct, sel_cw);
             else if (proposal_sampler) rc = draft_block_topk(ds, carry, position, draft);
             else rc = dfl_draft_block(ds, carry, position, draft, nullptr);
+            dsession_set_after_enqueue(ds, nullptr, nullptr);
             cudaEventRecord(dv.ev1, dv.st);
             if (rc != DFL_OK) break;
             cudaEventSynchronize(dv.ev1);
@@ -219,6 +249,7 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         }
         ++st.spec_steps;
         settle_restore(!replay || params->replay_runs_drafter);
+        if (rc != DFL_OK) break;
         // ---- packed verify of [carry, drafts...] ----
         verify_in[0] = carry;
         for (uint32_t i = 1; i < N; ++i) verify_in[i] = draft[i];
@@ -278,12 +309,9 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         }
         st.append_ms += now_ms() - t_app;
         if (n_keep < N) {
-            cudaEventRecord(s->ev0, s->st);
-            rc = n_keep == 0 ? dfl_restore_pre_block(m, s, sc, position) : restore_partial_launch(m, s, sc, n_keep, position);
-            cudaEventRecord(s->ev1, s->st);
-            if (rc != DFL_OK) break;
-            restore_pending = true;
-            ++st.restore_calls;
+            deferred.on = true;
+            deferred.n_keep = n_keep;
+            deferred.position = position;
         }
         st.accepted_drafts += dec.n_accepted;
         bool done = false;
