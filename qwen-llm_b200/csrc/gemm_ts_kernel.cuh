@@ -27,6 +27,10 @@ struct Params {
     int kblocks, splits, row_tiles, ctas_per_split;
     uint32_t n_out, ld_out;
     int* err;
+    const int32_t* tile_map;   // optional: row tiles to compute, and how many (device memory)
+    const int32_t* n_tiles;
+    const int32_t* kb_map;     // optional: column blocks to sum over, and how many (device memory)
+    const int32_t* n_kb;
 };
 
 #ifdef DFL_TS_TRACE
@@ -76,9 +80,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // warp-uniform by construction
     const int sp = blockIdx.x % p.splits, c = blockIdx.x / p.splits;
-    const int kb0 = (int)((long long)sp * p.kblocks / p.splits), kb1 = (int)((long long)(sp + 1) * p.kblocks / p.splits);
+    int row_tiles = p.row_tiles, kblocks = p.kblocks;
+    if (p.tile_map || p.kb_map) {   // the lists come from the preceding kernel: nothing may be fetched before it is complete
+        pdl_wait();
+        if (p.tile_map) row_tiles = *p.n_tiles;
+        if (p.kb_map) kblocks = *p.n_kb;
+    }
+    const int kb0 = (int)((long long)sp * kblocks / p.splits), kb1 = (int)((long long)(sp + 1) * kblocks / p.splits);
     const int n_kb = kb1 - kb0;
-    const int n_my = (p.row_tiles - c + p.ctas_per_split - 1) / p.ctas_per_split;   // row tiles c, c + cps, ...
+    const int n_my = (row_tiles - c + p.ctas_per_split - 1) / p.ctas_per_split;   // row tiles c, c + cps, ... (of the list)
     const int n_it = n_my * n_kb;            // entries
 
     if (threadIdx.x == 0) {
@@ -109,14 +119,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
         // ------------------------------ bulk-copy producer ------------------------------
         if (lane == 0) {
             const uint64_t tile_stride = (uint64_t)p.kblocks * F::STAGE;
-            const uint8_t* wbase = p.w + (uint64_t)kb0 * F::STAGE;
+            const uint8_t* wbase = p.w;
             int pt = 0, pk = 0;
             bool ok = true;
             for (int e = 0; e < n_it; ++e) {
                 const int s = e % STAGES;
                 if (e >= STAGES) ok = mbar_wait_bounded(&empty[s], ((e / STAGES) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
                 if (!ok) break;
-                const uint8_t* src = wbase + (uint64_t)(c + pt * p.ctas_per_split) * tile_stride + (uint64_t)pk * F::STAGE;
+                const int slot = c + pt * p.ctas_per_split;
+                const uint8_t* src = wbase + (uint64_t)(p.tile_map ? p.tile_map[slot] : slot) * tile_stride +
+                                     (uint64_t)(p.kb_map ? p.kb_map[kb0 + pk] : kb0 + pk) * F::STAGE;
                 mbar_arrive_expect_tx(&full[s], F::STAGE);
                 bulk_g2s(ring + s * F::STAGE, src, F::STAGE, &full[s]);
                 TS_TRACE(4, e);
@@ -126,7 +138,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                     pdl_wait();
                     mbar_arrive_expect_tx(acts_bar, (uint32_t)n_kb * ACTTS_CHUNK);
                     for (int k = 0; k < n_kb; ++k)
-                        bulk_g2s(acts_res + k * ACTTS_CHUNK, p.acts + (uint64_t)(kb0 + k) * ACTTS_CHUNK, ACTTS_CHUNK, acts_bar);
+                        bulk_g2s(acts_res + k * ACTTS_CHUNK, p.acts + (uint64_t)(p.kb_map ? p.kb_map[kb0 + k] : kb0 + k) * ACTTS_CHUNK, ACTTS_CHUNK, acts_bar);
                 }
             }
             if (!ok) abort_flag = 1;
@@ -224,7 +236,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                 const float other[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&x_free[t & 1]);
-                const uint32_t orow = (uint32_t)(c + t * p.ctas_per_split) * TILE_R + row;
+                const int slot = c + t * p.ctas_per_split;
+                const uint32_t orow = (uint32_t)(p.tile_map ? p.tile_map[slot] : slot) * TILE_R + row;
                 if (orow < p.n_out) {
                     float* dst = p.out + ((uint64_t)sp * MAX_ROWS + 8 * kp2) * p.ld_out + orow;
 #pragma unroll
@@ -386,6 +399,8 @@ int gemm_ts_choose_splits(const QMatrix& m) {
     const int tiles = m.row_tiles > 0 ? m.row_tiles : 1;
     return gemm_ts_choose_splits_multi(&tiles, 1, m.kblocks);
 }
+// CTAs per split of a launch over `row_tiles` row tiles (the least number of tiles a tile list must hold)
+int gemm_ts_ctas_per_split(int row_tiles, int splits) { return ts::ctas_per_split(row_tiles, splits); }
 // Several matrices that share their input and their partial buffer are launched one after the other
 // with one common split count: minimise the sum of their longest-CTA times.
 int gemm_ts_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks) {
@@ -428,6 +443,10 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
     p.n_out = (uint32_t)m.n_out;
     p.ld_out = ld_out ? ld_out : (uint32_t)m.n_out;
     p.err = dev_err;
+    p.tile_map = ep.tile_map;
+    p.n_tiles = ep.n_tiles;
+    p.kb_map = ep.kb_map;
+    p.n_kb = ep.n_kb;
     const int grid = p.ctas_per_split * splits;
     switch (m.dtype) {
         case DFL_Q4_K: return ts::launch_t<DFL_Q4_K>(st, p, grid, pdl);

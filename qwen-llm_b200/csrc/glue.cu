@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
             if (p.route_w) {
                 const float w = col0 < p.route_n * p.route_f ? p.route_w[tok * p.route_e + p.route_e0 + col0 / p.route_f] : p.route_sg[tok];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] *= w;
+                for (int j = 0; j < 4; ++j) v[j] = w != 0.f ? v[j] * w : 0.f;   // columns of experts nobody chose may hold stale partials
             }
         } else {
             float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -182,6 +182,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         return DFL_OK;
     };
     const uint64_t H = a.hidden_size, F = a.intermediate_size;
+    // DFL_MOE_ALL_EXPERTS=1 streams every expert of a routed layer instead of the chosen ones
+    static const bool moe_chosen_only = getenv("DFL_MOE_ALL_EXPERTS") == nullptr;
     const AttnGeom ag = m->attn_geom();
     const GdnGeom gg = m->gdn_geom();
     const int kb_h = (int)(H / GLUE_COLS);
@@ -260,8 +262,24 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             DFL_CHECK(fork_side());
             DFL_CHECK(launch_small_matmul(side, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
             DFL_CHECK(launch_moe_route(side, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
-            DFL_CHECK(launch_group(st, L.moe_gate_up, sc->acts_h, sc->part, ep_norm, s->err));
-            DFL_CHECK(join_side());
+            // only the experts some row chose (and the shared expert) are streamed when the four blocks sit in one
+            // tensor-memory matrix; otherwise every expert is, and the router runs beside the GEMM
+            const MatGroup& GU = L.moe_gate_up;
+            const bool down_chosen = L.moe_down.mats.size() == 1 && L.moe_down.mats[0].layout == LAYOUT_TS && Fe % TILE_K == 0;
+            const bool chosen_only = moe_chosen_only && GU.mats.size() == 1 && GU.mats[0].layout == LAYOUT_TS && Fe % TILE_R == 0 && Fs % TILE_R == 0;
+            if (chosen_only) {
+                DFL_CHECK(join_side());
+                DFL_CHECK(launch_moe_tiles(st, sc->route_w, (int)n, E, (int)m->ep_e0, En, Fe / TILE_R, Fs / TILE_R,
+                                           gemm_ts_ctas_per_split(GU.mats[0].row_tiles, GU.splits), sc->moe_tile_map, sc->moe_n_tiles,
+                                           Fe / TILE_K, L.moe_down.splits, down_chosen ? sc->moe_kb_map : nullptr, sc->moe_n_tiles + 1));
+                GemmEpilogue ep_gu = ep_norm;
+                ep_gu.tile_map = sc->moe_tile_map;
+                ep_gu.n_tiles = sc->moe_n_tiles;
+                DFL_CHECK(launch_group(st, GU, sc->acts_h, sc->part, ep_gu, s->err));
+            } else {
+                DFL_CHECK(launch_group(st, GU, sc->acts_h, sc->part, ep_norm, s->err));
+                DFL_CHECK(join_side());
+            }
             GlueParams p;
             p.mode = GLUE_SWIGLU;
             p.part = sc->part; p.splits = L.moe_gate_up.splits; p.ld_part = (int)L.moe_gate_up.total_cols;
@@ -274,7 +292,12 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             DFL_CHECK(launch_glue(st, p, (uint64_t)inner));
             GemmEpilogue ep_down;
             ep_down.out_scale = 64.0f;
-            DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part, ep_down, s->err));
+            GemmEpilogue ep_down_exps = ep_down;
+            if (chosen_only && down_chosen) {   // sum only over the chosen experts' column blocks
+                ep_down_exps.kb_map = sc->moe_kb_map;
+                ep_down_exps.n_kb = sc->moe_n_tiles + 1;
+            }
+            DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part, ep_down_exps, s->err));
             down_splits = L.moe_down.splits;
             if (Fs > 0) {
                 DFL_CHECK(launch_group(st, L.moe_down_sh, sc->acts_f + (uint64_t)(En * Fe / TILE_K) * act_chunk_bytes(m->act_layout),
@@ -706,6 +729,9 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
         alloc(&sc->route_sg, MAX_ROWS * 4);
         alloc(&sc->moe_out, MAX_ROWS * H * 4);
         alloc(&sc->route_idx, (size_t)MAX_ROWS * a.expert_used_count * 4);
+        alloc(&sc->moe_tile_map, (size_t)(2 * ((uint64_t)a.expert_count * a.expert_feed_forward_length + a.expert_shared_feed_forward_length) / 128 + 256) * 4);
+        alloc(&sc->moe_n_tiles, 16);
+        alloc(&sc->moe_kb_map, (size_t)((uint64_t)a.expert_count * a.expert_feed_forward_length / 256 + 64) * 4);
     }
     alloc(&sc->acts_v, std::max(q_dim, v_dim) / TILE_K * chunk);
     alloc(&sc->q_rot, MAX_ROWS * q_dim * 4);

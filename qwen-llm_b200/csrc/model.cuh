@@ -139,6 +139,7 @@ struct dfl_scratch {
     // routed experts: router logits [16][E + 1], dense route weights [16][E], shared-expert gates [16], chosen ids [16][k]
     float *route_logits = nullptr, *route_w = nullptr, *route_sg = nullptr, *moe_out = nullptr;
     int32_t* route_idx = nullptr;
+    int32_t *moe_tile_map = nullptr, *moe_n_tiles = nullptr, *moe_kb_map = nullptr;   // row tiles of the gate|up matrix the block's routing needs
     void* am_scratch = nullptr;
     float* capture = nullptr;  // [16][k][H]
     int32_t* tokens_dev = nullptr;

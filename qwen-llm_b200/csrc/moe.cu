@@ -81,4 +81,66 @@ dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_
     return DFL_OK;
 }
 
+// ---- the row tiles of the gate|up matrix that belong to chosen experts ------------------------------------------------
+// The gate|up matrix of a layer is [gate of every local expert | shared gate | up of every local expert | shared up],
+// T row tiles per expert and Ts per shared block.  An expert is active when any row of the block routes to it; the
+// list holds the tiles of the active experts and of the shared expert, so the GEMM streams only those.  It is padded
+// by repetition up to min_tiles (a repeated tile is computed twice with the same result), which keeps every CTA of the
+// fixed launch geometry busy with at least one tile.
+__global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float* route_w, int n_rows, int n_expert, int e0, int n_local, int T,
+                                                                    int Ts, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int KB, int min_kb, int32_t* kb_map,
+                                                                    int32_t* n_kb) {
+    pdl_prologue();
+    __shared__ int warp_count[MOE_MAX_EXPERTS / 32];
+    __shared__ int total_sh;
+    const int e = threadIdx.x, warp = e >> 5, lane = e & 31;
+    bool active = false;
+    if (e < n_local)
+        for (int tok = 0; tok < n_rows; ++tok) active = active || route_w[(uint64_t)tok * n_expert + e0 + e] != 0.f;
+    const uint32_t bal = __ballot_sync(0xffffffffu, active);
+    if (lane == 0) warp_count[warp] = __popc(bal);
+    __syncthreads();
+    if (e == 0) {
+        int run = 0;
+        for (int w = 0; w < MOE_MAX_EXPERTS / 32; ++w) { const int c = warp_count[w]; warp_count[w] = run; run += c; }
+        total_sh = run;
+    }
+    __syncthreads();
+    const int n_act = total_sh, rank = warp_count[warp] + __popc(bal & ((1u << lane) - 1u));
+    const int up_base = n_local * T + Ts, up_list = n_act * T + Ts, n = 2 * up_list;
+    if (active)
+        for (int j = 0; j < T; ++j) {
+            tile_map[rank * T + j] = e * T + j;
+            tile_map[up_list + rank * T + j] = up_base + e * T + j;
+        }
+    if (e < Ts) {
+        tile_map[n_act * T + e] = n_local * T + e;
+        tile_map[up_list + n_act * T + e] = up_base + n_local * T + e;
+    }
+    __syncthreads();
+    for (int i = n + e; i < min_tiles; i += MOE_MAX_EXPERTS) tile_map[i] = n > 0 ? tile_map[i % n] : i;
+    if (e == 0) *n_tiles = n > min_tiles ? n : min_tiles;
+    // column blocks of the down matrix (KB per expert): the active experts' blocks first, then the others, whose
+    // activations are zero - the list is cut after the active ones, but never below min_kb entries
+    if (kb_map && e < n_local) {
+        const int pos = active ? rank : n_act + (e - rank);
+        for (int j = 0; j < KB; ++j) kb_map[pos * KB + j] = e * KB + j;
+    }
+    if (kb_map && e == 0) {
+        const int want = n_act * KB, all = n_local * KB;
+        *n_kb = want > min_kb ? want : (min_kb < all ? min_kb : all);
+    }
+}
+
+dfl_status launch_moe_tiles(cudaStream_t st, const float* route_w, int n_rows, int n_expert, int e0, int n_local, int tiles_per_expert,
+                            int shared_tiles, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,
+                            int32_t* n_kb) {
+    if (n_local > MOE_MAX_EXPERTS || shared_tiles > MOE_MAX_EXPERTS) return fail(DFL_ERR_UNSUPPORTED, "moe_tiles: too many experts");
+    launch_kf(16, moe_tiles_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), 0, st, route_w, n_rows, n_expert, e0, n_local, tiles_per_expert, shared_tiles,
+              min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
 }  // namespace dfl

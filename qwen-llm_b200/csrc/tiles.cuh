@@ -189,6 +189,15 @@ struct GemmEpilogue {
     float norm_k = 1.f;
     float eps = 0.f;
     float out_scale = 1.f;
+    // optional list of row tiles to compute (tensor-memory family only): the kernel works on tiles
+    // tile_map[0 .. *n_tiles) of the matrix instead of all of them; both live in device memory and may be
+    // written by the preceding kernel.  *n_tiles must be at least the launch's CTAs per split.
+    const int32_t* tile_map = nullptr;
+    const int32_t* n_tiles = nullptr;
+    // the same for the column blocks summed over: blocks kb_map[0 .. *n_kb), *n_kb at least the split count and at most
+    // what the splits were chosen for (the activations of a listed block are used as they are)
+    const int32_t* kb_map = nullptr;
+    const int32_t* n_kb = nullptr;
 };
 int gemm_choose_splits(const QMatrix& m);
 int gemm_max_kblocks_per_cta(int dtype);  // column blocks one CTA can keep resident
