@@ -388,6 +388,15 @@ def run_verify_only(args, rank, world, device):
         extra = {"gemm_ms_per_step": ms / args.steps, "gemm_launches": n, "gemm_GBps": b / (ms * 1e-3) / 1e9}
     peak, kind = bench.measured_peaks()
     vb = model.verify_weight_bytes()
+    if moe and not os.environ.get("DFL_MOE_ALL_EXPERTS"):
+        # only the experts some row chose are streamed: expected count under the (near uniform) routing of random weights
+        E, k = arch.expert_count, arch.expert_used_count
+        frac = 1.0 - (1.0 - k / E) ** 16
+        n_layer_local = arch.n_layer
+        expert_bytes = n_layer_local * (E // world) * (2 * arch.hidden_size * arch.expert_feed_forward_length * 144 // 256 +
+                                                       arch.hidden_size * arch.expert_feed_forward_length * 210 // 256)
+        extra = {**extra, "model_weight_bytes": vb, "expected_active_expert_fraction": frac}
+        vb = int(vb - expert_bytes * (1.0 - frac))
     if ctx:   # the KV bytes one verify reads: attention layers x positions x (K + V) x n_kv x head_dim x 2 B
         n_attn = sum(1 for il in range(arch.n_layer) if syn.is_attn(arch, il))
         kvb = n_attn * (ctx + 16 * args.warmup) * 2 * arch.n_kv_heads * arch.attn_head_dim * 2
