@@ -796,8 +796,9 @@ dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* 
 }
 
 __global__ void reduce_partials_kernel(const float* part, int splits, int n_rows, uint64_t n_out, float* y,
-                                       int ld_y) {
+                                       int ld_y, const int32_t* splits_dev) {
     pdl_prologue();
+    if (splits_dev) splits += *splits_dev;
     const uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int r = blockIdx.y;
     if (o >= n_out || r >= n_rows) return;
@@ -806,9 +807,10 @@ __global__ void reduce_partials_kernel(const float* part, int splits, int n_rows
     y[(uint64_t)r * ld_y + o] = v;
 }
 
-dfl_status launch_reduce_partials(cudaStream_t st, const float* part, int splits, int n_rows, uint64_t n_out, float* y, int ld_y) {
+dfl_status launch_reduce_partials(cudaStream_t st, const float* part, int splits, int n_rows, uint64_t n_out, float* y, int ld_y,
+                                  const int32_t* splits_dev) {
     dim3 grid((unsigned)((n_out + 255) / 256), (unsigned)n_rows);
-    launch_k(reduce_partials_kernel, dim3(grid), dim3(256), 0, st, part, splits, n_rows, n_out, y, ld_y);
+    launch_k(reduce_partials_kernel, dim3(grid), dim3(256), 0, st, part, splits, n_rows, n_out, y, ld_y, splits_dev);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -104,6 +104,7 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
 int gemm_ts_choose_splits(const QMatrix& m);
 int gemm_ts_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks);
 int gemm_ts_ctas_per_split(int row_tiles, int splits);
+int gemm_ts_kc();
 int gemm_tsb_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks);
 dfl_status launch_gemm_tsb(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits, const GemmEpilogue& ep,
                            int* dev_err, bool pdl, uint32_t ld_out);

@@ -79,16 +79,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     __shared__ int abort_flag;
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;   // warp-uniform by construction
-    const int sp = blockIdx.x % p.splits, c = blockIdx.x / p.splits;
-    int row_tiles = p.row_tiles, kblocks = p.kblocks;
+    int row_tiles = p.row_tiles, kblocks = p.kblocks, splits = p.splits, cps = p.ctas_per_split;
     if (p.tile_map || p.kb_map) {   // the lists come from the preceding kernel: nothing may be fetched before it is complete
         pdl_wait();
         if (p.tile_map) row_tiles = *p.n_tiles;
-        if (p.kb_map) kblocks = *p.n_kb;
+        if (p.kb_map) {
+            kblocks = p.n_kb[0];
+            if (p.n_kb[1] > 0) {   // the list's author also chose the split geometry for its length (the launch is the worst case)
+                splits = p.n_kb[1];
+                cps = p.n_kb[2];
+            }
+        }
     }
-    const int kb0 = (int)((long long)sp * kblocks / p.splits), kb1 = (int)((long long)(sp + 1) * kblocks / p.splits);
+    if ((int)blockIdx.x >= splits * cps) return;   // nothing has been set up yet: a CTA beyond the geometry in use just leaves
+    const int sp = blockIdx.x % splits, c = blockIdx.x / splits;
+    const int kb0 = (int)((long long)sp * kblocks / splits), kb1 = (int)((long long)(sp + 1) * kblocks / splits);
     const int n_kb = kb1 - kb0;
-    const int n_my = (row_tiles - c + p.ctas_per_split - 1) / p.ctas_per_split;   // row tiles c, c + cps, ... (of the list)
+    const int n_my = (row_tiles - c + cps - 1) / cps;   // row tiles c, c + cps, ... (of the list)
     const int n_it = n_my * n_kb;            // entries
 
     if (threadIdx.x == 0) {
@@ -126,7 +133,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                 const int s = e % STAGES;
                 if (e >= STAGES) ok = mbar_wait_bounded(&empty[s], ((e / STAGES) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
                 if (!ok) break;
-                const int slot = c + pt * p.ctas_per_split;
+                const int slot = c + pt * cps;
                 const uint8_t* src = wbase + (uint64_t)(p.tile_map ? p.tile_map[slot] : slot) * tile_stride +
                                      (uint64_t)(p.kb_map ? p.kb_map[kb0 + pk] : kb0 + pk) * F::STAGE;
                 mbar_arrive_expect_tx(&full[s], F::STAGE);
@@ -236,7 +243,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                 const float other[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&x_free[t & 1]);
-                const int slot = c + t * p.ctas_per_split;
+                const int slot = c + t * cps;
                 const uint32_t orow = (uint32_t)(p.tile_map ? p.tile_map[slot] : slot) * TILE_R + row;
                 if (orow < p.n_out) {
                     float* dst = p.out + ((uint64_t)sp * MAX_ROWS + 8 * kp2) * p.ld_out + orow;
@@ -400,6 +407,7 @@ int gemm_ts_choose_splits(const QMatrix& m) {
     return gemm_ts_choose_splits_multi(&tiles, 1, m.kblocks);
 }
 // CTAs per split of a launch over `row_tiles` row tiles (the least number of tiles a tile list must hold)
+int gemm_ts_kc() { return ts::KC; }   // column blocks a CTA keeps resident
 int gemm_ts_ctas_per_split(int row_tiles, int splits) { return ts::ctas_per_split(row_tiles, splits); }
 // Several matrices that share their input and their partial buffer are launched one after the other
 // with one common split count: minimise the sum of their longest-CTA times.
@@ -447,7 +455,8 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
     p.n_tiles = ep.n_tiles;
     p.kb_map = ep.kb_map;
     p.n_kb = ep.n_kb;
-    const int grid = p.ctas_per_split * splits;
+    int grid = p.ctas_per_split * splits;
+    if (ep.kb_map && ep.dynamic_splits && grid < 148) grid = 148;   // room for the geometry chosen on the device
     switch (m.dtype) {
         case DFL_Q4_K: return ts::launch_t<DFL_Q4_K>(st, p, grid, pdl);
         case DFL_Q5_K: return ts::launch_t<DFL_Q5_K>(st, p, grid, pdl);

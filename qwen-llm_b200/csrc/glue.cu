@@ -14,6 +14,7 @@ namespace dfl {
 // split per thread keeps every global load of the kernel independent (one latency round).
 __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
     pdl_prologue();
+    const int n_splits = p.splits_dev ? p.splits + *p.splits_dev : p.splits;
     const int cb = blockIdx.x, tok = threadIdx.x >> 4, quad = threadIdx.x & 15;
     const int col0 = cb * GLUE_COLS + quad * 4;
     const bool live = tok < p.n_rows;
@@ -24,7 +25,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
             const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
             const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
 #pragma unroll 4
-            for (int s = 0; s < p.splits; ++s) {
+            for (int s = 0; s < n_splits; ++s) {
                 const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
                 const float4 b = *reinterpret_cast<const float4*>(base + s * stride + p.swiglu_f);
                 g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
                 const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
                 const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
 #pragma unroll 4
-                for (int s = 0; s < p.splits; ++s) {
+                for (int s = 0; s < n_splits; ++s) {
                     const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
                     acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
                 }

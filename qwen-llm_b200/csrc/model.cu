@@ -197,10 +197,11 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
     DFL_CUDA(cudaMemcpyAsync(sc->tokens_dev, sc->pinned_i, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
     DFL_CHECK(launch_embed_rows(st, m->embd_dtype, m->embd_ggml, H, sc->tokens_dev, (int)n, sc->x, (int)H));
 
-    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* norm_w, bool want_xn, float* capture) -> dfl_status {
+    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* norm_w, bool want_xn, float* capture,
+                         const int32_t* splits_dev = nullptr) -> dfl_status {
         GlueParams p;
         p.mode = GLUE_RESID;
-        p.part = part; p.splits = splits; p.ld_part = ld_part;
+        p.part = part; p.splits = splits; p.splits_dev = splits_dev; p.ld_part = ld_part;
         p.x = sc->x; p.ld_x = (int)H;
         p.mul_w = norm_w;
         p.acts = sc->acts_h; p.bf3 = m->act_layout;
@@ -252,6 +253,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         const bool moe = a.expert_count > 0;
         DFL_CHECK(norm_glue(sc->part, out_proj->splits, (int)out_proj->total_cols, L.post_norm_w, moe, nullptr));
         int down_splits;
+        const int32_t* down_splits_dev = nullptr;
         const float* moe_part = sc->part;
         if (moe) {
             // routed experts + shared expert (forward.rs:749-824): route, then every expert of the layer as two large
@@ -271,7 +273,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
                 DFL_CHECK(join_side());
                 DFL_CHECK(launch_moe_tiles(st, sc->route_w, (int)n, E, (int)m->ep_e0, En, Fe / TILE_R, Fs / TILE_R,
                                            gemm_ts_ctas_per_split(GU.mats[0].row_tiles, GU.splits), sc->moe_tile_map, sc->moe_n_tiles,
-                                           Fe / TILE_K, L.moe_down.splits, down_chosen ? sc->moe_kb_map : nullptr, sc->moe_n_tiles + 1));
+                                           Fe / TILE_K, 1, down_chosen ? sc->moe_kb_map : nullptr, sc->moe_n_tiles + 1, gemm_ts_kc(),
+                                           down_chosen ? L.moe_down.mats[0].row_tiles : 1, down_chosen ? L.moe_down.splits : 0));
                 GemmEpilogue ep_gu = ep_norm;
                 ep_gu.tile_map = sc->moe_tile_map;
                 ep_gu.n_tiles = sc->moe_n_tiles;
@@ -292,21 +295,25 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             DFL_CHECK(launch_glue(st, p, (uint64_t)inner));
             GemmEpilogue ep_down;
             ep_down.out_scale = 64.0f;
+            // partial slices: the shared expert's first, then the routed experts' - as many as the split count in use,
+            // which follows the number of chosen experts (written beside the lists) when only those are summed over
             GemmEpilogue ep_down_exps = ep_down;
-            if (chosen_only && down_chosen) {   // sum only over the chosen experts' column blocks
+            const int sh_splits = Fs > 0 ? L.moe_down_sh.splits : 0;
+            if (chosen_only && down_chosen) {
                 ep_down_exps.kb_map = sc->moe_kb_map;
                 ep_down_exps.n_kb = sc->moe_n_tiles + 1;
+                ep_down_exps.dynamic_splits = true;
+                down_splits_dev = sc->moe_n_tiles + 2;
             }
-            DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part, ep_down_exps, s->err));
-            down_splits = L.moe_down.splits;
-            if (Fs > 0) {
-                DFL_CHECK(launch_group(st, L.moe_down_sh, sc->acts_f + (uint64_t)(En * Fe / TILE_K) * act_chunk_bytes(m->act_layout),
-                                       sc->part + (uint64_t)L.moe_down.splits * MAX_ROWS * H, ep_down, s->err));
-                down_splits += L.moe_down_sh.splits;
-            }
+            if (Fs > 0)
+                DFL_CHECK(launch_group(st, L.moe_down_sh, sc->acts_f + (uint64_t)(En * Fe / TILE_K) * act_chunk_bytes(m->act_layout), sc->part,
+                                       ep_down, s->err));
+            DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part + (uint64_t)sh_splits * MAX_ROWS * H, ep_down_exps, s->err));
+            down_splits = sh_splits + (down_splits_dev ? 0 : L.moe_down.splits);
             if (m->ep_world > 1) {
                 // sum this rank's slices, then over the ranks: every rank continues with the same [16][H] block output
-                DFL_CHECK(launch_reduce_partials(st, sc->part, down_splits, MAX_ROWS, H, sc->moe_out, (int)H));
+                DFL_CHECK(launch_reduce_partials(st, sc->part, down_splits, MAX_ROWS, H, sc->moe_out, (int)H, down_splits_dev));
+                down_splits_dev = nullptr;
                 DFL_CHECK(ep_all_reduce_sum(m->ep_comm, sc->moe_out, (size_t)MAX_ROWS * H, st));
                 moe_part = sc->moe_out;
                 down_splits = 1;
@@ -335,7 +342,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         const bool last = il + 1 == a.n_layer;
         const float* next_w = last ? m->out_norm_w : m->layers[il + 1].attn_norm_w;
         const bool next_gdn = !last && !m->layers[il + 1].is_attn;
-        DFL_CHECK(norm_glue(moe_part, down_splits, (int)H, next_w, next_gdn, cap));
+        DFL_CHECK(norm_glue(moe_part, down_splits, (int)H, next_w, next_gdn, cap, down_splits_dev));
         if (cap) {
             // duplicate slots (same layer listed twice) get a device copy of the first one
             bool first = true;

@@ -89,7 +89,7 @@ dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_
 // fixed launch geometry busy with at least one tile.
 __global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float* route_w, int n_rows, int n_expert, int e0, int n_local, int T,
                                                                     int Ts, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int KB, int min_kb, int32_t* kb_map,
-                                                                    int32_t* n_kb) {
+                                                                    int32_t* n_kb, int kc, int down_tiles, int max_splits) {
     pdl_prologue();
     __shared__ int warp_count[MOE_MAX_EXPERTS / 32];
     __shared__ int total_sh;
@@ -128,16 +128,30 @@ __global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float*
     }
     if (kb_map && e == 0) {
         const int want = n_act * KB, all = n_local * KB;
-        *n_kb = want > min_kb ? want : (min_kb < all ? min_kb : all);
+        const int len = want > min_kb ? want : (min_kb < all ? min_kb : all);
+        n_kb[0] = len;
+        // split geometry for this list length: enough splits to keep a CTA's blocks resident and to give the 148 SMs
+        // work, as many CTAs per split as fit beside them; 0 = the launch's own geometry
+        int s = 0, cps = 0;
+        if (max_splits > 0) {
+            s = (len + kc - 1) / kc;
+            const int fill = (148 + down_tiles - 1) / down_tiles;
+            if (s < fill) s = fill;
+            if (s > max_splits) s = max_splits;
+            if (s > len) s = len;
+            cps = 148 / s < down_tiles ? 148 / s : down_tiles;
+        }
+        n_kb[1] = s;
+        n_kb[2] = cps;
     }
 }
 
 dfl_status launch_moe_tiles(cudaStream_t st, const float* route_w, int n_rows, int n_expert, int e0, int n_local, int tiles_per_expert,
                             int shared_tiles, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,
-                            int32_t* n_kb) {
+                            int32_t* n_kb, int kc, int down_tiles, int max_splits) {
     if (n_local > MOE_MAX_EXPERTS || shared_tiles > MOE_MAX_EXPERTS) return fail(DFL_ERR_UNSUPPORTED, "moe_tiles: too many experts");
     launch_kf(16, moe_tiles_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), 0, st, route_w, n_rows, n_expert, e0, n_local, tiles_per_expert, shared_tiles,
-              min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb);
+              min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb, kc, down_tiles, max_splits);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -78,6 +78,7 @@ struct GlueParams {
     int mode = GLUE_RESID;
     const float* part = nullptr;  // [splits][16][ld_part]
     int splits = 0;
+    const int32_t* splits_dev = nullptr;   // optional: *splits_dev more slices follow the first `splits` (a device-chosen count)
     int ld_part = 0;
     float* x = nullptr;           // [16][ld_x]
     int ld_x = 0;
@@ -110,7 +111,7 @@ dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_
 // row tiles of the gate|up matrix that belong to experts some row of the block chose (plus the shared expert)
 dfl_status launch_moe_tiles(cudaStream_t st, const float* route_w, int n_rows, int n_expert, int e0, int n_local, int tiles_per_expert,
                             int shared_tiles, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,
-                            int32_t* n_kb);
+                            int32_t* n_kb, int kc, int down_tiles, int max_splits);
 
 // x[tok][0..h) = decoded row tokens[tok] of a ggml matrix [vocab][h] (kernel_get_rows_*,
 // kernels/elementwise.metal:727-958).  tokens live on the device.

@@ -198,6 +198,9 @@ struct GemmEpilogue {
     // what the splits were chosen for (the activations of a listed block are used as they are)
     const int32_t* kb_map = nullptr;
     const int32_t* n_kb = nullptr;
+    // n_kb[1] / n_kb[2] (when n_kb[1] > 0): split count and CTAs per split to use for this list length, their product
+    // at most 148, the splits at most the launch's own; the caller sums that many partial slices
+    bool dynamic_splits = false;
 };
 int gemm_choose_splits(const QMatrix& m);
 int gemm_max_kblocks_per_cta(int dtype);  // column blocks one CTA can keep resident
@@ -226,7 +229,7 @@ dfl_status launch_prep_acts_for(cudaStream_t st, const QMatrix& m, const float* 
                                 int* dev_err);
 // Sum split-K partials: y[r][o] = sum_s part[s][r][o], r < n_rows.
 dfl_status launch_reduce_partials(cudaStream_t st, const float* part, int splits, int n_rows, uint64_t n_out,
-                                  float* y, int ld_y);
+                                  float* y, int ld_y, const int32_t* splits_dev = nullptr);   // *splits_dev more slices when given
 // Row argmax (lowest index on ties, total order) + gap to the runner-up.
 dfl_status launch_argmax_top2(cudaStream_t st, const float* logits, int n_rows, uint64_t vocab, uint64_t ld,
                               int32_t* argmax, float* gap, void* scratch /* >= n_rows*ARGMAX_PARTS*16 B */);
