@@ -95,8 +95,11 @@ __global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float*
     __shared__ int total_sh;
     const int e = threadIdx.x, warp = e >> 5, lane = e & 31;
     bool active = false;
-    if (e < n_local)
-        for (int tok = 0; tok < n_rows; ++tok) active = active || route_w[(uint64_t)tok * n_expert + e0 + e] != 0.f;
+    if (e < n_local) {
+#pragma unroll
+        for (int tok = 0; tok < MAX_ROWS; ++tok)   // independent loads (rows beyond the block are zero rows)
+            active |= route_w[(uint64_t)tok * n_expert + e0 + e] != 0.f;
+    }
     const uint32_t bal = __ballot_sync(0xffffffffu, active);
     if (lane == 0) warp_count[warp] = __popc(bal);
     __syncthreads();
