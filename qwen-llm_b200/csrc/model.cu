@@ -260,26 +260,34 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             // few-row GEMMs; the glue zeroes the inner columns of the experts a token did not choose
             const int E = (int)a.expert_count, Fe = (int)a.expert_feed_forward_length, Fs = (int)m->ep_fs, En = (int)m->ep_n;
             const int inner = En * Fe + Fs;
-            // router + selection beside the gate|up GEMM (which reads every expert and needs no routing)
-            DFL_CHECK(fork_side());
-            DFL_CHECK(launch_small_matmul(side, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
-            DFL_CHECK(launch_moe_route(side, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
-            // only the experts some row chose (and the shared expert) are streamed when the four blocks sit in one
-            // tensor-memory matrix; otherwise every expert is, and the router runs beside the GEMM
+            // Only the experts some row chose (and the shared expert) are streamed when the four gate / up blocks sit in
+            // one tensor-memory matrix: router -> selection + lists -> GEMM over the listed tiles, one after the other.
+            // Otherwise every expert is streamed and the router and the selection run beside that GEMM.
             const MatGroup& GU = L.moe_gate_up;
             const bool down_chosen = L.moe_down.mats.size() == 1 && L.moe_down.mats[0].layout == LAYOUT_TS && Fe % TILE_K == 0;
             const bool chosen_only = moe_chosen_only && GU.mats.size() == 1 && GU.mats[0].layout == LAYOUT_TS && Fe % TILE_R == 0 && Fs % TILE_R == 0;
             if (chosen_only) {
-                DFL_CHECK(join_side());
-                DFL_CHECK(launch_moe_tiles(st, sc->route_w, (int)n, E, (int)m->ep_e0, En, Fe / TILE_R, Fs / TILE_R,
-                                           gemm_ts_ctas_per_split(GU.mats[0].row_tiles, GU.splits), sc->moe_tile_map, sc->moe_n_tiles,
-                                           Fe / TILE_K, 1, down_chosen ? sc->moe_kb_map : nullptr, sc->moe_n_tiles + 1, gemm_ts_kc(),
-                                           down_chosen ? L.moe_down.mats[0].row_tiles : 1, down_chosen ? L.moe_down.splits : 0));
+                const int min_tiles = gemm_ts_ctas_per_split(GU.mats[0].row_tiles, GU.splits);
+                const int down_tiles = down_chosen ? L.moe_down.mats[0].row_tiles : 1, down_max = down_chosen ? L.moe_down.splits : 0;
+                int32_t* kb_map = down_chosen ? sc->moe_kb_map : nullptr;
+                DFL_CHECK(launch_small_matmul(st, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
+                if (moe_route_lists_fused(E)) {
+                    DFL_CHECK(launch_moe_route_lists(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg,
+                                                     sc->route_idx, (int)m->ep_e0, En, Fe / TILE_R, Fs / TILE_R, min_tiles, sc->moe_tile_map,
+                                                     sc->moe_n_tiles, Fe / TILE_K, 1, kb_map, sc->moe_n_tiles + 1, gemm_ts_kc(), down_tiles, down_max));
+                } else {
+                    DFL_CHECK(launch_moe_route(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
+                    DFL_CHECK(launch_moe_tiles(st, sc->route_w, (int)n, E, (int)m->ep_e0, En, Fe / TILE_R, Fs / TILE_R, min_tiles, sc->moe_tile_map,
+                                               sc->moe_n_tiles, Fe / TILE_K, 1, kb_map, sc->moe_n_tiles + 1, gemm_ts_kc(), down_tiles, down_max));
+                }
                 GemmEpilogue ep_gu = ep_norm;
                 ep_gu.tile_map = sc->moe_tile_map;
                 ep_gu.n_tiles = sc->moe_n_tiles;
                 DFL_CHECK(launch_group(st, GU, sc->acts_h, sc->part, ep_gu, s->err));
             } else {
+                DFL_CHECK(fork_side());
+                DFL_CHECK(launch_small_matmul(side, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
+                DFL_CHECK(launch_moe_route(side, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
                 DFL_CHECK(launch_group(st, GU, sc->acts_h, sc->part, ep_norm, s->err));
                 DFL_CHECK(join_side());
             }

@@ -14,12 +14,9 @@ namespace dfl {
 
 constexpr int MOE_MAX_EXPERTS = 1024;
 
-__global__ void __launch_bounds__(32) moe_route_kernel(const float* logits, int ld, int n_expert, int n_used, int n_rows,
-                                                       float* route_w, float* shared_gate,
-                                                       int32_t* route_idx) {
-    pdl_prologue();
-    __shared__ float p[MOE_MAX_EXPERTS];
-    const int tok = blockIdx.x, lane = threadIdx.x;
+// routing of one row by one warp; p = n_expert floats of shared memory of its own
+__device__ __forceinline__ void moe_route_row(float* p, int tok, int lane, const float* logits, int ld, int n_expert, int n_used, int n_rows,
+                                              float* route_w, float* shared_gate, int32_t* route_idx) {
     float* wrow = route_w + (uint64_t)tok * n_expert;
     for (int i = lane; i < n_expert; i += 32) wrow[i] = 0.f;
     if (tok >= n_rows) {
@@ -71,6 +68,14 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const float* logits, int 
     if (lane == 0) shared_gate[tok] = sigmoid_f(x[n_expert]);
 }
 
+__global__ void __launch_bounds__(32) moe_route_kernel(const float* logits, int ld, int n_expert, int n_used, int n_rows,
+                                                       float* route_w, float* shared_gate,
+                                                       int32_t* route_idx) {
+    pdl_prologue();
+    __shared__ float p[MOE_MAX_EXPERTS];
+    moe_route_row(p, blockIdx.x, threadIdx.x, logits, ld, n_expert, n_used, n_rows, route_w, shared_gate, route_idx);
+}
+
 dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_expert, int n_used, int n_rows, float* route_w,
                             float* shared_gate, int32_t* route_idx) {
     if (n_expert < 1 || n_expert > MOE_MAX_EXPERTS || n_used < 1 || n_used > 32 || n_used > n_expert)
@@ -87,10 +92,17 @@ dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_
 // list holds the tiles of the active experts and of the shared expert, so the GEMM streams only those.  It is padded
 // by repetition up to min_tiles (a repeated tile is computed twice with the same result), which keeps every CTA of the
 // fixed launch geometry busy with at least one tile.
-__global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float* route_w, int n_rows, int n_expert, int e0, int n_local, int T,
-                                                                    int Ts, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int KB, int min_kb, int32_t* kb_map,
-                                                                    int32_t* n_kb, int kc, int down_tiles, int max_splits) {
-    pdl_prologue();
+struct MoeListArgs {
+    int n_expert, e0, n_local, T, Ts, min_tiles;
+    int32_t *tile_map, *n_tiles;
+    int KB, min_kb;
+    int32_t *kb_map, *n_kb;
+    int kc, down_tiles, max_splits;
+};
+__device__ __forceinline__ void moe_build_lists(const float* route_w, const MoeListArgs a) {
+    const int n_expert = a.n_expert, e0 = a.e0, n_local = a.n_local, T = a.T, Ts = a.Ts, min_tiles = a.min_tiles, KB = a.KB, min_kb = a.min_kb;
+    const int kc = a.kc, down_tiles = a.down_tiles, max_splits = a.max_splits;
+    int32_t *tile_map = a.tile_map, *n_tiles = a.n_tiles, *kb_map = a.kb_map, *n_kb = a.n_kb;
     __shared__ int warp_count[MOE_MAX_EXPERTS / 32];
     __shared__ int total_sh;
     const int e = threadIdx.x, warp = e >> 5, lane = e & 31;
@@ -149,12 +161,54 @@ __global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float*
     }
 }
 
+__global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float* route_w, const MoeListArgs a) {
+    pdl_prologue();
+    moe_build_lists(route_w, a);
+}
+// routing of the block's rows (warps 0-15, one row each) and the lists in one launch
+__global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_route_lists_kernel(const float* logits, int ld, int n_used, int n_rows, float* route_w,
+                                                                          float* shared_gate, int32_t* route_idx, const MoeListArgs a) {
+    pdl_prologue();
+    extern __shared__ float p_rows[];   // [16][n_expert]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp < MAX_ROWS) moe_route_row(p_rows + warp * a.n_expert, warp, lane, logits, ld, a.n_expert, n_used, n_rows, route_w, shared_gate, route_idx);
+    __syncthreads();   // the rows' route weights (global, written by this CTA) are complete
+    moe_build_lists(route_w, a);
+}
+
+static MoeListArgs moe_list_args(int n_expert, int e0, int n_local, int tiles_per_expert, int shared_tiles, int min_tiles, int32_t* tile_map,
+                                 int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map, int32_t* n_kb, int kc, int down_tiles,
+                                 int max_splits) {
+    return MoeListArgs{n_expert, e0, n_local, tiles_per_expert, shared_tiles, min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb,
+                       kc, down_tiles, max_splits};
+}
+
 dfl_status launch_moe_tiles(cudaStream_t st, const float* route_w, int n_rows, int n_expert, int e0, int n_local, int tiles_per_expert,
                             int shared_tiles, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,
                             int32_t* n_kb, int kc, int down_tiles, int max_splits) {
+    (void)n_rows;
     if (n_local > MOE_MAX_EXPERTS || shared_tiles > MOE_MAX_EXPERTS) return fail(DFL_ERR_UNSUPPORTED, "moe_tiles: too many experts");
-    launch_kf(16, moe_tiles_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), 0, st, route_w, n_rows, n_expert, e0, n_local, tiles_per_expert, shared_tiles,
-              min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb, kc, down_tiles, max_splits);
+    launch_kf(16, moe_tiles_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), 0, st, route_w,
+              moe_list_args(n_expert, e0, n_local, tiles_per_expert, shared_tiles, min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb,
+                            kc, down_tiles, max_splits));
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+// routing + lists in one launch when the rows' probability scratch fits the default shared-memory window
+bool moe_route_lists_fused(int n_expert) { return (size_t)MAX_ROWS * n_expert * 4 <= 40 * 1024; }
+dfl_status launch_moe_route_lists(cudaStream_t st, const float* logits, int ld, int n_expert, int n_used, int n_rows, float* route_w,
+                                  float* shared_gate, int32_t* route_idx, int e0, int n_local, int tiles_per_expert, int shared_tiles,
+                                  int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,
+                                  int32_t* n_kb, int kc, int down_tiles, int max_splits) {
+    if (n_expert < 1 || n_used < 1 || n_used > 32 || n_used > n_expert || !moe_route_lists_fused(n_expert) || n_local > MOE_MAX_EXPERTS ||
+        shared_tiles > MOE_MAX_EXPERTS)
+        return fail(DFL_ERR_UNSUPPORTED, "moe_route_lists: geometry");
+    launch_kf(16, moe_route_lists_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), (size_t)MAX_ROWS * n_expert * 4, st, logits, ld, n_used, n_rows, route_w,
+              shared_gate, route_idx,
+              moe_list_args(n_expert, e0, n_local, tiles_per_expert, shared_tiles, min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb,
+                            kc, down_tiles, max_splits));
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
