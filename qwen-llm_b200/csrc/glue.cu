@@ -21,22 +21,27 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (live) {
         if (p.mode == GLUE_SWIGLU) {
-            float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
-            const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
-            const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
+            // route weight of this row for the expert the columns belong to (1 without routing); a row that did not
+            // choose the expert gets exact zeros and its partial sums - possibly stale - are not even read
+            float w = 1.f;
+            if (p.route_w) w = col0 < p.route_n * p.route_f ? p.route_w[tok * p.route_e + p.route_e0 + col0 / p.route_f] : p.route_sg[tok];
+            if (w != 0.f) {
+                float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+                const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
+                const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
 #pragma unroll 4
-            for (int s = 0; s < n_splits; ++s) {
-                const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
-                const float4 b = *reinterpret_cast<const float4*>(base + s * stride + p.swiglu_f);
-                g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
-                u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
-            }
+                for (int s = 0; s < n_splits; ++s) {
+                    const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
+                    const float4 b = *reinterpret_cast<const float4*>(base + s * stride + p.swiglu_f);
+                    g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+                    u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
+                }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = silu_f(g[j]) * u[j];
-            if (p.route_w) {
-                const float w = col0 < p.route_n * p.route_f ? p.route_w[tok * p.route_e + p.route_e0 + col0 / p.route_f] : p.route_sg[tok];
+                for (int j = 0; j < 4; ++j) v[j] = silu_f(g[j]) * u[j];
+                if (p.route_w) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = w != 0.f ? v[j] * w : 0.f;   // columns of experts nobody chose may hold stale partials
+                    for (int j = 0; j < 4; ++j) v[j] *= w;
+                }
             }
         } else {
             float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
