@@ -403,7 +403,7 @@ def run_verify_only(args, rank, world, device):
         extra = {**extra, "kv_bytes_per_verify": kvb, "weight_bytes_per_verify": vb}
         vb += kvb
     return {"metric": "verify_ms", "value": wall * 1e3, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": wall * 1e3, "higher_is_better": False, "config": {"workload": ("c4v: packed verify only, 16 rows, 256 experts top-8 + shared, every expert streamed" if moe
+            "ms_per_step": wall * 1e3, "higher_is_better": False, "config": {"workload": (("c4v: packed verify only, 16 rows, 256 experts top-8 + shared, " + ("every expert streamed" if os.environ.get("DFL_MOE_ALL_EXPERTS") else "chosen experts streamed")) if moe
                                     else f"c5v: packed verify only, 16 rows over a context of {ctx} positions (fp16 KV)" if ctx
                                     else "c2v: packed verify only, 16 rows")},
             "roofline": {"bound": "hbm", "achieved": vb / wall / 1e9, "peak": peak, "unit": "GB/s", "frac": vb / wall / 1e9 / peak,
