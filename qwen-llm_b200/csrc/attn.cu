@@ -285,6 +285,11 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
         set = true;
     }
     int rows_per_cta = (long long)n_chunks * g.n_kv >= 2 * 148 ? MAX_ROWS : ATTN_ROW_GROUP;
+    // Short contexts leave most SMs idle at four rows per CTA: narrow the row group while every warp still has a query.
+    const int group = g.n_q / g.n_kv;
+    while (rows_per_cta > 1 && rows_per_cta <= ATTN_ROW_GROUP && (rows_per_cta / 2) * group >= 8 &&
+           (long long)n_chunks * g.n_kv * ((n_rows + rows_per_cta - 1) / rows_per_cta) < 148)
+        rows_per_cta /= 2;
     if (const char* e = getenv("DFL_ATTN_ROWS_PER_CTA")) {   // test hook: results must not depend on the grouping
         const int v = atoi(e);
         if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) rows_per_cta = v;
