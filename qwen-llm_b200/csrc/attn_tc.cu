@@ -281,38 +281,45 @@ __global__ void __launch_bounds__(128) dattn_span_tc_kernel(AttnGeom g, const fl
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
 
+    float4 kk[8], vv[8];
+    bool have_half = false;
+    const uint64_t row_stride = (uint64_t)g.n_kv * TC_HD;
+    auto load_half = [&](int chunk, int half) {
+        const uint64_t base = ((uint64_t)(ctx_begin + chunk * ATTN_CHUNK) * g.n_kv + kvh) * TC_HD;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int idx = threadIdx.x + 128 * (8 * half + i), kp = idx >> 5, d4 = (idx & 31) * 4;
+            kk[i] = *reinterpret_cast<const float4*>(k_ctx + base + kp * row_stride + d4);
+            vv[i] = *reinterpret_cast<const float4*>(v_ctx + base + kp * row_stride + d4);
+        }
+    };
+    auto store_half = [&](int half) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int idx = threadIdx.x + 128 * (8 * half + i), kp = idx >> 5, d4 = (idx & 31) * 4;
+            uint32_t h01, l01, h23, l23;
+            split_pair(kk[i].x, kk[i].y, h01, l01);
+            split_pair(kk[i].z, kk[i].w, h23, l23);
+            *reinterpret_cast<uint2*>(k_hi + kp * TC_PITCH + d4) = make_uint2(h01, h23);
+            *reinterpret_cast<uint2*>(k_lo + kp * TC_PITCH + d4) = make_uint2(l01, l23);
+            split_pair(vv[i].x, vv[i].y, h01, l01);
+            split_pair(vv[i].z, vv[i].w, h23, l23);
+            *reinterpret_cast<uint2*>(v_hi + kp * TC_PITCH + d4) = make_uint2(h01, h23);
+            *reinterpret_cast<uint2*>(v_lo + kp * TC_PITCH + d4) = make_uint2(l01, l23);
+        }
+    };
     for (int c = c_begin; c < c_end; ++c) {
         const int j0 = c * ATTN_CHUNK;
         const int n_here = min(ATTN_CHUNK, n_keys - j0);
         __syncthreads();   // previous chunk fully consumed (and the query planes written)
         // K / V rows of the chunk: 64 x 512 B each, one float4 of K and of V per thread and step, split on the way in
         if (j0 + ATTN_CHUNK <= n_ctx) {
-            // whole chunk inside the context: eight K and eight V loads in flight per thread before any of them is split
-            const uint64_t base = ((uint64_t)(ctx_begin + j0) * g.n_kv + kvh) * TC_HD;
-            const uint64_t row_stride = (uint64_t)g.n_kv * TC_HD;
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
-                float4 kk[8], vv[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int idx = threadIdx.x + 128 * (8 * half + i), kp = idx >> 5, d4 = (idx & 31) * 4;
-                    kk[i] = *reinterpret_cast<const float4*>(k_ctx + base + kp * row_stride + d4);
-                    vv[i] = *reinterpret_cast<const float4*>(v_ctx + base + kp * row_stride + d4);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int idx = threadIdx.x + 128 * (8 * half + i), kp = idx >> 5, d4 = (idx & 31) * 4;
-                    uint32_t h01, l01, h23, l23;
-                    split_pair(kk[i].x, kk[i].y, h01, l01);
-                    split_pair(kk[i].z, kk[i].w, h23, l23);
-                    *reinterpret_cast<uint2*>(k_hi + kp * TC_PITCH + d4) = make_uint2(h01, h23);
-                    *reinterpret_cast<uint2*>(k_lo + kp * TC_PITCH + d4) = make_uint2(l01, l23);
-                    split_pair(vv[i].x, vv[i].y, h01, l01);
-                    split_pair(vv[i].z, vv[i].w, h23, l23);
-                    *reinterpret_cast<uint2*>(v_hi + kp * TC_PITCH + d4) = make_uint2(h01, h23);
-                    *reinterpret_cast<uint2*>(v_lo + kp * TC_PITCH + d4) = make_uint2(l01, l23);
-                }
-            }
+            // whole chunk inside the context: eight K and eight V loads in flight per thread before any of them is
+            // split; the first half was requested before the previous chunk's MMAs when that chunk took this path
+            if (!have_half) load_half(c, 0);
+            store_half(0);
+            load_half(c, 1);
+            store_half(1);
         } else
 #pragma unroll 4
         for (int i = 0; i < ATTN_CHUNK * 32 / 128; ++i) {
@@ -340,6 +347,8 @@ __global__ void __launch_bounds__(128) dattn_span_tc_kernel(AttnGeom g, const fl
             *reinterpret_cast<uint2*>(v_hi + kp * TC_PITCH + d4) = make_uint2(h01, h23);
             *reinterpret_cast<uint2*>(v_lo + kp * TC_PITCH + d4) = make_uint2(l01, l23);
         }
+        have_half = c + 1 < c_end && (c + 2) * ATTN_CHUNK <= n_ctx;
+        if (have_half) load_half(c + 1, 0);   // lands while this chunk's MMAs run
         if (threadIdx.x < ATTN_CHUNK) {
             const int j = j0 + (int)threadIdx.x;
             kpos[threadIdx.x] = j < n_ctx ? pos_ctx[ctx_begin + j] : noise_start + (uint32_t)(j - n_ctx);
