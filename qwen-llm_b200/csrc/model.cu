@@ -313,10 +313,14 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
                 ep_down_exps.dynamic_splits = true;
                 down_splits_dev = sc->moe_n_tiles + 2;
             }
-            if (Fs > 0)
-                DFL_CHECK(launch_group(st, L.moe_down_sh, sc->acts_f + (uint64_t)(En * Fe / TILE_K) * act_chunk_bytes(m->act_layout), sc->part,
+            // the shared expert's small down projection runs beside the routed experts' on the side stream
+            if (Fs > 0) {
+                DFL_CHECK(fork_side());
+                DFL_CHECK(launch_group(side, L.moe_down_sh, sc->acts_f + (uint64_t)(En * Fe / TILE_K) * act_chunk_bytes(m->act_layout), sc->part,
                                        ep_down, s->err));
+            }
             DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part + (uint64_t)sh_splits * MAX_ROWS * H, ep_down_exps, s->err));
+            if (Fs > 0) DFL_CHECK(join_side());
             down_splits = sh_splits + (down_splits_dev ? 0 : L.moe_down.splits);
             if (m->ep_world > 1) {
                 // sum this rank's slices, then over the ranks: every rank continues with the same [16][H] block output
