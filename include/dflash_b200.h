@@ -45,7 +45,8 @@ typedef enum dfl_status {
     DFL_ERR_BAD_TOKEN = 10,    /* ForwardError::BadToken, forward.rs:24 */
     DFL_ERR_SAMPLING = 11,     /* SamplingError / DFlashAcceptError */
     DFL_ERR_TIMEOUT = 12,      /* a bounded device-side wait gave up */
-    DFL_ERR_MISSING_TENSOR = 13
+    DFL_ERR_MISSING_TENSOR = 13,
+    DFL_ERR_ROUTE_STATUS = 14  /* expert routing reported NONFINITE (kernels/moe.metal:355-360); poisons the session */
 } dfl_status;
 
 /* ggml type ids (crates/qwen-llm/src/tensor.rs:159 `storage_layout`). */
@@ -176,19 +177,23 @@ dfl_status dfl_fewrow_matmul(const dfl_qmatrix* m, const float* x_host, int32_t 
 dfl_status dfl_argmax_top2(int32_t device, const float* logits_host, int32_t n_rows,
                            uint64_t vocab, int32_t* argmax_out, float* gap_out);
 /* The same row argmax for a caller that must not allocate device memory or
- * block: code running inside a host callback of a stream, a thread that holds a
- * lock the CUDA allocator may also need, or a serving loop with a fixed memory
- * budget.  This entry point has no counterpart in the reference; it exists for
- * such callers.  logits_dev [n_rows][ld] f32, argmax_dev [n_rows] and gap_dev
- * [n_rows] are the caller's own buffers on `device`; `stream` is a
- * cudaStream_t (NULL = the default stream).  The call enqueues two kernels
- * on `stream` and returns without waiting: results are valid once the stream
- * reaches that point.  It calls no allocation or free routine; its per-row
- * partial results live in one fixed 16 KiB array inside the library, sized
- * for n_rows <= 16 (larger n_rows is refused with DFL_ERR_BAD_SHAPE).  The
- * first call on each device also looks up the array's address, so make one
- * call per device before starting a stream capture.  Every call on a device
- * shares that array and each call overwrites the part it uses before
+ * wait for the GPU: an ordinary host thread that holds a lock the CUDA
+ * allocator may also need, or a serving loop with a fixed memory budget.  (It
+ * is not for code inside a stream's host callback: CUDA forbids runtime calls
+ * there, and this function makes several.)  This entry point has no counterpart
+ * in the reference; it exists for such callers.  logits_dev [n_rows][ld] f32,
+ * argmax_dev [n_rows] and gap_dev [n_rows] are the caller's own buffers on
+ * `device`; `stream` is a cudaStream_t (NULL = the default stream).  The call
+ * makes `device` the calling thread's current device and leaves it so, enqueues
+ * two kernels on `stream` and returns without waiting: results are valid once
+ * the stream reaches that point.  It calls no allocation or free routine; its
+ * per-row partial results live in one fixed 16 KiB array inside the library,
+ * sized for n_rows <= 16 (larger n_rows is refused with DFL_ERR_BAD_SHAPE).
+ * The first call on each device also looks up the array's address (and may
+ * make the driver load the library's kernels, which is not allocation-free from
+ * the driver's point of view), so make one call per device before starting a
+ * stream capture or entering the section that must not allocate.  Every call on
+ * a device shares that array and each call overwrites the part it uses before
  * reading it, so nothing needs clearing; but two calls whose kernels can
  * overlap (different streams, or different threads on different streams)
  * race on it: keep calls on one device in stream order. */
@@ -196,7 +201,7 @@ dfl_status dfl_argmax_top2_static(int32_t device, const float* logits_dev, int32
                                   uint64_t vocab, uint64_t ld, int32_t* argmax_dev,
                                   float* gap_dev, void* stream);
 
-/* ---- BASELINE config 1: two chained few-row GEMMs + greedy acceptance ---
+/* ---- the CPU-runnable verify/accept case: two chained few-row GEMMs + greedy acceptance ---
  * logits = head(x W1^T); argmax per row; greedy prefix accept against drafts.
  * Device-resident pipeline object so the timed region has no allocation. */
 typedef struct dfl_c1 dfl_c1;
@@ -262,7 +267,7 @@ dfl_status dfl_session_read_kv(const dfl_session* s, uint32_t attn_index, uint32
                                float* k_out, float* v_out, uint64_t n);
 
 /* ---- session snapshots (SessionSnapshot, metal_forward/session.rs:13-94) ---- */
-#define DFL_SNAPSHOT_LAYOUT_VERSION 1
+#define DFL_SNAPSHOT_LAYOUT_VERSION 2
 typedef struct dfl_snapshot_identity { /* SnapshotAbi  session.rs:27-37 */
     uint32_t layout_version;
     uint32_t n_attn_layers;
@@ -306,26 +311,54 @@ dfl_status dfl_packed_verify(const dfl_model* m, dfl_session* s, dfl_scratch* sc
                              const uint32_t* layer_ids, uint32_t n_layer_ids,
                              const int32_t* tokens, uint32_t n, uint32_t start_position,
                              int32_t* argmax_out, float* gap_out, float* logits_host);
+/* The same call with the reference's n_eff_override argument spelled out
+ * (metal_dflash.rs:9055-9094): n_eff_override < 0 is None (the chain is the
+ * scratch's block size), otherwise the effective chain length in [1, block];
+ * n_tokens must equal the resolved length. */
+dfl_status dfl_packed_verify_n_eff(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
+                                   const uint32_t* layer_ids, uint32_t n_layer_ids,
+                                   const int32_t* tokens, uint32_t n_tokens, uint32_t start_position,
+                                   int32_t n_eff_override, int32_t* argmax_out, float* gap_out,
+                                   float* logits_host);
 /* Copy captured hidden rows [n][k][H] of the last verify to the host. */
 dfl_status dfl_scratch_read_capture(const dfl_scratch* sc, uint32_t n, float* out_host,
                                     uint64_t n_floats);
+/* Expert ids the last routed-expert layer of the last verify chose, [n][expert_used_count] in
+ * choice order, -1 for a row that was not routed (moe_topk_idx of MetalDFlashLayerMajorScratch,
+ * metal_dflash.rs:7240-7443). */
+dfl_status dfl_scratch_read_route(const dfl_scratch* sc, uint32_t n, int32_t* idx_out, uint64_t n_idx);
+/* Failure-path probe: runs a one-thread kernel on the session's stream that waits, with a limit
+ * of `polls` polls (1..65536), on a barrier nobody arrives at.  The wait runs out, the kernel
+ * records that in the session's error word and returns normally; the call then reports
+ * DFL_ERR_TIMEOUT and the session is poisoned, exactly as when a bounded wait inside a GEMM
+ * gives up (the reference's completion check, metal/completion.rs:18, + poisoning,
+ * metal_forward/mod.rs:2161-2170). */
+dfl_status dfl_session_probe_wait_timeout(const dfl_model* m, dfl_session* s, uint32_t polls);
 
 /* encode_restore_after_partial_accept_inner  metal_dflash.rs:15649-15777:
  * n_keep in [1, n]; GDN state / conv := state after n_keep tokens of the last
  * verify block; kv_n_pos := start_position + n_keep. */
 dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
                                uint32_t n_keep, uint32_t start_position);
+/* ... with n_eff_override as above; it must resolve to the same length as the verify being
+ * undone (metal_dflash.rs:15655-15682). */
+dfl_status dfl_restore_partial_n_eff(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
+                                     uint32_t n_keep, uint32_t start_position, int32_t n_eff_override);
 /* encode_restore_to_pre_block  metal_dflash.rs:15789. */
 dfl_status dfl_restore_pre_block(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
                                  uint32_t start_position);
 
-/* MetalForward::single_token_with_multi_hidden  metal_forward/token.rs:984. */
+/* MetalForward::single_token_with_multi_hidden  metal_forward/token.rs:984.
+ * logits_host (optional) [vocab]; hidden_host (optional) [n_layer_ids][H]. */
 dfl_status dfl_single_token(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
                             const uint32_t* layer_ids, uint32_t n_layer_ids, int32_t token,
                             uint32_t position, float* logits_host, float* hidden_host);
 /* prefill_tokens_with_multi_hidden  metal_dflash.rs:10779-10787: feeds ids in
- * blocks of <=16 through the verify path; hidden_host (optional) [n][k][H];
- * last_logits_host (optional) [vocab]. */
+ * blocks of <=16 through the verify path; hidden_host (optional) [n][k][H] with
+ * k = the scratch's capture slots (slots beyond n_layer_ids are not written);
+ * last_logits_host (optional) [vocab].  With feed_drafter every captured row is
+ * appended to that drafter session, so n_layer_ids must equal the scratch's
+ * capture slots. */
 dfl_status dfl_prefill(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
                        const uint32_t* layer_ids, uint32_t n_layer_ids, const int32_t* ids,
                        uint64_t n, uint32_t start_position, dfl_dsession* feed_drafter,

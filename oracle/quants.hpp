@@ -213,14 +213,23 @@ inline void dequant_to_f32(int32_t dt, const uint8_t* src, uint64_t n_elements, 
     storage_layout(dt, blk, bytes);
     if (n_elements % blk) throw std::runtime_error("oracle: row not block aligned");
     const uint64_t nb = n_elements / blk;
-    switch (dt) {
-        case F32: std::memcpy(y, src, n_elements * 4); return;
-        case F16: for (uint64_t i = 0; i < n_elements; ++i) y[i] = f16_to_f32(rd16(src + 2 * i)); return;
-        case BF16: for (uint64_t i = 0; i < n_elements; ++i) y[i] = bf16_to_f32(rd16(src + 2 * i)); return;
-        case Q8_0: dequant_q8_0(src, y, nb); return;
-        case Q4_K: dequant_q4_k(src, y, nb); return;
-        case Q5_K: dequant_q5_k(src, y, nb); return;
-        case Q6_K: dequant_q6_k(src, y, nb); return;
+    // Large tensors are decoded in independent runs of blocks on several threads; every value is the same
+    // as in one sequential pass (a block never depends on another).
+    const int64_t run = 4096, n_runs = (int64_t)((nb + run - 1) / run);
+#pragma omp parallel for schedule(static) if (n_runs > 8)
+    for (int64_t r = 0; r < n_runs; ++r) {
+        const uint64_t b0 = (uint64_t)r * run, n = std::min<uint64_t>(run, nb - b0);
+        const uint8_t* s = src + b0 * bytes;
+        float* d = y + b0 * blk;
+        switch (dt) {
+            case F32: std::memcpy(d, s, n * blk * 4); break;
+            case F16: for (uint64_t i = 0; i < n * blk; ++i) d[i] = f16_to_f32(rd16(s + 2 * i)); break;
+            case BF16: for (uint64_t i = 0; i < n * blk; ++i) d[i] = bf16_to_f32(rd16(s + 2 * i)); break;
+            case Q8_0: dequant_q8_0(s, d, n); break;
+            case Q4_K: dequant_q4_k(s, d, n); break;
+            case Q5_K: dequant_q5_k(s, d, n); break;
+            case Q6_K: dequant_q6_k(s, d, n); break;
+        }
     }
 }
 

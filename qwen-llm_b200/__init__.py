@@ -19,7 +19,7 @@ MAX_TARGET_LAYERS = 8
 MAX_DRAFTER_LAYERS = 16
 
 STATUS_NAMES = {0: "OK", 1: "BAD_ARG", 2: "BAD_SHAPE", 3: "UNSUPPORTED", 4: "CUDA", 5: "NO_DEVICE", 6: "OOM", 7: "POISONED",
-                8: "CTX_OVERFLOW", 9: "KV_STATE", 10: "BAD_TOKEN", 11: "SAMPLING", 12: "TIMEOUT", 13: "MISSING_TENSOR"}
+                8: "CTX_OVERFLOW", 9: "KV_STATE", 10: "BAD_TOKEN", 11: "SAMPLING", 12: "TIMEOUT", 13: "MISSING_TENSOR", 14: "ROUTE_STATUS"}
 
 
 class DflError(RuntimeError):
@@ -293,6 +293,10 @@ class Session:
     def fail_next_completion(self):
         lib().dfl_session_fail_next_completion(self.h)
 
+    def probe_wait_timeout(self, polls=256):
+        """Runs the wait probe (a bounded device-side wait that nothing satisfies); raises DflError TIMEOUT."""
+        check(lib().dfl_session_probe_wait_timeout(self.model.h, self.h, C.c_uint32(polls)))
+
     def read_gdn_state(self, gdn_index):
         a = self.model.arch
         ssm = np.zeros(a.gdn_n_v_heads * 128 * 128, dtype=np.float32)
@@ -326,6 +330,12 @@ class Scratch:
         check(lib().dfl_scratch_read_capture(self.h, C.c_uint32(n), _ptr(out), C.c_uint64(out.size)))
         return out
 
+    def read_route(self, n):
+        """Expert ids [n][expert_used_count] the last routed-expert layer of the last verify chose."""
+        out = np.zeros((n, self.model.arch.expert_used_count), dtype=np.int32)
+        check(lib().dfl_scratch_read_route(self.h, C.c_uint32(n), _ptr(out), C.c_uint64(out.size)))
+        return out
+
     def close(self):
         if self.h:
             lib().dfl_scratch_destroy(self.h)
@@ -347,6 +357,23 @@ def packed_verify(model, session, scratch, layer_ids, tokens, start_position, wa
                                   C.c_uint32(n), C.c_uint32(start_position), _ptr(am), _ptr(gap),
                                   _ptr(logits) if want_logits else None))
     return am, gap, logits
+
+
+def packed_verify_n_eff(model, session, scratch, layer_ids, tokens, start_position, n_eff_override=None):
+    """packed_verify with the reference's n_eff_override argument (None = the scratch's block size)."""
+    tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+    ids = _u32(layer_ids)
+    am = np.zeros(max(tokens.size, 1), dtype=np.int32)
+    gap = np.zeros(max(tokens.size, 1), dtype=np.float32)
+    check(lib().dfl_packed_verify_n_eff(model.h, session.h, scratch.h, _ptr(ids) if ids.size else None, C.c_uint32(ids.size), _ptr(tokens),
+                                        C.c_uint32(tokens.size), C.c_uint32(start_position),
+                                        C.c_int32(-1 if n_eff_override is None else n_eff_override), _ptr(am), _ptr(gap), None))
+    return am[:tokens.size], gap[:tokens.size]
+
+
+def restore_partial_n_eff(model, session, scratch, n_keep, start_position, n_eff_override=None):
+    check(lib().dfl_restore_partial_n_eff(model.h, session.h, scratch.h, C.c_uint32(n_keep), C.c_uint32(start_position),
+                                          C.c_int32(-1 if n_eff_override is None else n_eff_override)))
 
 
 class SnapshotIdentity(C.Structure):
@@ -386,7 +413,7 @@ def restore_pre_block(model, session, scratch, start_position):
 def single_token(model, session, scratch, layer_ids, token, position, want_hidden=True):
     ids = _u32(layer_ids)
     logits = np.zeros(model.arch.vocab_size, dtype=np.float32)
-    hidden = np.zeros((scratch.k, model.arch.hidden_size), dtype=np.float32) if (want_hidden and ids.size) else None
+    hidden = np.zeros((ids.size, model.arch.hidden_size), dtype=np.float32) if (want_hidden and ids.size) else None
     check(lib().dfl_single_token(model.h, session.h, scratch.h, _ptr(ids) if ids.size else None, C.c_uint32(ids.size),
                                  C.c_int32(int(token)), C.c_uint32(position), _ptr(logits),
                                  _ptr(hidden) if hidden is not None else None))

@@ -42,7 +42,7 @@ enum DevErr : int {
     DEV_ERR_WAIT_DRAIN = 3,   // exit path gave up waiting for copies in flight
     DEV_ERR_NONFINITE = 4,    // NaN / Inf met where a finite value is required
     DEV_ERR_OVERFLOW = 5,     // activation outside the fp16 operand range
-    DEV_ERR_WAIT_FLAG = 6     // test hook: a flag nobody sets
+    DEV_ERR_WAIT_FLAG = 6     // the wait probe (dfl_session_probe_wait_timeout): a barrier nobody arrives at
 };
 
 #ifdef __CUDACC__
@@ -78,13 +78,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // (about a second with the back-off), records why in *err and returns false, so a
 // lost copy or a logic error ends the kernel instead of hanging the GPU.
 constexpr uint32_t kWaitPolls = 1u << 22;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* err, int code) {
-    for (uint32_t it = 0; it < kWaitPolls; ++it) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* err, int code, uint32_t polls) {
+    for (uint32_t it = 0; it < polls; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (it > 128) __nanosleep(200);
     }
     atomicCAS(err, 0, code);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* err, int code) {
+    return mbar_wait_limit(bar, parity, err, code, kWaitPolls);
 }
 // 1-D bulk async copy global -> shared, completion counted on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16 bytes.

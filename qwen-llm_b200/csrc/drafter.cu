@@ -611,11 +611,24 @@ dfl_status dsession_snapshot_write(dfl_dsession* ds, uint8_t* dst, uint32_t* col
     *cols_out = cols;
     return DFL_OK;
 }
-dfl_status dsession_snapshot_read(dfl_dsession* ds, const uint8_t* src, uint32_t cols, uint64_t n_bytes) {
+// what a drafter section depends on besides its column count: layer count, K/V row width, window
+void dsession_identity(const dfl_dsession* ds, uint32_t out[3]) {
+    const dfl_dflash_config& c = ds->d->cfg;
+    out[0] = c.n_layer;
+    out[1] = c.n_kv_heads * c.head_dim;
+    out[2] = c.swa_window;
+}
+dfl_status dsession_snapshot_validate(const dfl_dsession* ds, uint32_t cols, uint64_t n_bytes) {
     const dfl_dflash_config& c = ds->d->cfg;
     const uint64_t kv_dim = (uint64_t)c.n_kv_heads * c.head_dim, rows = (uint64_t)cols * kv_dim * 4;
     if (cols > ds->ctx_capacity) return fail(DFL_ERR_CTX_OVERFLOW, "snapshot: drafter context tail exceeds the session's capacity");
     if (n_bytes != (uint64_t)cols * 4 + (uint64_t)c.n_layer * 2 * rows) return fail(DFL_ERR_BAD_SHAPE, "snapshot: drafter section length mismatch");
+    return DFL_OK;
+}
+dfl_status dsession_snapshot_read(dfl_dsession* ds, const uint8_t* src, uint32_t cols, uint64_t n_bytes) {
+    const dfl_dflash_config& c = ds->d->cfg;
+    const uint64_t kv_dim = (uint64_t)c.n_kv_heads * c.head_dim, rows = (uint64_t)cols * kv_dim * 4;
+    DFL_CHECK(dsession_snapshot_validate(ds, cols, n_bytes));
     ds->ctx_len = ds->ready = ds->pending_base = 0;
     ds->pos_host.assign(reinterpret_cast<const uint32_t*>(src), reinterpret_cast<const uint32_t*>(src) + cols);
     if (cols) DFL_CUDA(cudaMemcpyAsync(ds->pos_ctx_dev, ds->pos_host.data(), (size_t)cols * 4, cudaMemcpyHostToDevice, ds->st));

@@ -46,7 +46,11 @@ dfl_status dfl_prefill(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
     if (!sc || sc->m != m || !ids || n == 0) return fail(DFL_ERR_BAD_ARG, "prefill: bad argument");
     if (s->kv_n_pos != start_position) return fail(DFL_ERR_KV_STATE, "prefill: kv_n_pos != start_position");
     if ((uint64_t)start_position + n > s->kv_capacity) return fail(DFL_ERR_KV_STATE, "prefill: prompt does not fit the KV capacity");
-    if (n_layer_ids > sc->k_layers) return fail(DFL_ERR_BAD_SHAPE, "prefill: capture layer count exceeds the scratch");
+    if (n_layer_ids > sc->k_layers || (n_layer_ids && !layer_ids)) return fail(DFL_ERR_BAD_SHAPE, "prefill: capture layer count exceeds the scratch");
+    for (uint32_t k = 0; k < n_layer_ids; ++k)
+        if (layer_ids[k] >= m->arch.n_layer) return fail(DFL_ERR_BAD_SHAPE, "prefill: capture layer id out of range");
+    // the drafter consumes every slot of a captured row: a shorter id list would feed it slots no layer wrote
+    if (feed_drafter && n_layer_ids != sc->k_layers) return fail(DFL_ERR_BAD_SHAPE, "prefill: feeding the drafter needs one capture layer per scratch slot");
     for (uint64_t i = 0; i < n; ++i)
         if (ids[i] < 0 || (uint32_t)ids[i] >= m->arch.vocab_size) return fail(DFL_ERR_BAD_TOKEN, "prefill: token id out of range");
     const uint64_t KH = (uint64_t)sc->k_layers * m->arch.hidden_size;

@@ -274,9 +274,9 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
                 if (moe_route_lists_fused(E)) {
                     DFL_CHECK(launch_moe_route_lists(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg,
                                                      sc->route_idx, (int)m->ep_e0, En, Fe / TILE_R, Fs / TILE_R, min_tiles, sc->moe_tile_map,
-                                                     sc->moe_n_tiles, Fe / TILE_K, 1, kb_map, sc->moe_n_tiles + 1, gemm_ts_kc(), down_tiles, down_max));
+                                                     sc->moe_n_tiles, Fe / TILE_K, 1, kb_map, sc->moe_n_tiles + 1, gemm_ts_kc(), down_tiles, down_max, s->err));
                 } else {
-                    DFL_CHECK(launch_moe_route(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
+                    DFL_CHECK(launch_moe_route(st, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx, s->err));
                     DFL_CHECK(launch_moe_tiles(st, sc->route_w, (int)n, E, (int)m->ep_e0, En, Fe / TILE_R, Fs / TILE_R, min_tiles, sc->moe_tile_map,
                                                sc->moe_n_tiles, Fe / TILE_K, 1, kb_map, sc->moe_n_tiles + 1, gemm_ts_kc(), down_tiles, down_max));
                 }
@@ -287,7 +287,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             } else {
                 DFL_CHECK(fork_side());
                 DFL_CHECK(launch_small_matmul(side, L.router_w, sc->xn, (int)H, (int)n, H, E + 1, ep_norm, sc->route_logits, E + 1));
-                DFL_CHECK(launch_moe_route(side, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx));
+                DFL_CHECK(launch_moe_route(side, sc->route_logits, E + 1, E, (int)a.expert_used_count, (int)n, sc->route_w, sc->route_sg, sc->route_idx, s->err));
                 DFL_CHECK(launch_group(st, GU, sc->acts_h, sc->part, ep_norm, s->err));
                 DFL_CHECK(join_side());
             }
@@ -350,7 +350,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         }
         float* cap = nullptr;
         for (uint32_t k = 0; k < n_ids; ++k)
-            if (layer_ids[k] == il) cap = sc->capture + (uint64_t)k * H;
+            if (layer_ids[k] == il) { cap = sc->capture + (uint64_t)k * H; break; }   // the kernel fills the first slot of this layer
         const bool last = il + 1 == a.n_layer;
         const float* next_w = last ? m->out_norm_w : m->layers[il + 1].attn_norm_w;
         const bool next_gdn = !last && !m->layers[il + 1].is_attn;
@@ -382,6 +382,7 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
     DFL_CHECK(join_side2());
     s->kv_n_pos = start + n;
     sc->last_n = n;
+    sc->last_n_verify = n;
     sc->last_start = start;
     sc->have_block = true;
     return DFL_OK;
@@ -836,6 +837,57 @@ dfl_status dfl_scratch_read_capture(const dfl_scratch* sc, uint32_t n, float* ou
     return DFL_OK;
 }
 
+
+dfl_status dfl_scratch_read_route(const dfl_scratch* sc, uint32_t n, int32_t* idx_out, uint64_t n_idx) {
+    if (!sc || !idx_out) return fail(DFL_ERR_BAD_ARG, "read_route: null argument");
+    const dfl_arch& a = sc->m->arch;
+    if (a.expert_count == 0) return fail(DFL_ERR_UNSUPPORTED, "read_route: the model has no routed experts");
+    if (n > MAX_ROWS || n_idx != (uint64_t)n * a.expert_used_count) return fail(DFL_ERR_BAD_SHAPE, "read_route: size");
+    DFL_CHECK(use_device(sc->m->device));
+    DFL_CUDA(cudaDeviceSynchronize());
+    DFL_CUDA(cudaMemcpy(idx_out, sc->route_idx, n_idx * 4, cudaMemcpyDeviceToHost));
+    return DFL_OK;
+}
+
+// The effective chain length of a call on a scratch made for block_size rows (metal_dflash.rs:9063-9094).
+static dfl_status resolve_n_eff(const dfl_scratch* sc, int32_t n_eff_override, const char* what, uint32_t* n_out) {
+    if (!sc) return fail(DFL_ERR_BAD_ARG, std::string(what) + ": null scratch");
+    const uint32_t n = n_eff_override < 0 ? sc->block_size : (uint32_t)n_eff_override;
+    if (n < 1 || n > sc->block_size)
+        return fail(DFL_ERR_BAD_SHAPE, std::string(what) + ": n_eff_override resolves to n=" + std::to_string(n) + " which must be in [1, n_block=" +
+                                           std::to_string(sc->block_size) + "]");
+    *n_out = n;
+    return DFL_OK;
+}
+
+dfl_status dfl_packed_verify_n_eff(const dfl_model* m, dfl_session* s, dfl_scratch* sc, const uint32_t* layer_ids, uint32_t n_layer_ids,
+                                   const int32_t* tokens, uint32_t n_tokens, uint32_t start_position, int32_t n_eff_override,
+                                   int32_t* argmax_out, float* gap_out, float* logits_host) {
+    uint32_t n = 0;
+    DFL_CHECK(resolve_n_eff(sc, n_eff_override, "packed_verify", &n));
+    if (n_tokens != n) return fail(DFL_ERR_BAD_SHAPE, "packed_verify: tokens.len()=" + std::to_string(n_tokens) + " != n_eff=" + std::to_string(n));
+    return dfl_packed_verify(m, s, sc, layer_ids, n_layer_ids, tokens, n, start_position, argmax_out, gap_out, logits_host);
+}
+
+__global__ void wait_probe_kernel(int* err, uint32_t polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        // nobody arrives: the wait runs out after `polls` polls, records why and the kernel returns normally
+        mbar_wait_limit(&bar, 0, err, DEV_ERR_WAIT_FLAG, polls);
+    }
+}
+
+dfl_status dfl_session_probe_wait_timeout(const dfl_model* m, dfl_session* s, uint32_t polls) {
+    DFL_CHECK(session_guard(m, s, "probe_wait_timeout"));
+    if (polls < 1 || polls > (1u << 16)) return fail(DFL_ERR_BAD_ARG, "probe_wait_timeout: polls must be in [1, 65536]");
+    wait_probe_kernel<<<1, 32, 0, s->st>>>(s->err, polls);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return completion_check(s);
+}
+
 }  // extern "C"
 
 namespace dfl {
@@ -874,11 +926,22 @@ dfl_status dfl_restore_partial(const dfl_model* m, dfl_session* s, dfl_scratch* 
     return completion_check(s);
 }
 
+dfl_status dfl_restore_partial_n_eff(const dfl_model* m, dfl_session* s, dfl_scratch* sc, uint32_t n_keep, uint32_t start_position,
+                                     int32_t n_eff_override) {
+    uint32_t n = 0;
+    DFL_CHECK(resolve_n_eff(sc, n_eff_override, "restore_partial", &n));
+    // the same n_eff as the verify this call undoes (metal_dflash.rs:15662-15666)
+    if (sc->have_block && n != sc->last_n_verify) return fail(DFL_ERR_BAD_SHAPE, "restore_partial: n_eff differs from the preceding verify's");
+    if (n_keep < 1 || n_keep > n) return fail(DFL_ERR_BAD_SHAPE, "restore_partial: n_keep must be in [1, n_eff=" + std::to_string(n) + "]");
+    return dfl_restore_partial(m, s, sc, n_keep, start_position);
+}
+
 // ---- session snapshots (SessionSnapshot, metal_forward/session.rs:13-94) ------------------------------------------
 struct SnapshotHeader {
     uint32_t magic, header_bytes;
     dfl_snapshot_identity id;
     uint32_t prefix_len, drafter_cols;
+    uint32_t drafter_id[3], _pad;   // drafter layer count, K/V row width, sliding window (zeros without a drafter section)
     uint64_t kv_bytes /* each of K and V */, conv_bytes, state_bytes, drafter_bytes;
 };
 static constexpr uint32_t kSnapshotMagic = 0x534C4644;   // "DFLS"
@@ -931,6 +994,7 @@ dfl_status dfl_session_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession
     DFL_CHECK(completion_check(s));
     if (ds) {
         h.drafter_bytes = dsession_snapshot_bytes(ds);
+        dsession_identity(ds, h.drafter_id);
         DFL_CHECK(dsession_snapshot_write(ds, p, &h.drafter_cols));
         p += h.drafter_bytes;
     }
@@ -958,6 +1022,12 @@ dfl_status dfl_session_restore_snapshot(const dfl_model* m, dfl_session* s, dfl_
         n_bytes != sizeof(h) + 2 * h.kv_bytes + h.conv_bytes + h.state_bytes + h.drafter_bytes)
         return fail(DFL_ERR_BAD_SHAPE, "snapshot section length mismatch");
     if (ds && h.drafter_bytes == 0 && h.prefix_len > 0) return fail(DFL_ERR_BAD_ARG, "restore_snapshot: the snapshot carries no drafter context");
+    if (ds) {   // before the first copy: a refused blob changes nothing
+        uint32_t did[3];
+        dsession_identity(ds, did);
+        if (h.drafter_bytes && memcmp(did, h.drafter_id, sizeof(did)) != 0) return fail(DFL_ERR_BAD_SHAPE, "snapshot drafter identity mismatch");
+        DFL_CHECK(dsession_snapshot_validate(ds, h.drafter_cols, h.drafter_bytes));
+    }
     const uint8_t* p = (const uint8_t*)blob + sizeof(h);
     for (int which = 0; which < 2; ++which)
         for (size_t ai = 0; ai < s->k_cache.size(); ++ai, p += per_layer)
@@ -993,8 +1063,8 @@ dfl_status dfl_single_token(const dfl_model* m, dfl_session* s, dfl_scratch* sc,
     dfl_status st = verify_core(m, s, sc, layer_ids, n_layer_ids, &token, 1, position, true);
     if (st != DFL_OK) { s->poisoned = true; return st; }
     if (logits_host) cudaMemcpyAsync(logits_host, sc->logits, (size_t)m->arch.vocab_size * 4, cudaMemcpyDeviceToHost, s->st);
-    if (hidden_host && n_layer_ids)
-        cudaMemcpyAsync(hidden_host, sc->capture, (size_t)sc->k_layers * m->arch.hidden_size * 4, cudaMemcpyDeviceToHost, s->st);
+    if (hidden_host && n_layer_ids)   // [n_layer_ids][H]: the caller's slots, whatever the scratch was sized for
+        cudaMemcpyAsync(hidden_host, sc->capture, (size_t)n_layer_ids * m->arch.hidden_size * 4, cudaMemcpyDeviceToHost, s->st);
     return completion_check(s);
 }
 

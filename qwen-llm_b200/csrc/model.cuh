@@ -147,6 +147,7 @@ struct dfl_scratch {
     float* pinned_f = nullptr;    // [16] gaps
     float* pinned_logits = nullptr;  // [block][vocab], made on first use by the sampled outer loop
     uint32_t last_n = 0, last_start = 0;
+    uint32_t last_n_verify = 0;   // rows of the last verify (last_n shrinks to n_keep after a partial restore)
     bool have_block = false;
     uint64_t part_floats = 0;
     std::vector<void*> allocs;
@@ -162,5 +163,7 @@ dfl_status session_guard(const dfl_model* m, dfl_session* s, const char* what);
 uint64_t dsession_snapshot_bytes(const dfl_dsession* ds);
 dfl_status dsession_snapshot_write(dfl_dsession* ds, uint8_t* dst, uint32_t* cols_out);
 dfl_status dsession_snapshot_read(dfl_dsession* ds, const uint8_t* src, uint32_t cols, uint64_t n_bytes);
+dfl_status dsession_snapshot_validate(const dfl_dsession* ds, uint32_t cols, uint64_t n_bytes);
+void dsession_identity(const dfl_dsession* ds, uint32_t out[3]);
 const dfl_model* dsession_target(const dfl_dsession* ds);
 }  // namespace dfl

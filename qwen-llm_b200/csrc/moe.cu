@@ -16,7 +16,7 @@ constexpr int MOE_MAX_EXPERTS = 1024;
 
 // routing of one row by one warp; p = n_expert floats of shared memory of its own
 __device__ __forceinline__ void moe_route_row(float* p, int tok, int lane, const float* logits, int ld, int n_expert, int n_used, int n_rows,
-                                              float* route_w, float* shared_gate, int32_t* route_idx) {
+                                              float* route_w, float* shared_gate, int32_t* route_idx, int* err) {
     float* wrow = route_w + (uint64_t)tok * n_expert;
     for (int i = lane; i < n_expert; i += 32) wrow[i] = 0.f;
     if (tok >= n_rows) {
@@ -26,7 +26,21 @@ __device__ __forceinline__ void moe_route_row(float* p, int tok, int lane, const
     }
     const float* x = logits + (uint64_t)tok * ld;
     float mx = -INFINITY;
-    for (int i = lane; i < n_expert; i += 32) mx = fmaxf(mx, x[i]);
+    bool bad = false;
+    for (int i = lane; i <= n_expert; i += 32) {   // the shared expert's gate logit (index n_expert) included
+        const float v = x[i];
+        bad |= !isfinite(v);
+        if (i < n_expert) mx = fmaxf(mx, v);
+    }
+    if (__any_sync(0xffffffffu, bad)) {
+        // route status NONFINITE (kernels/moe.metal:355-360): the row routes nowhere and the error word poisons the session
+        if (lane == 0) {
+            atomicCAS(err, 0, DEV_ERR_NONFINITE);
+            shared_gate[tok] = 0.f;
+        }
+        for (int j = lane; j < n_used; j += 32) route_idx[tok * n_used + j] = -1;
+        return;
+    }
     mx = warp_max(mx);
     float sum = 0.f;
     for (int i = lane; i < n_expert; i += 32) {
@@ -70,17 +84,17 @@ __device__ __forceinline__ void moe_route_row(float* p, int tok, int lane, const
 
 __global__ void __launch_bounds__(32) moe_route_kernel(const float* logits, int ld, int n_expert, int n_used, int n_rows,
                                                        float* route_w, float* shared_gate,
-                                                       int32_t* route_idx) {
+                                                       int32_t* route_idx, int* err) {
     pdl_prologue();
     __shared__ float p[MOE_MAX_EXPERTS];
-    moe_route_row(p, blockIdx.x, threadIdx.x, logits, ld, n_expert, n_used, n_rows, route_w, shared_gate, route_idx);
+    moe_route_row(p, blockIdx.x, threadIdx.x, logits, ld, n_expert, n_used, n_rows, route_w, shared_gate, route_idx, err);
 }
 
 dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_expert, int n_used, int n_rows, float* route_w,
-                            float* shared_gate, int32_t* route_idx) {
+                            float* shared_gate, int32_t* route_idx, int* err) {
     if (n_expert < 1 || n_expert > MOE_MAX_EXPERTS || n_used < 1 || n_used > 32 || n_used > n_expert)
         return fail(DFL_ERR_UNSUPPORTED, "moe_route: expert_count must be in [1, 1024] and expert_used_count in [1, 32]");
-    launch_kf(16, moe_route_kernel, dim3(MAX_ROWS), dim3(32), 0, st, logits, ld, n_expert, n_used, n_rows, route_w, shared_gate, route_idx);
+    launch_kf(16, moe_route_kernel, dim3(MAX_ROWS), dim3(32), 0, st, logits, ld, n_expert, n_used, n_rows, route_w, shared_gate, route_idx, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -167,11 +181,11 @@ __global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_tiles_kernel(const float*
 }
 // routing of the block's rows (warps 0-15, one row each) and the lists in one launch
 __global__ void __launch_bounds__(MOE_MAX_EXPERTS) moe_route_lists_kernel(const float* logits, int ld, int n_used, int n_rows, float* route_w,
-                                                                          float* shared_gate, int32_t* route_idx, const MoeListArgs a) {
+                                                                          float* shared_gate, int32_t* route_idx, int* err, const MoeListArgs a) {
     pdl_prologue();
     extern __shared__ float p_rows[];   // [16][n_expert]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp < MAX_ROWS) moe_route_row(p_rows + warp * a.n_expert, warp, lane, logits, ld, a.n_expert, n_used, n_rows, route_w, shared_gate, route_idx);
+    if (warp < MAX_ROWS) moe_route_row(p_rows + warp * a.n_expert, warp, lane, logits, ld, a.n_expert, n_used, n_rows, route_w, shared_gate, route_idx, err);
     __syncthreads();   // the rows' route weights (global, written by this CTA) are complete
     moe_build_lists(route_w, a);
 }
@@ -201,12 +215,12 @@ bool moe_route_lists_fused(int n_expert) { return (size_t)MAX_ROWS * n_expert * 
 dfl_status launch_moe_route_lists(cudaStream_t st, const float* logits, int ld, int n_expert, int n_used, int n_rows, float* route_w,
                                   float* shared_gate, int32_t* route_idx, int e0, int n_local, int tiles_per_expert, int shared_tiles,
                                   int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,
-                                  int32_t* n_kb, int kc, int down_tiles, int max_splits) {
+                                  int32_t* n_kb, int kc, int down_tiles, int max_splits, int* err) {
     if (n_expert < 1 || n_used < 1 || n_used > 32 || n_used > n_expert || !moe_route_lists_fused(n_expert) || n_local > MOE_MAX_EXPERTS ||
         shared_tiles > MOE_MAX_EXPERTS)
         return fail(DFL_ERR_UNSUPPORTED, "moe_route_lists: geometry");
     launch_kf(16, moe_route_lists_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), (size_t)MAX_ROWS * n_expert * 4, st, logits, ld, n_used, n_rows, route_w,
-              shared_gate, route_idx,
+              shared_gate, route_idx, err,
               moe_list_args(n_expert, e0, n_local, tiles_per_expert, shared_tiles, min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb,
                             kc, down_tiles, max_splits));
     count_launch();

@@ -106,14 +106,15 @@ dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k);
 // Softmax + top-k routing of n_rows tokens over n_expert experts; logits[tok][n_expert] is the extra router row of
 // the shared expert's gate.  Writes route_w[16][n_expert] (zeros for experts not chosen), shared_gate[16],
 // route_idx[16][n_used].
+// A NaN / Inf logit in a row leaves that row unrouted and sets DEV_ERR_NONFINITE in *err (the reference's NONFINITE route status).
 dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_expert, int n_used, int n_rows, float* route_w,
-                            float* shared_gate, int32_t* route_idx);
+                            float* shared_gate, int32_t* route_idx, int* err);
 // routing and the lists below in one launch (moe_route_lists_fused says whether the expert count allows it)
 bool moe_route_lists_fused(int n_expert);
 dfl_status launch_moe_route_lists(cudaStream_t st, const float* logits, int ld, int n_expert, int n_used, int n_rows, float* route_w,
                                   float* shared_gate, int32_t* route_idx, int e0, int n_local, int tiles_per_expert, int shared_tiles,
                                   int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,
-                                  int32_t* n_kb, int kc, int down_tiles, int max_splits);
+                                  int32_t* n_kb, int kc, int down_tiles, int max_splits, int* err);
 // row tiles of the gate|up matrix that belong to experts some row of the block chose (plus the shared expert)
 dfl_status launch_moe_tiles(cudaStream_t st, const float* route_w, int n_rows, int n_expert, int e0, int n_local, int tiles_per_expert,
                             int shared_tiles, int min_tiles, int32_t* tile_map, int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map,

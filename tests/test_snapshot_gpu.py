@@ -40,7 +40,7 @@ def test_restored_session_continues_bitwise(world, all_swa):
     carry = int(np.argmax(logits))
     blob = pkg.session_snapshot(gm, sess, ds)
     ident = pkg.snapshot_identity(gm, sess)
-    assert ident.layout_version == 1 and ident.kv_storage_kind == 1 and ident.kv_bytes_per_token == 2 * ident.kv_dim_elements
+    assert ident.layout_version == 2 and ident.kv_storage_kind == 1 and ident.kv_bytes_per_token == 2 * ident.kv_dim_elements
     # the drafter tail: all 37 columns, or the last swa_window (8) of an all-sliding-window drafter
     kv_dim = cfg.n_kv_heads * cfg.head_dim
     cols = 8 if all_swa else 37
@@ -70,7 +70,19 @@ def test_restored_session_continues_bitwise(world, all_swa):
         pkg.session_restore_snapshot(gm, pkg.Session(gm, 128), None, bad)                         # magic
     with pytest.raises(pkg.DflError):
         pkg.session_restore_snapshot(gm, pkg.Session(gm, 128), pkg.DSession(gd, 128), no_drafter)  # no drafter context inside
+    fresh = pkg.Session(gm, 128)
+    before = [np.concatenate(fresh.read_gdn_state(g)).tobytes() for g in range(2)]
     with pytest.raises(pkg.DflError) as e:
-        pkg.session_restore_snapshot(gm, pkg.Session(gm, 128), pkg.DSession(gd, 4), blob)         # drafter tail does not fit
+        pkg.session_restore_snapshot(gm, fresh, pkg.DSession(gd, 4), blob)                        # drafter tail does not fit
     assert e.value.name == "CTX_OVERFLOW"
+    # the refusal came before the first copy: the target session is as it was
+    assert fresh.kv_n_pos == 0 and not fresh.poisoned
+    assert [np.concatenate(fresh.read_gdn_state(g)).tobytes() for g in range(2)] == before
+    # a drafter of another shape (one more layer) does not accept this drafter's section
+    cfg3 = modelgen.tiny_dflash_config(arch, n_layer=3, swa=[1, 1, 1] if all_swa else [1, 1, 0])
+    gd3 = pkg.Drafter(gm, cfg3, modelgen.drafter_tensors(arch, cfg3, seed=4))
+    with pytest.raises(pkg.DflError):
+        pkg.session_restore_snapshot(gm, fresh, pkg.DSession(gd3, 128), blob)
+    assert fresh.kv_n_pos == 0
+    gd3.close()
     gd.close()

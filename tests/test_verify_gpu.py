@@ -318,3 +318,104 @@ def test_repeated_passes_are_bitwise_reproducible():
         assert out == ref, f"iteration {it} differs"
         sess.close(); scr.close()
     gm.close()
+
+
+def test_capture_of_a_layer_listed_twice_fills_both_slots(tiny):
+    # a drafter whose tap layers repeat (short targets) reads every slot: both must hold the layer's rows of THIS block
+    arch, om, gm = tiny
+    rng = np.random.default_rng(23)
+    one, sone = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 1)
+    two, stwo = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 3)
+    pos = 0
+    for n in (16, 9):    # two different blocks: a slot that is skipped would keep the first block's rows
+        toks = rng.integers(0, arch.vocab_size, size=n)
+        pkg.packed_verify(gm, one, sone, [2], toks, pos)
+        pkg.packed_verify(gm, two, stwo, [2, 2, 1], toks, pos)
+        want = sone.read_capture(n)[:, 0]
+        got = stwo.read_capture(n)
+        assert got[:, 0].tobytes() == want.tobytes() and got[:, 1].tobytes() == want.tobytes()
+        assert got[:, 2].tobytes() != want.tobytes()
+        pos += n
+    for x in (one, sone, two, stwo):
+        x.close()
+
+
+def test_n_eff_override_forms_of_verify_and_restore(tiny):
+    # metal_dflash.rs:9055-9094, :15655-15682: None = the scratch's block size; otherwise tokens.len() == n_eff, and
+    # the restore is given the same n_eff as the verify it undoes
+    arch, om, gm = tiny
+    rng = np.random.default_rng(29)
+    toks = rng.integers(0, arch.vocab_size, size=16)
+    a, sa = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 0)
+    b, sb = pkg.Session(gm, 64), pkg.Scratch(gm, 16, 0)
+    am_a, _ = pkg.packed_verify_n_eff(gm, a, sa, [], toks, 0, None)
+    am_b, _, _ = pkg.packed_verify(gm, b, sb, [], toks, 0)
+    assert np.array_equal(am_a, am_b)
+    with pytest.raises(pkg.DflError) as e:
+        pkg.packed_verify_n_eff(gm, a, sa, [], toks[:9], 16, None)       # None means 16 tokens
+    assert e.value.name == "BAD_SHAPE" and "n_eff" in str(e.value)
+    for bad in (0, 17):
+        with pytest.raises(pkg.DflError) as e:
+            pkg.packed_verify_n_eff(gm, a, sa, [], toks[:9], 16, bad)
+        assert e.value.name == "BAD_SHAPE" and "n_block=16" in str(e.value)
+    am_a, _ = pkg.packed_verify_n_eff(gm, a, sa, [], toks[:9], 16, 9)
+    am_b, _, _ = pkg.packed_verify(gm, b, sb, [], toks[:9], 16)
+    assert np.array_equal(am_a, am_b)
+    with pytest.raises(pkg.DflError):
+        pkg.restore_partial_n_eff(gm, a, sa, 4, 16, None)                # the verify ran with n_eff = 9
+    with pytest.raises(pkg.DflError):
+        pkg.restore_partial_n_eff(gm, a, sa, 10, 16, 9)                  # n_keep beyond n_eff
+    pkg.restore_partial_n_eff(gm, a, sa, 4, 16, 9)
+    pkg.restore_partial(gm, b, sb, 4, 16)
+    assert a.kv_n_pos == b.kv_n_pos == 20
+    for gi in range(3):
+        assert np.concatenate(a.read_gdn_state(gi)).tobytes() == np.concatenate(b.read_gdn_state(gi)).tobytes()
+    for x in (a, sa, b, sb):
+        x.close()
+
+
+def test_a_bounded_device_wait_that_runs_out_poisons_the_session(tiny):
+    # the give-up path of the device-side waits: the kernel records why and returns, the completion check maps the
+    # error word to TIMEOUT, the session is poisoned, the word is cleared and other sessions are unaffected
+    arch, om, gm = tiny
+    a, sa = pkg.Session(gm, 32), pkg.Scratch(gm, 16, 0)
+    pkg.packed_verify(gm, a, sa, [], [1, 2, 3], 0)
+    with pytest.raises(pkg.DflError) as e:
+        a.probe_wait_timeout(polls=200)
+    assert e.value.name == "TIMEOUT"
+    assert a.poisoned
+    with pytest.raises(pkg.DflError) as e:
+        pkg.packed_verify(gm, a, sa, [], [4], 3)
+    assert e.value.name == "POISONED"
+    b = pkg.Session(gm, 32)
+    am, _, _ = pkg.packed_verify(gm, b, sa, [], [1, 2, 3], 0)             # the next session works; same scratch
+    assert am.shape == (3,) and not b.poisoned
+    for x in (a, b, sa):
+        x.close()
+
+
+def test_a_non_finite_router_logit_raises_the_route_status_and_poisons():
+    # kernels/moe.metal:355-360 (route status NONFINITE) + metal_forward/mod.rs:2161-2170 (poisoning): an Inf in the
+    # router weights reaches the routing kernel as a non-finite logit
+    arch = modelgen.tiny_arch(expert_count=8, expert_used_count=2, expert_feed_forward_length=256,
+                              expert_shared_feed_forward_length=256)
+    T = modelgen.target_tensors(arch, seed=11)
+    good = pkg.Model(arch, T)
+    bad_T = []
+    for (name, dtype, shape, raw) in T:
+        if name == "blk.1.ffn_gate_inp.weight":
+            w = raw.view(np.float32).copy()
+            w[5] = np.inf
+            raw = w.view(np.uint8)
+        bad_T.append((name, dtype, shape, raw))
+    bad = pkg.Model(arch, bad_T)
+    toks = np.arange(1, 9)
+    s1, c1 = pkg.Session(bad, 32), pkg.Scratch(bad, 16, 0)
+    with pytest.raises(pkg.DflError) as e:
+        pkg.packed_verify(bad, s1, c1, [], toks, 0)
+    assert e.value.name == "ROUTE_STATUS" and s1.poisoned
+    s2, c2 = pkg.Session(good, 32), pkg.Scratch(good, 16, 0)
+    am, _, _ = pkg.packed_verify(good, s2, c2, [], toks, 0)
+    assert not s2.poisoned and (am >= 0).all()
+    for x in (s1, c1, s2, c2, good, bad):
+        x.close()

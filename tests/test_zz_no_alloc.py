@@ -26,13 +26,26 @@ def _run_static(torch, x, ld=None):
     buf[:, :vocab] = torch.from_numpy(x).to("cuda:0")
     am = torch.full((n,), -12345, dtype=torch.int32, device="cuda:0")
     gap = torch.full((n,), -1.0, dtype=torch.float32, device="cuda:0")
-    torch.cuda.synchronize()
-    before = torch.cuda.memory_allocated(0)
     st = torch.cuda.current_stream(0).cuda_stream
+    if not _run_static.warm:
+        # the first call on a device looks up the scratch array's address and may make the driver load the library's
+        # kernels; the witness below is taken on calls after it, as a caller with a fixed budget would make them
+        pkg.argmax_top2_static(buf.data_ptr(), n, vocab, ld, am.data_ptr(), gap.data_ptr(), stream=st, device=0)
+        _run_static.warm = True
+    torch.cuda.synchronize()
+    # device-level free bytes (cudaMemGetInfo): sees a cudaMalloc made by any library in the process, which torch's own
+    # allocator statistics would not
+    free_before, _ = torch.cuda.mem_get_info(0)
+    torch_before = torch.cuda.memory_allocated(0)
     pkg.argmax_top2_static(buf.data_ptr(), n, vocab, ld, am.data_ptr(), gap.data_ptr(), stream=st, device=0)
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated(0) == before
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after == free_before, "device memory was allocated or freed during the call"
+    assert torch.cuda.memory_allocated(0) == torch_before
     return am.cpu().numpy(), gap.cpu().numpy()
+
+
+_run_static.warm = False
 
 
 @pytest.mark.gpu
