@@ -22,6 +22,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 PROMPT = 512
+NEAR_TIE_MARGIN = 1e-4        # committed rows whose top-1 / top-2 gap is smaller are counted as near ties
 PATTERN = [3, 3, 4, 3, 4]     # accepted drafts per step -> emitted 4,4,5,4,5 (mean 4.4)
 KV_CAP = 4096
 
@@ -128,34 +129,54 @@ def run_schedule(w, cont, pattern, warm_steps, steps, runs_drafter=True):
             "restore_calls": st.restore_calls, "accepted": int(st.accepted_drafts)}
 
 
-def cpu_sample(arch, tensors, threads_hint=None):
-    """Times the oracle on a 4-layer (3 GDN + 1 attention) + lm_head slice with the real widths.
-    Returns (seconds per full 32-layer verify of 16 rows, threads, description)."""
-    import modelgen
-    import orc
-    a4 = _pkg().Arch()
-    for f, _ in arch._fields_:
-        setattr(a4, f, getattr(arch, f))
-    a4.n_layer = 4
-    om = modelgen.OracleModel(a4, tensors)
-    st = om.new_state(64, True)
-    rng = np.random.default_rng(0)
-    toks = rng.integers(0, arch.vocab_size, size=17)
-    om.single_token(st, toks[0], 0, (), want_logits=True)          # dequantises every weight once (not timed)
-    t0 = time.perf_counter()
-    for i in range(1, 9):
-        om.single_token(st, toks[i], i, (), want_logits=False)
-    t_layers = (time.perf_counter() - t0) / 8                       # 4 layers, one row
-    t0 = time.perf_counter()
-    for i in range(9, 13):
-        om.single_token(st, toks[i], i, (), want_logits=True)
-    t_full = (time.perf_counter() - t0) / 4
-    t_head = max(t_full - t_layers, 0.0)
-    per_verify = 16 * (t_layers * (arch.n_layer / 4.0) + t_head)
-    threads = int(orc.lib().orc_num_threads())
-    desc = ("oracle port, 12 single-token passes through a 4-layer (3 GDN + 1 attention) + lm_head slice with config-2 widths; "
-            "scaled to 32 layers x 16 rows; drafter not included")
-    return per_verify, threads, desc
+WORKLOAD_C2 = ("c2: 9B-class hybrid Q4_K_M target (32 layers, GDN:attn 3:1, H 4096, FFN 12288, V 151936) + 5-layer bf16 DFlash drafter, "
+               "greedy, batch 1, prompt 512, block 16; replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step")
+
+
+class CpuBlockSample:
+    """The reference's CPU path on a bounded sample of the config-2 verify: one block = 16 consecutive single-token
+    passes (forward.rs:173-220) through a 4-layer slice (3 GDN + 1 attention) with the real widths, plus the lm_head
+    for every row.  `step()` runs and times one such block; `full_step_s(t)` scales a measured block time to the whole
+    32-layer model: (layers part) x 32 / 4 + (head part)."""
+
+    def __init__(self, arch, tensors):
+        import modelgen
+        import orc
+        L = orc.lib()
+        cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        self.threads = int(L.orc_set_num_threads(int(cores)))   # all the cores this process may use, whatever OMP_NUM_THREADS says
+        a4 = _pkg().Arch()
+        for f, _ in arch._fields_:
+            setattr(a4, f, getattr(arch, f))
+        a4.n_layer = 4
+        self.arch, self.n_layer_full = arch, arch.n_layer
+        self.om = modelgen.OracleModel(a4, tensors)
+        self.rng = np.random.default_rng(0)
+        st = self.om.new_state(64, True)
+        self.om.single_token(st, 1, 0, (), want_logits=True)          # dequantises every weight once (not timed)
+        # the layers' share of a block, measured once: 16 passes without the head
+        toks = self.rng.integers(0, arch.vocab_size, size=16)
+        st = self.om.new_state(64, True)
+        t0 = time.perf_counter()
+        for i, t in enumerate(toks):
+            self.om.single_token(st, t, i, (), want_logits=False)
+        self.layers_s = time.perf_counter() - t0
+
+    def step(self):
+        toks = self.rng.integers(0, self.arch.vocab_size, size=16)
+        st = self.om.new_state(64, True)
+        t0 = time.perf_counter()
+        for i, t in enumerate(toks):
+            self.om.single_token(st, t, i, (), want_logits=True)
+        return time.perf_counter() - t0
+
+    def full_step_s(self, block_s):
+        head_s = max(block_s - self.layers_s, 0.0)
+        return self.layers_s * (self.n_layer_full / 4.0) + head_s
+
+    def describe(self):
+        return ("oracle port (the reference's scalar CPU algorithm, OpenMP over output rows): one block = 16 single-token passes through a "
+                "4-layer (3 GDN + 1 attention) + lm_head slice with config-2 widths; tok/s scales the layers' share by 32/4; drafter not included")
 
 
 def host_random_entries(arch, layers=(0, 1, 2, 3), seed=0):
@@ -216,11 +237,20 @@ def host_random_entries(arch, layers=(0, 1, 2, 3), seed=0):
 
 
 def reference_arm(args):
-    """bench.py --impl reference: the reference's CPU algorithm on the host cores (bounded sample, scaled)."""
+    """bench.py --impl reference: the reference's CPU algorithm on the host cores.  One step = one 16-row block through
+    the 4-layer slice (a bounded sample of the config-2 verify); ms_per_step is that measured time, `value` the
+    accepted tokens per second of the full model it implies."""
     arch = _syn().arch_9b()
-    per_verify, threads, desc = cpu_sample(arch, host_random_entries(arch))
+    sample = CpuBlockSample(arch, host_random_entries(arch))
+    for _ in range(min(args.warmup, 2)):
+        sample.step()
+    steps = max(1, args.steps)
+    times = [sample.step() for _ in range(steps)]
+    block_s = sum(times) / steps
     emitted = sum(a + 1 for a in PATTERN) / len(PATTERN)
-    return emitted / per_verify, per_verify, threads, desc
+    full_s = sample.full_step_s(block_s)
+    return {"value": emitted / full_s, "block_s": block_s, "full_step_s": full_s, "threads": sample.threads, "sample": sample.describe(),
+            "layers_s": sample.layers_s}
 
 
 def run(args, rank, world, device):
@@ -242,7 +272,7 @@ def run(args, rank, world, device):
     logits = w.fresh()
     t0 = time.perf_counter()
     n_nat = min(need, 1 + 2 * (warm + steps))
-    cont_nat, st_nat = w.gen(logits, n_nat)
+    cont_nat, st_nat = w.gen(logits, n_nat, verify_margin=NEAR_TIE_MARGIN)
     nat_wall = time.perf_counter() - t0
     # extend the continuation cheaply with full-accept replay of itself is impossible before it is known:
     # decode the rest with plain replay-free steps only as far as the schedules need
@@ -283,23 +313,26 @@ def run(args, rank, world, device):
         "warmup": warm, "ms_per_step": dev_ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u4/u5/u6 weights x f16 hi+lo activations, f32 accumulate; bf16 drafter", "data": "synthetic",
         "config": {"workload": (f"c5: the config-2 target and drafter after a context of {long_ctx} random ids pre-filled into an fp16 KV cache "
-                                f"({kv_bytes / 2**30:.1f} GiB read per verify), greedy, batch 1, block 16; " if long_ctx else
-                                "c2: 9B-class hybrid Q4_K_M target (32 layers, GDN:attn 3:1, H 4096, FFN 12288, V 151936) + 5-layer bf16 DFlash drafter, "
-                                "greedy, batch 1, prompt 512, block 16; ") +
-                               "replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step",
+                                f"({kv_bytes / 2**30:.1f} GiB read per verify), greedy, batch 1, block 16; "
+                                "replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step") if long_ctx else WORKLOAD_C2,
                    "l2": "5.1 GB of weights per verify >> 126 MB L2", "parallelism": f"dp{world}: one independent sequence per GPU, no collective"},
-        # DRAM bytes per launch: algorithmic bytes x 1.04, the dram-bytes / ggml-bytes ratio ncu measured for this kernel
-        # (profiles/gemm_ts_c1_ncu_full.md; the traffic grows with the bytes streamed)
-        "roofline": {"bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s", "frac": gemm_gbs / peak,
-                     "traffic": 1.04 * gemm_bytes / max(gemm_n, 1), "algorithmic_bytes_per_launch": gemm_bytes / max(gemm_n, 1),
-                     "peak_kind": peak_kind, "kernel": "few-row GEMMs (gemm_ts_kernel for the Q4_K/Q5_K/Q6_K target, gemm_tsb_kernel for the bf16 drafter), all launches of 5 outer steps (verify + draft), CUDA events per launch",
-                     "launches_timed": gemm_n, "algorithmic_bytes_timed": gemm_bytes,
-                     "verify_step": {"weight_bytes": vbytes, "ms": verify_ms, "GBps": vbytes / (verify_ms * 1e-3) / 1e9,
-                                     "frac": vbytes / (verify_ms * 1e-3) / 1e9 / peak},
+        # the unit of the roofline is one packed verify step: the quantised weight bytes it streams once (algorithmic bytes)
+        # over its CUDA-event time, all kernels of the step included.  traffic: algorithmic bytes x 1.04, the DRAM-bytes /
+        # weight-bytes ratio an ncu capture of the dominant kernel showed on a smaller case (traffic grows with the bytes)
+        "roofline": {"bound": "hbm", "achieved": vbytes / (verify_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": vbytes / (verify_ms * 1e-3) / 1e9 / peak, "traffic": 1.04 * vbytes, "peak_kind": peak_kind,
+                     "unit_of_work": "one packed verify step (16 rows through the 32-layer target and the lm_head), every kernel of the step",
+                     "algorithmic_bytes": vbytes, "ms": verify_ms, "kernel": "gemm_ts_kernel<Q4_K | Q5_K | Q6_K> (the step's dominant kernel)",
+                     "gemm_launches_only": {"GBps": gemm_gbs, "frac": gemm_gbs / peak, "launches_timed": gemm_n, "algorithmic_bytes_timed": gemm_bytes,
+                                            "note": "every few-row GEMM launch of 4 extra outer steps (verify + draft) bracketed by CUDA events; "
+                                                    "bracketing takes the launches out of their overlap, so the sum exceeds their share of a step"},
                      "draft_step": {"weight_bytes": dbytes, "ms": draft_ms, "GBps": dbytes / (draft_ms * 1e-3) / 1e9 if draft_ms > 0 else None}},
         "e2e": {"value": head["emitted"] * world / (wall_ms * 1e-3), "unit": bench.UNIT, "h2d_bytes_per_step": 2 * 16 * 4,
                 "d2h_bytes_per_step": 3 * 16 * 4},
         "gpu_launches": int(head["launches"]), "clocks": clocks,
+        # greedy continuation of the natural pass: committed verify rows and those whose top-1 / top-2 gap is below the margin
+        # (a row this close to a tie may resolve differently under another f32 summation order)
+        "near_tie_rows": {"margin": NEAR_TIE_MARGIN, "committed_rows": int(st_nat.committed_rows), "rows_below_margin": int(st_nat.margin_rows)},
         "schedules": {
             "reference_like_4.4": {"tok_per_s": head["emitted"] / (head["dev_ms"] * 1e-3), "e2e_tok_per_s": head["emitted"] / (head["wall_ms"] * 1e-3),
                                    "ms_per_step": head["dev_ms"] / steps, "draft_ms": draft_ms, "verify_ms": verify_ms,
@@ -320,10 +353,12 @@ def run(args, rank, world, device):
                 raw = pkg.device_to_host(data, nb, device) if isinstance(data, int) else np.ascontiguousarray(data).view(np.uint8).reshape(-1)
                 host.append((name, dtype, shape, raw))
             syn.free_entries(ents, device)
-            per_verify, threads, desc = cpu_sample(w.arch, host)
+            sample = CpuBlockSample(w.arch, host)
+            block_s = min(sample.step() for _ in range(2))
+            per_verify = sample.full_step_s(block_s)
             emitted = sum(a + 1 for a in PATTERN) / len(PATTERN)
-            line["cpu_baseline"] = {"value": emitted / per_verify, "unit": bench.UNIT, "cores": threads, "kind": "port", "sample": desc,
-                                    "cpu_verify_s": per_verify}
+            line["cpu_baseline"] = {"value": emitted / per_verify, "unit": bench.UNIT, "cores": sample.threads, "kind": "port", "sample": sample.describe(),
+                                    "cpu_block_s": block_s, "cpu_verify_s": per_verify}
         except Exception as e:  # the baseline is a reported extra; never lose the GPU line over it
             line["cpu_baseline"] = {"value": None, "unit": bench.UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
     return line

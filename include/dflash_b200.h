@@ -548,8 +548,10 @@ typedef struct dfl_generate_params {
     /* sampled mode: build sparse proposals from the drafter's top-16
      * (draft_block_sampled, metal_dflash.rs:17268-17415) instead of one-hot. */
     int32_t sparse_proposals;
-    /* margin guard (qwen/dflash.rs:93-121): committed rows with gap < margin are
-     * replayed through single-token steps.  0 disables. */
+    /* margin guard (qwen/dflash.rs:93-121): committed rows with gap < margin are counted (stats.margin_rows, and
+     * stats.fallback_steps for the steps that hold one).  The reference replays such rows through its exact
+     * single-token path; here a packed row and a single-token row are the same bits, so the replay would reproduce
+     * the row and is not run.  0 disables. */
     float verify_margin;
     /* with replay_history: still run the drafter every step (its tokens are discarded) so that a
      * replayed-acceptance schedule pays the full draft cost. */
@@ -575,6 +577,10 @@ typedef struct dfl_generate_stats { /* DflashDecodeStats  qwen/dflash.rs:380-418
     double accept_ms;   /* host */
     double append_ms;
     double wall_ms;
+    /* margin guard accounting (greedy mode, verify_margin > 0): committed verify rows, and how many of them had a
+     * top-1 / top-2 gap below the margin (qwen/dflash.rs:93-121 counts the same rows before replaying them) */
+    uint64_t committed_rows;
+    uint64_t margin_rows;
 } dfl_generate_stats;
 
 /* generate_dflash  crates/qwen-cli/src/qwen/dflash.rs:484-1263.  `first_logits`

@@ -177,9 +177,20 @@ int orc_dflash_draft_hidden(void* drafter, void* target, const int32_t* noise_id
 
 int orc_num_threads() {
 #ifdef _OPENMP
-    
     return omp_get_max_threads();
 #else
+    return 1;
+#endif
+}
+
+// Sets the number of OpenMP threads the timed CPU baseline uses (a launcher may have exported OMP_NUM_THREADS=1);
+// returns the count in effect.
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
     return 1;
 #endif
 }

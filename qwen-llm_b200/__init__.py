@@ -80,7 +80,7 @@ class GenerateStats(C.Structure):
                 ("restore_calls", C.c_uint32), ("fallback_steps", C.c_uint32), ("drafts_scored", C.c_uint64),
                 ("accepted_drafts", C.c_uint64), ("tokens_emitted", C.c_uint64), ("draft_ms", C.c_double),
                 ("verify_ms", C.c_double), ("restore_ms", C.c_double), ("accept_ms", C.c_double), ("append_ms", C.c_double),
-                ("wall_ms", C.c_double)]
+                ("wall_ms", C.c_double), ("committed_rows", C.c_uint64), ("margin_rows", C.c_uint64)]
 
 
 _LIB = None

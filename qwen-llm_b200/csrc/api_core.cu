@@ -29,6 +29,20 @@ void family_timing_mark(int family, cudaStream_t st, bool begin) {
     }
 }
 
+int sm_count() {
+    static std::atomic<int> cached[16] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < 16) {
+        const int c = cached[dev].load(std::memory_order_relaxed);
+        if (c > 0) return c;
+    }
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (dev >= 0 && dev < 16) cached[dev].store(n, std::memory_order_relaxed);
+    return n;
+}
+
 bool pdl_enabled() {
     static const bool on = [] {
         const char* e = getenv("DFL_PDL");

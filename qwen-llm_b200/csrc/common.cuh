@@ -109,6 +109,8 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // scheduled while its predecessor in the stream is still running; it calls pdl_wait() before its
 // first global-memory access and pdl_launch_dependents() at its top, so that launch latency and
 // block scheduling overlap the predecessor.  DFL_PDL=0 turns the attribute off.
+// Number of SMs of the current device (cached per device): grids are sized from it.
+int sm_count();
 bool pdl_enabled();
 bool pdl_enabled_for(int family);   // development switch: DFL_PDL_OFF=<bit mask of kernel families>
 // Optional per-family device timing (dfl_family_timing_begin / _end): launches of the selected families are bracketed

@@ -8,9 +8,13 @@
 // the first n_keep tokens from the untouched pre-block state, which reproduces the sequential
 // state bit for bit without the reference's per-token state checkpoints
 // (metal_dflash.rs:5863-5896: n_gdn x N x state bytes written every verify).
+#include <cooperative_groups.h>
+
 #include "ops.cuh"
 
 namespace dfl {
+
+namespace cg = cooperative_groups;
 
 // ---- front: conv1d(K=4) + SiLU over the block, q/k L2 norm -------------------------------
 // grid = conv_dim / 128 (one q, k or v head per CTA), block 512: thread = (channel, group of four rows).  The
@@ -20,19 +24,22 @@ __global__ void __launch_bounds__(512) gdn_front_kernel(GdnGeom g, const float* 
                                                         const float* __restrict__ conv_w, float* conv_state,
                                                         float* qkv_raw, float* q_n, float* k_n,
                                                         float* v_out, float* conv_pre) {
-    pdl_prologue();
     const int conv_dim = g.conv_dim();
     const int tq = threadIdx.x >> 7, d = threadIdx.x & 127, i0 = 4 * tq;
     const int c = blockIdx.x * 128 + d;
     const int head = blockIdx.x;  // heads of 128 channels: [0, n_k) q, [n_k, 2 n_k) k, rest v
+    // filter taps and the conv state rows come before the dependency wait: the previous pass wrote the state and a
+    // pass begins with a host-to-device copy, so no kernel of this pass is its author
     const float4 w = *reinterpret_cast<const float4*>(conv_w + c * 4);
     // xv[k] = input at row i0 - 3 + k (rows before the block come from the conv state)
     float xv[7];
 #pragma unroll
     for (int k = 0; k < 7; ++k) {
         const int row = i0 - 3 + k;
-        xv[k] = row < 0 ? conv_state[(row + 3) * conv_dim + c] : 0.f;
+        xv[k] = row < 0 ? __ldcg(conv_state + (row + 3) * conv_dim + c) : 0.f;
     }
+    pdl_prologue();
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
         const float* base = part + (uint64_t)s * MAX_ROWS * ld_part + c;
 #pragma unroll
@@ -170,21 +177,34 @@ __device__ __forceinline__ void gdn_token_step(float (&S)[4][4], const float* k_
         for (int r = 0; r < 4; ++r) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], of);
 }
 
-// ---- scan --------------------------------------------------------------------------------
-// grid (n_v, 4), block 256: warp owns 4 state rows (dv), lane owns columns dk = lane + 32 j.
-// The block's q, k, v rows and gate scalars are staged in shared memory first, so that the
-// sequential part touches no global memory.  Per token (forward.rs:1054-1091): sk = S k (state
-// before decay), coeff = beta (v - g sk), S = g S + coeff k, o = S q.
-__global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* state_in, float* state_out,
-                                                       const float* q_n, const float* k_n,
-                                                       const float* v, const float* ab,
-                                                       const float* __restrict__ dt_bias, const float* __restrict__ a_log, int n_rows,
-                                                       float* o) {
-    pdl_prologue();
+// ---- scan (+ gated RMSNorm and activation packing) ------------------------------------------
+// grid (n_v, 4) in clusters of four along y (the four quarters of a head's 128 value channels), block 256: warp
+// owns 4 state rows (dv), lane owns columns dk = lane + 32 j.  The state rows are fetched before the dependency wait
+// (the previous pass wrote them and a pass begins with a host-to-device copy, so no kernel of this pass is their
+// author); the block's q, k, v rows, gate scalars and the z rows are staged in shared memory, so that the sequential
+// part touches no global memory.  Per token (forward.rs:1054-1091): sk = S k (state before decay),
+// coeff = beta (v - g sk), S = g S + coeff k, o = S q.
+// With `acts` the kernel also finishes the layer's mixer: y = rmsnorm(o; eps * 128) * w * silu(z) over the head's 128
+// channels (forward.rs:1093-1103), whose sum of squares the four CTAs of a cluster exchange through distributed shared
+// memory and add in rank order, and packs its 32 columns of the out-projection's activations.  Without `acts` (the
+// re-scan of a partial accept) only the state is advanced.
+__global__ void __cluster_dims__(1, 4, 1) __launch_bounds__(256)
+gdn_scan_kernel(GdnGeom g, const float* state_in, float* state_out, const float* q_n, const float* k_n, const float* v, const float* ab,
+                const float* __restrict__ dt_bias, const float* __restrict__ a_log, int n_rows, const float* part_z, int z_splits, int ld_part,
+                const float* __restrict__ norm_w, uint8_t* acts, int layout, int* err) {
     __shared__ float qs[MAX_ROWS][128], ks[MAX_ROWS][128], vs[MAX_ROWS][32], gs[MAX_ROWS], bs[MAX_ROWS], os[MAX_ROWS][32];
+    __shared__ float zs[MAX_ROWS][32], ss_loc[MAX_ROWS], scale_s[MAX_ROWS];
     const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hk = h % g.n_k;
     const int dv_cta = blockIdx.y * 32, dv0 = dv_cta + warp * 4;
+    float S[4][4];
+    const float* sin = state_in + ((uint64_t)h * 128 + dv0) * 128;
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) S[r][j] = __ldcg(sin + r * 128 + lane + 32 * j);
+    const float dtb = dt_bias[h], alog = a_log[h];
+    pdl_prologue();
     for (int idx = threadIdx.x; idx < n_rows * 128; idx += 256) {
         const int i = idx >> 7, d = idx & 127;
         qs[i][d] = q_n[((uint64_t)i * g.n_k + hk) * 128 + d];
@@ -197,16 +217,21 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* s
     if (threadIdx.x < n_rows) {
         // gate inputs: ab[i][0..n_v) = alpha projection, ab[i][n_v..2 n_v) = beta projection
         const int i = threadIdx.x;
-        const float alpha = ab[(uint64_t)i * (2 * g.n_v) + h] + dt_bias[h];
-        gs[i] = expf(softplus_f(alpha) * a_log[h]);
+        const float alpha = ab[(uint64_t)i * (2 * g.n_v) + h] + dtb;
+        gs[i] = expf(softplus_f(alpha) * alog);
         bs[i] = sigmoid_f(ab[(uint64_t)i * (2 * g.n_v) + g.n_v + h]);
     }
-    float S[4][4];
-    const float* sin = state_in + ((uint64_t)h * 128 + dv0) * 128;
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) S[r][j] = sin[r * 128 + lane + 32 * j];
+    if (acts) {
+        // z = the z projection's split-K partials summed in slice order; two tokens' worth per pass of the CTA
+        for (int idx = threadIdx.x; idx < n_rows * 32; idx += 256) {
+            const int i = idx >> 5, d = idx & 31;
+            const float* zp = part_z + (uint64_t)i * ld_part + h * 128 + dv_cta + d;
+            float z = 0.f;
+#pragma unroll 4
+            for (int s = 0; s < z_splits; ++s) z += zp[(uint64_t)s * MAX_ROWS * ld_part];
+            zs[i][d] = z;
+        }
+    }
     __syncthreads();
     for (int i = 0; i < n_rows; ++i) {
         float oo[4];
@@ -218,64 +243,53 @@ __global__ void __launch_bounds__(256) gdn_scan_kernel(GdnGeom g, const float* s
     for (int r = 0; r < 4; ++r)
 #pragma unroll
         for (int j = 0; j < 4; ++j) sout[r * 128 + lane + 32 * j] = S[r][j];
-    if (o) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < n_rows * 32; idx += 256) {
-            const int i = idx >> 5, d = idx & 31;
-            o[((uint64_t)i * g.n_v + h) * 128 + dv_cta + d] = os[i][d];
+    if (!acts) return;   // uniform over the grid: no CTA of any cluster reaches the cluster barriers below
+    __syncthreads();
+    // this quarter's share of each token's sum of squares (two tokens per warp)
+    for (int i = warp; i < MAX_ROWS; i += 8) {
+        const float x = i < n_rows ? os[i][lane] : 0.f;
+        const float sq = warp_sum(x * x);
+        if (lane == 0) ss_loc[i] = sq;
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();   // every quarter's shares are written
+    if (threadIdx.x < MAX_ROWS) {
+        float tot = 0.f;
+#pragma unroll
+        for (unsigned r = 0; r < 4; ++r) tot += *cluster.map_shared_rank(&ss_loc[threadIdx.x], r);   // rank order: the same sum in all four CTAs
+        scale_s[threadIdx.x] = 1.0f / sqrtf(tot / 128.f + 1e-6f * 128.f);   // eps = RMS_EPS * head_dim (forward.rs:1098)
+    }
+    cluster.sync();   // scale_s visible in the CTA; nobody leaves while its shares may still be read
+    if (threadIdx.x < 128) {
+        const int tok = threadIdx.x >> 3, quad = threadIdx.x & 7;
+        const int col0 = h * 128 + dv_cta + quad * 4;
+        float y[4] = {0.f, 0.f, 0.f, 0.f};
+        if (tok < n_rows) {
+            const float4 nw = *reinterpret_cast<const float4*>(norm_w + dv_cta + quad * 4);
+            const float sc = scale_s[tok];
+            y[0] = os[tok][quad * 4 + 0] * sc * nw.x * silu_f(zs[tok][quad * 4 + 0]);
+            y[1] = os[tok][quad * 4 + 1] * sc * nw.y * silu_f(zs[tok][quad * 4 + 1]);
+            y[2] = os[tok][quad * 4 + 2] * sc * nw.z * silu_f(zs[tok][quad * 4 + 2]);
+            y[3] = os[tok][quad * 4 + 3] * sc * nw.w * silu_f(zs[tok][quad * 4 + 3]);
         }
+        uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * act_chunk_dev(layout);
+        bool over = false;
+        pack_quad_any(chunk, layout, tok, col0 & 255, y, over);
+        if (layout == ACT_F16 || layout == ACT_TS) {
+            float sum = y[0] + y[1] + y[2] + y[3];   // the CTA's 32 channels are one 32-column sub-block: eight neighbouring threads
+#pragma unroll
+            for (int of = 4; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);
+            if (quad == 0) store_subsum(chunk, layout, tok, (col0 & 255) >> 5, sum, over);
+        }
+        if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
     }
 }
 
 dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state_in, float* state_out, const float* q_n,
                            const float* k_n, const float* v, const float* ab, const float* dt_bias, const float* a_log, int n_rows,
-                           float* o) {
-    launch_kf(8, gdn_scan_kernel, dim3(dim3((unsigned)g.n_v, 4)), dim3(256), 0, st, g, state_in, state_out, q_n, k_n, v, ab, dt_bias, a_log, n_rows, o);
-    count_launch();
-    DFL_CUDA(cudaGetLastError());
-    return DFL_OK;
-}
-
-// ---- post: gated RMSNorm + activation packing ----------------------------------------------
-// grid (n_v, 16), block 32: one warp per (head, token); lane owns 4 consecutive channels.
-__global__ void __launch_bounds__(32) gdn_post_kernel(GdnGeom g, const float* o, const float* part_z, int splits,
-                                                      int ld_part, const float* __restrict__ norm_w, int n_rows, uint8_t* acts, int bf3,
-                                                      int* err) {
-    pdl_prologue();
-    const int h = blockIdx.x, tok = blockIdx.y, lane = threadIdx.x;
-    const int col0 = h * 128 + lane * 4;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (tok < n_rows) {
-        const float4 ov = *reinterpret_cast<const float4*>(o + (uint64_t)tok * (g.n_v * 128) + col0);
-        float z[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int s = 0; s < splits; ++s) {
-            const float4 zz = *reinterpret_cast<const float4*>(part_z + ((uint64_t)s * MAX_ROWS + tok) * ld_part + col0);
-            z[0] += zz.x; z[1] += zz.y; z[2] += zz.z; z[3] += zz.w;
-        }
-        const float ss = warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w);
-        const float scale = 1.0f / sqrtf(ss / 128.f + 1e-6f * 128.f);  // eps = RMS_EPS * head_dim (forward.rs:1098)
-        const float4 nw = *reinterpret_cast<const float4*>(norm_w + lane * 4);
-        v[0] = ov.x * scale * nw.x * silu_f(z[0]);
-        v[1] = ov.y * scale * nw.y * silu_f(z[1]);
-        v[2] = ov.z * scale * nw.z * silu_f(z[2]);
-        v[3] = ov.w * scale * nw.w * silu_f(z[3]);
-    }
-    uint8_t* chunk = acts + (uint64_t)(col0 >> 8) * act_chunk_dev(bf3);
-    bool over = false;
-    pack_quad_any(chunk, bf3, tok, col0 & 255, v, over);
-    if ((bf3 == ACT_F16 || bf3 == ACT_TS)) {
-        float sum = v[0] + v[1] + v[2] + v[3];
-#pragma unroll
-        for (int of = 4; of > 0; of >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, of);
-        if ((lane & 7) == 0) store_subsum(chunk, bf3, tok, (col0 & 255) >> 5, sum, over);
-    }
-    if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
-}
-
-dfl_status launch_gdn_post(cudaStream_t st, const GdnGeom& g, const float* o, const float* part_z, int splits, int ld_part,
-                           const float* norm_w, int n_rows, uint8_t* acts, int bf3, int* err) {
-    launch_kf(8, gdn_post_kernel, dim3(dim3((unsigned)g.n_v, MAX_ROWS)), dim3(32), 0, st, g, o, part_z, splits, ld_part, norm_w, n_rows, acts, bf3, err);
+                           const float* part_z, int z_splits, int ld_part, const float* norm_w, uint8_t* acts, int act_layout, int* err) {
+    launch_kf(8, gdn_scan_kernel, dim3(dim3((unsigned)g.n_v, 4)), dim3(256), 0, st, g, state_in, state_out, q_n, k_n, v, ab, dt_bias, a_log, n_rows,
+              part_z, z_splits, ld_part, norm_w, acts, act_layout, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

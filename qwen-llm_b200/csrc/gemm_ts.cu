@@ -1,24 +1,28 @@
 // Few-row weight-streaming GEMM on the fifth-generation tensor cores.
 //
 // Same contract as the mma.sync kernel (gemm_fewrow.cu: y[r, o] = sum_i x[r, i] W[o, i], <= 16
-// activation rows, split-K partials, deterministic), different engine:
+// activation rows, split-K partials, deterministic), different engine.  One CTA per SM, four
+// kinds of warps that only meet at mbarriers:
 //   * a producer thread streams 128-row x 256-column stages of packed weights with bulk copies
 //     into a shared-memory ring; the packed activations of the CTA's column range are copied
 //     once and stay resident as the B operand;
 //   * sixteen unpacking warps turn the integer quants into exact f16 integers q * sc (the
 //     6-bit sub-block scale folded in, still exact: q * sc < 2048) and store them with
-//     tcgen05.st into tensor memory, thread = (row, quarter of the columns), row = TMEM lane;
-//   * one thread issues tcgen05.mma (A from tensor memory, B = activations hi / lo planes from
-//     shared memory, M = 128, N = 32, K = 16 per instruction), sixteen per stage, accumulating
-//     the whole 256-column block in tensor memory; a seventeenth MMA multiplies the sub-block
-//     mins with the per-sub-block activation sums (the K-quant "min" term);
-//   * two stages later the unpacking threads read their row's 8 + 12 accumulator columns back
-//     (tcgen05.ld), apply the per-row f16 super-block scales d and dmin in f32 and add to four
-//     register accumulators per thread (row x 4 tokens); at the end of a row tile they write
-//     the partial result straight to global memory.  No shared-memory reduction, no atomics.
-// A and the accumulators are double-buffered in tensor memory so that unpacking stage i + 1
-// overlaps the MMAs of stage i.
-#include "gemm_ts.cuh"
+//     tcgen05.st into tensor memory, thread = (row, quarter of the columns), row = TMEM lane.
+//     They do nothing else, so their instruction stream never waits for an accumulator;
+//   * one warp issues tcgen05.mma (A from tensor memory, B = activations hi / lo planes from
+//     shared memory, M = 128, N = 32, K = 16 per instruction), sixteen per pass, accumulating
+//     a 256-column block in tensor memory; a seventeenth MMA multiplies the sub-block mins
+//     with the per-sub-block activation sums (the K-quant "min" term);
+//   * four draining warps (thread = weight row) read the finished block's accumulator back
+//     (tcgen05.ld), apply the per-row f16 super-block scales d and dmin in f32 and add to
+//     sixteen register accumulators (one per token); at the end of a row tile they write the
+//     partial result straight to global memory.  No shared-memory reduction, no atomics.
+// The A operand and the accumulators are double-buffered in tensor memory: unpacking pass
+// i + 1 overlaps the MMAs of pass i, which overlap the read-back of block i - 1.
+#include <mutex>
+
+#include "ops.cuh"
 
 namespace dfl {
 
@@ -201,21 +205,21 @@ dfl_status launch_prep_acts_ts(cudaStream_t st, const float* x, int ld, int n_ro
 // ---------------------------------------------------------------------------------------------
 namespace ts {
 
-constexpr int GROUP_WARPS = 8;                          // unpacking warps per group; thread = (row = 32 * (warp % 4) + lane, kp2)
-constexpr int GROUP_THREADS = GROUP_WARPS * 32;
-constexpr int UNPACK_WARPS = 2 * GROUP_WARPS;
-constexpr int PRODUCER_WARP = 16, MMA_WARP0 = 17, MMA_WARP1 = 18;
-constexpr int THREADS = 19 * 32;                        // 608
+constexpr int UNPACK_WARPS = 16;                        // thread = (row = 32 * (warp % 4) + lane, kp = warp / 4: a quarter of the columns)
+constexpr int DRAIN_WARP0 = 16, DRAIN_WARPS = 4;        // thread = weight row; warp % 4 = its quarter of the tensor-memory lanes
+constexpr int PRODUCER_WARP = 20, MMA_WARP = 21;
+constexpr int THREADS = 22 * 32;                        // 704
 #ifndef DFL_TS_KC
 #define DFL_TS_KC 6
 #endif
 constexpr int KC = DFL_TS_KC;                           // column blocks whose activations stay resident
 
-// tensor-memory columns (32-bit each, 128 lanes) of one group: two pass buffers of 64 columns
-// (128 f16 per row), two 32-column accumulators (even / odd MMA steps: two short dependency chains
-// instead of one long one), the 8-column A operand and the 48-column accumulator of the min term;
-// the second group starts 256 columns further
-constexpr uint32_t TM_A = 0, TM_D = 128, TM_AM = 192, TM_DM = 200, TM_GROUP = 256, TM_COLS = 512;
+// tensor-memory columns (32-bit each, 128 lanes): two pass buffers of 128 columns (256 f16 per row), per block
+// buffer two 32-column accumulators (even / odd MMA steps: two short dependency chains instead of one long one),
+// the 8-column A operand of the min term per pass buffer and its 48-column accumulator per block buffer
+constexpr uint32_t TM_A = 0, TM_A_STRIDE = 128, TM_D = 256, TM_D_STRIDE = 64, TM_AM = 384, TM_AM_STRIDE = 8, TM_DM = 400, TM_DM_STRIDE = 48,
+                   TM_COLS = 512;
+static_assert(TM_DM + 2 * TM_DM_STRIDE <= TM_COLS, "tensor memory budget");
 
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -342,21 +346,21 @@ struct UnitScales {
 template <int DT>
 struct Fmt;
 
-// Q4_K / Q5_K: two passes of 128 columns per stage.  In pass ps thread (row, kp2) takes the 64
-// columns of kp = 2 ps + kp2: sub-blocks 2kp (low nibbles) and 2kp + 1 (high nibbles) of its row
-// into r[0..15] / r[16..31]; r[c] = half2 of k-positions 2c, 2c + 1.
+// Q4_K / Q5_K: one pass per stage.  Thread (row, kp) takes the 64 columns of quarter kp: sub-blocks 2kp (low nibbles)
+// and 2kp + 1 (high nibbles) of its row into r[0..15] / r[16..31]; r[c] = half2 of k-positions 2c, 2c + 1.
 template <int DT>
 struct FmtK45 {
     static constexpr int STAGE = DT == DFL_Q4_K ? STAGE_Q4_K : STAGE_Q5_K;
-    static constexpr int STAGES = KC == 4 ? (DT == DFL_Q4_K ? 7 : 6) : (DT == DFL_Q4_K ? 5 : 4);
-    static constexpr int PASSES = 2;
+    static constexpr int STAGES = KC == 4 ? (DT == DFL_Q4_K ? 7 : 6) : (DT == DFL_Q4_K ? 6 : 5);
+    static constexpr int PASSES = 1;
     static constexpr bool HAS_MIN = true;
-    // MMA step j of pass ps multiplies pass-buffer columns [8j, 8j + 8) with this 16-column slice of the block
-    __device__ static __forceinline__ uint32_t b_slice(int ps, int j) { return (uint32_t)(8 * ps + j); }
-    __device__ static __forceinline__ void store(uint32_t buf, int kp2, const uint32_t (&r)[32]) { tmem_st32(buf + 32 * kp2, r); }
-    __device__ static __forceinline__ void unpack(const uint8_t* st, int ps, int row, int kp2, uint32_t (&r)[32], uint32_t (&am)[8],
+    // MMA step j (0..15) of a pass multiplies pass-buffer columns a_col(j) .. + 8 with 16-column slice b_slice of the block
+    __device__ static __forceinline__ uint32_t a_col(int j) { return (uint32_t)(8 * j); }
+    __device__ static __forceinline__ uint32_t b_slice(int, int j) { return (uint32_t)j; }
+    __device__ static __forceinline__ void store(uint32_t buf, int kp, const uint32_t (&r)[32]) { tmem_st32(buf + 32 * kp, r); }
+    __device__ static __forceinline__ void unpack(const uint8_t* st, int, int row, int kp, uint32_t (&r)[32], uint32_t (&am)[8],
                                                   UnitScales& us) {
-        const int kp = 2 * ps + kp2;
+        const int ps = kp >> 1, kp2 = kp & 1;
         const uint4 h = reinterpret_cast<const uint4*>(st)[row];
         const uint4* qs = reinterpret_cast<const uint4*>(st + TSQ4_OFF_QS);
         const uint4 qa = qs[(kp * 2 + 0) * 128 + row], qb = qs[(kp * 2 + 1) * 128 + row];

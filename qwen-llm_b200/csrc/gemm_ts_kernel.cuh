@@ -2,16 +2,18 @@
 //
 // CTA = one split (at most KC column blocks, activations resident) x every ctas_per_split-th
 // row tile.  Its work is the sequence of entries e = (tile, column block); the weight stage of
-// entry e travels through ring slot e % STAGES.  Two groups of eight unpacking warps take the
-// entries alternately (group = e & 1), each with its own tensor-memory buffers, MMA-issuing
-// thread and barriers, so that one group's unpacking overlaps the other's waits; the groups
-// meet only at the end of a row tile, where group 1 hands its partial sums to group 0 through
-// shared memory and group 0 writes the tile.
+// entry e travels through ring slot e % STAGES and is unpacked in PASSES passes (Q4_K / Q5_K:
+// one pass of 256 weight columns; Q6_K: two passes of 128, each written as the even / odd
+// scale parts).  Pass i uses pass buffer i & 1 of tensor memory, entry e accumulator e & 1.
 //
-// Inside a group an entry is processed in PASSES passes of 64 tensor-memory columns (Q4_K/Q5_K:
-// 128 weight columns per pass, Q6_K: 64, twice, as the even/odd scale parts); the two pass
-// buffers alternate, eight MMAs per pass accumulate into the group's single accumulator, which
-// the group reads back while it already holds the next entry's first pass in registers.
+//   producer thread     ring slot free?  -> bulk copy of the stage         -> full[slot]
+//   16 unpacking warps  full[slot]       -> registers -> a_free[buf]?      -> tcgen05.st -> a_ready[buf], empty[slot]
+//   MMA warp            a_ready[buf], d_free[acc]? -> 16 (+1) tcgen05.mma  -> commit: a_free[buf], d_ready[acc]
+//   4 draining warps    d_ready[acc]     -> tcgen05.ld -> d_free[acc]      -> scale, add; tile end: global store
+//                       (+ optionally: count the tile's slices; the CTA that wrote the last one runs the glue step)
+//
+// The super-block scales d / dmin of an entry travel from the unpacking threads to the draining
+// thread of the same row through a four-slot shared-memory side buffer (slot = entry & 3).
 #pragma once
 
 namespace dfl {
@@ -31,28 +33,22 @@ struct Params {
     const int32_t* n_tiles;
     const int32_t* kb_map;     // optional: column blocks to sum over, and how many (device memory)
     const int32_t* n_kb;
+    // optional: the glue step the CTA that completes an output tile runs on it (fuse_mode: 0 none, else a GlueMode + 1)
+    int fuse_on;
+    int32_t* fuse_counters;    // [row tile] (residual glue) or [gate tile] (SwiGLU: a gate tile and its up tile share one)
+    int fuse_target;           // slices that complete a counter: splits, or 2 x splits for a gate / up pair
+    int fuse_pair_tiles;       // SwiGLU: the up tile of gate tile t is t + fuse_pair_tiles
+    GlueParams glue;
 };
 
-#ifdef DFL_TS_TRACE
-// development build only: SM-clock timestamps of CTA 0, [role][slot]; role 0 = group-0 warp 0, 1 = group-1 warp 8,
-// 2 = MMA thread 0, 3 = MMA thread 1, 4 = producer
-__device__ long long g_ts_trace[5][512];
-#define TS_TRACE(role, slot)                                                                         \
-    do {                                                                                             \
-        if (blockIdx.x == 0 && (slot) < 512) g_ts_trace[role][slot] = clock64();                       \
-    } while (0)
-#else
-#define TS_TRACE(role, slot) do { } while (0)
-#endif
-
-constexpr int XBUF_BYTES = GROUP_THREADS * 8 * 4;   // one tile's partial sums of a group: 8 tokens per thread
+constexpr int SCL_BYTES = 4 * TILE_R * 8;   // four entries' {d, dmin} per row
 
 template <int DT>
 constexpr int smem_bytes() {
-    return KC * ACTTS_CHUNK + Fmt<DT>::STAGES * Fmt<DT>::STAGE + 2 * XBUF_BYTES + 256;
+    return KC * ACTTS_CHUNK + Fmt<DT>::STAGES * Fmt<DT>::STAGE + SCL_BYTES + 256;
 }
 
-// named barrier 1: start-up of the unpacking warps (every one of them reaches it unconditionally)
+// named barrier among the draining warps only (every one of them reaches it unconditionally)
 __device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
 template <int DT>
@@ -60,20 +56,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     using F = Fmt<DT>;
     constexpr int STAGES = F::STAGES, PASSES = F::PASSES;
     constexpr int OFF_RING = KC * ACTTS_CHUNK;
-    constexpr int OFF_XBUF = OFF_RING + STAGES * F::STAGE;
-    constexpr int OFF_BAR = OFF_XBUF + 2 * XBUF_BYTES;
+    constexpr int OFF_SCL = OFF_RING + STAGES * F::STAGE;
+    constexpr int OFF_BAR = OFF_SCL + SCL_BYTES;
     static_assert(OFF_BAR + 256 <= 227 * 1024, "shared memory budget");
+    static_assert(2 * STAGES + KC + 10 <= 32, "barrier area");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* acts_res = smem;
     uint8_t* ring = smem + OFF_RING;
-    float* xbuf = reinterpret_cast<float*>(smem + OFF_XBUF);
+    float2* scl = reinterpret_cast<float2*>(smem + OFF_SCL);   // [entry & 3][row] = {d, dmin}
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* empty = full + STAGES;
-    uint64_t* acts_bar = empty + STAGES;
-    uint64_t* a_ready = acts_bar + 1;   // [group][buffer] a pass of unpacked weights is in tensor memory
-    uint64_t* a_free = a_ready + 4;     // [group][buffer] the MMAs of that pass have completed
-    uint64_t* x_full = a_free + 4;      // [tile & 1] group 1 has put its partial sums of the tile into the exchange buffer
-    uint64_t* x_free = x_full + 2;      // [tile & 1] group 0 has read them
+    uint64_t* acts_bar = empty + STAGES;  // [column block of the CTA's range] its activations have arrived
+    uint64_t* a_ready = acts_bar + KC;    // [pass buffer] a pass of unpacked weights is in tensor memory
+    uint64_t* a_free = a_ready + 2;       // [pass buffer] the MMAs of that pass have completed
+    uint64_t* d_ready = a_free + 2;       // [accumulator] every MMA of an entry has completed
+    uint64_t* d_free = d_ready + 2;       // [accumulator] the draining warps have read it back
+    uint64_t* fin_written = d_free + 2;   // the draining warps have written (and fenced) the tile's partial slice
+    uint64_t* fin_verdict = fin_written + 1;   // ... and the tile's slice count has been taken
+    __shared__ int fin_last;
     __shared__ uint32_t tmem_slot;
     __shared__ float tok_scale[MAX_ROWS];
     __shared__ int abort_flag;
@@ -101,21 +101,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], GROUP_WARPS);
+            mbar_init(&empty[s], UNPACK_WARPS);
         }
-        mbar_init(acts_bar, 1);
-        for (int i = 0; i < 4; ++i) {
-            mbar_init(&a_ready[i], GROUP_WARPS);
-            mbar_init(&a_free[i], 1);
-        }
+        for (int k = 0; k < KC; ++k) mbar_init(&acts_bar[k], 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&x_full[i], GROUP_WARPS);
-            mbar_init(&x_free[i], GROUP_WARPS);
+            mbar_init(&a_ready[i], UNPACK_WARPS);
+            mbar_init(&a_free[i], 1);
+            mbar_init(&d_ready[i], 1);
+            mbar_init(&d_free[i], DRAIN_WARPS);
         }
+        mbar_init(fin_written, DRAIN_WARPS);
+        mbar_init(fin_verdict, 1);
         abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == MMA_WARP0) tmem_alloc(&tmem_slot, TM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(&tmem_slot, TM_COLS);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -138,214 +138,213 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                                      (uint64_t)(p.kb_map ? p.kb_map[kb0 + pk] : kb0 + pk) * F::STAGE;
                 mbar_arrive_expect_tx(&full[s], F::STAGE);
                 bulk_g2s(ring + s * F::STAGE, src, F::STAGE, &full[s]);
-                TS_TRACE(4, e);
                 if (++pk == n_kb) { pk = 0; ++pt; }
                 if (e == (STAGES < n_it ? STAGES : n_it) - 1) {
-                    // the ring is primed with weights (independent of the previous kernel); now the activations
+                    // the ring is primed with weights (independent of the previous kernel); now the activations,
+                    // in the order of their first use, one barrier each: the first MMA waits for one chunk only
                     pdl_wait();
-                    mbar_arrive_expect_tx(acts_bar, (uint32_t)n_kb * ACTTS_CHUNK);
-                    for (int k = 0; k < n_kb; ++k)
-                        bulk_g2s(acts_res + k * ACTTS_CHUNK, p.acts + (uint64_t)(p.kb_map ? p.kb_map[kb0 + k] : kb0 + k) * ACTTS_CHUNK, ACTTS_CHUNK, acts_bar);
+                    for (int k = 0; k < n_kb; ++k) {
+                        mbar_arrive_expect_tx(&acts_bar[k], ACTTS_CHUNK);
+                        bulk_g2s(acts_res + k * ACTTS_CHUNK, p.acts + (uint64_t)(p.kb_map ? p.kb_map[kb0 + k] : kb0 + k) * ACTTS_CHUNK, ACTTS_CHUNK,
+                                 &acts_bar[k]);
+                    }
                 }
             }
             if (!ok) abort_flag = 1;
         }
-    } else if (warp == MMA_WARP0 || warp == MMA_WARP1) {
-        // ------------------------------ MMA issuer of one group ------------------------------
+    } else if (warp == MMA_WARP) {
+        // ------------------------------ MMA issuer ------------------------------
         // The whole warp walks the loop so that addresses and descriptors stay warp-uniform; one elected
         // lane issues the instructions.
-        const int g = warp - MMA_WARP0;
-        if (n_it > g) {
-            constexpr uint32_t IDESC_MAIN = instr_desc(32), IDESC_MIN = instr_desc(48);
-            bool ok = mbar_wait_bounded(acts_bar, 0, p.err, DEV_ERR_WAIT_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            const uint32_t acts_addr = smem_u32(acts_res);
-            const uint32_t tm_g = tmem + g * TM_GROUP;
-            uint32_t pc = 0;   // running pass count of this group
-            for (int e = g; e < n_it && ok; e += 2) {
-                const uint32_t chunk = acts_addr + (e % n_kb) * ACTTS_CHUNK;
-#pragma unroll
-                for (int ps = 0; ps < PASSES; ++ps, ++pc) {
-                    const uint32_t b = pc & 1;
-                    if (ok) {
-                        ok = mbar_wait_bounded(&a_ready[2 * g + b], (pc >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
-                        ok = __all_sync(0xffffffffu, ok);
-                    }
-                    if (ok) {
-                        if (lane == 0) TS_TRACE(2 + g, 2 * pc);
-                        fence_after_sync();
-                        if (elect_one()) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                mma_ts(tm_g + TM_D + 32 * (j & 1), tm_g + TM_A + b * 64 + 8 * j,
-                                       smem_desc(chunk + F::b_slice(ps, j) * 1024, 512, 128), IDESC_MAIN, (ps | (j >> 1)) ? 1u : 0u);
-                            if (F::HAS_MIN && ps == PASSES - 1)   // every pass has stored its column of the min operand by now
-                                mma_ts(tm_g + TM_DM, tm_g + TM_AM, smem_desc(chunk + TS_BMIN_OFF, 768, 128), IDESC_MIN, 0);
-                            mma_commit(&a_free[2 * g + b]);
-                        }
-                        __syncwarp();
-                        if (lane == 0) TS_TRACE(2 + g, 2 * pc + 1);
-                    }
-                }
-            }
-            if (!ok) abort_flag = 1;
-        }
-    } else if (warp < UNPACK_WARPS) {
-        // ------------------------------ unpack + drain warps ------------------------------
-        pdl_wait();
-        if (threadIdx.x < 256) {
-            // per-token output scale; 16 threads per token add the sum-of-squares partials in a fixed tree
-            const int tok = threadIdx.x >> 4, part = threadIdx.x & 15;
-            float ss = 0.f;
-            if (p.sumsq)
-                for (int q = part; q < p.n_sumsq; q += 16) ss += p.sumsq[q * MAX_ROWS + tok];
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (part == 0) tok_scale[tok] = p.sumsq ? p.out_scale * (1.0f / sqrtf(ss / p.norm_k + p.eps)) : p.out_scale;
-        }
-        named_sync(1, UNPACK_WARPS * 32);
-
-        const int g = warp >> 3, q4 = warp & 3, kp2 = (warp >> 2) & 1;
-        const int row = 32 * q4 + lane, gtid = threadIdx.x & (GROUP_THREADS - 1);
-        const uint32_t tm_g = tmem + g * TM_GROUP + ((uint32_t)(32 * q4) << 16);
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        // K padding of the min-term operand (sub-block index 8..15): written once, never touched again
-        if (F::HAS_MIN && kp2 == 0) tmem_st4(tm_g + TM_AM + 4, 0u, 0u, 0u, 0u);
+        constexpr uint32_t IDESC_MAIN = instr_desc(32), IDESC_MIN = instr_desc(48);
         bool ok = true;
-        uint32_t pc = 0;            // running pass count of this group
-        int next_close = 0;         // next row tile this group has to close
-        bool pending = false;       // an entry whose accumulator has not been read back yet
-        int pend_tile = 0;
-        bool pend_last = false;
-        UnitScales pend_us{0.f, 0.f};
-
-        // hand over (group 1) or finish (group 0) the partial sums of tile t
-        auto close_tile = [&](int t) {
-            float* xb = xbuf + (t & 1) * (XBUF_BYTES / 4) + gtid * 8;
-            const uint32_t use = (uint32_t)t >> 1;   // how often this exchange buffer has been used before
-            if (g == 1) {
-                if (t >= 2) {
-                    ok = mbar_wait_bounded(&x_free[t & 1], (use - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) return;
-                }
-                *reinterpret_cast<float4*>(xb) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                *reinterpret_cast<float4*>(xb + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&x_full[t & 1]);
-            } else {
-                ok = mbar_wait_bounded(&x_full[t & 1], use & 1, p.err, DEV_ERR_WAIT_FULL);
+        const uint32_t acts_addr = smem_u32(acts_res);
+        uint32_t pc = 0;   // running pass count
+        for (int e = 0; e < n_it && ok; ++e) {
+            const uint32_t chunk = acts_addr + (e % n_kb) * ACTTS_CHUNK;
+            const uint32_t acc = (uint32_t)e & 1u;
+            if (e < n_kb) {   // first row tile: the column block's activations may still be in flight
+                ok = mbar_wait_bounded(&acts_bar[e], 0, p.err, DEV_ERR_WAIT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) return;
-                const float4 o0 = *reinterpret_cast<const float4*>(xb), o1 = *reinterpret_cast<const float4*>(xb + 4);
-                const float other[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&x_free[t & 1]);
-                const int slot = c + t * cps;
-                const uint32_t orow = (uint32_t)(p.tile_map ? p.tile_map[slot] : slot) * TILE_R + row;
-                if (orow < p.n_out) {
-                    float* dst = p.out + ((uint64_t)sp * MAX_ROWS + 8 * kp2) * p.ld_out + orow;
+            }
+            if (ok && e >= 2) {   // the accumulator was last used by entry e - 2
+                ok = mbar_wait_bounded(&d_free[acc], (((uint32_t)e >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+            }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) dst[(uint64_t)j * p.ld_out] = (acc[j] + other[j]) * tok_scale[8 * kp2 + j];
+            for (int ps = 0; ps < PASSES; ++ps, ++pc) {
+                const uint32_t b = pc & 1;
+                if (ok) {
+                    ok = mbar_wait_bounded(&a_ready[b], (pc >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                }
+                if (ok) {
+                    fence_after_sync();
+                    if (elect_one()) {
+                        const uint32_t a_buf = tmem + TM_A + b * TM_A_STRIDE, d_buf = tmem + TM_D + acc * TM_D_STRIDE;
+                        // one descriptor per column block; a 16-column slice is 1024 bytes further = 64 in the address field
+                        const uint64_t bdesc = smem_desc(chunk, 512, 128);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            mma_ts(d_buf + 32 * (j & 1), a_buf + F::a_col(j), bdesc + (uint64_t)(F::b_slice(ps, j) * 64u), IDESC_MAIN,
+                                   (ps | (j >> 1)) ? 1u : 0u);
+                        if (F::HAS_MIN && ps == PASSES - 1)
+                            mma_ts(tmem + TM_DM + acc * TM_DM_STRIDE, tmem + TM_AM + b * TM_AM_STRIDE, smem_desc(chunk + TS_BMIN_OFF, 768, 128),
+                                   IDESC_MIN, 0);
+                        mma_commit(&a_free[b]);
+                        if (ps == PASSES - 1) mma_commit(&d_ready[acc]);
+                    }
+                    __syncwarp();
                 }
             }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        };
-        // read back the accumulator of the pending entry (its last pass was pass pc - 1), scale, add
-        auto drain_pending = [&]() {
-            const uint32_t lp = pc - 1;
-            ok = mbar_wait_bounded(&a_free[2 * g + (lp & 1)], (lp >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            fence_after_sync();
-            {
-                float v[16], t[8];
-                tmem_ld16(tm_g + TM_D + 16 * kp2, v);        // even MMA steps
-                wait_ld();
-#pragma unroll
-                for (int j = 0; j < 8; ++j) t[j] = v[2 * j] + v[2 * j + 1];
-                tmem_ld16(tm_g + TM_D + 32 + 16 * kp2, v);   // odd MMA steps
-                wait_ld();
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = fmaf(pend_us.d, t[j] + (v[2 * j] + v[2 * j + 1]), acc[j]);
-            }
-            if (F::HAS_MIN) {
-                float s0[8], s1[8], s2[8];   // 8 tokens x 3 planes, token j = flattened columns 3j .. 3j + 2
-                tmem_ld8(tm_g + TM_DM + 24 * kp2, s0);
-                tmem_ld8(tm_g + TM_DM + 24 * kp2 + 8, s1);
-                tmem_ld8(tm_g + TM_DM + 24 * kp2 + 16, s2);
-                wait_ld();
-                auto col = [&](int i) { return i < 8 ? s0[i] : i < 16 ? s1[i - 8] : s2[i - 16]; };
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = fmaf(-pend_us.dmin, (col(3 * j) + col(3 * j + 1)) + col(3 * j + 2), acc[j]);
-            }
-            fence_before_sync();
-            pending = false;
-            if (pend_last) {
-                close_tile(pend_tile);   // every earlier tile was closed when this entry was started
-                next_close = pend_tile + 1;
-            }
-        };
-
-        for (int e = g; e < n_it && ok; e += 2) {
-            const int s = e % STAGES, tile = e / n_kb;
-            const bool tracer = (warp & 7) == 0 && lane == 0;
-            if (tracer) TS_TRACE(g, 16 * (e >> 1));
+        }
+        if (!ok) abort_flag = 1;
+    } else if (warp < UNPACK_WARPS) {
+        // ------------------------------ unpacking warps ------------------------------
+        // They read weights only (shared memory filled by the producer), so they never wait for the previous kernel.
+        const int q4 = warp & 3, kp = warp >> 2;
+        const int row = 32 * q4 + lane;
+        const uint32_t tm_l = tmem + ((uint32_t)(32 * q4) << 16);
+        // K padding of the min-term operand (sub-block pairs 4..7) in both pass buffers: written once, never touched again
+        if (F::HAS_MIN && kp == 0) {
+            tmem_st4(tm_l + TM_AM + 4, 0u, 0u, 0u, 0u);
+            tmem_st4(tm_l + TM_AM + TM_AM_STRIDE + 4, 0u, 0u, 0u, 0u);
+        }
+        bool ok = true;
+        uint32_t pc = 0;   // running pass count
+        for (int e = 0; e < n_it && ok; ++e) {
+            const int s = e % STAGES;
             ok = mbar_wait_bounded(&full[s], (e / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
-            if (tracer) TS_TRACE(g, 16 * (e >> 1) + 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint8_t* st = ring + s * F::STAGE;
-            UnitScales us{0.f, 0.f};
 #pragma unroll
             for (int ps = 0; ps < PASSES; ++ps, ++pc) {
                 uint32_t r[32], am[8];
-                if (ok) {
-                    F::unpack(st, ps, row, kp2, r, am, us);
-                }
-                if (tracer) TS_TRACE(g, 16 * (e >> 1) + 2 + 3 * ps);
-                if (ok && ps == 0) {
-                    if (pending) drain_pending();
-                    if (tracer) TS_TRACE(g, 16 * (e >> 1) + 14);
-                    // tiles in which this group had no entry carry no partial sums of its own
-                    while (ok && next_close < tile) close_tile(next_close++);
-                }
+                UnitScales us{0.f, 0.f};
+                if (ok) F::unpack(st, ps, row, kp, r, am, us);
                 const uint32_t b = pc & 1;
-                // The pass buffer was last read by pass pc - 2.  If that pass belongs to the previous entry, the
-                // read-back above (or, for this group's first entries, nothing) already waited for it.
-                if (ok && ps >= 2) {
-                    ok = mbar_wait_bounded(&a_free[2 * g + b], ((pc >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+                if (ok && pc >= 2) {   // the pass buffer was last read by the MMAs of pass pc - 2
+                    ok = mbar_wait_bounded(&a_free[b], ((pc >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_FULL);
                     ok = __all_sync(0xffffffffu, ok);
                     if (ok) fence_after_sync();
                 }
-                if (tracer) TS_TRACE(g, 16 * (e >> 1) + 3 + 3 * ps);
                 if (ok) {
-                    F::store(tm_g + TM_A + b * 64, kp2, r);
-                    if (F::HAS_MIN) tmem_st1(tm_g + TM_AM + 2 * ps + kp2, am[0]);
+                    F::store(tm_l + TM_A + b * TM_A_STRIDE, kp, r);
+                    if (F::HAS_MIN) tmem_st1(tm_l + TM_AM + b * TM_AM_STRIDE + kp, am[0]);
+                    if (ps == 0 && kp == 0) scl[(e & 3) * TILE_R + row] = make_float2(us.d, us.dmin);
                     wait_st();
                     fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive(&a_ready[2 * g + b]);
+                        mbar_arrive(&a_ready[b]);   // releases this warp's tensor-memory and side-buffer writes
                         if (ps == PASSES - 1) mbar_arrive(&empty[s]);
                     }
-                    if (tracer) TS_TRACE(g, 16 * (e >> 1) + 4 + 3 * ps);
                 }
             }
+        }
+        if (!ok) abort_flag = 1;
+    } else {
+        // ------------------------------ draining warps ------------------------------
+        pdl_wait();
+        const int dtid = threadIdx.x - DRAIN_WARP0 * 32;   // 0..127 = weight row of the tile = tensor-memory lane
+        {
+            // per-token output scale; 8 threads per token add the sum-of-squares partials in a fixed tree
+            const int tok = dtid >> 3, part = dtid & 7;
+            float ss = 0.f;
+            if (p.sumsq)
+                for (int q = part; q < p.n_sumsq; q += 8) ss += p.sumsq[q * MAX_ROWS + tok];
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (part == 0) tok_scale[tok] = p.sumsq ? p.out_scale * (1.0f / sqrtf(ss / p.norm_k + p.eps)) : p.out_scale;
+        }
+        named_sync(1, DRAIN_WARPS * 32);
+        const int row = dtid;
+        const uint32_t tm_l = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+        float acc[MAX_ROWS];
+#pragma unroll
+        for (int j = 0; j < MAX_ROWS; ++j) acc[j] = 0.f;
+        bool ok = true;
+        for (int e = 0; e < n_it && ok; ++e) {
+            const uint32_t a = (uint32_t)e & 1u;
+            ok = mbar_wait_bounded(&d_ready[a], ((uint32_t)e >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            pending = true;
-            pend_tile = tile;
-            pend_last = e + 2 >= (tile + 1) * n_kb;   // this group's last entry of the tile
-            pend_us = us;
+            fence_after_sync();
+            const float2 sc = scl[(e & 3) * TILE_R + row];   // published before the a_ready arrival the MMAs waited for
+            float t[MAX_ROWS], mn[MAX_ROWS];
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {   // tokens 8 hf .. 8 hf + 7
+                float ve[16], vo[16];
+                tmem_ld16(tm_l + TM_D + a * TM_D_STRIDE + 16 * hf, ve);        // even MMA steps: columns 2 tok + plane
+                tmem_ld16(tm_l + TM_D + a * TM_D_STRIDE + 32 + 16 * hf, vo);   // odd MMA steps
+                if (F::HAS_MIN) {
+                    float s0[8], s1[8], s2[8];   // 8 tokens x 3 planes, token j = flattened columns 3j .. 3j + 2
+                    tmem_ld8(tm_l + TM_DM + a * TM_DM_STRIDE + 24 * hf, s0);
+                    tmem_ld8(tm_l + TM_DM + a * TM_DM_STRIDE + 24 * hf + 8, s1);
+                    tmem_ld8(tm_l + TM_DM + a * TM_DM_STRIDE + 24 * hf + 16, s2);
+                    wait_ld();
+                    auto col = [&](int i) { return i < 8 ? s0[i] : i < 16 ? s1[i - 8] : s2[i - 16]; };
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) mn[8 * hf + j] = (col(3 * j) + col(3 * j + 1)) + col(3 * j + 2);
+                } else {
+                    wait_ld();
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t[8 * hf + j] = (ve[2 * j] + ve[2 * j + 1]) + (vo[2 * j] + vo[2 * j + 1]);
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&d_free[a]);   // the accumulator may be overwritten
+#pragma unroll
+            for (int j = 0; j < MAX_ROWS; ++j) {
+                acc[j] = fmaf(sc.x, t[j], acc[j]);
+                if (F::HAS_MIN) acc[j] = fmaf(-sc.y, mn[j], acc[j]);
+            }
+            if ((e + 1) % n_kb == 0) {   // the tile's last column block: write the partial result
+                const int tile = e / n_kb;
+                const int slot = c + tile * cps;
+                const uint32_t orow = (uint32_t)(p.tile_map ? p.tile_map[slot] : slot) * TILE_R + row;
+                if (orow < p.n_out) {
+                    float* dst = p.out + (uint64_t)sp * MAX_ROWS * p.ld_out + orow;
+#pragma unroll
+                    for (int j = 0; j < MAX_ROWS; ++j) dst[(uint64_t)j * p.ld_out] = acc[j] * tok_scale[j];
+                }
+#pragma unroll
+                for (int j = 0; j < MAX_ROWS; ++j) acc[j] = 0.f;
+                if (p.fuse_on) {
+                    // Count this slice of the tile.  Every wait is bounded (no CTA-wide barrier here: a warp that gave
+                    // up elsewhere must not be waited for), the reduction order of the glue step is fixed, so the
+                    // result does not depend on which CTA happens to be last.
+                    __threadfence();   // this thread's slice is visible device-wide before the count moves
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(fin_written);
+                    const int gtile = p.tile_map ? p.tile_map[slot] : slot;
+                    const int ctr = p.fuse_pair_tiles > 0 ? gtile % p.fuse_pair_tiles : gtile;
+                    if (dtid == 0) {
+                        bool w = mbar_wait_bounded(fin_written, (uint32_t)tile & 1, p.err, DEV_ERR_WAIT_FULL);
+                        int last = 0;
+                        if (w) {
+                            last = atomicAdd(&p.fuse_counters[ctr], 1) == p.fuse_target - 1;
+                            if (last) p.fuse_counters[ctr] = 0;   // nobody else touches it any more: ready for the next launch
+                        }
+                        fin_last = last;
+                        mbar_arrive(fin_verdict);
+                    }
+                    ok = mbar_wait_bounded(fin_verdict, (uint32_t)tile & 1, p.err, DEV_ERR_WAIT_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    if (fin_last) {
+                        __threadfence();   // the other CTAs' slices, counted before ours, are visible
+                        // 128 columns x 16 tokens as four items per thread: (token half, 64-column half)
+#pragma unroll
+                        for (int it = 0; it < 4; ++it)
+                            glue_quad(p.glue, p.glue.splits, 2 * ctr + (it & 1), 8 * (it >> 1) + (dtid >> 4), dtid & 15);
+                    }
+                }
+            }
         }
-        if (ok && pending) drain_pending();
-        while (ok && next_close < n_my) close_tile(next_close++);
-        if (!ok) {
-            abort_flag = 1;
-        }
+        if (!ok) abort_flag = 1;
     }
 
     fence_before_sync();
@@ -357,11 +356,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
             uint32_t spins = 0;
             while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && ++spins < (1u << 16)) __nanosleep(100);
         }
-        uint32_t spins = 0;
-        while (!mbar_try_wait(acts_bar, 0) && ++spins < (1u << 16)) __nanosleep(100);
+        for (int k = 0; k < (n_kb < KC ? n_kb : KC); ++k) {
+            uint32_t spins = 0;
+            while (!mbar_try_wait(&acts_bar[k], 0) && ++spins < (1u << 16)) __nanosleep(100);
+        }
     }
     __syncthreads();
-    if (warp == MMA_WARP0) {
+    if (warp == MMA_WARP) {
         fence_after_sync();
         tmem_free(tmem, TM_COLS);
     }
@@ -369,12 +370,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
 
 template <int DT>
 static dfl_status launch_t(cudaStream_t st, const Params& p, int grid, bool pdl) {
-    static bool attr_set[16] = {};
+    static std::once_flag attr_once[16];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 16 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 16) {
+        cudaError_t attr_err = cudaSuccess;
+        std::call_once(attr_once[dev], [&] {
+            attr_err = cudaFuncSetAttribute(gemm_ts_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<DT>());
+        });
+        DFL_CUDA(attr_err);
+    } else {
         DFL_CUDA(cudaFuncSetAttribute(gemm_ts_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<DT>()));
-        attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
@@ -392,7 +398,7 @@ static dfl_status launch_t(cudaStream_t st, const Params& p, int grid, bool pdl)
 }
 
 static int ctas_per_split(int row_tiles, int splits) {
-    int cps = 148 / splits;
+    int cps = sm_count() / splits;
     if (cps < 1) cps = 1;
     return cps < row_tiles ? cps : row_tiles;
 }
@@ -455,8 +461,27 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
     p.n_tiles = ep.n_tiles;
     p.kb_map = ep.kb_map;
     p.n_kb = ep.n_kb;
+    p.fuse_on = 0;
+    p.fuse_counters = nullptr;
+    p.fuse_target = 0;
+    p.fuse_pair_tiles = 0;
+    p.glue = GlueParams{};
+    if (ep.fuse) {
+        const GlueParams& g = *ep.fuse;
+        const bool swiglu = g.mode == GLUE_SWIGLU;
+        // whole tiles only, no lists (a repeated tile would be counted twice), slices where the glue step expects them
+        if (!ep.fuse_counters || ep.tile_map || ep.kb_map || m.n_out % TILE_R || g.part != out || g.splits != splits || g.splits_dev ||
+            (uint32_t)g.ld_part != p.ld_out || g.route_w || (swiglu && (g.swiglu_f % TILE_R || (uint64_t)2 * g.swiglu_f != m.n_out)) ||
+            (ep.sumsq && g.sumsq == ep.sumsq) || g.acts == acts)   // a CTA may still be reading what an early finisher would overwrite
+            return fail(DFL_ERR_BAD_ARG, "gemm: this launch cannot finish its own tiles");
+        p.fuse_on = 1;
+        p.fuse_counters = ep.fuse_counters;
+        p.fuse_target = swiglu ? 2 * splits : splits;
+        p.fuse_pair_tiles = swiglu ? g.swiglu_f / TILE_R : 0;
+        p.glue = g;
+    }
     int grid = p.ctas_per_split * splits;
-    if (ep.kb_map && ep.dynamic_splits && grid < 148) grid = 148;   // room for the geometry chosen on the device
+    if (ep.kb_map && ep.dynamic_splits && grid < sm_count()) grid = sm_count();   // room for the geometry chosen on the device
     switch (m.dtype) {
         case DFL_Q4_K: return ts::launch_t<DFL_Q4_K>(st, p, grid, pdl);
         case DFL_Q5_K: return ts::launch_t<DFL_Q5_K>(st, p, grid, pdl);
@@ -466,9 +491,3 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
 }
 
 }  // namespace dfl
-
-#ifdef DFL_TS_TRACE
-extern "C" int dfl_ts_trace_read(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, dfl::ts::g_ts_trace, sizeof(long long) * 5 * 512);
-}
-#endif

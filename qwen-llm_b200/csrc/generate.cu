@@ -302,8 +302,11 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         const uint32_t n_keep = dec.retain_input_count;
         // ---- margin guard (qwen/dflash.rs:859-1057): count committed rows whose gap is below the margin ----
         if (!sampled && params->verify_margin > 0.f) {
-            for (uint32_t r = 0; r < n_keep; ++r)
-                if (gap[r] < params->verify_margin) { ++st.fallback_steps; break; }
+            uint32_t flagged = 0;
+            for (uint32_t r = 0; r < n_keep; ++r) flagged += gap[r] < params->verify_margin;
+            st.committed_rows += n_keep;
+            st.margin_rows += flagged;
+            if (flagged) ++st.fallback_steps;
         }
         // ---- append captured hiddens of the committed rows, then roll the target back ----
         const double t_app = now_ms();

@@ -15,83 +15,7 @@ namespace dfl {
 __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
     pdl_prologue();
     const int n_splits = p.splits_dev ? p.splits + *p.splits_dev : p.splits;
-    const int cb = blockIdx.x, tok = threadIdx.x >> 4, quad = threadIdx.x & 15;
-    const int col0 = cb * GLUE_COLS + quad * 4;
-    const bool live = tok < p.n_rows;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (live) {
-        if (p.mode == GLUE_SWIGLU) {
-            // route weight of this row for the expert the columns belong to (1 without routing); a row that did not
-            // choose the expert gets exact zeros and its partial sums - possibly stale - are not even read
-            float w = 1.f;
-            if (p.route_w) w = col0 < p.route_n * p.route_f ? p.route_w[tok * p.route_e + p.route_e0 + col0 / p.route_f] : p.route_sg[tok];
-            if (w != 0.f) {
-                float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
-                const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
-                const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
-#pragma unroll 4
-                for (int s = 0; s < n_splits; ++s) {
-                    const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
-                    const float4 b = *reinterpret_cast<const float4*>(base + s * stride + p.swiglu_f);
-                    g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
-                    u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[j] = silu_f(g[j]) * u[j];
-                if (p.route_w) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] *= w;
-                }
-            }
-        } else {
-            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (p.x) xv = *reinterpret_cast<const float4*>(p.x + (uint64_t)tok * p.ld_x + col0);
-            if (p.mode == GLUE_RESID && p.part) {
-                // sum the split-K partials first (fixed order), then add to the residual
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
-                const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
-#pragma unroll 4
-                for (int s = 0; s < n_splits; ++s) {
-                    const float4 a = *reinterpret_cast<const float4*>(base + s * stride);
-                    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-                }
-                v[0] = xv.x + acc[0]; v[1] = xv.y + acc[1]; v[2] = xv.z + acc[2]; v[3] = xv.w + acc[3];
-                if (p.x) *reinterpret_cast<float4*>(p.x + (uint64_t)tok * p.ld_x + col0) = make_float4(v[0], v[1], v[2], v[3]);
-            } else {
-                v[0] = xv.x; v[1] = xv.y; v[2] = xv.z; v[3] = xv.w;
-            }
-        }
-        if (p.capture)
-            *reinterpret_cast<float4*>(p.capture + (uint64_t)tok * p.ld_capture + col0) = make_float4(v[0], v[1], v[2], v[3]);
-    }
-    if (p.sumsq) {
-        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (quad == 0) p.sumsq[cb * MAX_ROWS + tok] = ss;
-    }
-    if (p.mul_w) {
-        const float4 w = *reinterpret_cast<const float4*>(p.mul_w + col0);
-        v[0] *= w.x; v[1] *= w.y; v[2] *= w.z; v[3] *= w.w;
-    }
-    if (p.pre_scale != 1.f) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] *= p.pre_scale;
-    }
-    if (p.xn && live) *reinterpret_cast<float4*>(p.xn + (uint64_t)tok * p.ld_xn + col0) = make_float4(v[0], v[1], v[2], v[3]);
-    if (p.acts) {
-        uint8_t* chunk = p.acts + (uint64_t)(col0 >> 8) * act_chunk_dev(p.bf3);
-        bool over = false;
-        pack_quad_any(chunk, p.bf3, tok, col0 & 255, v, over);
-        if ((p.bf3 == ACT_F16 || p.bf3 == ACT_TS)) {
-            float sum = v[0] + v[1] + v[2] + v[3];  // 32-column sub-block = eight neighbouring threads
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if ((quad & 7) == 0) store_subsum(chunk, p.bf3, tok, (col0 & 255) >> 5, sum, over);
-        }
-        if (over) atomicCAS(p.err, 0, DEV_ERR_OVERFLOW);
-    }
+    glue_quad(p, n_splits, blockIdx.x, threadIdx.x >> 4, threadIdx.x & 15);
 }
 
 dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k) {

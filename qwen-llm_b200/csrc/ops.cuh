@@ -101,6 +101,90 @@ struct GlueParams {
     int n_rows = 0;
     int* err = nullptr;
 };
+#ifdef __CUDACC__
+// The glue of one (token, four consecutive columns) item: columns 64 cb + 4 quad .. + 3 of token `tok`.  The 32 lanes of
+// the calling warp must be two tokens x the sixteen quads of one 64-column block (lane = 16 (tok & 1) + quad): the sum
+// of squares is reduced over a token's 16 lanes and the 32-column sub-block sums over 8 lanes.  Shared by the
+// standalone glue kernel and the few-row GEMM that finishes its own output tiles.
+__device__ __forceinline__ void glue_quad(const GlueParams& p, int n_splits, int cb, int tok, int quad) {
+    const int col0 = cb * GLUE_COLS + quad * 4;
+    const bool live = tok < p.n_rows;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        if (p.mode == GLUE_SWIGLU) {
+            // route weight of this row for the expert the columns belong to (1 without routing); a row that did not
+            // choose the expert gets exact zeros and its partial sums - possibly stale - are not even read
+            float w = 1.f;
+            if (p.route_w) w = col0 < p.route_n * p.route_f ? p.route_w[tok * p.route_e + p.route_e0 + col0 / p.route_f] : p.route_sg[tok];
+            if (w != 0.f) {
+                float g[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+                const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
+                const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
+#pragma unroll 4
+                for (int s = 0; s < n_splits; ++s) {
+                    const float4 a = __ldcg(reinterpret_cast<const float4*>(base + s * stride));
+                    const float4 b = __ldcg(reinterpret_cast<const float4*>(base + s * stride + p.swiglu_f));
+                    g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+                    u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = silu_f(g[j]) * u[j];
+                if (p.route_w) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] *= w;
+                }
+            }
+        } else {
+            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.x) xv = *reinterpret_cast<const float4*>(p.x + (uint64_t)tok * p.ld_x + col0);
+            if (p.mode == GLUE_RESID && p.part) {
+                // sum the split-K partials first (fixed order), then add to the residual
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const float* base = p.part + (uint64_t)tok * p.ld_part + col0;
+                const uint64_t stride = (uint64_t)MAX_ROWS * p.ld_part;
+#pragma unroll 4
+                for (int s = 0; s < n_splits; ++s) {
+                    const float4 a = __ldcg(reinterpret_cast<const float4*>(base + s * stride));
+                    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+                }
+                v[0] = xv.x + acc[0]; v[1] = xv.y + acc[1]; v[2] = xv.z + acc[2]; v[3] = xv.w + acc[3];
+                if (p.x) *reinterpret_cast<float4*>(p.x + (uint64_t)tok * p.ld_x + col0) = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+                v[0] = xv.x; v[1] = xv.y; v[2] = xv.z; v[3] = xv.w;
+            }
+        }
+        if (p.capture)
+            *reinterpret_cast<float4*>(p.capture + (uint64_t)tok * p.ld_capture + col0) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    if (p.sumsq) {
+        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (quad == 0) p.sumsq[cb * MAX_ROWS + tok] = ss;
+    }
+    if (p.mul_w) {
+        const float4 w = *reinterpret_cast<const float4*>(p.mul_w + col0);
+        v[0] *= w.x; v[1] *= w.y; v[2] *= w.z; v[3] *= w.w;
+    }
+    if (p.pre_scale != 1.f) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] *= p.pre_scale;
+    }
+    if (p.xn && live) *reinterpret_cast<float4*>(p.xn + (uint64_t)tok * p.ld_xn + col0) = make_float4(v[0], v[1], v[2], v[3]);
+    if (p.acts) {
+        uint8_t* chunk = p.acts + (uint64_t)(col0 >> 8) * act_chunk_dev(p.bf3);
+        bool over = false;
+        pack_quad_any(chunk, p.bf3, tok, col0 & 255, v, over);
+        if ((p.bf3 == ACT_F16 || p.bf3 == ACT_TS)) {
+            float sum = v[0] + v[1] + v[2] + v[3];  // 32-column sub-block = eight neighbouring threads
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if ((quad & 7) == 0) store_subsum(chunk, p.bf3, tok, (col0 & 255) >> 5, sum, over);
+        }
+        if (over) atomicCAS(p.err, 0, DEV_ERR_OVERFLOW);
+    }
+}
+#endif
 // k = number of columns (multiple of 256)
 dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k);
 // Softmax + top-k routing of n_rows tokens over n_expert experts; logits[tok][n_expert] is the extra router row of
@@ -171,13 +255,13 @@ struct GdnGeom {
 // conv1d + SiLU over the block, q/k L2 norm; keeps raw qkv rows for rollback; updates conv state in place.
 dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
                             const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v, float* conv_pre = nullptr);
-// Sequential delta-rule scan over n_rows tokens from state_in to state_out (different buffers).
+// Sequential delta-rule scan over n_rows tokens from state_in to state_out (different buffers).  With `acts` it also
+// applies y = rmsnorm(o; eps*hd) * w * silu(z), z = sum of the z-GEMM partials, and packs the activations of out_proj;
+// acts == nullptr advances the state only (the re-scan of a partial accept).
 dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state_in, float* state_out, const float* q_n,
                            const float* k_n, const float* v, const float* ab, const float* dt_bias, const float* a_log,
-                           int n_rows, float* o);
-// y = rmsnorm(o; eps*hd) * w * silu(z), z = sum of the z-GEMM partials; packs activations for out_proj.
-dfl_status launch_gdn_post(cudaStream_t st, const GdnGeom& g, const float* o, const float* part_z, int splits, int ld_part,
-                           const float* norm_w, int n_rows, uint8_t* acts, int act_layout, int* err);
+                           int n_rows, const float* part_z, int z_splits, int ld_part, const float* norm_w, uint8_t* acts,
+                           int act_layout, int* err);
 // conv state := last (conv_k-1) rows of {pre-block conv rows, raw qkv rows 0..n_keep-1}
 dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const float* conv_pre, const float* qkv_raw, int n_keep,
                                    float* conv_state);
