@@ -302,6 +302,44 @@ def run_reference(args, rank, world):
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
+def with_secondary(line, args, rank, world, local):
+    """On more than one GPU the same launch also measures the two partitions that are not plain replicas and appends them
+    to the line as `secondary`: 32 sampled sequences split over the GPUs (strong scaling, end to end), and the packed
+    verify of the routed-expert model with its experts split over the GPUs.  A watchdog prints the primary line and ends
+    every rank if the extra measurements do not finish in time, so they can never cost the primary result."""
+    import signal
+    import copy
+
+    def bail(signum, frame):
+        if rank == 0:
+            line["secondary"] = {"error": "secondary measurements did not finish within the time limit"}
+            print(json.dumps(line), flush=True)
+        os._exit(0)
+
+    signal.signal(signal.SIGALRM, bail)
+    signal.alarm(int(os.environ.get("DFL_BENCH_SECONDARY_LIMIT_S", "420")))
+    c2 = importlib.import_module("bench_c2")
+    sec = {}
+    a3 = copy.copy(args)
+    a3.workload, a3.steps, a3.warmup = "c3", 10, 3
+    try:
+        l3 = c2.run_c3(a3, rank, world, local)
+        sec["c3_sampled_32_sequences"] = {"value": l3["value"], "unit": l3["unit"], "e2e": l3["e2e"]["value"], "scaling": l3.get("scaling"),
+                                          "per_outer_step_ms": l3.get("per_outer_step_ms"), "workload": l3["config"]["workload"]}
+    except Exception as e:
+        sec["c3_sampled_32_sequences"] = {"error": f"{type(e).__name__}: {e}"}
+    a4 = copy.copy(args)
+    a4.workload, a4.steps, a4.warmup = "c4v", 10, 3
+    try:
+        l4 = c2.run_verify_only(a4, rank, world, local)
+        sec["c4_routed_expert_verify"] = {"ms_per_verify": l4["value"], "parallelism": l4.get("parallelism"), "workload": l4["config"]["workload"]}
+    except Exception as e:
+        sec["c4_routed_expert_verify"] = {"error": f"{type(e).__name__}: {e}"}
+    signal.alarm(0)
+    line["secondary"] = sec
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -337,6 +375,8 @@ def main():
     else:
         c2 = importlib.import_module("bench_c2")
         line = c2.run(args, rank, world, local)
+        if world > 1 and args.workload == "c2" and os.environ.get("DFL_BENCH_SECONDARY", "1") != "0":
+            line = with_secondary(line, args, rank, world, local)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

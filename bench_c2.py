@@ -1,5 +1,5 @@
 """Workload c2 of bench.py: greedy DFlash decode, 9B-class hybrid Q4_K_M target + 5-layer bf16 drafter,
-batch 1, prompt 512 random ids, block 16 (BASELINE config 2).
+batch 1, prompt 512 random ids, block 16.
 
 One bench "step" is one DFlash outer step: draft 16 -> packed verify of 16 rows -> accept prefix ->
 context append -> rollback.  Random-init weights make the drafter's own acceptance ~0, so acceptance
@@ -490,7 +490,7 @@ def forced(vocab, tok):
 
 
 def run_c3(args, rank, world, device):
-    """BASELINE config 3: the config-2 target and drafter, sampled acceptance (temperature 0.7, top-p 0.95, fixed
+    """Sampled acceptance on the dense target and its drafter: sampled acceptance (temperature 0.7, top-p 0.95, fixed
     seeds, rejection sampling with one-hot coupling of the greedy drafts as the reference does for a drafter without
     selector, qwen/dflash.rs:508-522), 32 independent sequences with 1024-id prompts split round-robin over the GPUs.
     A step is one outer step of every sequence this rank owns.  Acceptance is controlled as in workload c2: the drafts

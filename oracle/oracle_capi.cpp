@@ -183,6 +183,22 @@ int orc_num_threads() {
 #endif
 }
 
+// The scalar primitives on their own (forward.rs:1256-1309), for the reference's known-answer checks (forward.rs:1377-1414).
+// kind: 0 rms_norm(x, w, eps) -> out, 1 l2_norm_in_place(eps), 2 softmax_in_place, 3 silu, 4 softplus, 5 sigmoid (element-wise).
+int orc_primitive(int32_t kind, const float* x, uint64_t n, const float* w, float eps, float* out) {
+    ORC_TRY
+    switch (kind) {
+        case 0: { auto y = rms_norm(x, n, w, eps); std::copy(y.begin(), y.end(), out); break; }
+        case 1: std::copy(x, x + n, out); l2_norm_in_place(out, n, eps); break;
+        case 2: std::copy(x, x + n, out); softmax_in_place(out, n); break;
+        case 3: for (uint64_t i = 0; i < n; ++i) out[i] = silu(x[i]); break;
+        case 4: for (uint64_t i = 0; i < n; ++i) out[i] = softplus(x[i]); break;
+        case 5: for (uint64_t i = 0; i < n; ++i) out[i] = sigmoid(x[i]); break;
+        default: throw std::runtime_error("oracle: unknown primitive");
+    }
+    ORC_CATCH
+}
+
 // Sets the number of OpenMP threads the timed CPU baseline uses (a launcher may have exported OMP_NUM_THREADS=1);
 // returns the count in effect.
 int orc_set_num_threads(int n) {

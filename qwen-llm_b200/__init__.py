@@ -11,7 +11,7 @@ import os
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("DFL_LIB_PATH") or os.path.join(HERE, "libdflash_b200.so")
+LIB_PATH = os.path.join(HERE, "libdflash_b200.so")
 
 F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 8, 12, 13, 14, 30
 MAX_BLOCK = 16
@@ -180,7 +180,7 @@ def argmax_top2_static(logits_ptr, n_rows, vocab, ld, argmax_ptr, gap_ptr, strea
 
 
 class C1Pipeline:
-    """BASELINE config 1: logits = head(x W1^T), row argmax, greedy prefix acceptance."""
+    """The CPU-runnable verify / accept case: logits = head(x W1^T), row argmax, greedy prefix acceptance."""
 
     def __init__(self, w1: QMatrix, head: QMatrix):
         self.w1, self.head = w1, head

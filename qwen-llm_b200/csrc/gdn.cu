@@ -17,105 +17,33 @@ namespace dfl {
 namespace cg = cooperative_groups;
 
 // ---- front: conv1d(K=4) + SiLU over the block, q/k L2 norm -------------------------------
-// grid = conv_dim / 128 (one q, k or v head per CTA), block 512: thread = (channel, group of four rows).  The
-// convolution is a 4-tap filter over {three state rows, the block's rows}, so the row groups are independent; every
-// thread loads the seven inputs its four rows see before any arithmetic starts.
-__global__ void __launch_bounds__(512) gdn_front_kernel(GdnGeom g, const float* part, int splits, int ld_part, int n_rows,
-                                                        const float* __restrict__ conv_w, float* conv_state,
-                                                        float* qkv_raw, float* q_n, float* k_n,
-                                                        float* v_out, float* conv_pre) {
-    const int conv_dim = g.conv_dim();
-    const int tq = threadIdx.x >> 7, d = threadIdx.x & 127, i0 = 4 * tq;
-    const int c = blockIdx.x * 128 + d;
-    const int head = blockIdx.x;  // heads of 128 channels: [0, n_k) q, [n_k, 2 n_k) k, rest v
-    // filter taps and the conv state rows come before the dependency wait: the previous pass wrote the state and a
-    // pass begins with a host-to-device copy, so no kernel of this pass is its author
-    const float4 w = *reinterpret_cast<const float4*>(conv_w + c * 4);
-    // xv[k] = input at row i0 - 3 + k (rows before the block come from the conv state)
-    float xv[7];
-#pragma unroll
-    for (int k = 0; k < 7; ++k) {
-        const int row = i0 - 3 + k;
-        xv[k] = row < 0 ? __ldcg(conv_state + (row + 3) * conv_dim + c) : 0.f;
-    }
+// grid = conv_dim / 128 (one q, k or v head per CTA), block 128: warp = group of four rows, lane = four channels
+// (gdn_front_tile).  The conv state rows are read before the dependency wait: the previous pass wrote them and a
+// pass begins with a host-to-device copy, so no kernel of this pass is their author.
+__global__ void __launch_bounds__(128) gdn_front_kernel(const GdnFrontParams p) {
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, head = blockIdx.x;
+    float4 old[3] = {};
+    if (w == 0) gdn_front_old_state(p, head, lane, old);
     pdl_prologue();
-#pragma unroll 4
-    for (int s = 0; s < splits; ++s) {
-        const float* base = part + (uint64_t)s * MAX_ROWS * ld_part + c;
-#pragma unroll
-        for (int k = 0; k < 7; ++k) {
-            const int row = i0 - 3 + k;
-            if (row >= 0 && row < n_rows) xv[k] += base[(uint64_t)row * ld_part];
-        }
-    }
-    if (conv_pre && tq == 0) {   // the pre-block rows a partial accept restores from
-        conv_pre[0 * conv_dim + c] = xv[0];
-        conv_pre[1 * conv_dim + c] = xv[1];
-        conv_pre[2 * conv_dim + c] = xv[2];
-    }
-    float y[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        y[j] = 0.f;
-        if (i0 + j < n_rows) {
-            qkv_raw[(uint64_t)(i0 + j) * conv_dim + c] = xv[j + 3];
-            // s = sum_k w[k] * window[k], k ascending (forward.rs:1000-1010)
-            float sacc = 0.f;
-            sacc += w.x * xv[j];
-            sacc += w.y * xv[j + 1];
-            sacc += w.z * xv[j + 2];
-            sacc += w.w * xv[j + 3];
-            y[j] = silu_f(sacc);
-        }
-    }
-    __syncthreads();   // every read of the old conv state is done
-    // new state = the last three rows of {old state rows, block rows}: row n_rows + t of that sequence, t = 0..2
-#pragma unroll
-    for (int t = 0; t < 3; ++t) {
-        const int v = n_rows + t;          // index into the virtual sequence
-        if (v < 3) {
-            if (tq == 0) conv_state[t * conv_dim + c] = xv[v];
-        } else if (v - 3 >= i0 && v - 3 < i0 + 4) {
-            conv_state[t * conv_dim + c] = xv[v - 3 - i0 + 3];
-        }
-    }
-    const bool is_v = head >= 2 * g.n_k;
-    if (!is_v) {
-        // y / max(||y||, eps) over the head's 128 channels, all rows at once (forward.rs:1269-1275)
-        __shared__ float red[16][4];
-        __shared__ float inv[MAX_ROWS];
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float sq = warp_sum(y[j] * y[j]);
-            if (lane == 0) red[warp][j] = sq;
-        }
-        __syncthreads();
-        if (threadIdx.x < MAX_ROWS) {
-            const int q = threadIdx.x >> 2, j = threadIdx.x & 3;   // row 4 q + j: warps 4 q .. 4 q + 3 in channel order
-            const float tot = red[4 * q][j] + red[4 * q + 1][j] + red[4 * q + 2][j] + red[4 * q + 3][j];
-            inv[threadIdx.x] = 1.0f / fmaxf(sqrtf(tot), 1e-6f);
-        }
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) y[j] *= inv[i0 + j];
-    }
-    float* dst = is_v ? v_out + (uint64_t)(head - 2 * g.n_k) * 128 + d
-                      : (head < g.n_k ? q_n + (uint64_t)head * 128 + d : k_n + (uint64_t)(head - g.n_k) * 128 + d);
-    const int dst_ld = is_v ? g.n_v * 128 : g.n_k * 128;
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-        if (i0 + j < n_rows) dst[(uint64_t)(i0 + j) * dst_ld] = y[j];
+    __syncthreads();   // the old state has been read before any warp writes the new one
+    gdn_front_tile(p, head, w, lane, old);
+}
+
+dfl_status launch_gdn_front_p(cudaStream_t st, const GdnFrontParams& p) {
+    if (p.g.hd != 128 || p.g.conv_k != 4) return fail(DFL_ERR_UNSUPPORTED, "gdn: head_dim must be 128 and conv kernel 4");
+    launch_kf(8, gdn_front_kernel, dim3(p.g.conv_dim() / 128), dim3(128), 0, st, p);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
 }
 
 dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
                             const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v, float* conv_pre) {
-    if (g.hd != 128 || g.conv_k != 4) return fail(DFL_ERR_UNSUPPORTED, "gdn: head_dim must be 128 and conv kernel 4");
-    launch_kf(8, gdn_front_kernel, dim3(g.conv_dim() / 128), dim3(512), 0, st, g, part_qkv, splits, ld_part, n_rows, conv_w, conv_state, qkv_raw, q_n, k_n, v,
-              conv_pre);
-    count_launch();
-    DFL_CUDA(cudaGetLastError());
-    return DFL_OK;
+    GdnFrontParams p;
+    p.g = g;
+    p.part = part_qkv; p.splits = splits; p.ld_part = ld_part; p.n_rows = n_rows;
+    p.conv_w = conv_w; p.conv_state = conv_state; p.qkv_raw = qkv_raw; p.q_n = q_n; p.k_n = k_n; p.v_out = v; p.conv_pre = conv_pre;
+    return launch_gdn_front_p(st, p);
 }
 
 __global__ void gdn_conv_restore_kernel(int conv_dim, const float* conv_pre, const float* qkv_raw, int n_keep,

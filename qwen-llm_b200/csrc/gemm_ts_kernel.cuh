@@ -10,7 +10,6 @@
 //   16 unpacking warps  full[slot]       -> registers -> a_free[buf]?      -> tcgen05.st -> a_ready[buf], empty[slot]
 //   MMA warp            a_ready[buf], d_free[acc]? -> 16 (+1) tcgen05.mma  -> commit: a_free[buf], d_ready[acc]
 //   4 draining warps    d_ready[acc]     -> tcgen05.ld -> d_free[acc]      -> scale, add; tile end: global store
-//                       (+ optionally: count the tile's slices; the CTA that wrote the last one runs the glue step)
 //
 // The super-block scales d / dmin of an entry travel from the unpacking threads to the draining
 // thread of the same row through a four-slot shared-memory side buffer (slot = entry & 3).
@@ -33,12 +32,6 @@ struct Params {
     const int32_t* n_tiles;
     const int32_t* kb_map;     // optional: column blocks to sum over, and how many (device memory)
     const int32_t* n_kb;
-    // optional: the glue step the CTA that completes an output tile runs on it (fuse_mode: 0 none, else a GlueMode + 1)
-    int fuse_on;
-    int32_t* fuse_counters;    // [row tile] (residual glue) or [gate tile] (SwiGLU: a gate tile and its up tile share one)
-    int fuse_target;           // slices that complete a counter: splits, or 2 x splits for a gate / up pair
-    int fuse_pair_tiles;       // SwiGLU: the up tile of gate tile t is t + fuse_pair_tiles
-    GlueParams glue;
 };
 
 constexpr int SCL_BYTES = 4 * TILE_R * 8;   // four entries' {d, dmin} per row
@@ -59,7 +52,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     constexpr int OFF_SCL = OFF_RING + STAGES * F::STAGE;
     constexpr int OFF_BAR = OFF_SCL + SCL_BYTES;
     static_assert(OFF_BAR + 256 <= 227 * 1024, "shared memory budget");
-    static_assert(2 * STAGES + KC + 10 <= 32, "barrier area");
+    static_assert(2 * STAGES + KC + 8 <= 32, "barrier area");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* acts_res = smem;
     uint8_t* ring = smem + OFF_RING;
@@ -71,9 +64,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     uint64_t* a_free = a_ready + 2;       // [pass buffer] the MMAs of that pass have completed
     uint64_t* d_ready = a_free + 2;       // [accumulator] every MMA of an entry has completed
     uint64_t* d_free = d_ready + 2;       // [accumulator] the draining warps have read it back
-    uint64_t* fin_written = d_free + 2;   // the draining warps have written (and fenced) the tile's partial slice
-    uint64_t* fin_verdict = fin_written + 1;   // ... and the tile's slice count has been taken
-    __shared__ int fin_last;
     __shared__ uint32_t tmem_slot;
     __shared__ float tok_scale[MAX_ROWS];
     __shared__ int abort_flag;
@@ -110,8 +100,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
             mbar_init(&d_ready[i], 1);
             mbar_init(&d_free[i], DRAIN_WARPS);
         }
-        mbar_init(fin_written, DRAIN_WARPS);
-        mbar_init(fin_verdict, 1);
+
         abort_flag = 0;
         mbar_fence_init();
     }
@@ -312,36 +301,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                 }
 #pragma unroll
                 for (int j = 0; j < MAX_ROWS; ++j) acc[j] = 0.f;
-                if (p.fuse_on) {
-                    // Count this slice of the tile.  Every wait is bounded (no CTA-wide barrier here: a warp that gave
-                    // up elsewhere must not be waited for), the reduction order of the glue step is fixed, so the
-                    // result does not depend on which CTA happens to be last.
-                    __threadfence();   // this thread's slice is visible device-wide before the count moves
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(fin_written);
-                    const int gtile = p.tile_map ? p.tile_map[slot] : slot;
-                    const int ctr = p.fuse_pair_tiles > 0 ? gtile % p.fuse_pair_tiles : gtile;
-                    if (dtid == 0) {
-                        bool w = mbar_wait_bounded(fin_written, (uint32_t)tile & 1, p.err, DEV_ERR_WAIT_FULL);
-                        int last = 0;
-                        if (w) {
-                            last = atomicAdd(&p.fuse_counters[ctr], 1) == p.fuse_target - 1;
-                            if (last) p.fuse_counters[ctr] = 0;   // nobody else touches it any more: ready for the next launch
-                        }
-                        fin_last = last;
-                        mbar_arrive(fin_verdict);
-                    }
-                    ok = mbar_wait_bounded(fin_verdict, (uint32_t)tile & 1, p.err, DEV_ERR_WAIT_FULL);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    if (fin_last) {
-                        __threadfence();   // the other CTAs' slices, counted before ours, are visible
-                        // 128 columns x 16 tokens as four items per thread: (token half, 64-column half)
-#pragma unroll
-                        for (int it = 0; it < 4; ++it)
-                            glue_quad(p.glue, p.glue.splits, 2 * ctr + (it & 1), 8 * (it >> 1) + (dtid >> 4), dtid & 15);
-                    }
-                }
             }
         }
         if (!ok) abort_flag = 1;
@@ -461,25 +420,6 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
     p.n_tiles = ep.n_tiles;
     p.kb_map = ep.kb_map;
     p.n_kb = ep.n_kb;
-    p.fuse_on = 0;
-    p.fuse_counters = nullptr;
-    p.fuse_target = 0;
-    p.fuse_pair_tiles = 0;
-    p.glue = GlueParams{};
-    if (ep.fuse) {
-        const GlueParams& g = *ep.fuse;
-        const bool swiglu = g.mode == GLUE_SWIGLU;
-        // whole tiles only, no lists (a repeated tile would be counted twice), slices where the glue step expects them
-        if (!ep.fuse_counters || ep.tile_map || ep.kb_map || m.n_out % TILE_R || g.part != out || g.splits != splits || g.splits_dev ||
-            (uint32_t)g.ld_part != p.ld_out || g.route_w || (swiglu && (g.swiglu_f % TILE_R || (uint64_t)2 * g.swiglu_f != m.n_out)) ||
-            (ep.sumsq && g.sumsq == ep.sumsq) || g.acts == acts)   // a CTA may still be reading what an early finisher would overwrite
-            return fail(DFL_ERR_BAD_ARG, "gemm: this launch cannot finish its own tiles");
-        p.fuse_on = 1;
-        p.fuse_counters = ep.fuse_counters;
-        p.fuse_target = swiglu ? 2 * splits : splits;
-        p.fuse_pair_tiles = swiglu ? g.swiglu_f / TILE_R : 0;
-        p.glue = g;
-    }
     int grid = p.ctas_per_split * splits;
     if (ep.kb_map && ep.dynamic_splits && grid < sm_count()) grid = sm_count();   // room for the geometry chosen on the device
     switch (m.dtype) {

@@ -14,22 +14,6 @@ dfl_status launch_group(cudaStream_t st, const MatGroup& g, const uint8_t* acts,
 }
 
 // A group of one K-quant matrix on the tensor-memory kernel can run the glue step that follows it inside the GEMM.
-bool group_can_finish_tiles(const MatGroup& g) {
-    static const bool enabled = [] { const char* e = getenv("DFL_FUSED_GLUE"); return !(e && e[0] == '0'); }();
-    return enabled && g.mats.size() == 1 && g.mats[0].layout == LAYOUT_TS && g.mats[0].dtype != DFL_BF16 && g.mats[0].n_out % TILE_R == 0;
-}
-// The GEMM, then the glue step `glue` on its output: inside the GEMM when the group allows it, else as its own kernel.
-dfl_status launch_group_glue(cudaStream_t st, const MatGroup& g, const uint8_t* acts, float* part, GemmEpilogue ep, const GlueParams& glue,
-                             uint64_t glue_cols, int32_t* counters, int* err) {
-    if (counters && group_can_finish_tiles(g) && !glue.splits_dev && !glue.route_w) {
-        ep.fuse = &glue;
-        ep.fuse_counters = counters;
-        return launch_group(st, g, acts, part, ep, err);
-    }
-    DFL_CHECK(launch_group(st, g, acts, part, ep, err));
-    return launch_glue(st, glue, glue_cols);
-}
-
 static uint64_t tensor_elems(const dfl_tensor* t) {
     uint64_t n = 1;
     for (int i = 0; i < t->n_dims; ++i) n *= t->shape[i];
@@ -214,8 +198,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
     DFL_CUDA(cudaMemcpyAsync(sc->tokens_dev, sc->pinned_i, n * sizeof(int32_t), cudaMemcpyHostToDevice, st));
     DFL_CHECK(launch_embed_rows(st, m->embd_dtype, m->embd_ggml, H, sc->tokens_dev, (int)n, sc->x, (int)H));
 
-    auto norm_glue_params = [&](const float* part, int splits, int ld_part, const float* norm_w, bool want_xn, float* capture,
-                                const int32_t* splits_dev = nullptr) {
+    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* norm_w, bool want_xn, float* capture,
+                         const int32_t* splits_dev = nullptr) -> dfl_status {
         GlueParams p;
         p.mode = GLUE_RESID;
         p.part = part; p.splits = splits; p.splits_dev = splits_dev; p.ld_part = ld_part;
@@ -226,14 +210,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         p.sumsq = sc->sumsq;
         p.capture = capture; p.ld_capture = (int)(sc->k_layers * H);
         p.n_rows = (int)n; p.err = s->err;
-        return p;
+        return launch_glue(st, p, H);
     };
-    auto norm_glue = [&](const float* part, int splits, int ld_part, const float* norm_w, bool want_xn, float* capture,
-                         const int32_t* splits_dev = nullptr) -> dfl_status {
-        return launch_glue(st, norm_glue_params(part, splits, ld_part, norm_w, want_xn, capture, splits_dev), H);
-    };
-    // tile counters of the GEMMs that finish their own output: zero at the start of every pass (a failed pass may leave some)
-    DFL_CUDA(cudaMemsetAsync(sc->tile_counters, 0, sizeof(int32_t) * kTileCounters, st));
     DFL_CHECK(norm_glue(nullptr, 0, 0, m->layers[0].attn_norm_w, !m->layers[0].is_attn, nullptr));
 
     int gi = 0, ai = 0;
@@ -272,9 +250,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             ++gi;
         }
         const bool moe = a.expert_count > 0;
-        DFL_CHECK(launch_group_glue(st, *out_proj, sc->acts_v, sc->part, GemmEpilogue{},
-                                    norm_glue_params(sc->part, out_proj->splits, (int)out_proj->total_cols, L.post_norm_w, moe, nullptr), H,
-                                    sc->tile_counters, s->err));
+        DFL_CHECK(launch_group(st, *out_proj, sc->acts_v, sc->part, GemmEpilogue{}, s->err));
+        DFL_CHECK(norm_glue(sc->part, out_proj->splits, (int)out_proj->total_cols, L.post_norm_w, moe, nullptr));
         int down_splits;
         const int32_t* down_splits_dev = nullptr;
         const float* moe_part = sc->part;
@@ -363,7 +340,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             p.pre_scale = 1.0f / 64.0f;  // keeps silu(g)*u inside the f16 operand range; undone in the GEMM epilogue
             p.acts = sc->acts_f; p.bf3 = m->act_layout;
             p.n_rows = (int)n; p.err = s->err;
-            DFL_CHECK(launch_group_glue(st, L.gate_up, sc->acts_h, sc->part, ep_norm, p, F, sc->tile_counters, s->err));
+            DFL_CHECK(launch_group(st, L.gate_up, sc->acts_h, sc->part, ep_norm, s->err));
+            DFL_CHECK(launch_glue(st, p, F));
         }
         down_splits = L.down.splits;
         }
@@ -373,15 +351,12 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         const bool last = il + 1 == a.n_layer;
         const float* next_w = last ? m->out_norm_w : m->layers[il + 1].attn_norm_w;
         const bool next_gdn = !last && !m->layers[il + 1].is_attn;
-        if (moe) {
-            DFL_CHECK(norm_glue(moe_part, down_splits, (int)H, next_w, next_gdn, cap, down_splits_dev));
-        } else {
-            // the down projection, the residual add and the next layer's norm fold in one launch
+        if (!moe) {
             GemmEpilogue ep_down;
             ep_down.out_scale = 64.0f;
-            DFL_CHECK(launch_group_glue(st, L.down, sc->acts_f, sc->part, ep_down, norm_glue_params(sc->part, down_splits, (int)H, next_w, next_gdn, cap), H,
-                                        sc->tile_counters, s->err));
+            DFL_CHECK(launch_group(st, L.down, sc->acts_f, sc->part, ep_down, s->err));
         }
+        DFL_CHECK(norm_glue(moe_part, down_splits, (int)H, next_w, next_gdn, cap, down_splits_dev));
         if (cap) {
             // duplicate slots (same layer listed twice) get a device copy of the first one
             bool first = true;
@@ -800,7 +775,6 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
     { uint8_t* am = nullptr; alloc(&am, MAX_ROWS * ARGMAX_PARTS * 16); sc->am_scratch = am; }
     alloc(&sc->capture, (size_t)MAX_ROWS * sc->k_layers * H * 4);
     alloc(&sc->tokens_dev, MAX_ROWS * 4);
-    alloc(&sc->tile_counters, sizeof(int32_t) * kTileCounters);
     ok = ok && cudaMallocHost(&sc->pinned_i, 2 * MAX_ROWS * 4) == cudaSuccess && cudaMallocHost(&sc->pinned_f, MAX_ROWS * 4) == cudaSuccess;
     if (!ok) {
         std::string why = cudaGetErrorString(cudaGetLastError());

@@ -126,8 +126,6 @@ struct dfl_session {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_join2 = nullptr;
 };
 
-constexpr int kTileCounters = 4096;   // row tiles of the widest matrix a GEMM may finish itself (524 288 output columns)
-
 struct dfl_scratch {
     const dfl_model* m = nullptr;
     uint32_t block_size = 0, k_layers = 0;
@@ -145,7 +143,6 @@ struct dfl_scratch {
     void* am_scratch = nullptr;
     float* capture = nullptr;  // [16][k][H]
     int32_t* tokens_dev = nullptr;
-    int32_t* tile_counters = nullptr;   // [kTileCounters] slice counts of the GEMMs that finish their own output tiles
     int32_t* pinned_i = nullptr;  // [16] tokens in, [16] argmax out
     float* pinned_f = nullptr;    // [16] gaps
     float* pinned_logits = nullptr;  // [block][vocab], made on first use by the sampled outer loop

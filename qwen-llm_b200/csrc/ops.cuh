@@ -104,8 +104,7 @@ struct GlueParams {
 #ifdef __CUDACC__
 // The glue of one (token, four consecutive columns) item: columns 64 cb + 4 quad .. + 3 of token `tok`.  The 32 lanes of
 // the calling warp must be two tokens x the sixteen quads of one 64-column block (lane = 16 (tok & 1) + quad): the sum
-// of squares is reduced over a token's 16 lanes and the 32-column sub-block sums over 8 lanes.  Shared by the
-// standalone glue kernel and the few-row GEMM that finishes its own output tiles.
+// of squares is reduced over a token's 16 lanes and the 32-column sub-block sums over 8 lanes.
 __device__ __forceinline__ void glue_quad(const GlueParams& p, int n_splits, int cb, int tok, int quad) {
     const int col0 = cb * GLUE_COLS + quad * 4;
     const bool live = tok < p.n_rows;
@@ -252,7 +251,107 @@ struct GdnGeom {
     int n_v, n_k, hd, conv_k;  // hd must be 128, conv_k 4
     __host__ __device__ int conv_dim() const { return (2 * n_k + n_v) * hd; }
 };
+// The conv + norm stage of one GDN layer (oracle: forward.rs:985-1050), as data: inputs are the split-K partial sums of
+// the qkv projection.
+struct GdnFrontParams {
+    GdnGeom g{};
+    const float* part = nullptr;   // [splits][16][ld_part], this projection's columns first
+    int splits = 0, ld_part = 0, n_rows = 0;
+    const float* conv_w = nullptr; // [conv_dim][4]
+    float* conv_state = nullptr;   // [3][conv_dim], updated in place
+    float* qkv_raw = nullptr;      // [16][conv_dim] rows of the block before the convolution (kept for rollback)
+    float *q_n = nullptr, *k_n = nullptr, *v_out = nullptr;
+    float* conv_pre = nullptr;     // [3][conv_dim] the conv state before the block (kept for rollback)
+};
+#ifdef __CUDACC__
+// The three conv-state rows of head `head` (128 channels) that precede the block, for the lane's four channels.  Only
+// the warp that owns rows 0..3 needs them; it reads them before any warp of the CTA starts to write the new state.
+__device__ __forceinline__ void gdn_front_old_state(const GdnFrontParams& p, int head, int lane, float4 (&old)[3]) {
+    const int c = head * 128 + 4 * lane, conv_dim = p.g.conv_dim();
+#pragma unroll
+    for (int t = 0; t < 3; ++t) old[t] = __ldcg(reinterpret_cast<const float4*>(p.conv_state + t * conv_dim + c));
+}
+// conv1d (4 taps) + SiLU over the block's rows and the L2 norm of q / k heads, for one head of 128 channels by four
+// warps: warp w owns rows 4w .. 4w + 3, lane owns channels 4 lane .. 4 lane + 3, so that a row's norm is one warp
+// reduction.  `old` = gdn_front_old_state (used by warp 0 only).  A row's result does not depend on n_rows.
+__device__ __forceinline__ void gdn_front_tile(const GdnFrontParams& p, int head, int w, int lane, const float4 (&old)[3]) {
+    const int conv_dim = p.g.conv_dim(), i0 = 4 * w, c = head * 128 + 4 * lane;
+    // xv[k] = input at row i0 - 3 + k (rows before the block come from the conv state)
+    float4 xv[7];
+#pragma unroll
+    for (int k = 0; k < 7; ++k) {
+        const int row = i0 - 3 + k;
+        xv[k] = (row < 0 && w == 0) ? old[k < 3 ? k : 0] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll 2
+    for (int s = 0; s < p.splits; ++s) {
+        const float* base = p.part + (uint64_t)s * MAX_ROWS * p.ld_part + c;
+#pragma unroll
+        for (int k = 0; k < 7; ++k) {
+            const int row = i0 - 3 + k;
+            if (row >= 0 && row < p.n_rows) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(base + (uint64_t)row * p.ld_part));
+                xv[k].x += a.x; xv[k].y += a.y; xv[k].z += a.z; xv[k].w += a.w;
+            }
+        }
+    }
+    if (p.conv_pre && w == 0) {   // the pre-block rows a partial accept restores from
+#pragma unroll
+        for (int t = 0; t < 3; ++t) *reinterpret_cast<float4*>(p.conv_pre + t * conv_dim + c) = xv[t];
+    }
+    // filter taps of the lane's four channels
+    float4 tap[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) tap[e] = *reinterpret_cast<const float4*>(p.conv_w + (uint64_t)(c + e) * 4);
+    float y[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const bool live = i0 + j < p.n_rows;
+        if (live) *reinterpret_cast<float4*>(p.qkv_raw + (uint64_t)(i0 + j) * conv_dim + c) = xv[j + 3];
+        const float in[4][4] = {{xv[j].x, xv[j + 1].x, xv[j + 2].x, xv[j + 3].x}, {xv[j].y, xv[j + 1].y, xv[j + 2].y, xv[j + 3].y},
+                                {xv[j].z, xv[j + 1].z, xv[j + 2].z, xv[j + 3].z}, {xv[j].w, xv[j + 1].w, xv[j + 2].w, xv[j + 3].w}};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            // s = sum_k w[k] * window[k], k ascending (forward.rs:1000-1010)
+            float sacc = 0.f;
+            sacc += tap[e].x * in[e][0];
+            sacc += tap[e].y * in[e][1];
+            sacc += tap[e].z * in[e][2];
+            sacc += tap[e].w * in[e][3];
+            y[j][e] = live ? silu_f(sacc) : 0.f;
+        }
+    }
+    // new state = the last three rows of {old state rows, block rows}: row n_rows + t of that sequence, t = 0..2
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        const int v = p.n_rows + t;          // index into the virtual sequence
+        if (v < 3) {
+            if (w == 0) *reinterpret_cast<float4*>(p.conv_state + t * conv_dim + c) = xv[v];
+        } else if (v - 3 >= i0 && v - 3 < i0 + 4) {
+            *reinterpret_cast<float4*>(p.conv_state + t * conv_dim + c) = xv[v - 3 - i0 + 3];
+        }
+    }
+    const bool is_v = head >= 2 * p.g.n_k;
+    if (!is_v) {
+        // y / max(||y||, eps) over the head's 128 channels (forward.rs:1269-1275)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float sq = warp_sum((y[j][0] * y[j][0] + y[j][1] * y[j][1]) + (y[j][2] * y[j][2] + y[j][3] * y[j][3]));
+            const float inv = 1.0f / fmaxf(sqrtf(sq), 1e-6f);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[j][e] *= inv;
+        }
+    }
+    float* dst = is_v ? p.v_out + (uint64_t)(head - 2 * p.g.n_k) * 128 + 4 * lane
+                      : (head < p.g.n_k ? p.q_n + (uint64_t)head * 128 + 4 * lane : p.k_n + (uint64_t)(head - p.g.n_k) * 128 + 4 * lane);
+    const int dst_ld = is_v ? p.g.n_v * 128 : p.g.n_k * 128;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (i0 + j < p.n_rows) *reinterpret_cast<float4*>(dst + (uint64_t)(i0 + j) * dst_ld) = make_float4(y[j][0], y[j][1], y[j][2], y[j][3]);
+}
+#endif
 // conv1d + SiLU over the block, q/k L2 norm; keeps raw qkv rows for rollback; updates conv state in place.
+dfl_status launch_gdn_front_p(cudaStream_t st, const GdnFrontParams& p);
 dfl_status launch_gdn_front(cudaStream_t st, const GdnGeom& g, const float* part_qkv, int splits, int ld_part, int n_rows,
                             const float* conv_w, float* conv_state, float* qkv_raw, float* q_n, float* k_n, float* v, float* conv_pre = nullptr);
 // Sequential delta-rule scan over n_rows tokens from state_in to state_out (different buffers).  With `acts` it also

@@ -183,7 +183,6 @@ dfl_status decode_tiles(cudaStream_t st, const QMatrix& m, float* out_dev);
 // How a GEMM output is scaled per token: y = acc * out_scale * rs[tok], with
 // rs = 1/sqrt(sum(partials)/norm_k + eps) when sumsq != nullptr (a fused RMSNorm whose
 // element-wise weight was folded into the activations), else 1.
-struct GlueParams;
 struct GemmEpilogue {
     const float* sumsq = nullptr;  // [n_sumsq][16]
     int n_sumsq = 0;
@@ -202,12 +201,6 @@ struct GemmEpilogue {
     // n_kb[1] / n_kb[2] (when n_kb[1] > 0): split count and CTAs per split to use for this list length, their product
     // at most 148, the splits at most the launch's own; the caller sums that many partial slices
     bool dynamic_splits = false;
-    // optional (tensor-memory family, no lists): the GEMM finishes its own output.  The CTA that writes the last
-    // split-K slice of a 128-column tile (counted in fuse_counters[tile], zero before the launch and again after it)
-    // runs the glue step `fuse` describes on those columns - residual add or SwiGLU, norm-weight fold, packing of
-    // the next GEMM's activations - so that no separate kernel sits between the two GEMMs.
-    const GlueParams* fuse = nullptr;
-    int32_t* fuse_counters = nullptr;
 };
 int gemm_choose_splits(const QMatrix& m);
 int gemm_max_kblocks_per_cta(int dtype);  // column blocks one CTA can keep resident

@@ -15,7 +15,7 @@ F32, F16, Q8_0, Q4_K, Q5_K, Q6_K, BF16 = pkg.F32, pkg.F16, pkg.Q8_0, pkg.Q4_K, p
 
 
 def arch_9b():
-    """BASELINE config 2: 9B-class qwen35-style hybrid (GDN:attention 3:1)."""
+    """The dense benchmark target: 9B-class qwen35-style hybrid (32 layers, GDN:attention 3:1, hidden 4096, vocabulary 151 936)."""
     a = pkg.Arch()
     for k, v in dict(n_layer=32, hidden_size=4096, intermediate_size=12288, vocab_size=151936, full_attention_interval=4,
                      n_q_heads=32, n_kv_heads=8, attn_head_dim=128, rope_theta=10000000.0, partial_rotary_factor=0.25,
@@ -26,7 +26,7 @@ def arch_9b():
 
 
 def arch_35b_a3b():
-    """BASELINE config 4: 35B-A3B-shaped qwen35moe hybrid (256 routed experts top-8 + one shared expert)."""
+    """The routed-expert benchmark target: 35B-A3B-shaped qwen35moe hybrid (256 routed experts top-8 + one shared expert)."""
     a = pkg.Arch()
     for k, v in dict(n_layer=40, hidden_size=2048, intermediate_size=0, vocab_size=151936, full_attention_interval=4,
                      n_q_heads=16, n_kv_heads=2, attn_head_dim=256, rope_theta=10000000.0, partial_rotary_factor=0.25,

@@ -115,7 +115,7 @@ def test_argmax_top2_ties_signed_zero_nan_and_gap():
 
 
 def test_config1_pipeline_matches_oracle_and_accepts_same_prefix():
-    # BASELINE config 1: 4096x4096 Q4_K, 4096 -> 32000 Q6_K head, 16 rows, greedy prefix acceptance
+    # the CPU-runnable verify / accept case at full size: 4096x4096 Q4_K, 4096 -> 32000 Q6_K head, 16 rows, greedy prefix acceptance
     h, v, n = 4096, 32000, 16
     raw1, _ = make_weight(orc.Q4_K, h, h, 101)
     raw2, _ = make_weight(orc.Q6_K, h, v, 102)
