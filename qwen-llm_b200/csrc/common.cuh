@@ -74,15 +74,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: every spin in these kernels gives up after a fixed number of polls
-// (about a second with the back-off), records why in *err and returns false, so a
-// lost copy or a logic error ends the kernel instead of hanging the GPU.
-constexpr uint32_t kWaitPolls = 1u << 22;
+// The same with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds and is woken when the
+// phase completes, so a waiting warp takes no issue slots from the warps that do the work.
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: every wait in these kernels gives up after a fixed number of polls (each may sleep up to a
+// microsecond: about a second in all), records why in *err and returns false, so a lost copy or a logic error ends
+// the kernel instead of hanging the GPU.
+constexpr uint32_t kWaitPolls = 1u << 20;
+constexpr uint32_t kWaitSleepNs = 1000;
 __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int* err, int code, uint32_t polls) {
-    for (uint32_t it = 0; it < polls; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (it > 128) __nanosleep(200);
-    }
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t it = 0; it < polls; ++it)
+        if (mbar_try_wait_for(bar, parity, kWaitSleepNs)) return true;
     atomicCAS(err, 0, code);
     return false;
 }

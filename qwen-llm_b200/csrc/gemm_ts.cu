@@ -10,10 +10,10 @@
 //     6-bit sub-block scale folded in, still exact: q * sc < 2048) and store them with
 //     tcgen05.st into tensor memory, thread = (row, quarter of the columns), row = TMEM lane.
 //     They do nothing else, so their instruction stream never waits for an accumulator;
-//   * one warp issues tcgen05.mma (A from tensor memory, B = activations hi / lo planes from
-//     shared memory, M = 128, N = 32, K = 16 per instruction), sixteen per pass, accumulating
-//     a 256-column block in tensor memory; a seventeenth MMA multiplies the sub-block mins
-//     with the per-sub-block activation sums (the K-quant "min" term);
+//   * four warps, one per scheduler, issue tcgen05.mma (A from tensor memory, B = activations
+//     hi / lo planes from shared memory, M = 128, N = 32, K = 16 per instruction), sixteen per
+//     256-column block, accumulating it in tensor memory; a seventeenth MMA multiplies the
+//     sub-block mins with the per-sub-block activation sums (the K-quant "min" term);
 //   * four draining warps (thread = weight row) read the finished block's accumulator back
 //     (tcgen05.ld), apply the per-row f16 super-block scales d and dmin in f32 and add to
 //     sixteen register accumulators (one per token); at the end of a row tile they write the
@@ -205,18 +205,20 @@ dfl_status launch_prep_acts_ts(cudaStream_t st, const float* x, int ld, int n_ro
 // ---------------------------------------------------------------------------------------------
 namespace ts {
 
-constexpr int UNPACK_WARPS = 16;                        // thread = (row = 32 * (warp % 4) + lane, kp = warp / 4: a quarter of the columns)
+constexpr int GROUP_WARPS = 8;                          // unpacking warps per group; thread = (row = 32 * (warp % 4) + lane, kp2 = (warp / 4) % 2)
+constexpr int UNPACK_WARPS = 2 * GROUP_WARPS;           // two groups that take the entries alternately, so that their phases interleave
 constexpr int DRAIN_WARP0 = 16, DRAIN_WARPS = 4;        // thread = weight row; warp % 4 = its quarter of the tensor-memory lanes
-constexpr int PRODUCER_WARP = 20, MMA_WARP = 21;
-constexpr int THREADS = 22 * 32;                        // 704
+constexpr int MMA_WARP0 = 20, MMA_WARPS = 4;            // warp 20 + 2 g + c issues the MMAs of group g's halves h with h % 2 == c
+constexpr int PRODUCER_WARP = 24;
+constexpr int THREADS = 25 * 32;                        // 800
 #ifndef DFL_TS_KC
 #define DFL_TS_KC 6
 #endif
 constexpr int KC = DFL_TS_KC;                           // column blocks whose activations stay resident
 
-// tensor-memory columns (32-bit each, 128 lanes): two pass buffers of 128 columns (256 f16 per row), per block
-// buffer two 32-column accumulators (even / odd MMA steps: two short dependency chains instead of one long one),
-// the 8-column A operand of the min term per pass buffer and its 48-column accumulator per block buffer
+// tensor-memory columns (32-bit each, 128 lanes), everything once per group: a 128-column A buffer (256 f16 per row)
+// written and consumed in two halves, two 32-column accumulators (even / odd MMA steps), the 8-column A operand of the
+// min term and its 48-column accumulator
 constexpr uint32_t TM_A = 0, TM_A_STRIDE = 128, TM_D = 256, TM_D_STRIDE = 64, TM_AM = 384, TM_AM_STRIDE = 8, TM_DM = 400, TM_DM_STRIDE = 48,
                    TM_COLS = 512;
 static_assert(TM_DM + 2 * TM_DM_STRIDE <= TM_COLS, "tensor memory budget");
@@ -242,13 +244,17 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem descriptor]; M x N x 16, f16 inputs, f32 accumulate
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem descriptor]; M x N x 16, f16 inputs, f32 accumulate.  The descriptor comes as its two
+// words so that stepping through the slices of one operand is a 32-bit add on the address field, and the accumulate
+// flag is a compile-time constant: the issuing warp shares its scheduler with unpacking warps, every instruction it
+// does not need is time the tensor pipe gets its next MMA earlier.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi, uint32_t idesc) {
     const uint32_t zero = 0;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero)
+        "{\n\t.reg .pred p;\n\t.reg .b64 dd;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 dd, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], dd, %4, {%6, %6, %6, %6}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "n"(ACCUMULATE ? 1 : 0), "r"(zero)
         : "memory");
 }
 // K-major, no swizzle: 8-row groups 128 B apart (stride offset), the two k-cores `lbo` bytes apart
@@ -346,21 +352,23 @@ struct UnitScales {
 template <int DT>
 struct Fmt;
 
-// Q4_K / Q5_K: one pass per stage.  Thread (row, kp) takes the 64 columns of quarter kp: sub-blocks 2kp (low nibbles)
-// and 2kp + 1 (high nibbles) of its row into r[0..15] / r[16..31]; r[c] = half2 of k-positions 2c, 2c + 1.
+// Q4_K / Q5_K: two halves per stage.  In half h thread (row, kp2) takes the 64 columns of quarter kp = 2h + kp2:
+// sub-blocks 2kp (low nibbles) and 2kp + 1 (high nibbles) of its row into r[0..15] / r[16..31]; r[c] = half2 of
+// k-positions 2c, 2c + 1.
 template <int DT>
 struct FmtK45 {
     static constexpr int STAGE = DT == DFL_Q4_K ? STAGE_Q4_K : STAGE_Q5_K;
     static constexpr int STAGES = KC == 4 ? (DT == DFL_Q4_K ? 7 : 6) : (DT == DFL_Q4_K ? 6 : 5);
-    static constexpr int PASSES = 1;
+    static constexpr int HALVES = 2;
     static constexpr bool HAS_MIN = true;
-    // MMA step j (0..15) of a pass multiplies pass-buffer columns a_col(j) .. + 8 with 16-column slice b_slice of the block
-    __device__ static __forceinline__ uint32_t a_col(int j) { return (uint32_t)(8 * j); }
-    __device__ static __forceinline__ uint32_t b_slice(int, int j) { return (uint32_t)j; }
-    __device__ static __forceinline__ void store(uint32_t buf, int kp, const uint32_t (&r)[32]) { tmem_st32(buf + 32 * kp, r); }
-    __device__ static __forceinline__ void unpack(const uint8_t* st, int, int row, int kp, uint32_t (&r)[32], uint32_t (&am)[8],
+    // MMA step jj (0..7) of half h multiplies A-buffer columns a_col .. + 8 with 16-column slice b_slice of the block
+    __device__ static __forceinline__ uint32_t a_col(int h, int jj) { return (uint32_t)(64 * h + 8 * jj); }
+    __device__ static __forceinline__ uint32_t b_slice(int h, int jj) { return (uint32_t)(8 * h + jj); }
+    __device__ static __forceinline__ void store(uint32_t buf, int h, int kp2, const uint32_t (&r)[32]) { tmem_st32(buf + 64 * h + 32 * kp2, r); }
+    __device__ static __forceinline__ int min_col(int h, int kp2) { return 2 * h + kp2; }
+    __device__ static __forceinline__ void unpack(const uint8_t* st, int ps, int row, int kp2, uint32_t (&r)[32], uint32_t (&am)[8],
                                                   UnitScales& us) {
-        const int ps = kp >> 1, kp2 = kp & 1;
+        const int kp = 2 * ps + kp2;
         const uint4 h = reinterpret_cast<const uint4*>(st)[row];
         const uint4* qs = reinterpret_cast<const uint4*>(st + TSQ4_OFF_QS);
         const uint4 qa = qs[(kp * 2 + 0) * 128 + row], qb = qs[(kp * 2 + 1) * 128 + row];

@@ -2,14 +2,19 @@
 //
 // CTA = one split (at most KC column blocks, activations resident) x every ctas_per_split-th
 // row tile.  Its work is the sequence of entries e = (tile, column block); the weight stage of
-// entry e travels through ring slot e % STAGES and is unpacked in PASSES passes (Q4_K / Q5_K:
-// one pass of 256 weight columns; Q6_K: two passes of 128, each written as the even / odd
-// scale parts).  Pass i uses pass buffer i & 1 of tensor memory, entry e accumulator e & 1.
+// entry e travels through ring slot e % STAGES.  The sixteen unpacking warps form two groups of
+// eight that take the entries alternately (group = e & 1), each with its own A buffer,
+// accumulators and barriers, so that one group's arithmetic fills the time the other spends
+// storing to tensor memory and waiting.  A group unpacks an entry in HALVES steps of 64 A-buffer
+// columns (Q4_K / Q5_K: two halves of 128 weight columns; Q6_K: four of 64, each written as the
+// even / odd scale parts); the MMA warp issues eight MMAs per half as soon as it is stored.
 //
-//   producer thread     ring slot free?  -> bulk copy of the stage         -> full[slot]
-//   16 unpacking warps  full[slot]       -> registers -> a_free[buf]?      -> tcgen05.st -> a_ready[buf], empty[slot]
-//   MMA warp            a_ready[buf], d_free[acc]? -> 16 (+1) tcgen05.mma  -> commit: a_free[buf], d_ready[acc]
-//   4 draining warps    d_ready[acc]     -> tcgen05.ld -> d_free[acc]      -> scale, add; tile end: global store
+//   producer thread     ring slot free?   -> bulk copy of the stage          -> full[slot]
+//   unpacking group g   full[slot]        -> registers -> a_free[g][half]?   -> tcgen05.st -> a_ready[g][half], empty[slot]
+//   MMA warp (g, c)     a_ready[g][c], d_free[g]?    -> 8 tcgen05.mma (+ min) -> commit: a_free[g][c], d_ready[g]
+//                       (c = half % 2: its MMAs accumulate into accumulator c of the group, so the order in which the
+//                       two warps of a group reach the tensor pipe does not change a bit of the result)
+//   4 draining warps    d_ready[g]        -> tcgen05.ld -> d_free[g]         -> scale, add; tile end: global store
 //
 // The super-block scales d / dmin of an entry travel from the unpacking threads to the draining
 // thread of the same row through a four-slot shared-memory side buffer (slot = entry & 3).
@@ -44,15 +49,33 @@ constexpr int smem_bytes() {
 // named barrier among the draining warps only (every one of them reaches it unconditionally)
 __device__ __forceinline__ void named_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
+// The eight MMAs of half h = 2 h2 + C of an entry into one accumulator (the first of them overwrites it when the half is
+// the accumulator's first of the entry).
+template <class F, int C>
+__device__ __forceinline__ void issue_half(int h2, uint32_t d, uint32_t a_buf, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+#pragma unroll
+    for (int hh = 0; hh < F::HALVES / 2; ++hh) {
+        if (hh != h2) continue;
+        constexpr int dummy = 0;
+        (void)dummy;
+        const int h = 2 * hh + C;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+            if (hh == 0 && jj == 0) mma_ts<false>(d, a_buf + F::a_col(h, jj), b_lo + F::b_slice(h, jj) * 64u, b_hi, idesc);
+            else mma_ts<true>(d, a_buf + F::a_col(h, jj), b_lo + F::b_slice(h, jj) * 64u, b_hi, idesc);
+        }
+    }
+}
+
 template <int DT>
 __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     using F = Fmt<DT>;
-    constexpr int STAGES = F::STAGES, PASSES = F::PASSES;
+    constexpr int STAGES = F::STAGES, HALVES = F::HALVES;
     constexpr int OFF_RING = KC * ACTTS_CHUNK;
     constexpr int OFF_SCL = OFF_RING + STAGES * F::STAGE;
     constexpr int OFF_BAR = OFF_SCL + SCL_BYTES;
     static_assert(OFF_BAR + 256 <= 227 * 1024, "shared memory budget");
-    static_assert(2 * STAGES + KC + 8 <= 32, "barrier area");
+    static_assert(2 * STAGES + KC + 12 <= 32, "barrier area");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* acts_res = smem;
     uint8_t* ring = smem + OFF_RING;
@@ -60,10 +83,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
     uint64_t* empty = full + STAGES;
     uint64_t* acts_bar = empty + STAGES;  // [column block of the CTA's range] its activations have arrived
-    uint64_t* a_ready = acts_bar + KC;    // [pass buffer] a pass of unpacked weights is in tensor memory
-    uint64_t* a_free = a_ready + 2;       // [pass buffer] the MMAs of that pass have completed
-    uint64_t* d_ready = a_free + 2;       // [accumulator] every MMA of an entry has completed
-    uint64_t* d_free = d_ready + 2;       // [accumulator] the draining warps have read it back
+    uint64_t* a_ready = acts_bar + KC;    // [group][half buffer] a half of unpacked weights is in tensor memory
+    uint64_t* a_free = a_ready + 4;       // [group][half buffer] the MMAs of that half have completed
+    uint64_t* d_ready = a_free + 4;       // [group] every MMA of an entry has completed
+    uint64_t* d_free = d_ready + 2;       // [group] the draining warps have read the accumulator back
     __shared__ uint32_t tmem_slot;
     __shared__ float tok_scale[MAX_ROWS];
     __shared__ int abort_flag;
@@ -91,20 +114,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], UNPACK_WARPS);
+            mbar_init(&empty[s], GROUP_WARPS);
         }
         for (int k = 0; k < KC; ++k) mbar_init(&acts_bar[k], 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&a_ready[i], UNPACK_WARPS);
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&a_ready[i], GROUP_WARPS);
             mbar_init(&a_free[i], 1);
-            mbar_init(&d_ready[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&d_ready[i], 2);
             mbar_init(&d_free[i], DRAIN_WARPS);
         }
 
         abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == MMA_WARP) tmem_alloc(&tmem_slot, TM_COLS);
+    if (warp == MMA_WARP0) tmem_alloc(&tmem_slot, TM_COLS);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -141,47 +166,47 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
             }
             if (!ok) abort_flag = 1;
         }
-    } else if (warp == MMA_WARP) {
-        // ------------------------------ MMA issuer ------------------------------
-        // The whole warp walks the loop so that addresses and descriptors stay warp-uniform; one elected
-        // lane issues the instructions.
+    } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + MMA_WARPS) {
+        // ------------------------------ MMA issuers ------------------------------
+        // Warp (g, c) issues the halves h with h % 2 == c of group g's entries into accumulator c of that group.  The
+        // whole warp walks the loop so that addresses and descriptors stay warp-uniform; one elected lane issues.
         constexpr uint32_t IDESC_MAIN = instr_desc(32), IDESC_MIN = instr_desc(48);
+        const uint32_t g = (uint32_t)(warp - MMA_WARP0) >> 1, c = (uint32_t)(warp - MMA_WARP0) & 1u;
         bool ok = true;
         const uint32_t acts_addr = smem_u32(acts_res);
-        uint32_t pc = 0;   // running pass count
-        for (int e = 0; e < n_it && ok; ++e) {
+        const uint32_t a_buf = tmem + TM_A + g * TM_A_STRIDE, d_buf = tmem + TM_D + g * TM_D_STRIDE + 32 * c;
+        uint32_t uses = 0;   // how often this warp's half buffer has been used
+        for (int e = (int)g; e < n_it && ok; e += 2) {
             const uint32_t chunk = acts_addr + (e % n_kb) * ACTTS_CHUNK;
-            const uint32_t acc = (uint32_t)e & 1u;
             if (e < n_kb) {   // first row tile: the column block's activations may still be in flight
                 ok = mbar_wait_bounded(&acts_bar[e], 0, p.err, DEV_ERR_WAIT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
             }
-            if (ok && e >= 2) {   // the accumulator was last used by entry e - 2
-                ok = mbar_wait_bounded(&d_free[acc], (((uint32_t)e >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
+            if (ok && e >= 2) {   // the group's accumulators were last used by entry e - 2
+                ok = mbar_wait_bounded(&d_free[g], (((uint32_t)e >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
                 ok = __all_sync(0xffffffffu, ok);
             }
+            // one descriptor per column block; a 16-column slice is 1024 bytes further = 64 in the address field (bits 0-13
+            // of the low word, which cannot carry: shared-memory addresses stay below 256 KiB)
+            const uint64_t bdesc = smem_desc(chunk, 512, 128), mdesc = smem_desc(chunk + TS_BMIN_OFF, 768, 128);
+            const uint32_t b_lo = (uint32_t)bdesc, b_hi = (uint32_t)(bdesc >> 32);
 #pragma unroll
-            for (int ps = 0; ps < PASSES; ++ps, ++pc) {
-                const uint32_t b = pc & 1;
+            for (int h2 = 0; h2 < HALVES / 2; ++h2, ++uses) {
+                const int h = 2 * h2 + (int)c;   // this warp's half; the unrolled code below needs it as a constant: see the switch on c
                 if (ok) {
-                    ok = mbar_wait_bounded(&a_ready[b], (pc >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+                    ok = mbar_wait_bounded(&a_ready[2 * g + c], uses & 1, p.err, DEV_ERR_WAIT_FULL);
                     ok = __all_sync(0xffffffffu, ok);
                 }
                 if (ok) {
                     fence_after_sync();
                     if (elect_one()) {
-                        const uint32_t a_buf = tmem + TM_A + b * TM_A_STRIDE, d_buf = tmem + TM_D + acc * TM_D_STRIDE;
-                        // one descriptor per column block; a 16-column slice is 1024 bytes further = 64 in the address field
-                        const uint64_t bdesc = smem_desc(chunk, 512, 128);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            mma_ts(d_buf + 32 * (j & 1), a_buf + F::a_col(j), bdesc + (uint64_t)(F::b_slice(ps, j) * 64u), IDESC_MAIN,
-                                   (ps | (j >> 1)) ? 1u : 0u);
-                        if (F::HAS_MIN && ps == PASSES - 1)
-                            mma_ts(tmem + TM_DM + acc * TM_DM_STRIDE, tmem + TM_AM + b * TM_AM_STRIDE, smem_desc(chunk + TS_BMIN_OFF, 768, 128),
-                                   IDESC_MIN, 0);
-                        mma_commit(&a_free[b]);
-                        if (ps == PASSES - 1) mma_commit(&d_ready[acc]);
+                        if (c == 0) issue_half<F, 0>(h2, d_buf, a_buf, b_lo, b_hi, IDESC_MAIN);
+                        else issue_half<F, 1>(h2, d_buf, a_buf, b_lo, b_hi, IDESC_MAIN);
+                        if (F::HAS_MIN && h == HALVES - 1)   // every half has stored its column of the min operand by now
+                            mma_ts<false>(tmem + TM_DM + g * TM_DM_STRIDE, tmem + TM_AM + g * TM_AM_STRIDE, (uint32_t)mdesc, (uint32_t)(mdesc >> 32),
+                                          IDESC_MIN);
+                        mma_commit(&a_free[2 * g + c]);
+                        if (h2 == HALVES / 2 - 1) mma_commit(&d_ready[g]);   // this warp's share of the entry; the barrier counts both warps
                     }
                     __syncwarp();
                 }
@@ -191,43 +216,49 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     } else if (warp < UNPACK_WARPS) {
         // ------------------------------ unpacking warps ------------------------------
         // They read weights only (shared memory filled by the producer), so they never wait for the previous kernel.
-        const int q4 = warp & 3, kp = warp >> 2;
+        const int g = warp >> 3, q4 = warp & 3, kp2 = (warp >> 2) & 1;
         const int row = 32 * q4 + lane;
         const uint32_t tm_l = tmem + ((uint32_t)(32 * q4) << 16);
-        // K padding of the min-term operand (sub-block pairs 4..7) in both pass buffers: written once, never touched again
-        if (F::HAS_MIN && kp == 0) {
-            tmem_st4(tm_l + TM_AM + 4, 0u, 0u, 0u, 0u);
-            tmem_st4(tm_l + TM_AM + TM_AM_STRIDE + 4, 0u, 0u, 0u, 0u);
-        }
+        const uint32_t a_buf = tm_l + TM_A + g * TM_A_STRIDE, am_buf = tm_l + TM_AM + g * TM_AM_STRIDE;
+        // K padding of the group's min-term operand (sub-block pairs 4..7): written once, never touched again
+        if (F::HAS_MIN && kp2 == 0) tmem_st4(am_buf + 4, 0u, 0u, 0u, 0u);
         bool ok = true;
-        uint32_t pc = 0;   // running pass count
-        for (int e = 0; e < n_it && ok; ++e) {
+        uint32_t hc = 0;   // running half count of this group
+        for (int e = g; e < n_it && ok; e += 2) {
             const int s = e % STAGES;
             ok = mbar_wait_bounded(&full[s], (e / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint8_t* st = ring + s * F::STAGE;
+            uint32_t am_keep[HALVES];
 #pragma unroll
-            for (int ps = 0; ps < PASSES; ++ps, ++pc) {
+            for (int h = 0; h < HALVES; ++h, ++hc) {
                 uint32_t r[32], am[8];
                 UnitScales us{0.f, 0.f};
-                if (ok) F::unpack(st, ps, row, kp, r, am, us);
-                const uint32_t b = pc & 1;
-                if (ok && pc >= 2) {   // the pass buffer was last read by the MMAs of pass pc - 2
-                    ok = mbar_wait_bounded(&a_free[b], ((pc >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_FULL);
+                if (ok) F::unpack(st, h, row, kp2, r, am, us);
+                if (F::HAS_MIN && h < HALVES - 1) am_keep[h] = am[0];
+                const uint32_t hb = hc & 1;
+                if (ok && hc >= 2) {   // the half buffer was last read by the MMAs of the group's half hc - 2
+                    ok = mbar_wait_bounded(&a_free[2 * g + hb], ((hc >> 1) - 1) & 1, p.err, DEV_ERR_WAIT_FULL);
                     ok = __all_sync(0xffffffffu, ok);
                     if (ok) fence_after_sync();
                 }
                 if (ok) {
-                    F::store(tm_l + TM_A + b * TM_A_STRIDE, kp, r);
-                    if (F::HAS_MIN) tmem_st1(tm_l + TM_AM + b * TM_AM_STRIDE + kp, am[0]);
-                    if (ps == 0 && kp == 0) scl[(e & 3) * TILE_R + row] = make_float2(us.d, us.dmin);
+                    F::store(a_buf, h, kp2, r);
+                    if (F::HAS_MIN && h == HALVES - 1) {
+                        // The min operand is read by the entry's last MMA, so it may only be replaced once the previous
+                        // entry's last half has completed - which this half's wait has just established.
+#pragma unroll
+                        for (int hh = 0; hh < HALVES - 1; ++hh) tmem_st1(am_buf + F::min_col(hh, kp2), am_keep[hh]);
+                        tmem_st1(am_buf + F::min_col(h, kp2), am[0]);
+                    }
+                    if (h == 0 && kp2 == 0) scl[(e & 3) * TILE_R + row] = make_float2(us.d, us.dmin);
                     wait_st();
                     fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive(&a_ready[b]);   // releases this warp's tensor-memory and side-buffer writes
-                        if (ps == PASSES - 1) mbar_arrive(&empty[s]);
+                        mbar_arrive(&a_ready[2 * g + hb]);   // releases this warp's tensor-memory and side-buffer writes
+                        if (h == HALVES - 1) mbar_arrive(&empty[s]);
                     }
                 }
             }
@@ -321,7 +352,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
         }
     }
     __syncthreads();
-    if (warp == MMA_WARP) {
+    if (warp == MMA_WARP0) {
         fence_after_sync();
         tmem_free(tmem, TM_COLS);
     }

@@ -73,22 +73,24 @@ template <>
 struct Fmt<DFL_Q6_K> {
     static constexpr int STAGE = STAGE_Q6_K;
     static constexpr int STAGES = KC == 4 ? 5 : 4;
-    static constexpr int PASSES = 2;   // one 128-column unit each: 64 pass-buffer columns of A1, 64 of A2
+    static constexpr int HALVES = 4;   // half h: unit h / 2 (128 columns), column quarters 2 (h % 2) + kp2; written as A1 (64 columns) and A2 (64)
     static constexpr bool HAS_MIN = false;
-    // steps 0..7 multiply A1, steps 8..15 A2, both with the unit's eight 16-column slices
-    __device__ static __forceinline__ uint32_t a_col(int j) { return (uint32_t)(j < 8 ? 8 * j : 64 + 8 * (j - 8)); }
-    __device__ static __forceinline__ uint32_t b_slice(int ps, int j) { return (uint32_t)(8 * ps + (j & 7)); }
-    __device__ static __forceinline__ void store(uint32_t buf, int kp, const uint32_t (&r)[32]) {
+    // steps 0..3 multiply A1, steps 4..7 A2, both with the half's four 16-column slices
+    __device__ static __forceinline__ uint32_t a_col(int h, int jj) { return (uint32_t)((jj < 4 ? 0 : 64) + 32 * (h & 1) + 8 * (jj & 3)); }
+    __device__ static __forceinline__ uint32_t b_slice(int h, int jj) { return (uint32_t)(8 * (h >> 1) + 4 * (h & 1) + (jj & 3)); }
+    __device__ static __forceinline__ void store(uint32_t buf, int h, int kp2, const uint32_t (&r)[32]) {
+        const int kp = 2 * (h & 1) + kp2;
         uint32_t lo[16], hi[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) { lo[i] = r[i]; hi[i] = r[16 + i]; }
         tmem_st16(buf + 16 * kp, lo);
         tmem_st16(buf + 64 + 16 * kp, hi);
     }
+    __device__ static __forceinline__ int min_col(int, int) { return 0; }
     // r[0..15] = A1 (q * even part of the scale), r[16..31] = A2 (q * odd bit), column c = k' pair (2c, 2c + 1)
-    __device__ static __forceinline__ void unpack(const uint8_t* st, int unit, int row, int kp, uint32_t (&r)[32], uint32_t (&)[8],
+    __device__ static __forceinline__ void unpack(const uint8_t* st, int h, int row, int kp2, uint32_t (&r)[32], uint32_t (&)[8],
                                                   UnitScales& us) {
-        // columns 128 unit + 32 kp + l of the block
+        const int unit = h >> 1, kp = 2 * (h & 1) + kp2;   // columns 128 unit + 32 kp + l of the block
         const uint4 nib = reinterpret_cast<const uint4*>(st + TSQ6_OFF_NIB)[(unit * 4 + kp) * 128 + row];
         const uint2 hi2 = reinterpret_cast<const uint2*>(st + TSQ6_OFF_HI2)[(unit * 4 + kp) * 128 + row];
         us.d = __half2float(__ushort_as_half(reinterpret_cast<const uint16_t*>(st + TSQ6_OFF_D)[row]));
