@@ -396,9 +396,6 @@ def run_verify_only(args, rank, world, device):
         pos += 16
     launches0 = pkg.launch_count()
     pkg.gemm_timing_begin() if os.environ.get("DFL_GEMM_TIMING") else None
-    fam_mask = int(os.environ.get("DFL_FAMILY_TIMING", "0"))   # diagnostics: per-family kernel time (takes them out of the launch overlap)
-    if fam_mask:
-        pkg.lib().dfl_family_timing_begin(C.c_int32(fam_mask))
     t0 = time.perf_counter()
     for _ in range(args.steps):
         pkg.packed_verify(model, sess, scr, ids, rng.integers(0, arch.vocab_size, size=16), pos)
@@ -410,14 +407,6 @@ def run_verify_only(args, rank, world, device):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         wall = float(t[0])
     extra = {"parallelism": f"ep{world}: experts split over {world} GPUs, one all-reduce per routed-expert block"} if ep else {}
-    if fam_mask:
-        fams = {}
-        for bit in (2, 4, 8, 16):
-            if fam_mask & bit:
-                ms, cnt = C.c_double(0), C.c_uint64(0)
-                pkg.lib().dfl_family_timing_end(C.c_int32(bit), C.byref(ms), C.byref(cnt))
-                fams[str(bit)] = {"ms_per_step": ms.value / args.steps, "launches_per_step": cnt.value / args.steps}
-        extra = {**extra, "family_kernel_ms": fams}
     if os.environ.get("DFL_GEMM_TIMING"):
         ms, n, b = pkg.gemm_timing_end()
         extra = {"gemm_ms_per_step": ms / args.steps, "gemm_launches": n, "gemm_GBps": b / (ms * 1e-3) / 1e9}

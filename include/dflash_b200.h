@@ -149,12 +149,6 @@ uint64_t dfl_launch_count(void);
  * bracketed by CUDA events on its own stream; end synchronises them and returns the summed kernel
  * time, the launch count and the ggml weight bytes those launches streamed. */
 void dfl_gemm_timing_begin(void);
-/* The same for the other kernel families of the step (bit mask: 2 glue / small kernels, 4 attention,
- * 8 gated-delta-net, 16 routed-expert selection): launches of the selected families are bracketed by
- * events, which takes them out of the launch overlap - durations for ranking kernels, not a
- * decomposition of the step.  _end returns the sum and count of one family and switches timing off. */
-void dfl_family_timing_begin(int32_t family_mask);
-dfl_status dfl_family_timing_end(int32_t family, double* ms_total, uint64_t* n_launches);
 dfl_status dfl_gemm_timing_end(double* ms_total, uint64_t* n_launches, uint64_t* weight_bytes);
 
 /* ---- few-row quantised GEMM (the weight-streaming hot kernel) ----------

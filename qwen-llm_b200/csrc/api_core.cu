@@ -9,26 +9,6 @@ namespace dfl {
 
 static thread_local std::string t_last_error;
 std::atomic<uint64_t> g_launches{0};
-int g_family_timing_mask = 0;
-namespace {
-struct FamilyMark { int family; cudaEvent_t e0, e1; };
-std::vector<FamilyMark> g_family_marks;
-std::mutex g_family_mutex;
-}  // namespace
-void family_timing_mark(int family, cudaStream_t st, bool begin) {
-    std::lock_guard<std::mutex> lock(g_family_mutex);
-    if (begin) {
-        FamilyMark m{family, nullptr, nullptr};
-        cudaEventCreate(&m.e0);
-        cudaEventCreate(&m.e1);
-        cudaEventRecord(m.e0, st);
-        g_family_marks.push_back(m);
-    } else {
-        for (size_t i = g_family_marks.size(); i-- > 0;)
-            if (g_family_marks[i].family == family) { cudaEventRecord(g_family_marks[i].e1, st); break; }
-    }
-}
-
 int sm_count() {
     static std::atomic<int> cached[16] = {};
     int dev = 0;
@@ -49,14 +29,6 @@ bool pdl_enabled() {
         return !(e && e[0] == '0');
     }();
     return on;
-}
-
-bool pdl_enabled_for(int family) {
-    static const int off = [] {
-        const char* e = getenv("DFL_PDL_OFF");
-        return e ? atoi(e) : 0;
-    }();
-    return pdl_enabled() && !(off & family);
 }
 
 void set_error(const std::string& msg) { t_last_error = msg; }
@@ -130,9 +102,7 @@ dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, 
         if (tmp) cudaFree(tmp);
         return fail(DFL_ERR_OOM, std::string("qmatrix: cudaMalloc: ") + cudaGetErrorString(e));
     }
-    // DFL_GEMM_PATH=legacy keeps every matrix on the mma.sync kernel (A/B runs)
-    const char* path = getenv("DFL_GEMM_PATH");
-    m->layout = (allow_ts && ts_supported(dtype) && !(path && std::string(path) == "legacy")) ? LAYOUT_TS : LAYOUT_FRAG;
+    m->layout = (allow_ts && ts_supported(dtype)) ? LAYOUT_TS : LAYOUT_FRAG;
     if (kb_group > 0 && m->layout != LAYOUT_TS) {
         if (tmp) cudaFree(tmp);
         cudaFree(m->tiles);
@@ -191,27 +161,6 @@ int32_t dfl_device_count(void) {
     return n;
 }
 uint64_t dfl_launch_count(void) { return g_launches.load(); }
-void dfl_family_timing_begin(int32_t family_mask) {
-    std::lock_guard<std::mutex> lock(g_family_mutex);
-    for (auto& m : g_family_marks) { cudaEventDestroy(m.e0); cudaEventDestroy(m.e1); }
-    g_family_marks.clear();
-    g_family_timing_mask = family_mask;
-}
-dfl_status dfl_family_timing_end(int32_t family, double* ms_total, uint64_t* n_launches) {
-    std::lock_guard<std::mutex> lock(g_family_mutex);
-    g_family_timing_mask = 0;
-    double ms = 0;
-    uint64_t n = 0;
-    for (auto& m : g_family_marks) {
-        if (m.family != family) continue;
-        float one = 0;
-        cudaEventSynchronize(m.e1);
-        if (cudaEventElapsedTime(&one, m.e0, m.e1) == cudaSuccess) { ms += one; ++n; }
-    }
-    if (ms_total) *ms_total = ms;
-    if (n_launches) *n_launches = n;
-    return DFL_OK;
-}
 
 dfl_status dfl_qmatrix_create(int32_t device, int32_t dtype, uint64_t n_in, uint64_t n_out, const void* data, uint64_t n_bytes,
                               int32_t on_device, dfl_qmatrix** out) {

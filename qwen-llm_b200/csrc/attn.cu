@@ -82,7 +82,7 @@ dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, con
                              const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
                              void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override, long long cache_row0) {
     dim3 grid((unsigned)(g.n_q + 2 * g.n_kv), (unsigned)n_rows);
-    launch_kf(4, attn_front_kernel, dim3(grid), dim3(128), (g.hd + 4) * sizeof(float), st, g, gated ? 1 : 0, part, splits, ld_part, q_norm_w, k_norm_w, start,
+    launch_k(attn_front_kernel, dim3(grid), dim3(128), (g.hd + 4) * sizeof(float), st, g, gated ? 1 : 0, part, splits, ld_part, q_norm_w, k_norm_w, start,
                                                                    k_cache, v_cache, kv_f16 ? 1 : 0, q_rot, gate, pos_override, cache_row0);
     count_launch();
     DFL_CUDA(cudaGetLastError());
@@ -264,7 +264,7 @@ __global__ void acts_clear_kernel(uint8_t* acts, uint64_t bytes) {
     if (i < bytes) *reinterpret_cast<uint4*>(acts + i) = make_uint4(0, 0, 0, 0);
 }
 dfl_status launch_acts_clear(cudaStream_t st, uint8_t* acts, uint64_t bytes) {
-    launch_kf(4, acts_clear_kernel, dim3((unsigned)((bytes / 16 + 255) / 256)), dim3(256), 0, st, acts, bytes);
+    launch_k(acts_clear_kernel, dim3((unsigned)((bytes / 16 + 255) / 256)), dim3(256), 0, st, acts, bytes);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -284,17 +284,17 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
         DFL_CUDA(cudaFuncSetAttribute(attn_chunk_kernel<KV, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = true;
     }
-    int rows_per_cta = (long long)n_chunks * g.n_kv >= 2 * 148 ? MAX_ROWS : ATTN_ROW_GROUP;
+    int rows_per_cta = (long long)n_chunks * g.n_kv >= 2 * sm_count() ? MAX_ROWS : ATTN_ROW_GROUP;
     // Short contexts leave most SMs idle at four rows per CTA: narrow the row group while every warp still has a query.
     const int group = g.n_q / g.n_kv;
     while (rows_per_cta > 1 && rows_per_cta <= ATTN_ROW_GROUP && (rows_per_cta / 2) * group >= 8 &&
-           (long long)n_chunks * g.n_kv * ((n_rows + rows_per_cta - 1) / rows_per_cta) < 148)
+           (long long)n_chunks * g.n_kv * ((n_rows + rows_per_cta - 1) / rows_per_cta) < sm_count())
         rows_per_cta /= 2;
     if (const char* e = getenv("DFL_ATTN_ROWS_PER_CTA")) {   // test hook: results must not depend on the grouping
         const int v = atoi(e);
         if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) rows_per_cta = v;
     }
-    launch_kf(4, attn_chunk_kernel<KV, HD>, dim3((unsigned)n_chunks, (unsigned)g.n_kv, (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta)), dim3(256), smem, st,
+    launch_k(attn_chunk_kernel<KV, HD>, dim3((unsigned)n_chunks, (unsigned)g.n_kv, (unsigned)((n_rows + rows_per_cta - 1) / rows_per_cta)), dim3(256), smem, st,
               g, q_rot, reinterpret_cast<const KV*>(k_cache), reinterpret_cast<const KV*>(v_cache), start, n_rows, partials, rows_per_cta);
     count_launch();
     DFL_CUDA(cudaGetLastError());
@@ -322,8 +322,8 @@ dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q
         DFL_CHECK(launch_acts_clear(st, acts, (uint64_t)g.n_q * g.hd / TILE_K * (uint64_t)act_chunk_bytes(bf3)));
     }
     (void)n_chunks;
-    if (g.hd == 128) launch_kf(4, attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
-    else launch_kf(4, attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
+    if (g.hd == 128) launch_k(attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
+    else launch_k(attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -483,7 +483,7 @@ dfl_status launch_dattn_span_tc(cudaStream_t st, const AttnGeom& g, const float*
     const int cps = attn_tc_chunks_per_span(g, ctx_capacity + MAX_ROWS);
     const int n_chunks = (n_ctx + n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK;
     const int n_spans = (n_chunks + cps - 1) / cps;
-    launch_kf(4, dattn_span_tc_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(128), (size_t)DTC_SMEM, st, g, q_rot, k_ctx, v_ctx, pos_ctx,
+    launch_k(dattn_span_tc_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(128), (size_t)DTC_SMEM, st, g, q_rot, k_ctx, v_ctx, pos_ctx,
               ctx_begin, n_ctx, k_noise, v_noise, noise_start, n_rows, causal ? 1 : 0, window, partials, cps);
     count_launch();
     DFL_CUDA(cudaGetLastError());
@@ -496,7 +496,8 @@ bool attn_tc_supported(const AttnGeom& g, bool kv_f16) { return kv_f16 && g.hd =
 // chunks per span from the session's KV capacity only (never from the call): two CTAs per SM, two waves
 int attn_tc_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity) {
     const uint64_t cap_chunks = ((uint64_t)kv_capacity + ATTN_CHUNK - 1) / ATTN_CHUNK;
-    uint64_t b = (cap_chunks * g.n_kv + 4 * 148 - 1) / (4 * 148);
+    const uint64_t slots = 4ull * (uint64_t)sm_count();
+    uint64_t b = (cap_chunks * g.n_kv + slots - 1) / slots;
     if (b < 1) b = 1;
     if (b > 64) b = 64;
     return (int)b;
@@ -511,7 +512,7 @@ dfl_status launch_attn_span_tc(cudaStream_t st, const AttnGeom& g, const float* 
     }
     const int n_chunks = (int)((start + (uint32_t)n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK);
     const int n_spans = (n_chunks + chunks_per_span - 1) / chunks_per_span;
-    launch_kf(4, attn_span_tc_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(128), (size_t)TC_SMEM, st, g, q_rot,
+    launch_k(attn_span_tc_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(128), (size_t)TC_SMEM, st, g, q_rot,
               reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), start, n_rows, partials, chunks_per_span);
     count_launch();
     DFL_CUDA(cudaGetLastError());

@@ -125,38 +125,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // Number of SMs of the current device (cached per device): grids are sized from it.
 int sm_count();
 bool pdl_enabled();
-bool pdl_enabled_for(int family);   // development switch: DFL_PDL_OFF=<bit mask of kernel families>
-// Optional per-family device timing (dfl_family_timing_begin / _end): launches of the selected families are bracketed
-// by CUDA events on their own stream, which also takes them out of the programmatic overlap - the sums are the
-// kernels' own durations with a warm L2, for ranking, not a decomposition of the step time.
-extern int g_family_timing_mask;
-void family_timing_mark(int family, cudaStream_t st, bool begin);
 #ifdef __CUDACC__
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kf(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
-    if (g_family_timing_mask & family) {
-        family_timing_mark(family, st, true);
-        cudaLaunchConfig_t c2 = {};
-        c2.gridDim = grid;
-        c2.blockDim = block;
-        c2.dynamicSmemBytes = smem;
-        c2.stream = st;
-        const cudaError_t e = cudaLaunchKernelEx(&c2, kernel, static_cast<KArgs>(args)...);
-        family_timing_mark(family, st, false);
-        return e;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled_for(family) ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
     cudaLaunchConfig_t cfg = {};

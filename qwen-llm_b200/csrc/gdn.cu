@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(128) gdn_front_kernel(const GdnFrontParams p) 
 
 dfl_status launch_gdn_front_p(cudaStream_t st, const GdnFrontParams& p) {
     if (p.g.hd != 128 || p.g.conv_k != 4) return fail(DFL_ERR_UNSUPPORTED, "gdn: head_dim must be 128 and conv kernel 4");
-    launch_kf(8, gdn_front_kernel, dim3(p.g.conv_dim() / 128), dim3(128), 0, st, p);
+    launch_k(gdn_front_kernel, dim3(p.g.conv_dim() / 128), dim3(128), 0, st, p);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -61,7 +61,7 @@ __global__ void gdn_conv_restore_kernel(int conv_dim, const float* conv_pre, con
 dfl_status launch_gdn_conv_restore(cudaStream_t st, const GdnGeom& g, const float* conv_pre, const float* qkv_raw, int n_keep,
                                    float* conv_state) {
     const int cd = g.conv_dim();
-    launch_kf(8, gdn_conv_restore_kernel, dim3((cd + 255) / 256), dim3(256), 0, st, cd, conv_pre, qkv_raw, n_keep, conv_state);
+    launch_k(gdn_conv_restore_kernel, dim3((cd + 255) / 256), dim3(256), 0, st, cd, conv_pre, qkv_raw, n_keep, conv_state);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -216,7 +216,7 @@ gdn_scan_kernel(GdnGeom g, const float* state_in, float* state_out, const float*
 dfl_status launch_gdn_scan(cudaStream_t st, const GdnGeom& g, const float* state_in, float* state_out, const float* q_n,
                            const float* k_n, const float* v, const float* ab, const float* dt_bias, const float* a_log, int n_rows,
                            const float* part_z, int z_splits, int ld_part, const float* norm_w, uint8_t* acts, int act_layout, int* err) {
-    launch_kf(8, gdn_scan_kernel, dim3(dim3((unsigned)g.n_v, 4)), dim3(256), 0, st, g, state_in, state_out, q_n, k_n, v, ab, dt_bias, a_log, n_rows,
+    launch_k(gdn_scan_kernel, dim3(dim3((unsigned)g.n_v, 4)), dim3(256), 0, st, g, state_in, state_out, q_n, k_n, v, ab, dt_bias, a_log, n_rows,
               part_z, z_splits, ld_part, norm_w, acts, act_layout, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());

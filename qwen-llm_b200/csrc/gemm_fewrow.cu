@@ -579,8 +579,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
     }
 }
 
-constexpr int kSmCount = 148;
-
 int gemm_max_kblocks_per_cta(int dtype) {
     switch (dtype) {
         case DFL_Q4_K: return Fmt<DFL_Q4_K>::KC;
@@ -593,7 +591,7 @@ int gemm_max_kblocks_per_cta(int dtype) {
 }
 
 static int ctas_per_split(int row_tiles, int splits) {
-    int cps = kSmCount / splits;
+    int cps = sm_count() / splits;
     if (cps < 1) cps = 1;
     return cps < row_tiles ? cps : row_tiles;
 }

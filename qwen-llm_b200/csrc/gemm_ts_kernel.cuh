@@ -9,7 +9,7 @@
 // columns (Q4_K / Q5_K: two halves of 128 weight columns; Q6_K: four of 64, each written as the
 // even / odd scale parts); the MMA warp issues eight MMAs per half as soon as it is stored.
 //
-//   producer thread     ring slot free?   -> bulk copy of the stage          -> full[slot]
+//   producer thread     ring slot free?   -> bulk copy of the stage          -> full[slot]   (activations: a draining thread)
 //   unpacking group g   full[slot]        -> registers -> a_free[g][half]?   -> tcgen05.st -> a_ready[g][half], empty[slot]
 //   MMA warp (g, c)     a_ready[g][c], d_free[g]?    -> 8 tcgen05.mma (+ min) -> commit: a_free[g][c], d_ready[g]
 //                       (c = half % 2: its MMAs accumulate into accumulator c of the group, so the order in which the
@@ -139,29 +139,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     if (warp == PRODUCER_WARP) {
         // ------------------------------ bulk-copy producer ------------------------------
         if (lane == 0) {
+            // weights do not depend on the previous kernel: the ring is filled without waiting for it.  The loop keeps
+            // running slot / round / source counters so that issuing a stage is a handful of instructions.
             const uint64_t tile_stride = (uint64_t)p.kblocks * F::STAGE;
-            const uint8_t* wbase = p.w;
-            int pt = 0, pk = 0;
+            const bool mapped = p.tile_map != nullptr || p.kb_map != nullptr;
+            int pt = 0, pk = 0, s = 0;
+            uint32_t round = 0;
+            const uint8_t* src = p.w + (uint64_t)c * tile_stride + (uint64_t)kb0 * F::STAGE;   // tile c, first column block of the range
             bool ok = true;
             for (int e = 0; e < n_it; ++e) {
-                const int s = e % STAGES;
-                if (e >= STAGES) ok = mbar_wait_bounded(&empty[s], ((e / STAGES) - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
+                if (round > 0) ok = mbar_wait_bounded(&empty[s], (round - 1) & 1, p.err, DEV_ERR_WAIT_EMPTY);
                 if (!ok) break;
-                const int slot = c + pt * cps;
-                const uint8_t* src = wbase + (uint64_t)(p.tile_map ? p.tile_map[slot] : slot) * tile_stride +
-                                     (uint64_t)(p.kb_map ? p.kb_map[kb0 + pk] : kb0 + pk) * F::STAGE;
+                if (mapped) {
+                    const int slot = c + pt * cps;
+                    src = p.w + (uint64_t)(p.tile_map ? p.tile_map[slot] : slot) * tile_stride +
+                          (uint64_t)(p.kb_map ? p.kb_map[kb0 + pk] : kb0 + pk) * F::STAGE;
+                }
                 mbar_arrive_expect_tx(&full[s], F::STAGE);
                 bulk_g2s(ring + s * F::STAGE, src, F::STAGE, &full[s]);
-                if (++pk == n_kb) { pk = 0; ++pt; }
-                if (e == (STAGES < n_it ? STAGES : n_it) - 1) {
-                    // the ring is primed with weights (independent of the previous kernel); now the activations,
-                    // in the order of their first use, one barrier each: the first MMA waits for one chunk only
-                    pdl_wait();
-                    for (int k = 0; k < n_kb; ++k) {
-                        mbar_arrive_expect_tx(&acts_bar[k], ACTTS_CHUNK);
-                        bulk_g2s(acts_res + k * ACTTS_CHUNK, p.acts + (uint64_t)(p.kb_map ? p.kb_map[kb0 + k] : kb0 + k) * ACTTS_CHUNK, ACTTS_CHUNK,
-                                 &acts_bar[k]);
-                    }
+                src += F::STAGE;
+                if (++s == STAGES) { s = 0; ++round; }
+                if (++pk == n_kb) {   // next row tile of this CTA: cps tiles further, back to the first column block
+                    pk = 0;
+                    ++pt;
+                    src += (uint64_t)cps * tile_stride - (uint64_t)n_kb * F::STAGE;
                 }
             }
             if (!ok) abort_flag = 1;
@@ -268,6 +269,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
         // ------------------------------ draining warps ------------------------------
         pdl_wait();
         const int dtid = threadIdx.x - DRAIN_WARP0 * 32;   // 0..127 = weight row of the tile = tensor-memory lane
+        if (dtid == 0 && n_it > 0) {
+            // the activations (the previous kernel's output), in the order of their first use, one barrier each: the
+            // first MMA waits for one chunk only.  Issued here rather than by the producer, whose first iterations are
+            // busy priming the weight ring.
+            for (int k = 0; k < n_kb; ++k) {
+                mbar_arrive_expect_tx(&acts_bar[k], ACTTS_CHUNK);
+                bulk_g2s(acts_res + k * ACTTS_CHUNK, p.acts + (uint64_t)(p.kb_map ? p.kb_map[kb0 + k] : kb0 + k) * ACTTS_CHUNK, ACTTS_CHUNK, &acts_bar[k]);
+            }
+        }
         {
             // per-token output scale; 8 threads per token add the sum-of-squares partials in a fixed tree
             const int tok = dtid >> 3, part = dtid & 7;
@@ -346,7 +356,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
             uint32_t spins = 0;
             while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && ++spins < (1u << 16)) __nanosleep(100);
         }
-        for (int k = 0; k < (n_kb < KC ? n_kb : KC); ++k) {
+        for (int k = 0; k < (n_it > 0 ? (n_kb < KC ? n_kb : KC) : 0); ++k) {
             uint32_t spins = 0;
             while (!mbar_try_wait(&acts_bar[k], 0) && ++spins < (1u << 16)) __nanosleep(100);
         }

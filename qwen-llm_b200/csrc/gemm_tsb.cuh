@@ -266,7 +266,7 @@ int gemm_tsb_choose_splits_multi(const int* row_tiles, int n_mats, int kblocks) 
         double cost = 0.0;
         for (int i = 0; i < n_mats; ++i) {
             const int tiles = row_tiles[i] > 0 ? row_tiles[i] : 1;
-            int cps = 148 / s;
+            int cps = sm_count() / s;
             if (cps < 1) cps = 1;
             if (cps > tiles) cps = tiles;
             const int rounds = (tiles + cps - 1) / cps;
@@ -293,7 +293,7 @@ dfl_status launch_gemm_tsb(cudaStream_t st, const QMatrix& m, const uint8_t* act
     p.kblocks = m.kblocks;
     p.splits = splits;
     p.row_tiles = m.row_tiles;
-    int cps = 148 / splits;
+    int cps = sm_count() / splits;
     if (cps < 1) cps = 1;
     if (cps > m.row_tiles) cps = m.row_tiles;
     p.ctas_per_split = cps;

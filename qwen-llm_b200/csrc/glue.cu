@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(256) glue_kernel(const GlueParams p) {
 
 dfl_status launch_glue(cudaStream_t st, const GlueParams& p, uint64_t k) {
     if (k == 0 || k % TILE_K) return fail(DFL_ERR_BAD_SHAPE, "glue: column count must be a positive multiple of 256");
-    launch_kf(2, glue_kernel, dim3((unsigned)(k / GLUE_COLS)), dim3(256), 0, st, p);
+    launch_k(glue_kernel, dim3((unsigned)(k / GLUE_COLS)), dim3(256), 0, st, p);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -41,7 +41,7 @@ __global__ void embed_rows_kernel(int dtype, const uint8_t* __restrict__ ggml, u
 dfl_status launch_embed_rows(cudaStream_t st, int dtype, const uint8_t* ggml, uint64_t h, const int32_t* tokens, int n_rows,
                              float* x, int ld) {
     if (h % 256 || ggml_bytes_per_256(dtype) == 0) return fail(DFL_ERR_UNSUPPORTED, "embed_rows: dtype or width");
-    launch_kf(2, embed_rows_kernel, dim3(dim3((unsigned)((h + 255) / 256), (unsigned)n_rows)), dim3(256), 0, st, dtype, ggml, h, tokens, x, ld);
+    launch_k(embed_rows_kernel, dim3(dim3((unsigned)((h + 255) / 256), (unsigned)n_rows)), dim3(256), 0, st, dtype, ggml, h, tokens, x, ld);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(512) small_matmul_kernel(const float* __restri
 dfl_status launch_small_matmul(cudaStream_t st, const float* w, const float* xn, int ld_xn, int n_rows, uint64_t k, int n_out,
                                const GemmEpilogue& ep, float* out, int ld_out) {
     if (k % 4) return fail(DFL_ERR_BAD_SHAPE, "small_matmul: k must be a multiple of 4");
-    launch_kf(2, small_matmul_kernel, dim3(n_out), dim3(512), 0, st, w, xn, ld_xn, n_rows, k, ep.sumsq, ep.n_sumsq, ep.norm_k, ep.eps, ep.out_scale, out,
+    launch_k(small_matmul_kernel, dim3(n_out), dim3(512), 0, st, w, xn, ld_xn, n_rows, k, ep.sumsq, ep.n_sumsq, ep.norm_k, ep.eps, ep.out_scale, out,
                                                ld_out);
     count_launch();
     DFL_CUDA(cudaGetLastError());

@@ -9,7 +9,7 @@ namespace dfl {
 
 dfl_status launch_group(cudaStream_t st, const MatGroup& g, const uint8_t* acts, float* part, const GemmEpilogue& ep, int* err) {
     for (size_t i = 0; i < g.mats.size(); ++i)
-        DFL_CHECK(launch_gemm_fewrow(st, g.mats[i], acts, part + g.col_off[i], g.splits, ep, err, pdl_enabled_for(1), g.total_cols));
+        DFL_CHECK(launch_gemm_fewrow(st, g.mats[i], acts, part + g.col_off[i], g.splits, ep, err, pdl_enabled(), g.total_cols));
     return DFL_OK;
 }
 
@@ -233,10 +233,10 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             // input and write disjoint outputs; the scan waits for alpha / beta, the gated norm for z
             const MatGroup& G = L.in_qkv_z;
             DFL_CHECK(fork_side());
-            DFL_CHECK(launch_gemm_fewrow(st, G.mats[0], sc->acts_h, sc->part + G.col_off[0], G.splits, ep_norm, s->err, pdl_enabled_for(1), G.total_cols));
+            DFL_CHECK(launch_gemm_fewrow(st, G.mats[0], sc->acts_h, sc->part + G.col_off[0], G.splits, ep_norm, s->err, pdl_enabled(), G.total_cols));
             DFL_CHECK(launch_small_matmul(side, L.w_ab, sc->xn, (int)H, (int)n, H, 2 * gg.n_v, ep_norm, sc->ab[gi], 2 * gg.n_v));
             for (size_t i = 1; i < G.mats.size(); ++i)
-                DFL_CHECK(launch_gemm_fewrow(side2, G.mats[i], sc->acts_h, sc->part + G.col_off[i], G.splits, ep_norm, s->err, pdl_enabled_for(1), G.total_cols));
+                DFL_CHECK(launch_gemm_fewrow(side2, G.mats[i], sc->acts_h, sc->part + G.col_off[i], G.splits, ep_norm, s->err, pdl_enabled(), G.total_cols));
             const int cur = s->ssm_cur[gi];
             DFL_CHECK(launch_gdn_front(st, gg, sc->part, L.in_qkv_z.splits, (int)L.in_qkv_z.total_cols, (int)n, L.conv_w, s->conv[gi],
                                        sc->qkv_raw[gi], sc->q_n[gi], sc->k_n[gi], sc->v[gi], sc->conv_pre[gi]));
@@ -432,18 +432,14 @@ static dfl_status model_create_impl(int32_t device, const dfl_arch* arch, const 
     m->ep_fs = ep_rank == 0 ? arch->expert_shared_feed_forward_length : 0;
     std::vector<dfl_tensor> sliced;   // this rank's views of the stacked expert tensors
     sliced.reserve(3 * (size_t)arch->n_layer);
-    // One kernel family per model: the tensor-memory GEMM when every 2-D quantised tensor has a
-    // row-lane layout (Q4_K / Q5_K / Q6_K), else the mma.sync kernel for all of them, so that every
-    // packed-activation buffer has a single format.  DFL_GEMM_PATH=legacy forces the latter.
+    // One kernel family per model, so that every packed-activation buffer has a single format: the tensor-memory GEMM
+    // when every 2-D quantised tensor has a row-lane layout (Q4_K / Q5_K / Q6_K), else - a model that holds Q8_0
+    // matrices - the mma.sync kernel for all of them.
     bool allow_ts = true;
     for (uint64_t i = 0; i < n_tensors; ++i)
         if (tensors[i].n_dims >= 2 && stage_bytes_of(tensors[i].dtype) != 0 &&
             !(tensors[i].dtype == DFL_Q4_K || tensors[i].dtype == DFL_Q5_K || tensors[i].dtype == DFL_Q6_K))
             allow_ts = false;
-    {
-        const char* path = getenv("DFL_GEMM_PATH");
-        if (path && std::string(path) == "legacy") allow_ts = false;
-    }
     m->act_layout = allow_ts ? ACT_TS : ACT_F16;
     m->arch = a;
     cudaStream_t st = 0;
@@ -758,7 +754,6 @@ dfl_status dfl_scratch_create(const dfl_model* m, uint32_t block_size, uint32_t 
     alloc(&sc->acts_v, std::max(q_dim, v_dim) / TILE_K * chunk);
     alloc(&sc->q_rot, MAX_ROWS * q_dim * 4);
     alloc(&sc->gate, MAX_ROWS * q_dim * 4);
-    alloc(&sc->o, MAX_ROWS * v_dim * 4);
     for (int i = 0; i < m->n_gdn; ++i) {
         float *a0, *a1, *a2, *a3, *a4, *a5;
         alloc(&a0, (size_t)MAX_ROWS * gg.conv_dim() * 4);

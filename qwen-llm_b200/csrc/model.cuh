@@ -131,7 +131,7 @@ struct dfl_scratch {
     uint32_t block_size = 0, k_layers = 0;
     float *x = nullptr, *xn = nullptr, *part = nullptr, *sumsq = nullptr;
     uint8_t *acts_h = nullptr, *acts_f = nullptr, *acts_v = nullptr;
-    float *q_rot = nullptr, *gate = nullptr, *o = nullptr;
+    float *q_rot = nullptr, *gate = nullptr;
     // per GDN layer, kept for rollback
     std::vector<float*> qkv_raw, conv_pre, q_n, k_n, v, ab;
     float *logits = nullptr, *gap = nullptr;

@@ -94,7 +94,7 @@ dfl_status launch_moe_route(cudaStream_t st, const float* logits, int ld, int n_
                             float* shared_gate, int32_t* route_idx, int* err) {
     if (n_expert < 1 || n_expert > MOE_MAX_EXPERTS || n_used < 1 || n_used > 32 || n_used > n_expert)
         return fail(DFL_ERR_UNSUPPORTED, "moe_route: expert_count must be in [1, 1024] and expert_used_count in [1, 32]");
-    launch_kf(16, moe_route_kernel, dim3(MAX_ROWS), dim3(32), 0, st, logits, ld, n_expert, n_used, n_rows, route_w, shared_gate, route_idx, err);
+    launch_k(moe_route_kernel, dim3(MAX_ROWS), dim3(32), 0, st, logits, ld, n_expert, n_used, n_rows, route_w, shared_gate, route_idx, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -111,11 +111,11 @@ struct MoeListArgs {
     int32_t *tile_map, *n_tiles;
     int KB, min_kb;
     int32_t *kb_map, *n_kb;
-    int kc, down_tiles, max_splits;
+    int kc, down_tiles, max_splits, n_sm;
 };
 __device__ __forceinline__ void moe_build_lists(const float* route_w, const MoeListArgs a) {
     const int n_expert = a.n_expert, e0 = a.e0, n_local = a.n_local, T = a.T, Ts = a.Ts, min_tiles = a.min_tiles, KB = a.KB, min_kb = a.min_kb;
-    const int kc = a.kc, down_tiles = a.down_tiles, max_splits = a.max_splits;
+    const int kc = a.kc, down_tiles = a.down_tiles, max_splits = a.max_splits, n_sm = a.n_sm;
     int32_t *tile_map = a.tile_map, *n_tiles = a.n_tiles, *kb_map = a.kb_map, *n_kb = a.n_kb;
     __shared__ int warp_count[MOE_MAX_EXPERTS / 32];
     __shared__ int total_sh;
@@ -159,16 +159,16 @@ __device__ __forceinline__ void moe_build_lists(const float* route_w, const MoeL
         const int want = n_act * KB, all = n_local * KB;
         const int len = want > min_kb ? want : (min_kb < all ? min_kb : all);
         n_kb[0] = len;
-        // split geometry for this list length: enough splits to keep a CTA's blocks resident and to give the 148 SMs
+        // split geometry for this list length: enough splits to keep a CTA's blocks resident and to give every SM
         // work, as many CTAs per split as fit beside them; 0 = the launch's own geometry
         int s = 0, cps = 0;
         if (max_splits > 0) {
             s = (len + kc - 1) / kc;
-            const int fill = (148 + down_tiles - 1) / down_tiles;
+            const int fill = (n_sm + down_tiles - 1) / down_tiles;
             if (s < fill) s = fill;
             if (s > max_splits) s = max_splits;
             if (s > len) s = len;
-            cps = 148 / s < down_tiles ? 148 / s : down_tiles;
+            cps = n_sm / s < down_tiles ? n_sm / s : down_tiles;
         }
         n_kb[1] = s;
         n_kb[2] = cps;
@@ -194,7 +194,7 @@ static MoeListArgs moe_list_args(int n_expert, int e0, int n_local, int tiles_pe
                                  int32_t* n_tiles, int kb_per_expert, int min_kb, int32_t* kb_map, int32_t* n_kb, int kc, int down_tiles,
                                  int max_splits) {
     return MoeListArgs{n_expert, e0, n_local, tiles_per_expert, shared_tiles, min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb,
-                       kc, down_tiles, max_splits};
+                       kc, down_tiles, max_splits, sm_count()};
 }
 
 dfl_status launch_moe_tiles(cudaStream_t st, const float* route_w, int n_rows, int n_expert, int e0, int n_local, int tiles_per_expert,
@@ -202,7 +202,7 @@ dfl_status launch_moe_tiles(cudaStream_t st, const float* route_w, int n_rows, i
                             int32_t* n_kb, int kc, int down_tiles, int max_splits) {
     (void)n_rows;
     if (n_local > MOE_MAX_EXPERTS || shared_tiles > MOE_MAX_EXPERTS) return fail(DFL_ERR_UNSUPPORTED, "moe_tiles: too many experts");
-    launch_kf(16, moe_tiles_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), 0, st, route_w,
+    launch_k(moe_tiles_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), 0, st, route_w,
               moe_list_args(n_expert, e0, n_local, tiles_per_expert, shared_tiles, min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb,
                             kc, down_tiles, max_splits));
     count_launch();
@@ -219,7 +219,7 @@ dfl_status launch_moe_route_lists(cudaStream_t st, const float* logits, int ld, 
     if (n_expert < 1 || n_used < 1 || n_used > 32 || n_used > n_expert || !moe_route_lists_fused(n_expert) || n_local > MOE_MAX_EXPERTS ||
         shared_tiles > MOE_MAX_EXPERTS)
         return fail(DFL_ERR_UNSUPPORTED, "moe_route_lists: geometry");
-    launch_kf(16, moe_route_lists_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), (size_t)MAX_ROWS * n_expert * 4, st, logits, ld, n_used, n_rows, route_w,
+    launch_k(moe_route_lists_kernel, dim3(1), dim3(MOE_MAX_EXPERTS), (size_t)MAX_ROWS * n_expert * 4, st, logits, ld, n_used, n_rows, route_w,
               shared_gate, route_idx, err,
               moe_list_args(n_expert, e0, n_local, tiles_per_expert, shared_tiles, min_tiles, tile_map, n_tiles, kb_per_expert, min_kb, kb_map, n_kb,
                             kc, down_tiles, max_splits));

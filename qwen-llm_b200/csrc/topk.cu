@@ -94,8 +94,8 @@ uint64_t topk16_scratch_bytes(int n_rows) { return (uint64_t)n_rows * TOPK_SLICE
 
 dfl_status launch_topk16(cudaStream_t st, const float* x, int n_rows, uint64_t n, uint64_t ld, int32_t* ids, float* vals, void* scratch) {
     if (n_rows < 1 || n == 0 || n >= 0xFFFFFFFFull) return fail(DFL_ERR_BAD_SHAPE, "topk16: shape");
-    launch_kf(2, topk16_stage1_kernel, dim3(TOPK_SLICES, (unsigned)n_rows), dim3(TOPK_WARPS * 32), 0, st, x, n, ld, (uint64_t*)scratch);
-    launch_kf(2, topk16_stage2_kernel, dim3((unsigned)n_rows), dim3(TOPK_WARPS * 32), 0, st, (const uint64_t*)scratch, TOPK_SLICES * TOPK_WARPS, ids, vals);
+    launch_k(topk16_stage1_kernel, dim3(TOPK_SLICES, (unsigned)n_rows), dim3(TOPK_WARPS * 32), 0, st, x, n, ld, (uint64_t*)scratch);
+    launch_k(topk16_stage2_kernel, dim3((unsigned)n_rows), dim3(TOPK_WARPS * 32), 0, st, (const uint64_t*)scratch, TOPK_SLICES * TOPK_WARPS, ids, vals);
     count_launch(2);
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
