@@ -117,7 +117,7 @@ def run_schedule(w, cont, pattern, warm_steps, steps, runs_drafter=True):
     launches0 = w.pkg.launch_count()
     t0 = time.perf_counter()
     toks_b, st = w.gen(one_hot(V, int(toks_a[-1])), n_b, replay_history=hist[n_a - 1:], replay_runs_drafter=runs_drafter,
-                       replay_unchecked=True)
+                       replay_unchecked=True, verify_margin=NEAR_TIE_MARGIN)
     wall = time.perf_counter() - t0
     launches = w.pkg.launch_count() - launches0
     assert np.array_equal(toks_b, cont[n_a - 1:n_a - 1 + n_b]), "timed output differs from the greedy continuation"
@@ -126,7 +126,8 @@ def run_schedule(w, cont, pattern, warm_steps, steps, runs_drafter=True):
     dev_ms = st.draft_ms + st.verify_ms + st.restore_ms
     return {"emitted": emitted, "steps": steps, "dev_ms": dev_ms, "wall_ms": wall * 1e3, "draft_ms": st.draft_ms, "verify_ms": st.verify_ms,
             "restore_ms": st.restore_ms, "accept_ms": st.accept_ms, "append_ms": st.append_ms, "launches": launches,
-            "restore_calls": st.restore_calls, "accepted": int(st.accepted_drafts)}
+            "restore_calls": st.restore_calls, "accepted": int(st.accepted_drafts), "committed_rows": int(st.committed_rows),
+            "margin_rows": int(st.margin_rows)}
 
 
 WORKLOAD_C2 = ("c2: 9B-class hybrid Q4_K_M target (32 layers, GDN:attn 3:1, H 4096, FFN 12288, V 151936) + 5-layer bf16 DFlash drafter, "
@@ -332,7 +333,10 @@ def run(args, rank, world, device):
         "gpu_launches": int(head["launches"]), "clocks": clocks,
         # greedy continuation of the natural pass: committed verify rows and those whose top-1 / top-2 gap is below the margin
         # (a row this close to a tie may resolve differently under another f32 summation order)
-        "near_tie_rows": {"margin": NEAR_TIE_MARGIN, "committed_rows": int(st_nat.committed_rows), "rows_below_margin": int(st_nat.margin_rows)},
+        # committed rows of all three schedules (each row is one verify-pass logits row that decided an emitted token)
+        "near_tie_rows": {"margin": NEAR_TIE_MARGIN,
+                          "committed_rows": int(st_nat.committed_rows) + head["committed_rows"] + full["committed_rows"],
+                          "rows_below_margin": int(st_nat.margin_rows) + head["margin_rows"] + full["margin_rows"]},
         "schedules": {
             "reference_like_4.4": {"tok_per_s": head["emitted"] / (head["dev_ms"] * 1e-3), "e2e_tok_per_s": head["emitted"] / (head["wall_ms"] * 1e-3),
                                    "ms_per_step": head["dev_ms"] / steps, "draft_ms": draft_ms, "verify_ms": verify_ms,

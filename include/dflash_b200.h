@@ -46,7 +46,8 @@ typedef enum dfl_status {
     DFL_ERR_SAMPLING = 11,     /* SamplingError / DFlashAcceptError */
     DFL_ERR_TIMEOUT = 12,      /* a bounded device-side wait gave up */
     DFL_ERR_MISSING_TENSOR = 13,
-    DFL_ERR_ROUTE_STATUS = 14  /* expert routing reported NONFINITE (kernels/moe.metal:355-360); poisons the session */
+    DFL_ERR_ROUTE_STATUS = 14, /* expert routing reported NONFINITE (kernels/moe.metal:355-360); poisons the session */
+    DFL_ERR_COLLECTIVE = 15    /* expert-parallel watchdog: a collective failed or did not complete; communicator aborted */
 } dfl_status;
 
 /* ggml type ids (crates/qwen-llm/src/tensor.rs:159 `storage_layout`). */
@@ -235,6 +236,19 @@ dfl_status dfl_ep_unique_id(uint8_t* id_out_128);
 dfl_status dfl_model_create_ep(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors,
                                uint64_t n_tensors, int32_t ep_rank, int32_t ep_world,
                                const uint8_t* nccl_id_128, dfl_model** out);
+/* Host watchdog of expert-parallel passes.  Every call that waits for a pass of an
+ * expert-parallel model polls an event instead of blocking, asks the communicator
+ * for an asynchronous error between polls, and gives up after DFL_EP_TIMEOUT_MS
+ * (environment, default 30000): the communicator is aborted, the call returns
+ * DFL_ERR_COLLECTIVE, the session is poisoned and every later pass on the model
+ * is refused with the same status.  dfl_ep_watchdog_selftest drives the same
+ * polling loop with scripted actions and no GPU: scenario 0 = the pass completes
+ * after `after_polls` polls (expects DFL_OK, no abort), 1 = the communicator
+ * reports an asynchronous error at poll `after_polls`, 2 = the pass never
+ * completes (runs into timeout_ms), 3 = the pass itself fails with a CUDA error.
+ * *aborted_out = how often the abort action ran (0 or 1). */
+dfl_status dfl_ep_watchdog_selftest(int32_t scenario, uint32_t after_polls, uint32_t timeout_ms,
+                                    int32_t* aborted_out);
 
 /* MetalDFlashHead::load  metal_dflash.rs:4944-5050 (names loader.rs:1179-1230). */
 dfl_status dfl_drafter_create(const dfl_model* target, const dfl_dflash_config* cfg,

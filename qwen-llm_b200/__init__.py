@@ -19,7 +19,7 @@ MAX_TARGET_LAYERS = 8
 MAX_DRAFTER_LAYERS = 16
 
 STATUS_NAMES = {0: "OK", 1: "BAD_ARG", 2: "BAD_SHAPE", 3: "UNSUPPORTED", 4: "CUDA", 5: "NO_DEVICE", 6: "OOM", 7: "POISONED",
-                8: "CTX_OVERFLOW", 9: "KV_STATE", 10: "BAD_TOKEN", 11: "SAMPLING", 12: "TIMEOUT", 13: "MISSING_TENSOR", 14: "ROUTE_STATUS"}
+                8: "CTX_OVERFLOW", 9: "KV_STATE", 10: "BAD_TOKEN", 11: "SAMPLING", 12: "TIMEOUT", 13: "MISSING_TENSOR", 14: "ROUTE_STATUS", 15: "COLLECTIVE"}
 
 
 class DflError(RuntimeError):
@@ -241,6 +241,18 @@ def ep_unique_id():
     buf = (C.c_uint8 * 128)()
     check(lib().dfl_ep_unique_id(buf))
     return bytes(buf)
+
+
+def ep_watchdog_selftest(scenario, after_polls=3, timeout_ms=200):
+    """Drives the expert-parallel host watchdog's polling loop with scripted actions (no GPU).  Returns how often the
+    abort action ran; raises DflError COLLECTIVE when the loop gave up (scenarios 1-3)."""
+    aborted = C.c_int32(-1)
+    st = lib().dfl_ep_watchdog_selftest(C.c_int32(scenario), C.c_uint32(after_polls), C.c_uint32(timeout_ms), C.byref(aborted))
+    if st != 0:
+        err = DflError(st, lib().dfl_last_error().decode(errors="replace"))
+        err.aborted = aborted.value
+        raise err
+    return aborted.value
 
 
 class Model:

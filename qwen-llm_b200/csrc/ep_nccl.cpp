@@ -2,11 +2,21 @@
 // and the one collective the routed-expert block needs - an all-reduce of the block's [16][H] output
 // over the ranks that hold disjoint expert ranges.  The reference runs its routed experts on one device
 // (crates/qwen-llm/src/metal_forward/moe.rs:349-751); the multi-GPU split is this library's own.
+//
+// Host watchdog: a pass of an expert-parallel model does not block in cudaStreamSynchronize, where a peer that
+// never joins the collective would hold the caller for ever.  It records an event behind the pass and polls it,
+// asking the communicator for an asynchronous error between polls; on an error, or when the event has not
+// completed within the limit, the communicator is aborted (which ends the collective's kernels on this rank), the
+// stream drains, and the caller gets DFL_ERR_COLLECTIVE with the session poisoned and the model's communicator
+// marked dead.  The polling loop (ep_watch_core) takes its three actions as callbacks, so that it is exercised on the
+// host with scripted ones (dfl_ep_watchdog_selftest).
 #include <dlfcn.h>
 
+#include <chrono>
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <thread>
 
 #include "model.cuh"
 
@@ -20,6 +30,8 @@ struct NcclApi {
     int (*CommInitRank)(comm_t*, int, NcclId, int) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, comm_t, cudaStream_t) = nullptr;
     int (*CommDestroy)(comm_t) = nullptr;
+    int (*CommAbort)(comm_t) = nullptr;
+    int (*CommGetAsyncError)(comm_t, int*) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
     bool ok = false;
 };
@@ -39,6 +51,8 @@ void load_nccl() {
     g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
     g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(dlsym(h, "ncclAllReduce"));
     g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+    g_nccl.CommAbort = reinterpret_cast<decltype(g_nccl.CommAbort)>(dlsym(h, "ncclCommAbort"));
+    g_nccl.CommGetAsyncError = reinterpret_cast<decltype(g_nccl.CommGetAsyncError)>(dlsym(h, "ncclCommGetAsyncError"));
     g_nccl.GetErrorString = reinterpret_cast<decltype(g_nccl.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
     g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.AllReduce && g_nccl.CommDestroy;
 }
@@ -71,8 +85,74 @@ dfl_status ep_comm_create(int rank, int world, const uint8_t* id_bytes, void** c
     *comm_out = c;
     return DFL_OK;
 }
-void ep_comm_destroy(void* comm) {
-    if (comm && g_nccl.ok) g_nccl.CommDestroy(comm);
+void ep_comm_destroy(void* comm, bool aborted) {
+    if (comm && g_nccl.ok && !aborted) g_nccl.CommDestroy(comm);   // an aborted communicator has been released by the abort
+}
+
+// The watchdog's loop.  query(): 0 = the pass has completed, 1 = still running, anything else = a CUDA error.
+// async_error(): 0 = none (ncclSuccess), 7 = a non-blocking operation still in progress (ncclInProgress), anything else
+// = the communicator has failed.  Returns DFL_OK when the pass completed; otherwise calls abort() once, waits (bounded)
+// for the pass to drain, and returns DFL_ERR_COLLECTIVE.
+dfl_status ep_watch_core(const EpWatchHooks& h, uint32_t timeout_ms, uint32_t poll_us, bool* aborted) {
+    using clock = std::chrono::steady_clock;
+    const auto t0 = clock::now();
+    auto last_async = t0;
+    *aborted = false;
+    std::string why;
+    for (;;) {
+        const int q = h.query();
+        if (q == 0) return DFL_OK;
+        if (q != 1) { why = "the pass failed with a CUDA error while a collective was in flight"; break; }
+        const auto now = clock::now();
+        if (now - last_async >= std::chrono::microseconds(500)) {
+            last_async = now;
+            const int e = h.async_error();
+            if (e != 0 && e != 7) { why = "the communicator reported an asynchronous error (" + std::to_string(e) + ")"; break; }
+        }
+        if (now - t0 >= std::chrono::milliseconds(timeout_ms)) {
+            why = "a collective did not complete within " + std::to_string(timeout_ms) + " ms (a peer is missing or stalled)";
+            break;
+        }
+        if (poll_us) std::this_thread::sleep_for(std::chrono::microseconds(poll_us));
+        else std::this_thread::yield();
+    }
+    h.abort();
+    *aborted = true;
+    // the abort ends the collective's kernels; give the rest of the pass a bounded time to drain
+    const auto t1 = clock::now();
+    while (h.query() == 1 && clock::now() - t1 < std::chrono::milliseconds(timeout_ms)) std::this_thread::sleep_for(std::chrono::microseconds(200));
+    return fail(DFL_ERR_COLLECTIVE, "expert-parallel watchdog: " + why + "; communicator aborted");
+}
+
+uint32_t ep_watch_timeout_ms() {
+    // DFL_EP_TIMEOUT_MS: how long a pass of an expert-parallel model may take before its communicator is aborted
+    static const uint32_t ms = [] {
+        const char* e = getenv("DFL_EP_TIMEOUT_MS");
+        const long v = e ? atol(e) : 0;
+        return (uint32_t)(v > 0 ? v : 30000);
+    }();
+    return ms;
+}
+
+dfl_status ep_watch_stream(void* comm, cudaStream_t st, cudaEvent_t ev, bool* aborted) {
+    *aborted = false;
+    if (!g_nccl.CommAbort || !g_nccl.CommGetAsyncError) {   // an NCCL without these entry points: plain blocking wait
+        DFL_CUDA(cudaStreamSynchronize(st));
+        return DFL_OK;
+    }
+    DFL_CUDA(cudaEventRecord(ev, st));
+    EpWatchHooks h;
+    h.query = [ev]() -> int {
+        const cudaError_t e = cudaEventQuery(ev);
+        return e == cudaSuccess ? 0 : e == cudaErrorNotReady ? 1 : 2;
+    };
+    h.async_error = [comm]() -> int {
+        int e = 0;
+        const int rc = g_nccl.CommGetAsyncError(comm, &e);
+        return rc != 0 ? rc : e;
+    };
+    h.abort = [comm]() { g_nccl.CommAbort(comm); };
+    return ep_watch_core(h, ep_watch_timeout_ms(), 20, aborted);
 }
 // in-place sum over the ranks, f32; every rank receives the same bits
 dfl_status ep_all_reduce_sum(void* comm, float* buf, size_t count, cudaStream_t st) {
@@ -82,3 +162,27 @@ dfl_status ep_all_reduce_sum(void* comm, float* buf, size_t count, cudaStream_t 
 }
 
 }  // namespace dfl
+
+extern "C" dfl_status dfl_ep_watchdog_selftest(int32_t scenario, uint32_t after_polls, uint32_t timeout_ms, int32_t* aborted_out) {
+    using namespace dfl;
+    if (!aborted_out || scenario < 0 || scenario > 3 || timeout_ms == 0 || timeout_ms > 10000)
+        return fail(DFL_ERR_BAD_ARG, "ep_watchdog_selftest: scenario in [0, 3], timeout in (0, 10000] ms");
+    uint32_t polls = 0;
+    int aborts = 0;
+    bool drained = false;
+    EpWatchHooks h;
+    h.query = [&]() -> int {
+        ++polls;
+        if (drained) return 0;   // after the abort the pass drains
+        if (scenario == 0 && polls > after_polls) return 0;
+        if (scenario == 3 && polls > after_polls) return 2;
+        return 1;
+    };
+    h.async_error = [&]() -> int { return scenario == 1 && polls >= after_polls ? 6 /* ncclRemoteError */ : polls & 1 ? 0 : 7; };
+    h.abort = [&]() { ++aborts; drained = true; };
+    bool aborted = false;
+    const dfl_status st = ep_watch_core(h, timeout_ms, 50, &aborted);
+    *aborted_out = aborts;
+    if ((aborts == 1) != aborted) return fail(DFL_ERR_CUDA, "ep_watchdog_selftest: abort ran a different number of times than reported");
+    return st;
+}

@@ -65,7 +65,7 @@ dfl_status dfl_prefill(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         if (last && last_logits_host)
             cudaMemcpyAsync(last_logits_host, sc->logits + (uint64_t)(nb - 1) * m->arch.vocab_size, (size_t)m->arch.vocab_size * 4,
                             cudaMemcpyDeviceToHost, s->st);
-        DFL_CUDA(cudaStreamSynchronize(s->st));
+        DFL_CHECK(session_drain(s));
         if (feed_drafter) DFL_CHECK(dfl_dsession_append_from_scratch(feed_drafter, sc, 0, nb, start_position + (uint32_t)off));
     }
     dfl_status st = check_dev_err(s->st, s->err);

@@ -136,12 +136,27 @@ dfl_status session_guard(const dfl_model* m, dfl_session* s, const char* what) {
     if (!m || !s) return fail(DFL_ERR_BAD_ARG, std::string(what) + ": null handle");
     if (s->m != m) return fail(DFL_ERR_BAD_ARG, std::string(what) + ": session belongs to another model");
     if (s->poisoned) return fail(DFL_ERR_POISONED, std::string(what) + ": session is poisoned by an earlier failure");
+    if (m->ep_dead.load()) return fail(DFL_ERR_COLLECTIVE, std::string(what) + ": the model's expert-parallel communicator was aborted by the watchdog");
     return use_device(m->device);
 }
 
 static bool layer_is_attn(const dfl_arch& a, uint32_t il) {
     const uint32_t iv = a.full_attention_interval ? a.full_attention_interval : 1;
     return il % iv == iv - 1;
+}
+
+// Waits for everything queued on the session's stream.  A pass with collectives in it (expert-parallel model) is
+// waited for under the host watchdog, not in a blocking synchronize.
+dfl_status session_drain(dfl_session* s) {
+    if (s->m->ep_world > 1) {
+        bool aborted = false;
+        dfl_status w = ep_watch_stream(s->m->ep_comm, s->st, s->ev_watch, &aborted);
+        if (aborted) s->m->ep_dead.store(true);
+        if (w != DFL_OK) { s->poisoned = true; return w; }
+        return DFL_OK;
+    }
+    DFL_CUDA(cudaStreamSynchronize(s->st));
+    return DFL_OK;
 }
 
 // After the stream has drained: completion check (metal/completion.rs:18) incl. the injected failure.
@@ -151,6 +166,7 @@ static dfl_status completion_check(dfl_session* s) {
         s->poisoned = true;
         return fail(DFL_ERR_CUDA, "completion check failed (injected): command discarded; session poisoned");
     }
+    DFL_CHECK(session_drain(s));
     dfl_status st = check_dev_err(s->st, s->err);
     if (st != DFL_OK) s->poisoned = true;
     return st;
@@ -584,7 +600,7 @@ void dfl_model_destroy(dfl_model* m) {
             if (p) cudaFree(p);
     }
     m->lm_head.release();
-    ep_comm_destroy(m->ep_comm);
+    ep_comm_destroy(m->ep_comm, m->ep_dead.load());
     if (m->embd_ggml) cudaFree(m->embd_ggml);
     if (m->out_norm_w) cudaFree(m->out_norm_w);
     delete m;
@@ -629,7 +645,8 @@ dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t 
          cudaStreamCreateWithFlags(&s->st_side2, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&s->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
          cudaEventCreateWithFlags(&s->ev_join, cudaEventDisableTiming) == cudaSuccess &&
-         cudaEventCreateWithFlags(&s->ev_join2, cudaEventDisableTiming) == cudaSuccess;
+         cudaEventCreateWithFlags(&s->ev_join2, cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&s->ev_watch, cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
         std::string why = cudaGetErrorString(cudaGetLastError());
         dfl_session_destroy(s);
@@ -656,6 +673,7 @@ void dfl_session_destroy(dfl_session* s) {
     if (s->ev_fork) cudaEventDestroy(s->ev_fork);
     if (s->ev_join) cudaEventDestroy(s->ev_join);
     if (s->ev_join2) cudaEventDestroy(s->ev_join2);
+    if (s->ev_watch) cudaEventDestroy(s->ev_watch);
     if (s->st_side) cudaStreamDestroy(s->st_side);
     if (s->st_side2) cudaStreamDestroy(s->st_side2);
     if (s->st) cudaStreamDestroy(s->st);

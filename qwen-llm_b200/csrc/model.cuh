@@ -3,6 +3,8 @@
 // MetalSession / MetalDFlashVerifyScratch / MetalDFlashHead / MetalDFlashSession
 // (crates/qwen-llm/src/metal_forward/mod.rs:443,2095; crates/qwen-llm/src/metal_dflash.rs:4944,5492,6003).
 #pragma once
+#include <atomic>
+#include <functional>
 #include <map>
 #include <string>
 #include <vector>
@@ -66,12 +68,23 @@ struct LayerW {
 
 }  // namespace dfl
 
+struct dfl_session;
+
 namespace dfl {
 // expert parallelism (ep_nccl.cpp)
 dfl_status ep_unique_id(uint8_t* id_out);
 dfl_status ep_comm_create(int rank, int world, const uint8_t* id_bytes, void** comm_out);
-void ep_comm_destroy(void* comm);
+void ep_comm_destroy(void* comm, bool aborted);
 dfl_status ep_all_reduce_sum(void* comm, float* buf, size_t count, cudaStream_t st);
+// host watchdog over a pass that contains collectives (ep_nccl.cpp)
+struct EpWatchHooks {
+    std::function<int()> query;
+    std::function<int()> async_error;
+    std::function<void()> abort;
+};
+dfl_status ep_watch_core(const EpWatchHooks& h, uint32_t timeout_ms, uint32_t poll_us, bool* aborted);
+dfl_status ep_watch_stream(void* comm, cudaStream_t st, cudaEvent_t ev, bool* aborted);
+dfl_status session_drain(dfl_session* s);
 }  // namespace dfl
 
 struct dfl_model {
@@ -81,6 +94,7 @@ struct dfl_model {
     int ep_rank = 0, ep_world = 1;
     uint32_t ep_e0 = 0, ep_n = 0, ep_fs = 0;
     void* ep_comm = nullptr;
+    mutable std::atomic<bool> ep_dead{false};   // the watchdog aborted the communicator: every later pass is refused
     int act_layout = dfl::ACT_F16;  // packed-activation format all its GEMMs consume (follows the kernel family)
     dfl_arch arch{};
     std::vector<dfl::LayerW> layers;
@@ -123,7 +137,7 @@ struct dfl_session {
     // side stream for the branches of a layer that only depend on the layer's normalised input (the GDN z and
     // alpha / beta projections, the expert router): they run beside the main projection instead of after it
     cudaStream_t st_side = nullptr, st_side2 = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_join2 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_join2 = nullptr, ev_watch = nullptr;
 };
 
 struct dfl_scratch {
