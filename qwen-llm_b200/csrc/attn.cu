@@ -15,7 +15,7 @@ namespace dfl {
 __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, const float* part, int splits,
                                                          int ld_part, const float* __restrict__ q_norm_w,
                                                          const float* __restrict__ k_norm_w, uint32_t start, void* k_cache,
-                                                         void* v_cache, int kv_f16, float* q_rot,
+                                                         void* v_cache, int kv_mode, float* q_rot,
                                                          float* gate, const uint32_t* pos_override, long long cache_row0) {
     pdl_prologue();
     extern __shared__ float sh[];  // [hd] values, then 4 partial sums
@@ -46,7 +46,9 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
     if (kind == 2) {
         for (int d = threadIdx.x; d < hd; d += blockDim.x) {
             const uint64_t o = (crow * g.n_kv + h) * hd + d;
-            if (kv_f16) reinterpret_cast<__half*>(v_cache)[o] = __float2half_rn(sh[d]);
+            if (kv_mode == KV_F16_TILED)
+                reinterpret_cast<__half*>(v_cache)[kv_tile_base((uint32_t)crow, g.n_kv, h) + kv_tile_v_off((uint32_t)crow % KV_TILE_KEYS, d)] = __float2half_rn(sh[d]);
+            else if (kv_mode == KV_F16_ROWS) reinterpret_cast<__half*>(v_cache)[o] = __float2half_rn(sh[d]);
             else reinterpret_cast<float*>(v_cache)[o] = sh[d];
         }
         return;
@@ -72,7 +74,9 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
         if (kind == 0) q_rot[((uint64_t)tok * g.n_q + h) * hd + d] = out;
         else {
             const uint64_t o = (crow * g.n_kv + h) * hd + d;
-            if (kv_f16) reinterpret_cast<__half*>(k_cache)[o] = __float2half_rn(out);
+            if (kv_mode == KV_F16_TILED)
+                reinterpret_cast<__half*>(k_cache)[kv_tile_base((uint32_t)crow, g.n_kv, h) + kv_tile_k_off((uint32_t)crow % KV_TILE_KEYS, d)] = __float2half_rn(out);
+            else if (kv_mode == KV_F16_ROWS) reinterpret_cast<__half*>(k_cache)[o] = __float2half_rn(out);
             else reinterpret_cast<float*>(k_cache)[o] = out;
         }
     }
@@ -80,10 +84,10 @@ __global__ void __launch_bounds__(128) attn_front_kernel(AttnGeom g, int gated, 
 
 dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, const float* part, int splits, int ld_part,
                              const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
-                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override, long long cache_row0) {
+                             void* v_cache, int kv_mode, float* q_rot, float* gate, const uint32_t* pos_override, long long cache_row0) {
     dim3 grid((unsigned)(g.n_q + 2 * g.n_kv), (unsigned)n_rows);
     launch_k(attn_front_kernel, dim3(grid), dim3(128), (g.hd + 4) * sizeof(float), st, g, gated ? 1 : 0, part, splits, ld_part, q_norm_w, k_norm_w, start,
-                                                                   k_cache, v_cache, kv_f16 ? 1 : 0, q_rot, gate, pos_override, cache_row0);
+                                                                   k_cache, v_cache, kv_mode, q_rot, gate, pos_override, cache_row0);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;
@@ -193,15 +197,16 @@ __global__ void __launch_bounds__(256) attn_chunk_kernel(AttnGeom g, const float
 // ---- combine + sigmoid gate + activation packing ---------------------------------------------
 // grid (n_q, n_rows), block 32: one warp per (row, q head); lane owns hd/32 consecutive dims.
 template <int HD>
-__global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* partials, int chunks_per_record,
+__global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* partials, int pos_per_span, int recs_per_span,
                                                        const float* gate, uint32_t start, uint8_t* acts, int bf3,
                                                        float* out_f32, int* err) {
     pdl_prologue();
     constexpr int PER = HD / 32;  // 4 or 8
     const int qh = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
     const int group = g.n_q / g.n_kv, kvh = qh / group, qi = row * group + qh % group;
-    // records holding visible positions: one per 64-position chunk (scalar kernel) or per span of chunks (tensor-core kernel)
-    const int n_chunks = (int)((start + (uint32_t)row) / ATTN_CHUNK) / chunks_per_record + 1;
+    // records holding visible positions: one per 64-position chunk (scalar kernel), one per span of chunks (mma.sync
+    // kernel) or two per span of tiles (tcgen05 kernel: one per half of the keys)
+    const int n_chunks = ((int)((start + (uint32_t)row) / (uint32_t)pos_per_span) + 1) * recs_per_span;
     float M = -INFINITY;
     for (int c = lane; c < n_chunks; c += 32) {
         const float* rec = partials + (((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
@@ -212,14 +217,30 @@ __global__ void __launch_bounds__(32) attn_post_kernel(AttnGeom g, const float* 
 #pragma unroll
     for (int j = 0; j < PER; ++j) acc[j] = 0.f;
     float L = 0.f;
-    for (int c = 0; c < n_chunks; ++c) {
-        const float* rec = partials + (((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
-        const float m = rec[0];
-        if (m == -INFINITY) continue;
-        const float f = expf(m - M);
-        L = fmaf(rec[1], f, L);
+    // records are merged in index order; their loads are issued eight records at a time so that the latency of one
+    // round trip covers eight records (a long context has dozens)
+    constexpr int BATCH = 8;
+    const uint64_t rec_stride = (uint64_t)g.n_kv * (MAX_ROWS * group) * (HD + 2);
+    const float* rec0 = partials + ((uint64_t)kvh * (MAX_ROWS * group) + qi) * (HD + 2);
+    for (int c0 = 0; c0 < n_chunks; c0 += BATCH) {
+        float mb[BATCH], lb[BATCH], vb[BATCH][PER];
 #pragma unroll
-        for (int j = 0; j < PER; ++j) acc[j] = fmaf(rec[2 + lane * PER + j], f, acc[j]);
+        for (int u = 0; u < BATCH; ++u) {
+            const int c = c0 + u < n_chunks ? c0 + u : n_chunks - 1;
+            const float* rec = rec0 + (uint64_t)c * rec_stride;
+            mb[u] = rec[0];
+            lb[u] = rec[1];
+#pragma unroll
+            for (int j = 0; j < PER; ++j) vb[u][j] = rec[2 + lane * PER + j];
+        }
+#pragma unroll
+        for (int u = 0; u < BATCH; ++u) {
+            if (c0 + u >= n_chunks || mb[u] == -INFINITY) continue;
+            const float f = expf(mb[u] - M);
+            L = fmaf(lb[u], f, L);
+#pragma unroll
+            for (int j = 0; j < PER; ++j) acc[j] = fmaf(vb[u][j], f, acc[j]);
+        }
     }
     const float inv = 1.0f / L;
     const int col0 = qh * HD + lane * PER;
@@ -302,16 +323,23 @@ static dfl_status launch_chunk(cudaStream_t st, const AttnGeom& g, const float* 
 }
 
 dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
-                              const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts, int bf3,
+                              const void* v_cache, int kv_mode, uint32_t start, int n_rows, float* partials, uint8_t* acts, int bf3,
                               float* out_f32, int* err, uint32_t kv_capacity) {
     if (g.hd != 128 && g.hd != 256) return fail(DFL_ERR_UNSUPPORTED, "attention: head_dim must be 128 or 256");
     const int n_chunks = (int)((start + (uint32_t)n_rows + ATTN_CHUNK - 1) / ATTN_CHUNK);
     dfl_status s;
-    int chunks_per_record = 1;
+    const bool kv_f16 = kv_mode != KV_F32_ROWS;
+    int pos_per_span = ATTN_CHUNK, recs_per_span = 1;
     const char* tc_env = getenv("DFL_ATTN_TC");
-    if (attn_tc_supported(g, kv_f16) && !(tc_env && tc_env[0] == '0')) {
-        chunks_per_record = attn_tc_chunks_per_span(g, kv_capacity);
-        s = launch_attn_span_tc(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, chunks_per_record);
+    if (kv_mode == KV_F16_TILED) {
+        const int cps = attn_t5_chunks_per_span(g, kv_capacity);
+        pos_per_span = cps * KV_TILE_KEYS;
+        recs_per_span = 2;
+        s = launch_attn_t5(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, cps, err);
+    } else if (attn_tc_supported(g, kv_f16) && !(tc_env && tc_env[0] == '0')) {
+        const int cps = attn_tc_chunks_per_span(g, kv_capacity);
+        pos_per_span = cps * ATTN_CHUNK;
+        s = launch_attn_span_tc(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, cps);
     } else if (g.hd == 128) s = kv_f16 ? launch_chunk<__half, 128>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks)
                                 : launch_chunk<float, 128>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks);
     else s = kv_f16 ? launch_chunk<__half, 256>(st, g, q_rot, k_cache, v_cache, start, n_rows, partials, n_chunks)
@@ -322,8 +350,8 @@ dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q
         DFL_CHECK(launch_acts_clear(st, acts, (uint64_t)g.n_q * g.hd / TILE_K * (uint64_t)act_chunk_bytes(bf3)));
     }
     (void)n_chunks;
-    if (g.hd == 128) launch_k(attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
-    else launch_k(attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, chunks_per_record, gate, start, acts, bf3, out_f32, err);
+    if (g.hd == 128) launch_k(attn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, pos_per_span, recs_per_span, gate, start, acts, bf3, out_f32, err);
+    else launch_k(attn_post_kernel<256>, dim3(dim3((unsigned)g.n_q, (unsigned)n_rows)), dim3(32), 0, st, g, partials, pos_per_span, recs_per_span, gate, start, acts, bf3, out_f32, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -1,0 +1,384 @@
+// Verify attention over a long fp16 KV cache on the fifth-generation tensor cores (tcgen05 + tensor memory), for
+// 128-wide heads in GQA groups of four (reference: kernel_attn_decode_* / attn_v4, kernels/attn_v4.metal:65-265; CPU
+// oracle forward.rs:896-921).
+//
+// Cache layout ("tiled", sessions whose KV capacity makes the scan the dominant cost): per (128-position chunk, KV head)
+// one 32 KiB K tile and one 32 KiB V tile, each already in the K-major, no-swizzle operand layout of tcgen05.mma
+// (8 x 16-byte core matrices): K as B[n = key][k = dim], V as B[n = dim][k = key].  A tile is one bulk copy into shared
+// memory and is consumed by the tensor cores as it lies; appending a position writes 16-byte pieces (K) and single
+// halfs (V) into the last tile (attn_front_kernel).
+//
+// One CTA = one KV head x one span of `chunks_per_span` tiles; the 16 block rows x 4 query heads of the group are the
+// 64 queries.  Tensor-memory lane r and lane r + 64 both hold query r & 63: the A operand of S = Q K^T is [Q; Q]
+// (M = 128) with K = 256 - the f16 hi plane, then the lo plane of the pre-scaled queries, each against the K tile - so S
+// is exact to ~2^-22 like the mma.sync kernel's.  The operand lives in tensor memory (written once per CTA with
+// tcgen05.st), so shared memory only carries K and V tiles.  Every lane is one softmax thread: lanes 0-63 own keys 0-63
+// of each tile for their query, lanes 64-127 keys 64-127 - two independent online-softmax states per query, each with
+// its own running maximum, sum and output row.  P (f16; the lane's own half of the keys, zeros in the other half) is
+// written over the scores it came from and is the A operand of O += P V, so each lane's output row only collects its
+// own keys.  The output is rescaled only when a lane's maximum grows by more than 2^8 (its P values stay below 256; the
+// record keeps the maximum that was used), which leaves the O accumulator in tensor memory untouched in nearly every
+// step.  At the end each lane writes one [m, l, O[128]] record; attn_post_kernel merges the two records per span and the
+// spans exactly as it merges the other kernels' records.  Span boundaries depend only on the session's KV capacity,
+// never on the call.
+//
+// Warps 0-3: softmax / rescale / epilogue (thread = lane of tensor memory); warp 4: MMA issue (one elected lane) and
+// tensor-memory allocation; warp 5: bulk copies of the tiles into a ring of six 32 KiB slots (K and V tiles alternate;
+// a K slot is released when its S is complete, a V slot when its O += P V is).  Every wait is bounded and reports
+// through the error word; a role that gave up raises a flag the others test, all of them leave through the common exit,
+// and tensor memory is freed on every path.
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "ops.cuh"
+#include "tcgen05_prims.cuh"
+
+namespace dfl {
+
+namespace {
+using namespace ts;
+
+constexpr int T5_HD = 128, T5_GROUP = 4, T5_Q = MAX_ROWS * T5_GROUP;   // 64 queries per CTA
+constexpr int T5_TILE = KV_TILE_KEYS * T5_HD * 2;                      // 32768 bytes: one K or V tile
+constexpr int T5_SLOTS = 6;
+constexpr int T5_OFF_BAR = T5_SLOTS * T5_TILE;
+constexpr int T5_SMEM = T5_OFF_BAR + 256;
+constexpr int T5_THREADS = 192;
+// tensor memory: two score buffers of 128 columns (P overlays the first 64 of its buffer), the output, the query operand
+constexpr uint32_t T5_TM_S = 0, T5_TM_O = 256, T5_TM_Q = 384, T5_TM_COLS = 512;
+constexpr float T5_RESCALE = 8.0f;   // log2 units: rescale when the maximum grows by more than this
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_h2f(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ void split_pair_f(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 back = __half22float2(h);
+    const __half2 l = __floats2half2_rn(a - back.x, b - back.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+}  // namespace
+
+__global__ void __launch_bounds__(T5_THREADS, 1)
+attn_t5_kernel(AttnGeom g, const float* q_rot, const __half* k_cache, const __half* v_cache, uint32_t start, int n_rows, float* partials,
+               int chunks_per_span, int* err) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + T5_OFF_BAR);   // [6] a slot's tile has landed
+    uint64_t* empty = full + T5_SLOTS;        // [6] the MMAs that read the slot have completed
+    uint64_t* s_ready = empty + T5_SLOTS;     // [2] S = Q K^T of a tile is in tensor memory
+    uint64_t* p_ready = s_ready + 2;          // [2] P (and a rescaled O) are in tensor memory
+    uint64_t* pv_done = p_ready + 2;          // [2] O += P V of a tile has completed: its score buffer is free, O is at rest
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const int span = blockIdx.x, kvh = blockIdx.y;
+    const uint32_t n_pos = start + (uint32_t)n_rows;
+    const int c_begin = span * chunks_per_span;
+    int c_end = (int)((n_pos + KV_TILE_KEYS - 1) / KV_TILE_KEYS);
+    if (c_end > c_begin + chunks_per_span) c_end = c_begin + chunks_per_span;
+    const int n_c = c_end - c_begin;   // >= 1 by the launch geometry
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < T5_SLOTS; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_ready[i], 1);
+            mbar_init(&p_ready[i], 4);
+            mbar_init(&pv_done[i], 1);
+        }
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 4) tmem_alloc(&tmem_slot, T5_TM_COLS);
+    pdl_launch_dependents();
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp < 4) {
+        // ================= softmax / rescale / epilogue: thread = tensor-memory lane =================
+        const int L = 32 * warp + lane, q = L & 63, half = L >> 6, tok = q >> 2;
+        const uint32_t tm_lane = tmem + ((uint32_t)(32 * warp) << 16);
+        pdl_wait();   // the rotated queries come from the kernel before
+        {
+            // this lane's query (row = q / 4, head = kvh * 4 + q % 4), scaled by log2(e) / sqrt(hd) (scores live in the
+            // exp2 domain) and split into an exact f16 hi + lo pair: columns 0-63 = hi plane (k = 0..127), 64-127 = lo
+            const float scale = 1.4426950408889634f / sqrtf((float)T5_HD);
+            const float4* src = reinterpret_cast<const float4*>(q_rot + ((uint64_t)tok * g.n_q + kvh * T5_GROUP + (q & 3)) * T5_HD);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {   // 64 dims at a time
+                uint32_t hi[32], lo[32];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (tok < n_rows) v = src[16 * c + j];
+                    split_pair_f(v.x * scale, v.y * scale, hi[2 * j], lo[2 * j]);
+                    split_pair_f(v.z * scale, v.w * scale, hi[2 * j + 1], lo[2 * j + 1]);
+                }
+                tmem_st32(tm_lane + T5_TM_Q + 32 * c, hi);
+                tmem_st32(tm_lane + T5_TM_Q + 64 + 32 * c, lo);
+            }
+            wait_st();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[1]);   // phase 0 of p_ready[1] doubles as "the query operand is written"
+        }
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_c && ok; ++i) {
+            const int b = i & 1;
+            if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&abort_flag) != 0)) { ok = false; break; }
+            ok = mbar_wait_spin(&s_ready[b], (uint32_t)(i >> 1) & 1u, err, DEV_ERR_WAIT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            float s[64];
+            {
+                float t0[32], t1[32];
+                tmem_ld32(tm_lane + T5_TM_S + 128 * b + 64 * half, t0);
+                tmem_ld32(tm_lane + T5_TM_S + 128 * b + 64 * half + 32, t1);
+                wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { s[j] = t0[j]; s[32 + j] = t1[j]; }
+            }
+            const uint32_t p0 = (uint32_t)(c_begin + i) * KV_TILE_KEYS + 64u * (uint32_t)half;   // position of this lane's first key
+            if (p0 + 64u > start + 1u) {
+                // keys visible to the query: positions <= start + tok; rows beyond the call see nothing
+                const long long lim = tok < n_rows ? (long long)start + tok + 1 - (long long)p0 : 0;
+#pragma unroll
+                for (int j = 0; j < 64; ++j)
+                    if ((long long)j >= lim) s[j] = -INFINITY;
+            }
+            float mx[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mx[j] = s[j];
+#pragma unroll
+            for (int j = 8; j < 64; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
+            const float mc = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+            const bool need = mc > m_ref + T5_RESCALE;   // also the first finite maximum (m_ref = -inf)
+            if (__any_sync(0xffffffffu, need)) {
+                const float alpha = need ? ex2f(m_ref - mc) : 1.0f;   // 0 when there was no maximum yet
+                if (i >= 1) {
+                    // O must be at rest: the previous tile's O += P V has completed
+                    ok = mbar_wait_spin(&pv_done[(i - 1) & 1], (uint32_t)((i - 1) >> 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float o[32];
+                        tmem_ld32(tm_lane + T5_TM_O + 32 * c, o);
+                        wait_ld();
+                        uint32_t r[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(o[j] * alpha);
+                        tmem_st32(tm_lane + T5_TM_O + 32 * c, r);
+                    }
+                }
+                l *= alpha;
+                if (need) m_ref = mc;
+            }
+            const float ms = m_ref > -INFINITY ? m_ref : 0.f;   // exp2(-inf - ms) = 0, never NaN
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pr[32], zero[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float e0 = ex2f(s[2 * j] - ms), e1 = ex2f(s[2 * j + 1] - ms);
+                sum[j & 3] += e0 + e1;
+                pr[j] = pack_h2f(e0, e1);
+                zero[j] = 0u;
+            }
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            // P over the scores it came from: this lane's keys in its half of the 64 columns, zeros in the other half
+            tmem_st32(tm_lane + T5_TM_S + 128 * b + 32 * half, pr);
+            tmem_st32(tm_lane + T5_TM_S + 128 * b + 32 * (half ^ 1), zero);
+            wait_st();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[b]);
+        }
+        if (ok) {
+            ok = mbar_wait_spin(&pv_done[(n_c - 1) & 1], (uint32_t)((n_c - 1) >> 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (!ok) abort_flag = 1;
+        fence_after_sync();
+        // one record per (span, key half, kv head, query): [m, l, O[128]], m back in the natural-log domain
+        float* rec = partials + (((uint64_t)(2 * span + half) * g.n_kv + kvh) * T5_Q + q) * (T5_HD + 2);
+        rec[0] = ok ? m_ref * 0.6931471805599453f : -INFINITY;
+        rec[1] = ok ? l : 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float o[32];
+            tmem_ld32(tm_lane + T5_TM_O + 32 * c, o);
+            wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) *reinterpret_cast<float2*>(rec + 2 + 32 * c + j) = make_float2(o[j], o[j + 1]);
+        }
+    } else if (warp == 4) {
+        // ================= MMA issue =================
+        constexpr uint32_t IDESC = instr_desc(128);
+        const uint32_t ring_addr = smem_u32(ring);
+        // the query operand: p_ready[1] counts the four softmax warps once before its first use for a tile (tile 1 waits
+        // for its phase 1)
+        bool ok = mbar_wait_spin(&p_ready[1], 0u, err, DEV_ERR_WAIT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        auto issue_qk = [&](int i) {
+            const int b = i & 1, slot = (2 * i) % T5_SLOTS;
+            ok = mbar_wait_spin(&full[slot], (uint32_t)((2 * i) / T5_SLOTS) & 1u, err, DEV_ERR_WAIT_FULL);
+            // the buffer's P was the operand of the tile two steps back
+            if (ok && i >= 2) ok = mbar_wait_spin(&pv_done[b], (uint32_t)((i >> 1) - 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            fence_after_sync();
+            if (elect_one()) {
+                const uint32_t k_addr = ring_addr + (uint32_t)slot * T5_TILE;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)   // k steps of 16: the hi plane against the tile, then the lo plane against it again
+                    mma_ts_rt(tmem + T5_TM_S + 128u * (uint32_t)b, tmem + T5_TM_Q + 8u * (uint32_t)j,
+                              smem_desc(k_addr + (uint32_t)(j & 7) * 4096u, 2048, 128), IDESC, j > 0 ? 1u : 0u);
+                mma_commit(&s_ready[b]);
+                mma_commit(&empty[slot]);
+            }
+            __syncwarp();
+        };
+        if (ok) issue_qk(0);
+        for (int i = 0; i < n_c && ok; ++i) {
+            if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&abort_flag) != 0)) { ok = false; break; }
+            if (i + 1 < n_c) {
+                issue_qk(i + 1);
+                if (!ok) break;
+            }
+            const int b = i & 1, slot = (2 * i + 1) % T5_SLOTS;
+            // tile 1's P arrives in phase 1 of p_ready[1] (phase 0 announced the query operand)
+            const uint32_t p_phase = b == 1 ? (uint32_t)((i >> 1) + 1) & 1u : (uint32_t)(i >> 1) & 1u;
+            ok = mbar_wait_spin(&p_ready[b], p_phase, err, DEV_ERR_WAIT_FULL);
+            if (ok) ok = mbar_wait_spin(&full[slot], (uint32_t)((2 * i + 1) / T5_SLOTS) & 1u, err, DEV_ERR_WAIT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            if (elect_one()) {
+                const uint32_t v_addr = ring_addr + (uint32_t)slot * T5_TILE;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)   // 16 keys per step
+                    mma_ts_rt(tmem + T5_TM_O, tmem + T5_TM_S + 128u * (uint32_t)b + 8u * (uint32_t)j, smem_desc(v_addr + (uint32_t)j * 4096u, 2048, 128),
+                              IDESC, (i > 0 || j > 0) ? 1u : 0u);
+                mma_commit(&empty[slot]);
+                mma_commit(&pv_done[b]);
+            }
+            __syncwarp();
+        }
+        if (!ok) abort_flag = 1;
+    } else {
+        // ================= producer =================
+        if (lane == 0) {
+            pdl_wait();   // the block's own K / V rows come from the kernel before
+            bool ok = true;
+            int issued = 0;
+            const int n_t = 2 * n_c;   // tiles: K of tile i, V of tile i, K of tile i + 1, ...
+            for (int t = 0; t < n_t && ok; ++t) {
+                const int slot = t % T5_SLOTS;
+                if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+                if (t >= T5_SLOTS) ok = mbar_wait_bounded(&empty[slot], (uint32_t)(t / T5_SLOTS - 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+                if (!ok) break;
+                const uint64_t tile = ((uint64_t)(c_begin + (t >> 1)) * g.n_kv + kvh) * (uint64_t)(KV_TILE_KEYS * T5_HD);
+                mbar_arrive_expect_tx(&full[slot], T5_TILE);
+                bulk_g2s(ring + slot * T5_TILE, ((t & 1) ? v_cache : k_cache) + tile, T5_TILE, &full[slot]);
+                issued = t + 1;
+            }
+            if (!ok) abort_flag = 1;
+            // nothing may still be in flight into this CTA's shared memory when it leaves
+            for (int t = issued > T5_SLOTS ? issued - T5_SLOTS : 0; t < issued; ++t)
+                mbar_wait_bounded(&full[t % T5_SLOTS], (uint32_t)(t / T5_SLOTS) & 1u, err, DEV_ERR_WAIT_DRAIN);
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        fence_after_sync();
+        tmem_free(tmem, T5_TM_COLS);
+    }
+}
+
+bool attn_t5_supported(const AttnGeom& g, bool kv_f16) { return kv_f16 && g.hd == T5_HD && g.n_q / g.n_kv == T5_GROUP; }
+
+// tiles per span from the session's KV capacity only (never from the call): one CTA per SM and one wave at full
+// capacity - as many spans per KV head as whole heads' worth of CTAs fit on the SMs
+int attn_t5_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity) {
+    const uint64_t cap_chunks = ((uint64_t)kv_capacity + KV_TILE_KEYS - 1) / KV_TILE_KEYS;
+    uint64_t slots = (uint64_t)sm_count() / (uint64_t)g.n_kv * (uint64_t)g.n_kv;
+    if (slots < (uint64_t)g.n_kv) slots = (uint64_t)g.n_kv;
+    uint64_t b = (cap_chunks * g.n_kv + slots - 1) / slots;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+dfl_status launch_attn_t5(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* k_cache, const void* v_cache, uint32_t start,
+                          int n_rows, float* partials, int chunks_per_span, int* err) {
+    static std::once_flag once[16];
+    int dev = 0;
+    DFL_CUDA(cudaGetDevice(&dev));
+    cudaError_t attr = cudaSuccess;
+    std::call_once(once[dev & 15], [&] { attr = cudaFuncSetAttribute(attn_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T5_SMEM); });
+    DFL_CUDA(attr);
+    const int n_chunks = (int)((start + (uint32_t)n_rows + KV_TILE_KEYS - 1) / KV_TILE_KEYS);
+    const int n_spans = (n_chunks + chunks_per_span - 1) / chunks_per_span;
+    launch_k(attn_t5_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(T5_THREADS), (size_t)T5_SMEM, st, g, q_rot,
+              reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), start, n_rows, partials, chunks_per_span, err);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+// ---- conversions between the tiled cache and position-major rows [pos][n_kv][128] (snapshots, host reads) ----
+__global__ void kv_tiled_to_rows_kernel(const __half* tiled, int is_v, int n_kv, uint32_t pos0, uint32_t n_pos, __half* rows) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one element
+    const uint64_t per_pos = (uint64_t)n_kv * T5_HD;
+    if (i >= (uint64_t)n_pos * per_pos) return;
+    const uint32_t pos = pos0 + (uint32_t)(i / per_pos);
+    const int h = (int)((i % per_pos) / T5_HD), d = (int)(i % T5_HD);
+    const uint64_t src = kv_tile_base(pos, n_kv, h) + (is_v ? kv_tile_v_off(pos & (KV_TILE_KEYS - 1), d) : kv_tile_k_off(pos & (KV_TILE_KEYS - 1), d));
+    rows[i] = tiled[src];
+}
+__global__ void kv_rows_to_tiled_kernel(const __half* rows, int is_v, int n_kv, uint32_t pos0, uint32_t n_pos, __half* tiled) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t per_pos = (uint64_t)n_kv * T5_HD;
+    if (i >= (uint64_t)n_pos * per_pos) return;
+    const uint32_t pos = pos0 + (uint32_t)(i / per_pos);
+    const int h = (int)((i % per_pos) / T5_HD), d = (int)(i % T5_HD);
+    const uint64_t dst = kv_tile_base(pos, n_kv, h) + (is_v ? kv_tile_v_off(pos & (KV_TILE_KEYS - 1), d) : kv_tile_k_off(pos & (KV_TILE_KEYS - 1), d));
+    tiled[dst] = rows[i];
+}
+dfl_status launch_kv_tiled_to_rows(cudaStream_t st, const void* tiled, bool is_v, int n_kv, uint32_t pos0, uint32_t n_pos, void* rows) {
+    if (n_pos == 0) return DFL_OK;
+    const uint64_t n = (uint64_t)n_pos * n_kv * T5_HD;
+    kv_tiled_to_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(reinterpret_cast<const __half*>(tiled), is_v ? 1 : 0, n_kv, pos0, n_pos,
+                                                                        reinterpret_cast<__half*>(rows));
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+dfl_status launch_kv_rows_to_tiled(cudaStream_t st, const void* rows, bool is_v, int n_kv, uint32_t pos0, uint32_t n_pos, void* tiled) {
+    if (n_pos == 0) return DFL_OK;
+    const uint64_t n = (uint64_t)n_pos * n_kv * T5_HD;
+    kv_rows_to_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(reinterpret_cast<const __half*>(rows), is_v ? 1 : 0, n_kv, pos0, n_pos,
+                                                                        reinterpret_cast<__half*>(tiled));
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+}  // namespace dfl

@@ -102,6 +102,14 @@ __device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, 
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* err, int code) {
     return mbar_wait_limit(bar, parity, err, code, kWaitPolls);
 }
+// The same bound for a hand-off that sits on a kernel's critical path: polls without a suspend hint first (a sleeping
+// thread is not always woken the moment the phase completes), then falls back to the sleeping wait.
+constexpr uint32_t kSpinPolls = 1u << 14;
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* err, int code) {
+    for (uint32_t it = 0; it < kSpinPolls; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_limit(bar, parity, err, code, kWaitPolls);
+}
 // 1-D bulk async copy global -> shared, completion counted on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {

@@ -547,7 +547,7 @@ dfl_status dsession_project_pending(dfl_dsession* ds, bool on_side) {
             const DLayerW& L = d->layers[il];
             DFL_CHECK(launch_group(st, L.kv, ds->acts_hc, ds->part_c, ep_norm, ds->err));
             DFL_CHECK(launch_attn_front(st, gkv, false, ds->part_c, L.kv.splits, (int)L.kv.total_cols, nullptr, L.k_norm_w, 0, (int)nb, ds->k_ctx[il],
-                                        ds->v_ctx[il], false, nullptr, nullptr, ds->pos_ctx_dev + c0, (long long)c0));
+                                        ds->v_ctx[il], KV_F32_ROWS, nullptr, nullptr, ds->pos_ctx_dev + c0, (long long)c0));
             if (on_side && last_block) DFL_CUDA(cudaEventRecord(ds->ev_ctx[il], st));
         }
         ds->ready += nb;
@@ -692,7 +692,7 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, boo
         const DLayerW& L = d->layers[il];
         DFL_CHECK(launch_group(st, L.qkv, ds->acts_h, ds->part, ep_norm, ds->err));
         DFL_CHECK(launch_attn_front(st, g, false, ds->part, L.qkv.splits, (int)L.qkv.total_cols, L.q_norm_w, L.k_norm_w, noise_start, n, ds->k_noise,
-                                    ds->v_noise, false, ds->q_rot, nullptr, nullptr, 0));
+                                    ds->v_noise, KV_F32_ROWS, ds->q_rot, nullptr, nullptr, 0));
         const uint32_t window = L.is_swa ? c.swa_window : 0;
         int ctx_begin = 0;
         if (window > 0 && monotonic) {  // dflash_swa_ctx_scan_start, metal_dflash.rs:570-594

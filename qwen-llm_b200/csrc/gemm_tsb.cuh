@@ -77,15 +77,6 @@ struct ParamsB {
 
 constexpr int tsb_smem_bytes() { return TSB_KC * ACTTSB_CHUNK + TSB_STAGES * TSB_SLOT + 256; }
 
-// SS form: both operands from shared memory
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    const uint32_t zero = 0;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero)
-        : "memory");
-}
 // bf16 x bf16 -> f32, both K-major, M = 128
 __host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);

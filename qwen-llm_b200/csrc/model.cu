@@ -237,8 +237,8 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         if (L.is_attn) {
             DFL_CHECK(launch_group(st, L.qkv, sc->acts_h, sc->part, ep_norm, s->err));
             DFL_CHECK(launch_attn_front(st, ag, true, sc->part, L.qkv.splits, (int)L.qkv.total_cols, L.q_norm_w, L.k_norm_w, start, (int)n,
-                                        s->k_cache[ai], s->v_cache[ai], s->kv_f16, sc->q_rot, sc->gate, nullptr));
-            DFL_CHECK(launch_attn_verify(st, ag, sc->q_rot, sc->gate, s->k_cache[ai], s->v_cache[ai], s->kv_f16, start, (int)n,
+                                        s->k_cache[ai], s->v_cache[ai], s->kv_mode, sc->q_rot, sc->gate, nullptr));
+            DFL_CHECK(launch_attn_verify(st, ag, sc->q_rot, sc->gate, s->k_cache[ai], s->v_cache[ai], s->kv_mode, start, (int)n,
                                          s->attn_partials, sc->acts_v, m->act_layout, nullptr, s->err, s->kv_capacity));
             out_proj = &L.wo;
             ++ai;
@@ -618,7 +618,16 @@ dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t 
     s->kv_capacity = kv_capacity;
     s->kv_f16 = kv_f16 != 0;
     const dfl_arch& a = m->arch;
-    const size_t kv_elems = (size_t)kv_capacity * a.n_kv_heads * a.attn_head_dim;
+    // Tiled storage (the tcgen05 attention kernel) where the KV scan is what a verify pass spends its time on: fp16
+    // caches of 16384 positions and more, when the geometry fits.  DFL_ATTN_TILED=1 / 0 forces it on (where supported)
+    // or off.
+    s->kv_mode = s->kv_f16 ? KV_F16_ROWS : KV_F32_ROWS;
+    if (m->n_attn && attn_t5_supported(m->attn_geom(), s->kv_f16)) {
+        const char* e = getenv("DFL_ATTN_TILED");
+        if (e ? e[0] == '1' : kv_capacity >= 16384) s->kv_mode = KV_F16_TILED;
+    }
+    const size_t cap_alloc = s->kv_mode == KV_F16_TILED ? ((size_t)kv_capacity + KV_TILE_KEYS - 1) / KV_TILE_KEYS * KV_TILE_KEYS : kv_capacity;
+    const size_t kv_elems = cap_alloc * a.n_kv_heads * a.attn_head_dim;
     const size_t kv_bytes = kv_elems * (s->kv_f16 ? 2 : 4);
     const size_t conv_bytes = (size_t)3 * m->gdn_geom().conv_dim() * 4;
     const size_t ssm_bytes = (size_t)a.gdn_n_v_heads * 128 * 128 * 4;
@@ -626,6 +635,8 @@ dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t 
     for (int i = 0; i < m->n_attn && ok; ++i) {
         void *k = nullptr, *v = nullptr;
         ok = cudaMalloc(&k, kv_bytes) == cudaSuccess && cudaMalloc(&v, kv_bytes) == cudaSuccess;
+        // whole tiles go through the tensor cores, positions not yet written included: they must hold finite values
+        if (ok && s->kv_mode == KV_F16_TILED) { cudaMemset(k, 0, kv_bytes); cudaMemset(v, 0, kv_bytes); }
         s->k_cache.push_back(k);
         s->v_cache.push_back(v);
     }
@@ -708,7 +719,22 @@ dfl_status dfl_session_read_kv(const dfl_session* s, uint32_t attn_index, uint32
     if (n != stride) return fail(DFL_ERR_BAD_SHAPE, "read_kv: row size");
     DFL_CHECK(use_device(s->m->device));
     DFL_CUDA(cudaStreamSynchronize(s->st));
-    if (s->kv_f16) {
+    if (s->kv_mode == KV_F16_TILED) {
+        std::vector<__half> hk(stride), hv(stride);
+        __half* tmp = nullptr;
+        DFL_CUDA(cudaMalloc(&tmp, 2 * stride * 2));
+        dfl_status st = launch_kv_tiled_to_rows(s->st, s->k_cache[attn_index], false, (int)s->m->arch.n_kv_heads, pos, 1, tmp);
+        if (st == DFL_OK) st = launch_kv_tiled_to_rows(s->st, s->v_cache[attn_index], true, (int)s->m->arch.n_kv_heads, pos, 1, tmp + stride);
+        cudaError_t e = cudaStreamSynchronize(s->st);
+        if (st == DFL_OK && e == cudaSuccess) {
+            cudaMemcpy(hk.data(), tmp, stride * 2, cudaMemcpyDeviceToHost);
+            e = cudaMemcpy(hv.data(), tmp + stride, stride * 2, cudaMemcpyDeviceToHost);
+        }
+        cudaFree(tmp);
+        DFL_CHECK(st);
+        DFL_CUDA(e);
+        for (uint64_t i = 0; i < stride; ++i) { k_out[i] = __half2float(hk[i]); v_out[i] = __half2float(hv[i]); }
+    } else if (s->kv_f16) {
         std::vector<__half> hk(stride), hv(stride);
         DFL_CUDA(cudaMemcpy(hk.data(), (const __half*)s->k_cache[attn_index] + pos * stride, stride * 2, cudaMemcpyDeviceToHost));
         DFL_CUDA(cudaMemcpy(hv.data(), (const __half*)s->v_cache[attn_index] + pos * stride, stride * 2, cudaMemcpyDeviceToHost));
@@ -998,9 +1024,26 @@ dfl_status dfl_session_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession
     h.state_bytes = (uint64_t)h.id.n_gdn_layers * h.id.gdn_state_elements_per_layer * 4;
     uint8_t* p = (uint8_t*)blob + sizeof(SnapshotHeader);
     const uint64_t per_layer = (uint64_t)h.prefix_len * h.id.kv_bytes_per_token;
-    for (int which = 0; which < 2; ++which)   // packed to the prefix: the unused tail of the cache is not carried
-        for (size_t ai = 0; ai < s->k_cache.size(); ++ai, p += per_layer)
-            if (per_layer) DFL_CUDA(cudaMemcpyAsync(p, which ? s->v_cache[ai] : s->k_cache[ai], per_layer, cudaMemcpyDeviceToHost, s->st));
+    // packed to the prefix, as position-major rows whatever the session's storage: the unused tail of the cache is not
+    // carried, and a snapshot restores into a session of either storage
+    void* rows_tmp = nullptr;
+    if (s->kv_mode == KV_F16_TILED && per_layer) DFL_CUDA(cudaMalloc(&rows_tmp, per_layer));
+    for (int which = 0; which < 2; ++which)
+        for (size_t ai = 0; ai < s->k_cache.size(); ++ai, p += per_layer) {
+            if (!per_layer) continue;
+            const void* src = which ? s->v_cache[ai] : s->k_cache[ai];
+            if (rows_tmp) {
+                dfl_status cs = launch_kv_tiled_to_rows(s->st, src, which != 0, (int)m->arch.n_kv_heads, 0, h.prefix_len, rows_tmp);
+                cudaError_t ce = cs == DFL_OK ? cudaMemcpyAsync(p, rows_tmp, per_layer, cudaMemcpyDeviceToHost, s->st) : cudaSuccess;
+                if (ce == cudaSuccess) ce = cudaStreamSynchronize(s->st);   // the staging rows are reused by the next layer
+                if (cs != DFL_OK || ce != cudaSuccess) {
+                    cudaFree(rows_tmp);
+                    DFL_CHECK(cs);
+                    DFL_CUDA(ce);
+                }
+            } else DFL_CUDA(cudaMemcpyAsync(p, src, per_layer, cudaMemcpyDeviceToHost, s->st));
+        }
+    if (rows_tmp) cudaFree(rows_tmp);
     for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)h.id.gdn_conv_elements_per_layer * 4)
         DFL_CUDA(cudaMemcpyAsync(p, s->conv[gi], (uint64_t)h.id.gdn_conv_elements_per_layer * 4, cudaMemcpyDeviceToHost, s->st));
     for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)h.id.gdn_state_elements_per_layer * 4)
@@ -1044,9 +1087,25 @@ dfl_status dfl_session_restore_snapshot(const dfl_model* m, dfl_session* s, dfl_
         DFL_CHECK(dsession_snapshot_validate(ds, h.drafter_cols, h.drafter_bytes));
     }
     const uint8_t* p = (const uint8_t*)blob + sizeof(h);
+    void* rows_tmp = nullptr;
+    if (s->kv_mode == KV_F16_TILED && per_layer) DFL_CUDA(cudaMalloc(&rows_tmp, per_layer));
     for (int which = 0; which < 2; ++which)
-        for (size_t ai = 0; ai < s->k_cache.size(); ++ai, p += per_layer)
-            if (per_layer) DFL_CUDA(cudaMemcpyAsync(which ? s->v_cache[ai] : s->k_cache[ai], p, per_layer, cudaMemcpyHostToDevice, s->st));
+        for (size_t ai = 0; ai < s->k_cache.size(); ++ai, p += per_layer) {
+            if (!per_layer) continue;
+            void* dst = which ? s->v_cache[ai] : s->k_cache[ai];
+            if (rows_tmp) {
+                cudaError_t ce = cudaMemcpyAsync(rows_tmp, p, per_layer, cudaMemcpyHostToDevice, s->st);
+                dfl_status cs = ce == cudaSuccess ? launch_kv_rows_to_tiled(s->st, rows_tmp, which != 0, (int)m->arch.n_kv_heads, 0, h.prefix_len, dst) : DFL_OK;
+                if (ce == cudaSuccess) ce = cudaStreamSynchronize(s->st);
+                if (cs != DFL_OK || ce != cudaSuccess) {
+                    cudaFree(rows_tmp);
+                    s->poisoned = true;   // part of the state has been overwritten
+                    DFL_CHECK(cs);
+                    DFL_CUDA(ce);
+                }
+            } else DFL_CUDA(cudaMemcpyAsync(dst, p, per_layer, cudaMemcpyHostToDevice, s->st));
+        }
+    if (rows_tmp) cudaFree(rows_tmp);
     for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)id.gdn_conv_elements_per_layer * 4)
         DFL_CUDA(cudaMemcpyAsync(s->conv[gi], p, (uint64_t)id.gdn_conv_elements_per_layer * 4, cudaMemcpyHostToDevice, s->st));
     for (size_t gi = 0; gi < s->conv.size(); ++gi, p += (uint64_t)id.gdn_state_elements_per_layer * 4)

@@ -123,10 +123,11 @@ struct dfl_session {
     const dfl_model* m = nullptr;
     uint32_t kv_capacity = 0;
     bool kv_f16 = false;
+    int kv_mode = dfl::KV_F32_ROWS;   // storage of the K / V caches (ops.cuh KvMode); tiled only for f16, 128-wide heads, groups of four
     uint32_t kv_n_pos = 0;
     bool poisoned = false;
     bool fail_next = false;
-    std::vector<void*> k_cache, v_cache;  // per attention layer: [capacity][n_kv][hd]
+    std::vector<void*> k_cache, v_cache;  // per attention layer: [capacity][n_kv][hd] rows, or tiles of 128 positions per KV head (kv_mode)
     std::vector<float*> conv;             // per GDN layer: [3][conv_dim]
     std::vector<float*> ssm[2];           // per GDN layer, double buffered: [n_v][128][128]
     std::vector<int> ssm_cur;

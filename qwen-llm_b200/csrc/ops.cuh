@@ -219,6 +219,15 @@ struct AttnGeom {
 };
 constexpr int ATTN_CHUNK = 64;
 constexpr int ATTN_ROW_GROUP = 4;  // query rows per attention CTA
+// KV cache storage: position-major rows [pos][n_kv][hd] of f32 or f16, or (f16, 128-wide heads) tiles of 128 positions
+// per KV head in the operand layout of tcgen05.mma (attn_t5.cu)
+enum KvMode { KV_F32_ROWS = 0, KV_F16_ROWS = 1, KV_F16_TILED = 2 };
+constexpr int KV_TILE_KEYS = 128;
+// element index (in halfs) of a tile and of (key, dim) inside a K tile (B[n = key][k = dim]) and a V tile (B[n = dim][k = key]):
+// 8 x 8 core matrices of 64 halfs, the sixteen n-groups of a k-core contiguous, k-cores 1024 halfs apart
+__host__ __device__ inline uint64_t kv_tile_base(uint32_t pos, int n_kv, int h) { return ((uint64_t)(pos / KV_TILE_KEYS) * n_kv + h) * (uint64_t)(KV_TILE_KEYS * 128); }
+__host__ __device__ inline uint32_t kv_tile_k_off(uint32_t key, int d) { return (uint32_t)((d >> 3) * 1024 + (int)(key >> 3) * 64 + (int)(key & 7) * 8 + (d & 7)); }
+__host__ __device__ inline uint32_t kv_tile_v_off(uint32_t key, int d) { return (uint32_t)((int)(key >> 3) * 1024 + (d >> 3) * 64 + (d & 7) * 8 + (int)(key & 7)); }
 // Reduces the fused q|k|v GEMM partials, applies per-head RMSNorm + partial NeoX RoPE, appends K/V
 // at positions start..start+n_rows-1 and leaves rotated Q and the raw gate for the attention kernel.
 // gated: q rows are interleaved (q, gate) per head as in the target; otherwise plain q.
@@ -226,13 +235,20 @@ constexpr int ATTN_ROW_GROUP = 4;  // query rows per attention CTA
 // K/V at rows cache_row0 + tok instead of at the position (the drafter's context cache).
 dfl_status launch_attn_front(cudaStream_t st, const AttnGeom& g, bool gated, const float* part, int splits, int ld_part,
                              const float* q_norm_w, const float* k_norm_w, uint32_t start, int n_rows, void* k_cache,
-                             void* v_cache, bool kv_f16, float* q_rot, float* gate, const uint32_t* pos_override,
+                             void* v_cache, int kv_mode, float* q_rot, float* gate, const uint32_t* pos_override,
                              long long cache_row0 = -1);
 // Causal attention of the n_rows query rows over cache positions [0, start + row]; partials per
 // 64-position chunk, then combine, sigmoid gate and activation packing for the o-projection.
 dfl_status launch_attn_verify(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* gate, const void* k_cache,
-                              const void* v_cache, bool kv_f16, uint32_t start, int n_rows, float* partials, uint8_t* acts,
+                              const void* v_cache, int kv_mode, uint32_t start, int n_rows, float* partials, uint8_t* acts,
                               int act_layout, float* out_f32, int* err, uint32_t kv_capacity = 0);
+// tcgen05 span kernel over a tiled fp16 cache (attn_t5.cu) and the conversions between that cache and position-major rows
+bool attn_t5_supported(const AttnGeom& g, bool kv_f16);
+int attn_t5_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity);
+dfl_status launch_attn_t5(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* k_cache, const void* v_cache, uint32_t start,
+                          int n_rows, float* partials, int chunks_per_span, int* err);
+dfl_status launch_kv_tiled_to_rows(cudaStream_t st, const void* tiled, bool is_v, int n_kv, uint32_t pos0, uint32_t n_pos, void* rows);
+dfl_status launch_kv_rows_to_tiled(cudaStream_t st, const void* rows, bool is_v, int n_kv, uint32_t pos0, uint32_t n_pos, void* tiled);
 // tensor-core span kernel over an fp16 cache (attn_tc.cu)
 bool attn_tc_supported(const AttnGeom& g, bool kv_f16);
 int attn_tc_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity);

@@ -11,7 +11,7 @@ logits, captured hidden rows, recurrent state, KV rows and (routed experts) the 
 fed the accepted tokens one at a time (forward.rs:173-220, :749-824, :834-932, :940-1107).  The weights are made
 on the GPU by the library's seeded generator and copied to the host for the oracle, so both sides decode the same
 bytes.  The measured logit error and the share of rows whose oracle top-1 / top-2 gap is below 1e-4 are printed
-(run with -s) and written to gpurun_out/geometry_parity.json when that directory exists."""
+(run with -s) and, when DFL_PARITY_REPORT_DIR names a directory, written to geometry_parity.json there."""
 import importlib
 import json
 import os
@@ -31,8 +31,8 @@ GAP = 1e-4               # rows with a smaller oracle top-1 / top-2 gap are near
 
 def _report(name, stats):
     print(name, json.dumps(stats))
-    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("DFL_PARITY_REPORT_DIR", "")
+    if out and os.path.isdir(out):
         path = os.path.join(out, "geometry_parity.json")
         allr = json.load(open(path)) if os.path.exists(path) else {}
         allr[name] = stats
@@ -166,6 +166,14 @@ def test_dense_9b_widths_verify_and_rollback_match_oracle():
     # the first 64-position KV chunk
     arch = _slice_arch(syn.arch_9b(), 4, 4)
     _verify_rollback_case("dense_9b_widths", arch, seed=41, n_gdn=3, warm_blocks=5)
+
+
+def test_dense_9b_widths_with_the_tiled_kv_cache(monkeypatch):
+    # the same slice over the tiled fp16 cache (tcgen05 attention kernel): 8 KV heads' tiles side by side, nine warm-up
+    # blocks so that the checked blocks attend over two 128-position tiles (two spans at this capacity)
+    monkeypatch.setenv("DFL_ATTN_TILED", "1")
+    arch = _slice_arch(syn.arch_9b(), 4, 4)
+    _verify_rollback_case("dense_9b_widths_tiled_kv", arch, seed=41, n_gdn=3, warm_blocks=9)
 
 
 def test_routed_35b_a3b_widths_verify_and_rollback_match_oracle():

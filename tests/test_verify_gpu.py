@@ -259,9 +259,15 @@ def tiny_g4():
     gm.close()
 
 
-@pytest.mark.parametrize("cap", [384, 40000])
-def test_tensor_core_attention_matches_oracle_and_single_token_steps(tiny_g4, cap):
-    # cap 384: one 64-position chunk per record; cap 40000: several chunks per span (online softmax inside the CTA)
+@pytest.mark.parametrize("cap,tiled", [(384, "0"), (40000, "0"), (384, "1"), (40000, None)])
+def test_tensor_core_attention_matches_oracle_and_single_token_steps(tiny_g4, cap, tiled, monkeypatch):
+    # row-major cache (mma.sync kernel): cap 384 = one 64-position chunk per record, cap 40000 = several chunks per span
+    # (online softmax inside the CTA).  Tiled cache (tcgen05 kernel): forced on at cap 384 (one 128-position tile per
+    # span, so the 240 positions make two spans), chosen by the capacity itself at 40000 (two tiles in one span)
+    if tiled is None:
+        monkeypatch.delenv("DFL_ATTN_TILED", raising=False)
+    else:
+        monkeypatch.setenv("DFL_ATTN_TILED", tiled)
     arch, om, gm = tiny_g4
     rng = np.random.default_rng(31)
     sess, scr = pkg.Session(gm, cap, True), pkg.Scratch(gm, 16, 1)
@@ -293,6 +299,42 @@ def test_tensor_core_attention_matches_oracle_and_single_token_steps(tiny_g4, ca
     _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=True)
     np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
     for o in (sess, scr, single, scr1):
+        o.close()
+
+
+def test_snapshot_moves_between_tiled_and_row_major_caches(tiny_g4, monkeypatch):
+    # a snapshot carries K / V as position-major rows whatever the session's storage: tiled -> tiled continues bitwise,
+    # tiled -> rows and rows -> tiled hold the same f16 rows
+    arch, om, gm = tiny_g4
+    rng = np.random.default_rng(77)
+    cap = 384
+    monkeypatch.setenv("DFL_ATTN_TILED", "1")
+    src, scr = pkg.Session(gm, cap, True), pkg.Scratch(gm, 16, 1)
+    pos = 0
+    for _ in range(9):                                # 144 positions: one full tile and a partial one
+        pkg.packed_verify(gm, src, scr, [3], rng.integers(0, arch.vocab_size, size=16), pos)
+        pos += 16
+    blob = pkg.session_snapshot(gm, src, None)
+    same = pkg.Session(gm, cap, True)
+    pkg.session_restore_snapshot(gm, same, None, blob)
+    monkeypatch.setenv("DFL_ATTN_TILED", "0")
+    rows = pkg.Session(gm, cap, True)
+    pkg.session_restore_snapshot(gm, rows, None, blob)
+    blob_rows = pkg.session_snapshot(gm, rows, None)
+    assert bytes(blob_rows) == bytes(blob)            # rows -> snapshot is the identical byte string
+    for p in (0, 127, 128, pos - 1):
+        k0, v0 = src.read_kv(0, p)
+        for other in (same, rows):
+            k1, v1 = other.read_kv(0, p)
+            assert k0.tobytes() == k1.tobytes() and v0.tobytes() == v1.tobytes(), p
+    toks = rng.integers(0, arch.vocab_size, size=16)
+    scr2 = pkg.Scratch(gm, 16, 1)
+    _, _, a = pkg.packed_verify(gm, src, scr, [3], toks, pos, want_logits=True)
+    _, _, b = pkg.packed_verify(gm, same, scr2, [3], toks, pos, want_logits=True)
+    assert a.tobytes() == b.tobytes()
+    _, _, c = pkg.packed_verify(gm, rows, scr2, [3], toks, pos, want_logits=True)   # other kernel, same values to tolerance
+    np.testing.assert_allclose(c, a, rtol=RTOL, atol=ATOL)
+    for o in (src, same, rows, scr, scr2):
         o.close()
 
 
