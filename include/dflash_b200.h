@@ -258,7 +258,13 @@ uint64_t dfl_drafter_weight_bytes(const dfl_drafter* d);
 
 /* MetalSession::fresh(ctx, model, kv_capacity)  metal_forward/mod.rs:2238-2391.
  * kv_f16 != 0 stores K/V as fp16 (the reference GPU layout, mod.rs:2330-2341);
- * 0 stores f32 (the CPU oracle's layout, forward.rs:1142-1151). */
+ * 0 stores f32 (the CPU oracle's layout, forward.rs:1142-1151).  An fp16 cache of
+ * 128-wide heads in GQA groups of four is stored as position-major rows below
+ * 16384 positions of capacity and as 128-position tiles in the tensor cores'
+ * operand layout from there on (the long-context attention kernel); the choice is
+ * fixed per session, invisible through this interface (dfl_session_read_kv and
+ * snapshots speak position-major rows for both) and can be forced with
+ * DFL_ATTN_TILED=1 / 0 in the environment. */
 dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t kv_f16,
                               dfl_session** out);
 void dfl_session_destroy(dfl_session* s);

@@ -42,8 +42,12 @@ using namespace ts;
 constexpr int T5_HD = 128, T5_GROUP = 4, T5_Q = MAX_ROWS * T5_GROUP;   // 64 queries per CTA
 constexpr int T5_TILE = KV_TILE_KEYS * T5_HD * 2;                      // 32768 bytes: one K or V tile
 constexpr int T5_SLOTS = 6;
-constexpr int T5_OFF_BAR = T5_SLOTS * T5_TILE;
+constexpr int T5_QPITCH = T5_HD + 1;                                   // floats per staged query row (odd: a row per lane is conflict-free)
+constexpr int T5_OFF_QSTAGE = T5_SLOTS * T5_TILE;
+constexpr int T5_OFF_BAR = T5_OFF_QSTAGE + T5_Q * T5_QPITCH * 4;
 constexpr int T5_SMEM = T5_OFF_BAR + 256;
+static_assert(T5_SMEM <= 227 * 1024, "shared memory budget");
+static_assert(T5_Q * 2 * (T5_HD + 2) * 4 <= T5_SLOTS * T5_TILE, "the records are staged in the ring");
 constexpr int T5_THREADS = 192;
 // tensor memory: two score buffers of 128 columns (P overlays the first 64 of its buffer), the output, the query operand
 constexpr uint32_t T5_TM_S = 0, T5_TM_O = 256, T5_TM_Q = 384, T5_TM_COLS = 512;
@@ -72,6 +76,7 @@ attn_t5_kernel(AttnGeom g, const float* q_rot, const __half* k_cache, const __ha
                int chunks_per_span, int* err) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
+    float* q_stage = reinterpret_cast<float*>(smem + T5_OFF_QSTAGE);   // [64][129] f32: the queries, loaded row by row
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + T5_OFF_BAR);   // [6] a slot's tile has landed
     uint64_t* empty = full + T5_SLOTS;        // [6] the MMAs that read the slot have completed
     uint64_t* s_ready = empty + T5_SLOTS;     // [2] S = Q K^T of a tile is in tensor memory
@@ -114,20 +119,25 @@ attn_t5_kernel(AttnGeom g, const float* q_rot, const __half* k_cache, const __ha
         const uint32_t tm_lane = tmem + ((uint32_t)(32 * warp) << 16);
         pdl_wait();   // the rotated queries come from the kernel before
         {
-            // this lane's query (row = q / 4, head = kvh * 4 + q % 4), scaled by log2(e) / sqrt(hd) (scores live in the
-            // exp2 domain) and split into an exact f16 hi + lo pair: columns 0-63 = hi plane (k = 0..127), 64-127 = lo
+            // the 64 queries (pair = row * 4 + head-in-group) into shared memory with coalesced loads, then each lane takes
+            // its own: scaled by log2(e) / sqrt(hd) (scores live in the exp2 domain) and split into an exact f16 hi + lo
+            // pair; columns 0-63 of the operand = hi plane (k = 0..127), 64-127 = lo plane
+            for (int idx = L; idx < T5_Q * (T5_HD / 4); idx += 128) {
+                const int pair = idx / (T5_HD / 4), d4 = (idx % (T5_HD / 4)) * 4;
+                const int row = pair / T5_GROUP;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (row < n_rows) v = *reinterpret_cast<const float4*>(q_rot + ((uint64_t)row * g.n_q + kvh * T5_GROUP + pair % T5_GROUP) * T5_HD + d4);
+                float* dst = q_stage + pair * T5_QPITCH + d4;
+                dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // the four softmax warps
             const float scale = 1.4426950408889634f / sqrtf((float)T5_HD);
-            const float4* src = reinterpret_cast<const float4*>(q_rot + ((uint64_t)tok * g.n_q + kvh * T5_GROUP + (q & 3)) * T5_HD);
+            const float* src = q_stage + q * T5_QPITCH;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {   // 64 dims at a time
                 uint32_t hi[32], lo[32];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (tok < n_rows) v = src[16 * c + j];
-                    split_pair_f(v.x * scale, v.y * scale, hi[2 * j], lo[2 * j]);
-                    split_pair_f(v.z * scale, v.w * scale, hi[2 * j + 1], lo[2 * j + 1]);
-                }
+                for (int j = 0; j < 32; ++j) split_pair_f(src[64 * c + 2 * j] * scale, src[64 * c + 2 * j + 1] * scale, hi[j], lo[j]);
                 tmem_st32(tm_lane + T5_TM_Q + 32 * c, hi);
                 tmem_st32(tm_lane + T5_TM_Q + 64 + 32 * c, lo);
             }
@@ -216,17 +226,27 @@ attn_t5_kernel(AttnGeom g, const float* q_rot, const __half* k_cache, const __ha
         }
         if (!ok) abort_flag = 1;
         fence_after_sync();
-        // one record per (span, key half, kv head, query): [m, l, O[128]], m back in the natural-log domain
-        float* rec = partials + (((uint64_t)(2 * span + half) * g.n_kv + kvh) * T5_Q + q) * (T5_HD + 2);
-        rec[0] = ok ? m_ref * 0.6931471805599453f : -INFINITY;
-        rec[1] = ok ? l : 0.f;
+        // one record per (span, key half, kv head, query): [m, l, O[128]], m back in the natural-log domain.  The two
+        // groups of 64 records are contiguous in global memory; they are laid out in the ring (idle by now: every tile
+        // has been consumed) and written with coalesced stores.
+        float* stage = reinterpret_cast<float*>(ring) + (uint64_t)L * (T5_HD + 2);
+        stage[0] = ok ? m_ref * 0.6931471805599453f : -INFINITY;
+        stage[1] = ok ? l : 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             float o[32];
             tmem_ld32(tm_lane + T5_TM_O + 32 * c, o);
             wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) *reinterpret_cast<float2*>(rec + 2 + 32 * c + j) = make_float2(o[j], o[j + 1]);
+            for (int j = 0; j < 32; j += 2) *reinterpret_cast<float2*>(stage + 2 + 32 * c + j) = make_float2(o[j], o[j + 1]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        constexpr int REC2 = T5_Q * (T5_HD + 2) / 2;   // float2 per group of 64 records
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float2* dst = reinterpret_cast<float2*>(partials + ((uint64_t)(2 * span + hh) * g.n_kv + kvh) * T5_Q * (T5_HD + 2));
+            const float2* src2 = reinterpret_cast<const float2*>(ring) + hh * REC2;
+            for (int idx = L; idx < REC2; idx += 128) dst[idx] = src2[idx];
         }
     } else if (warp == 4) {
         // ================= MMA issue =================
