@@ -12,8 +12,10 @@
 //
 // Parity status: the primitives are pinned by forward.rs:1377-1414; the reference
 // has no golden vectors for whole-model logits that can run without its model files
-// (forward.rs:1416-1886 need GGUFs), so end-to-end logits parity is pinned by
-// construction only ("parity unpinned" for the full forward).
+// (forward.rs:1416-1886 need GGUFs), so end-to-end logits parity is "parity unpinned"
+// for the full forward: it rests on this restatement and on its agreement, token by
+// token, with a second restatement written separately in numpy over other block
+// decoders (oracle/forward_np.py, tests/test_oracle_twin.py).
 #pragma once
 #include <algorithm>
 #include <cmath>

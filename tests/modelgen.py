@@ -128,6 +128,13 @@ class OracleModel:
         assert self.L.orc_state_read_gdn(st, C.c_uint32(gi), p(ssm), p(conv)) == 0
         return ssm, conv
 
+    def last_route(self, cap=64):
+        """Expert ids the last routed-expert call chose (the model's last MoE layer of the last token)."""
+        import ctypes as C
+        out = np.zeros(cap, dtype=np.int32)
+        n = int(self.L.orc_last_route(self.h, out.ctypes.data_as(C.c_void_p), C.c_uint32(cap)))
+        return [int(v) for v in out[:n]]
+
     def read_kv(self, st, ai, pos):
         import ctypes as C
         n = self.arch.n_kv_heads * self.arch.attn_head_dim
