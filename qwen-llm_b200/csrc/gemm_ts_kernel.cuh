@@ -177,8 +177,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
         const uint32_t acts_addr = smem_u32(acts_res);
         const uint32_t a_buf = tmem + TM_A + g * TM_A_STRIDE, d_buf = tmem + TM_D + g * TM_D_STRIDE + 32 * c;
         uint32_t uses = 0;   // how often this warp's half buffer has been used
+        int kb_e = (int)g % n_kb;   // e % n_kb, kept by addition
+        const int kb_step = 2 % n_kb;
         for (int e = (int)g; e < n_it && ok; e += 2) {
-            const uint32_t chunk = acts_addr + (e % n_kb) * ACTTS_CHUNK;
+            const uint32_t chunk = acts_addr + (uint32_t)kb_e * ACTTS_CHUNK;
+            kb_e += kb_step;
+            if (kb_e >= n_kb) kb_e -= n_kb;
             if (e < n_kb) {   // first row tile: the column block's activations may still be in flight
                 ok = mbar_wait_bounded(&acts_bar[e], 0, p.err, DEV_ERR_WAIT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
@@ -295,6 +299,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
 #pragma unroll
         for (int j = 0; j < MAX_ROWS; ++j) acc[j] = 0.f;
         bool ok = true;
+        int kb_e = 0, tile = 0;   // e % n_kb and e / n_kb, kept by addition
         for (int e = 0; e < n_it && ok; ++e) {
             const uint32_t a = (uint32_t)e & 1u;
             ok = mbar_wait_bounded(&d_ready[a], ((uint32_t)e >> 1) & 1, p.err, DEV_ERR_WAIT_FULL);
@@ -331,9 +336,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                 acc[j] = fmaf(sc.x, t[j], acc[j]);
                 if (F::HAS_MIN) acc[j] = fmaf(-sc.y, mn[j], acc[j]);
             }
-            if ((e + 1) % n_kb == 0) {   // the tile's last column block: write the partial result
-                const int tile = e / n_kb;
+            if (++kb_e == n_kb) {   // the tile's last column block: write the partial result
+                kb_e = 0;
                 const int slot = c + tile * cps;
+                ++tile;
                 const uint32_t orow = (uint32_t)(p.tile_map ? p.tile_map[slot] : slot) * TILE_R + row;
                 if (orow < p.n_out) {
                     float* dst = p.out + (uint64_t)sp * MAX_ROWS * p.ld_out + orow;
