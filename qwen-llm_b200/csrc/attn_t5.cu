@@ -51,7 +51,7 @@ static_assert(T5_Q * 2 * (T5_HD + 2) * 4 <= T5_SLOTS * T5_TILE, "the records are
 constexpr int T5_THREADS = 192;
 // tensor memory: two score buffers of 128 columns (P overlays the first 64 of its buffer), the output, the query operand
 constexpr uint32_t T5_TM_S = 0, T5_TM_O = 256, T5_TM_Q = 384, T5_TM_COLS = 512;
-constexpr float T5_RESCALE = 8.0f;   // log2 units: rescale when the maximum grows by more than this
+constexpr float T5_RESCALE = 8.0f;   // log2 units: rescale when the maximum grows by more than this (P stays below 2^8)
 
 __device__ __forceinline__ float ex2f(float x) {
     float y;
@@ -73,7 +73,7 @@ __device__ __forceinline__ void split_pair_f(float a, float b, uint32_t& hi, uin
 
 __global__ void __launch_bounds__(T5_THREADS, 1)
 attn_t5_kernel(AttnGeom g, const float* q_rot, const __half* k_cache, const __half* v_cache, uint32_t start, int n_rows, float* partials,
-               int chunks_per_span, int* err) {
+               int chunks_per_span, float rescale_above, int* err) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     float* q_stage = reinterpret_cast<float*>(smem + T5_OFF_QSTAGE);   // [64][129] f32: the queries, loaded row by row
@@ -178,7 +178,7 @@ attn_t5_kernel(AttnGeom g, const float* q_rot, const __half* k_cache, const __ha
 #pragma unroll
             for (int j = 8; j < 64; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
             const float mc = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-            const bool need = mc > m_ref + T5_RESCALE;   // also the first finite maximum (m_ref = -inf)
+            const bool need = mc > m_ref + rescale_above;   // also the first finite maximum (m_ref = -inf)
             if (__any_sync(0xffffffffu, need)) {
                 const float alpha = need ? ex2f(m_ref - mc) : 1.0f;   // 0 when there was no maximum yet
                 if (i >= 1) {
@@ -356,8 +356,15 @@ dfl_status launch_attn_t5(cudaStream_t st, const AttnGeom& g, const float* q_rot
     DFL_CUDA(attr);
     const int n_chunks = (int)((start + (uint32_t)n_rows + KV_TILE_KEYS - 1) / KV_TILE_KEYS);
     const int n_spans = (n_chunks + chunks_per_span - 1) / chunks_per_span;
+    // DFL_ATTN_T5_RESCALE (test hook): the growth of a lane's maximum, in log2 units within [0, 12], above which the
+    // output is rescaled; 0 rescales at every new maximum.  Results must agree with the oracle at any setting.
+    float rescale_above = T5_RESCALE;
+    if (const char* e = getenv("DFL_ATTN_T5_RESCALE")) {
+        const float v = (float)atof(e);
+        if (v >= 0.f && v <= 12.f) rescale_above = v;
+    }
     launch_k(attn_t5_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(T5_THREADS), (size_t)T5_SMEM, st, g, q_rot,
-              reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), start, n_rows, partials, chunks_per_span, err);
+              reinterpret_cast<const __half*>(k_cache), reinterpret_cast<const __half*>(v_cache), start, n_rows, partials, chunks_per_span, rescale_above, err);
     count_launch();
     DFL_CUDA(cudaGetLastError());
     return DFL_OK;

@@ -1,5 +1,7 @@
-// Verify attention over an fp16 KV cache on the tensor cores, for the long-context shape of the step
-// (reference: kernel_attn_decode_* / attn_v4, kernels/attn_v4.metal:65-265; CPU oracle forward.rs:896-921).
+// Verify attention over an fp16 KV cache stored as position-major rows, on the tensor cores through mma.sync
+// (reference: kernel_attn_decode_* / attn_v4, kernels/attn_v4.metal:65-265; CPU oracle forward.rs:896-921).  Sessions
+// whose capacity reaches 16384 positions store the cache as tiles and use the tcgen05 kernel of attn_t5.cu instead;
+// this kernel serves the shorter ones, where a CTA sees one or two chunks and launch latency is what counts.
 //
 // One CTA = one KV head x one span of `chunks_per_span` 64-position chunks; all 16 block rows x the 4 query
 // heads of the GQA group (64 queries) share every K/V byte the CTA reads.  Four warps, warp w owns queries

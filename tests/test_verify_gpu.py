@@ -302,6 +302,37 @@ def test_tensor_core_attention_matches_oracle_and_single_token_steps(tiny_g4, ca
         o.close()
 
 
+@pytest.mark.parametrize("rescale", ["0", "1.5", "12"])
+def test_tcgen05_attention_agrees_with_the_oracle_at_any_rescale_threshold(monkeypatch, rescale):
+    # the kernel rescales its output accumulator only when a lane's maximum grows by more than a threshold; with the
+    # threshold at 0 every new maximum takes the rescale path (classic online softmax), at 12 almost none does.  Wide
+    # score ranges (query norm weights x 6) over 2.5 tiles in one span and over three spans.
+    monkeypatch.setenv("DFL_ATTN_TILED", "1")
+    monkeypatch.setenv("DFL_ATTN_T5_RESCALE", rescale)
+    arch = modelgen.tiny_arch(n_q_heads=4)
+    T = modelgen.target_tensors(arch, seed=23)
+    T = [(n, d, s, (np.frombuffer(bytes(b), dtype=np.float32) * 6.0).astype(np.float32).view(np.uint8)) if n.endswith("attn_q_norm.weight") else (n, d, s, b)
+         for n, d, s, b in T]
+    om, gm = modelgen.OracleModel(arch, T), pkg.Model(arch, T)
+    rng = np.random.default_rng(41)
+    for cap in (384, 40000):                         # one tile per span / all tiles in one span
+        sess, scr = pkg.Session(gm, cap, True), pkg.Scratch(gm, 16, 1)
+        ost = om.new_state(cap, True)
+        pos = 0
+        for blk_i in range(20):                      # 320 positions
+            toks = rng.integers(0, arch.vocab_size, size=16)
+            check = blk_i in (0, 8, 15, 19)
+            _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=check)
+            if check:
+                want, _ = oracle_block(om, om.clone_state(ost), toks, pos, [3])
+                np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+            for i, t in enumerate(toks):
+                om.single_token(ost, t, pos + i, (), want_logits=False)
+            pos += 16
+        sess.close(); scr.close()
+    gm.close()
+
+
 def test_snapshot_moves_between_tiled_and_row_major_caches(tiny_g4, monkeypatch):
     # a snapshot carries K / V as position-major rows whatever the session's storage: tiled -> tiled continues bitwise,
     # tiled -> rows and rows -> tiled hold the same f16 rows
