@@ -224,14 +224,20 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
 void dfl_model_destroy(dfl_model* m);
 /* Bytes of quantised weights one verify step streams (the roofline numerator). */
 uint64_t dfl_model_verify_weight_bytes(const dfl_model* m);
-/* Expert parallelism for routed-expert models (one process per GPU).  Rank r of
- * ep_world keeps experts [r*E/ep_world, (r+1)*E/ep_world) of every layer (rank 0
- * also the shared expert), everything else is replicated, and each routed-expert
- * block ends with an NCCL all-reduce of its [16][hidden] output, so every rank
- * returns the same logits.  `tensors` is the full table on every rank.  The
- * 128-byte id comes from dfl_ep_unique_id on one rank and is distributed by the
- * caller; all ranks must call dfl_model_create_ep together and then issue the same
- * verify calls in the same order.  NCCL is loaded at run time (libnccl.so.2). */
+/* Expert parallelism for routed-expert models (one process per GPU of one node).
+ * Rank r of ep_world keeps experts [r*E/ep_world, (r+1)*E/ep_world) of every layer
+ * (rank 0 also the shared expert), everything else is replicated.  Each
+ * routed-expert block ends with a combine over peer memory: every rank sums its
+ * own slices and stores its [16][hidden] result into every rank's receive buffer
+ * (plain peer stores over NVLink, per-CTA sequence flags), and the layer's glue
+ * kernel adds the ranks' slots in rank order, so every rank returns the same
+ * bits.  `tensors` is the full table on every rank.  The 128-byte id comes from
+ * dfl_ep_unique_id on one rank and is distributed by the caller; all ranks must
+ * call dfl_model_create_ep together and then issue the same verify calls in the
+ * same order, one pass at a time per model.  NCCL (loaded at run time,
+ * libnccl.so.2) carries the bootstrap - the exchange of the buffers' inter-process
+ * handles - and, with DFL_EP_COMBINE=nccl in the environment, the sum itself as
+ * an all-reduce (kept for comparison).  At most 8 ranks. */
 dfl_status dfl_ep_unique_id(uint8_t* id_out_128);
 dfl_status dfl_model_create_ep(int32_t device, const dfl_arch* arch, const dfl_tensor* tensors,
                                uint64_t n_tensors, int32_t ep_rank, int32_t ep_world,

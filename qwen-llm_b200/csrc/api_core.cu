@@ -61,6 +61,7 @@ dfl_status check_dev_err(cudaStream_t st, int* dev_err) {
         case DEV_ERR_WAIT_FULL:
         case DEV_ERR_WAIT_EMPTY:
         case DEV_ERR_WAIT_DRAIN:
+        case DEV_ERR_WAIT_PEER:
         case DEV_ERR_WAIT_FLAG: return fail(DFL_ERR_TIMEOUT, "device-side bounded wait gave up (code " + std::to_string(h) + ")");
         case DEV_ERR_OVERFLOW: return fail(DFL_ERR_CUDA, "activation outside the f16 operand range");
         case DEV_ERR_NONFINITE: return fail(DFL_ERR_ROUTE_STATUS, "expert routing met a NaN / Inf router logit (route status NONFINITE)");

@@ -42,7 +42,8 @@ enum DevErr : int {
     DEV_ERR_WAIT_DRAIN = 3,   // exit path gave up waiting for copies in flight
     DEV_ERR_NONFINITE = 4,    // NaN / Inf met where a finite value is required
     DEV_ERR_OVERFLOW = 5,     // activation outside the fp16 operand range
-    DEV_ERR_WAIT_FLAG = 6     // the wait probe (dfl_session_probe_wait_timeout): a barrier nobody arrives at
+    DEV_ERR_WAIT_FLAG = 6,    // the wait probe (dfl_session_probe_wait_timeout): a barrier nobody arrives at
+    DEV_ERR_WAIT_PEER = 7     // expert-parallel combine: a peer's contribution did not arrive (or the watchdog said stop)
 };
 
 #ifdef __CUDACC__

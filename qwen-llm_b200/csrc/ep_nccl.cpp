@@ -29,6 +29,7 @@ struct NcclApi {
     int (*GetUniqueId)(NcclId*) = nullptr;
     int (*CommInitRank)(comm_t*, int, NcclId, int) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, comm_t, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, comm_t, cudaStream_t) = nullptr;
     int (*CommDestroy)(comm_t) = nullptr;
     int (*CommAbort)(comm_t) = nullptr;
     int (*CommGetAsyncError)(comm_t, int*) = nullptr;
@@ -50,6 +51,7 @@ void load_nccl() {
     g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
     g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
     g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(dlsym(h, "ncclAllReduce"));
+    g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(dlsym(h, "ncclAllGather"));
     g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
     g_nccl.CommAbort = reinterpret_cast<decltype(g_nccl.CommAbort)>(dlsym(h, "ncclCommAbort"));
     g_nccl.CommGetAsyncError = reinterpret_cast<decltype(g_nccl.CommGetAsyncError)>(dlsym(h, "ncclCommGetAsyncError"));
@@ -124,6 +126,71 @@ dfl_status ep_watch_core(const EpWatchHooks& h, uint32_t timeout_ms, uint32_t po
     return fail(DFL_ERR_COLLECTIVE, "expert-parallel watchdog: " + why + "; communicator aborted");
 }
 
+// Exchanges the inter-process handles of every rank's exchange buffer over the communicator and maps the peers' buffers
+// into this process (plain peer access over NVLink; no multicast object is involved).
+dfl_status ep_p2p_exchange(void* comm, int rank, int world, void* local, cudaStream_t st, void** peers_out) {
+    if (!g_nccl.AllGather) return fail(DFL_ERR_UNSUPPORTED, "expert-parallel combine: this NCCL has no ncclAllGather");
+    if (world > EP_MAX_WORLD) return fail(DFL_ERR_UNSUPPORTED, "expert-parallel combine: at most 8 ranks");
+    cudaIpcMemHandle_t mine;
+    DFL_CUDA(cudaIpcGetMemHandle(&mine, local));
+    uint8_t* dev_all = nullptr;
+    DFL_CUDA(cudaMalloc(&dev_all, (size_t)world * sizeof(mine)));
+    std::vector<cudaIpcMemHandle_t> all((size_t)world);
+    cudaError_t e = cudaMemcpyAsync(dev_all + (size_t)rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice, st);
+    int rc = 0;
+    if (e == cudaSuccess) rc = g_nccl.AllGather(dev_all + (size_t)rank * sizeof(mine), dev_all, sizeof(mine), /*ncclUint8*/ 1, comm, st);
+    if (e == cudaSuccess && rc == 0) e = cudaMemcpyAsync(all.data(), dev_all, (size_t)world * sizeof(mine), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && rc == 0) e = cudaStreamSynchronize(st);
+    cudaFree(dev_all);
+    if (rc != 0) return nccl_fail("ncclAllGather", rc);
+    DFL_CUDA(e);
+    for (int p = 0; p < world; ++p) {
+        if (p == rank) { peers_out[p] = local; continue; }
+        void* ptr = nullptr;
+        e = cudaIpcOpenMemHandle(&ptr, all[(size_t)p], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int q = 0; q < p; ++q)
+                if (q != rank) cudaIpcCloseMemHandle(peers_out[q]);
+            return fail(DFL_ERR_CUDA, std::string("expert-parallel combine: cannot map a peer's exchange buffer: ") + cudaGetErrorString(e));
+        }
+        peers_out[p] = ptr;
+    }
+    return DFL_OK;
+}
+void ep_p2p_close(int rank, int world, void* const* peers) {
+    for (int p = 0; p < world; ++p)
+        if (p != rank && peers[p]) cudaIpcCloseMemHandle(peers[p]);
+}
+// Every rank has reached this point: a one-element all-reduce, waited for under the watchdog loop with its own short
+// limit, so that a peer that has already gone does not hold the caller.  False when the peers did not answer.
+bool ep_barrier_bounded(void* comm, cudaStream_t st, uint32_t timeout_ms) {
+    if (!g_nccl.CommAbort || !g_nccl.CommGetAsyncError) return false;
+    float* one = nullptr;
+    cudaEvent_t ev = nullptr;
+    if (cudaMalloc(&one, 4) != cudaSuccess) return false;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) { cudaFree(one); return false; }
+    cudaMemsetAsync(one, 0, 4, st);
+    bool ok = g_nccl.AllReduce(one, one, 1, 7, 0, comm, st) == 0 && cudaEventRecord(ev, st) == cudaSuccess;
+    if (ok) {
+        EpWatchHooks h;
+        h.query = [ev]() -> int {
+            const cudaError_t e = cudaEventQuery(ev);
+            return e == cudaSuccess ? 0 : e == cudaErrorNotReady ? 1 : 2;
+        };
+        h.async_error = [comm]() -> int {
+            int e = 0;
+            const int rc = g_nccl.CommGetAsyncError(comm, &e);
+            return rc != 0 ? rc : e;
+        };
+        h.abort = [comm]() { g_nccl.CommAbort(comm); };
+        bool aborted = false;
+        ok = ep_watch_core(h, timeout_ms, 100, &aborted) == DFL_OK;
+    }
+    cudaEventDestroy(ev);
+    if (ok) cudaFree(one);   // after an abort the allocation is left to the end of the process
+    return ok;
+}
+
 uint32_t ep_watch_timeout_ms() {
     // DFL_EP_TIMEOUT_MS: how long a pass of an expert-parallel model may take before its communicator is aborted
     static const uint32_t ms = [] {
@@ -134,7 +201,7 @@ uint32_t ep_watch_timeout_ms() {
     return ms;
 }
 
-dfl_status ep_watch_stream(void* comm, cudaStream_t st, cudaEvent_t ev, bool* aborted) {
+dfl_status ep_watch_stream(void* comm, cudaStream_t st, cudaEvent_t ev, volatile int* abort_word, bool* aborted) {
     *aborted = false;
     if (!g_nccl.CommAbort || !g_nccl.CommGetAsyncError) {   // an NCCL without these entry points: plain blocking wait
         DFL_CUDA(cudaStreamSynchronize(st));
@@ -151,7 +218,10 @@ dfl_status ep_watch_stream(void* comm, cudaStream_t st, cudaEvent_t ev, bool* ab
         const int rc = g_nccl.CommGetAsyncError(comm, &e);
         return rc != 0 ? rc : e;
     };
-    h.abort = [comm]() { g_nccl.CommAbort(comm); };
+    h.abort = [comm, abort_word]() {
+        if (abort_word) *abort_word = 1;   // ends the waits of the peer-memory combine kernels
+        g_nccl.CommAbort(comm);
+    };
     return ep_watch_core(h, ep_watch_timeout_ms(), 20, aborted);
 }
 // in-place sum over the ranks, f32; every rank receives the same bits

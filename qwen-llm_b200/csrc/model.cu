@@ -150,7 +150,7 @@ static bool layer_is_attn(const dfl_arch& a, uint32_t il) {
 dfl_status session_drain(dfl_session* s) {
     if (s->m->ep_world > 1) {
         bool aborted = false;
-        dfl_status w = ep_watch_stream(s->m->ep_comm, s->st, s->ev_watch, &aborted);
+        dfl_status w = ep_watch_stream(s->m->ep_comm, s->st, s->ev_watch, s->m->ep_abort_host, &aborted);
         if (aborted) s->m->ep_dead.store(true);
         if (w != DFL_OK) { s->poisoned = true; return w; }
         return DFL_OK;
@@ -168,7 +168,10 @@ static dfl_status completion_check(dfl_session* s) {
     }
     DFL_CHECK(session_drain(s));
     dfl_status st = check_dev_err(s->st, s->err);
-    if (st != DFL_OK) s->poisoned = true;
+    if (st != DFL_OK) {
+        s->poisoned = true;
+        if (s->m->ep_world > 1) s->m->ep_dead.store(true);   // the ranks are no longer in step: no further pass on this model
+    }
     return st;
 }
 
@@ -338,8 +341,16 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
             DFL_CHECK(launch_group(st, L.moe_down, sc->acts_f, sc->part + (uint64_t)sh_splits * MAX_ROWS * H, ep_down_exps, s->err));
             if (Fs > 0) DFL_CHECK(join_side());
             down_splits = sh_splits + (down_splits_dev ? 0 : L.moe_down.splits);
-            if (m->ep_world > 1) {
-                // sum this rank's slices, then over the ranks: every rank continues with the same [16][H] block output
+            if (m->ep_world > 1 && m->ep_p2p) {
+                // this rank's slices summed and pushed into every rank's receive buffer; the glue below adds the ranks'
+                // slots in rank order, so every rank continues with the same [16][H] block output
+                const uint32_t seq = ++m->ep_seq;
+                DFL_CHECK(launch_ep_push_sum(st, sc->part, down_splits, down_splits_dev, H, m->ep_peers, m->ep_rank, m->ep_world, seq, m->ep_abort_dev, s->err));
+                down_splits_dev = nullptr;
+                moe_part = m->ep_peers.base[m->ep_rank] + (uint64_t)(seq & 1u) * m->ep_world * MAX_ROWS * H;
+                down_splits = m->ep_world;
+            } else if (m->ep_world > 1) {
+                // the same through the library: local sum, then an all-reduce over the ranks
                 DFL_CHECK(launch_reduce_partials(st, sc->part, down_splits, MAX_ROWS, H, sc->moe_out, (int)H, down_splits_dev));
                 down_splits_dev = nullptr;
                 DFL_CHECK(ep_all_reduce_sum(m->ep_comm, sc->moe_out, (size_t)MAX_ROWS * H, st));
@@ -567,6 +578,30 @@ static dfl_status model_create_impl(int32_t device, const dfl_arch* arch, const 
     if (ep_world > 1) {
         s = ep_comm_create(ep_rank, ep_world, nccl_id, &m->ep_comm);
         if (s != DFL_OK) goto failed;
+        // DFL_EP_COMBINE=nccl keeps the block-output sum on ncclAllReduce (for comparison); the default is the
+        // peer-memory combine of ep_combine.cu
+        const char* e = getenv("DFL_EP_COMBINE");
+        if (!(e && e[0] == 'n') && ep_world <= EP_MAX_WORLD) {
+            const uint64_t recv_bytes = ep_recv_floats(ep_world, H) * 4;
+            const uint64_t flag_bytes = 2ull * ep_world * ep_combine_ctas(H) * 4;
+            void* local = nullptr;
+            if (cudaMalloc(&local, recv_bytes + flag_bytes) != cudaSuccess) { s = fail(DFL_ERR_OOM, "model_create: exchange buffer"); goto failed; }
+            cudaMemset(local, 0, recv_bytes + flag_bytes);
+            cudaDeviceSynchronize();
+            void* peers[EP_MAX_WORLD] = {};
+            s = ep_p2p_exchange(m->ep_comm, ep_rank, ep_world, local, st, peers);
+            if (s != DFL_OK) { cudaFree(local); goto failed; }
+            for (int p = 0; p < ep_world; ++p) m->ep_peers.base[p] = (float*)peers[p];
+            m->ep_peers.flags_off = recv_bytes;
+            if (cudaHostAlloc((void**)&m->ep_abort_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+                cudaHostGetDevicePointer((void**)&m->ep_abort_dev, m->ep_abort_host, 0) != cudaSuccess) {
+                s = fail(DFL_ERR_OOM, "model_create: abort word");
+                m->ep_p2p = true;   // so that the destructor unmaps what was mapped
+                goto failed;
+            }
+            *m->ep_abort_host = 0;
+            m->ep_p2p = true;
+        }
     }
     *out = m;
     return DFL_OK;
@@ -600,6 +635,19 @@ void dfl_model_destroy(dfl_model* m) {
             if (p) cudaFree(p);
     }
     m->lm_head.release();
+    if (m->ep_p2p) {
+        // Peers unmap first; a rank frees its buffer only once every rank has unmapped it, which a bounded barrier
+        // establishes.  When the peers do not answer within two seconds (they have gone, or never destroy their
+        // model) the communicator is aborted and the buffer stays allocated until the process ends.
+        void* peers[EP_MAX_WORLD];
+        for (int p = 0; p < EP_MAX_WORLD; ++p) peers[p] = m->ep_peers.base[p];
+        ep_p2p_close(m->ep_rank, m->ep_world, peers);
+        if (!m->ep_dead.load() && m->ep_comm) {
+            if (ep_barrier_bounded(m->ep_comm, 0, 2000)) cudaFree(m->ep_peers.base[m->ep_rank]);
+            else m->ep_dead.store(true);
+        }
+        if (m->ep_abort_host) cudaFreeHost(m->ep_abort_host);
+    }
     ep_comm_destroy(m->ep_comm, m->ep_dead.load());
     if (m->embd_ggml) cudaFree(m->embd_ggml);
     if (m->out_norm_w) cudaFree(m->out_norm_w);

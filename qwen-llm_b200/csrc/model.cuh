@@ -76,6 +76,20 @@ dfl_status ep_unique_id(uint8_t* id_out);
 dfl_status ep_comm_create(int rank, int world, const uint8_t* id_bytes, void** comm_out);
 void ep_comm_destroy(void* comm, bool aborted);
 dfl_status ep_all_reduce_sum(void* comm, float* buf, size_t count, cudaStream_t st);
+// peer-memory combine (ep_combine.cu): every rank's exchange buffer - receive slots [2 parities][world][16][H] f32,
+// then flags [2][world][ctas] u32 at flags_off - mapped into this process
+constexpr int EP_MAX_WORLD = 8;
+struct EpPeers {
+    float* base[EP_MAX_WORLD];
+    uint64_t flags_off;
+};
+inline int ep_combine_ctas(uint64_t n_out) { return (int)((MAX_ROWS * n_out / 4 + 255) / 256); }
+inline uint64_t ep_recv_floats(int world, uint64_t n_out) { return 2ull * (uint64_t)world * MAX_ROWS * n_out; }
+dfl_status ep_p2p_exchange(void* comm, int rank, int world, void* local, cudaStream_t st, void** peers_out);
+void ep_p2p_close(int rank, int world, void* const* peers);
+bool ep_barrier_bounded(void* comm, cudaStream_t st, uint32_t timeout_ms);
+dfl_status launch_ep_push_sum(cudaStream_t st, const float* part, int splits, const int32_t* splits_dev, uint64_t n_out, const EpPeers& peers,
+                              int rank, int world, uint32_t seq, const int* abort_host_dev, int* err);
 // host watchdog over a pass that contains collectives (ep_nccl.cpp)
 struct EpWatchHooks {
     std::function<int()> query;
@@ -83,7 +97,7 @@ struct EpWatchHooks {
     std::function<void()> abort;
 };
 dfl_status ep_watch_core(const EpWatchHooks& h, uint32_t timeout_ms, uint32_t poll_us, bool* aborted);
-dfl_status ep_watch_stream(void* comm, cudaStream_t st, cudaEvent_t ev, bool* aborted);
+dfl_status ep_watch_stream(void* comm, cudaStream_t st, cudaEvent_t ev, volatile int* abort_word, bool* aborted);
 dfl_status session_drain(dfl_session* s);
 }  // namespace dfl
 
@@ -95,6 +109,13 @@ struct dfl_model {
     uint32_t ep_e0 = 0, ep_n = 0, ep_fs = 0;
     void* ep_comm = nullptr;
     mutable std::atomic<bool> ep_dead{false};   // the watchdog aborted the communicator: every later pass is refused
+    // peer-memory combine: the exchange buffers of all ranks (own one at [ep_rank]), the combine counter every rank
+    // advances alike, and the host-mapped word the watchdog raises to end waiting kernels
+    bool ep_p2p = false;
+    dfl::EpPeers ep_peers{};
+    mutable uint32_t ep_seq = 0;
+    int* ep_abort_host = nullptr;
+    int* ep_abort_dev = nullptr;
     int act_layout = dfl::ACT_F16;  // packed-activation format all its GEMMs consume (follows the kernel family)
     dfl_arch arch{};
     std::vector<dfl::LayerW> layers;
