@@ -127,7 +127,7 @@ dfl_status ep_watch_core(const EpWatchHooks& h, uint32_t timeout_ms, uint32_t po
 }
 
 // Exchanges the inter-process handles of every rank's exchange buffer over the communicator and maps the peers' buffers
-// into this process (plain peer access over NVLink; no multicast object is involved).
+// into this process (plain peer loads and stores over NVLink).
 dfl_status ep_p2p_exchange(void* comm, int rank, int world, void* local, cudaStream_t st, void** peers_out) {
     if (!g_nccl.AllGather) return fail(DFL_ERR_UNSUPPORTED, "expert-parallel combine: this NCCL has no ncclAllGather");
     if (world > EP_MAX_WORLD) return fail(DFL_ERR_UNSUPPORTED, "expert-parallel combine: at most 8 ranks");
