@@ -729,11 +729,11 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, boo
     const MatGroup& lm = tgt->lm_head;
     if (lm.splits == 1) {
         DFL_CHECK(launch_group(st, lm, ds->acts_lm, ds->logits, ep_norm, ds->err));
+        DFL_CHECK(launch_argmax_top2(st, ds->logits, n, V, V, ds->argmax, ds->gap, ds->am_scratch));
     } else {
         DFL_CHECK(launch_group(st, lm, ds->acts_lm, ds->part, ep_norm, ds->err));
-        DFL_CHECK(launch_reduce_partials(st, ds->part, lm.splits, n, V, ds->logits, (int)V));
+        DFL_CHECK(launch_reduce_argmax_top2(st, ds->part, lm.splits, n, V, ds->logits, V, ds->argmax, ds->gap, ds->am_scratch));
     }
-    DFL_CHECK(launch_argmax_top2(st, ds->logits, n, V, V, ds->argmax, ds->gap, ds->am_scratch));
     ds->have_topk = false;
     if (topk || d->has_selector) {
         DFL_CHECK(launch_topk16(st, ds->logits, n, V, V, ds->topk_ids, ds->topk_vals, ds->topk_scratch));

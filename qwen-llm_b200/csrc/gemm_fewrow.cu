@@ -873,6 +873,33 @@ __global__ void argmax_part_kernel(const float* logits, uint64_t vocab, uint64_t
     a = top2_block_reduce(a);
     if (threadIdx.x == 0) parts[row * ARGMAX_PARTS + part] = a;
 }
+// The same over split-K partial sums: each element is first reduced over the slices (slice order, as
+// reduce_partials_kernel does) and written to `logits`, so the head's logits are produced and ranked in one pass.
+__global__ void argmax_part_reduce_kernel(const float* part, int splits, uint64_t vocab, float* logits, uint64_t ld, Top2* parts) {
+    pdl_prologue();
+    const int row = blockIdx.y, pt = blockIdx.x;
+    const uint64_t per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+    const uint64_t lo = pt * per, hi = lo + per < vocab ? lo + per : vocab;
+    Top2 a{INT32_MIN, INT32_MAX, INT32_MIN, 0};
+    const uint64_t slice = (uint64_t)MAX_ROWS * vocab;
+    for (uint64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float* src = part + (uint64_t)row * vocab + i;
+        float v = 0.f;
+        for (int s0 = 0; s0 < splits; s0 += 4) {   // four slices in flight per round trip, added in slice order
+            float t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) t[u] = __ldcg(src + (uint64_t)(s0 + u < splits ? s0 + u : splits - 1) * slice);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (s0 + u < splits) v += t[u];
+        }
+        logits[row * ld + i] = v;
+        const int32_t key = (v != v) ? INT32_MAX : total_order_key(v);
+        top2_push(a, key, (int32_t)i);
+    }
+    a = top2_block_reduce(a);
+    if (threadIdx.x == 0) parts[row * ARGMAX_PARTS + pt] = a;
+}
 __global__ void argmax_final_kernel(const Top2* parts, int32_t* argmax, float* gap) {
     pdl_prologue();
     const int row = blockIdx.x;
@@ -893,6 +920,16 @@ dfl_status launch_argmax_top2(cudaStream_t st, const float* logits, int n_rows, 
                               float* gap, void* scratch) {
     if (n_rows < 1 || vocab == 0) return fail(DFL_ERR_BAD_SHAPE, "argmax: shape");
     launch_k(argmax_part_kernel, dim3(dim3(ARGMAX_PARTS, n_rows)), dim3(256), 0, st, logits, vocab, ld, reinterpret_cast<Top2*>(scratch));
+    launch_k(argmax_final_kernel, dim3(n_rows), dim3(64), 0, st, reinterpret_cast<const Top2*>(scratch), argmax, gap);
+    count_launch(2);
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+dfl_status launch_reduce_argmax_top2(cudaStream_t st, const float* part, int splits, int n_rows, uint64_t vocab, float* logits, uint64_t ld,
+                                     int32_t* argmax, float* gap, void* scratch) {
+    if (n_rows < 1 || vocab == 0 || splits < 1) return fail(DFL_ERR_BAD_SHAPE, "argmax: shape");
+    launch_k(argmax_part_reduce_kernel, dim3(dim3(ARGMAX_PARTS, n_rows)), dim3(256), 0, st, part, splits, vocab, logits, ld, reinterpret_cast<Top2*>(scratch));
     launch_k(argmax_final_kernel, dim3(n_rows), dim3(64), 0, st, reinterpret_cast<const Top2*>(scratch), argmax, gap);
     count_launch(2);
     DFL_CUDA(cudaGetLastError());

@@ -401,11 +401,11 @@ dfl_status verify_core(const dfl_model* m, dfl_session* s, dfl_scratch* sc, cons
         float* logits = sc->logits;
         if (lm.splits == 1) {
             DFL_CHECK(launch_group(st, lm, sc->acts_h, logits, ep_norm, s->err));
+            DFL_CHECK(launch_argmax_top2(st, logits, (int)n, V, V, sc->argmax, sc->gap, sc->am_scratch));
         } else {
             DFL_CHECK(launch_group(st, lm, sc->acts_h, sc->part, ep_norm, s->err));
-            DFL_CHECK(launch_reduce_partials(st, sc->part, lm.splits, (int)n, V, logits, (int)V));
+            DFL_CHECK(launch_reduce_argmax_top2(st, sc->part, lm.splits, (int)n, V, logits, V, sc->argmax, sc->gap, sc->am_scratch));
         }
-        DFL_CHECK(launch_argmax_top2(st, logits, (int)n, V, V, sc->argmax, sc->gap, sc->am_scratch));
     }
     DFL_CHECK(join_side());   // whatever the side streams still hold belongs to this pass
     DFL_CHECK(join_side2());

@@ -233,6 +233,9 @@ dfl_status launch_reduce_partials(cudaStream_t st, const float* part, int splits
 // Row argmax (lowest index on ties, total order) + gap to the runner-up.
 dfl_status launch_argmax_top2(cudaStream_t st, const float* logits, int n_rows, uint64_t vocab, uint64_t ld,
                               int32_t* argmax, float* gap, void* scratch /* >= n_rows*ARGMAX_PARTS*16 B */);
+// the head's split-K partial sums reduced into `logits` and ranked in the same pass
+dfl_status launch_reduce_argmax_top2(cudaStream_t st, const float* part, int splits, int n_rows, uint64_t vocab, float* logits, uint64_t ld,
+                                     int32_t* argmax, float* gap, void* scratch);
 constexpr int ARGMAX_PARTS = 64;
 
 }  // namespace dfl
