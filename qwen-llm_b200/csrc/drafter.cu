@@ -139,14 +139,28 @@ __global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float*
             M = fmaxf(M, partials[(((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2)]);
         M = warp_max(M);
         float L = 0.f;
-        for (int c = 0; c < n_chunks; ++c) {
-            const float* rec = partials + (((uint64_t)c * g.n_kv + kvh) * (MAX_ROWS * group) + qi) * (HD + 2);
-            const float m = rec[0];
-            if (m == -INFINITY) continue;
-            const float f = expf(m - M);
-            L = fmaf(rec[1], f, L);
+        // records merged in index order, their loads issued eight records at a time
+        constexpr int BATCH = 8;
+        const uint64_t rec_stride = (uint64_t)g.n_kv * (MAX_ROWS * group) * (HD + 2);
+        const float* rec0 = partials + ((uint64_t)kvh * (MAX_ROWS * group) + qi) * (HD + 2);
+        for (int c0 = 0; c0 < n_chunks; c0 += BATCH) {
+            float mb[BATCH], lb[BATCH], vb[BATCH][PER];
 #pragma unroll
-            for (int j = 0; j < PER; ++j) v[j] = fmaf(rec[2 + lane * PER + j], f, v[j]);
+            for (int u = 0; u < BATCH; ++u) {
+                const float* rec = rec0 + (uint64_t)(c0 + u < n_chunks ? c0 + u : n_chunks - 1) * rec_stride;
+                mb[u] = rec[0];
+                lb[u] = rec[1];
+#pragma unroll
+                for (int j = 0; j < PER; ++j) vb[u][j] = rec[2 + lane * PER + j];
+            }
+#pragma unroll
+            for (int u = 0; u < BATCH; ++u) {
+                if (c0 + u >= n_chunks || mb[u] == -INFINITY) continue;
+                const float f = expf(mb[u] - M);
+                L = fmaf(lb[u], f, L);
+#pragma unroll
+                for (int j = 0; j < PER; ++j) v[j] = fmaf(vb[u][j], f, v[j]);
+            }
         }
         const float inv = 1.0f / L;
 #pragma unroll
