@@ -333,6 +333,361 @@ attn_t5_kernel(AttnGeom g, const float* q_rot, const __half* k_cache, const __ha
     }
 }
 
+// ---- the drafter's attention on the same scheme ---------------------------------------------------------------------
+// Queries = the block's noise rows; keys = the context columns followed by the noise rows' own K / V;
+// allowed(q, k) = !causal || k_pos <= q_pos (kernels/dflash_attn.metal:99-103; sliding-window layers keep the mma.sync
+// kernel, their span is short).  The drafter's context cache holds f32 rows; layers that attend over the whole context
+// of a long session keep a shadow of it as tiles - per (128 columns, KV head) four 32 KiB tiles: K hi, K lo, V hi, V lo,
+// the exact f16 hi + lo split of the f32 values in the operand layouts of attn_t5_kernel - written when columns are
+// appended (dctx_tile_kernel).  The noise rows are one more tile set, rebuilt per pass.  Per tile of 128 keys:
+//   S = Qh Kh + Ql Kh + Qh Kl   (24 MMAs),   O += P Vh + P Vl   (16 MMAs),   P rounded to f16 as in the verify kernel,
+// so the result keeps f32-class accuracy against the f32 cache, like the mma.sync kernel it replaces.  The key
+// positions of a context tile are staged beside it (512 bytes) for the causal mask.  Six ring slots hold the four
+// tiles of a step plus half of the next.
+constexpr int D5_OFF_POS = T5_OFF_BAR + 256;           // [2][128] u32 key positions
+constexpr int D5_SMEM = D5_OFF_POS + 2 * 128 * 4;
+static_assert(D5_SMEM <= 227 * 1024, "shared memory budget");
+
+__global__ void __launch_bounds__(T5_THREADS, 1)
+dattn_t5_kernel(AttnGeom g, const float* q_rot, const __half* ctx_tiles, const __half* noise_tiles, const uint32_t* pos_ctx, int n_ctx,
+                uint32_t noise_start, int n_rows, int causal, float* partials, int chunks_per_span, float rescale_above, int* err) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem;
+    float* q_stage = reinterpret_cast<float*>(smem + T5_OFF_QSTAGE);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + T5_OFF_BAR);
+    uint64_t* empty = full + T5_SLOTS;
+    uint64_t* s_ready = empty + T5_SLOTS;
+    uint64_t* p_ready = s_ready + 2;
+    uint64_t* pv_done = p_ready + 2;
+    uint32_t* kpos = reinterpret_cast<uint32_t*>(smem + D5_OFF_POS);
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+    const int span = blockIdx.x, kvh = blockIdx.y;
+    const int n_ctx_chunks = (n_ctx + KV_TILE_KEYS - 1) / KV_TILE_KEYS;   // the noise rows are chunk n_ctx_chunks
+    const int c_begin = span * chunks_per_span;
+    int c_end = n_ctx_chunks + 1;
+    if (c_end > c_begin + chunks_per_span) c_end = c_begin + chunks_per_span;
+    const int n_c = c_end - c_begin;   // >= 1 by the launch geometry
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < T5_SLOTS; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_ready[i], 1);
+            mbar_init(&p_ready[i], 4);
+            mbar_init(&pv_done[i], 1);
+        }
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 4) tmem_alloc(&tmem_slot, T5_TM_COLS);
+    pdl_launch_dependents();
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp < 4) {
+        const int L = 32 * warp + lane, q = L & 63, half = L >> 6, tok = q >> 2;
+        const uint32_t tm_lane = tmem + ((uint32_t)(32 * warp) << 16);
+        pdl_wait();
+        {
+            for (int idx = L; idx < T5_Q * (T5_HD / 4); idx += 128) {
+                const int pair = idx / (T5_HD / 4), d4 = (idx % (T5_HD / 4)) * 4;
+                const int row = pair / T5_GROUP;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (row < n_rows) v = *reinterpret_cast<const float4*>(q_rot + ((uint64_t)row * g.n_q + kvh * T5_GROUP + pair % T5_GROUP) * T5_HD + d4);
+                float* dst = q_stage + pair * T5_QPITCH + d4;
+                dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const float scale = 1.4426950408889634f / sqrtf((float)T5_HD);
+            const float* src = q_stage + q * T5_QPITCH;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t hi[32], lo[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) split_pair_f(src[64 * c + 2 * j] * scale, src[64 * c + 2 * j + 1] * scale, hi[j], lo[j]);
+                tmem_st32(tm_lane + T5_TM_Q + 32 * c, hi);
+                tmem_st32(tm_lane + T5_TM_Q + 64 + 32 * c, lo);
+            }
+            wait_st();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[1]);   // phase 0 of p_ready[1]: the query operand is written
+        }
+        const uint32_t q_pos = noise_start + (uint32_t)tok;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_c && ok; ++i) {
+            const int b = i & 1, chunk = c_begin + i;
+            if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&abort_flag) != 0)) { ok = false; break; }
+            ok = mbar_wait_spin(&s_ready[b], (uint32_t)(i >> 1) & 1u, err, DEV_ERR_WAIT_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            float s[64];
+            {
+                float t0[32], t1[32];
+                tmem_ld32(tm_lane + T5_TM_S + 128 * b + 64 * half, t0);
+                tmem_ld32(tm_lane + T5_TM_S + 128 * b + 64 * half + 32, t1);
+                wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { s[j] = t0[j]; s[32 + j] = t1[j]; }
+            }
+            const bool noise = chunk == n_ctx_chunks;
+            const int k0 = 64 * half;   // this lane's first key inside the tile
+            if (tok >= n_rows) {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) s[j] = -INFINITY;
+            } else if (noise) {
+                // keys = the block's own rows: row j is visible when it exists and (bidirectional, or not after the query)
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    const int kj = k0 + j;
+                    if (kj >= n_rows || (causal && kj > tok)) s[j] = -INFINITY;
+                }
+            } else if (causal || (chunk + 1) * KV_TILE_KEYS > n_ctx) {
+                // positions were staged with the tile's first plane: observe that copy's barrier before reading them (the
+                // phase completed long ago; the slot's next use cannot complete before this step's P is written)
+                if (causal) {
+                    const int u0 = 4 * i;
+                    ok = mbar_wait_spin(&full[u0 % T5_SLOTS], (uint32_t)(u0 / T5_SLOTS) & 1u, err, DEV_ERR_WAIT_FULL);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+                const uint32_t* kp = kpos + 128 * b + k0;
+                const int lim = n_ctx - chunk * KV_TILE_KEYS - k0;   // columns of this half that exist
+#pragma unroll
+                for (int j = 0; j < 64; ++j)
+                    if (j >= lim || (causal && kp[j] > q_pos)) s[j] = -INFINITY;
+            }
+            float mx[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mx[j] = s[j];
+#pragma unroll
+            for (int j = 8; j < 64; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
+            const float mc = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+            const bool need = mc > m_ref + rescale_above;
+            if (__any_sync(0xffffffffu, need)) {
+                const float alpha = need ? ex2f(m_ref - mc) : 1.0f;
+                if (i >= 1) {
+                    ok = mbar_wait_spin(&pv_done[(i - 1) & 1], (uint32_t)((i - 1) >> 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float o[32];
+                        tmem_ld32(tm_lane + T5_TM_O + 32 * c, o);
+                        wait_ld();
+                        uint32_t r[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(o[j] * alpha);
+                        tmem_st32(tm_lane + T5_TM_O + 32 * c, r);
+                    }
+                }
+                l *= alpha;
+                if (need) m_ref = mc;
+            }
+            const float ms = m_ref > -INFINITY ? m_ref : 0.f;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pr[32], zero[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float e0 = ex2f(s[2 * j] - ms), e1 = ex2f(s[2 * j + 1] - ms);
+                sum[j & 3] += e0 + e1;
+                pr[j] = pack_h2f(e0, e1);
+                zero[j] = 0u;
+            }
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            tmem_st32(tm_lane + T5_TM_S + 128 * b + 32 * half, pr);
+            tmem_st32(tm_lane + T5_TM_S + 128 * b + 32 * (half ^ 1), zero);
+            wait_st();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[b]);
+        }
+        if (ok) {
+            ok = mbar_wait_spin(&pv_done[(n_c - 1) & 1], (uint32_t)((n_c - 1) >> 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (!ok) abort_flag = 1;
+        fence_after_sync();
+        float* stage = reinterpret_cast<float*>(ring) + (uint64_t)L * (T5_HD + 2);
+        stage[0] = ok ? m_ref * 0.6931471805599453f : -INFINITY;
+        stage[1] = ok ? l : 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float o[32];
+            tmem_ld32(tm_lane + T5_TM_O + 32 * c, o);
+            wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) *reinterpret_cast<float2*>(stage + 2 + 32 * c + j) = make_float2(o[j], o[j + 1]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        constexpr int REC2 = T5_Q * (T5_HD + 2) / 2;
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            float2* dst = reinterpret_cast<float2*>(partials + ((uint64_t)(2 * span + hh) * g.n_kv + kvh) * T5_Q * (T5_HD + 2));
+            const float2* src2 = reinterpret_cast<const float2*>(ring) + hh * REC2;
+            for (int idx = L; idx < REC2; idx += 128) dst[idx] = src2[idx];
+        }
+    } else if (warp == 4) {
+        constexpr uint32_t IDESC = instr_desc(128);
+        const uint32_t ring_addr = smem_u32(ring);
+        bool ok = mbar_wait_spin(&p_ready[1], 0u, err, DEV_ERR_WAIT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        // tile u of this CTA (four per step: K hi, K lo, V hi, V lo) lives in ring slot u % 6, use u / 6
+        auto wait_tile = [&](int u) { return mbar_wait_spin(&full[u % T5_SLOTS], (uint32_t)(u / T5_SLOTS) & 1u, err, DEV_ERR_WAIT_FULL); };
+        auto issue_qk = [&](int i) {
+            const int b = i & 1, u = 4 * i;
+            ok = wait_tile(u) && wait_tile(u + 1);
+            if (ok && i >= 2) ok = mbar_wait_spin(&pv_done[b], (uint32_t)((i >> 1) - 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            fence_after_sync();
+            if (elect_one()) {
+                const uint32_t kh = ring_addr + (uint32_t)(u % T5_SLOTS) * T5_TILE, kl = ring_addr + (uint32_t)((u + 1) % T5_SLOTS) * T5_TILE;
+#pragma unroll
+                for (int j = 0; j < 24; ++j) {   // Qh Kh, Ql Kh, Qh Kl: eight k steps of 16 dims each
+                    const uint32_t a_col = j < 8 ? 8u * j : j < 16 ? 64u + 8u * (j - 8) : 8u * (j - 16);
+                    const uint32_t k_addr = (j < 16 ? kh : kl) + (uint32_t)(j & 7) * 4096u;
+                    mma_ts_rt(tmem + T5_TM_S + 128u * (uint32_t)b, tmem + T5_TM_Q + a_col, smem_desc(k_addr, 2048, 128), IDESC, j > 0 ? 1u : 0u);
+                }
+                mma_commit(&s_ready[b]);
+                mma_commit(&empty[u % T5_SLOTS]);
+                mma_commit(&empty[(u + 1) % T5_SLOTS]);
+            }
+            __syncwarp();
+        };
+        if (ok) issue_qk(0);
+        for (int i = 0; i < n_c && ok; ++i) {
+            if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&abort_flag) != 0)) { ok = false; break; }
+            if (i + 1 < n_c) {
+                issue_qk(i + 1);
+                if (!ok) break;
+            }
+            const int b = i & 1, u = 4 * i + 2;
+            const uint32_t p_phase = b == 1 ? (uint32_t)((i >> 1) + 1) & 1u : (uint32_t)(i >> 1) & 1u;
+            ok = mbar_wait_spin(&p_ready[b], p_phase, err, DEV_ERR_WAIT_FULL);
+            if (ok) ok = wait_tile(u) && wait_tile(u + 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after_sync();
+            if (elect_one()) {
+                const uint32_t vh = ring_addr + (uint32_t)(u % T5_SLOTS) * T5_TILE, vl = ring_addr + (uint32_t)((u + 1) % T5_SLOTS) * T5_TILE;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)   // P Vh, then P Vl: 16 keys per step
+                    mma_ts_rt(tmem + T5_TM_O, tmem + T5_TM_S + 128u * (uint32_t)b + 8u * (uint32_t)(j & 7),
+                              smem_desc((j < 8 ? vh : vl) + (uint32_t)(j & 7) * 4096u, 2048, 128), IDESC, (i > 0 || j > 0) ? 1u : 0u);
+                mma_commit(&empty[u % T5_SLOTS]);
+                mma_commit(&empty[(u + 1) % T5_SLOTS]);
+                mma_commit(&pv_done[b]);
+            }
+            __syncwarp();
+        }
+        if (!ok) abort_flag = 1;
+    } else {
+        if (lane == 0) {
+            pdl_wait();
+            bool ok = true;
+            int issued = 0;
+            const int n_t = 4 * n_c;
+            for (int t = 0; t < n_t && ok; ++t) {
+                const int slot = t % T5_SLOTS, i = t >> 2, plane = t & 3, chunk = c_begin + i;
+                if (*reinterpret_cast<volatile int*>(&abort_flag)) break;
+                if (t >= T5_SLOTS) ok = mbar_wait_bounded(&empty[slot], (uint32_t)(t / T5_SLOTS - 1) & 1u, err, DEV_ERR_WAIT_EMPTY);
+                if (!ok) break;
+                const bool noise = chunk == n_ctx_chunks;
+                const __half* src = noise ? noise_tiles + ((uint64_t)kvh * 4 + plane) * (uint64_t)(KV_TILE_KEYS * T5_HD)
+                                          : ctx_tiles + (((uint64_t)chunk * g.n_kv + kvh) * 4 + plane) * (uint64_t)(KV_TILE_KEYS * T5_HD);
+                // the key positions of a context tile ride on the barrier of its first plane (the buffer of step i - 2 was
+                // last read by that step's softmax, which completed before the slot's previous tile was released)
+                const bool with_pos = plane == 0 && !noise;
+                mbar_arrive_expect_tx(&full[slot], T5_TILE + (with_pos ? 512u : 0u));
+                bulk_g2s(ring + slot * T5_TILE, src, T5_TILE, &full[slot]);
+                if (with_pos) bulk_g2s(kpos + 128 * (i & 1), pos_ctx + (uint64_t)chunk * KV_TILE_KEYS, 512, &full[slot]);
+                issued = t + 1;
+            }
+            if (!ok) abort_flag = 1;
+            for (int t = issued > T5_SLOTS ? issued - T5_SLOTS : 0; t < issued; ++t)
+                mbar_wait_bounded(&full[t % T5_SLOTS], (uint32_t)(t / T5_SLOTS) & 1u, err, DEV_ERR_WAIT_DRAIN);
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        fence_after_sync();
+        tmem_free(tmem, T5_TM_COLS);
+    }
+}
+
+// f32 K / V rows [first, first + count) of a position-major cache -> their f16 hi + lo tiles (row index = key index)
+__global__ void dctx_tile_kernel(const float* k_rows, const float* v_rows, int n_kv, uint32_t first, uint32_t count, uint32_t row0, __half* tiles) {
+    pdl_prologue();
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one element of one row
+    const uint64_t per_row = (uint64_t)n_kv * T5_HD;
+    if (i >= (uint64_t)count * per_row) return;
+    const uint32_t r = (uint32_t)(i / per_row);
+    const int h = (int)((i % per_row) / T5_HD), d = (int)(i % T5_HD);
+    const uint32_t key_index = first + r;                                   // position of the row in the tiled sequence
+    const uint64_t src = ((uint64_t)(row0 + r) * n_kv + h) * T5_HD + d;
+    __half* base = tiles + (((uint64_t)(key_index / KV_TILE_KEYS) * n_kv + h) * 4) * (uint64_t)(KV_TILE_KEYS * T5_HD);
+    const uint32_t key = key_index % KV_TILE_KEYS;
+    const float kf = k_rows[src], vf = v_rows[src];
+    const __half khi = __float2half_rn(kf), vhi = __float2half_rn(vf);
+    const uint32_t ko = kv_tile_k_off(key, d), vo = kv_tile_v_off(key, d);
+    constexpr uint64_t PLANE = (uint64_t)KV_TILE_KEYS * T5_HD;
+    base[ko] = khi;
+    base[PLANE + ko] = __float2half_rn(kf - __half2float(khi));
+    base[2 * PLANE + vo] = vhi;
+    base[3 * PLANE + vo] = __float2half_rn(vf - __half2float(vhi));
+}
+
+uint64_t dattn_t5_tile_halfs(int n_kv, uint32_t n_keys) { return ((uint64_t)(n_keys + KV_TILE_KEYS - 1) / KV_TILE_KEYS) * n_kv * 4 * (uint64_t)(KV_TILE_KEYS * T5_HD); }
+
+// rows [row0, row0 + count) of the f32 caches become keys [first, first + count) of the tiled sequence
+dfl_status launch_dctx_tiles(cudaStream_t st, const float* k_rows, const float* v_rows, int n_kv, uint32_t first, uint32_t count, uint32_t row0,
+                             void* tiles) {
+    if (count == 0) return DFL_OK;
+    const uint64_t n = (uint64_t)count * n_kv * T5_HD;
+    launch_k(dctx_tile_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, k_rows, v_rows, n_kv, first, count, row0, reinterpret_cast<__half*>(tiles));
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
+dfl_status launch_dattn_t5(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* ctx_tiles, const void* noise_tiles,
+                           const uint32_t* pos_ctx, int n_ctx, uint32_t noise_start, int n_rows, bool causal, float* partials, uint32_t ctx_capacity,
+                           int* err, int* n_records_out) {
+    static std::once_flag once[16];
+    int dev = 0;
+    DFL_CUDA(cudaGetDevice(&dev));
+    cudaError_t attr = cudaSuccess;
+    std::call_once(once[dev & 15], [&] { attr = cudaFuncSetAttribute(dattn_t5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, D5_SMEM); });
+    DFL_CUDA(attr);
+    const int cps = attn_t5_chunks_per_span(g, ctx_capacity + KV_TILE_KEYS);
+    const int n_chunks = (n_ctx + KV_TILE_KEYS - 1) / KV_TILE_KEYS + 1;
+    const int n_spans = (n_chunks + cps - 1) / cps;
+    float rescale_above = T5_RESCALE;
+    if (const char* e = getenv("DFL_ATTN_T5_RESCALE")) {
+        const float v = (float)atof(e);
+        if (v >= 0.f && v <= 12.f) rescale_above = v;
+    }
+    launch_k(dattn_t5_kernel, dim3((unsigned)n_spans, (unsigned)g.n_kv), dim3(T5_THREADS), (size_t)D5_SMEM, st, g, q_rot,
+              reinterpret_cast<const __half*>(ctx_tiles), reinterpret_cast<const __half*>(noise_tiles), pos_ctx, n_ctx, noise_start, n_rows,
+              causal ? 1 : 0, partials, cps, rescale_above, err);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    *n_records_out = 2 * n_spans;
+    return DFL_OK;
+}
+
 bool attn_t5_supported(const AttnGeom& g, bool kv_f16) { return kv_f16 && g.hd == T5_HD && g.n_q / g.n_kv == T5_GROUP; }
 
 // tiles per span from the session's KV capacity only (never from the call): one CTA per SM and one wave at full

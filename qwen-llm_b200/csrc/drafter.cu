@@ -187,6 +187,14 @@ __global__ void __launch_bounds__(32) dattn_post_kernel(AttnGeom g, const float*
     if (over) atomicCAS(err, 0, DEV_ERR_OVERFLOW);
 }
 
+// merge of `n_records` records per query + packing (128-wide heads)
+dfl_status launch_dattn_post(cudaStream_t st, const AttnGeom& g, const float* partials, int n_records, int n_rows, uint8_t* acts, int bf3, int* err) {
+    launch_k(dattn_post_kernel<128>, dim3(dim3((unsigned)g.n_q, MAX_ROWS)), dim3(32), 0, st, g, partials, n_records, n_rows, acts, bf3, err);
+    count_launch();
+    DFL_CUDA(cudaGetLastError());
+    return DFL_OK;
+}
+
 dfl_status launch_drafter_attn(cudaStream_t st, const AttnGeom& g, const float* q_rot, const float* k_ctx, const float* v_ctx,
                                const int32_t* pos_ctx, int ctx_begin, int ctx_len, const float* k_noise, const float* v_noise,
                                uint32_t noise_start, int n_rows, bool causal, uint32_t window, float* partials, uint8_t* acts, int bf3,
@@ -260,6 +268,10 @@ struct dfl_dsession {
     uint32_t* pos_ctx_dev = nullptr;    // [capacity]
     std::vector<uint32_t> pos_host;
     std::vector<float*> k_ctx, v_ctx;   // per layer [capacity][n_kv][hd]
+    // long sessions: per full-attention layer a shadow of the rows above as f16 hi + lo tiles for the tcgen05 attention
+    // kernel (null for the other layers), and the tile set of the block's own rows
+    std::vector<void*> ctx_tiles;
+    void* noise_tiles = nullptr;
     // scratch
     float *x = nullptr, *part = nullptr, *sumsq = nullptr, *q_rot = nullptr, *k_noise = nullptr, *v_noise = nullptr, *attn_part = nullptr;
     uint8_t *acts_h = nullptr, *acts_f = nullptr, *acts_q = nullptr, *acts_fc = nullptr, *acts_lm = nullptr;
@@ -421,18 +433,29 @@ dfl_status dfl_dsession_create(const dfl_drafter* d, uint32_t ctx_capacity, dfl_
     };
     const AttnGeom g = d->geom((int)c.n_q_heads);
     ds->staging = (float*)alloc((size_t)kPendingCap * KH * 4);
-    ds->pos_ctx_dev = (uint32_t*)alloc((size_t)ctx_capacity * 4);
+    ds->pos_ctx_dev = (uint32_t*)alloc(((size_t)ctx_capacity + KV_TILE_KEYS) / KV_TILE_KEYS * KV_TILE_KEYS * 4);   // whole tiles of positions are staged
+    // Tiled shadow (tcgen05 attention) for the layers that attend over the whole context, where scanning it is what the
+    // draft pass spends its time on: contexts of 16384 columns and more, 128-wide heads in groups of four.
+    // DFL_DATTN_TILED=1 / 0 forces it on (where the geometry fits) or off.
+    bool tiled = false;
+    if (c.head_dim == 128 && c.n_kv_heads && c.n_q_heads / c.n_kv_heads == 4 && c.n_q_heads % c.n_kv_heads == 0) {
+        const char* e = getenv("DFL_DATTN_TILED");
+        tiled = e ? e[0] == '1' : ctx_capacity >= 16384;
+    }
     for (uint32_t il = 0; il < c.n_layer; ++il) {
         ds->k_ctx.push_back((float*)alloc((size_t)ctx_capacity * kv_dim * 4));
         ds->v_ctx.push_back((float*)alloc((size_t)ctx_capacity * kv_dim * 4));
+        const bool full_layer = !(c.layer_is_swa[il] && c.swa_window > 0);
+        ds->ctx_tiles.push_back(tiled && full_layer ? alloc(dattn_t5_tile_halfs((int)c.n_kv_heads, ctx_capacity) * 2) : nullptr);
     }
+    if (tiled) ds->noise_tiles = alloc(dattn_t5_tile_halfs((int)c.n_kv_heads, MAX_ROWS) * 2);
     ds->x = (float*)alloc(MAX_ROWS * H * 4);
     ds->part = (float*)alloc(part * 4);
     ds->sumsq = (float*)alloc((H / GLUE_COLS) * MAX_ROWS * 4);
     ds->q_rot = (float*)alloc(MAX_ROWS * q_dim * 4);
     ds->k_noise = (float*)alloc(MAX_ROWS * kv_dim * 4);
     ds->v_noise = (float*)alloc(MAX_ROWS * kv_dim * 4);
-    ds->attn_part = (float*)alloc(attn_partials_floats(g, ctx_capacity + MAX_ROWS) * 4);
+    ds->attn_part = (float*)alloc(attn_partials_floats(g, (ctx_capacity + KV_TILE_KEYS - 1) / KV_TILE_KEYS * KV_TILE_KEYS + 2 * KV_TILE_KEYS) * 4);   // also two records per tile of the tiled path, the block's own tile included
     ds->acts_h = (uint8_t*)alloc(acts_bytes(DFL_BF16, H));
     ds->acts_f = (uint8_t*)alloc(acts_bytes(DFL_BF16, F));
     ds->acts_q = (uint8_t*)alloc(acts_bytes(DFL_BF16, q_dim));
@@ -562,6 +585,7 @@ dfl_status dsession_project_pending(dfl_dsession* ds, bool on_side) {
             DFL_CHECK(launch_group(st, L.kv, ds->acts_hc, ds->part_c, ep_norm, ds->err));
             DFL_CHECK(launch_attn_front(st, gkv, false, ds->part_c, L.kv.splits, (int)L.kv.total_cols, nullptr, L.k_norm_w, 0, (int)nb, ds->k_ctx[il],
                                         ds->v_ctx[il], KV_F32_ROWS, nullptr, nullptr, ds->pos_ctx_dev + c0, (long long)c0));
+            if (ds->ctx_tiles[il]) DFL_CHECK(launch_dctx_tiles(st, ds->k_ctx[il], ds->v_ctx[il], (int)c.n_kv_heads, c0, nb, c0, ds->ctx_tiles[il]));
             if (on_side && last_block) DFL_CUDA(cudaEventRecord(ds->ev_ctx[il], st));
         }
         ds->ready += nb;
@@ -650,6 +674,7 @@ dfl_status dsession_snapshot_read(dfl_dsession* ds, const uint8_t* src, uint32_t
     for (uint32_t il = 0; il < c.n_layer && cols; ++il) {
         DFL_CUDA(cudaMemcpyAsync(ds->k_ctx[il], src, rows, cudaMemcpyHostToDevice, ds->st));
         DFL_CUDA(cudaMemcpyAsync(ds->v_ctx[il], src + rows, rows, cudaMemcpyHostToDevice, ds->st));
+        if (ds->ctx_tiles[il]) DFL_CHECK(launch_dctx_tiles(ds->st, ds->k_ctx[il], ds->v_ctx[il], (int)c.n_kv_heads, 0, cols, 0, ds->ctx_tiles[il]));
         src += 2 * rows;
     }
     DFL_CUDA(cudaStreamSynchronize(ds->st));
@@ -714,6 +739,14 @@ dfl_status draft_core(dfl_dsession* ds, int32_t carry, uint32_t noise_start, boo
             ctx_begin = (int)(std::lower_bound(ds->pos_host.begin(), ds->pos_host.begin() + ds->ctx_len, min_pos) - ds->pos_host.begin());
         }
         if (ctx_on_side) DFL_CUDA(cudaStreamWaitEvent(st, ds->ev_ctx[il], 0));
+        if (ds->ctx_tiles[il] && window == 0) {
+            // the whole context through the tcgen05 kernel: the block's own rows become one more tile set first
+            int n_records = 0;
+            DFL_CHECK(launch_dctx_tiles(st, ds->k_noise, ds->v_noise, (int)c.n_kv_heads, 0, (uint32_t)n, 0, ds->noise_tiles));
+            DFL_CHECK(launch_dattn_t5(st, g, ds->q_rot, ds->ctx_tiles[il], ds->noise_tiles, ds->pos_ctx_dev, (int)ds->ctx_len, noise_start, n,
+                                      c.causal != 0, ds->attn_part, ds->ctx_capacity, ds->err, &n_records));
+            DFL_CHECK(launch_dattn_post(st, g, ds->attn_part, n_records, n, ds->acts_q, bf(L.wo), ds->err));
+        } else
         DFL_CHECK(launch_drafter_attn(st, g, ds->q_rot, ds->k_ctx[il], ds->v_ctx[il], reinterpret_cast<const int32_t*>(ds->pos_ctx_dev), ctx_begin,
                                       (int)ds->ctx_len, ds->k_noise, ds->v_noise, noise_start, n, c.causal != 0, window, ds->attn_part, ds->acts_q,
                                       bf(L.wo), ds->err,

@@ -697,7 +697,7 @@ dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t 
         s->ssm[1].push_back(s1);
         s->ssm_cur.push_back(0);
     }
-    if (ok && m->n_attn) ok = cudaMalloc(&s->attn_partials, attn_partials_floats(m->attn_geom(), kv_capacity) * 4) == cudaSuccess;
+    if (ok && m->n_attn) ok = cudaMalloc(&s->attn_partials, attn_partials_floats(m->attn_geom(), (uint32_t)cap_alloc) * 4) == cudaSuccess;   // two records per 128-position tile in tiled storage
     ok = ok && cudaMalloc(&s->err, 4) == cudaSuccess;
     ok = ok && cudaEventCreate(&s->ev0) == cudaSuccess && cudaEventCreate(&s->ev1) == cudaSuccess;
     ok = ok && cudaStreamCreateWithFlags(&s->st_side, cudaStreamNonBlocking) == cudaSuccess &&

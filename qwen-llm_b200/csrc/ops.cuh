@@ -247,6 +247,13 @@ bool attn_t5_supported(const AttnGeom& g, bool kv_f16);
 int attn_t5_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity);
 dfl_status launch_attn_t5(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* k_cache, const void* v_cache, uint32_t start,
                           int n_rows, float* partials, int chunks_per_span, int* err);
+// the drafter's attention over a tiled hi + lo shadow of its f32 context cache (attn_t5.cu)
+uint64_t dattn_t5_tile_halfs(int n_kv, uint32_t n_keys);
+dfl_status launch_dctx_tiles(cudaStream_t st, const float* k_rows, const float* v_rows, int n_kv, uint32_t first, uint32_t count, uint32_t row0,
+                             void* tiles);
+dfl_status launch_dattn_t5(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* ctx_tiles, const void* noise_tiles,
+                           const uint32_t* pos_ctx, int n_ctx, uint32_t noise_start, int n_rows, bool causal, float* partials, uint32_t ctx_capacity,
+                           int* err, int* n_records_out);
 dfl_status launch_kv_tiled_to_rows(cudaStream_t st, const void* tiled, bool is_v, int n_kv, uint32_t pos0, uint32_t n_pos, void* rows);
 dfl_status launch_kv_rows_to_tiled(cudaStream_t st, const void* rows, bool is_v, int n_kv, uint32_t pos0, uint32_t n_pos, void* tiled);
 // tensor-core span kernel over an fp16 cache (attn_tc.cu)

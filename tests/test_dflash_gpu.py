@@ -191,3 +191,36 @@ def test_draft_block_with_tensor_core_attention_matches_oracle():
         for x in (sess, scr, ds, ds2):
             x.close()
     gd.close(); gm.close()
+
+
+@pytest.mark.parametrize("causal", [0, 1])
+def test_drafter_attention_over_the_tiled_context_matches_oracle(monkeypatch, causal):
+    # the full-attention layer of a long drafter session reads a tiled f16 hi + lo shadow of its f32 context through
+    # the tcgen05 kernel: forced on here for a 300-column context (three tiles + the block's own tile, one tile per
+    # span), positions with gaps, bidirectional and causal; checked against the oracle and against the row-major path
+    arch = modelgen.tiny_arch()
+    cfg = modelgen.tiny_dflash_config(arch, n_q_heads=4, causal=causal)
+    T, D = modelgen.target_tensors(arch, seed=3), modelgen.drafter_tensors(arch, cfg, seed=6)
+    om, gm = modelgen.OracleModel(arch, T), pkg.Model(arch, T)
+    od, gd = modelgen.OracleDrafter(cfg, D), pkg.Drafter(gm, cfg, D)
+    rng = np.random.default_rng(12)
+    n_ctx = 300
+    ctx = (rng.standard_normal((n_ctx, cfg.n_target_layers * arch.hidden_size)) * 0.5).astype(np.float32)
+    pos = np.cumsum(rng.integers(1, 3, size=n_ctx)).astype(np.uint32)      # increasing, with gaps
+    start = int(pos[-1]) + 1 if causal else int(pos[n_ctx // 2])            # bidirectional: later context columns too
+    carry = 11
+    noise = [carry] + [cfg.mask_token_id] * 15
+    want = od.draft(om, noise, ctx, pos, start)
+    outs = {}
+    for tiled in ("1", "0"):
+        monkeypatch.setenv("DFL_DATTN_TILED", tiled)
+        ds = pkg.DSession(gd, 384)
+        ds.append_columns(ctx[:250], pos[:250])
+        ds.draft_block(carry, start)                                       # a pass in between: the shadow grows incrementally
+        ds.append_columns(ctx[250:], pos[250:])
+        _, got = ds.draft_block(carry, start, want_logits=True)
+        np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL, err_msg=f"tiled={tiled}")
+        outs[tiled] = got
+        ds.close()
+    np.testing.assert_allclose(outs["1"], outs["0"], rtol=1e-3, atol=2e-4)
+    gd.close(); gm.close()
