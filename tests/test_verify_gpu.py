@@ -333,6 +333,35 @@ def test_tcgen05_attention_agrees_with_the_oracle_at_any_rescale_threshold(monke
     gm.close()
 
 
+def test_tcgen05_attention_block_across_a_tile_boundary_and_at_full_capacity(tiny_g4, monkeypatch):
+    # a 16-row block whose rows sit on both sides of a 128-position tile boundary (its first rows see one tile, its last
+    # rows two: the new tile holds eight written keys), and a cache filled to its last position
+    monkeypatch.setenv("DFL_ATTN_TILED", "1")
+    arch, om, gm = tiny_g4
+    rng = np.random.default_rng(57)
+    cap = 256
+    sess, scr = pkg.Session(gm, cap, True), pkg.Scratch(gm, 16, 1)
+    ost = om.new_state(cap, True)
+    pos = 0
+    for n in [16] * 7 + [8]:                          # 120 positions
+        toks = rng.integers(0, arch.vocab_size, size=n)
+        pkg.packed_verify(gm, sess, scr, [3], toks, pos)
+        for i, t in enumerate(toks):
+            om.single_token(ost, t, pos + i, (), want_logits=False)
+        pos += n
+    while pos < cap:                                  # 120-135 straddles the boundary; the last block ends at capacity
+        toks = rng.integers(0, arch.vocab_size, size=min(16, cap - pos))
+        want, _ = oracle_block(om, ost, toks, pos, [3])
+        _, _, got = pkg.packed_verify(gm, sess, scr, [3], toks, pos, want_logits=True)
+        np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL, err_msg=f"block at {pos}")
+        pos += len(toks)
+    assert sess.kv_n_pos == cap
+    with pytest.raises(pkg.DflError) as e:            # the guard wall still holds
+        pkg.packed_verify(gm, sess, scr, [3], [1], pos)
+    assert e.value.name == "KV_STATE"
+    sess.close(); scr.close()
+
+
 def test_snapshot_moves_between_tiled_and_row_major_caches(tiny_g4, monkeypatch):
     # a snapshot carries K / V as position-major rows whatever the session's storage: tiled -> tiled continues bitwise,
     # tiled -> rows and rows -> tiled hold the same f16 rows
