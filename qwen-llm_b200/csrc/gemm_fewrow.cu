@@ -507,7 +507,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_fewrow_kernel(const Gemm
             ok = mbar_wait_bounded(&empty[sj], (j / STAGES) & 1, p.err, DEV_ERR_WAIT_EMPTY);
             if (ok) issue(sj);
         }
-        if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the producer's verdict, warp-uniform
+        if (warp == 0) ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the producer's outcome, warp-uniform
         const int s = i % STAGES;
         if (ok) ok = mbar_wait_bounded(&full[s], (i / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
         if (ok) {

@@ -101,7 +101,7 @@ def main():
                 fresh = e.name
             torch.cuda.synchronize()        # the context is still usable
             print("EP_WATCHDOG", outcome, later, fresh, f"{dt:.2f}", flush=True)
-        # rank 1 joins no pass; it waits on the host for rank 0's verdict, then both leave without touching the
+        # rank 1 joins no pass; it waits on the host for rank 0's result, then both leave without touching the
         # aborted communicator again
         store = dist.distributed_c10d._get_default_store()
         if rank == 0:
