@@ -289,9 +289,9 @@ def run_reference(args, rank, world):
                 "warmup": args.warmup, "ms_per_step": r["block_s"] * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
                 "config": {"workload": c2.WORKLOAD_C2, "l2": "5.1 GB of weights per verify >> 126 MB L2",
-                           "parallelism": f"dp{world}: one independent sequence per GPU, no collective",
-                           "reference_step": "a step of this arm is one 16-row block through a 4-layer slice of the model (bounded sample); "
-                                             "value = 4.4 emitted tokens / (layers' share x 32/4 + head share)"},
+                           "parallelism": f"dp{world}: one independent sequence per GPU, no collective"},
+                "reference_step": "a step of this arm is one 16-row block through a 4-layer slice of the model (bounded sample); "
+                                  "value = 4.4 emitted tokens / (layers' share x 32/4 + head share)",
                 "extrapolated_full_step_ms": r["full_step_s"] * 1e3,
                 "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["threads"], "kind": "port", "sample": r["sample"]},
                 "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
