@@ -410,7 +410,7 @@ def run_verify_only(args, rank, world, device):
         t = torch.tensor([wall], dtype=torch.float64, device=f"cuda:{device}")
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         wall = float(t[0])
-    extra = {"parallelism": f"ep{world}: experts split over {world} GPUs, one all-reduce per routed-expert block"} if ep else {}
+    extra = {"parallelism": f"ep{world}: experts split over {world} GPUs, block outputs combined over peer memory (DFL_EP_COMBINE=nccl: ncclAllReduce)"} if ep else {}
     if os.environ.get("DFL_GEMM_TIMING"):
         ms, n, b = pkg.gemm_timing_end()
         extra = {"gemm_ms_per_step": ms / args.steps, "gemm_launches": n, "gemm_GBps": b / (ms * 1e-3) / 1e9}
