@@ -443,6 +443,12 @@ def run_verify_only(args, rank, world, device):
 # ---------------------------------------------------------------------------
 C3_SEQS, C3_PROMPT, C3_T, C3_TOP_P, C3_SEED, C3_KV = 32, 1024, 0.7, 0.95, 0xC3, 2048
 C3_THREADS = int(os.environ.get("DFL_C3_THREADS", "4"))   # host threads driving a rank's sequences in the end-to-end pass
+# End-to-end pass on a host whose cores are all taken by driving threads (ranks x threads >= cores): the verify rows are
+# ordered on the device (the host sampler then skips its sort, 45 % of its work per row) and the driving threads block
+# instead of spinning while they wait for the GPU.  On a host with cores to spare both cost more than they give (the
+# sort and the second 9.7 MB copy are GPU time, a blocked thread wakes up late), so the rule is applied per launch:
+# DFL_C3_HOST_OFFLOAD=auto (default) | 1 | 0.  The device-timed pass always runs the plain path.
+C3_HOST_OFFLOAD = os.environ.get("DFL_C3_HOST_OFFLOAD", "auto")
 
 
 class Seq:
@@ -551,6 +557,9 @@ def run_c3(args, rank, world, device):
     n_done = n_b - 1           # tokens emitted by the device-timed pass, after the n_a of the warm-up
     n_c = tokens_for_steps(PATTERN, warm + steps, steps)
     threads = max(1, min(C3_THREADS, len(seqs)))
+    offload = C3_HOST_OFFLOAD == "1" or (C3_HOST_OFFLOAD == "auto" and world * threads >= (os.cpu_count() or 1))
+    if offload:
+        pkg.set_host_wait("block")
     scratches = [w.scr] + [pkg.Scratch(w.model, 16, len(w.layer_ids)) for _ in range(threads - 1)]
     errors, emitted_e2e = [], [0] * threads
 
@@ -559,7 +568,8 @@ def run_c3(args, rank, world, device):
             for q, (cont, hist, n_a, last) in list(zip(seqs, state))[ti::threads]:
                 at = n_a - 1 + n_done
                 toks_c, st = pkg.generate(w.model, q.sess, scratches[ti], q.ds, q.sampler(at_draw=at), forced(V, int(cont[at])), n_c,
-                                          replay_history=hist[at:], replay_runs_drafter=True, replay_unchecked=True)
+                                          replay_history=hist[at:], replay_runs_drafter=True, replay_unchecked=True,
+                                          device_row_order=offload)
                 assert np.array_equal(toks_c, cont[at:at + n_c]), "end-to-end output differs from the plain sampled continuation"
                 assert st.spec_steps == steps, (st.spec_steps, steps)
                 emitted_e2e[ti] += n_c - 1
@@ -575,6 +585,8 @@ def run_c3(args, rank, world, device):
         t.join()
     torch.cuda.synchronize(device)
     wall_ms = (time.perf_counter() - t0) * 1e3
+    if offload:
+        pkg.set_host_wait("auto")
     if errors:
         raise errors[0]
     for sc in scratches[1:]:
@@ -603,7 +615,8 @@ def run_c3(args, rank, world, device):
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_kind": peak_kind,
                      "kernel": "one packed verify (all kernels), weight bytes / CUDA-event time"},
         "e2e": {"value": emitted_wall / (wall_max * 1e-3), "unit": bench.UNIT, "h2d_bytes_per_step": len(seqs) * 2 * 16 * 4,
-                "d2h_bytes_per_step": len(seqs) * (16 * V * 4 + 3 * 16 * 4), "host_threads": threads,
+                "d2h_bytes_per_step": len(seqs) * (16 * V * 4 * (2 if offload else 1) + 3 * 16 * 4),
+                "host_offload": "verify rows ordered on the device, driving threads block while waiting" if offload else "off (cores to spare)", "host_threads": threads,
                 "one_thread_tok_per_s": tot["emitted"] / (wall_serial_ms * 1e-3)},
         "gpu_launches": int(launches), "clocks": clocks,
         "per_outer_step_ms": {"draft": tot["draft_ms"] / n_steps_rank, "verify": verify_ms, "restore": tot["restore_ms"] / n_steps_rank,

@@ -143,6 +143,12 @@ const char* dfl_version(void);
 const char* dfl_last_error(void);
 /* Number of usable CUDA devices (0 when the driver or a device is missing). */
 int32_t dfl_device_count(void);
+/* How this process's host threads wait for the device in every synchronising call of this library: 0 the driver's
+ * default (spins while contexts are fewer than cores), 1 spin, 2 yield, 3 block on an OS primitive.  Blocking frees the
+ * core for the sampler's worker threads when many driving threads share a host (one per sequence, several ranks); it
+ * costs a wake-up per wait, so a single driving thread is faster with the default.  The environment variable
+ * DFL_HOST_WAIT=auto|spin|yield|block sets the initial policy.  Takes effect at each device's next use. */
+dfl_status dfl_set_host_wait(int32_t mode);
 /* Kernel launches this library issued on the calling process since load. */
 uint64_t dfl_launch_count(void);
 /* Per-kernel device timing of the few-row GEMM (the reference reads per-phase GPU time from
@@ -315,6 +321,15 @@ dfl_status dfl_session_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession
  * continuing from the session the snapshot was taken from. */
 dfl_status dfl_session_restore_snapshot(const dfl_model* m, dfl_session* s, dfl_dsession* ds,
                                         const void* blob, uint64_t n_bytes);
+
+/* When order_host is not NULL, every later dfl_packed_verify on this scratch that returns logits to the host also
+ * orders each returned row on the device - token ids by descending logit in the f32 total order, ties by ascending
+ * token - and copies the [n][vocab] order to order_host (u32, caller-owned, at least block_size * vocab entries;
+ * pinned memory recommended) in the same call.  NULL switches it off. */
+dfl_status dfl_scratch_set_order_host(dfl_scratch* sc, uint32_t* order_host);
+/* The same ordering on rows given by the host (host-to-host test entry): order_out [n_rows][vocab]. */
+dfl_status dfl_sort_rows_desc(int32_t device, const float* logits_host, int32_t n_rows, uint64_t vocab,
+                              uint32_t* order_out);
 
 /* MetalDFlashVerifyScratch::fresh + MetalDFlashLayerMajorScratch::fresh
  * metal_dflash.rs:6003-6075, :8025. */
@@ -500,6 +515,16 @@ void dfl_sampler_destroy(dfl_sampler* s);
 void dfl_sampler_get_config(const dfl_sampler* s, dfl_sampling_config* out);
 uint64_t dfl_sampler_draws(const dfl_sampler* s);
 void dfl_sampler_rng_state(const dfl_sampler* s, uint64_t out_state[4]);
+/* Presorted rows.  The sampler orders a row's candidates by descending logit (total order, ties by ascending
+ * token: sampling.rs:305-790) before anything else; that order is a pure function of the logits' bits, and the device
+ * can produce it (dfl_scratch_set_order_host).  After this call, a row whose logits pointer is
+ * logits_base + r * vocab (r < n_rows) takes its order from order_base + r * vocab instead of sorting; an order that
+ * is not the row's sorted order is detected and ignored (the row is then sorted on the host).  NULL bases clear the
+ * registration.  The caller keeps both arrays alive while registered. */
+dfl_status dfl_sampler_set_row_order(dfl_sampler* s, const float* logits_base, const uint32_t* order_base,
+                                     uint32_t n_rows, uint64_t vocab);
+/* Rows that took a registered order since the sampler was created (rows whose order was refused are not counted). */
+uint64_t dfl_sampler_preordered_rows(const dfl_sampler* s);
 /* Sampler::sample  sampling.rs:530 */
 dfl_status dfl_sampler_sample(dfl_sampler* s, const float* logits, uint64_t vocab,
                               int32_t* token_out, uint64_t* candidate_index_out);
@@ -580,6 +605,10 @@ typedef struct dfl_generate_params {
      * with what was emitted (the reference stops replaying at the first divergence).  Lets a caller
      * script an acceptance schedule by corrupting chosen draft positions. */
     int32_t replay_unchecked;
+    /* sampled mode: order every verify row on the device (dfl_scratch_set_order_host) and hand the order to the
+     * sampler (dfl_sampler_set_row_order), which then skips its own ordering of the 151 936-token rows.  Draws,
+     * decisions and generator state are unchanged. */
+    int32_t device_row_order;
 } dfl_generate_params;
 
 typedef struct dfl_generate_stats { /* DflashDecodeStats  qwen/dflash.rs:380-418 */

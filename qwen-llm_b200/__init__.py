@@ -72,7 +72,8 @@ class AcceptDecision(C.Structure):
 class GenerateParams(C.Structure):
     _fields_ = [("max_tokens", C.c_uint32), ("stop_ids", C.POINTER(C.c_int32)), ("n_stop_ids", C.c_uint32),
                 ("replay_history", C.POINTER(C.c_int32)), ("n_replay_history", C.c_uint32), ("sparse_proposals", C.c_int32),
-                ("verify_margin", C.c_float), ("replay_runs_drafter", C.c_int32), ("replay_unchecked", C.c_int32)]
+                ("verify_margin", C.c_float), ("replay_runs_drafter", C.c_int32), ("replay_unchecked", C.c_int32),
+                ("device_row_order", C.c_int32)]
 
 
 class GenerateStats(C.Structure):
@@ -98,7 +99,7 @@ def lib():
         L.dfl_last_error.restype = C.c_char_p
         L.dfl_device_count.restype = C.c_int32
         L.dfl_launch_count.restype = C.c_uint64
-        for name in ("dfl_model_verify_weight_bytes", "dfl_drafter_weight_bytes", "dfl_sampler_draws",
+        for name in ("dfl_model_verify_weight_bytes", "dfl_drafter_weight_bytes", "dfl_sampler_draws", "dfl_sampler_preordered_rows",
                      "dfl_splitmix64_next", "dfl_sampler_next_u64"):
             if hasattr(L, name):
                 getattr(L, name).restype = C.c_uint64
@@ -121,6 +122,11 @@ def check(status):
 
 def _ptr(a, t=C.c_void_p):
     return a.ctypes.data_as(t)
+
+
+def set_host_wait(mode):
+    """'auto' | 'spin' | 'yield' | 'block': how host threads wait for the device (dfl_set_host_wait)."""
+    check(lib().dfl_set_host_wait(C.c_int32({"auto": 0, "spin": 1, "yield": 2, "block": 3}[mode])))
 
 
 def device_count():
@@ -358,13 +364,23 @@ def _u32(a):
     return np.ascontiguousarray(a, dtype=np.uint32)
 
 
-def packed_verify(model, session, scratch, layer_ids, tokens, start_position, want_logits=False):
+def packed_verify(model, session, scratch, layer_ids, tokens, start_position, want_logits=False, want_order=False):
+    """want_order (with want_logits): also returns each row's token ids by descending logit, ordered on the device."""
     tokens = np.ascontiguousarray(tokens, dtype=np.int32)
     n = tokens.size
     ids = _u32(layer_ids)
     am = np.zeros(n, dtype=np.int32)
     gap = np.zeros(n, dtype=np.float32)
     logits = np.zeros((n, model.arch.vocab_size), dtype=np.float32) if want_logits else None
+    if want_order:
+        order = np.zeros((scratch.block_size, model.arch.vocab_size), dtype=np.uint32)
+        check(lib().dfl_scratch_set_order_host(scratch.h, _ptr(order, C.POINTER(C.c_uint32))))
+        try:
+            check(lib().dfl_packed_verify(model.h, session.h, scratch.h, _ptr(ids) if ids.size else None, C.c_uint32(ids.size),
+                                          _ptr(tokens), C.c_uint32(n), C.c_uint32(start_position), _ptr(am), _ptr(gap), _ptr(logits)))
+        finally:
+            lib().dfl_scratch_set_order_host(scratch.h, None)
+        return am, gap, logits, order[:n]
     check(lib().dfl_packed_verify(model.h, session.h, scratch.h, _ptr(ids) if ids.size else None, C.c_uint32(ids.size), _ptr(tokens),
                                   C.c_uint32(n), C.c_uint32(start_position), _ptr(am), _ptr(gap),
                                   _ptr(logits) if want_logits else None))
@@ -459,6 +475,10 @@ class Sampler:
     def draws(self):
         return int(lib().dfl_sampler_draws(self.h))
 
+    @property
+    def preordered_rows(self):
+        return int(lib().dfl_sampler_preordered_rows(self.h))
+
     def rng_state(self):
         st = (C.c_uint64 * 4)()
         lib().dfl_sampler_rng_state(self.h, st)
@@ -469,6 +489,19 @@ class Sampler:
 
     def next_unit_f64(self):
         return float(lib().dfl_sampler_next_unit_f64(self.h))
+
+    def set_row_order(self, logits, order):
+        """Registers presorted rows: `order` [n][vocab] u32 for the C-contiguous f32 `logits` [n][vocab] (both kept alive
+        by this object and passed to sample() / accept_prefix() as views of these very arrays); None clears."""
+        self._row_order_keep = None
+        if logits is None or order is None:
+            check(lib().dfl_sampler_set_row_order(self.h, None, None, C.c_uint32(0), C.c_uint64(0)))
+            return
+        assert logits.dtype == np.float32 and order.dtype == np.uint32 and logits.flags.c_contiguous and order.flags.c_contiguous
+        assert logits.shape == order.shape and logits.ndim == 2
+        check(lib().dfl_sampler_set_row_order(self.h, _ptr(logits), _ptr(order, C.POINTER(C.c_uint32)), C.c_uint32(logits.shape[0]),
+                                              C.c_uint64(logits.shape[1])))
+        self._row_order_keep = (logits, order)   # the library reads both arrays until the registration is cleared
 
     def sample(self, logits):
         logits = np.ascontiguousarray(logits, dtype=np.float32)
@@ -493,6 +526,14 @@ def topk16(x, device=0):
     vals = np.zeros((x.shape[0], 16), dtype=np.float32)
     check(lib().dfl_topk16(C.c_int32(device), _ptr(x), C.c_int32(x.shape[0]), C.c_uint64(x.shape[1]), _ptr(ids), _ptr(vals)))
     return ids, vals
+
+
+def sort_rows_desc(x, device=0):
+    """Token ids of every row by descending value (f32 total order, ties by ascending index), ordered on the device."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    order = np.zeros(x.shape, dtype=np.uint32)
+    check(lib().dfl_sort_rows_desc(C.c_int32(device), _ptr(x), C.c_int32(x.shape[0]), C.c_uint64(x.shape[1]), _ptr(order)))
+    return order
 
 
 class Codebook:
@@ -697,7 +738,8 @@ def prefill(model, session, scratch, layer_ids, ids, start_position=0, feed_draf
 
 
 def generate(model, session, scratch, dsession, sampler, first_logits, max_tokens, stop_ids=(), replay_history=None,
-             sparse_proposals=False, verify_margin=0.0, replay_runs_drafter=False, replay_unchecked=False):
+             sparse_proposals=False, verify_margin=0.0, replay_runs_drafter=False, replay_unchecked=False,
+             device_row_order=False):
     first_logits = np.ascontiguousarray(first_logits, dtype=np.float32)
     stops = np.ascontiguousarray(stop_ids, dtype=np.int32)
     hist = np.ascontiguousarray(replay_history, dtype=np.int32) if replay_history is not None else None
@@ -711,6 +753,7 @@ def generate(model, session, scratch, dsession, sampler, first_logits, max_token
     p.verify_margin = verify_margin
     p.replay_runs_drafter = 1 if replay_runs_drafter else 0
     p.replay_unchecked = 1 if replay_unchecked else 0
+    p.device_row_order = 1 if device_row_order else 0
     out = np.zeros(max_tokens, dtype=np.int32)
     n = C.c_uint32(0)
     stats = GenerateStats()

@@ -1,5 +1,8 @@
 // C ABI: library diagnostics, resident quantised matrices, the standalone few-row
 // GEMM / argmax entry points and the two-GEMM "config 1" pipeline.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -37,6 +40,27 @@ dfl_status fail(dfl_status st, const std::string& msg) {
     return st;
 }
 
+// How a host thread waits for the device (stream and event synchronisation): the driver's default spins while there are
+// fewer contexts than cores, which is the lowest latency for one driving thread and the wrong choice when many driving
+// threads share the cores with the sampler's worker threads - a spinning waiter then takes a core from a thread that
+// has work.  DFL_HOST_WAIT=block|yield|spin|auto (or dfl_set_host_wait) picks the policy per process.
+namespace {
+std::atomic<int> g_host_wait{-1};        // -1: environment not read yet; 0 auto, 1 spin, 2 yield, 3 block
+std::atomic<uint32_t> g_wait_applied{0}; // bit d: device d carries the current policy
+int host_wait_policy() {
+    int p = g_host_wait.load(std::memory_order_acquire);
+    if (p >= 0) return p;
+    const char* e = std::getenv("DFL_HOST_WAIT");
+    p = 0;
+    if (e && !std::strcmp(e, "spin")) p = 1;
+    else if (e && !std::strcmp(e, "yield")) p = 2;
+    else if (e && !std::strcmp(e, "block")) p = 3;
+    int expected = -1;
+    g_host_wait.compare_exchange_strong(expected, p);
+    return g_host_wait.load(std::memory_order_acquire);
+}
+}  // namespace
+
 dfl_status use_device(int device) {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
@@ -45,6 +69,28 @@ dfl_status use_device(int device) {
     }
     if (device < 0 || device >= n) return fail(DFL_ERR_BAD_ARG, "device index out of range");
     DFL_CUDA(cudaSetDevice(device));
+    const int policy = host_wait_policy();
+    if (policy > 0 && device < 32 && !(g_wait_applied.load(std::memory_order_acquire) & (1u << device))) {
+        const unsigned flag = policy == 1 ? cudaDeviceScheduleSpin : policy == 2 ? cudaDeviceScheduleYield : cudaDeviceScheduleBlockingSync;
+        DFL_CUDA(cudaSetDeviceFlags(flag));
+        g_wait_applied.fetch_or(1u << device, std::memory_order_acq_rel);
+    }
+    return DFL_OK;
+}
+
+extern "C" dfl_status dfl_set_host_wait(int32_t mode) {
+    if (mode < 0 || mode > 3) return fail(DFL_ERR_BAD_ARG, "set_host_wait: mode is 0 (driver default), 1 (spin), 2 (yield) or 3 (block)");
+    g_host_wait.store(mode, std::memory_order_release);
+    const uint32_t had = g_wait_applied.exchange(0, std::memory_order_acq_rel);   // every device takes the new policy at its next use
+    if (mode == 0 && had) {   // back to the driver's default on the devices this library changed, and only on those
+        int cur = 0;
+        if (cudaGetDevice(&cur) == cudaSuccess) {
+            for (int d = 0; d < 32; ++d)
+                if ((had >> d & 1u) && cudaSetDevice(d) == cudaSuccess) cudaSetDeviceFlags(cudaDeviceScheduleAuto);
+            cudaSetDevice(cur);
+        }
+        cudaGetLastError();
+    }
     return DFL_OK;
 }
 

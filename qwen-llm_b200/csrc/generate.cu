@@ -105,6 +105,17 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         return fail(DFL_ERR_OOM, "generate: pinned logits buffer");
     }
     struct { float* p; float* data() const { return p; } } logits_host{sc->pinned_logits};
+    // rows ordered on the device: the order lands beside the logits and the sampler is told where (cleared on every exit)
+    const bool device_order = sampled && params->device_row_order;
+    if (device_order) {
+        if (!sc->pinned_order && cudaMallocHost(&sc->pinned_order, (size_t)sc->block_size * V * 4) != cudaSuccess) {
+            sc->pinned_order = nullptr;
+            if (proposal_sampler) dfl_sampler_destroy(proposal_sampler);
+            return fail(DFL_ERR_OOM, "generate: pinned row-order buffer");
+        }
+        dfl_scratch_set_order_host(sc, sc->pinned_order);
+        dfl_sampler_set_row_order(sampler, sc->pinned_logits, sc->pinned_order, sc->block_size, V);
+    }
     auto is_stop = [&](int32_t t) {
         for (uint32_t i = 0; i < params->n_stop_ids; ++i)
             if (params->stop_ids[i] == t) return true;
@@ -330,6 +341,10 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
         carry = dec.next_carry;
     }
     if (proposal_sampler) dfl_sampler_destroy(proposal_sampler);
+    if (device_order) {
+        dfl_scratch_set_order_host(sc, nullptr);
+        dfl_sampler_set_row_order(sampler, nullptr, nullptr, 0, 0);
+    }
     settle_restore(false);
     if (rc == DFL_OK) {   // nothing of this call is left in flight when it returns
         if (cudaStreamSynchronize(s->st) != cudaSuccess) rc = fail(DFL_ERR_CUDA, "generate: stream synchronize failed");

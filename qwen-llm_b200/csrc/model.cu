@@ -880,6 +880,9 @@ void dfl_scratch_destroy(dfl_scratch* sc) {
     if (sc->pinned_i) cudaFreeHost(sc->pinned_i);
     if (sc->pinned_f) cudaFreeHost(sc->pinned_f);
     if (sc->pinned_logits) cudaFreeHost(sc->pinned_logits);
+    if (sc->pinned_order) cudaFreeHost(sc->pinned_order);
+    if (sc->order_dev) cudaFree(sc->order_dev);
+    if (sc->sort_scratch) cudaFree(sc->sort_scratch);
     delete sc;
 }
 
@@ -910,9 +913,24 @@ dfl_status dfl_packed_verify(const dfl_model* m, dfl_session* s, dfl_scratch* sc
     cudaMemcpyAsync(sc->pinned_i + MAX_ROWS, sc->argmax, n * 4, cudaMemcpyDeviceToHost, s->st);
     cudaMemcpyAsync(sc->pinned_f, sc->gap, n * 4, cudaMemcpyDeviceToHost, s->st);
     if (logits_host) cudaMemcpyAsync(logits_host, sc->logits, (size_t)n * m->arch.vocab_size * 4, cudaMemcpyDeviceToHost, s->st);
+    if (logits_host && sc->order_host) {
+        // the rows' order for the host sampler, produced while the logits travel
+        const uint64_t V = m->arch.vocab_size;
+        if (!sc->order_dev) DFL_CUDA(cudaMalloc(&sc->order_dev, (size_t)sc->block_size * V * 4));
+        if (!sc->sort_scratch) DFL_CUDA(cudaMalloc(&sc->sort_scratch, sort_rows_scratch_bytes((int)sc->block_size, V)));
+        st = launch_sort_rows_desc(s->st, sc->logits, (int)n, V, V, sc->sort_scratch, sc->order_dev);
+        if (st != DFL_OK) { s->poisoned = true; return st; }
+        cudaMemcpyAsync(sc->order_host, sc->order_dev, (size_t)n * V * 4, cudaMemcpyDeviceToHost, s->st);
+    }
     DFL_CHECK(completion_check(s));
     memcpy(argmax_out, sc->pinned_i + MAX_ROWS, n * 4);
     if (gap_out) memcpy(gap_out, sc->pinned_f, n * 4);
+    return DFL_OK;
+}
+
+dfl_status dfl_scratch_set_order_host(dfl_scratch* sc, uint32_t* order_host) {
+    if (!sc) return fail(DFL_ERR_BAD_ARG, "set_order_host: null scratch");
+    sc->order_host = order_host;
     return DFL_OK;
 }
 

@@ -182,6 +182,12 @@ struct dfl_scratch {
     int32_t* pinned_i = nullptr;  // [16] tokens in, [16] argmax out
     float* pinned_f = nullptr;    // [16] gaps
     float* pinned_logits = nullptr;  // [block][vocab], made on first use by the sampled outer loop
+    // rows ordered on the device for the host sampler (sortrows.cu): destination on the host (null = off), device
+    // order [block][vocab] and the sort's scratch (made on first use), and a pinned destination of the outer loop
+    uint32_t* order_host = nullptr;
+    uint32_t* order_dev = nullptr;
+    void* sort_scratch = nullptr;
+    uint32_t* pinned_order = nullptr;
     uint32_t last_n = 0, last_start = 0;
     uint32_t last_n_verify = 0;   // rows of the last verify (last_n shrinks to n_keep after a partial restore)
     bool have_block = false;

@@ -247,6 +247,9 @@ bool attn_t5_supported(const AttnGeom& g, bool kv_f16);
 int attn_t5_chunks_per_span(const AttnGeom& g, uint32_t kv_capacity);
 dfl_status launch_attn_t5(cudaStream_t st, const AttnGeom& g, const float* q_rot, const void* k_cache, const void* v_cache, uint32_t start,
                           int n_rows, float* partials, int chunks_per_span, int* err);
+// rows of logits ordered for the host sampler (sortrows.cu)
+uint64_t sort_rows_scratch_bytes(int n_rows, uint64_t vocab);
+dfl_status launch_sort_rows_desc(cudaStream_t st, const float* logits, int n_rows, uint64_t vocab, uint64_t ld, void* scratch, uint32_t* order);
 // the drafter's attention over a tiled hi + lo shadow of its f32 context cache (attn_t5.cu)
 uint64_t dattn_t5_tile_halfs(int n_kv, uint32_t n_keys);
 dfl_status launch_dctx_tiles(cudaStream_t st, const float* k_rows, const float* v_rows, int n_kv, uint32_t first, uint32_t count, uint32_t row0,

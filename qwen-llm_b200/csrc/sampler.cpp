@@ -5,6 +5,7 @@
 // :1370-1438, xoshiro256++ / SplitMix64 :1619-1670) and crates/qwen-llm/src/metal_dflash/accept.rs
 // (`decide_dflash_accept_prefix` :76-183).  Acceptance runs on the host in the reference too.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <thread>
@@ -75,12 +76,42 @@ struct Buffers {
     std::vector<double> cumulative;
 };
 
+// Keys of a row from an order made elsewhere (the device): token order[i] is the i-th candidate.  The order is checked
+// - every token in range, keys non-decreasing, which for a permutation is exactly "sorted, ties by ascending token"
+// when equal keys also ascend in token - and refused (false) when it is not this row's order.
+bool keys_from_order(const float* logits, uint64_t n, const uint32_t* order, uint64_t take, std::vector<uint64_t>& keys) {
+    keys.resize(take);
+    uint64_t prev = 0;
+    for (uint64_t i = 0; i < take; ++i) {
+        const uint32_t t = order[i];
+        if (t >= n) return false;
+        const uint64_t k = ((uint64_t)descending_bits(logits[t]) << 32) | t;
+        if (i && k <= prev) return false;   // strictly increasing 64-bit keys: sorted by logit, then by token, no repeats
+        keys[i] = k;
+        prev = k;
+    }
+    return true;
+}
+
 // Orders candidate keys: whole row when top-k is off, else the top_k best.  Returns count or error.
-SErr order_keys(const float* logits, uint64_t n, uint64_t top_k, Buffers& b, uint64_t* count, uint64_t* nan_token) {
+SErr order_keys(const float* logits, uint64_t n, uint64_t top_k, Buffers& b, uint64_t* count, uint64_t* nan_token,
+                const uint32_t* order = nullptr, bool* order_used = nullptr) {
     if (n == 0) return S_EMPTY;
     if (n > 0x7fffffffull) return S_TOO_LARGE;
-    b.keys.resize(n);
     const bool full = top_k == 0 || top_k >= n;
+    if (order) {
+        for (uint64_t t = 0; t < n; ++t)
+            if (std::isnan(logits[t])) { *nan_token = t; return S_NAN; }
+        const uint64_t take = full ? n : top_k;
+        // a prefix of a sorted permutation is the sorted top-k; for the whole row the strict increase over n keys in
+        // [0, n) token range makes it a permutation
+        if (keys_from_order(logits, n, order, take, b.keys)) {
+            *count = take;
+            if (order_used) *order_used = true;
+            return S_OK;
+        }
+    }
+    b.keys.resize(n);
     // keys in token order; the four byte histograms of the logit half are taken in the same pass
     uint32_t hist[4][256];
     if (full) std::memset(hist, 0, sizeof(hist));
@@ -142,6 +173,18 @@ struct dfl_sampler {
         uint64_t nan_token = 0;
         Buffers buf;
     };
+    // rows whose order was made elsewhere (dfl_sampler_set_row_order)
+    const float* ord_logits = nullptr;
+    const uint32_t* ord_base = nullptr;
+    uint32_t ord_rows = 0;
+    uint64_t ord_vocab = 0;
+    mutable std::atomic<uint64_t> ord_used{0};   // rows that took a registered order (rows are built on several threads)
+    const uint32_t* order_for(const float* logits, uint64_t n) const {
+        if (!ord_logits || n != ord_vocab || logits < ord_logits) return nullptr;
+        const uint64_t off = (uint64_t)(logits - ord_logits);
+        if (off % ord_vocab || off / ord_vocab >= ord_rows) return nullptr;
+        return ord_base + off;
+    }
     std::vector<Prepared> prepared;
     const float* block_logits = nullptr;
     uint64_t block_vocab = 0;
@@ -197,7 +240,9 @@ struct dfl_sampler {
     }
     SErr distribution(const float* logits, uint64_t n, Dist& d, uint64_t* nan_token, Buffers& buf) const {
         uint64_t len = 0;
-        SErr e = order_keys(logits, n, cfg.top_k, buf, &len, nan_token);
+        bool order_used = false;
+        SErr e = order_keys(logits, n, cfg.top_k, buf, &len, nan_token, order_for(logits, n), &order_used);
+        if (order_used) ord_used.fetch_add(1, std::memory_order_relaxed);
         if (e != S_OK) return e;
         const uint64_t* keys = buf.keys.data();
         if (cfg.min_p > 0.0f) {
@@ -410,6 +455,25 @@ dfl_status dfl_sampler_create_at_draw(const dfl_sampling_config* cfg, uint64_t d
     return DFL_OK;
 }
 void dfl_sampler_destroy(dfl_sampler* s) { delete s; }
+
+uint64_t dfl_sampler_preordered_rows(const dfl_sampler* s) { return s ? s->ord_used.load(std::memory_order_relaxed) : 0; }
+
+dfl_status dfl_sampler_set_row_order(dfl_sampler* s, const float* logits_base, const uint32_t* order_base, uint32_t n_rows,
+                                     uint64_t vocab) {
+    if (!s) return DFL_ERR_BAD_ARG;
+    if (!logits_base || !order_base || n_rows == 0 || vocab == 0) {
+        s->ord_logits = nullptr;
+        s->ord_base = nullptr;
+        s->ord_rows = 0;
+        s->ord_vocab = 0;
+        return DFL_OK;
+    }
+    s->ord_logits = logits_base;
+    s->ord_base = order_base;
+    s->ord_rows = n_rows;
+    s->ord_vocab = vocab;
+    return DFL_OK;
+}
 void dfl_sampler_get_config(const dfl_sampler* s, dfl_sampling_config* out) { if (s && out) *out = s->cfg; }
 uint64_t dfl_sampler_draws(const dfl_sampler* s) { return s ? s->draws : 0; }
 void dfl_sampler_rng_state(const dfl_sampler* s, uint64_t out_state[4]) {
