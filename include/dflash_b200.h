@@ -167,6 +167,9 @@ dfl_status dfl_qmatrix_create(int32_t device, int32_t dtype, uint64_t n_in, uint
                               const void* data, uint64_t n_bytes, int32_t on_device,
                               dfl_qmatrix** out);
 void dfl_qmatrix_destroy(dfl_qmatrix* m);
+/* Which kernel serves this matrix: 2 the tcgen05 / tensor-memory few-row GEMM (Q4_K, Q5_K, Q6_K, bf16, and Q8_0 whose
+ * block scales are finite and at most 256 in magnitude), 1 the mma.sync few-row GEMM, 0 the f32 small-matrix kernel. */
+int32_t dfl_qmatrix_engine(const dfl_qmatrix* m);
 /* Decode the resident (re-tiled) matrix back to f32 [n_out][n_in] on the host:
  * proves the integer unpack equals ggml's (codec.rs:287 dequant_to_f32). */
 dfl_status dfl_qmatrix_dequant(const dfl_qmatrix* m, float* out_host, uint64_t n_floats);

@@ -158,6 +158,11 @@ class QMatrix:
         except Exception:
             pass
 
+    @property
+    def engine(self):
+        """'tcgen05' | 'mma.sync' | 'f32' (dfl_qmatrix_engine)."""
+        return {2: "tcgen05", 1: "mma.sync", 0: "f32"}[int(lib().dfl_qmatrix_engine(self.h))]
+
     def dequant(self):
         out = np.zeros((self.n_out, self.n_in), dtype=np.float32)
         check(lib().dfl_qmatrix_dequant(self.h, _ptr(out), C.c_uint64(out.size)))

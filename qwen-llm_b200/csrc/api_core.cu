@@ -150,11 +150,22 @@ dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, 
         return fail(DFL_ERR_OOM, std::string("qmatrix: cudaMalloc: ") + cudaGetErrorString(e));
     }
     m->layout = (allow_ts && ts_supported(dtype)) ? LAYOUT_TS : LAYOUT_FRAG;
+    if (m->layout == LAYOUT_TS && dtype == DFL_Q8_0) {   // its scales are folded into the f16 operand: they have to leave room for q
+        bool fits = false;
+        const dfl_status fs = q80_scales_fit_ts(st, src, n_in, n_out, &fits);
+        if (fs != DFL_OK) {
+            if (tmp) cudaFree(tmp);
+            cudaFree(m->tiles);
+            m->tiles = nullptr;
+            return fs;
+        }
+        if (!fits) m->layout = LAYOUT_FRAG;
+    }
     if (kb_group > 0 && m->layout != LAYOUT_TS) {
         if (tmp) cudaFree(tmp);
         cudaFree(m->tiles);
         m->tiles = nullptr;
-        return fail(DFL_ERR_UNSUPPORTED, "qmatrix: expert-grouped matrices need the tensor-memory GEMM (Q4_K / Q5_K / Q6_K)");
+        return fail(DFL_ERR_UNSUPPORTED, "qmatrix: expert-grouped matrices need the tensor-memory GEMM (Q4_K / Q5_K / Q6_K / Q8_0 with scales in range)");
     }
     dfl_status s = m->layout == LAYOUT_TS ? retile_matrix_ts(st, dtype, src, n_in, n_out, m->tiles, kb_group)
                                           : retile_matrix(st, dtype, src, n_in, n_out, m->tiles);
@@ -228,6 +239,11 @@ void dfl_qmatrix_destroy(dfl_qmatrix* m) {
     if (!m) return;
     qmatrix_release(&m->m);
     delete m;
+}
+
+int32_t dfl_qmatrix_engine(const dfl_qmatrix* m) {
+    if (!m || m->m.dtype == DFL_F32) return 0;
+    return m->m.layout == LAYOUT_TS ? 2 : 1;
 }
 
 dfl_status dfl_qmatrix_dequant(const dfl_qmatrix* m, float* out_host, uint64_t n_floats) {

@@ -31,6 +31,9 @@ namespace dfl {
 __device__ __forceinline__ uint64_t src_block_index(uint64_t row, int kb, int kblocks, uint64_t n_out, int kb_group);
 __global__ void retile_ts_q6k_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks, int kb_group);
 __device__ float decode_ts_q6k_elem(const uint8_t* stage, int r, int k);
+__global__ void retile_ts_q80_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_out, int kblocks, int kb_group);
+__device__ float decode_ts_q80_elem(const uint8_t* stage, int r, int k);
+__global__ void q80_scale_range_kernel(const uint8_t* __restrict__ src, uint64_t n_blocks, int* flag);
 __global__ void retile_tsb_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n_in, uint64_t n_out, int kblocks);
 __device__ float decode_tsb_elem(const uint8_t* stage, int r, int k);
 
@@ -106,6 +109,7 @@ dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev,
         case DFL_Q4_K: retile_ts_kernel<DFL_Q4_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks, kb_group); break;
         case DFL_Q5_K: retile_ts_kernel<DFL_Q5_K><<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks, kb_group); break;
         case DFL_Q6_K: retile_ts_q6k_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks, kb_group); break;
+        case DFL_Q8_0: retile_ts_q80_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_out, kblocks, kb_group); break;
         case DFL_BF16:
             if (kb_group > 0) return fail(DFL_ERR_UNSUPPORTED, "retile: grouped column blocks are not built for bf16");
             retile_tsb_kernel<<<grid, block, 0, st>>>(ggml_dev, dst_tiles, n_in, n_out, kblocks);
@@ -143,10 +147,29 @@ __global__ void decode_tiles_ts_kernel(const uint8_t* __restrict__ tiles, int dt
         v = __fsub_rn(__fmul_rn(d * (float)sc, (float)q), dmin * (float)m);
     } else if (dtype == DFL_Q6_K) {
         v = decode_ts_q6k_elem(stage, r, k);
+    } else if (dtype == DFL_Q8_0) {
+        v = decode_ts_q80_elem(stage, r, k);
     } else if (dtype == DFL_BF16) {
         v = decode_tsb_elem(stage, r, k);
     }
     out[idx] = v;
+}
+
+// Whether every block scale of a Q8_0 matrix (ggml bytes on the device) leaves q * d inside the f16 range.
+dfl_status q80_scales_fit_ts(cudaStream_t st, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, bool* fits) {
+    int* flag = nullptr;
+    DFL_CUDA(cudaMalloc(&flag, sizeof(int)));
+    cudaMemsetAsync(flag, 0, sizeof(int), st);
+    const uint64_t n_blocks = n_in / 32 * n_out;
+    q80_scale_range_kernel<<<(unsigned)((n_blocks + 255) / 256), 256, 0, st>>>(ggml_dev, n_blocks, flag);
+    count_launch();
+    int h = 1;
+    cudaError_t e = cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(flag);
+    if (e != cudaSuccess) return fail(DFL_ERR_CUDA, std::string("q80 scale range: ") + cudaGetErrorString(e));
+    *fits = h == 0;
+    return DFL_OK;
 }
 
 dfl_status decode_tiles_ts(cudaStream_t st, const QMatrix& m, float* out_dev) {
@@ -318,5 +341,6 @@ struct Fmt<DFL_Q5_K> : FmtK45<DFL_Q5_K> {};
 }  // namespace dfl
 
 #include "gemm_ts_q6k.cuh"
+#include "gemm_ts_q80.cuh"
 #include "gemm_tsb.cuh"
 #include "gemm_ts_kernel.cuh"

@@ -10,6 +10,7 @@
 //   Q5_K: as Q4_K, then [half 2][row 128][16 B of qh]
 //   Q6_K: [128 x 16 B scales i8] [128 x f16 d] [unit 2][kp 4][row 128][16 B nibbles]
 //         [unit 2][kp 4][row 128][8 B of 2-bit high parts]
+//   Q8_0: [128 x 8 f16 d] [block 8][half 2][row 128][16 B of q + 128]
 //
 // Activation chunk per 256 columns (ACT_TS): the canonical K-major, no-swizzle operand layout of
 // tcgen05.mma: core matrices of 8 rows (n) x 16 bytes (8 halfs along k), the four n-groups of a
@@ -41,7 +42,10 @@ __host__ __device__ inline int ts_act_kpos(int k) { return (k & ~3) + (((k & 1) 
 __host__ __device__ inline int ts_b_offset(int n, int kpos) { return (kpos >> 3) * 512 + (n >> 3) * 128 + (n & 7) * 16 + (kpos & 7) * 2; }
 __host__ __device__ inline int ts_bmin_offset(int n2, int j) { return TS_BMIN_OFF + (j >> 3) * 768 + (n2 >> 3) * 128 + (n2 & 7) * 16 + (j & 7) * 2; }
 
-inline bool ts_supported(int dtype) { return dtype == DFL_Q4_K || dtype == DFL_Q5_K || dtype == DFL_Q6_K || dtype == DFL_BF16; }
+// Q8_0 additionally needs its block scales inside a range (q80_scales_fit_ts)
+inline bool ts_supported(int dtype) {
+    return dtype == DFL_Q4_K || dtype == DFL_Q5_K || dtype == DFL_Q6_K || dtype == DFL_Q8_0 || dtype == DFL_BF16;
+}
 // bf16-weight operand (gemm_tsb.cuh): n = 3 * token + plane (x = b1 + b2 + b3), natural column order
 __host__ __device__ inline int tsb_b_offset(int n, int k) { return (k >> 3) * 768 + (n >> 3) * 128 + (n & 7) * 16 + (k & 7) * 2; }
 
@@ -97,6 +101,7 @@ __device__ __forceinline__ void pack_subsum_ts(uint8_t* chunk, int tok, int j, f
 dfl_status retile_matrix_ts(cudaStream_t st, int dtype, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, uint8_t* dst_tiles,
                             int kb_group = 0);
 dfl_status decode_tiles_ts(cudaStream_t st, const QMatrix& m, float* out_dev);
+dfl_status q80_scales_fit_ts(cudaStream_t st, const uint8_t* ggml_dev, uint64_t n_in, uint64_t n_out, bool* fits);
 dfl_status launch_prep_acts_ts(cudaStream_t st, const float* x, int ld, int n_rows, uint64_t k, float pre_scale, uint8_t* acts,
                                int* dev_err);
 dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts, float* out, int splits, const GemmEpilogue& ep,

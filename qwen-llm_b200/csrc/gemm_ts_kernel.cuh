@@ -473,6 +473,7 @@ dfl_status launch_gemm_ts(cudaStream_t st, const QMatrix& m, const uint8_t* acts
         case DFL_Q4_K: return ts::launch_t<DFL_Q4_K>(st, p, grid, pdl);
         case DFL_Q5_K: return ts::launch_t<DFL_Q5_K>(st, p, grid, pdl);
         case DFL_Q6_K: return ts::launch_t<DFL_Q6_K>(st, p, grid, pdl);
+        case DFL_Q8_0: return ts::launch_t<DFL_Q8_0>(st, p, grid, pdl);
         default: return fail(DFL_ERR_UNSUPPORTED, "gemm: weight dtype has no tensor-memory kernel");
     }
 }

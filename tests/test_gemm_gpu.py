@@ -78,6 +78,53 @@ def test_rows_do_not_depend_on_row_count(dtype, name):
     m.close()
 
 
+def q8_0_bytes(q, d):
+    """ggml Q8_0 rows from int8 codes q [n_out][n_in] and f16 block scales d [n_out][n_in / 32]"""
+    n_out, n_in = q.shape
+    blocks = np.zeros((n_out, n_in // 32, 34), dtype=np.uint8)
+    blocks[:, :, :2] = np.ascontiguousarray(d.astype(np.float16)).view(np.uint8).reshape(n_out, n_in // 32, 2)
+    blocks[:, :, 2:] = q.reshape(n_out, n_in // 32, 32).view(np.uint8)
+    return blocks.reshape(-1)
+
+
+@pytest.mark.parametrize("scales,engine", [([2.0 ** -24, 2.0 ** -20, 6.1e-5, 1e-3, 0.0371, 1.0], "tcgen05"), ([256.0, -256.0, 0.5, -3e-4], "tcgen05"),
+                                           ([300.0, 1.0], "mma.sync"), ([float("inf"), 1.0], "mma.sync")])
+def test_q8_0_scale_range_decides_the_engine_and_every_weight_stays_exact(scales, engine):
+    """The tensor-memory kernel folds a block's f16 scale into its operand as an exact pair of halfs; that holds for
+    subnormal scales and up to |d| = 256 (q * d inside the f16 range).  Matrices beyond it run the mma.sync kernel."""
+    rng = np.random.default_rng(31)
+    n_in, n_out = 512, 130
+    q = rng.integers(-128, 128, size=(n_out, n_in), dtype=np.int8)
+    q[0, :32] = -128
+    q[1, :32] = 127
+    d = rng.choice(np.array(scales, dtype=np.float16), size=(n_out, n_in // 32))
+    m = pkg.QMatrix(orc.Q8_0, n_in, n_out, q8_0_bytes(q, d))
+    assert m.engine == engine
+    if not np.all(np.isfinite(d.astype(np.float32))):
+        m.close()
+        return
+    wf = q.astype(np.float32) * np.repeat(d.astype(np.float32), 32, axis=1)
+    assert m.dequant().tobytes() == wf.tobytes()
+    for base in range(0, n_in, 16):
+        x = np.zeros((16, n_in), dtype=np.float32)
+        x[np.arange(16), base + np.arange(16)] = 1.0
+        # value equality: a zero code under a negative scale decodes to -0.0, while a sum of products starts from +0.0
+        assert np.array_equal(m.matmul(x), wf[:, base:base + 16].T), f"columns {base}..{base + 15}"
+    x = rng.standard_normal((16, n_in)).astype(np.float32)
+    exact = x.astype(np.float64) @ wf.astype(np.float64).T
+    bound = (np.abs(x).astype(np.float64) @ np.abs(wf).astype(np.float64).T) * (n_in * 2.0 ** -24) + 1e-30
+    assert np.all(np.abs(m.matmul(x) - exact) <= bound)
+    m.close()
+
+
+def test_engines_by_dtype():
+    for dtype, name in DTYPES:
+        raw, _ = make_weight(dtype, 256, 128, 1)
+        m = pkg.QMatrix(dtype, 256, 128, raw)
+        assert m.engine == "tcgen05", name
+        m.close()
+
+
 def test_bad_shapes_are_refused():
     raw, _ = make_weight(orc.Q4_K, 256, 128, 1)
     with pytest.raises(pkg.DflError) as e:
