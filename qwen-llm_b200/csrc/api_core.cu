@@ -144,22 +144,20 @@ dfl_status qmatrix_create(int device, int dtype, uint64_t n_in, uint64_t n_out, 
         DFL_CUDA(cudaMemcpyAsync(tmp, data, n_bytes, cudaMemcpyHostToDevice, st));
         src = tmp;
     }
-    cudaError_t e = cudaMalloc(&m->tiles, m->bytes());
-    if (e != cudaSuccess) {
-        if (tmp) cudaFree(tmp);
-        return fail(DFL_ERR_OOM, std::string("qmatrix: cudaMalloc: ") + cudaGetErrorString(e));
-    }
     m->layout = (allow_ts && ts_supported(dtype)) ? LAYOUT_TS : LAYOUT_FRAG;
     if (m->layout == LAYOUT_TS && dtype == DFL_Q8_0) {   // its scales are folded into the f16 operand: they have to leave room for q
         bool fits = false;
         const dfl_status fs = q80_scales_fit_ts(st, src, n_in, n_out, &fits);
         if (fs != DFL_OK) {
             if (tmp) cudaFree(tmp);
-            cudaFree(m->tiles);
-            m->tiles = nullptr;
             return fs;
         }
         if (!fits) m->layout = LAYOUT_FRAG;
+    }
+    cudaError_t e = cudaMalloc(&m->tiles, m->bytes());   // the layout decides the resident size
+    if (e != cudaSuccess) {
+        if (tmp) cudaFree(tmp);
+        return fail(DFL_ERR_OOM, std::string("qmatrix: cudaMalloc: ") + cudaGetErrorString(e));
     }
     if (kb_group > 0 && m->layout != LAYOUT_TS) {
         if (tmp) cudaFree(tmp);

@@ -130,7 +130,7 @@ __global__ void decode_tiles_ts_kernel(const uint8_t* __restrict__ tiles, int dt
     const int kb = kk >> 8, k = kk & 255;
     const uint64_t rt = row / TILE_R;
     const int r = (int)(row % TILE_R);
-    const uint8_t* stage = tiles + (rt * kblocks + kb) * (uint64_t)stage_bytes_of(dtype);
+    const uint8_t* stage = tiles + (rt * kblocks + kb) * (uint64_t)stage_bytes_of(dtype, LAYOUT_TS);
     float v = 0.f;
     if (dtype == DFL_Q4_K || dtype == DFL_Q5_K) {
         const uint8_t* h = stage + r * 16;

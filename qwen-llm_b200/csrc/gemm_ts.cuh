@@ -2,14 +2,14 @@
 // into exact f16 integers, stored into tensor memory as the A operand of tcgen05.mma, and the
 // packed activations are the B operand read from shared memory.
 //
-// Weight tiles ("row-lane" tiles, LAYOUT_TS): still [row_tile][k_block][stage bytes] with the
-// ggml byte counts, but ordered so that thread (row, kp) of the unpacking CTA - row = its
+// Weight tiles ("row-lane" tiles, LAYOUT_TS): still [row_tile][k_block][stage bytes], with the
+// ggml byte counts except for Q6_K, ordered so that thread (row, kp) of the unpacking CTA - row = its
 // tensor-memory lane, kp = its quarter of the 256 columns - finds its bytes with conflict-free
 // 128-bit shared-memory loads:
 //   Q4_K: [128 x 16 B header {d, dmin, scales[12]}] [kp 4][half 2][row 128][16 B of qs]
 //   Q5_K: as Q4_K, then [half 2][row 128][16 B of qh]
-//   Q6_K: [128 x 16 B scales i8] [128 x f16 d] [unit 2][kp 4][row 128][16 B nibbles]
-//         [unit 2][kp 4][row 128][8 B of 2-bit high parts]
+//   Q6_K: [128 x 16 B scales i8] [128 x f16 d] [block 8][half 2][row 128][16 B of six-bit codes, one per byte]
+//         (35072 bytes per stage instead of ggml's 26880: see gemm_ts_q6k.cuh)
 //   Q8_0: [128 x 8 f16 d] [block 8][half 2][row 128][16 B of q + 128]
 //
 // Activation chunk per 256 columns (ACT_TS): the canonical K-major, no-swizzle operand layout of
@@ -35,8 +35,7 @@ static_assert(ACTTS_CHUNK == TS_B_BYTES + TS_BMIN_BYTES, "activation chunk size"
 constexpr int TSQ4_OFF_QS = 2048;
 constexpr int TSQ5_OFF_QH = 2048 + 16384;
 constexpr int TSQ6_OFF_D = 2048;
-constexpr int TSQ6_OFF_NIB = 2304;
-constexpr int TSQ6_OFF_HI2 = 2304 + 16384;
+constexpr int TSQ6_OFF_QS = 2304;
 
 __host__ __device__ inline int ts_act_kpos(int k) { return (k & ~3) + (((k & 1) << 1) | ((k >> 1) & 1)); }
 __host__ __device__ inline int ts_b_offset(int n, int kpos) { return (kpos >> 3) * 512 + (n >> 3) * 128 + (n & 7) * 16 + (kpos & 7) * 2; }

@@ -40,10 +40,11 @@ struct Params {
 };
 
 constexpr int SCL_BYTES = 4 * TILE_R * 8;   // four entries' {d, dmin} per row
+constexpr int BAR_BYTES = 512;              // up to 64 mbarriers
 
 template <int DT>
 constexpr int smem_bytes() {
-    return KC * ACTTS_CHUNK + Fmt<DT>::STAGES * Fmt<DT>::STAGE + SCL_BYTES + 256;
+    return KC * ACTTS_CHUNK + Fmt<DT>::STAGES * Fmt<DT>::STAGE + SCL_BYTES + BAR_BYTES;
 }
 
 // named barrier among the draining warps only (every one of them reaches it unconditionally)
@@ -74,14 +75,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     constexpr int OFF_RING = KC * ACTTS_CHUNK;
     constexpr int OFF_SCL = OFF_RING + STAGES * F::STAGE;
     constexpr int OFF_BAR = OFF_SCL + SCL_BYTES;
-    static_assert(OFF_BAR + 256 <= 227 * 1024, "shared memory budget");
-    static_assert(2 * STAGES + KC + 12 <= 32, "barrier area");
+    // "Stage landed" barriers.  A parity wait is only meaningful to a waiter that knows the phase before is over, i.e. to
+    // the one party that waits on that barrier phase after phase.  With an even number of stages a ring slot always
+    // serves the same unpacking group; with an odd number its uses alternate between the two groups, and a group that
+    // ran ahead could take the other group's still outstanding copy for its own (copies complete out of order).  So with
+    // an odd number every slot has one barrier per group, each used by that group's uses of the slot only.
+    constexpr int FULL_SETS = (STAGES & 1) ? 2 : 1;
+    static_assert(OFF_BAR + BAR_BYTES <= 227 * 1024, "shared memory budget");
+    static_assert((FULL_SETS + 1) * STAGES + KC + 12 <= BAR_BYTES / 8, "barrier area");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* acts_res = smem;
     uint8_t* ring = smem + OFF_RING;
     float2* scl = reinterpret_cast<float2*>(smem + OFF_SCL);   // [entry & 3][row] = {d, dmin}
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-    uint64_t* empty = full + STAGES;
+    uint64_t* empty = full + FULL_SETS * STAGES;
+    auto full_bar = [](uint64_t* f, int e, int s) { return f + ((STAGES & 1) ? (e & 1) * STAGES : 0) + s; };
+    // use number of the barrier: every use of the slot (even), or every second one (odd: the group's own)
+    auto full_parity = [](int e) { return (uint32_t)((STAGES & 1) ? ((e / STAGES) >> 1) : (e / STAGES)) & 1u; };
     uint64_t* acts_bar = empty + STAGES;  // [column block of the CTA's range] its activations have arrived
     uint64_t* a_ready = acts_bar + KC;    // [group][half buffer] a half of unpacked weights is in tensor memory
     uint64_t* a_free = a_ready + 4;       // [group][half buffer] the MMAs of that half have completed
@@ -112,10 +122,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     const int n_it = n_my * n_kb;            // entries
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], GROUP_WARPS);
-        }
+        for (int s = 0; s < FULL_SETS * STAGES; ++s) mbar_init(&full[s], 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(&empty[s], GROUP_WARPS);
         for (int k = 0; k < KC; ++k) mbar_init(&acts_bar[k], 1);
         for (int i = 0; i < 4; ++i) {
             mbar_init(&a_ready[i], GROUP_WARPS);
@@ -155,8 +163,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
                     src = p.w + (uint64_t)(p.tile_map ? p.tile_map[slot] : slot) * tile_stride +
                           (uint64_t)(p.kb_map ? p.kb_map[kb0 + pk] : kb0 + pk) * F::STAGE;
                 }
-                mbar_arrive_expect_tx(&full[s], F::STAGE);
-                bulk_g2s(ring + s * F::STAGE, src, F::STAGE, &full[s]);
+                uint64_t* fb = full_bar(full, e, s);
+                mbar_arrive_expect_tx(fb, F::STAGE);
+                bulk_g2s(ring + s * F::STAGE, src, F::STAGE, fb);
                 src += F::STAGE;
                 if (++s == STAGES) { s = 0; ++round; }
                 if (++pk == n_kb) {   // next row tile of this CTA: cps tiles further, back to the first column block
@@ -231,7 +240,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
         uint32_t hc = 0;   // running half count of this group
         for (int e = g; e < n_it && ok; e += 2) {
             const int s = e % STAGES;
-            ok = mbar_wait_bounded(&full[s], (e / STAGES) & 1, p.err, DEV_ERR_WAIT_FULL);
+            ok = mbar_wait_bounded(full_bar(full, e, s), full_parity(e), p.err, DEV_ERR_WAIT_FULL);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint8_t* st = ring + s * F::STAGE;
@@ -358,7 +367,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_ts_kernel(const Params p) {
     if (abort_flag && threadIdx.x == 0) {
         // Error word already set.  Give every copy this CTA armed a bounded chance to land before
         // the shared memory is released.
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < FULL_SETS * STAGES; ++s) {
             uint32_t spins = 0;
             while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && ++spins < (1u << 16)) __nanosleep(100);
         }

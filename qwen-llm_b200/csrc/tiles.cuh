@@ -87,6 +87,11 @@ __host__ __device__ inline bool dtype_uses_bf16_acts(int dtype) { return dtype =
 // row-lane tiles for the tensor-memory kernel (gemm_ts.cuh).  The packed activation format
 // follows the kernel that consumes it.
 constexpr int LAYOUT_FRAG = 0, LAYOUT_TS = 1;
+// Q6_K row-lane tiles hold one code per byte: [128 x 16 i8 scales][128 x f16 d][128 rows x 256 bytes]
+constexpr int STAGE_Q6_K_TS = 2304 + TILE_R * 256;  // 35072
+__host__ __device__ inline int stage_bytes_of(int dtype, int layout) {
+    return (dtype == DFL_Q6_K && layout == LAYOUT_TS) ? STAGE_Q6_K_TS : stage_bytes_of(dtype);
+}
 constexpr int ACT_F16 = 0, ACT_BF3 = 1, ACT_TS = 2, ACT_TSB = 3;
 constexpr int ACTTS_CHUNK = 16384 + 1536;  // tensor-memory kernel: B operand + min-term operand per 256 columns
 constexpr int ACTTSB_CHUNK = 32 * 768;     // bf16-weight tensor-core kernel: three bf16 planes as one 48-row B operand
@@ -168,7 +173,7 @@ struct QMatrix {
     int row_tiles = 0;  // ceil(n_out / 128)
     uint8_t* tiles = nullptr;  // device, [row_tiles][kblocks][stage bytes]; f32 matrices: plain [n_out][n_in]
     bool owns = true;
-    uint64_t bytes() const { return (uint64_t)row_tiles * kblocks * stage_bytes_of(dtype); }
+    uint64_t bytes() const { return (uint64_t)row_tiles * kblocks * stage_bytes_of(dtype, layout); }   // resident bytes: set layout first
     // bytes of the ggml source (what a roofline should count)
     uint64_t ggml_bytes() const { return n_out * (uint64_t)kblocks * ggml_bytes_per_256(dtype); }
 };

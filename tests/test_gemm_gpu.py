@@ -117,6 +117,34 @@ def test_q8_0_scale_range_decides_the_engine_and_every_weight_stays_exact(scales
     m.close()
 
 
+@pytest.mark.parametrize("dtype,name,n_in,n_out", [(orc.Q6_K, "q6_k", 4096, 151936), (orc.Q8_0, "q8_0", 4096, 32768), (orc.Q5_K, "q5_k", 4096, 32768),
+                                                   (orc.Q4_K, "q4_k", 4096, 32768)])
+def test_repeated_launches_on_a_large_cold_matrix_give_the_same_bits(dtype, name, n_in, n_out):
+    """The weight ring's "stage landed" barriers are per unpacking group when the stage count is odd (Q5_K, Q6_K, Q8_0):
+    bulk copies complete out of order, and on a shared barrier a group that ran ahead once took the other group's
+    outstanding copy for its own - one wrong row tile in the first, cold launch on a matrix of this size."""
+    rng = np.random.default_rng(7)
+    blk = {orc.Q4_K: 144, orc.Q5_K: 176, orc.Q6_K: 210, orc.Q8_0: 272}[dtype]
+    nb = n_out * (n_in // 256)
+    b = rng.integers(0, 256, size=(nb, blk), dtype=np.uint8)
+    d = np.full(nb, 1e-4, dtype=np.float16).view(np.uint8).reshape(nb, 2)   # sane f16 block scales over random codes
+    if dtype == orc.Q6_K:
+        b[:, 208:210] = d
+    elif dtype == orc.Q8_0:
+        for j in range(8):
+            b[:, 34 * j:34 * j + 2] = d
+    else:
+        b[:, 0:2] = d
+        b[:, 2:4] = d
+    m = pkg.QMatrix(dtype, n_in, n_out, b.reshape(-1))
+    assert m.engine == "tcgen05"
+    x = (rng.standard_normal((16, n_in)) * 0.1).astype(np.float32)
+    first = m.matmul(x)
+    for _ in range(40):
+        assert m.matmul(x).tobytes() == first.tobytes()
+    m.close()
+
+
 def test_engines_by_dtype():
     for dtype, name in DTYPES:
         raw, _ = make_weight(dtype, 256, 128, 1)
