@@ -306,6 +306,7 @@ def run(args, rank, world, device):
         n_attn = sum(1 for il in range(w.arch.n_layer) if _syn().is_attn(w.arch, il))
         kv_bytes = n_attn * long_ctx * 2 * w.arch.n_kv_heads * w.arch.attn_head_dim * 2
     vbytes += kv_bytes
+    rbytes = w.model.verify_resident_bytes() + kv_bytes   # what the step streams from HBM: Q6_K tiles hold a byte per code
     verify_ms = head["verify_ms"] / steps
     draft_ms = head["draft_ms"] / steps
     gemm_gbs = gemm_bytes / (gemm_ms * 1e-3) / 1e9 if gemm_ms > 0 else 0.0
@@ -318,10 +319,11 @@ def run(args, rank, world, device):
                                 "replayed drafts accept 3,3,4,3,4 per step (4.4 emitted/step), drafter runs every step") if long_ctx else WORKLOAD_C2,
                    "l2": "5.1 GB of weights per verify >> 126 MB L2", "parallelism": f"dp{world}: one independent sequence per GPU, no collective"},
         # the unit of the roofline is one packed verify step: the quantised weight bytes it streams once (algorithmic bytes)
-        # over its CUDA-event time, all kernels of the step included.  traffic: algorithmic bytes x 1.04, the DRAM-bytes /
-        # weight-bytes ratio an ncu capture of the dominant kernel showed on a smaller case (traffic grows with the bytes)
+        # over its CUDA-event time, all kernels of the step included.  traffic: resident bytes x 1.04, the DRAM-bytes /
+        # tile-bytes ratio an ncu capture of the dominant kernel showed on a smaller case (traffic grows with the bytes);
+        # resident bytes exceed the algorithmic (ggml) bytes because Q6_K tiles hold one six-bit code per byte
         "roofline": {"bound": "hbm", "achieved": vbytes / (verify_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": vbytes / (verify_ms * 1e-3) / 1e9 / peak, "traffic": 1.04 * vbytes, "peak_kind": peak_kind,
+                     "frac": vbytes / (verify_ms * 1e-3) / 1e9 / peak, "traffic": 1.04 * rbytes, "resident_bytes": rbytes, "peak_kind": peak_kind,
                      "unit_of_work": "one packed verify step (16 rows through the 32-layer target and the lm_head), every kernel of the step",
                      "algorithmic_bytes": vbytes, "ms": verify_ms, "kernel": "gemm_ts_kernel<Q4_K | Q5_K | Q6_K> (the step's dominant kernel)",
                      "gemm_launches_only": {"GBps": gemm_gbs, "frac": gemm_gbs / peak, "launches_timed": gemm_n, "algorithmic_bytes_timed": gemm_bytes,

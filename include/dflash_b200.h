@@ -233,6 +233,9 @@ dfl_status dfl_model_create(int32_t device, const dfl_arch* arch, const dfl_tens
 void dfl_model_destroy(dfl_model* m);
 /* Bytes of quantised weights one verify step streams (the roofline numerator). */
 uint64_t dfl_model_verify_weight_bytes(const dfl_model* m);
+/* The same matrices counted as they are resident in HBM: equal to the above except that Q6_K tiles of the
+ * tensor-memory GEMM hold one six-bit code per byte (274 bytes per 256 weights against ggml's 210). */
+uint64_t dfl_model_verify_resident_bytes(const dfl_model* m);
 /* Expert parallelism for routed-expert models (one process per GPU of one node).
  * Rank r of ep_world keeps experts [r*E/ep_world, (r+1)*E/ep_world) of every layer
  * (rank 0 also the shared expert), everything else is replicated.  Each

@@ -99,7 +99,7 @@ def lib():
         L.dfl_last_error.restype = C.c_char_p
         L.dfl_device_count.restype = C.c_int32
         L.dfl_launch_count.restype = C.c_uint64
-        for name in ("dfl_model_verify_weight_bytes", "dfl_drafter_weight_bytes", "dfl_sampler_draws", "dfl_sampler_preordered_rows",
+        for name in ("dfl_model_verify_weight_bytes", "dfl_model_verify_resident_bytes", "dfl_drafter_weight_bytes", "dfl_sampler_draws", "dfl_sampler_preordered_rows",
                      "dfl_splitmix64_next", "dfl_sampler_next_u64"):
             if hasattr(L, name):
                 getattr(L, name).restype = C.c_uint64
@@ -292,6 +292,9 @@ class Model:
 
     def verify_weight_bytes(self):
         return int(lib().dfl_model_verify_weight_bytes(self.h))
+
+    def verify_resident_bytes(self):
+        return int(lib().dfl_model_verify_resident_bytes(self.h))
 
     def close(self):
         if self.h:

@@ -492,6 +492,7 @@ static dfl_status model_create_impl(int32_t device, const dfl_arch* arch, const 
         MC(build_group(device, st, tm, {head_name}, H, {V}, &m->lm_head, allow_ts));
         MC(upload_f32(device, st, tm, "output_norm.weight", H, &m->out_norm_w));
         m->verify_weight_bytes = m->lm_head.ggml_bytes();
+        m->verify_resident_bytes = m->lm_head.bytes();
     }
     m->layers.resize(a.n_layer);
     for (uint32_t il = 0; il < a.n_layer; ++il) {
@@ -507,6 +508,7 @@ static dfl_status model_create_impl(int32_t device, const dfl_arch* arch, const 
             MC(upload_f32(device, st, tm, blk(il, "attn_q_norm.weight"), hd, &L.q_norm_w));
             MC(upload_f32(device, st, tm, blk(il, "attn_k_norm.weight"), hd, &L.k_norm_w));
             m->verify_weight_bytes += L.qkv.ggml_bytes() + L.wo.ggml_bytes();
+            m->verify_resident_bytes += L.qkv.bytes() + L.wo.bytes();
         } else {
             ++m->n_gdn;
             MC(build_group(device, st, tm, {blk(il, "attn_qkv.weight"), blk(il, "attn_gate.weight")}, H, {conv_dim, v_dim}, &L.in_qkv_z, allow_ts));
@@ -527,6 +529,7 @@ static dfl_status model_create_impl(int32_t device, const dfl_arch* arch, const 
             MC(upload_f32(device, st, tm, blk(il, "ssm_conv1d.weight"), conv_dim * 4, &L.conv_w));
             MC(upload_f32(device, st, tm, blk(il, "ssm_norm.weight"), 128, &L.ssm_norm_w));
             m->verify_weight_bytes += L.in_qkv_z.ggml_bytes() + L.w_out.ggml_bytes() + 2 * H * a.gdn_n_v_heads * 4;
+            m->verify_resident_bytes += L.in_qkv_z.bytes() + L.w_out.bytes() + 2 * H * a.gdn_n_v_heads * 4;
         }
         if (a.expert_count > 0) {
             // forward.rs:749-824; tensor shapes as in loader.rs (experts stacked along the last ggml dimension)
@@ -567,10 +570,12 @@ static dfl_status model_create_impl(int32_t device, const dfl_arch* arch, const 
                 cudaFree(sgw);
             }
             m->verify_weight_bytes += L.moe_gate_up.ggml_bytes() + L.moe_down.ggml_bytes() + L.moe_down_sh.ggml_bytes() + (E + 1) * H * 4;
+            m->verify_resident_bytes += L.moe_gate_up.bytes() + L.moe_down.bytes() + L.moe_down_sh.bytes() + (E + 1) * H * 4;
         } else {
             MC(build_group(device, st, tm, {blk(il, "ffn_gate.weight"), blk(il, "ffn_up.weight")}, H, {F, F}, &L.gate_up, allow_ts));
             MC(build_group(device, st, tm, {blk(il, "ffn_down.weight")}, F, {H}, &L.down, allow_ts));
             m->verify_weight_bytes += L.gate_up.ggml_bytes() + L.down.ggml_bytes();
+            m->verify_resident_bytes += L.gate_up.bytes() + L.down.bytes();
         }
     }
 #undef MC
@@ -655,6 +660,7 @@ void dfl_model_destroy(dfl_model* m) {
 }
 
 uint64_t dfl_model_verify_weight_bytes(const dfl_model* m) { return m ? m->verify_weight_bytes : 0; }
+uint64_t dfl_model_verify_resident_bytes(const dfl_model* m) { return m ? m->verify_resident_bytes : 0; }
 
 dfl_status dfl_session_create(const dfl_model* m, uint32_t kv_capacity, int32_t kv_f16, dfl_session** out) {
     if (!m || !out) return fail(DFL_ERR_BAD_ARG, "session_create: null argument");

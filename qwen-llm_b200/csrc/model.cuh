@@ -28,6 +28,7 @@ struct MatGroup {
     uint64_t n_in = 0;
     int splits = 1;
     uint64_t ggml_bytes() const { uint64_t b = 0; for (auto& m : mats) b += m.ggml_bytes(); return b; }
+    uint64_t bytes() const { uint64_t b = 0; for (auto& m : mats) b += m.bytes(); return b; }   // as resident in HBM
     void release() { for (auto& m : mats) qmatrix_release(&m); mats.clear(); }
 };
 dfl_status launch_group(cudaStream_t st, const MatGroup& g, const uint8_t* acts, float* part, const GemmEpilogue& ep, int* err);
@@ -123,7 +124,8 @@ struct dfl_model {
     int embd_dtype = 0;
     dfl::MatGroup lm_head;
     float* out_norm_w = nullptr;
-    uint64_t verify_weight_bytes = 0;
+    uint64_t verify_weight_bytes = 0;     // ggml bytes one verify pass touches
+    uint64_t verify_resident_bytes = 0;   // the same matrices as they are resident (Q6_K tiles hold a byte per code)
     std::vector<void*> allocs;
     int n_gdn = 0, n_attn = 0;
     dfl::AttnGeom attn_geom() const {
