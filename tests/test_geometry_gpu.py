@@ -218,3 +218,29 @@ def test_drafter_at_dense_9b_widths_matches_oracle():
                                         "rows": 16, "near_tie_rows": int((~safe).sum()), "min_cos": float(cos.min())})
     for x in (sess, scr, ds, gd, gm):
         x.close()
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_a_repeated_verify_from_the_same_state_gives_the_same_bits(moe):
+    """One packed verify repeated from the same session state, at the benchmark widths (every weight format and ring
+    depth of the few-row GEMM, the 151 936-row head included): logits and captured rows must not change by a bit.
+    This is the check that caught a group of the GEMM taking the other group's outstanding weight copy for its own."""
+    arch = _slice_arch(syn.arch_35b_a3b(), 2, 2) if moe else _slice_arch(syn.arch_9b(), 4, 4)
+    ents = syn.target_entries(arch, seed=47, device=0)
+    gm = syn.build_model(arch, ents)
+    syn.free_entries(ents)
+    layer_ids = [0, 1] if moe else [0, 1, 2, 3]
+    sess, scr = pkg.Session(gm, 256, True), pkg.Scratch(gm, 16, len(layer_ids))
+    rng = np.random.default_rng(6)
+    pkg.packed_verify(gm, sess, scr, layer_ids, rng.integers(0, arch.vocab_size, size=16), 0)
+    pos = sess.kv_n_pos
+    toks = rng.integers(0, arch.vocab_size, size=16)
+    first = None
+    for _ in range(60):
+        am, gap, logits = pkg.packed_verify(gm, sess, scr, layer_ids, toks, pos, want_logits=True)
+        got = (logits.tobytes(), scr.read_capture(16).tobytes(), am.tobytes())
+        if first is None:
+            first = got
+        assert got == first
+        pkg.restore_pre_block(gm, sess, scr, pos)
+    sess.close(); scr.close(); gm.close()
