@@ -445,11 +445,14 @@ def run_verify_only(args, rank, world, device):
 # ---------------------------------------------------------------------------
 C3_SEQS, C3_PROMPT, C3_T, C3_TOP_P, C3_SEED, C3_KV = 32, 1024, 0.7, 0.95, 0xC3, 2048
 C3_THREADS = int(os.environ.get("DFL_C3_THREADS", "4"))   # host threads driving a rank's sequences in the end-to-end pass
-# End-to-end pass on a host whose cores are all taken by driving threads (ranks x threads >= cores): the verify rows are
-# ordered on the device (the host sampler then skips its sort, 45 % of its work per row) and the driving threads block
-# instead of spinning while they wait for the GPU.  On a host with cores to spare both cost more than they give (the
-# sort and the second 9.7 MB copy are GPU time, a blocked thread wakes up late), so the rule is applied per launch:
-# DFL_C3_HOST_OFFLOAD=auto (default) | 1 | 0.  The device-timed pass always runs the plain path.
+# End-to-end pass on a host with few cores per driving thread (cores / (ranks x threads)).  Three switches, each "auto" by
+# default and decided per launch from that ratio; the device-timed pass always runs the plain path:
+#   DFL_C3_WAIT     block | spin   driving threads block instead of spinning while they wait for the GPU
+#   DFL_C3_WORKERS  n              threads the sampler may use to build a block's rows ahead of its loop (1 = none)
+#   DFL_C3_HOST_OFFLOAD  1 | 0     verify rows ordered on the device (the sampler then skips its sort, 45 % of its
+#                                  work per row, for 0.5 ms of GPU time per step)
+C3_WAIT = os.environ.get("DFL_C3_WAIT", "auto")
+C3_WORKERS = os.environ.get("DFL_C3_WORKERS", "auto")
 C3_HOST_OFFLOAD = os.environ.get("DFL_C3_HOST_OFFLOAD", "auto")
 
 
@@ -559,8 +562,14 @@ def run_c3(args, rank, world, device):
     n_done = n_b - 1           # tokens emitted by the device-timed pass, after the n_a of the warm-up
     n_c = tokens_for_steps(PATTERN, warm + steps, steps)
     threads = max(1, min(C3_THREADS, len(seqs)))
-    offload = C3_HOST_OFFLOAD == "1" or (C3_HOST_OFFLOAD == "auto" and world * threads >= (os.cpu_count() or 1))
-    if offload:
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    per_driver = cores / float(world * threads)          # host cores per driving thread
+    scarce = per_driver < 2.0
+    offload = C3_HOST_OFFLOAD == "1" or (C3_HOST_OFFLOAD == "auto" and scarce)
+    workers = int(C3_WORKERS) if C3_WORKERS != "auto" else (0 if per_driver >= 6 else max(1, int(per_driver)))
+    # spinning waits are the faster ones as long as every thread has a core of its own
+    block = C3_WAIT == "block" or (C3_WAIT == "auto" and world * threads * (workers or 6) > cores)
+    if block:
         pkg.set_host_wait("block")
     scratches = [w.scr] + [pkg.Scratch(w.model, 16, len(w.layer_ids)) for _ in range(threads - 1)]
     errors, emitted_e2e = [], [0] * threads
@@ -569,7 +578,9 @@ def run_c3(args, rank, world, device):
         try:
             for q, (cont, hist, n_a, last) in list(zip(seqs, state))[ti::threads]:
                 at = n_a - 1 + n_done
-                toks_c, st = pkg.generate(w.model, q.sess, scratches[ti], q.ds, q.sampler(at_draw=at), forced(V, int(cont[at])), n_c,
+                smp = q.sampler(at_draw=at)
+                smp.set_worker_threads(workers)
+                toks_c, st = pkg.generate(w.model, q.sess, scratches[ti], q.ds, smp, forced(V, int(cont[at])), n_c,
                                           replay_history=hist[at:], replay_runs_drafter=True, replay_unchecked=True,
                                           device_row_order=offload)
                 assert np.array_equal(toks_c, cont[at:at + n_c]), "end-to-end output differs from the plain sampled continuation"
@@ -587,7 +598,7 @@ def run_c3(args, rank, world, device):
         t.join()
     torch.cuda.synchronize(device)
     wall_ms = (time.perf_counter() - t0) * 1e3
-    if offload:
+    if block:
         pkg.set_host_wait("auto")
     if errors:
         raise errors[0]
@@ -618,7 +629,8 @@ def run_c3(args, rank, world, device):
                      "kernel": "one packed verify (all kernels), weight bytes / CUDA-event time"},
         "e2e": {"value": emitted_wall / (wall_max * 1e-3), "unit": bench.UNIT, "h2d_bytes_per_step": len(seqs) * 2 * 16 * 4,
                 "d2h_bytes_per_step": len(seqs) * (16 * V * 4 * (2 if offload else 1) + 3 * 16 * 4),
-                "host_offload": "verify rows ordered on the device, driving threads block while waiting" if offload else "off (cores to spare)", "host_threads": threads,
+                "host_policy": {"cores_per_driving_thread": per_driver, "wait": "block" if block else "spin",
+                                "sampler_worker_threads": workers or "host concurrency", "row_order": "device" if offload else "host"}, "host_threads": threads,
                 "one_thread_tok_per_s": tot["emitted"] / (wall_serial_ms * 1e-3)},
         "gpu_launches": int(launches), "clocks": clocks,
         "per_outer_step_ms": {"draft": tot["draft_ms"] / n_steps_rank, "verify": verify_ms, "restore": tot["restore_ms"] / n_steps_rank,

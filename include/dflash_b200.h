@@ -529,6 +529,11 @@ void dfl_sampler_rng_state(const dfl_sampler* s, uint64_t out_state[4]);
  * registration.  The caller keeps both arrays alive while registered. */
 dfl_status dfl_sampler_set_row_order(dfl_sampler* s, const float* logits_base, const uint32_t* order_base,
                                      uint32_t n_rows, uint64_t vocab);
+/* Host threads dfl_accept_prefix may use to build a block's row distributions ahead of its sequential loop (the picks
+ * stay sequential, so nothing drawn or decided changes): 0 = as many as the host reports, 1 = none - every row is built
+ * by the calling thread when the loop reaches it, which is the right choice when every core already drives a sequence -
+ * n > 1 = at most n. */
+dfl_status dfl_sampler_set_worker_threads(dfl_sampler* s, uint32_t n);
 /* Rows that took a registered order since the sampler was created (rows whose order was refused are not counted). */
 uint64_t dfl_sampler_preordered_rows(const dfl_sampler* s);
 /* Sampler::sample  sampling.rs:530 */

@@ -483,6 +483,10 @@ class Sampler:
     def draws(self):
         return int(lib().dfl_sampler_draws(self.h))
 
+    def set_worker_threads(self, n):
+        """0: as many row-building threads as the host reports; 1: none (rows built on demand); n: at most n."""
+        check(lib().dfl_sampler_set_worker_threads(self.h, C.c_uint32(n)))
+
     @property
     def preordered_rows(self):
         return int(lib().dfl_sampler_preordered_rows(self.h))

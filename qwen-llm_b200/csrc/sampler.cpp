@@ -179,6 +179,7 @@ struct dfl_sampler {
     uint32_t ord_rows = 0;
     uint64_t ord_vocab = 0;
     mutable std::atomic<uint64_t> ord_used{0};   // rows that took a registered order (rows are built on several threads)
+    uint32_t workers = 0;   // threads that build a block's rows ahead of the accept loop: 0 = the host's concurrency, 1 = none
     const uint32_t* order_for(const float* logits, uint64_t n) const {
         if (!ord_logits || n != ord_vocab || logits < ord_logits) return nullptr;
         const uint64_t off = (uint64_t)(logits - ord_logits);
@@ -193,15 +194,16 @@ struct dfl_sampler {
     void prepare_rows(const float* logits, uint32_t n_rows, uint64_t vocab) {
         block_logits = nullptr;
         n_prepared = block_rows = 0;
-        if (cfg.temperature == 0.0f || n_rows < 2 || vocab < 4096 || std::thread::hardware_concurrency() < 2) return;
+        if (cfg.temperature == 0.0f || n_rows < 2 || vocab < 4096 || worker_limit() < 2) return;
         block_logits = logits;
         block_vocab = vocab;
         block_rows = n_rows;
         if (prepared.size() < n_rows) prepared.resize(n_rows);
     }
     void end_block() { block_logits = nullptr; n_prepared = block_rows = 0; }
+    unsigned worker_limit() const { return workers ? workers : std::thread::hardware_concurrency(); }
     void prepare_wave(uint32_t upto) {
-        const unsigned hw = std::max(2u, std::thread::hardware_concurrency());
+        const unsigned hw = std::max(2u, worker_limit());
         const uint32_t first = n_prepared, last = std::min(block_rows, std::max(upto + 1, first + std::min<uint32_t>(hw, first == 0 ? 6 : 10)));
         const uint32_t n_threads = std::min<uint32_t>(last - first, hw);
         auto work = [&](uint32_t t) {
@@ -455,6 +457,12 @@ dfl_status dfl_sampler_create_at_draw(const dfl_sampling_config* cfg, uint64_t d
     return DFL_OK;
 }
 void dfl_sampler_destroy(dfl_sampler* s) { delete s; }
+
+dfl_status dfl_sampler_set_worker_threads(dfl_sampler* s, uint32_t n) {
+    if (!s) return DFL_ERR_BAD_ARG;
+    s->workers = n;
+    return DFL_OK;
+}
 
 uint64_t dfl_sampler_preordered_rows(const dfl_sampler* s) { return s ? s->ord_used.load(std::memory_order_relaxed) : 0; }
 

@@ -118,3 +118,19 @@ def test_host_wait_policy_argument_check():
         pkg.set_host_wait(mode)
     with pytest.raises(pkg.DflError):
         pkg.check(pkg.lib().dfl_set_host_wait(7))
+
+
+@pytest.mark.parametrize("workers", [1, 2, 5])
+def test_worker_thread_limit_changes_nothing_that_is_decided(workers):
+    rng = np.random.default_rng(8)
+    n, v = 16, 4608
+    rows = (rng.standard_normal((n, v)) * 5).astype(np.float32)
+    rows[:, :8] += 14.0
+    verified = [int(rng.integers(0, v))] + [int(np.argmax(rows[r])) if r % 5 else int(rng.integers(0, v)) for r in range(n - 1)]
+    cfg = dict(temperature=0.7, top_p=0.95)
+    plain, capped = pkg.Sampler(seed=3, **cfg), pkg.Sampler(seed=3, **cfg)
+    capped.set_worker_threads(workers)
+    for _ in range(3):
+        a = pkg.accept_prefix(verified, rows, v, None, plain, 100, [])
+        b = pkg.accept_prefix(verified, rows, v, None, capped, 100, [])
+        assert a == b and plain.draws == capped.draws and plain.rng_state() == capped.rng_state()
