@@ -113,7 +113,11 @@ dfl_status dfl_generate(const dfl_model* m, dfl_session* s, dfl_scratch* sc, dfl
             if (proposal_sampler) dfl_sampler_destroy(proposal_sampler);
             return fail(DFL_ERR_OOM, "generate: pinned row-order buffer");
         }
-        dfl_scratch_set_order_host(sc, sc->pinned_order);
+        const dfl_status os = dfl_scratch_set_order_host(sc, sc->pinned_order);
+        if (os != DFL_OK) {
+            if (proposal_sampler) dfl_sampler_destroy(proposal_sampler);
+            return os;
+        }
         dfl_sampler_set_row_order(sampler, sc->pinned_logits, sc->pinned_order, sc->block_size, V);
     }
     auto is_stop = [&](int32_t t) {

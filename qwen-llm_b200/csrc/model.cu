@@ -921,9 +921,7 @@ dfl_status dfl_packed_verify(const dfl_model* m, dfl_session* s, dfl_scratch* sc
     if (logits_host) cudaMemcpyAsync(logits_host, sc->logits, (size_t)n * m->arch.vocab_size * 4, cudaMemcpyDeviceToHost, s->st);
     if (logits_host && sc->order_host) {
         // the rows' order for the host sampler, produced while the logits travel
-        const uint64_t V = m->arch.vocab_size;
-        if (!sc->order_dev) DFL_CUDA(cudaMalloc(&sc->order_dev, (size_t)sc->block_size * V * 4));
-        if (!sc->sort_scratch) DFL_CUDA(cudaMalloc(&sc->sort_scratch, sort_rows_scratch_bytes((int)sc->block_size, V)));
+        const uint64_t V = m->arch.vocab_size;   // the device buffers exist: dfl_scratch_set_order_host made them
         st = launch_sort_rows_desc(s->st, sc->logits, (int)n, V, V, sc->sort_scratch, sc->order_dev);
         if (st != DFL_OK) { s->poisoned = true; return st; }
         cudaMemcpyAsync(sc->order_host, sc->order_dev, (size_t)n * V * 4, cudaMemcpyDeviceToHost, s->st);
@@ -936,6 +934,22 @@ dfl_status dfl_packed_verify(const dfl_model* m, dfl_session* s, dfl_scratch* sc
 
 dfl_status dfl_scratch_set_order_host(dfl_scratch* sc, uint32_t* order_host) {
     if (!sc) return fail(DFL_ERR_BAD_ARG, "set_order_host: null scratch");
+    sc->order_host = nullptr;
+    if (!order_host) return DFL_OK;
+    if (!sc->order_dev || !sc->sort_scratch) {   // device side of the ordering, made once per scratch and here, where failing is clean
+        DFL_CHECK(use_device(sc->m->device));
+        const uint64_t V = sc->m->arch.vocab_size;
+        if (!sc->order_dev && cudaMalloc(&sc->order_dev, (size_t)sc->block_size * V * 4) != cudaSuccess) {
+            sc->order_dev = nullptr;
+            cudaGetLastError();
+            return fail(DFL_ERR_OOM, "set_order_host: device order buffer");
+        }
+        if (!sc->sort_scratch && cudaMalloc(&sc->sort_scratch, sort_rows_scratch_bytes((int)sc->block_size, V)) != cudaSuccess) {
+            sc->sort_scratch = nullptr;
+            cudaGetLastError();
+            return fail(DFL_ERR_OOM, "set_order_host: sort scratch");
+        }
+    }
     sc->order_host = order_host;
     return DFL_OK;
 }
