@@ -331,7 +331,9 @@ dfl_status dfl_session_restore_snapshot(const dfl_model* m, dfl_session* s, dfl_
 /* When order_host is not NULL, every later dfl_packed_verify on this scratch that returns logits to the host also
  * orders each returned row on the device - token ids by descending logit in the f32 total order, ties by ascending
  * token - and copies the [n][vocab] order to order_host (u32, caller-owned, at least block_size * vocab entries;
- * pinned memory recommended) in the same call.  NULL switches it off. */
+ * pinned memory recommended) in the same call.  NULL switches it off.  The first registration on a scratch allocates
+ * the device side of the ordering (5 x block_size x vocab x 4 bytes) and can fail with DFL_ERR_OOM; nothing is
+ * registered then. */
 dfl_status dfl_scratch_set_order_host(dfl_scratch* sc, uint32_t* order_host);
 /* The same ordering on rows given by the host (host-to-host test entry): order_out [n_rows][vocab]. */
 dfl_status dfl_sort_rows_desc(int32_t device, const float* logits_host, int32_t n_rows, uint64_t vocab,
